@@ -1,0 +1,110 @@
+/* turkce_b200 -- C ABI of the sm_100a matrix-multiplication hot path.
+ *
+ * Plain pointers and sizes only.  Every pointer named d_* is a CUDA device pointer
+ * on the current device; h_* is host memory.  `stream` is a cudaStream_t passed as
+ * void* (NULL = the default stream).  Every function returns 0 on success; on
+ * failure it returns non-zero and tb_last_error() gives the message.  The reference
+ * treats every CUDA error as fatal (cuda/cuda_backend.c:15-34): a C caller keeps that
+ * behaviour by printing tb_last_error() and exiting on a non-zero return.
+ *
+ * Citations name the reference interface each entry point replaces
+ * (paths relative to the reference project).
+ */
+#ifndef TURKCE_B200_H
+#define TURKCE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* GEMM kinds: the reference's GemmKind (model/gpu_train.c:41) */
+#define TB_GEMM_NN 0   /* A [M,K] lda, B [K,N] ldb */
+#define TB_GEMM_NT 1   /* A [M,K] lda, B [N,K] ldb */
+#define TB_GEMM_TN 2   /* A [K,M] lda, B [K,N] ldb */
+
+/* operand precision of the tensor-core product; accumulation is always FP32 */
+#define TB_PREC_BF16 0
+#define TB_PREC_TF32 1
+#define TB_PREC_FP32 2
+
+/* causal structure of batched square attention products (see tb_gemm_bf16) */
+#define TB_CAUSAL_NONE 0
+#define TB_CAUSAL_SKIP_UPPER 1
+#define TB_CAUSAL_K_PREFIX 2
+#define TB_CAUSAL_K_SUFFIX 3
+
+/* ---- library / device ------------------------------------------------------ */
+
+/* cuda_init_on_device + cuda_set_current (cuda/cuda_backend.h:19-40): selects the
+ * device for the calling thread and creates the library's per-device state. */
+int tb_init(int device);
+/* cuda_device_count (cuda/cuda_backend.h:27) */
+int tb_device_count(void);
+const char* tb_last_error(void);
+/* Number of kernels this library has launched on the current device so far. */
+long long tb_launch_count(void);
+/* Waits for `stream` and reports a kernel that gave up on a bounded wait. */
+int tb_check(void* stream);
+/* cuda_shutdown (cuda/cuda_backend.h:33): frees the library's scratch memory. */
+int tb_shutdown(void);
+
+/* cuda_alloc / cuda_free / cuda_h2d / cuda_d2h / cuda_memset_zero / cuda_sync
+ * (cuda/cuda_backend.h:42-65) for C callers that have no other CUDA runtime. */
+int tb_alloc(void** d_ptr, uint64_t bytes);
+int tb_free(void* d_ptr);
+int tb_h2d(void* d_dst, const void* h_src, uint64_t bytes);
+int tb_d2h(void* h_dst, const void* d_src, uint64_t bytes);
+int tb_memset_zero(void* d_ptr, uint64_t bytes);
+int tb_sync(void);
+
+/* ---- GEMM on float32 device matrices (the reference's storage format) ------- */
+
+/* gemm() / bf16_gemm() host helpers and the k_gemm_{nn,nt,tn} / k_bf16_gemm_{nn,nt,tn}
+ * kernels they launch (model/gpu_train.c:45-78; cuda/train_kernels.cu:187-193, :343-467):
+ *   C = alpha * op(A) @ op(B) + beta * C   for `batch` matrices at element strides.
+ * Operands are rounded to `precision` (bf16: round-to-nearest-even, as
+ * cuda/train_kernels.cu:207-212) on the way into the tensor cores. */
+int tb_gemm_f32(int kind, const float* d_A, const float* d_B, float* d_C,
+                int M, int N, int K, int lda, int ldb, int ldc,
+                int batch, int64_t strideA, int64_t strideB, int64_t strideC,
+                float alpha, float beta, int precision, void* stream);
+
+/* bf16_gemm_bias() and k_bf16_gemm_nn_bias (model/gpu_train.c:103-107;
+ * cuda/train_kernels.cu:226-329): C[M,N] = A[M,K] @ B[K,N] + bias[N] (+ residual[M,N]);
+ * a NULL bias or residual is skipped. All matrices contiguous. */
+int tb_gemm_bias_f32(const float* d_A, const float* d_B, const float* d_bias, const float* d_residual,
+                     float* d_C, int M, int N, int K, int precision, void* stream);
+
+/* gpu_matmul() behind node_matmul2d_gpu, and k_matmul (model/gpu_ops.c:118-160;
+ * cuda/kernels.cu:35-65): host matrices in, host matrix out, copies included.
+ * C[M,N] = A[M,K] @ B[K,N], all contiguous row-major float32 in host memory. */
+int tb_matmul_host(const float* h_A, const float* h_B, float* h_C, int M, int K, int N, int precision);
+
+/* ---- GEMM on bf16 device matrices (native format of this library) ----------- */
+
+/* Same product on operands already in bf16 (leading dimensions and batch strides must
+ * be multiples of 8 elements, pointers 16-byte aligned).  Either or both outputs may
+ * be given: d_C32 float32 (beta applies to its previous contents), d_C16 bf16.
+ * bias [N] and residual [M,N] (float32, leading dimension ldr, batch stride strideR)
+ * are optional.  `causal` restricts batched square attention products to the lower
+ * triangle: SKIP_UPPER leaves output tiles wholly above the diagonal unwritten;
+ * K_PREFIX / K_SUFFIX shorten the k range for a lower-triangular A / transposed A.
+ * splits: 0 = chosen by the library; >1 = split-K with fixed-order partial sums
+ * (bitwise reproducible, as the reference requires: cuda/train_kernels.cu:17-20). */
+int tb_gemm_bf16(int kind, const void* d_A, const void* d_B, int M, int N, int K,
+                 int64_t lda, int64_t ldb, int batch, int64_t strideA, int64_t strideB,
+                 float* d_C32, int64_t ldc32, int64_t strideC32,
+                 void* d_C16, int64_t ldc16, int64_t strideC16,
+                 const float* d_bias, const float* d_residual, int64_t ldr, int64_t strideR,
+                 float alpha, float beta, int causal, int splits, int tile_n, void* stream);
+
+/* float32 [rows, cols] (ld_src) -> bf16 [rows, cols] (ld_dst), `batch` matrices. */
+int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld_src, int64_t ld_dst,
+                 int batch, int64_t stride_src, int64_t stride_dst, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURKCE_B200_H */

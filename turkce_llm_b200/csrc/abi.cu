@@ -1,0 +1,176 @@
+// extern "C" entry points declared in include/turkce_b200.h (library, memory and GEMM part).
+#include "../../include/turkce_b200.h"
+#include "common.h"
+
+using namespace tb;
+
+static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+
+extern "C" {
+
+int tb_init(int device) {
+    TB_CUDA(cudaSetDevice(device));
+    DeviceCtx* ctx;
+    return get_ctx(&ctx);
+}
+
+int tb_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+    return n;
+}
+
+const char* tb_last_error(void) { return last_error(); }
+
+long long tb_launch_count(void) {
+    DeviceCtx* ctx;
+    if (get_ctx(&ctx) != 0) return -1;
+    return ctx->launches;
+}
+
+int tb_check(void* stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    return check_device_error(ctx, S(stream));
+}
+
+int tb_shutdown(void) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    TB_CUDA(cudaDeviceSynchronize());
+    if (ctx->scratch) TB_CUDA(cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    return 0;
+}
+
+int tb_alloc(void** d_ptr, uint64_t bytes) { TB_CUDA(cudaMalloc(d_ptr, bytes)); return 0; }
+int tb_free(void* d_ptr) { TB_CUDA(cudaFree(d_ptr)); return 0; }
+int tb_h2d(void* d_dst, const void* h_src, uint64_t bytes) {
+    TB_CUDA(cudaMemcpy(d_dst, h_src, bytes, cudaMemcpyHostToDevice));
+    return 0;
+}
+int tb_d2h(void* h_dst, const void* d_src, uint64_t bytes) {
+    TB_CUDA(cudaMemcpy(h_dst, d_src, bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+int tb_memset_zero(void* d_ptr, uint64_t bytes) { TB_CUDA(cudaMemset(d_ptr, 0, bytes)); return 0; }
+int tb_sync(void) { TB_CUDA(cudaDeviceSynchronize()); return 0; }
+
+int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld_src, int64_t ld_dst,
+                 int batch, int64_t stride_src, int64_t stride_dst, void* stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    return launch_pack_bf16(ctx, d_src, static_cast<bf16*>(d_dst), rows, cols, ld_src, ld_dst, batch, stride_src,
+                            stride_dst, S(stream));
+}
+
+int tb_gemm_bf16(int kind, const void* d_A, const void* d_B, int M, int N, int K,
+                 int64_t lda, int64_t ldb, int batch, int64_t strideA, int64_t strideB,
+                 float* d_C32, int64_t ldc32, int64_t strideC32,
+                 void* d_C16, int64_t ldc16, int64_t strideC16,
+                 const float* d_bias, const float* d_residual, int64_t ldr, int64_t strideR,
+                 float alpha, float beta, int causal, int splits, int tile_n, void* stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    TB_CHECK(kind >= 0 && kind <= 2, "unknown GEMM kind %d", kind);
+    TB_CHECK(causal >= 0 && causal <= 3, "unknown causal mode %d", causal);
+    GemmArgs a;
+    a.kind = static_cast<GemmKind>(kind);
+    a.A = static_cast<const bf16*>(d_A); a.B = static_cast<const bf16*>(d_B);
+    a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldb = ldb;
+    a.batch = batch; a.strideA = strideA; a.strideB = strideB;
+    a.C32 = d_C32; a.ldc32 = ldc32; a.strideC32 = strideC32;
+    a.C16 = static_cast<bf16*>(d_C16); a.ldc16 = ldc16; a.strideC16 = strideC16;
+    a.bias = d_bias; a.residual = d_residual; a.ldr = ldr; a.strideR = strideR;
+    a.alpha = alpha; a.beta = beta;
+    a.causal = static_cast<CausalMode>(causal);
+    a.splits = splits; a.bn = tile_n;
+    return launch_gemm_bf16(ctx, a, S(stream));
+}
+
+// Packs both float32 operands to bf16 in scratch memory, then runs the bf16 GEMM.
+static int gemm_f32_impl(int kind, const float* A, const float* B, float* C, int M, int N, int K,
+                         long long lda, long long ldb, long long ldc, int batch, long long sA, long long sB,
+                         long long sC, float alpha, float beta, const float* bias, const float* residual,
+                         int precision, cudaStream_t stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    TB_CHECK(kind >= 0 && kind <= 2, "unknown GEMM kind %d", kind);
+    TB_CHECK(precision == TB_PREC_BF16, "precision %d is not built yet: only TB_PREC_BF16 runs", precision);
+    TB_CHECK(M > 0 && N > 0 && K > 0 && batch > 0, "GEMM dims must be positive");
+    // stored shapes
+    const int a_rows = (kind == TB_GEMM_TN) ? K : M, a_cols = (kind == TB_GEMM_TN) ? M : K;
+    const int b_rows = (kind == TB_GEMM_NT) ? N : K, b_cols = (kind == TB_GEMM_NT) ? K : N;
+    const long long a_ld = round_up(a_cols, 8), b_ld = round_up(b_cols, 8);
+    const long long a_stride = (long long)a_rows * a_ld, b_stride = (long long)b_rows * b_ld;
+    const size_t a_bytes = round_up((size_t)a_stride * batch * 2, 256);
+    const size_t b_bytes = round_up((size_t)b_stride * batch * 2, 256);
+
+    GemmArgs g;
+    g.kind = static_cast<GemmKind>(kind);
+    g.M = M; g.N = N; g.K = K; g.lda = a_ld; g.ldb = b_ld;
+    g.batch = batch; g.strideA = a_stride; g.strideB = b_stride;
+    g.C32 = C; g.ldc32 = ldc; g.strideC32 = sC;
+    g.bias = bias; g.residual = residual; g.ldr = ldc; g.strideR = sC;
+    g.alpha = alpha; g.beta = beta;
+    const int bn = (N <= 64) ? 64 : 128;
+    g.bn = 0;
+    int splits = residual ? 1 : choose_splits(ctx, g, bn);
+    g.splits = splits;
+    const size_t ws_floats = splits > 1 ? (size_t)splits * batch * M * N : 0;
+    TB_TRY(ensure_scratch(ctx, a_bytes + b_bytes + ws_floats * sizeof(float)));
+    bf16* pa = static_cast<bf16*>(ctx->scratch);
+    bf16* pb = reinterpret_cast<bf16*>(static_cast<char*>(ctx->scratch) + a_bytes);
+    float* ws = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + a_bytes + b_bytes);
+    TB_TRY(launch_pack_bf16(ctx, A, pa, a_rows, a_cols, lda, a_ld, batch, sA, a_stride, stream));
+    TB_TRY(launch_pack_bf16(ctx, B, pb, b_rows, b_cols, ldb, b_ld, batch, sB, b_stride, stream));
+    g.A = pa; g.B = pb;
+    return launch_gemm_bf16_ws(ctx, g, ws, ws_floats, stream);
+}
+
+int tb_gemm_f32(int kind, const float* d_A, const float* d_B, float* d_C,
+                int M, int N, int K, int lda, int ldb, int ldc,
+                int batch, int64_t strideA, int64_t strideB, int64_t strideC,
+                float alpha, float beta, int precision, void* stream) {
+    return gemm_f32_impl(kind, d_A, d_B, d_C, M, N, K, lda, ldb, ldc, batch, strideA, strideB, strideC, alpha, beta,
+                         nullptr, nullptr, precision, S(stream));
+}
+
+int tb_gemm_bias_f32(const float* d_A, const float* d_B, const float* d_bias, const float* d_residual,
+                     float* d_C, int M, int N, int K, int precision, void* stream) {
+    return gemm_f32_impl(TB_GEMM_NN, d_A, d_B, d_C, M, N, K, K, N, N, 1, 0, 0, 0, 1.0f, 0.0f, d_bias, d_residual,
+                         precision, S(stream));
+}
+
+int tb_matmul_host(const float* h_A, const float* h_B, float* h_C, int M, int K, int N, int precision) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    TB_CHECK(M > 0 && N > 0 && K > 0, "matmul dims must be positive");
+    const size_t na = (size_t)M * K, nb = (size_t)K * N, nc = (size_t)M * N;
+    float *dA = nullptr, *dB = nullptr, *dC = nullptr;
+    TB_CUDA(cudaMalloc(&dA, na * 4));
+    TB_CUDA(cudaMalloc(&dB, nb * 4));
+    TB_CUDA(cudaMalloc(&dC, nc * 4));
+    int rc = 0;
+    do {
+        if (cudaMemcpy(dA, h_A, na * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(dB, h_B, nb * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+            set_error("tb_matmul_host: host to device copy failed");
+            rc = -1; break;
+        }
+        rc = gemm_f32_impl(TB_GEMM_NN, dA, dB, dC, M, N, K, K, N, N, 1, 0, 0, 0, 1.0f, 0.0f, nullptr, nullptr,
+                           precision, nullptr);
+        if (rc) break;
+        rc = check_device_error(ctx, nullptr);
+        if (rc) break;
+        if (cudaMemcpy(h_C, dC, nc * 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+            set_error("tb_matmul_host: device to host copy failed");
+            rc = -1;
+        }
+    } while (0);
+    cudaFree(dA); cudaFree(dB); cudaFree(dC);
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,101 @@
+// Shared host-side declarations of the library: error reporting, the per-device
+// context (scratch memory, error word, driver entry points) and the launchers the
+// C-ABI layer and the trainer call.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+namespace tb {
+
+typedef __nv_bfloat16 bf16;
+
+// ---- errors: every entry point returns 0 on success; the message of the last
+// failure on the calling thread is kept for tb_last_error().
+void set_error(const char* fmt, ...);
+const char* last_error();
+
+#define TB_CUDA(expr)                                                                        \
+    do {                                                                                     \
+        cudaError_t _e = (expr);                                                             \
+        if (_e != cudaSuccess) {                                                             \
+            tb::set_error("[CUDA] %s -> %s: %s (%s:%d)", #expr, cudaGetErrorName(_e),        \
+                          cudaGetErrorString(_e), __FILE__, __LINE__);                       \
+            return -1;                                                                       \
+        }                                                                                    \
+    } while (0)
+
+#define TB_CHECK(cond, ...)                  \
+    do {                                     \
+        if (!(cond)) {                       \
+            tb::set_error(__VA_ARGS__);      \
+            return -2;                       \
+        }                                    \
+    } while (0)
+
+#define TB_TRY(expr)              \
+    do {                          \
+        int _r = (expr);          \
+        if (_r != 0) return _r;   \
+    } while (0)
+
+// ---- per-device context
+struct DeviceCtx {
+    int device = -1;
+    int sm_count = 0;
+    int* d_err = nullptr;          // device error word written by kernels whose bounded waits ran out
+    void* scratch = nullptr;       // growable scratch (operand packing, split-K partials)
+    size_t scratch_bytes = 0;
+    long long launches = 0;        // kernels launched by this library on this device
+};
+
+// Returns the context of the current device, creating it on first use.
+int get_ctx(DeviceCtx** out);
+// Makes sure the scratch buffer holds at least `bytes`; may reallocate (synchronises).
+int ensure_scratch(DeviceCtx* ctx, size_t bytes);
+// Reads and clears the device error word (synchronises the stream first).
+int check_device_error(DeviceCtx* ctx, cudaStream_t stream);
+
+// ---- GEMM on BF16 operands (gemm_tcgen05.cu)
+enum GemmKind { GEMM_NN = 0, GEMM_NT = 1, GEMM_TN = 2 };
+enum CausalMode {
+    CAUSAL_NONE = 0,
+    CAUSAL_SKIP_UPPER = 1,   // square score-shaped output: tiles wholly above the diagonal are not computed
+    CAUSAL_K_PREFIX = 2,     // A is lower-triangular [M,K]: k runs only to the end of the tile's rows
+    CAUSAL_K_SUFFIX = 3      // op(A) = A^T of a lower-triangular matrix: k starts at the tile's first row
+};
+
+struct GemmArgs {
+    GemmKind kind = GEMM_NN;
+    const bf16* A = nullptr;   // NN/NT: [M,K] lda   TN: [K,M] lda
+    const bf16* B = nullptr;   // NN/TN: [K,N] ldb   NT: [N,K] ldb
+    int M = 0, N = 0, K = 0;
+    long long lda = 0, ldb = 0;
+    int batch = 1;
+    long long strideA = 0, strideB = 0;     // elements
+    // outputs: either or both
+    float* C32 = nullptr; long long ldc32 = 0, strideC32 = 0;
+    bf16* C16 = nullptr;  long long ldc16 = 0, strideC16 = 0;
+    const float* bias = nullptr;            // [N]
+    const float* residual = nullptr; long long ldr = 0, strideR = 0;   // [M,N] fp32
+    float alpha = 1.0f, beta = 0.0f;        // beta applies to the previous contents of C32
+    CausalMode causal = CAUSAL_NONE;
+    int splits = 0;                         // 0 = choose; >1 uses scratch for fixed-order partial sums
+    int bn = 0;                             // 0 = choose tile width (64 or 128)
+};
+
+int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream);
+// split-K with caller-provided partial-sum storage (needs splits*batch*M*N floats)
+int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, size_t workspace_floats,
+                        cudaStream_t stream);
+int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn);
+
+// ---- operand packing (pack.cu): float32 [rows, cols] (ld) -> bf16 [rows, cols] (ld_out), batched
+int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int cols, long long ld_src,
+                     long long ld_dst, int batch, long long stride_src, long long stride_dst, cudaStream_t stream);
+
+static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
+
+}  // namespace tb

@@ -1,0 +1,80 @@
+// Per-device library state and error reporting.
+//
+// The reference aborts the process on any CUDA error (cuda/cuda_backend.c:15-34).  A shared
+// library cannot do that to its host, so every entry point returns a code and keeps the
+// message; a C caller that wants the reference's behaviour prints tb_last_error() and exits.
+#include "common.h"
+
+#include <cstdarg>
+#include <cstring>
+#include <mutex>
+
+namespace tb {
+
+static thread_local char g_err[1024] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+const char* last_error() { return g_err; }
+
+static DeviceCtx g_ctx[64];
+static std::mutex g_ctx_mutex;
+
+int get_ctx(DeviceCtx** out) {
+    int dev = -1;
+    TB_CUDA(cudaGetDevice(&dev));
+    TB_CHECK(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+    DeviceCtx* c = &g_ctx[dev];
+    if (c->device != dev) {
+        std::lock_guard<std::mutex> lock(g_ctx_mutex);
+        if (c->device != dev) {
+            cudaDeviceProp prop;
+            TB_CUDA(cudaGetDeviceProperties(&prop, dev));
+            TB_CHECK(prop.major == 10, "this library is built for sm_100a only; device %d is sm_%d%d", dev, prop.major,
+                     prop.minor);
+            c->sm_count = prop.multiProcessorCount;
+            TB_CUDA(cudaMalloc(&c->d_err, sizeof(int)));
+            TB_CUDA(cudaMemset(c->d_err, 0, sizeof(int)));
+            c->scratch = nullptr;
+            c->scratch_bytes = 0;
+            c->launches = 0;
+            c->device = dev;
+        }
+    }
+    *out = c;
+    return 0;
+}
+
+int ensure_scratch(DeviceCtx* ctx, size_t bytes) {
+    if (bytes <= ctx->scratch_bytes) return 0;
+    // growing: earlier work may still be reading the old buffer
+    TB_CUDA(cudaDeviceSynchronize());
+    if (ctx->scratch) TB_CUDA(cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    want = (want + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+    TB_CUDA(cudaMalloc(&ctx->scratch, want));
+    ctx->scratch_bytes = want;
+    return 0;
+}
+
+int check_device_error(DeviceCtx* ctx, cudaStream_t stream) {
+    int h = 0;
+    TB_CUDA(cudaStreamSynchronize(stream));
+    TB_CUDA(cudaMemcpy(&h, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (h != 0) {
+        cudaMemset(ctx->d_err, 0, sizeof(int));
+        const char* who = h == 1 ? "TMA producer" : h == 2 ? "MMA issuer" : h == 3 ? "epilogue" : "kernel";
+        set_error("a kernel gave up on a bounded wait (%s, code %d); its output is invalid", who, h);
+        return -3;
+    }
+    return 0;
+}
+
+}  // namespace tb

@@ -1,0 +1,501 @@
+// Persistent TMA + tcgen05 GEMM for sm_100a on BF16 operands with FP32 accumulation in TMEM.
+//
+//   C = alpha * op(A) * op(B) [+ bias] [+ residual] [+ beta * C]
+//
+// replaces the reference's gemm_body / bf16_gemm_body / k_bf16_gemm_nn_bias
+// (cuda/train_kernels.cu:110-193, :226-329, :343-467).  One kernel covers NN, NT and TN:
+// a transposed operand is not transposed in memory, it is described to the tensor core
+// as an MN-major shared-memory tile instead of a K-major one.
+//
+// CTA = 6 warps, one CTA per SM, tiles 128 x BN handed out round-robin:
+//   warp 0     TMA producer: 64-wide K slices of A and B into a ring of 128B-swizzled stages
+//   warp 1     owns TMEM (2 accumulators of BN columns) and issues tcgen05.mma (one lane)
+//   warps 2-5  epilogue: tcgen05.ld -> registers -> per-warp shared staging -> coalesced
+//              global stores with bias / residual / beta*C / bf16 copy fused
+// The two accumulators let the epilogue of tile i overlap the main loop of tile i+1,
+// which matters because K is only 384..1024 here (6..16 slices per tile).
+//
+// Split-K (weight gradients: small M,N, K = tokens) writes one partial tile per split into
+// scratch memory; reduce_splits_kernel then adds the partials in split order, so the result
+// does not depend on scheduling (the reference forbids atomics: train_kernels.cu:17-20).
+#include "common.h"
+#include "ptx.cuh"
+
+namespace tb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;              // bf16 elements = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int STAGE_LD = 36;        // floats per staging row (32 + 4 pad: conflict-free float4 access)
+
+template <int BN> struct GemmCfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 128) ? 6 : 8;
+    static constexpr int STAGING_BYTES = 4 * 32 * STAGE_LD * 4;
+    static constexpr int BAR_BYTES = 512;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;   // 128 or 256: powers of two >= 32
+};
+
+struct GemmParams {
+    int M, N, K;
+    int batch, splits;
+    int mt, nt;                 // tiles along M, N
+    int a_mn, b_mn;             // 1 = operand tile is MN-major (stored transposed)
+    int causal;
+    float* C32; long long ldc32, strideC32;
+    bf16* C16; long long ldc16, strideC16;
+    const float* bias;
+    const float* residual; long long ldr, strideR;
+    float alpha, beta;
+    int vec32, vec16, vecr;     // 16-byte (8-byte for bf16) vector access allowed
+    int* err;
+};
+
+struct TileCoord { int z, s, m0, n0, kb0, kb1; bool skip; };
+
+template <int BN>
+__device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t) {
+    TileCoord c;
+    const int n_idx = t % p.nt; t /= p.nt;
+    const int m_idx = t % p.mt; t /= p.mt;
+    c.s = t % p.splits;
+    c.z = t / p.splits;
+    c.m0 = m_idx * BM;
+    c.n0 = n_idx * BN;
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int kb_per = (kb_total + p.splits - 1) / p.splits;
+    c.kb0 = c.s * kb_per;
+    c.kb1 = min(kb_total, c.kb0 + kb_per);
+    c.skip = false;
+    if (p.causal == CAUSAL_SKIP_UPPER) {
+        c.skip = c.n0 > c.m0 + BM - 1;
+    } else if (p.causal == CAUSAL_K_PREFIX) {
+        c.kb1 = min(c.kb1, (c.m0 + BM + BK - 1) / BK);
+    } else if (p.causal == CAUSAL_K_SUFFIX) {
+        c.kb0 = max(c.kb0, c.m0 / BK);
+    }
+    if (c.kb1 < c.kb0) c.kb1 = c.kb0;   // empty range: the accumulator is treated as zero
+    return c;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+
+    uint8_t* stage_base = smem;
+    float* staging = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::STAGING_BYTES);
+    uint64_t* full_bar = bars;                    // [STAGES]
+    uint64_t* empty_bar = bars + STAGES;          // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;       // [2]
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.batch * p.splits * p.mt * p.nt;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmB);
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const TileCoord c = tile_of<BN>(p, t);
+                if (c.skip) continue;
+                for (int kb = c.kb0; kb < c.kb1; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    uint8_t* sA = stage_base + stage * Cfg::STAGE_BYTES;
+                    uint8_t* sB = sA + Cfg::A_BYTES;
+                    mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                    if (!p.a_mn) {
+                        tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, c.m0, c.z);
+                    } else {
+                        tma_load_3d(sA, &tmA, &full_bar[stage], c.m0, kb * BK, c.z);
+                        tma_load_3d(sA + 64 * BK * 2, &tmA, &full_bar[stage], c.m0 + 64, kb * BK, c.z);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, c.n0, c.z);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_3d(sB + j * 64 * BK * 2, &tmB, &full_bar[stage], c.n0 + j * 64, kb * BK, c.z);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 1); }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(1u, (uint32_t)p.a_mn, (uint32_t)p.b_mn, BM, BN);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const TileCoord c = tile_of<BN>(p, t);
+                if (c.skip) continue;
+                const int buf = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = c.kb0; kb < c.kb1; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(stage_base + stage * Cfg::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t a_desc = p.a_mn ? umma_desc_sw128(a_addr + k * 2048, 64 * BK * 2, 1024)
+                                                       : umma_desc_sw128(a_addr + k * 32, 16, 1024);
+                        const uint64_t b_desc = p.b_mn ? umma_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
+                                                       : umma_desc_sw128(b_addr + k * 32, 16, 1024);
+                        umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[buf]);          // accumulator complete
+                ++it;
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 2); }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int q = warp & 3;                        // TMEM lane quarter this warp may read
+        float* stg = staging + (warp - 2) * 32 * STAGE_LD;
+        const int r_sub = lane >> 3;                   // 0..3
+        const int cg = lane & 7;                       // 0..7 -> columns 4*cg..4*cg+3
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const TileCoord c = tile_of<BN>(p, t);
+            if (c.skip) continue;
+            const int buf = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const bool have_acc = c.kb1 > c.kb0;
+            if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const long long zc = (long long)c.z * p.splits + c.s;
+            float* C32 = p.C32 ? p.C32 + zc * p.strideC32 : nullptr;
+            bf16* C16 = p.C16 ? p.C16 + zc * p.strideC16 : nullptr;
+            const float* R = p.residual ? p.residual + (long long)c.z * p.strideR : nullptr;
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                uint32_t v[32];
+                if (have_acc) {
+                    tmem_ld32(t_row + (uint32_t)(ch * 32), v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
+                float* srow = stg + lane * STAGE_LD;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float4 f;
+                    f.x = __uint_as_float(v[4 * j + 0]); f.y = __uint_as_float(v[4 * j + 1]);
+                    f.z = __uint_as_float(v[4 * j + 2]); f.w = __uint_as_float(v[4 * j + 3]);
+                    *reinterpret_cast<float4*>(srow + 4 * j) = f;
+                }
+                __syncwarp();
+                const int gn = c.n0 + ch * 32 + 4 * cg;
+                float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+                if (p.bias) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) if (gn + e < p.N) bias4[e] = p.bias[gn + e];
+                }
+#pragma unroll 2
+                for (int itr = 0; itr < 8; ++itr) {
+                    const int row = itr * 4 + r_sub;
+                    const int gm = c.m0 + q * 32 + row;
+                    if (gm >= p.M || gn >= p.N) continue;
+                    const float4 x = *reinterpret_cast<const float4*>(stg + row * STAGE_LD + 4 * cg);
+                    float o[4] = {x.x * p.alpha + bias4[0], x.y * p.alpha + bias4[1],
+                                  x.z * p.alpha + bias4[2], x.w * p.alpha + bias4[3]};
+                    const bool full4 = gn + 3 < p.N;
+                    if (R) {
+                        const float* rp = R + (long long)gm * p.ldr + gn;
+                        if (full4 && p.vecr) {
+                            const float4 r4 = *reinterpret_cast<const float4*>(rp);
+                            o[0] += r4.x; o[1] += r4.y; o[2] += r4.z; o[3] += r4.w;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) if (gn + e < p.N) o[e] += rp[e];
+                        }
+                    }
+                    if (C32) {
+                        float* cp = C32 + (long long)gm * p.ldc32 + gn;
+                        if (full4 && p.vec32) {
+                            if (p.beta != 0.0f) {
+                                const float4 c4 = *reinterpret_cast<const float4*>(cp);
+                                o[0] += p.beta * c4.x; o[1] += p.beta * c4.y; o[2] += p.beta * c4.z; o[3] += p.beta * c4.w;
+                            }
+                            *reinterpret_cast<float4*>(cp) = make_float4(o[0], o[1], o[2], o[3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) if (gn + e < p.N) {
+                                if (p.beta != 0.0f) o[e] += p.beta * cp[e];
+                                cp[e] = o[e];
+                            }
+                        }
+                    }
+                    if (C16) {
+                        bf16* hp = C16 + (long long)gm * p.ldc16 + gn;
+                        if (full4 && p.vec16) {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]);
+                            __nv_bfloat162 hi = __floats2bfloat162_rn(o[2], o[3]);
+                            uint2 pk;
+                            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(hp) = pk;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) if (gn + e < p.N) hp[e] = __float2bfloat16_rn(o[e]);
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            ++it;
+        }
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 3); }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    __syncwarp();
+    if (*abort_flag) {
+        // a bounded wait ran out: give copies in flight time to land before the CTA's
+        // shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// Adds split-K partials in split order: out = sum_s part[s] (+ beta * out), float4-wide.
+__global__ void reduce_splits_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                     bf16* __restrict__ out16, int M, int N, long long ldc32, long long ldc16,
+                                     int splits, long long strideC32, long long strideC16, float beta,
+                                     const float* __restrict__ bias) {
+    const long long per = (long long)M * N;
+    const int z = blockIdx.y;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / N), cidx = (int)(i % N);
+        const float* src = part + ((long long)z * splits) * per + i;
+        float s = src[0];
+        for (int k = 1; k < splits; ++k) s += src[(long long)k * per];
+        if (bias) s += bias[cidx];
+        if (out) {
+            float* o = out + (long long)z * strideC32 + (long long)r * ldc32 + cidx;
+            if (beta != 0.0f) s += beta * *o;
+            *o = s;
+        }
+        if (out16) out16[(long long)z * strideC16 + (long long)r * ldc16 + cidx] = __float2bfloat16_rn(s);
+    }
+}
+
+// ===================================================================== host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 3-D view (inner, rows, batch) of a bf16 matrix with a 64-element (128-byte) inner box.
+static int make_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld,
+                    int batch, long long batch_stride, int box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    TB_CHECK(enc != nullptr, "cuTensorMapEncodeTiled entry point not available");
+    TB_CHECK((reinterpret_cast<uintptr_t>(ptr) & 15u) == 0, "GEMM operand must be 16-byte aligned");
+    TB_CHECK((ld * 2) % 16 == 0, "GEMM operand leading dimension must be a multiple of 8 bf16 elements (got %lld)", ld);
+    TB_CHECK(batch == 1 || (batch_stride * 2) % 16 == 0, "GEMM batch stride must be a multiple of 8 elements");
+    cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t bs = batch > 1 ? (cuuint64_t)batch_stride * 2 : (cuuint64_t)rows * (cuuint64_t)ld * 2;
+    if (bs == 0) bs = 16;
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, bs};
+    cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<bf16*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (inner=%lld rows=%lld ld=%lld batch=%d)",
+             (int)r, inner, rows, ld, batch);
+    return 0;
+}
+
+static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
+    if (a.bn == 64 || a.bn == 128) return a.bn;
+    if (a.N <= 64) return 64;
+    // time ~ waves * tile width; the narrow tile pays ~15% for re-reading A
+    const long long mt = (a.M + BM - 1) / BM;
+    const long long t128 = mt * ((a.N + 127) / 128) * a.batch;
+    const long long t64 = mt * ((a.N + 63) / 64) * a.batch;
+    const long long w128 = (t128 + ctx->sm_count - 1) / ctx->sm_count;
+    const long long w64 = (t64 + ctx->sm_count - 1) / ctx->sm_count;
+    return (double)w64 * 64.0 * 1.15 < (double)w128 * 128.0 ? 64 : 128;
+}
+
+int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
+    if (a.causal != CAUSAL_NONE) return 1;
+    const long long tiles = (long long)((a.M + BM - 1) / BM) * ((a.N + bn - 1) / bn) * a.batch;
+    const int kb_total = (a.K + BK - 1) / BK;
+    if (tiles * 2 > ctx->sm_count || kb_total < 16) return 1;
+    int s = (int)(ctx->sm_count / tiles);
+    if (s > kb_total / 4) s = kb_total / 4;     // at least 4 K slices per split
+    if (s < 1) s = 1;
+    const int kb_per = (kb_total + s - 1) / s;
+    return (kb_total + kb_per - 1) / kb_per;     // no empty split
+}
+
+template <int BN>
+static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, const CUtensorMap& tmA,
+                       const CUtensorMap& tmB, cudaStream_t stream) {
+    using Cfg = GemmCfg<BN>;
+    static bool attr_set[64] = {false};
+    if (!attr_set[ctx->device & 63]) {
+        TB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::SMEM_BYTES));
+        attr_set[ctx->device & 63] = true;
+    }
+    const long long total = (long long)p.batch * p.splits * p.mt * p.nt;
+    int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+    if (grid < 1) grid = 1;
+    gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    TB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    (void)a;
+    return 0;
+}
+
+static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, float* ws, cudaStream_t stream) {
+    TB_CHECK(a.M > 0 && a.N > 0 && a.K > 0 && a.batch > 0, "GEMM dims must be positive (M=%d N=%d K=%d batch=%d)",
+             a.M, a.N, a.K, a.batch);
+    TB_CHECK(a.A && a.B && (a.C32 || a.C16), "GEMM needs A, B and at least one output");
+    const int a_mn = (a.kind == GEMM_TN) ? 1 : 0;
+    const int b_mn = (a.kind == GEMM_NT) ? 0 : 1;
+    CUtensorMap tmA, tmB;
+    if (!a_mn) TB_TRY(make_map(&tmA, a.A, a.K, a.M, a.lda, a.batch, a.strideA, BM));
+    else       TB_TRY(make_map(&tmA, a.A, a.M, a.K, a.lda, a.batch, a.strideA, BK));
+    if (!b_mn) TB_TRY(make_map(&tmB, a.B, a.K, a.N, a.ldb, a.batch, a.strideB, bn));
+    else       TB_TRY(make_map(&tmB, a.B, a.N, a.K, a.ldb, a.batch, a.strideB, BK));
+
+    GemmParams p;
+    p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch; p.splits = splits;
+    p.mt = (a.M + BM - 1) / BM; p.nt = (a.N + bn - 1) / bn;
+    p.a_mn = a_mn; p.b_mn = b_mn; p.causal = (int)a.causal;
+    p.err = ctx->d_err;
+    if (splits > 1) {
+        // partial tiles, one [M,N] slab per (batch, split); everything else happens in the reduction
+        p.C32 = ws; p.ldc32 = a.N; p.strideC32 = (long long)a.M * a.N;
+        p.C16 = nullptr; p.ldc16 = 0; p.strideC16 = 0;
+        p.bias = nullptr; p.residual = nullptr; p.ldr = 0; p.strideR = 0;
+        p.alpha = a.alpha; p.beta = 0.0f;
+    } else {
+        p.C32 = a.C32; p.ldc32 = a.ldc32; p.strideC32 = a.strideC32;
+        p.C16 = a.C16; p.ldc16 = a.ldc16; p.strideC16 = a.strideC16;
+        p.bias = a.bias; p.residual = a.residual; p.ldr = a.ldr; p.strideR = a.strideR;
+        p.alpha = a.alpha; p.beta = a.beta;
+    }
+    p.vec32 = p.C32 && (reinterpret_cast<uintptr_t>(p.C32) % 16 == 0) && p.ldc32 % 4 == 0 && p.strideC32 % 4 == 0;
+    p.vec16 = p.C16 && (reinterpret_cast<uintptr_t>(p.C16) % 8 == 0) && p.ldc16 % 4 == 0 && p.strideC16 % 4 == 0;
+    p.vecr = p.residual && (reinterpret_cast<uintptr_t>(p.residual) % 16 == 0) && p.ldr % 4 == 0 && p.strideR % 4 == 0;
+
+    if (bn == 64) TB_TRY(launch_impl<64>(ctx, a, p, tmA, tmB, stream));
+    else          TB_TRY(launch_impl<128>(ctx, a, p, tmA, tmB, stream));
+
+    if (splits > 1) {
+        TB_CHECK(a.residual == nullptr, "split-K GEMM does not take a residual operand");
+        const long long per = (long long)a.M * a.N;
+        int blocks = (int)((per + 255) / 256);
+        if (blocks > 4 * ctx->sm_count) blocks = 4 * ctx->sm_count;
+        dim3 grid(blocks, a.batch);
+        reduce_splits_kernel<<<grid, 256, 0, stream>>>(ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits,
+                                                       a.strideC32, a.strideC16, a.beta, a.bias);
+        TB_CUDA(cudaGetLastError());
+        ctx->launches++;
+    }
+    return 0;
+}
+
+int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream) {
+    const int bn = pick_bn(ctx, a);
+    int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
+    if (a.residual) splits = 1;
+    float* ws = nullptr;
+    if (splits > 1) {
+        const size_t need = (size_t)splits * a.batch * a.M * a.N * sizeof(float);
+        TB_TRY(ensure_scratch(ctx, need));
+        ws = static_cast<float*>(ctx->scratch);
+    }
+    return launch_core(ctx, a, bn, splits, ws, stream);
+}
+
+int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, size_t workspace_floats,
+                        cudaStream_t stream) {
+    const int bn = pick_bn(ctx, a);
+    int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
+    if (a.residual) splits = 1;
+    if (splits > 1) {
+        const size_t need = (size_t)splits * a.batch * a.M * a.N;
+        TB_CHECK(workspace != nullptr && workspace_floats >= need,
+                 "split-K workspace too small: need %zu floats, have %zu", need, workspace_floats);
+    }
+    return launch_core(ctx, a, bn, splits, workspace, stream);
+}
+
+}  // namespace tb

@@ -1,0 +1,62 @@
+// float32 -> bf16 operand packing for callers that keep their matrices in float32, as the
+// reference does (its kernels convert while staging tiles: cuda/train_kernels.cu:256-263).
+// Rounding is round-to-nearest-even, the same as the reference's f32_to_bf16
+// (cuda/train_kernels.cu:207-212) on every finite input.
+//
+// The packed copy gets a leading dimension that is a multiple of 8 elements so that TMA can
+// address it whatever the source's leading dimension was (the 31,769-column logits included).
+#include "common.h"
+
+namespace tb {
+
+__global__ void pack_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst, int rows, int cols,
+                                 long long ld_src, long long ld_dst, long long stride_src, long long stride_dst,
+                                 int vec) {
+    const int z = blockIdx.z;
+    const float* s = src + (long long)z * stride_src;
+    bf16* d = dst + (long long)z * stride_dst;
+    if (vec) {
+        const int c4 = cols >> 2;
+        const long long total = (long long)rows * c4;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+             i += (long long)gridDim.x * blockDim.x) {
+            const long long r = i / c4;
+            const int c = (int)(i % c4) << 2;
+            const float4 v = *reinterpret_cast<const float4*>(s + r * ld_src + c);
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(d + r * ld_dst + c) = pk;
+        }
+    } else {
+        const long long total = (long long)rows * cols;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+             i += (long long)gridDim.x * blockDim.x) {
+            const long long r = i / cols;
+            const int c = (int)(i % cols);
+            d[r * ld_dst + c] = __float2bfloat16_rn(s[r * ld_src + c]);
+        }
+    }
+}
+
+int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int cols, long long ld_src,
+                     long long ld_dst, int batch, long long stride_src, long long stride_dst, cudaStream_t stream) {
+    TB_CHECK(rows > 0 && cols > 0 && batch > 0, "pack: empty matrix");
+    const int vec = (cols % 4 == 0) && (ld_src % 4 == 0) && (ld_dst % 4 == 0) && (stride_src % 4 == 0) &&
+                    (stride_dst % 4 == 0) && (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
+                    (reinterpret_cast<uintptr_t>(dst) % 8 == 0);
+    const long long work = (long long)rows * (vec ? cols / 4 : cols);
+    long long blocks = (work + 255) / 256;
+    const long long cap = 8LL * ctx->sm_count;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    dim3 grid((unsigned)blocks, 1, (unsigned)batch);
+    pack_bf16_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst, vec);
+    TB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return 0;
+}
+
+}  // namespace tb

@@ -1,0 +1,118 @@
+"""ctypes binding of the C ABI in include/turkce_b200.h.
+
+There is no fallback: if libturkce_b200.so is missing or a call fails, an exception is raised.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libturkce_b200.so")
+
+NN, NT, TN = 0, 1, 2
+PREC_BF16, PREC_TF32, PREC_FP32 = 0, 1, 2
+CAUSAL_NONE, CAUSAL_SKIP_UPPER, CAUSAL_K_PREFIX, CAUSAL_K_SUFFIX = 0, 1, 2, 3
+
+_vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+# name -> (restype, argtypes); every symbol include/turkce_b200.h declares is listed here
+SIGNATURES = {
+    "tb_init": (_i, [_i]),
+    "tb_device_count": (_i, []),
+    "tb_last_error": (C.c_char_p, []),
+    "tb_launch_count": (C.c_longlong, []),
+    "tb_check": (_i, [_vp]),
+    "tb_shutdown": (_i, []),
+    "tb_alloc": (_i, [C.POINTER(_vp), C.c_uint64]),
+    "tb_free": (_i, [_vp]),
+    "tb_h2d": (_i, [_vp, _vp, C.c_uint64]),
+    "tb_d2h": (_i, [_vp, _vp, C.c_uint64]),
+    "tb_memset_zero": (_i, [_vp, C.c_uint64]),
+    "tb_sync": (_i, []),
+    "tb_gemm_f32": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _f, _f, _i, _vp]),
+    "tb_gemm_bias_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "tb_matmul_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
+    "tb_gemm_bf16": (_i, [_i, _vp, _vp, _i, _i, _i, _i64, _i64, _i, _i64, _i64,
+                          _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _i64,
+                          _f, _f, _i, _i, _i, _vp]),
+    "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
+}
+
+_lib = None
+
+
+class TbError(RuntimeError):
+    pass
+
+
+def load():
+    """Loads the shared library (once) and declares every entry point."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise TbError("%s is missing: run `python -m turkce_llm_b200.build` (there is no CPU fallback)" % LIB_PATH)
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise TbError(load().tb_last_error().decode("utf-8", "replace"))
+
+
+def _ptr(t):
+    """Device/host pointer of a torch tensor or numpy array, or None."""
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        return t.data_ptr()
+    return t.ctypes.data
+
+
+def _stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def init(device=0):
+    check(load().tb_init(int(device)))
+
+
+def sync_check():
+    """Waits for the current stream and raises if a kernel reported a failed bounded wait."""
+    check(load().tb_check(_stream()))
+
+
+def launch_count():
+    return int(load().tb_launch_count())
+
+
+def gemm_f32(kind, A, B, C_out, M, N, K, lda, ldb, ldc, batch=1, sA=0, sB=0, sC=0, alpha=1.0, beta=0.0,
+             precision=PREC_BF16):
+    check(load().tb_gemm_f32(kind, _ptr(A), _ptr(B), _ptr(C_out), M, N, K, lda, ldb, ldc, batch, sA, sB, sC,
+                             alpha, beta, precision, _stream()))
+
+
+def gemm_bias_f32(A, B, bias, residual, C_out, M, N, K, precision=PREC_BF16):
+    check(load().tb_gemm_bias_f32(_ptr(A), _ptr(B), _ptr(bias), _ptr(residual), _ptr(C_out), M, N, K, precision,
+                                  _stream()))
+
+
+def matmul_host(hA, hB, hC, M, K, N, precision=PREC_BF16):
+    check(load().tb_matmul_host(_ptr(hA), _ptr(hB), _ptr(hC), M, K, N, precision))
+
+
+def gemm_bf16(kind, A, B, M, N, K, lda, ldb, batch=1, sA=0, sB=0, C32=None, ldc32=0, sC32=0, C16=None, ldc16=0,
+              sC16=0, bias=None, residual=None, ldr=0, sR=0, alpha=1.0, beta=0.0, causal=CAUSAL_NONE, splits=0,
+              tile_n=0):
+    check(load().tb_gemm_bf16(kind, _ptr(A), _ptr(B), M, N, K, lda, ldb, batch, sA, sB,
+                              _ptr(C32), ldc32, sC32, _ptr(C16), ldc16, sC16, _ptr(bias), _ptr(residual), ldr, sR,
+                              alpha, beta, causal, splits, tile_n, _stream()))
+
+
+def pack_bf16(src, dst, rows, cols, ld_src, ld_dst, batch=1, s_src=0, s_dst=0):
+    check(load().tb_pack_bf16(_ptr(src), _ptr(dst), rows, cols, ld_src, ld_dst, batch, s_src, s_dst, _stream()))
