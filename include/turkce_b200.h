@@ -104,6 +104,64 @@ int tb_gemm_bf16(int kind, const void* d_A, const void* d_B, int M, int N, int K
 int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld_src, int64_t ld_dst,
                  int batch, int64_t stride_src, int64_t stride_dst, void* stream);
 
+/* ---- GPU-resident trainer ---------------------------------------------------- */
+
+/* GpuTrainer (model/gpu_train.h:51-80).  Parameters, gradients and Adam state are flat
+ * float32 buffers in lm_collect_params order (model/lm_model.c:84-98): embedding [V,D];
+ * per layer attn_norm [D], w_qkv [D,3D], b_qkv [3D], wo [D,D], bo [D], ffn_norm [D],
+ * w_gate_up [D,2F], b_gate_up [2F], w_down [F,D], b_down [D]; final_norm [D]. */
+typedef struct TbTrainer TbTrainer;
+
+/* gpu_trainer_create (model/gpu_train.h:86-92): the architecture comes as numbers instead of
+ * an LMModel*, the weights through tb_trainer_upload.  d_model, d_ff and head_dim must be
+ * multiples of 8.  All work of this trainer is issued on `stream`. */
+int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T, int B, float eps, void* stream);
+/* gpu_trainer_destroy (model/gpu_train.h:93) */
+int tb_trainer_destroy(TbTrainer* g);
+int64_t tb_trainer_total_scalars(const TbTrainer* g);
+int tb_trainer_num_params(const TbTrainer* g);                       /* 10*L + 2 */
+int tb_trainer_param_layout(const TbTrainer* g, int64_t* offsets, int64_t* numels);
+
+/* `which` selects a flat buffer: 0 parameters, 1 gradients, 2 Adam m, 3 Adam v.
+ * gpu_trainer_upload / gpu_trainer_upload_grads (model/gpu_train.h:97,103) */
+int tb_trainer_upload(TbTrainer* g, int which, const float* h_flat);
+/* gpu_trainer_download / gpu_trainer_download_grads (model/gpu_train.h:99,101) */
+int tb_trainer_download(TbTrainer* g, int which, float* h_flat);
+/* Device address of a flat buffer (for a collective over the gradients). */
+void* tb_trainer_device_ptr(TbTrainer* g, int which);
+
+/* gpu_trainer_forward_backward (model/gpu_train.h:114): zeroes the gradients, runs forward and
+ * backward on host ids/targets [B*T], returns the mean loss (mean inside a sequence, then over
+ * sequences) and leaves the mean gradients on the device. */
+int tb_trainer_forward_backward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, float* loss_out);
+/* gpu_trainer_eval_loss (model/gpu_train.h:119): forward only; bit-identical to the loss of
+ * tb_trainer_forward_backward on the same input. */
+int tb_trainer_eval_loss(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, float* loss_out);
+/* gpu_trainer_grad_norm (model/gpu_train.h:122): global L2 norm, fixed summation order. */
+int tb_trainer_grad_norm(TbTrainer* g, double* norm_out);
+/* gpu_trainer_adam_step_scaled (model/gpu_train.h:125) with the optimiser's scalars passed in;
+ * t is the step counter after the increment (first step: 1). grad_scale 1 = gpu_trainer_adam_step. */
+int tb_trainer_adam_step_scaled(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
+                                float grad_scale);
+/* One iteration of the training loop (training/train_lm_gpu.c:212-223): forward, backward,
+ * gradient norm, clip to max_norm (<= 0: no clipping) and Adam, with a single host read. */
+int tb_trainer_train_step(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, uint64_t t, float lr,
+                          float beta1, float beta2, float eps, float max_norm, float* loss_out, double* norm_out);
+
+/* The same step in pieces, so that a data-parallel caller can start the all-reduce of a
+ * layer's gradients while the layers below are still in backward (the multi-GPU extension of
+ * training/data_parallel.c:119-163).  Order: zero_grads, forward(want_grad=1), backward_head,
+ * backward_layer(L-1 .. 0), backward_embed, [all-reduce], clip_adam_async, read_loss. */
+int tb_trainer_zero_grads(TbTrainer* g);
+int tb_trainer_forward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, int want_grad);
+int tb_trainer_backward_head(TbTrainer* g);
+int tb_trainer_backward_layer(TbTrainer* g, int layer);
+int tb_trainer_backward_embed(TbTrainer* g);
+/* grad_scale multiplies the gradients before the norm is applied (1/world_size after a sum). */
+int tb_trainer_clip_adam_async(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
+                               float max_norm, float grad_scale);
+int tb_trainer_read_loss(TbTrainer* g, float* loss_out);
+
 #ifdef __cplusplus
 }
 #endif

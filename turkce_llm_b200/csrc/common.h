@@ -76,8 +76,9 @@ struct GemmArgs {
     int batch = 1;
     long long strideA = 0, strideB = 0;     // elements
     // outputs: either or both
-    float* C32 = nullptr; long long ldc32 = 0, strideC32 = 0;
-    bf16* C16 = nullptr;  long long ldc16 = 0, strideC16 = 0;
+    float* C32 = nullptr; long long ldc32 = 0, strideC32 = 0, strideC32_in = 0;
+    bf16* C16 = nullptr;  long long ldc16 = 0, strideC16 = 0, strideC16_in = 0;
+    int c_inner = 1;   // >1: output of batch z goes to (z / c_inner) * strideC + (z % c_inner) * strideC_in
     const float* bias = nullptr;            // [N]
     const float* residual = nullptr; long long ldr = 0, strideR = 0;   // [M,N] fp32
     float alpha = 1.0f, beta = 0.0f;        // beta applies to the previous contents of C32

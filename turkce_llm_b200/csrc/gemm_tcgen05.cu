@@ -46,8 +46,9 @@ struct GemmParams {
     int mt, nt;                 // tiles along M, N
     int a_mn, b_mn;             // 1 = operand tile is MN-major (stored transposed)
     int causal;
-    float* C32; long long ldc32, strideC32;
-    bf16* C16; long long ldc16, strideC16;
+    float* C32; long long ldc32, strideC32, strideC32_in;
+    bf16* C16; long long ldc16, strideC16, strideC16_in;
+    int c_inner;                // output batch index z -> (z / c_inner) * stride + (z % c_inner) * stride_in
     const float* bias;
     const float* residual; long long ldr, strideR;
     float alpha, beta;
@@ -209,8 +210,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const long long zc = (long long)c.z * p.splits + c.s;
-            float* C32 = p.C32 ? p.C32 + zc * p.strideC32 : nullptr;
-            bf16* C16 = p.C16 ? p.C16 + zc * p.strideC16 : nullptr;
+            const long long zo = zc / p.c_inner, zi = zc % p.c_inner;
+            float* C32 = p.C32 ? p.C32 + zo * p.strideC32 + zi * p.strideC32_in : nullptr;
+            bf16* C16 = p.C16 ? p.C16 + zo * p.strideC16 + zi * p.strideC16_in : nullptr;
             const float* R = p.residual ? p.residual + (long long)c.z * p.strideR : nullptr;
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
 
@@ -441,18 +443,23 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     p.err = ctx->d_err;
     if (splits > 1) {
         // partial tiles, one [M,N] slab per (batch, split); everything else happens in the reduction
-        p.C32 = ws; p.ldc32 = a.N; p.strideC32 = (long long)a.M * a.N;
-        p.C16 = nullptr; p.ldc16 = 0; p.strideC16 = 0;
+        TB_CHECK(a.c_inner <= 1, "split-K GEMM does not take a two-level output batch stride");
+        p.C32 = ws; p.ldc32 = a.N; p.strideC32 = (long long)a.M * a.N; p.strideC32_in = 0;
+        p.C16 = nullptr; p.ldc16 = 0; p.strideC16 = 0; p.strideC16_in = 0;
+        p.c_inner = 1;
         p.bias = nullptr; p.residual = nullptr; p.ldr = 0; p.strideR = 0;
         p.alpha = a.alpha; p.beta = 0.0f;
     } else {
-        p.C32 = a.C32; p.ldc32 = a.ldc32; p.strideC32 = a.strideC32;
-        p.C16 = a.C16; p.ldc16 = a.ldc16; p.strideC16 = a.strideC16;
+        p.C32 = a.C32; p.ldc32 = a.ldc32; p.strideC32 = a.strideC32; p.strideC32_in = a.strideC32_in;
+        p.C16 = a.C16; p.ldc16 = a.ldc16; p.strideC16 = a.strideC16; p.strideC16_in = a.strideC16_in;
+        p.c_inner = a.c_inner > 1 ? a.c_inner : 1;
         p.bias = a.bias; p.residual = a.residual; p.ldr = a.ldr; p.strideR = a.strideR;
         p.alpha = a.alpha; p.beta = a.beta;
     }
-    p.vec32 = p.C32 && (reinterpret_cast<uintptr_t>(p.C32) % 16 == 0) && p.ldc32 % 4 == 0 && p.strideC32 % 4 == 0;
-    p.vec16 = p.C16 && (reinterpret_cast<uintptr_t>(p.C16) % 8 == 0) && p.ldc16 % 4 == 0 && p.strideC16 % 4 == 0;
+    p.vec32 = p.C32 && (reinterpret_cast<uintptr_t>(p.C32) % 16 == 0) && p.ldc32 % 4 == 0 && p.strideC32 % 4 == 0 &&
+              p.strideC32_in % 4 == 0;
+    p.vec16 = p.C16 && (reinterpret_cast<uintptr_t>(p.C16) % 8 == 0) && p.ldc16 % 4 == 0 && p.strideC16 % 4 == 0 &&
+              p.strideC16_in % 4 == 0;
     p.vecr = p.residual && (reinterpret_cast<uintptr_t>(p.residual) % 16 == 0) && p.ldr % 4 == 0 && p.strideR % 4 == 0;
 
     if (bn == 64) TB_TRY(launch_impl<64>(ctx, a, p, tmA, tmB, stream));
@@ -475,7 +482,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
 int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual) splits = 1;
+    if (a.residual || a.c_inner > 1) splits = 1;
     float* ws = nullptr;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N * sizeof(float);
@@ -489,7 +496,7 @@ int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, siz
                         cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual) splits = 1;
+    if (a.residual || a.c_inner > 1) splits = 1;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N;
         TB_CHECK(workspace != nullptr && workspace_floats >= need,

@@ -1,0 +1,514 @@
+// Row / element kernels that complete a training step (see step_kernels.h).
+// Formulas follow the reference's kernels (cuda/train_kernels.cu:503-800) and the CPU
+// definitions they mirror (model/model_ops.c, model/rope.c, model/loss.c, training/adam.c);
+// the parallel decomposition is this library's own: one warp per row with shuffle
+// reductions instead of one 256-thread block per row with shared-memory trees.
+#include "step_kernels.h"
+
+namespace tb {
+
+static inline int grid_for(long long work, int block, const DeviceCtx* ctx, int per_sm = 16) {
+    long long b = (work + block - 1) / block;
+    const long long cap = (long long)per_sm * ctx->sm_count;
+    if (b > cap) b = cap;
+    return (int)(b < 1 ? 1 : b);
+}
+
+#define TB_LAUNCHED(ctx)            \
+    do {                            \
+        TB_CUDA(cudaGetLastError()); \
+        (ctx)->launches++;          \
+    } while (0)
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void embed_fwd_kernel(const float* __restrict__ E, const uint32_t* __restrict__ ids,
+                                 float* __restrict__ x, long long total, int D) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long n = i / D;
+        const int j = (int)(i % D);
+        x[i] = E[(long long)ids[n] * D + j];
+    }
+}
+
+int launch_embed_fwd(DeviceCtx* ctx, const float* E, const uint32_t* ids, float* x, int rows, int D,
+                     cudaStream_t st) {
+    const long long total = (long long)rows * D;
+    embed_fwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(E, ids, x, total, D);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// One block per run of equal tokens (rows pre-sorted by token, ties by position): thread j
+// adds the rows of the run in ascending position, then adds the sum to dE[token, j].
+__global__ void embed_bwd_kernel(const float* __restrict__ dx, const uint32_t* __restrict__ order,
+                                 const uint32_t* __restrict__ seg_start, const uint32_t* __restrict__ seg_token,
+                                 float* __restrict__ dE, int D) {
+    const int seg = blockIdx.x;
+    const uint32_t r0 = seg_start[seg], r1 = seg_start[seg + 1];
+    const long long tok = seg_token[seg];
+    for (int j = threadIdx.x; j < D; j += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t r = r0; r < r1; ++r) acc += dx[(long long)order[r] * D + j];
+        dE[tok * D + j] += acc;
+    }
+}
+
+int launch_embed_bwd(DeviceCtx* ctx, const float* dx, const uint32_t* order, const uint32_t* seg_start,
+                     const uint32_t* seg_token, int nseg, float* dE, int D, cudaStream_t st) {
+    if (nseg <= 0) return 0;
+    const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : 64);
+    embed_bwd_kernel<<<nseg, threads, 0, st>>>(dx, order, seg_start, seg_token, dE, D);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// -------------------------------------------------------------------- RMSNorm
+// y = x * r * w,  r = 1/sqrt(mean(x^2) + eps)   (model/model_ops.c; eps inside the root)
+__global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                   bf16* __restrict__ out, float* __restrict__ rinv, int rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
+         row += (long long)gridDim.x * wpb) {
+        const float* xr = x + row * cols;
+        float ss = 0.0f;
+        for (int i = lane; i < cols; i += 32) ss += xr[i] * xr[i];
+        ss = warp_sum(ss);
+        const float ms = ss / (float)cols;
+        const float r = 1.0f / (float)sqrt((double)(ms + eps));
+        if (lane == 0) rinv[row] = r;
+        bf16* orow = out + row * cols;
+        for (int i = lane; i < cols; i += 32) orow[i] = __float2bfloat16_rn(xr[i] * r * w[i]);
+    }
+}
+
+int launch_rmsnorm_fwd(DeviceCtx* ctx, const float* x, const float* w, bf16* out, float* rinv, int rows, int cols,
+                       float eps, cudaStream_t st) {
+    rmsnorm_fwd_kernel<<<grid_for(rows, 8, ctx), 256, 0, st>>>(x, w, out, rinv, rows, cols, eps);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// dx[j] (+)= w[j]*r*dy[j] - (r^3/cols) * x[j] * S,  S = sum_j dy*w*x ;  wtmp[j] = dy[j]*x[j]*r
+__global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                   const float* __restrict__ rinv, const float* __restrict__ dy,
+                                   float* __restrict__ dx, bf16* __restrict__ dx16, float* __restrict__ wtmp,
+                                   int rows, int cols, int accumulate) {
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
+         row += (long long)gridDim.x * wpb) {
+        const float* xr = x + row * cols;
+        const float* dyr = dy + row * cols;
+        const float r = rinv[row];
+        float S = 0.0f;
+        for (int i = lane; i < cols; i += 32) S += dyr[i] * w[i] * xr[i];
+        S = warp_sum(S);
+        const float k = (r * r * r) / (float)cols;
+        for (int j = lane; j < cols; j += 32) {
+            const long long o = row * cols + j;
+            float v = w[j] * r * dyr[j] - k * xr[j] * S;
+            if (accumulate) v += dx[o];
+            dx[o] = v;
+            dx16[o] = __float2bfloat16_rn(v);
+            wtmp[o] = dyr[j] * xr[j] * r;
+        }
+    }
+}
+
+int launch_rmsnorm_bwd(DeviceCtx* ctx, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
+                       bf16* dx16, float* wtmp, int rows, int cols, int accumulate, cudaStream_t st) {
+    rmsnorm_bwd_kernel<<<grid_for(rows, 8, ctx), 256, 0, st>>>(x, w, rinv, dy, dx, dx16, wtmp, rows, cols, accumulate);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// ----------------------------------------------------------------------- RoPE
+// qkv [B*T, 3D] -> Q, K rotated on interleaved pairs (2k, 2k+1), V copied; all [B,H,T,hd] bf16
+__global__ void rope_split_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, bf16* __restrict__ Q, bf16* __restrict__ K,
+                                  bf16* __restrict__ V, int B, int T, int H, int hd) {
+    const int half = hd >> 1;
+    const int D = H * hd;
+    const long long total = (long long)B * T * H * half;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int k = (int)(i % half);
+        long long rest = i / half;
+        const int h = (int)(rest % H);
+        const long long n = rest / H;
+        const int t = (int)(n % T);
+        const long long b = n / T;
+        const float* row = qkv + n * 3LL * D;
+        const int c0 = h * hd + 2 * k;
+        const float c = cos_t[t * half + k], s = sin_t[t * half + k];
+        const long long o = ((b * H + h) * T + t) * hd + 2 * k;
+        const float2 q = *reinterpret_cast<const float2*>(row + c0);
+        const float2 kk = *reinterpret_cast<const float2*>(row + D + c0);
+        const float2 v = *reinterpret_cast<const float2*>(row + 2 * D + c0);
+        *reinterpret_cast<__nv_bfloat162*>(Q + o) = __floats2bfloat162_rn(q.x * c - q.y * s, q.x * s + q.y * c);
+        *reinterpret_cast<__nv_bfloat162*>(K + o) = __floats2bfloat162_rn(kk.x * c - kk.y * s, kk.x * s + kk.y * c);
+        *reinterpret_cast<__nv_bfloat162*>(V + o) = __floats2bfloat162_rn(v.x, v.y);
+    }
+}
+
+int launch_rope_split(DeviceCtx* ctx, const float* qkv, const float* cos_t, const float* sin_t, bf16* Q, bf16* K,
+                      bf16* V, int B, int T, int H, int hd, cudaStream_t st) {
+    TB_CHECK(hd % 2 == 0, "head dim must be even");
+    const long long total = (long long)B * T * H * (hd / 2);
+    rope_split_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(qkv, cos_t, sin_t, Q, K, V, B, T, H, hd);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// inverse rotation of dQ, dK and merge with dV into dqkv [B*T, 3D] (bf16)
+__global__ void rope_merge_bwd_kernel(const float* __restrict__ dQ, const float* __restrict__ dK,
+                                      const float* __restrict__ dV, const float* __restrict__ cos_t,
+                                      const float* __restrict__ sin_t, bf16* __restrict__ dqkv, int B, int T, int H,
+                                      int hd) {
+    const int half = hd >> 1;
+    const int D = H * hd;
+    const long long total = (long long)B * T * H * half;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int k = (int)(i % half);
+        long long rest = i / half;
+        const int h = (int)(rest % H);
+        const long long n = rest / H;
+        const int t = (int)(n % T);
+        const long long b = n / T;
+        bf16* row = dqkv + n * 3LL * D;
+        const int c0 = h * hd + 2 * k;
+        const float c = cos_t[t * half + k], s = sin_t[t * half + k];
+        const long long o = ((b * H + h) * T + t) * hd + 2 * k;
+        const float2 a = *reinterpret_cast<const float2*>(dQ + o);
+        const float2 bb = *reinterpret_cast<const float2*>(dK + o);
+        const float2 v = *reinterpret_cast<const float2*>(dV + o);
+        *reinterpret_cast<__nv_bfloat162*>(row + c0) = __floats2bfloat162_rn(a.x * c + a.y * s, -a.x * s + a.y * c);
+        *reinterpret_cast<__nv_bfloat162*>(row + D + c0) =
+            __floats2bfloat162_rn(bb.x * c + bb.y * s, -bb.x * s + bb.y * c);
+        *reinterpret_cast<__nv_bfloat162*>(row + 2 * D + c0) = __floats2bfloat162_rn(v.x, v.y);
+    }
+}
+
+int launch_rope_merge_bwd(DeviceCtx* ctx, const float* dQ, const float* dK, const float* dV, const float* cos_t,
+                          const float* sin_t, bf16* dqkv, int B, int T, int H, int hd, cudaStream_t st) {
+    const long long total = (long long)B * T * H * (hd / 2);
+    rope_merge_bwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(dQ, dK, dV, cos_t, sin_t, dqkv, B, T, H, hd);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// ------------------------------------------------------------- causal softmax
+// Row i of a [T,T] score matrix: p_j = softmax_j(s_j * scale) over j <= i.  The reference adds
+// -1e9 to j > i (model/attention.c:11), which underflows to exactly 0 after exp in float32, so
+// leaving those entries out is the same function.  Zeros are written from i+1 to the end of the
+// 128-wide tile that holds the diagonal: the following GEMMs read whole tiles up to there.
+__global__ void attn_softmax_fwd_kernel(const float* __restrict__ S, bf16* __restrict__ P, long long rows, int T,
+                                        long long ld, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
+         row += (long long)gridDim.x * wpb) {
+        const int i = (int)(row % T);
+        const float* s = S + row * ld;
+        bf16* p = P + row * ld;
+        float mx = -3.0e38f;
+        for (int j = lane; j <= i; j += 32) mx = fmaxf(mx, s[j] * scale);
+        mx = warp_max(mx);
+        float sum = 0.0f;
+        for (int j = lane; j <= i; j += 32) sum += expf(s[j] * scale - mx);
+        sum = warp_sum(sum);
+        for (int j = lane; j <= i; j += 32) p[j] = __float2bfloat16_rn(expf(s[j] * scale - mx) / sum);
+        const int end = min(T, ((i >> 7) + 1) << 7);
+        for (int j = i + 1 + lane; j < end; j += 32) p[j] = __float2bfloat16_rn(0.0f);
+    }
+}
+
+int launch_attn_softmax_fwd(DeviceCtx* ctx, const float* S, bf16* P, int BH, int T, long long ld, float scale,
+                            cudaStream_t st) {
+    const long long rows = (long long)BH * T;
+    attn_softmax_fwd_kernel<<<grid_for(rows, 8, ctx, 32), 256, 0, st>>>(S, P, rows, T, ld, scale);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// dS = P * (dP - <dP, P>) * scale   (softmax backward then the score scale)
+__global__ void attn_softmax_bwd_kernel(const bf16* __restrict__ P, const float* __restrict__ dP,
+                                        bf16* __restrict__ dS, long long rows, int T, long long ld, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
+         row += (long long)gridDim.x * wpb) {
+        const int i = (int)(row % T);
+        const bf16* p = P + row * ld;
+        const float* d = dP + row * ld;
+        bf16* o = dS + row * ld;
+        float dot = 0.0f;
+        for (int j = lane; j <= i; j += 32) dot += d[j] * __bfloat162float(p[j]);
+        dot = warp_sum(dot);
+        for (int j = lane; j <= i; j += 32) o[j] = __float2bfloat16_rn(__bfloat162float(p[j]) * (d[j] - dot) * scale);
+        const int end = min(T, ((i >> 7) + 1) << 7);
+        for (int j = i + 1 + lane; j < end; j += 32) o[j] = __float2bfloat16_rn(0.0f);
+    }
+}
+
+int launch_attn_softmax_bwd(DeviceCtx* ctx, const bf16* P, const float* dP, bf16* dS, int BH, int T, long long ld,
+                            float scale, cudaStream_t st) {
+    const long long rows = (long long)BH * T;
+    attn_softmax_bwd_kernel<<<grid_for(rows, 8, ctx, 32), 256, 0, st>>>(P, dP, dS, rows, T, ld, scale);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// dout [B*T, H*hd] -> dO [B,H,T,hd]
+__global__ void heads_split_kernel(const bf16* __restrict__ dout, bf16* __restrict__ dO, int B, int T, int H,
+                                   int hd) {
+    const long long total = (long long)B * T * H * hd;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int d = (int)(i % hd);
+        long long rest = i / hd;
+        const int h = (int)(rest % H);
+        const long long n = rest / H;
+        const int t = (int)(n % T);
+        const long long b = n / T;
+        dO[((b * H + h) * T + t) * hd + d] = dout[i];
+    }
+}
+
+int launch_heads_split(DeviceCtx* ctx, const bf16* dout, bf16* dO, int B, int T, int H, int hd, cudaStream_t st) {
+    const long long total = (long long)B * T * H * hd;
+    heads_split_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(dout, dO, B, T, H, hd);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// --------------------------------------------------------------------- SwiGLU
+// h = g * sigmoid(g) * u with g = gu[:, :F], u = gu[:, F:]   (model/feedforward.c:9-14)
+__global__ void swiglu_fwd_kernel(const float* __restrict__ gu, bf16* __restrict__ h, long long total, int F) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long n = i / F;
+        const int j = (int)(i % F);
+        const float g = gu[n * 2 * F + j], u = gu[n * 2 * F + F + j];
+        const float sg = 1.0f / (1.0f + expf(-g));
+        h[i] = __float2bfloat16_rn(g * sg * u);
+    }
+}
+
+int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F, cudaStream_t st) {
+    const long long total = (long long)rows * F;
+    swiglu_fwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(gu, h, total, F);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// dg = dh*u*(sg + g*sg*(1-sg)),  du = dh*g*sg
+__global__ void swiglu_bwd_kernel(const float* __restrict__ gu, const float* __restrict__ dh,
+                                  bf16* __restrict__ dgu, long long total, int F) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long n = i / F;
+        const int j = (int)(i % F);
+        const float g = gu[n * 2 * F + j], u = gu[n * 2 * F + F + j];
+        const float sg = 1.0f / (1.0f + expf(-g));
+        const float d = dh[i];
+        const float dsilu = d * u;
+        dgu[n * 2 * F + j] = __float2bfloat16_rn(dsilu * sg + dsilu * g * sg * (1.0f - sg));
+        dgu[n * 2 * F + F + j] = __float2bfloat16_rn(d * g * sg);
+    }
+}
+
+int launch_swiglu_bwd(DeviceCtx* ctx, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t st) {
+    const long long total = (long long)rows * F;
+    swiglu_bwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(gu, dh, dgu, total, F);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// -------------------------------------------------------------- cross-entropy
+__device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = is_max ? warp_max(v) : warp_sum(v);
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float r = sh[0];
+    for (int k = 1; k < nw; ++k) r = is_max ? fmaxf(r, sh[k]) : r + sh[k];
+    __syncthreads();
+    return r;
+}
+
+// loss = log(sum exp(z - max)) + max - z[target];  dlogits = (softmax - onehot) * grad_scale
+__global__ void cross_entropy_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
+                                     float* __restrict__ loss_rows, bf16* __restrict__ dlogits, int V, long long ld,
+                                     float grad_scale) {
+    __shared__ float sh[32];
+    const long long row = blockIdx.x;
+    const float* z = logits + row * ld;
+    const int t = (int)targets[row];
+    float mx = -3.0e38f;
+    for (int j = threadIdx.x; j < V; j += blockDim.x) mx = fmaxf(mx, z[j]);
+    mx = block_reduce(mx, sh, true);
+    float sum = 0.0f;
+    for (int j = threadIdx.x; j < V; j += blockDim.x) sum += expf(z[j] - mx);
+    sum = block_reduce(sum, sh, false);
+    if (threadIdx.x == 0) loss_rows[row] = (float)log((double)sum) + mx - z[t];
+    if (dlogits) {
+        const float inv = 1.0f / sum;
+        bf16* d = dlogits + row * ld;
+        for (int j = threadIdx.x; j < V; j += blockDim.x) {
+            float p = expf(z[j] - mx) * inv;
+            if (j == t) p -= 1.0f;
+            d[j] = __float2bfloat16_rn(p * grad_scale);
+        }
+    }
+}
+
+int launch_cross_entropy(DeviceCtx* ctx, const float* logits, const uint32_t* targets, float* loss_rows,
+                         bf16* dlogits, int rows, int V, long long ld, float grad_scale, cudaStream_t st) {
+    cross_entropy_kernel<<<rows, 512, 0, st>>>(logits, targets, loss_rows, dlogits, V, ld, grad_scale);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// ---------------------------------------------------------------- column sums
+// Stage 1: block (32 columns x 8 row-lanes) sums its chunk of rows -> partial[chunk][c];
+// stage 2: out[c] += partial[0][c] + partial[1][c] + ... in chunk order.
+constexpr int kColsumChunks = 64;
+
+size_t colsum_partial_floats(int cols) { return (size_t)kColsumChunks * cols; }
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__global__ void colsum_stage1_kernel(const T* __restrict__ in, float* __restrict__ partial, int rows, int cols) {
+    __shared__ float part[8][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int c = blockIdx.x * 32 + tx;
+    const int chunk = blockIdx.y;
+    const int per = (rows + kColsumChunks - 1) / kColsumChunks;
+    const int r0 = chunk * per, r1 = min(rows, r0 + per);
+    float s = 0.0f;
+    if (c < cols)
+        for (int r = r0 + ty; r < r1; r += 8) s += to_f32<T>(in[(long long)r * cols + c]);
+    part[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && c < cols) {
+        float t = part[0][tx];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) t += part[k][tx];
+        partial[(long long)chunk * cols + c] = t;
+    }
+}
+
+__global__ void colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float t = partial[c];
+    for (int k = 1; k < kColsumChunks; ++k) t += partial[(long long)k * cols + c];
+    out[c] += t;
+}
+
+template <typename T>
+static int colsum_impl(DeviceCtx* ctx, const T* in, float* out, float* partial, int rows, int cols, cudaStream_t st) {
+    dim3 grid((cols + 31) / 32, kColsumChunks), block(32, 8);
+    colsum_stage1_kernel<T><<<grid, block, 0, st>>>(in, partial, rows, cols);
+    TB_LAUNCHED(ctx);
+    colsum_stage2_kernel<<<(cols + 127) / 128, 128, 0, st>>>(partial, out, cols);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+int launch_colsum_f32(DeviceCtx* ctx, const float* in, float* out, float* partial, int rows, int cols,
+                      cudaStream_t st) {
+    return colsum_impl<float>(ctx, in, out, partial, rows, cols, st);
+}
+int launch_colsum_bf16(DeviceCtx* ctx, const bf16* in, float* out, float* partial, int rows, int cols,
+                       cudaStream_t st) {
+    return colsum_impl<bf16>(ctx, in, out, partial, rows, cols, st);
+}
+
+// ------------------------------------------------------- gradient norm, Adam
+__global__ void sumsq_partial_kernel(const float* __restrict__ x, long long n, float* __restrict__ partial) {
+    __shared__ float sh[32];
+    float s = 0.0f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        s += x[i] * x[i];
+    s = block_reduce(s, sh, false);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+int launch_sumsq_partial(DeviceCtx* ctx, const float* x, long long n, float* partial, cudaStream_t st) {
+    sumsq_partial_kernel<<<kNormBlocks, 256, 0, st>>>(x, n, partial);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// The reference sums the block partials on the host in float64 (model/gpu_train.c:508-511);
+// one device thread does the same sum so the step needs no host round trip.
+__global__ void clip_scale_kernel(const float* __restrict__ partial, float max_norm, float* __restrict__ scalars,
+                                  double* __restrict__ norm64) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    double ss = 0.0;
+    for (int i = 0; i < kNormBlocks; ++i) ss += (double)partial[i];
+    const double norm = sqrt(ss);
+    *norm64 = norm;
+    scalars[0] = (float)norm;
+    scalars[1] = (max_norm > 0.0f && norm > (double)max_norm) ? (float)((double)max_norm / norm) : 1.0f;
+}
+
+int launch_clip_scale(DeviceCtx* ctx, const float* partial, float max_norm, float* scalars, double* norm64,
+                      cudaStream_t st) {
+    clip_scale_kernel<<<1, 32, 0, st>>>(partial, max_norm, scalars, norm64);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// m = b1*m + (1-b1)*g; v = b2*v + (1-b2)*g^2; p -= lr * (m/bc1) / (sqrt(v/bc2) + eps)
+// (training/adam.c:38-53).  The square root is IEEE sqrtf.
+__global__ void adam_kernel(float* __restrict__ p, bf16* __restrict__ p16, const float* __restrict__ g,
+                            float* __restrict__ m, float* __restrict__ v, long long n, float lr, float b1, float b2,
+                            float eps, float bc1, float bc2, float grad_scale, const float* __restrict__ dev_scale) {
+    const float gs = dev_scale ? grad_scale * dev_scale[1] : grad_scale;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float gi = g[i] * gs;
+        const float mi = b1 * m[i] + (1.0f - b1) * gi;
+        const float vi = b2 * v[i] + (1.0f - b2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        const float m_hat = mi / bc1;
+        const float v_hat = vi / bc2;
+        const float pi = p[i] - lr * m_hat / (sqrtf(v_hat) + eps);
+        p[i] = pi;
+        if (p16) p16[i] = __float2bfloat16_rn(pi);
+    }
+}
+
+int launch_adam(DeviceCtx* ctx, float* p, bf16* p16, const float* g, float* m, float* v, long long n, float lr,
+                float b1, float b2, float eps, float bc1, float bc2, float grad_scale, const float* dev_scale,
+                cudaStream_t st) {
+    adam_kernel<<<grid_for(n, 256, ctx, 32), 256, 0, st>>>(p, p16, g, m, v, n, lr, b1, b2, eps, bc1, bc2, grad_scale,
+                                                            dev_scale);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+}  // namespace tb

@@ -1,0 +1,49 @@
+// Launchers of the kernels that complete a training step around the GEMMs: embedding,
+// RMSNorm, RoPE split/merge, causal softmax, SwiGLU, cross-entropy, column sums, gradient
+// norm and Adam.  All are bandwidth-bound row or element kernels; activations that feed a
+// GEMM are written in bf16 so the tensor cores read them through TMA without a conversion
+// pass.  None uses atomics: every reduction has a fixed order, so a step is bitwise
+// reproducible (the reference's rule: cuda/train_kernels.cu:17-20).
+#pragma once
+#include "common.h"
+
+namespace tb {
+
+int launch_embed_fwd(DeviceCtx*, const float* E, const uint32_t* ids, float* x, int rows, int D, cudaStream_t);
+int launch_rmsnorm_fwd(DeviceCtx*, const float* x, const float* w, bf16* out, float* rinv, int rows, int cols,
+                       float eps, cudaStream_t);
+// dx (+)= rmsnorm backward; dx16 = bf16(dx); wtmp[n,j] = dy*x*r (summed over rows by colsum)
+int launch_rmsnorm_bwd(DeviceCtx*, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
+                       bf16* dx16, float* wtmp, int rows, int cols, int accumulate, cudaStream_t);
+int launch_rope_split(DeviceCtx*, const float* qkv, const float* cos_t, const float* sin_t, bf16* Q, bf16* K, bf16* V,
+                      int B, int T, int H, int hd, cudaStream_t);
+int launch_rope_merge_bwd(DeviceCtx*, const float* dQ, const float* dK, const float* dV, const float* cos_t,
+                          const float* sin_t, bf16* dqkv, int B, int T, int H, int hd, cudaStream_t);
+// S [BH*T rows, leading dimension ld >= T] fp32 (entries j<=i valid) -> P bf16, same shape
+// (zero from the diagonal to the end of its 128-tile)
+int launch_attn_softmax_fwd(DeviceCtx*, const float* S, bf16* P, int BH, int T, long long ld, float scale,
+                            cudaStream_t);
+int launch_attn_softmax_bwd(DeviceCtx*, const bf16* P, const float* dP, bf16* dS, int BH, int T, long long ld,
+                            float scale, cudaStream_t);
+int launch_heads_split(DeviceCtx*, const bf16* dout, bf16* dO, int B, int T, int H, int hd, cudaStream_t);
+int launch_swiglu_fwd(DeviceCtx*, const float* gu, bf16* h, int rows, int F, cudaStream_t);
+int launch_swiglu_bwd(DeviceCtx*, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t);
+// logits [rows, ld] fp32 -> loss_rows, dlogits bf16 [rows, ld] = (softmax - onehot) * grad_scale
+int launch_cross_entropy(DeviceCtx*, const float* logits, const uint32_t* targets, float* loss_rows, bf16* dlogits,
+                         int rows, int V, long long ld, float grad_scale, cudaStream_t);
+// out[c] += sum_r in[r,c]; in is fp32 or bf16; partial needs colsum_partial_floats(cols) floats
+size_t colsum_partial_floats(int cols);
+int launch_colsum_f32(DeviceCtx*, const float* in, float* out, float* partial, int rows, int cols, cudaStream_t);
+int launch_colsum_bf16(DeviceCtx*, const bf16* in, float* out, float* partial, int rows, int cols, cudaStream_t);
+// dE[token] += sum of dx rows of that token, rows taken in ascending position order
+int launch_embed_bwd(DeviceCtx*, const float* dx, const uint32_t* order, const uint32_t* seg_start,
+                     const uint32_t* seg_token, int nseg, float* dE, int D, cudaStream_t);
+constexpr int kNormBlocks = 1024;
+int launch_sumsq_partial(DeviceCtx*, const float* x, long long n, float* partial, cudaStream_t);
+// scalars[0] = norm (as float), scalars[1] = min(1, max_norm / norm) (1 when max_norm <= 0); norm64 = norm
+int launch_clip_scale(DeviceCtx*, const float* partial, float max_norm, float* scalars, double* norm64, cudaStream_t);
+// Adam; gradient is multiplied by grad_scale * (*dev_scale if given); writes the bf16 shadow copy too
+int launch_adam(DeviceCtx*, float* p, bf16* p16, const float* g, float* m, float* v, long long n, float lr, float b1,
+                float b2, float eps, float bc1, float bc2, float grad_scale, const float* dev_scale, cudaStream_t);
+
+}  // namespace tb

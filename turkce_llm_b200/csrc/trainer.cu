@@ -1,0 +1,563 @@
+// GPU-resident trainer: the whole decoder's forward, backward and Adam on one device, with
+// the schedule and the flat parameter layout of the reference's GpuTrainer
+// (model/gpu_train.c:144-529, model/gpu_train.h:33-125) and this library's kernels underneath.
+//
+// Differences from the reference that do not change the function computed:
+//  * every GEMM operand lives in bf16 in HBM (weights as a shadow copy refreshed by Adam,
+//    activations written in bf16 by the kernel that produces them), so the tensor cores read
+//    through TMA with no conversion pass; residual stream, logits, gradients and Adam state
+//    stay float32;
+//  * the weight-gradient (TN) GEMMs run on tensor cores with deterministic split-K instead of
+//    the reference's FP32 SIMT kernel;
+//  * attention skips the masked upper triangle (exact: the reference's -1e9 mask underflows to
+//    0 after exp) and P*V writes the merged [B*T, D] layout directly;
+//  * the gradient norm and clip factor are reduced on the device, so a full training step
+//    needs one host read (the loss rows) instead of three.
+#include "../../include/turkce_b200.h"
+#include "common.h"
+#include "step_kernels.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+using namespace tb;
+
+namespace {
+
+enum { PK_ATTN_NORM = 0, PK_WQKV, PK_BQKV, PK_WO, PK_BO, PK_FFN_NORM, PK_WGU, PK_BGU, PK_WDOWN, PK_BDOWN };
+
+struct LayerActs {
+    float* x_in;  bf16* n1; float* r1;
+    bf16 *Q, *K, *V, *P, *att;
+    float* x2;    bf16* n2; float* r2;
+    float* gu;    bf16* h;
+};
+
+}  // namespace
+
+struct TbTrainer {
+    DeviceCtx* ctx = nullptr;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int V = 0, D = 0, H = 0, L = 0, F = 0, T = 0, B = 0, N = 0, hd = 0;
+    long long Vp = 0;   // logits leading dimension (V rounded up to 8)
+    long long Tp = 0;   // score-matrix leading dimension (T rounded up to 8)
+    float eps = 1e-5f;
+    float scale = 0.f;
+
+    std::vector<long long> offsets, numels;
+    long long total = 0;
+    float *params = nullptr, *grads = nullptr, *adam_m = nullptr, *adam_v = nullptr;
+    bf16* params16 = nullptr;
+
+    std::vector<LayerActs> layers;
+    float* x_final = nullptr; bf16* nf = nullptr; float* rf = nullptr;
+    float* logits = nullptr; bf16* dlogits = nullptr;
+
+    float *qkv = nullptr, *S = nullptr, *dP = nullptr, *dn = nullptr, *dres = nullptr, *wtmp = nullptr, *dh = nullptr;
+    float *dQ = nullptr, *dK = nullptr, *dV = nullptr;
+    bf16 *dres16 = nullptr, *dgu = nullptr, *datt = nullptr, *dO = nullptr, *dS = nullptr, *dqkv = nullptr;
+    float* colsum_partial = nullptr;
+    float* splitk_ws = nullptr; size_t splitk_floats = 0;
+
+    uint32_t *ids = nullptr, *targets = nullptr, *order = nullptr, *seg_start = nullptr, *seg_token = nullptr;
+    float *loss_rows = nullptr, *cos_t = nullptr, *sin_t = nullptr;
+    float* norm_partial = nullptr; float* scalars = nullptr; double* norm64 = nullptr;
+
+    // pinned host staging
+    uint32_t *h_ids = nullptr, *h_targets = nullptr, *h_seg = nullptr;
+    float* h_loss_rows = nullptr; double* h_norm = nullptr;
+    int nseg = 0;
+    std::vector<void*> allocs;
+};
+
+namespace {
+
+template <typename T>
+int dalloc(TbTrainer* g, T** p, size_t count) {
+    void* q = nullptr;
+    TB_CUDA(cudaMalloc(&q, std::max<size_t>(count, 1) * sizeof(T)));
+    g->allocs.push_back(q);
+    *p = static_cast<T*>(q);
+    return 0;
+}
+
+inline long long pidx(int layer, int k) { return 1 + 10LL * layer + k; }
+inline float* P32(TbTrainer* g, long long i) { return g->params + g->offsets[i]; }
+inline bf16* P16(TbTrainer* g, long long i) { return g->params16 + g->offsets[i]; }
+inline float* G32(TbTrainer* g, long long i) { return g->grads + g->offsets[i]; }
+
+int gemm(TbTrainer* g, GemmArgs& a) {
+    return launch_gemm_bf16_ws(g->ctx, a, g->splitk_ws, g->splitk_floats, g->stream);
+}
+
+// C[M,N] = A[M,K] @ W[K,N] + bias (+ residual): the reference's bf16_gemm_bias (gpu_train.c:103-107)
+int linear_fwd(TbTrainer* g, const bf16* A, const bf16* W, const float* bias, const float* residual, float* C32,
+               bf16* C16, int M, int N, int K) {
+    GemmArgs a;
+    a.kind = GEMM_NN; a.A = A; a.B = W; a.M = M; a.N = N; a.K = K; a.lda = K; a.ldb = N;
+    a.C32 = C32; a.ldc32 = N; a.C16 = C16; a.ldc16 = N;
+    a.bias = bias; a.residual = residual; a.ldr = N;
+    a.splits = 1;
+    return gemm(g, a);
+}
+
+// dX[M,K] = dY[M,N] @ W[K,N]^T : the reference's bf16_gemm1(GEMM_NT) (gpu_train.c:419,427,434,463)
+int linear_dx(TbTrainer* g, const bf16* dY, const bf16* W, float* dX32, bf16* dX16, int M, int N, int K) {
+    GemmArgs a;
+    a.kind = GEMM_NT; a.A = dY; a.B = W; a.M = M; a.N = K; a.K = N; a.lda = N; a.ldb = N;
+    a.C32 = dX32; a.ldc32 = K; a.C16 = dX16; a.ldc16 = K;
+    a.splits = 1;
+    return gemm(g, a);
+}
+
+// dW[K,N] += X[M,K]^T @ dY[M,N] : the reference's gemm1(GEMM_TN, beta=1) (gpu_train.c:417,425,432,461)
+int linear_dw(TbTrainer* g, const bf16* X, const bf16* dY, float* dW, int M, int N, int K) {
+    GemmArgs a;
+    a.kind = GEMM_TN; a.A = X; a.B = dY; a.M = K; a.N = N; a.K = M; a.lda = K; a.ldb = N;
+    a.C32 = dW; a.ldc32 = N; a.beta = 1.0f;
+    a.splits = 0;
+    return gemm(g, a);
+}
+
+int forward(TbTrainer* g, bool want_grad) {
+    DeviceCtx* c = g->ctx;
+    cudaStream_t st = g->stream;
+    const int N = g->N, D = g->D, F = g->F, T = g->T, V = g->V, H = g->H, hd = g->hd, B = g->B;
+    const int BH = B * H;
+    const long long Tp = g->Tp, sTT = (long long)T * Tp, sThd = (long long)T * hd;
+
+    float* x0 = g->L > 0 ? g->layers[0].x_in : g->x_final;
+    TB_TRY(launch_embed_fwd(c, P32(g, 0), g->ids, x0, N, D, st));
+
+    for (int l = 0; l < g->L; ++l) {
+        LayerActs& a = g->layers[l];
+        float* x_out = (l + 1 < g->L) ? g->layers[l + 1].x_in : g->x_final;
+        TB_TRY(launch_rmsnorm_fwd(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.n1, a.r1, N, D, g->eps, st));
+        TB_TRY(linear_fwd(g, a.n1, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, N,
+                          3 * D, D));
+        TB_TRY(launch_rope_split(c, g->qkv, g->cos_t, g->sin_t, a.Q, a.K, a.V, B, T, H, hd, st));
+        {   // S = Q K^T per (batch, head), lower-triangular tiles only
+            GemmArgs s;
+            s.kind = GEMM_NT; s.A = a.Q; s.B = a.K; s.M = T; s.N = T; s.K = hd; s.lda = hd; s.ldb = hd;
+            s.batch = BH; s.strideA = sThd; s.strideB = sThd;
+            s.C32 = g->S; s.ldc32 = Tp; s.strideC32 = sTT;
+            s.causal = CAUSAL_SKIP_UPPER; s.splits = 1;
+            TB_TRY(gemm(g, s));
+        }
+        TB_TRY(launch_attn_softmax_fwd(c, g->S, a.P, BH, T, Tp, g->scale, st));
+        {   // att[b*T+t, h*hd+d] = sum_j P[j] V[j,d], written straight into the merged layout
+            GemmArgs o;
+            o.kind = GEMM_NN; o.A = a.P; o.B = a.V; o.M = T; o.N = hd; o.K = T; o.lda = Tp; o.ldb = hd;
+            o.batch = BH; o.strideA = sTT; o.strideB = sThd;
+            o.C16 = a.att; o.ldc16 = D; o.c_inner = H; o.strideC16 = (long long)T * D; o.strideC16_in = hd;
+            o.causal = CAUSAL_K_PREFIX; o.splits = 1;
+            TB_TRY(gemm(g, o));
+        }
+        TB_TRY(linear_fwd(g, a.att, P16(g, pidx(l, PK_WO)), P32(g, pidx(l, PK_BO)), a.x_in, a.x2, nullptr, N, D, D));
+        TB_TRY(launch_rmsnorm_fwd(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.n2, a.r2, N, D, g->eps, st));
+        TB_TRY(linear_fwd(g, a.n2, P16(g, pidx(l, PK_WGU)), P32(g, pidx(l, PK_BGU)), nullptr, a.gu, nullptr, N, 2 * F,
+                          D));
+        TB_TRY(launch_swiglu_fwd(c, a.gu, a.h, N, F, st));
+        TB_TRY(linear_fwd(g, a.h, P16(g, pidx(l, PK_WDOWN)), P32(g, pidx(l, PK_BDOWN)), a.x2, x_out, nullptr, N, D,
+                          F));
+    }
+
+    const long long p_final = pidx(g->L, 0);
+    TB_TRY(launch_rmsnorm_fwd(c, g->x_final, P32(g, p_final), g->nf, g->rf, N, D, g->eps, st));
+    {   // logits = nf @ E^T (tied head): gpu_train.c:378
+        GemmArgs a;
+        a.kind = GEMM_NT; a.A = g->nf; a.B = P16(g, 0); a.M = N; a.N = V; a.K = D; a.lda = D; a.ldb = D;
+        a.C32 = g->logits; a.ldc32 = g->Vp; a.splits = 1;
+        TB_TRY(gemm(g, a));
+    }
+    TB_TRY(launch_cross_entropy(c, g->logits, g->targets, g->loss_rows, want_grad ? g->dlogits : nullptr, N, V, g->Vp,
+                                1.0f / (float)N, st));
+    return 0;
+}
+
+int backward_head(TbTrainer* g) {
+    DeviceCtx* c = g->ctx;
+    cudaStream_t st = g->stream;
+    const int N = g->N, D = g->D, V = g->V;
+    const long long p_final = pidx(g->L, 0);
+    {   // dE += dlogits^T @ nf  (gpu_train.c:403)
+        GemmArgs a;
+        a.kind = GEMM_TN; a.A = g->dlogits; a.B = g->nf; a.M = V; a.N = D; a.K = N; a.lda = g->Vp; a.ldb = D;
+        a.C32 = G32(g, 0); a.ldc32 = D; a.beta = 1.0f; a.splits = 1;
+        TB_TRY(gemm(g, a));
+    }
+    {   // dnf = dlogits @ E  (gpu_train.c:404)
+        GemmArgs a;
+        a.kind = GEMM_NN; a.A = g->dlogits; a.B = P16(g, 0); a.M = N; a.N = D; a.K = V; a.lda = g->Vp; a.ldb = D;
+        a.C32 = g->dn; a.ldc32 = D; a.splits = 1;
+        TB_TRY(gemm(g, a));
+    }
+    TB_TRY(launch_rmsnorm_bwd(c, g->x_final, P32(g, p_final), g->rf, g->dn, g->dres, g->dres16, g->wtmp, N, D, 0, st));
+    TB_TRY(launch_colsum_f32(c, g->wtmp, G32(g, p_final), g->colsum_partial, N, D, st));
+    return 0;
+}
+
+int backward_layer(TbTrainer* g, int l) {
+    DeviceCtx* c = g->ctx;
+    cudaStream_t st = g->stream;
+    const int N = g->N, D = g->D, F = g->F, T = g->T, H = g->H, hd = g->hd, B = g->B;
+    const int BH = B * H;
+    const long long Tp = g->Tp, sTT = (long long)T * Tp, sThd = (long long)T * hd;
+    LayerActs& a = g->layers[l];
+
+    // ---- FFN: x3 = x2 + (h @ Wd + bd); dres = dx3
+    TB_TRY(linear_dw(g, a.h, g->dres16, G32(g, pidx(l, PK_WDOWN)), N, D, F));
+    TB_TRY(launch_colsum_f32(c, g->dres, G32(g, pidx(l, PK_BDOWN)), g->colsum_partial, N, D, st));
+    TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WDOWN)), g->dh, nullptr, N, D, F));
+    TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->dgu, N, F, st));
+    TB_TRY(linear_dw(g, a.n2, g->dgu, G32(g, pidx(l, PK_WGU)), N, 2 * F, D));
+    TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
+    TB_TRY(linear_dx(g, g->dgu, P16(g, pidx(l, PK_WGU)), g->dn, nullptr, N, 2 * F, D));
+    TB_TRY(launch_rmsnorm_bwd(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.r2, g->dn, g->dres, g->dres16, g->wtmp, N, D, 1,
+                              st));
+    TB_TRY(launch_colsum_f32(c, g->wtmp, G32(g, pidx(l, PK_FFN_NORM)), g->colsum_partial, N, D, st));
+
+    // ---- attention: x2 = x + (att @ Wo + bo); dres = dx2
+    TB_TRY(linear_dw(g, a.att, g->dres16, G32(g, pidx(l, PK_WO)), N, D, D));
+    TB_TRY(launch_colsum_f32(c, g->dres, G32(g, pidx(l, PK_BO)), g->colsum_partial, N, D, st));
+    TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WO)), nullptr, g->datt, N, D, D));
+    TB_TRY(launch_heads_split(c, g->datt, g->dO, B, T, H, hd, st));
+    {   // dV = P^T dO
+        GemmArgs v;
+        v.kind = GEMM_TN; v.A = a.P; v.B = g->dO; v.M = T; v.N = hd; v.K = T; v.lda = Tp; v.ldb = hd;
+        v.batch = BH; v.strideA = sTT; v.strideB = sThd;
+        v.C32 = g->dV; v.ldc32 = hd; v.strideC32 = sThd; v.causal = CAUSAL_K_SUFFIX; v.splits = 1;
+        TB_TRY(gemm(g, v));
+    }
+    {   // dP = dO V^T
+        GemmArgs p;
+        p.kind = GEMM_NT; p.A = g->dO; p.B = a.V; p.M = T; p.N = T; p.K = hd; p.lda = hd; p.ldb = hd;
+        p.batch = BH; p.strideA = sThd; p.strideB = sThd;
+        p.C32 = g->dP; p.ldc32 = Tp; p.strideC32 = sTT; p.causal = CAUSAL_SKIP_UPPER; p.splits = 1;
+        TB_TRY(gemm(g, p));
+    }
+    TB_TRY(launch_attn_softmax_bwd(c, a.P, g->dP, g->dS, BH, T, Tp, g->scale, st));
+    {   // dQ = dS K
+        GemmArgs q;
+        q.kind = GEMM_NN; q.A = g->dS; q.B = a.K; q.M = T; q.N = hd; q.K = T; q.lda = Tp; q.ldb = hd;
+        q.batch = BH; q.strideA = sTT; q.strideB = sThd;
+        q.C32 = g->dQ; q.ldc32 = hd; q.strideC32 = sThd; q.causal = CAUSAL_K_PREFIX; q.splits = 1;
+        TB_TRY(gemm(g, q));
+    }
+    {   // dK = dS^T Q
+        GemmArgs k;
+        k.kind = GEMM_TN; k.A = g->dS; k.B = a.Q; k.M = T; k.N = hd; k.K = T; k.lda = Tp; k.ldb = hd;
+        k.batch = BH; k.strideA = sTT; k.strideB = sThd;
+        k.C32 = g->dK; k.ldc32 = hd; k.strideC32 = sThd; k.causal = CAUSAL_K_SUFFIX; k.splits = 1;
+        TB_TRY(gemm(g, k));
+    }
+    TB_TRY(launch_rope_merge_bwd(c, g->dQ, g->dK, g->dV, g->cos_t, g->sin_t, g->dqkv, B, T, H, hd, st));
+    TB_TRY(linear_dw(g, a.n1, g->dqkv, G32(g, pidx(l, PK_WQKV)), N, 3 * D, D));
+    TB_TRY(launch_colsum_bf16(c, g->dqkv, G32(g, pidx(l, PK_BQKV)), g->colsum_partial, N, 3 * D, st));
+    TB_TRY(linear_dx(g, g->dqkv, P16(g, pidx(l, PK_WQKV)), g->dn, nullptr, N, 3 * D, D));
+    TB_TRY(launch_rmsnorm_bwd(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.r1, g->dn, g->dres, g->dres16, g->wtmp, N, D,
+                              1, st));
+    TB_TRY(launch_colsum_f32(c, g->wtmp, G32(g, pidx(l, PK_ATTN_NORM)), g->colsum_partial, N, D, st));
+    return 0;
+}
+
+int backward_embed(TbTrainer* g) {
+    return launch_embed_bwd(g->ctx, g->dres, g->order, g->seg_start, g->seg_token, g->nseg, G32(g, 0), g->D,
+                            g->stream);
+}
+
+// Stages ids/targets through pinned memory and starts their copy to the device.
+int stage_inputs(TbTrainer* g, const uint32_t* ids, const uint32_t* targets) {
+    const size_t bytes = (size_t)g->N * sizeof(uint32_t);
+    for (int i = 0; i < g->N; ++i)
+        TB_CHECK(ids[i] < (uint32_t)g->V && targets[i] < (uint32_t)g->V, "token id out of range at position %d", i);
+    std::memcpy(g->h_ids, ids, bytes);
+    std::memcpy(g->h_targets, targets, bytes);
+    TB_CUDA(cudaMemcpyAsync(g->ids, g->h_ids, bytes, cudaMemcpyHostToDevice, g->stream));
+    TB_CUDA(cudaMemcpyAsync(g->targets, g->h_targets, bytes, cudaMemcpyHostToDevice, g->stream));
+    return 0;
+}
+
+// Rows grouped by token (ties in ascending position) for the embedding gradient.
+int stage_segments(TbTrainer* g) {
+    const int N = g->N;
+    std::vector<uint64_t> keys(N);
+    for (int i = 0; i < N; ++i) keys[i] = ((uint64_t)g->h_ids[i] << 32) | (uint32_t)i;
+    std::sort(keys.begin(), keys.end());
+    uint32_t* order = g->h_seg;
+    uint32_t* seg_start = g->h_seg + N;
+    uint32_t* seg_token = g->h_seg + 2 * N + 1;
+    int nseg = 0;
+    for (int i = 0; i < N; ++i) {
+        order[i] = (uint32_t)(keys[i] & 0xffffffffu);
+        const uint32_t tok = (uint32_t)(keys[i] >> 32);
+        if (i == 0 || tok != (uint32_t)(keys[i - 1] >> 32)) {
+            seg_start[nseg] = (uint32_t)i;
+            seg_token[nseg] = tok;
+            ++nseg;
+        }
+    }
+    seg_start[nseg] = (uint32_t)N;
+    g->nseg = nseg;
+    const size_t b = sizeof(uint32_t);
+    TB_CUDA(cudaMemcpyAsync(g->order, order, N * b, cudaMemcpyHostToDevice, g->stream));
+    TB_CUDA(cudaMemcpyAsync(g->seg_start, seg_start, (nseg + 1) * b, cudaMemcpyHostToDevice, g->stream));
+    TB_CUDA(cudaMemcpyAsync(g->seg_token, seg_token, nseg * b, cudaMemcpyHostToDevice, g->stream));
+    return 0;
+}
+
+// mean over the T rows of each sequence, then over sequences (gpu_train.c:478-487)
+float mean_loss_host(const TbTrainer* g) {
+    float loss_sum = 0.0f;
+    for (int b = 0; b < g->B; ++b) {
+        float s = 0.0f;
+        for (int t = 0; t < g->T; ++t) s += g->h_loss_rows[(size_t)b * g->T + t];
+        loss_sum += s / (float)g->T;
+    }
+    return loss_sum / (float)g->B;
+}
+
+int read_loss(TbTrainer* g, float* loss_out) {
+    TB_CUDA(cudaMemcpyAsync(g->h_loss_rows, g->loss_rows, (size_t)g->N * sizeof(float), cudaMemcpyDeviceToHost,
+                            g->stream));
+    TB_TRY(check_device_error(g->ctx, g->stream));
+    if (loss_out) *loss_out = mean_loss_host(g);
+    return 0;
+}
+
+int adam_launch(TbTrainer* g, uint64_t t, float lr, float b1, float b2, float eps, float grad_scale,
+                const float* dev_scale) {
+    const float bc1 = 1.0f - powf(b1, (float)t);
+    const float bc2 = 1.0f - powf(b2, (float)t);
+    return launch_adam(g->ctx, g->params, g->params16, g->grads, g->adam_m, g->adam_v, g->total, lr, b1, b2, eps, bc1,
+                       bc2, grad_scale, dev_scale, g->stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T, int B, float eps, void* stream) {
+    TB_CHECK(out != nullptr, "tb_trainer_create: out is NULL");
+    TB_CHECK(V > 0 && D > 0 && H > 0 && L >= 0 && F > 0 && T > 0 && B > 0, "trainer dims must be positive");
+    TB_CHECK(D % H == 0, "d_model %d not divisible by heads %d", D, H);
+    TB_CHECK(D % 8 == 0 && F % 8 == 0 && (D / H) % 8 == 0,
+             "d_model, d_ff and head_dim must be multiples of 8 (16-byte rows for TMA); got D=%d F=%d hd=%d", D, F,
+             D / H);
+    TbTrainer* g = new TbTrainer();
+    TB_TRY(get_ctx(&g->ctx));
+    g->device = g->ctx->device;
+    g->stream = static_cast<cudaStream_t>(stream);
+    g->V = V; g->D = D; g->H = H; g->L = L; g->F = F; g->T = T; g->B = B; g->N = B * T; g->hd = D / H;
+    g->Vp = round_up(V, 8);
+    g->Tp = round_up(T, 8);
+    g->eps = eps;
+    g->scale = 1.0f / sqrtf((float)g->hd);
+
+    // flat layout in lm_collect_params order (model/lm_model.c:84-98)
+    auto push = [&](long long n) { g->offsets.push_back(g->total); g->numels.push_back(n); g->total += n; };
+    push((long long)V * D);
+    for (int l = 0; l < L; ++l) {
+        push(D); push((long long)D * 3 * D); push(3LL * D); push((long long)D * D); push(D);
+        push(D); push((long long)D * 2 * F); push(2LL * F); push((long long)F * D); push(D);
+    }
+    push(D);
+
+    const size_t N = g->N, BHT = (size_t)B * H * T;
+    const size_t Tp = (size_t)g->Tp;
+    TB_TRY(dalloc(g, &g->params, g->total)); TB_TRY(dalloc(g, &g->grads, g->total));
+    TB_TRY(dalloc(g, &g->adam_m, g->total)); TB_TRY(dalloc(g, &g->adam_v, g->total));
+    TB_TRY(dalloc(g, &g->params16, g->total));
+    TB_CUDA(cudaMemset(g->params, 0, g->total * 4)); TB_CUDA(cudaMemset(g->grads, 0, g->total * 4));
+    TB_CUDA(cudaMemset(g->adam_m, 0, g->total * 4)); TB_CUDA(cudaMemset(g->adam_v, 0, g->total * 4));
+    TB_CUDA(cudaMemset(g->params16, 0, g->total * 2));
+
+    g->layers.resize(L);
+    for (int l = 0; l < L; ++l) {
+        LayerActs& a = g->layers[l];
+        TB_TRY(dalloc(g, &a.x_in, N * D)); TB_TRY(dalloc(g, &a.n1, N * D)); TB_TRY(dalloc(g, &a.r1, N));
+        TB_TRY(dalloc(g, &a.Q, N * D)); TB_TRY(dalloc(g, &a.K, N * D)); TB_TRY(dalloc(g, &a.V, N * D));
+        TB_TRY(dalloc(g, &a.P, BHT * Tp)); TB_TRY(dalloc(g, &a.att, N * D));
+        TB_TRY(dalloc(g, &a.x2, N * D)); TB_TRY(dalloc(g, &a.n2, N * D)); TB_TRY(dalloc(g, &a.r2, N));
+        TB_TRY(dalloc(g, &a.gu, N * 2 * F)); TB_TRY(dalloc(g, &a.h, N * F));
+    }
+    TB_TRY(dalloc(g, &g->x_final, N * D)); TB_TRY(dalloc(g, &g->nf, N * D)); TB_TRY(dalloc(g, &g->rf, N));
+    TB_TRY(dalloc(g, &g->logits, N * g->Vp)); TB_TRY(dalloc(g, &g->dlogits, N * g->Vp));
+    TB_TRY(dalloc(g, &g->qkv, N * 3 * D)); TB_TRY(dalloc(g, &g->S, BHT * Tp)); TB_TRY(dalloc(g, &g->dP, BHT * Tp));
+    TB_TRY(dalloc(g, &g->dn, N * D)); TB_TRY(dalloc(g, &g->dres, N * D)); TB_TRY(dalloc(g, &g->wtmp, N * D));
+    TB_TRY(dalloc(g, &g->dh, N * F));
+    TB_TRY(dalloc(g, &g->dQ, N * D)); TB_TRY(dalloc(g, &g->dK, N * D)); TB_TRY(dalloc(g, &g->dV, N * D));
+    TB_TRY(dalloc(g, &g->dres16, N * D)); TB_TRY(dalloc(g, &g->dgu, N * 2 * F)); TB_TRY(dalloc(g, &g->datt, N * D));
+    TB_TRY(dalloc(g, &g->dO, N * D)); TB_TRY(dalloc(g, &g->dS, BHT * Tp)); TB_TRY(dalloc(g, &g->dqkv, N * 3 * D));
+    TB_TRY(dalloc(g, &g->colsum_partial, colsum_partial_floats(std::max(3 * D, 2 * F))));
+    // dS and P rows are read by whole 128-tiles: start them from zero so never-written tails are finite
+    TB_CUDA(cudaMemset(g->dS, 0, BHT * Tp * 2));
+    for (int l = 0; l < L; ++l) TB_CUDA(cudaMemset(g->layers[l].P, 0, BHT * Tp * 2));
+
+    // split-K partials for the weight-gradient GEMMs: the largest is [D, 2F] or [D, 3D] or [F, D]
+    {
+        // a split count never exceeds SMs / tiles, so splits * M * N stays below about one 128x128
+        // tile per SM, plus one unsplit copy of the largest weight matrix for rounding slack
+        size_t biggest = std::max({(size_t)D * 2 * F, (size_t)D * 3 * D, (size_t)F * D, (size_t)D * D});
+        g->splitk_floats = biggest + 2 * (size_t)g->ctx->sm_count * 128 * 128;
+        TB_TRY(dalloc(g, &g->splitk_ws, g->splitk_floats));
+    }
+
+    TB_TRY(dalloc(g, &g->ids, N)); TB_TRY(dalloc(g, &g->targets, N)); TB_TRY(dalloc(g, &g->order, N));
+    TB_TRY(dalloc(g, &g->seg_start, N + 1)); TB_TRY(dalloc(g, &g->seg_token, N));
+    TB_TRY(dalloc(g, &g->loss_rows, N));
+    TB_TRY(dalloc(g, &g->norm_partial, (size_t)kNormBlocks)); TB_TRY(dalloc(g, &g->scalars, 4));
+    TB_TRY(dalloc(g, &g->norm64, 1));
+    TB_CUDA(cudaMallocHost(&g->h_ids, N * 4)); TB_CUDA(cudaMallocHost(&g->h_targets, N * 4));
+    TB_CUDA(cudaMallocHost(&g->h_seg, (3 * N + 2) * 4)); TB_CUDA(cudaMallocHost(&g->h_loss_rows, N * 4));
+    TB_CUDA(cudaMallocHost(&g->h_norm, sizeof(double)));
+
+    // RoPE tables [T, hd/2] (model/rope.c:4-18), built on the host in float32
+    {
+        const int half = g->hd / 2;
+        std::vector<float> ct((size_t)T * half), sn((size_t)T * half);
+        for (int pos = 0; pos < T; ++pos)
+            for (int k = 0; k < half; ++k) {
+                const float exponent = -(2.0f * (float)k) / (float)g->hd;
+                const float theta = powf(10000.0f, exponent);
+                const float angle = (float)pos * theta;
+                ct[(size_t)pos * half + k] = cosf(angle);
+                sn[(size_t)pos * half + k] = sinf(angle);
+            }
+        TB_TRY(dalloc(g, &g->cos_t, ct.size())); TB_TRY(dalloc(g, &g->sin_t, sn.size()));
+        TB_CUDA(cudaMemcpy(g->cos_t, ct.data(), ct.size() * 4, cudaMemcpyHostToDevice));
+        TB_CUDA(cudaMemcpy(g->sin_t, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+    }
+    *out = g;
+    return 0;
+}
+
+int tb_trainer_destroy(TbTrainer* g) {
+    if (!g) return 0;
+    cudaDeviceSynchronize();
+    for (void* p : g->allocs) cudaFree(p);
+    cudaFreeHost(g->h_ids); cudaFreeHost(g->h_targets); cudaFreeHost(g->h_seg);
+    cudaFreeHost(g->h_loss_rows); cudaFreeHost(g->h_norm);
+    delete g;
+    return 0;
+}
+
+int64_t tb_trainer_total_scalars(const TbTrainer* g) { return g->total; }
+int tb_trainer_num_params(const TbTrainer* g) { return (int)g->offsets.size(); }
+
+int tb_trainer_param_layout(const TbTrainer* g, int64_t* offsets, int64_t* numels) {
+    for (size_t i = 0; i < g->offsets.size(); ++i) { offsets[i] = g->offsets[i]; numels[i] = g->numels[i]; }
+    return 0;
+}
+
+static float* flat_ptr(TbTrainer* g, int which) {
+    switch (which) { case 0: return g->params; case 1: return g->grads; case 2: return g->adam_m; case 3: return g->adam_v; }
+    return nullptr;
+}
+
+void* tb_trainer_device_ptr(TbTrainer* g, int which) { return flat_ptr(g, which); }
+
+int tb_trainer_upload(TbTrainer* g, int which, const float* h_flat) {
+    float* d = flat_ptr(g, which);
+    TB_CHECK(d != nullptr, "tb_trainer_upload: unknown buffer %d", which);
+    TB_CUDA(cudaStreamSynchronize(g->stream));
+    TB_CUDA(cudaMemcpy(d, h_flat, (size_t)g->total * 4, cudaMemcpyHostToDevice));
+    if (which == 0) {
+        // refresh the bf16 shadow copy the GEMMs read
+        TB_CHECK(g->total < (1LL << 31), "model too large for the single-row pack");
+        TB_TRY(launch_pack_bf16(g->ctx, g->params, g->params16, 1, (int)g->total, g->total, g->total, 1, 0, 0,
+                                g->stream));
+        TB_CUDA(cudaStreamSynchronize(g->stream));
+    }
+    return 0;
+}
+
+int tb_trainer_download(TbTrainer* g, int which, float* h_flat) {
+    float* d = flat_ptr(g, which);
+    TB_CHECK(d != nullptr, "tb_trainer_download: unknown buffer %d", which);
+    TB_CUDA(cudaStreamSynchronize(g->stream));
+    TB_CUDA(cudaMemcpy(h_flat, d, (size_t)g->total * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int tb_trainer_zero_grads(TbTrainer* g) {
+    TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->total * 4, g->stream));
+    return 0;
+}
+
+int tb_trainer_forward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, int want_grad) {
+    TB_CUDA(cudaSetDevice(g->device));
+    TB_TRY(stage_inputs(g, h_ids, h_targets));
+    TB_TRY(forward(g, want_grad != 0));
+    if (want_grad) TB_TRY(stage_segments(g));
+    return 0;
+}
+
+int tb_trainer_backward_head(TbTrainer* g) { return backward_head(g); }
+int tb_trainer_backward_layer(TbTrainer* g, int layer) {
+    TB_CHECK(layer >= 0 && layer < g->L, "layer %d out of range", layer);
+    return backward_layer(g, layer);
+}
+int tb_trainer_backward_embed(TbTrainer* g) { return backward_embed(g); }
+int tb_trainer_read_loss(TbTrainer* g, float* loss_out) { return read_loss(g, loss_out); }
+
+int tb_trainer_forward_backward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, float* loss_out) {
+    TB_CUDA(cudaSetDevice(g->device));
+    TB_TRY(tb_trainer_zero_grads(g));
+    TB_TRY(tb_trainer_forward(g, h_ids, h_targets, 1));
+    TB_TRY(backward_head(g));
+    for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
+    TB_TRY(backward_embed(g));
+    return read_loss(g, loss_out);
+}
+
+int tb_trainer_eval_loss(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, float* loss_out) {
+    TB_CUDA(cudaSetDevice(g->device));
+    TB_TRY(tb_trainer_forward(g, h_ids, h_targets, 0));
+    return read_loss(g, loss_out);
+}
+
+int tb_trainer_grad_norm(TbTrainer* g, double* norm_out) {
+    TB_TRY(launch_sumsq_partial(g->ctx, g->grads, g->total, g->norm_partial, g->stream));
+    TB_TRY(launch_clip_scale(g->ctx, g->norm_partial, 0.0f, g->scalars, g->norm64, g->stream));
+    TB_CUDA(cudaMemcpyAsync(g->h_norm, g->norm64, sizeof(double), cudaMemcpyDeviceToHost, g->stream));
+    TB_CUDA(cudaStreamSynchronize(g->stream));
+    *norm_out = *g->h_norm;
+    return 0;
+}
+
+int tb_trainer_adam_step_scaled(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
+                                float grad_scale) {
+    TB_CHECK(t >= 1, "Adam step counter starts at 1");
+    TB_TRY(adam_launch(g, t, lr, beta1, beta2, eps, grad_scale, nullptr));
+    TB_CUDA(cudaStreamSynchronize(g->stream));
+    return 0;
+}
+
+int tb_trainer_clip_adam_async(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
+                               float max_norm, float grad_scale) {
+    TB_CHECK(t >= 1, "Adam step counter starts at 1");
+    TB_TRY(launch_sumsq_partial(g->ctx, g->grads, g->total, g->norm_partial, g->stream));
+    TB_TRY(launch_clip_scale(g->ctx, g->norm_partial, max_norm, g->scalars, g->norm64, g->stream));
+    TB_CUDA(cudaMemcpyAsync(g->h_norm, g->norm64, sizeof(double), cudaMemcpyDeviceToHost, g->stream));
+    return adam_launch(g, t, lr, beta1, beta2, eps, grad_scale, g->scalars);
+}
+
+int tb_trainer_train_step(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, uint64_t t, float lr,
+                          float beta1, float beta2, float eps, float max_norm, float* loss_out, double* norm_out) {
+    TB_CUDA(cudaSetDevice(g->device));
+    TB_TRY(tb_trainer_zero_grads(g));
+    TB_TRY(tb_trainer_forward(g, h_ids, h_targets, 1));
+    TB_TRY(backward_head(g));
+    for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
+    TB_TRY(backward_embed(g));
+    TB_TRY(tb_trainer_clip_adam_async(g, t, lr, beta1, beta2, eps, max_norm, 1.0f));
+    TB_TRY(read_loss(g, loss_out));
+    if (norm_out) *norm_out = *g->h_norm;
+    return 0;
+}
+
+}  // extern "C"

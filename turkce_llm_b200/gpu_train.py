@@ -1,0 +1,136 @@
+"""Host-side mirror of the reference's GPU-resident trainer API (model/gpu_train.h:86-125),
+a thin layer over the C ABI (include/turkce_b200.h).  Method names follow the reference's
+gpu_trainer_* functions; parameters are flat float32 numpy arrays in lm_collect_params order.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import lib
+
+PARAMS, GRADS, ADAM_M, ADAM_V = 0, 1, 2, 3
+
+
+class AdamState:
+    """The scalars of the reference's AdamOptimizer (training/adam.h): step counter and hyper-parameters."""
+
+    def __init__(self, lr=3e-4, beta1=0.9, beta2=0.999, eps=1e-8):
+        self.t = 0
+        self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
+
+
+def _u32(a):
+    a = np.ascontiguousarray(a, dtype=np.uint32)
+    return a, a.ctypes.data
+
+
+class GpuTrainer:
+    def __init__(self, V, D, H, L, F, T, B, eps=1e-5, device=0, stream=None):
+        self._lib = lib.load()
+        lib.init(device)
+        h = C.c_void_p()
+        lib.check(self._lib.tb_trainer_create(C.byref(h), V, D, H, L, F, T, B, eps, stream))
+        self.h = h
+        self.cfg = (V, D, H, L, F, T, B, eps)
+        self.total = int(self._lib.tb_trainer_total_scalars(self.h))
+        self.num_params = int(self._lib.tb_trainer_num_params(self.h))
+
+    # gpu_trainer_destroy
+    def destroy(self):
+        if self.h:
+            self._lib.tb_trainer_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+    def param_layout(self):
+        off = np.zeros(self.num_params, dtype=np.int64)
+        num = np.zeros(self.num_params, dtype=np.int64)
+        lib.check(self._lib.tb_trainer_param_layout(self.h, off.ctypes.data, num.ctypes.data))
+        return off, num
+
+    # gpu_trainer_upload / gpu_trainer_upload_grads
+    def upload(self, flat, which=PARAMS):
+        flat = np.ascontiguousarray(flat, dtype=np.float32)
+        if flat.size != self.total:
+            raise ValueError("expected %d scalars, got %d" % (self.total, flat.size))
+        lib.check(self._lib.tb_trainer_upload(self.h, which, flat.ctypes.data))
+
+    # gpu_trainer_download / gpu_trainer_download_grads
+    def download(self, which=PARAMS):
+        out = np.empty(self.total, dtype=np.float32)
+        lib.check(self._lib.tb_trainer_download(self.h, which, out.ctypes.data))
+        return out
+
+    def device_ptr(self, which):
+        return int(self._lib.tb_trainer_device_ptr(self.h, which))
+
+    # gpu_trainer_forward_backward
+    def forward_backward(self, ids, targets):
+        ids, pi = _u32(ids)
+        targets, pt = _u32(targets)
+        loss = C.c_float()
+        lib.check(self._lib.tb_trainer_forward_backward(self.h, pi, pt, C.byref(loss)))
+        return loss.value
+
+    # gpu_trainer_eval_loss
+    def eval_loss(self, ids, targets):
+        ids, pi = _u32(ids)
+        targets, pt = _u32(targets)
+        loss = C.c_float()
+        lib.check(self._lib.tb_trainer_eval_loss(self.h, pi, pt, C.byref(loss)))
+        return loss.value
+
+    # gpu_trainer_grad_norm
+    def grad_norm(self):
+        n = C.c_double()
+        lib.check(self._lib.tb_trainer_grad_norm(self.h, C.byref(n)))
+        return n.value
+
+    # gpu_trainer_adam_step / gpu_trainer_adam_step_scaled
+    def adam_step(self, opt, grad_scale=1.0):
+        opt.t += 1
+        lib.check(self._lib.tb_trainer_adam_step_scaled(self.h, opt.t, opt.lr, opt.beta1, opt.beta2, opt.eps,
+                                                        grad_scale))
+
+    def train_step(self, ids, targets, opt, max_norm=1.0):
+        """forward + backward + clip + Adam (one iteration of training/train_lm_gpu.c:212-223)."""
+        ids, pi = _u32(ids)
+        targets, pt = _u32(targets)
+        opt.t += 1
+        loss, norm = C.c_float(), C.c_double()
+        lib.check(self._lib.tb_trainer_train_step(self.h, pi, pt, opt.t, opt.lr, opt.beta1, opt.beta2, opt.eps,
+                                                  max_norm, C.byref(loss), C.byref(norm)))
+        return loss.value, norm.value
+
+    # ---- staged step for data parallelism
+    def zero_grads(self):
+        lib.check(self._lib.tb_trainer_zero_grads(self.h))
+
+    def forward(self, ids, targets, want_grad=True):
+        ids, pi = _u32(ids)
+        targets, pt = _u32(targets)
+        lib.check(self._lib.tb_trainer_forward(self.h, pi, pt, 1 if want_grad else 0))
+
+    def backward_head(self):
+        lib.check(self._lib.tb_trainer_backward_head(self.h))
+
+    def backward_layer(self, layer):
+        lib.check(self._lib.tb_trainer_backward_layer(self.h, layer))
+
+    def backward_embed(self):
+        lib.check(self._lib.tb_trainer_backward_embed(self.h))
+
+    def clip_adam_async(self, opt, max_norm=1.0, grad_scale=1.0):
+        opt.t += 1
+        lib.check(self._lib.tb_trainer_clip_adam_async(self.h, opt.t, opt.lr, opt.beta1, opt.beta2, opt.eps,
+                                                       max_norm, grad_scale))
+
+    def read_loss(self):
+        loss = C.c_float()
+        lib.check(self._lib.tb_trainer_read_loss(self.h, C.byref(loss)))
+        return loss.value

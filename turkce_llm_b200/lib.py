@@ -35,6 +35,27 @@ SIGNATURES = {
                           _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _i64,
                           _f, _f, _i, _i, _i, _vp]),
     "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
+    "tb_trainer_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "tb_trainer_destroy": (_i, [_vp]),
+    "tb_trainer_total_scalars": (_i64, [_vp]),
+    "tb_trainer_num_params": (_i, [_vp]),
+    "tb_trainer_param_layout": (_i, [_vp, _vp, _vp]),
+    "tb_trainer_upload": (_i, [_vp, _i, _vp]),
+    "tb_trainer_download": (_i, [_vp, _i, _vp]),
+    "tb_trainer_device_ptr": (_vp, [_vp, _i]),
+    "tb_trainer_forward_backward": (_i, [_vp, _vp, _vp, C.POINTER(_f)]),
+    "tb_trainer_eval_loss": (_i, [_vp, _vp, _vp, C.POINTER(_f)]),
+    "tb_trainer_grad_norm": (_i, [_vp, C.POINTER(C.c_double)]),
+    "tb_trainer_adam_step_scaled": (_i, [_vp, C.c_uint64, _f, _f, _f, _f, _f]),
+    "tb_trainer_train_step": (_i, [_vp, _vp, _vp, C.c_uint64, _f, _f, _f, _f, _f, C.POINTER(_f),
+                                   C.POINTER(C.c_double)]),
+    "tb_trainer_zero_grads": (_i, [_vp]),
+    "tb_trainer_forward": (_i, [_vp, _vp, _vp, _i]),
+    "tb_trainer_backward_head": (_i, [_vp]),
+    "tb_trainer_backward_layer": (_i, [_vp, _i]),
+    "tb_trainer_backward_embed": (_i, [_vp]),
+    "tb_trainer_clip_adam_async": (_i, [_vp, C.c_uint64, _f, _f, _f, _f, _f, _f]),
+    "tb_trainer_read_loss": (_i, [_vp, C.POINTER(_f)]),
 }
 
 _lib = None
