@@ -49,6 +49,12 @@ long long tb_launch_count(void);
 int tb_check(void* stream);
 /* cuda_shutdown (cuda/cuda_backend.h:33): frees the library's scratch memory. */
 int tb_shutdown(void);
+/* Per-launch timing with CUDA events (the reference only has wall-clock counters,
+ * model/gpu_ops.c:57-68).  Between begin and end every launch of this library on the
+ * current device is timed; end writes one text line per kernel:
+ * "<name> <launches> <total ms> <algorithmic flops> <algorithmic bytes>". */
+int tb_profile_begin(void);
+int tb_profile_end(void* stream, char* out, int cap);
 
 /* cuda_alloc / cuda_free / cuda_h2d / cuda_d2h / cuda_memset_zero / cuda_sync
  * (cuda/cuda_backend.h:42-65) for C callers that have no other CUDA runtime. */
@@ -161,6 +167,16 @@ int tb_trainer_backward_embed(TbTrainer* g);
 int tb_trainer_clip_adam_async(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
                                float max_norm, float grad_scale);
 int tb_trainer_read_loss(TbTrainer* g, float* loss_out);
+/* Copies host ids/targets to the device (and prepares the embedding-gradient row order)
+ * without running anything; tb_trainer_step_resident then runs complete training steps on
+ * those device-resident inputs with no host transfer and no host synchronisation. */
+int tb_trainer_set_inputs(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets);
+int tb_trainer_step_resident(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
+                             float max_norm);
+/* Forward on the device-resident inputs (the staged form of tb_trainer_step_resident). */
+int tb_trainer_forward_resident(TbTrainer* g, int want_grad);
+/* Gradient norm computed by the last tb_trainer_clip_adam_async (waits for the stream). */
+int tb_trainer_last_norm(TbTrainer* g, double* norm_out);
 
 #ifdef __cplusplus
 }

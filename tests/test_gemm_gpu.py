@@ -1,0 +1,248 @@
+"""Parity of the sm_100a GEMM path with the CPU oracle, through the C ABI.
+
+Two comparisons per case, both with the reference's metric max|got-want| / max|want|
+(tests/test_gpu_train.c:53-66):
+  * against the oracle with operands rounded to bf16 first -- only the float32 summation order
+    differs, so the bound is 2e-5;
+  * against the float32 oracle -- the BF16-mode bound 2e-2 the task states.
+"""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_path, rel_to_maxabs
+from oracle.pyoracle import BF16, FP32
+
+pytestmark = pytest.mark.gpu
+
+TOL_SAME_OPERANDS = 2e-5
+TOL_BF16_MODE = 2e-2
+
+KINDS = {"NN": 0, "NT": 1, "TN": 2}
+
+
+def stored_shapes(kind, M, N, K):
+    a = (K, M) if kind == 2 else (M, K)
+    b = (N, K) if kind == 1 else (K, N)
+    return a, b
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("kind", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("shape", [(1, 1, 1), (4, 5, 3), (64, 48, 32), (127, 129, 65), (128, 128, 64),
+                                   (200, 100, 72), (300, 260, 520), (1024, 384, 384)])
+def test_gemm_f32_matches_oracle(tb, oracle, kind, shape):
+    M, N, K = shape
+    k = KINDS[kind]
+    rng = np.random.default_rng(hash((kind, shape)) % (1 << 31))
+    (ar, ac), (br, bc) = stored_shapes(k, M, N, K)
+    A = rng.standard_normal((ar, ac)).astype(np.float32)
+    B = (rng.standard_normal((br, bc)) * 0.02).astype(np.float32)
+    C = torch.full((M, N), float("nan"), device="cuda")
+    tb.gemm_f32(k, dev(A), dev(B), C, M, N, K, ac, bc, N)
+    tb.sync_check()
+    got = C.cpu().numpy()
+    want16 = oracle.gemm(k // 2, k % 2, A, B, M, N, K, mode=BF16).reshape(M, N)
+    want32 = oracle.gemm(k // 2, k % 2, A, B, M, N, K, mode=FP32).reshape(M, N)
+    assert np.isfinite(got).all()
+    assert rel_to_maxabs(got, want16) <= TOL_SAME_OPERANDS
+    assert rel_to_maxabs(got, want32) <= TOL_BF16_MODE
+
+
+def test_known_answer_vectors(tb):
+    ka = json.load(open(golden_path("matmul_known_answers.json")))
+    for name in ("test_tensor_2x2", "test_cuda_4x3x5"):
+        c = ka[name]
+        A, B = np.array(c["A"], np.float32), np.array(c["B"], np.float32)
+        M, K = A.shape
+        N = B.shape[1]
+        out = np.zeros((M, N), np.float32)
+        tb.matmul_host(A, B, out, M, K, N)          # small integers and halves: exact in bf16
+        assert out.tolist() == c["C"], name
+    c = ka["test_tensor_2x2_transposed_view"]
+    At, B = np.array(c["A_stored"], np.float32), np.array(c["B"], np.float32)
+    C = torch.zeros(2, 2, device="cuda")
+    tb.gemm_f32(2, dev(At), dev(B), C, 2, 2, 2, 2, 2, 2)
+    assert C.cpu().numpy().tolist() == c["C"]
+
+
+def test_strided_batched_alpha_beta(tb, oracle):
+    """The gemm()/bf16_gemm() interface in full: leading dimensions larger than the rows,
+    batch strides, alpha and beta (model/gpu_train.c:45-78)."""
+    rng = np.random.default_rng(3)
+    M, N, K, batch = 70, 50, 40, 3
+    lda, ldb, ldc = 44, 53, 57
+    sA, sB, sC = M * lda + 5, K * ldb + 3, M * ldc + 7
+    A = rng.standard_normal(batch * sA).astype(np.float32)
+    B = rng.standard_normal(batch * sB).astype(np.float32)
+    C0 = rng.standard_normal(batch * sC).astype(np.float32)
+    C = dev(C0.copy())
+    tb.gemm_f32(0, dev(A), dev(B), C, M, N, K, lda, ldb, ldc, batch, sA, sB, sC, alpha=0.5, beta=2.0)
+    tb.sync_check()
+    want = oracle.gemm(0, 0, A, B, M, N, K, lda, ldb, ldc, batch, sA, sB, sC, alpha=0.5, beta=2.0, C_in=C0, mode=BF16)
+    got = C.cpu().numpy()
+    assert rel_to_maxabs(got, want) <= TOL_SAME_OPERANDS
+    # elements outside the [M,N] windows are untouched
+    mask = np.ones(batch * sC, bool)
+    for z in range(batch):
+        for i in range(M):
+            mask[z * sC + i * ldc: z * sC + i * ldc + N] = False
+    assert np.array_equal(got[mask], C0[mask])
+
+
+def test_gemm_bias_residual(tb, oracle):
+    """k_bf16_gemm_nn_bias semantics: NULL bias / residual are skipped (train_kernels.cu:226-329)."""
+    rng = np.random.default_rng(4)
+    M, N, K = 260, 96, 384
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    for b, r in ((bias, res), (bias, None), (None, res), (None, None)):
+        C = torch.zeros(M, N, device="cuda")
+        tb.gemm_bias_f32(dev(A), dev(B), None if b is None else dev(b), None if r is None else dev(r), C, M, N, K)
+        tb.sync_check()
+        want = oracle.gemm_bias(A, B, b, r, mode=BF16)
+        assert rel_to_maxabs(C.cpu().numpy(), want) <= TOL_SAME_OPERANDS
+
+
+@pytest.mark.parametrize("name", ["qkv", "out", "gate_up", "down"])
+def test_layer_gemms_fwd_dx_dw(tb, oracle, name):
+    """One layer's linear GEMMs at M = 4*256 tokens: forward, dX = dY W^T, dW = X^T dY
+    (the float32 oracle results are pinned to the reference by tests/golden/gemm_layer_digests.json)."""
+    import os, sys
+    sys.path.insert(0, os.path.dirname(golden_path("x")))
+    from make_golden import gemm_inputs
+    d = json.load(open(golden_path("gemm_layer_digests.json")))[name]
+    M, K, N = d["M"], d["K"], d["N"]
+    X, W, dY = gemm_inputs(d["seed"], M, K, N)
+    dX_, dW_, dY_ = dev(X), dev(W), dev(dY)
+    C = torch.zeros(M, N, device="cuda")
+    dX = torch.zeros(M, K, device="cuda")
+    dW = torch.zeros(K, N, device="cuda")
+    tb.gemm_f32(0, dX_, dW_, C, M, N, K, K, N, N)
+    tb.gemm_f32(1, dY_, dW_, dX, M, K, N, N, N, K)
+    tb.gemm_f32(2, dX_, dY_, dW, K, N, M, K, N, N)
+    tb.sync_check()
+    for got, (ta, tb_, A, B, m, n, k), key in (
+            (C, (0, 0, X, W, M, N, K), "C"), (dX, (0, 1, dY, W, M, K, N), "dX"), (dW, (1, 0, X, dY, K, N, M), "dW")):
+        got = got.cpu().numpy().reshape(-1)
+        want32 = oracle.gemm(ta, tb_, A, B, m, n, k)
+        want16 = oracle.gemm(ta, tb_, A, B, m, n, k, mode=BF16)
+        step = max(1, want32.size // 16)
+        assert np.allclose(want32[::step][:16], d[key + "_sample"], rtol=0, atol=0)   # same oracle as the fixture
+        assert rel_to_maxabs(got, want16) <= TOL_SAME_OPERANDS, key
+        assert rel_to_maxabs(got, want32) <= TOL_BF16_MODE, key
+
+
+@pytest.mark.parametrize("kind", ["NN", "NT", "TN"])
+def test_bf16_entry_tiles_splits_outputs(tb, oracle, kind):
+    """The native entry point: both tile widths, split-K with fixed-order partials, float32 and
+    bf16 outputs, bias and beta; split results are bitwise reproducible."""
+    k = KINDS[kind]
+    rng = np.random.default_rng(10 + k)
+    M, N, K = 384, 200, 4096
+    (ar, ac), (br, bc) = stored_shapes(k, M, N, K)
+    lda, ldb = (ac + 7) // 8 * 8, (bc + 7) // 8 * 8
+    A = np.zeros((ar, lda), np.float32)
+    B = np.zeros((br, ldb), np.float32)
+    A[:, :ac] = oracle.round(rng.standard_normal((ar, ac)).astype(np.float32), BF16)
+    B[:, :bc] = oracle.round(rng.standard_normal((br, bc)).astype(np.float32), BF16)
+    A16, B16 = dev(A).to(torch.bfloat16), dev(B).to(torch.bfloat16)
+    bias = rng.standard_normal(N).astype(np.float32)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    want = oracle.gemm(k // 2, k % 2, A, B, M, N, K, lda, ldb, N, beta=1.0, C_in=C0).reshape(M, N) + bias
+    results = []
+    for tile_n, splits in ((128, 1), (64, 1), (128, 8), (64, 5), (0, 0)):
+        C = dev(C0.copy())
+        C16 = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+        tb.gemm_bf16(k, A16, B16, M, N, K, lda, ldb, C32=C, ldc32=N, C16=C16, ldc16=N, bias=dev(bias), beta=1.0,
+                     splits=splits, tile_n=tile_n)
+        tb.sync_check()
+        got = C.cpu().numpy()
+        assert rel_to_maxabs(got, want) <= TOL_SAME_OPERANDS, (tile_n, splits)
+        assert rel_to_maxabs(C16.float().cpu().numpy(), want) <= 1e-2
+        C2 = dev(C0.copy())
+        tb.gemm_bf16(k, A16, B16, M, N, K, lda, ldb, C32=C2, ldc32=N, bias=dev(bias), beta=1.0, splits=splits,
+                     tile_n=tile_n)
+        assert torch.equal(C, C2), "same launch twice must be bitwise identical"
+        results.append(got)
+
+
+def test_causal_modes(tb, oracle):
+    """Batched square attention products restricted to the lower triangle."""
+    rng = np.random.default_rng(20)
+    T, hd, BH = 320, 64, 3
+    Q = oracle.round(rng.standard_normal((BH, T, hd)).astype(np.float32), BF16)
+    Kk = oracle.round(rng.standard_normal((BH, T, hd)).astype(np.float32), BF16)
+    Q16, K16 = dev(Q).to(torch.bfloat16), dev(Kk).to(torch.bfloat16)
+    S = torch.full((BH, T, T), float("nan"), device="cuda")
+    tb.gemm_bf16(1, Q16, K16, T, T, hd, hd, hd, BH, T * hd, T * hd, C32=S, ldc32=T, sC32=T * T, causal=tb.CAUSAL_SKIP_UPPER)
+    tb.sync_check()
+    want = oracle.gemm(0, 1, Q, Kk, T, T, hd, batch=BH, sA=T * hd, sB=T * hd, sC=T * T).reshape(BH, T, T)
+    got = S.cpu().numpy()
+    low = np.tril(np.ones((T, T), bool))
+    assert rel_to_maxabs(got[:, low], want[:, low]) <= TOL_SAME_OPERANDS
+    # lower-triangular P times V with the k range cut at the tile's last row
+    P = np.tril(rng.standard_normal((BH, T, T))).astype(np.float32)
+    P = oracle.round(P, BF16)
+    V = oracle.round(rng.standard_normal((BH, T, hd)).astype(np.float32), BF16)
+    O = torch.zeros(BH, T, hd, device="cuda")
+    tb.gemm_bf16(0, dev(P).to(torch.bfloat16), dev(V).to(torch.bfloat16), T, hd, T, T, hd, BH, T * T, T * hd,
+                 C32=O, ldc32=hd, sC32=T * hd, causal=tb.CAUSAL_K_PREFIX)
+    dV = torch.zeros(BH, T, hd, device="cuda")
+    tb.gemm_bf16(2, dev(P).to(torch.bfloat16), dev(V).to(torch.bfloat16), T, hd, T, T, hd, BH, T * T, T * hd,
+                 C32=dV, ldc32=hd, sC32=T * hd, causal=tb.CAUSAL_K_SUFFIX)
+    tb.sync_check()
+    wantO = oracle.gemm(0, 0, P, V, T, hd, T, batch=BH, sA=T * T, sB=T * hd, sC=T * hd)
+    wantdV = oracle.gemm(1, 0, P, V, T, hd, T, batch=BH, sA=T * T, sB=T * hd, sC=T * hd)
+    assert rel_to_maxabs(O.cpu().numpy().reshape(-1), wantO) <= TOL_SAME_OPERANDS
+    assert rel_to_maxabs(dV.cpu().numpy().reshape(-1), wantdV) <= TOL_SAME_OPERANDS
+
+
+def test_linearity_at_benchmark_size(tb):
+    """Size-independent property at the benchmark's M = 8192: (A1 + A2) W = A1 W + A2 W up to
+    float32 summation error, and the ragged 31,769-column head writes nothing past its edge."""
+    torch.manual_seed(0)
+    M, K, N = 8192, 384, 1152
+    A1 = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    A2 = (torch.randn(M, K, device="cuda") * 4).to(torch.bfloat16)
+    W = (torch.randn(K, N, device="cuda") * 0.02).to(torch.bfloat16)
+    # pick A1, A2 with an exactly representable sum
+    A1 = (A1.float() * 0 + torch.round(A1.float() * 8) / 8).to(torch.bfloat16)
+    A2 = (torch.round(A2.float() * 8) / 8).to(torch.bfloat16)
+    As = (A1.float() + A2.float()).to(torch.bfloat16)
+    assert torch.equal(As.float(), A1.float() + A2.float())
+    outs = []
+    for A in (A1, A2, As):
+        C = torch.zeros(M, N, device="cuda")
+        tb.gemm_bf16(0, A, W, M, N, K, K, N, C32=C, ldc32=N)
+        outs.append(C)
+    tb.sync_check()
+    err = (outs[2] - (outs[0] + outs[1])).abs().max().item() / outs[2].abs().max().item()
+    assert err <= 1e-5
+    V, ld = 31769, 31776
+    nf = torch.randn(256, K, device="cuda").to(torch.bfloat16)
+    E = (torch.randn(V, K, device="cuda") * 0.02).to(torch.bfloat16)
+    logits = torch.full((256, ld), -7.0, device="cuda")
+    tb.gemm_bf16(1, nf, E, 256, V, K, K, K, C32=logits, ldc32=ld)
+    tb.sync_check()
+    assert (logits[:, V:] == -7.0).all()
+    want = nf.float() @ E.float().T
+    assert ((logits[:, :V] - want).abs().max() / want.abs().max()).item() <= TOL_SAME_OPERANDS
+
+
+def test_rejects_bad_arguments(tb):
+    A = torch.zeros(8, 8, device="cuda", dtype=torch.bfloat16)
+    C = torch.zeros(8, 8, device="cuda")
+    with pytest.raises(tb.TbError):
+        tb.gemm_bf16(0, A, A, 8, 8, 8, 7, 8, C32=C, ldc32=8)       # leading dimension not a multiple of 8
+    with pytest.raises(tb.TbError):
+        tb.gemm_bf16(0, A, A, 0, 8, 8, 8, 8, C32=C, ldc32=8)       # empty problem
+    with pytest.raises(tb.TbError):
+        tb.gemm_f32(0, C, C, C, 8, 8, 8, 8, 8, 8, precision=tb.PREC_FP32)   # not built: must not fall back silently

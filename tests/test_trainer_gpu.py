@@ -1,0 +1,198 @@
+"""The GPU-resident trainer against the CPU oracle, with the checks and bounds of the reference's
+own trainer test (tests/test_gpu_train.c): loss, every gradient tensor, bitwise determinism,
+eval loss, gradient norm, Adam, lossless upload/download and the scaled-Adam identity."""
+import numpy as np
+import pytest
+
+from conftest import compare_tensor_bad, golden_path, rel_to_maxabs
+from oracle.pyoracle import BF16, FP32
+
+pytestmark = pytest.mark.gpu
+
+LOSS_TOL = 2e-2      # tests/test_gpu_train.c:119
+GRAD_TOL = 8e-2      # tests/test_gpu_train.c:128 (per tensor, scaled by max |want|)
+
+
+def make_params(oracle, cfg, seed):
+    """N(0, 0.02) matrices, unit norm weights, small random biases (so bias paths are exercised)."""
+    from turkce_llm_b200.gpu_train import GpuTrainer
+    V, D, H, L, F, T, B, eps = cfg
+    g = GpuTrainer(V, D, H, L, F, T, B, eps)
+    assert g.total == oracle.model_total_scalars(cfg)
+    rng = np.random.default_rng(seed)
+    p = (rng.standard_normal(g.total) * 0.02).astype(np.float32)
+    off, num = g.param_layout()
+    for i, (o, n) in enumerate(zip(off, num)):
+        k = (i - 1) % 10 if 0 < i < len(off) - 1 else -1
+        if i == len(off) - 1 or k in (0, 5):
+            p[o:o + n] = 1.0 + 0.05 * rng.standard_normal(n)
+    return g, p, off, num
+
+
+CASES = {
+    # the three cases of tests/test_gpu_train.c:261-271 (the last with 2 layers so the CPU oracle stays fast)
+    "off_tile": (50, 32, 2, 2, 48, 12, 5, 1e-5),
+    "long_context": (500, 64, 2, 2, 128, 1024, 2, 1e-5),
+    "real_width": (31769, 384, 6, 2, 1024, 128, 4, 1e-5),
+}
+
+
+@pytest.mark.parametrize("case", list(CASES))
+def test_forward_backward_matches_oracle(tb, oracle, case):
+    from turkce_llm_b200.gpu_train import GRADS
+    cfg = CASES[case]
+    V, D, H, L, F, T, B, eps = cfg
+    g, p, off, num = make_params(oracle, cfg, 1)
+    rng = np.random.default_rng(2)
+    ids = rng.integers(0, V, B * T).astype(np.uint32)
+    tgt = rng.integers(0, V, B * T).astype(np.uint32)
+    g.upload(p)
+    loss = g.forward_backward(ids, tgt)
+    grads = g.download(GRADS)
+    want_loss, want_grads, _ = oracle.model_forward_backward(cfg, p, ids, tgt, mode=FP32)
+    assert abs(loss - want_loss) <= LOSS_TOL * abs(want_loss)
+    assert abs(loss - want_loss) <= 1e-4 * abs(want_loss)      # in practice far tighter than the bound
+    for i, (o, n) in enumerate(zip(off, num)):
+        assert compare_tensor_bad(grads[o:o + n], want_grads[o:o + n], GRAD_TOL) == 0, "parameter %d" % i
+    # against the oracle with the same bf16 operand rounding the error is an order smaller
+    _, g16, _ = oracle.model_forward_backward(cfg, p, ids, tgt, mode=BF16, mode_dw=BF16)
+    worst = max(rel_to_maxabs(grads[o:o + n], g16[o:o + n]) for o, n in zip(off, num))
+    assert worst <= 3e-2
+
+    # bitwise determinism, eval loss == training loss (tests/test_gpu_train.c:139-161)
+    loss2 = g.forward_backward(ids, tgt)
+    grads2 = g.download(GRADS)
+    assert np.float32(loss).tobytes() == np.float32(loss2).tobytes()
+    assert np.array_equal(grads.view(np.uint32), grads2.view(np.uint32))
+    assert np.float32(g.eval_loss(ids, tgt)).tobytes() == np.float32(loss2).tobytes()
+
+    # gradient norm: float64 sum of squares, deterministic (tests/test_gpu_train.c:164-174)
+    n1, n2 = g.grad_norm(), g.grad_norm()
+    assert n1 == n2
+    assert abs(n1 - oracle.grad_norm(grads)) / oracle.grad_norm(grads) < 1e-5
+    g.destroy()
+
+
+def test_reference_golden_step(tb, oracle):
+    """The reference's CPU production path on its own small case (fixture generated from the
+    reference's sources): loss, gradients, and the weights after Adam."""
+    from turkce_llm_b200.gpu_train import ADAM_M, ADAM_V, GRADS, PARAMS, AdamState, GpuTrainer
+    gold = np.load(golden_path("model_step_small.npz"))
+    V, D, H, L, F, T, B = (int(v) for v in gold["dims"])
+    g = GpuTrainer(V, D, H, L, F, T, B, 1e-5)
+    g.upload(gold["params0"])
+    loss = g.forward_backward(gold["ids"], gold["targets"])
+    assert abs(loss - float(gold["loss"])) <= LOSS_TOL * abs(float(gold["loss"]))
+    grads = g.download(GRADS)
+    off = 0
+    for n in gold["numels"]:
+        n = int(n)
+        assert compare_tensor_bad(grads[off:off + n], gold["grads"][off:off + n], GRAD_TOL) == 0
+        off += n
+    # Adam on the reference's gradients (the reference test does the same to keep the first
+    # step's sign sensitivity out: tests/test_gpu_train.c:186-203)
+    g.upload(gold["grads"], GRADS)
+    opt = AdamState(lr=3e-4)
+    g.adam_step(opt)
+    assert opt.t == 1
+    p1 = g.download(PARAMS)
+    bad = np.abs(p1 - gold["params1"]) > 1e-3 * 3e-4 + 1e-6 * np.abs(gold["params1"])
+    assert bad.sum() == 0
+    assert rel_to_maxabs(g.download(ADAM_M), gold["adam_m"]) < 1e-6
+    assert rel_to_maxabs(g.download(ADAM_V), gold["adam_v"]) < 1e-6
+    g.destroy()
+
+
+def test_upload_download_and_scaled_adam(tb, oracle):
+    from turkce_llm_b200.gpu_train import ADAM_M, ADAM_V, GRADS, PARAMS, AdamState
+    cfg = CASES["off_tile"]
+    g, p, off, num = make_params(oracle, cfg, 5)
+    rng = np.random.default_rng(6)
+    G = rng.standard_normal(g.total).astype(np.float32)
+    g.upload(p)
+    assert np.array_equal(g.download(PARAMS).view(np.uint32), p.view(np.uint32))     # lossless round trip
+
+    def run(grads, scale):
+        g.upload(p, PARAMS)
+        g.upload(np.zeros_like(p), ADAM_M)
+        g.upload(np.zeros_like(p), ADAM_V)
+        g.upload(grads, GRADS)
+        opt = AdamState(lr=3e-4)
+        g.adam_step(opt, grad_scale=scale)
+        return g.download(PARAMS)
+
+    a = run(0.5 * G, 1.0)
+    b = run(G, 0.5)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))      # tests/test_gpu_train.c:216-250
+    want, _, _ = oracle.adam(p, 0.5 * G, np.zeros_like(p), np.zeros_like(p), 3e-4, 0.9, 0.999, 1e-8,
+                             np.float32(1 - 0.9), np.float32(1 - 0.999))
+    assert np.abs(a - want).max() <= 1e-3 * 3e-4
+    g.destroy()
+
+
+def test_train_step_equals_pieces(tb, oracle):
+    """train_step (one host read) == forward_backward + grad_norm + clip + adam_step, bitwise."""
+    from turkce_llm_b200.gpu_train import PARAMS, AdamState
+    cfg = CASES["long_context"]
+    V, D, H, L, F, T, B, eps = cfg
+    rng = np.random.default_rng(8)
+    ids = rng.integers(0, V, B * T).astype(np.uint32)
+    tgt = rng.integers(0, V, B * T).astype(np.uint32)
+    ga, p, _, _ = make_params(oracle, cfg, 7)
+    ga.upload(p)
+    oa = AdamState(lr=1e-3)
+    loss_a, norm_a = ga.train_step(ids, tgt, oa, max_norm=0.05)
+    pa = ga.download(PARAMS)
+    ga.destroy()
+    gb, _, _, _ = make_params(oracle, cfg, 7)
+    gb.upload(p)
+    ob = AdamState(lr=1e-3)
+    loss_b = gb.forward_backward(ids, tgt)
+    norm_b = gb.grad_norm()
+    scale = np.float32(0.05 / norm_b) if norm_b > 0.05 else np.float32(1.0)
+    gb.adam_step(ob, grad_scale=float(scale))
+    pb = gb.download(PARAMS)
+    assert loss_a == loss_b and norm_a == norm_b and norm_a > 0.05
+    assert rel_to_maxabs(pa, pb) < 1e-6
+    # device-resident variant: same result as the host-input variant
+    gc, _, _, _ = make_params(oracle, cfg, 7)
+    gc.upload(p)
+    oc = AdamState(lr=1e-3)
+    gc.set_inputs(ids, tgt)
+    gc.step_resident(oc, max_norm=0.05)
+    assert gc.read_loss() == loss_a
+    assert np.array_equal(gc.download(PARAMS).view(np.uint32), pa.view(np.uint32))
+    gb.destroy()
+    gc.destroy()
+
+
+def test_loss_trajectory_200_steps(tb, oracle):
+    """200 optimisation steps on the GPU (bf16 tensor-core GEMMs) against the float32 CPU oracle
+    from the same start: every loss within 1% (the bound the task states)."""
+    from turkce_llm_b200.gpu_train import AdamState
+    cfg = (300, 64, 2, 2, 128, 64, 4, 1e-5)
+    V, D, H, L, F, T, B, eps = cfg
+    g, p, _, _ = make_params(oracle, cfg, 11)
+    g.upload(p)
+    rng = np.random.default_rng(12)
+    stream = rng.zipf(1.1, 200 * B * T + 1) % V          # Zipf(1.1) ids stand in for the corpus
+    opt = AdamState(lr=1e-3)
+    pc = p.copy()
+    m = np.zeros_like(pc)
+    v = np.zeros_like(pc)
+    worst = 0.0
+    for step in range(200):
+        chunk = stream[step * B * T: (step + 1) * B * T + 1]
+        ids = chunk[:-1].astype(np.uint32)
+        tgt = chunk[1:].astype(np.uint32)
+        loss_g, _ = g.train_step(ids, tgt, opt, max_norm=1.0)
+        loss_c, grads, _ = oracle.model_forward_backward(cfg, pc, ids, tgt)
+        norm = oracle.grad_norm(grads)
+        scale = np.float32(1.0 / norm) if norm > 1.0 else np.float32(1.0)
+        t = step + 1
+        pc, m, v = oracle.adam(pc, grads, m, v, 1e-3, 0.9, 0.999, 1e-8, np.float32(1 - np.float32(0.9) ** t),
+                               np.float32(1 - np.float32(0.999) ** t), float(scale))
+        worst = max(worst, abs(loss_g - loss_c) / abs(loss_c))
+    assert worst <= 1e-2, worst
+    assert loss_c < np.log(V) - 0.3       # it actually trained
+    g.destroy()

@@ -2,6 +2,10 @@
 #include "../../include/turkce_b200.h"
 #include "common.h"
 
+#include <cstring>
+#include <map>
+#include <string>
+
 using namespace tb;
 
 static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
@@ -41,6 +45,53 @@ int tb_shutdown(void) {
     if (ctx->scratch) TB_CUDA(cudaFree(ctx->scratch));
     ctx->scratch = nullptr;
     ctx->scratch_bytes = 0;
+    return 0;
+}
+
+int tb_profile_begin(void) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    if (ctx->prof) {
+        for (auto& r : *ctx->prof) cudaEventDestroy(r.ev);
+        ctx->prof->clear();
+    }
+    ctx->prof_on = true;
+    return 0;
+}
+
+int tb_profile_end(void* stream, char* out, int cap) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    ctx->prof_on = false;
+    TB_CHECK(out != nullptr && cap > 0, "tb_profile_end: no output buffer");
+    out[0] = 0;
+    if (!ctx->prof || ctx->prof->empty()) return 0;
+    cudaEvent_t last;
+    TB_CUDA(cudaEventCreate(&last));
+    TB_CUDA(cudaEventRecord(last, S(stream)));
+    TB_CUDA(cudaEventSynchronize(last));
+    struct Agg { long long n = 0; double ms = 0, flops = 0, bytes = 0; };
+    std::map<std::string, Agg> agg;
+    auto& v = *ctx->prof;
+    for (size_t i = 0; i < v.size(); ++i) {
+        float ms = 0.f;
+        cudaEvent_t next = (i + 1 < v.size()) ? v[i + 1].ev : last;
+        if (cudaEventElapsedTime(&ms, v[i].ev, next) != cudaSuccess) ms = 0.f;
+        Agg& a = agg[v[i].tag];
+        a.n++; a.ms += ms; a.flops += v[i].flops; a.bytes += v[i].bytes;
+    }
+    std::string text;
+    char line[256];
+    for (auto& kv : agg) {
+        snprintf(line, sizeof(line), "%s %lld %.6f %.6e %.6e\n", kv.first.c_str(), kv.second.n, kv.second.ms,
+                 kv.second.flops, kv.second.bytes);
+        text += line;
+    }
+    for (auto& r : v) cudaEventDestroy(r.ev);
+    v.clear();
+    cudaEventDestroy(last);
+    strncpy(out, text.c_str(), (size_t)cap - 1);
+    out[cap - 1] = 0;
     return 0;
 }
 

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstdio>
+#include <vector>
 
 namespace tb {
 
@@ -41,6 +42,10 @@ const char* last_error();
         if (_r != 0) return _r;   \
     } while (0)
 
+// ---- optional per-launch timing: an event is recorded in front of every launch; the time
+// to the next mark on the same stream is attributed to that launch (idle gaps included).
+struct ProfRec { const char* tag; cudaEvent_t ev; double flops; double bytes; };
+
 // ---- per-device context
 struct DeviceCtx {
     int device = -1;
@@ -49,7 +54,12 @@ struct DeviceCtx {
     void* scratch = nullptr;       // growable scratch (operand packing, split-K partials)
     size_t scratch_bytes = 0;
     long long launches = 0;        // kernels launched by this library on this device
+    bool prof_on = false;
+    std::vector<ProfRec>* prof = nullptr;
 };
+
+// Records a timing mark when profiling is on (no-op otherwise).
+void prof_mark(DeviceCtx* ctx, const char* tag, double flops, double bytes, cudaStream_t stream);
 
 // Returns the context of the current device, creating it on first use.
 int get_ctx(DeviceCtx** out);

@@ -64,6 +64,16 @@ int ensure_scratch(DeviceCtx* ctx, size_t bytes) {
     return 0;
 }
 
+void prof_mark(DeviceCtx* ctx, const char* tag, double flops, double bytes, cudaStream_t stream) {
+    if (!ctx->prof_on) return;
+    if (!ctx->prof) ctx->prof = new std::vector<ProfRec>();
+    ProfRec r;
+    r.tag = tag; r.flops = flops; r.bytes = bytes;
+    if (cudaEventCreate(&r.ev) != cudaSuccess) return;
+    cudaEventRecord(r.ev, stream);
+    ctx->prof->push_back(r);
+}
+
 int check_device_error(DeviceCtx* ctx, cudaStream_t stream) {
     int h = 0;
     TB_CUDA(cudaStreamSynchronize(stream));

@@ -462,6 +462,15 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
               p.strideC16_in % 4 == 0;
     p.vecr = p.residual && (reinterpret_cast<uintptr_t>(p.residual) % 16 == 0) && p.ldr % 4 == 0 && p.strideR % 4 == 0;
 
+    {
+        // algorithmic work: the causal products touch only the lower triangle (half the MACs)
+        const double macs = (double)a.M * a.N * a.K * a.batch * (a.causal != CAUSAL_NONE ? 0.5 : 1.0);
+        const double out_bytes = (double)a.M * a.N * a.batch * ((a.C32 ? 4.0 : 0.0) + (a.C16 ? 2.0 : 0.0)) *
+                                 (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);
+        const double in_bytes = 2.0 * a.batch * ((double)a.M * a.K + (double)a.K * a.N) *
+                                (a.causal == CAUSAL_K_PREFIX || a.causal == CAUSAL_K_SUFFIX ? 0.75 : 1.0);
+        prof_mark(ctx, "gemm_bf16", 2.0 * macs, in_bytes + out_bytes, stream);
+    }
     if (bn == 64) TB_TRY(launch_impl<64>(ctx, a, p, tmA, tmB, stream));
     else          TB_TRY(launch_impl<128>(ctx, a, p, tmA, tmB, stream));
 
@@ -471,6 +480,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
         int blocks = (int)((per + 255) / 256);
         if (blocks > 4 * ctx->sm_count) blocks = 4 * ctx->sm_count;
         dim3 grid(blocks, a.batch);
+        prof_mark(ctx, "splitk_reduce", 0.0, (double)(splits + 2) * per * a.batch * 4.0, stream);
         reduce_splits_kernel<<<grid, 256, 0, stream>>>(ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits,
                                                        a.strideC32, a.strideC16, a.beta, a.bias);
         TB_CUDA(cudaGetLastError());

@@ -53,6 +53,7 @@ int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int 
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     dim3 grid((unsigned)blocks, 1, (unsigned)batch);
+    prof_mark(ctx, "pack_bf16", 0.0, (double)rows * cols * batch * 6.0, stream);
     pack_bf16_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst, vec);
     TB_CUDA(cudaGetLastError());
     ctx->launches++;

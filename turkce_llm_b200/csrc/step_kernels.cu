@@ -45,6 +45,7 @@ __global__ void embed_fwd_kernel(const float* __restrict__ E, const uint32_t* __
 int launch_embed_fwd(DeviceCtx* ctx, const float* E, const uint32_t* ids, float* x, int rows, int D,
                      cudaStream_t st) {
     const long long total = (long long)rows * D;
+    prof_mark(ctx, "embed_fwd", 0.0, 0.0, st);
     embed_fwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(E, ids, x, total, D);
     TB_LAUNCHED(ctx);
     return 0;
@@ -69,6 +70,7 @@ int launch_embed_bwd(DeviceCtx* ctx, const float* dx, const uint32_t* order, con
                      const uint32_t* seg_token, int nseg, float* dE, int D, cudaStream_t st) {
     if (nseg <= 0) return 0;
     const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : 64);
+    prof_mark(ctx, "embed_bwd", 0.0, 0.0, st);
     embed_bwd_kernel<<<nseg, threads, 0, st>>>(dx, order, seg_start, seg_token, dE, D);
     TB_LAUNCHED(ctx);
     return 0;
@@ -96,6 +98,7 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
 
 int launch_rmsnorm_fwd(DeviceCtx* ctx, const float* x, const float* w, bf16* out, float* rinv, int rows, int cols,
                        float eps, cudaStream_t st) {
+    prof_mark(ctx, "rmsnorm_fwd", 0.0, 0.0, st);
     rmsnorm_fwd_kernel<<<grid_for(rows, 8, ctx), 256, 0, st>>>(x, w, out, rinv, rows, cols, eps);
     TB_LAUNCHED(ctx);
     return 0;
@@ -130,6 +133,7 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
 
 int launch_rmsnorm_bwd(DeviceCtx* ctx, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
                        bf16* dx16, float* wtmp, int rows, int cols, int accumulate, cudaStream_t st) {
+    prof_mark(ctx, "rmsnorm_bwd", 0.0, 0.0, st);
     rmsnorm_bwd_kernel<<<grid_for(rows, 8, ctx), 256, 0, st>>>(x, w, rinv, dy, dx, dx16, wtmp, rows, cols, accumulate);
     TB_LAUNCHED(ctx);
     return 0;
@@ -168,6 +172,7 @@ int launch_rope_split(DeviceCtx* ctx, const float* qkv, const float* cos_t, cons
                       bf16* V, int B, int T, int H, int hd, cudaStream_t st) {
     TB_CHECK(hd % 2 == 0, "head dim must be even");
     const long long total = (long long)B * T * H * (hd / 2);
+    prof_mark(ctx, "rope_split", 0.0, 0.0, st);
     rope_split_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(qkv, cos_t, sin_t, Q, K, V, B, T, H, hd);
     TB_LAUNCHED(ctx);
     return 0;
@@ -206,6 +211,7 @@ __global__ void rope_merge_bwd_kernel(const float* __restrict__ dQ, const float*
 int launch_rope_merge_bwd(DeviceCtx* ctx, const float* dQ, const float* dK, const float* dV, const float* cos_t,
                           const float* sin_t, bf16* dqkv, int B, int T, int H, int hd, cudaStream_t st) {
     const long long total = (long long)B * T * H * (hd / 2);
+    prof_mark(ctx, "rope_merge_bwd", 0.0, 0.0, st);
     rope_merge_bwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(dQ, dK, dV, cos_t, sin_t, dqkv, B, T, H, hd);
     TB_LAUNCHED(ctx);
     return 0;
@@ -240,6 +246,7 @@ __global__ void attn_softmax_fwd_kernel(const float* __restrict__ S, bf16* __res
 int launch_attn_softmax_fwd(DeviceCtx* ctx, const float* S, bf16* P, int BH, int T, long long ld, float scale,
                             cudaStream_t st) {
     const long long rows = (long long)BH * T;
+    prof_mark(ctx, "attn_softmax_fwd", 0.0, 0.0, st);
     attn_softmax_fwd_kernel<<<grid_for(rows, 8, ctx, 32), 256, 0, st>>>(S, P, rows, T, ld, scale);
     TB_LAUNCHED(ctx);
     return 0;
@@ -268,6 +275,7 @@ __global__ void attn_softmax_bwd_kernel(const bf16* __restrict__ P, const float*
 int launch_attn_softmax_bwd(DeviceCtx* ctx, const bf16* P, const float* dP, bf16* dS, int BH, int T, long long ld,
                             float scale, cudaStream_t st) {
     const long long rows = (long long)BH * T;
+    prof_mark(ctx, "attn_softmax_bwd", 0.0, 0.0, st);
     attn_softmax_bwd_kernel<<<grid_for(rows, 8, ctx, 32), 256, 0, st>>>(P, dP, dS, rows, T, ld, scale);
     TB_LAUNCHED(ctx);
     return 0;
@@ -291,6 +299,7 @@ __global__ void heads_split_kernel(const bf16* __restrict__ dout, bf16* __restri
 
 int launch_heads_split(DeviceCtx* ctx, const bf16* dout, bf16* dO, int B, int T, int H, int hd, cudaStream_t st) {
     const long long total = (long long)B * T * H * hd;
+    prof_mark(ctx, "heads_split", 0.0, 0.0, st);
     heads_split_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(dout, dO, B, T, H, hd);
     TB_LAUNCHED(ctx);
     return 0;
@@ -311,6 +320,7 @@ __global__ void swiglu_fwd_kernel(const float* __restrict__ gu, bf16* __restrict
 
 int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F, cudaStream_t st) {
     const long long total = (long long)rows * F;
+    prof_mark(ctx, "swiglu_fwd", 0.0, 0.0, st);
     swiglu_fwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(gu, h, total, F);
     TB_LAUNCHED(ctx);
     return 0;
@@ -334,6 +344,7 @@ __global__ void swiglu_bwd_kernel(const float* __restrict__ gu, const float* __r
 
 int launch_swiglu_bwd(DeviceCtx* ctx, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t st) {
     const long long total = (long long)rows * F;
+    prof_mark(ctx, "swiglu_bwd", 0.0, 0.0, st);
     swiglu_bwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(gu, dh, dgu, total, F);
     TB_LAUNCHED(ctx);
     return 0;
@@ -379,6 +390,7 @@ __global__ void cross_entropy_kernel(const float* __restrict__ logits, const uin
 
 int launch_cross_entropy(DeviceCtx* ctx, const float* logits, const uint32_t* targets, float* loss_rows,
                          bf16* dlogits, int rows, int V, long long ld, float grad_scale, cudaStream_t st) {
+    prof_mark(ctx, "cross_entropy", 0.0, 0.0, st);
     cross_entropy_kernel<<<rows, 512, 0, st>>>(logits, targets, loss_rows, dlogits, V, ld, grad_scale);
     TB_LAUNCHED(ctx);
     return 0;
@@ -428,8 +440,10 @@ __global__ void colsum_stage2_kernel(const float* __restrict__ partial, float* _
 template <typename T>
 static int colsum_impl(DeviceCtx* ctx, const T* in, float* out, float* partial, int rows, int cols, cudaStream_t st) {
     dim3 grid((cols + 31) / 32, kColsumChunks), block(32, 8);
+    prof_mark(ctx, "colsum_stage1", 0.0, 0.0, st);
     colsum_stage1_kernel<T><<<grid, block, 0, st>>>(in, partial, rows, cols);
     TB_LAUNCHED(ctx);
+    prof_mark(ctx, "colsum_stage2", 0.0, 0.0, st);
     colsum_stage2_kernel<<<(cols + 127) / 128, 128, 0, st>>>(partial, out, cols);
     TB_LAUNCHED(ctx);
     return 0;
@@ -456,6 +470,7 @@ __global__ void sumsq_partial_kernel(const float* __restrict__ x, long long n, f
 }
 
 int launch_sumsq_partial(DeviceCtx* ctx, const float* x, long long n, float* partial, cudaStream_t st) {
+    prof_mark(ctx, "sumsq_partial", 0.0, 0.0, st);
     sumsq_partial_kernel<<<kNormBlocks, 256, 0, st>>>(x, n, partial);
     TB_LAUNCHED(ctx);
     return 0;
@@ -476,6 +491,7 @@ __global__ void clip_scale_kernel(const float* __restrict__ partial, float max_n
 
 int launch_clip_scale(DeviceCtx* ctx, const float* partial, float max_norm, float* scalars, double* norm64,
                       cudaStream_t st) {
+    prof_mark(ctx, "clip_scale", 0.0, 0.0, st);
     clip_scale_kernel<<<1, 32, 0, st>>>(partial, max_norm, scalars, norm64);
     TB_LAUNCHED(ctx);
     return 0;
@@ -505,6 +521,7 @@ __global__ void adam_kernel(float* __restrict__ p, bf16* __restrict__ p16, const
 int launch_adam(DeviceCtx* ctx, float* p, bf16* p16, const float* g, float* m, float* v, long long n, float lr,
                 float b1, float b2, float eps, float bc1, float bc2, float grad_scale, const float* dev_scale,
                 cudaStream_t st) {
+    prof_mark(ctx, "adam", 0.0, 0.0, st);
     adam_kernel<<<grid_for(n, 256, ctx, 32), 256, 0, st>>>(p, p16, g, m, v, n, lr, b1, b2, eps, bc1, bc2, grad_scale,
                                                             dev_scale);
     TB_LAUNCHED(ctx);

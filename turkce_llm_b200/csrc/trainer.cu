@@ -496,6 +496,36 @@ int tb_trainer_forward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_ta
     return 0;
 }
 
+int tb_trainer_set_inputs(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets) {
+    TB_CUDA(cudaSetDevice(g->device));
+    TB_TRY(stage_inputs(g, h_ids, h_targets));
+    TB_TRY(stage_segments(g));
+    TB_CUDA(cudaStreamSynchronize(g->stream));
+    return 0;
+}
+
+int tb_trainer_step_resident(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
+                             float max_norm) {
+    TB_CHECK(g->nseg > 0, "tb_trainer_step_resident: call tb_trainer_set_inputs first");
+    TB_TRY(tb_trainer_zero_grads(g));
+    TB_TRY(forward(g, true));
+    TB_TRY(backward_head(g));
+    for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
+    TB_TRY(backward_embed(g));
+    return tb_trainer_clip_adam_async(g, t, lr, beta1, beta2, eps, max_norm, 1.0f);
+}
+
+int tb_trainer_forward_resident(TbTrainer* g, int want_grad) {
+    TB_CHECK(g->nseg > 0, "tb_trainer_forward_resident: call tb_trainer_set_inputs first");
+    return forward(g, want_grad != 0);
+}
+
+int tb_trainer_last_norm(TbTrainer* g, double* norm_out) {
+    TB_CUDA(cudaStreamSynchronize(g->stream));
+    *norm_out = *g->h_norm;
+    return 0;
+}
+
 int tb_trainer_backward_head(TbTrainer* g) { return backward_head(g); }
 int tb_trainer_backward_layer(TbTrainer* g, int layer) {
     TB_CHECK(layer >= 0 && layer < g->L, "layer %d out of range", layer);

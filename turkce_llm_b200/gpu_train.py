@@ -107,6 +107,24 @@ class GpuTrainer:
                                                   max_norm, C.byref(loss), C.byref(norm)))
         return loss.value, norm.value
 
+    # ---- device-resident inputs: steps with no host transfer or synchronisation
+    def set_inputs(self, ids, targets):
+        ids, pi = _u32(ids)
+        targets, pt = _u32(targets)
+        lib.check(self._lib.tb_trainer_set_inputs(self.h, pi, pt))
+
+    def step_resident(self, opt, max_norm=1.0):
+        opt.t += 1
+        lib.check(self._lib.tb_trainer_step_resident(self.h, opt.t, opt.lr, opt.beta1, opt.beta2, opt.eps, max_norm))
+
+    def forward_resident(self, want_grad=True):
+        lib.check(self._lib.tb_trainer_forward_resident(self.h, 1 if want_grad else 0))
+
+    def last_norm(self):
+        n = C.c_double()
+        lib.check(self._lib.tb_trainer_last_norm(self.h, C.byref(n)))
+        return n.value
+
     # ---- staged step for data parallelism
     def zero_grads(self):
         lib.check(self._lib.tb_trainer_zero_grads(self.h))

@@ -22,6 +22,8 @@ SIGNATURES = {
     "tb_launch_count": (C.c_longlong, []),
     "tb_check": (_i, [_vp]),
     "tb_shutdown": (_i, []),
+    "tb_profile_begin": (_i, []),
+    "tb_profile_end": (_i, [_vp, C.c_char_p, _i]),
     "tb_alloc": (_i, [C.POINTER(_vp), C.c_uint64]),
     "tb_free": (_i, [_vp]),
     "tb_h2d": (_i, [_vp, _vp, C.c_uint64]),
@@ -56,6 +58,10 @@ SIGNATURES = {
     "tb_trainer_backward_embed": (_i, [_vp]),
     "tb_trainer_clip_adam_async": (_i, [_vp, C.c_uint64, _f, _f, _f, _f, _f, _f]),
     "tb_trainer_read_loss": (_i, [_vp, C.POINTER(_f)]),
+    "tb_trainer_set_inputs": (_i, [_vp, _vp, _vp]),
+    "tb_trainer_step_resident": (_i, [_vp, C.c_uint64, _f, _f, _f, _f, _f]),
+    "tb_trainer_forward_resident": (_i, [_vp, _i]),
+    "tb_trainer_last_norm": (_i, [_vp, C.POINTER(C.c_double)]),
 }
 
 _lib = None
@@ -106,6 +112,21 @@ def init(device=0):
 def sync_check():
     """Waits for the current stream and raises if a kernel reported a failed bounded wait."""
     check(load().tb_check(_stream()))
+
+
+def profile_begin():
+    check(load().tb_profile_begin())
+
+
+def profile_end(stream=None):
+    """Returns {kernel name: {"launches", "ms", "flops", "bytes"}} for the launches since profile_begin()."""
+    buf = C.create_string_buffer(1 << 16)
+    check(load().tb_profile_end(stream, buf, len(buf)))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms, fl, by = line.split()
+        out[name] = {"launches": int(n), "ms": float(ms), "flops": float(fl), "bytes": float(by)}
+    return out
 
 
 def launch_count():
