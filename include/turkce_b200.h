@@ -106,6 +106,24 @@ int tb_gemm_bf16(int kind, const void* d_A, const void* d_B, int M, int N, int K
                  const float* d_bias, const float* d_residual, int64_t ldr, int64_t strideR,
                  float alpha, float beta, int causal, int splits, int tile_n, void* stream);
 
+/* No counterpart in the reference.  The split-K form of tb_gemm_bf16 for hosts that must not
+ * allocate device memory: processes whose HBM is wholly owned by another allocator, and loops
+ * that cannot take cudaMalloc's device-wide synchronisation.  It calls no cudaMalloc / cudaFree
+ * and no allocating library routine; the per-split partial sums go to a 16 MiB array built into
+ * the library image (held by every GPU that loads the library until the process exits), so
+ * splits * M * N must not exceed 4,194,304 floats -- larger problems are rejected with an error.
+ *   C32 = alpha * op(A) @ op(B) [+ bias] [+ beta * C32],  one matrix, bf16 operands as tb_gemm_bf16.
+ * splits: 0 = chosen by the library, else the number of K splits (partials are added in split
+ * order: bitwise reproducible).  wait != 0: the call waits for `stream` and returns non-zero if a
+ * kernel gave up on a bounded wait; wait == 0: fully asynchronous.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+ * queries device attributes; make that first call before any stream capture begins.
+ * All calls on a device share the one array and one status word: two calls whose kernels can
+ * overlap on the GPU (different streams, no ordering between them) race on them. */
+int tb_gemm_bf16_splitk_static(int kind, const void* d_A, const void* d_B, int M, int N, int K,
+                               int64_t lda, int64_t ldb, float* d_C32, int64_t ldc32,
+                               const float* d_bias, float alpha, float beta, int splits, int wait, void* stream);
+
 /* float32 [rows, cols] (ld_src) -> bf16 [rows, cols] (ld_dst), `batch` matrices. */
 int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld_src, int64_t ld_dst,
                  int batch, int64_t stride_src, int64_t stride_dst, void* stream);

@@ -18,6 +18,7 @@
 // Split-K (weight gradients: small M,N, K = tokens) writes one partial tile per split into
 // scratch memory; reduce_splits_kernel then adds the partials in split order, so the result
 // does not depend on scheduling (the reference forbids atomics: train_kernels.cu:17-20).
+#include "../../include/turkce_b200.h"
 #include "common.h"
 #include "ptx.cuh"
 
@@ -515,4 +516,100 @@ int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, siz
     return launch_core(ctx, a, bn, splits, workspace, stream);
 }
 
+// =====================================================================================
+// Split-K GEMM that allocates nothing.
+//
+// Some hosts of this library must not call cudaMalloc at all: a process whose device memory is
+// entirely owned by another allocator (a framework's caching pool that has reserved the card, a
+// fixed partition handed to a service), and loops that cannot afford cudaMalloc's device-wide
+// synchronisation because other streams are in flight.  For them the split-K partial sums live in
+// a fixed array inside the library image instead of the growable scratch buffer, and the word that
+// reports a timed-out wait lives beside it.  Every GPU that loads the library carries the array
+// (16 MiB) until the process exits.
+//
+// In host code `g_static_partials` is only a stand-in for the symbol: its device address is looked
+// up once per device with cudaGetSymbolAddress and that address is what the kernels receive.
+constexpr size_t kStaticPartialFloats = 4u * 1024u * 1024u;   // 16 MiB: split count x batch x M x N floats
+static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
+static __device__ int g_static_status;
+
+namespace {
+struct StaticSetup {
+    bool done = false;
+    float* partials = nullptr;   // device address of g_static_partials on this device
+    int* status = nullptr;       // device address of g_static_status
+    int sm_count = 0;
+};
+StaticSetup g_static_setup[64];
+
+int static_setup(int dev, StaticSetup** out) {
+    TB_CHECK(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+    StaticSetup* s = &g_static_setup[dev];
+    if (!s->done) {
+        void* p = nullptr;
+        TB_CUDA(cudaGetSymbolAddress(&p, g_static_partials));
+        s->partials = static_cast<float*>(p);
+        TB_CUDA(cudaGetSymbolAddress(&p, g_static_status));
+        s->status = static_cast<int*>(p);
+        int major = 0;
+        TB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        TB_CHECK(major == 10, "this library is built for sm_100a only; device %d has compute capability %d.x", dev,
+                 major);
+        TB_CUDA(cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, dev));
+        s->done = true;
+    }
+    *out = s;
+    return 0;
+}
+}  // namespace
+
 }  // namespace tb
+
+extern "C" int tb_gemm_bf16_splitk_static(int kind, const void* d_A, const void* d_B, int M, int N, int K,
+                                          int64_t lda, int64_t ldb, float* d_C32, int64_t ldc32,
+                                          const float* d_bias, float alpha, float beta, int splits, int wait,
+                                          void* stream) {
+    using namespace tb;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int dev = -1;
+    TB_CUDA(cudaGetDevice(&dev));
+    StaticSetup* s = nullptr;
+    TB_TRY(static_setup(dev, &s));
+    TB_CHECK(kind >= 0 && kind <= 2, "unknown GEMM kind %d", kind);
+    TB_CHECK(d_C32 != nullptr, "tb_gemm_bf16_splitk_static writes a float32 output: d_C32 is NULL");
+
+    // a context on the stack: nothing here owns device memory
+    DeviceCtx ctx;
+    ctx.device = dev;
+    ctx.sm_count = s->sm_count;
+    ctx.d_err = s->status;
+
+    GemmArgs a;
+    a.kind = static_cast<GemmKind>(kind);
+    a.A = static_cast<const bf16*>(d_A); a.B = static_cast<const bf16*>(d_B);
+    a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldb = ldb;
+    a.C32 = d_C32; a.ldc32 = ldc32;
+    a.bias = d_bias; a.alpha = alpha; a.beta = beta;
+    TB_CHECK(M > 0 && N > 0 && K > 0, "GEMM dims must be positive (M=%d N=%d K=%d)", M, N, K);
+    const int bn = pick_bn(&ctx, a);
+    if (splits <= 0) splits = choose_splits(&ctx, a, bn);
+    const int kb_total = (K + BK - 1) / BK;
+    TB_CHECK(splits <= kb_total, "splits=%d exceeds the %d K slices of 64 this problem has", splits, kb_total);
+    const size_t need = splits > 1 ? (size_t)splits * (size_t)M * (size_t)N : 0;
+    TB_CHECK(need <= kStaticPartialFloats,
+             "tb_gemm_bf16_splitk_static: splits*M*N = %zu floats exceeds the built-in scratch of %zu floats "
+             "(16 MiB); use fewer splits or tb_gemm_bf16",
+             need, kStaticPartialFloats);
+    // the status word keeps the previous call's value: clear it; the partial sums need no clearing,
+    // every element the reduction reads is written by this call's tiles first
+    TB_CUDA(cudaMemsetAsync(s->status, 0, sizeof(int), st));
+    a.splits = splits;
+    TB_TRY(launch_core(&ctx, a, bn, splits, s->partials, st));
+    if (wait) {
+        int h = 0;
+        TB_CUDA(cudaStreamSynchronize(st));
+        TB_CUDA(cudaMemcpy(&h, s->status, sizeof(int), cudaMemcpyDeviceToHost));
+        TB_CHECK(h == 0, "tb_gemm_bf16_splitk_static: a kernel gave up on a bounded wait (code %d); output invalid", h);
+    }
+    return 0;
+}

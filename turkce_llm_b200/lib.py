@@ -36,6 +36,7 @@ SIGNATURES = {
     "tb_gemm_bf16": (_i, [_i, _vp, _vp, _i, _i, _i, _i64, _i64, _i, _i64, _i64,
                           _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _i64,
                           _f, _f, _i, _i, _i, _vp]),
+    "tb_gemm_bf16_splitk_static": (_i, [_i, _vp, _vp, _i, _i, _i, _i64, _i64, _vp, _i64, _vp, _f, _f, _i, _i, _vp]),
     "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
     "tb_trainer_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "tb_trainer_destroy": (_i, [_vp]),
@@ -154,6 +155,13 @@ def gemm_bf16(kind, A, B, M, N, K, lda, ldb, batch=1, sA=0, sB=0, C32=None, ldc3
     check(load().tb_gemm_bf16(kind, _ptr(A), _ptr(B), M, N, K, lda, ldb, batch, sA, sB,
                               _ptr(C32), ldc32, sC32, _ptr(C16), ldc16, sC16, _ptr(bias), _ptr(residual), ldr, sR,
                               alpha, beta, causal, splits, tile_n, _stream()))
+
+
+def gemm_bf16_splitk_static(kind, A, B, M, N, K, lda, ldb, C32, ldc32, bias=None, alpha=1.0, beta=0.0, splits=0,
+                            wait=True):
+    """Split-K GEMM whose scratch is built into the library image: allocates nothing (see the header)."""
+    check(load().tb_gemm_bf16_splitk_static(kind, _ptr(A), _ptr(B), M, N, K, lda, ldb, _ptr(C32), ldc32, _ptr(bias),
+                                            alpha, beta, splits, 1 if wait else 0, _stream()))
 
 
 def pack_bf16(src, dst, rows, cols, ld_src, ld_dst, batch=1, s_src=0, s_dst=0):
