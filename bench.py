@@ -224,8 +224,19 @@ def run_ours(args):
     if rank == 0:
         result["clocks"] = clocks
         result["roofline"] = roofline(prof)
+        kern = {}
+        for k, v in prof.items():
+            name = k.split(":")[0]
+            e = kern.setdefault(name, {"launches": 0, "ms": 0.0})
+            e["launches"] += v["launches"]
+            e["ms"] += v["ms"]
         result["kernels"] = {k: {"launches": v["launches"], "ms": round(v["ms"], 4)} for k, v in
-                             sorted(prof.items(), key=lambda kv: -kv[1]["ms"])}
+                             sorted(kern.items(), key=lambda kv: -kv[1]["ms"])}
+        if os.environ.get("TB_BENCH_GEMM_SHAPES"):
+            result["gemm_shapes"] = {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
+                                         "tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 1) if v["ms"] > 0 else 0}
+                                     for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])
+                                     if k.startswith("gemm_bf16")}
         if world == 1:
             result["cpu_baseline"] = cpu_baseline_port()
         print(json.dumps(result), flush=True)
@@ -237,8 +248,12 @@ def roofline(prof):
     """Roofline of the dominant kernel (the tcgen05 GEMM): algorithmic flops of all its launches in
     one step / their summed duration, against the measured sustained bf16 peak."""
     pk = peaks()
-    gemm = prof.get("gemm_bf16")
-    if not gemm or gemm["ms"] <= 0:
+    gemm = {"launches": 0, "ms": 0.0, "flops": 0.0, "bytes": 0.0}
+    for name, v in prof.items():
+        if name.startswith("gemm_bf16"):
+            for k in gemm:
+                gemm[k] += v[k]
+    if gemm["ms"] <= 0:
         return None
     achieved = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12
     total_ms = sum(v["ms"] for v in prof.values())

@@ -60,6 +60,8 @@ struct DeviceCtx {
 
 // Records a timing mark when profiling is on (no-op otherwise).
 void prof_mark(DeviceCtx* ctx, const char* tag, double flops, double bytes, cudaStream_t stream);
+// Returns a pointer that stays valid for the life of the process (for composed tags).
+const char* prof_intern(const char* text);
 
 // Returns the context of the current device, creating it on first use.
 int get_ctx(DeviceCtx** out);
@@ -95,6 +97,7 @@ struct GemmArgs {
     CausalMode causal = CAUSAL_NONE;
     int splits = 0;                         // 0 = choose; >1 uses scratch for fixed-order partial sums
     int bn = 0;                             // 0 = choose tile width (64 or 128)
+    bool pad_cols_writable = false;         // columns N .. round_up(N, 16 bytes) of each output row are padding
 };
 
 int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream);

@@ -8,6 +8,8 @@
 #include <cstdarg>
 #include <cstring>
 #include <mutex>
+#include <set>
+#include <string>
 
 namespace tb {
 
@@ -62,6 +64,13 @@ int ensure_scratch(DeviceCtx* ctx, size_t bytes) {
     TB_CUDA(cudaMalloc(&ctx->scratch, want));
     ctx->scratch_bytes = want;
     return 0;
+}
+
+const char* prof_intern(const char* text) {
+    static std::set<std::string> pool;
+    static std::mutex m;
+    std::lock_guard<std::mutex> lock(m);
+    return pool.insert(text).first->c_str();
 }
 
 void prof_mark(DeviceCtx* ctx, const char* tag, double flops, double bytes, cudaStream_t stream) {

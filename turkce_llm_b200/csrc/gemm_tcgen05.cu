@@ -22,20 +22,27 @@
 #include "common.h"
 #include "ptx.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace tb {
 
 constexpr int BM = 128;
 constexpr int BK = 64;              // bf16 elements = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;      // TMA warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;
 constexpr int STAGE_LD = 36;        // floats per staging row (32 + 4 pad: conflict-free float4 access)
 
 template <int BN> struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 128) ? 6 : 8;
-    static constexpr int STAGING_BYTES = 4 * 32 * STAGE_LD * 4;
+    static constexpr int STAGES = (BN == 128) ? 4 : 5;
+    // per epilogue warp: 2 output buffers + 1 residual buffer of 32 rows x 128 B (TMA path);
+    // the generic path uses the front of the same region (32 x 36 floats per warp)
+    static constexpr int EPI_WARP_BYTES = 3 * 4096;
+    static constexpr int STAGING_BYTES = EPI_WARPS * EPI_WARP_BYTES;
     static constexpr int BAR_BYTES = 512;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;   // 128 or 256: powers of two >= 32
@@ -54,6 +61,10 @@ struct GemmParams {
     const float* residual; long long ldr, strideR;
     float alpha, beta;
     int vec32, vec16, vecr;     // 16-byte (8-byte for bf16) vector access allowed
+    int tma_mode;               // 0: generic epilogue; 1: fp32 tile stores by TMA; 2: bf16 tile stores by TMA
+    int tma_res;                // TMA path: add res_scale * (tile of tmR) -- the residual, or the old C for beta
+    float res_scale;
+    int bias_vec;               // bias pointer is 16-byte aligned
     int* err;
 };
 
@@ -87,6 +98,7 @@ __device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t) {
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  const GemmParams p) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
@@ -102,7 +114,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint64_t* empty_bar = bars + STAGES;          // [STAGES]
     uint64_t* acc_full = bars + 2 * STAGES;       // [2]
     uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    uint64_t* res_bar = bars + 2 * STAGES + 4;    // [EPI_WARPS]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + EPI_WARPS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -111,7 +124,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], EPI_WARPS); }
+        for (int i = 0; i < EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -194,10 +208,131 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 2); }
         }
+    } else if (p.tma_mode != 0) {
+        // ------------------------------------------------ epilogue, tile stores by TMA
+        // Per 32-column chunk: tcgen05.ld -> registers (+bias, +scaled residual tile) -> this warp's
+        // 32 x 128 B staging buffer in the 128B-swizzle pattern -> one TMA store (clipped at the
+        // matrix edge by the hardware).  Two buffers per warp: the store of chunk i drains while
+        // chunk i+1 is produced; the residual tile of chunk i+1 is fetched by TMA meanwhile.
+        const int q = warp & 3;                  // TMEM lane quarter this warp may read
+        const int ew = warp - 2;                 // 0..7; warps ew and ew+4 share a quarter
+        const int half = ew >> 2;                // which half of the tile's column chunks
+        uint8_t* obuf = reinterpret_cast<uint8_t*>(staging) + ew * Cfg::EPI_WARP_BYTES;
+        uint8_t* rbuf = obuf + 8192;
+        uint64_t* rbar = res_bar + ew;
+        constexpr int NCH = BN / 64;             // chunks of 32 columns per warp and tile
+        uint32_t cnt = 0;                        // chunks produced so far (selects the output buffer)
+        uint32_t rphase = 0;
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const TileCoord c = tile_of<BN>(p, t);
+            if (c.skip) continue;
+            const int buf = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const bool have_acc = c.kb1 > c.kb0;
+            const int zc = c.z * p.splits + c.s;
+            const int zo = zc / p.c_inner, zi = zc % p.c_inner;
+            const int gm0 = c.m0 + q * 32;
+            const bool rows_in = gm0 < p.M;
+            const int col0 = c.n0 + half * (BN / 2);
+            if (p.tma_res && lane == 0 && rows_in && col0 < p.N) {
+                mbar_expect_tx(rbar, 4096);
+                tma_load_4d(rbuf, &tmR, rbar, col0, gm0, 0, c.z);
+            }
+            if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
+#pragma unroll 1
+            for (int ch = 0; ch < NCH; ++ch) {
+                const uint32_t b = cnt & 1u;
+                const int gn0 = col0 + ch * 32;
+                const bool active = rows_in && gn0 < p.N;
+                if (lane == 0) tma_store_wait_read<1>();      // output buffer b (chunk cnt-2) has been read out
+                __syncwarp();
+                uint32_t v[32];
+                if (have_acc) {
+                    tmem_ld32(t_row + (uint32_t)(ch * 32), v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
+                float o[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(v[j]) * p.alpha;
+                if (p.bias) {
+                    if (p.bias_vec && gn0 + 32 <= p.N) {
+                        const float4* b4 = reinterpret_cast<const float4*>(p.bias + gn0);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 bb = __ldg(b4 + j);
+                            o[4 * j] += bb.x; o[4 * j + 1] += bb.y; o[4 * j + 2] += bb.z; o[4 * j + 3] += bb.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (gn0 + j < p.N) o[j] += __ldg(p.bias + gn0 + j);
+                    }
+                }
+                if (p.tma_res && active) {
+                    if (!mbar_wait(rbar, rphase, abort_flag)) { ok = false; break; }
+                    rphase ^= 1u;
+                    const uint8_t* rrow = rbuf + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 r4 = *reinterpret_cast<const float4*>(rrow + ((j ^ (lane & 7)) << 4));
+                        o[4 * j] += p.res_scale * r4.x; o[4 * j + 1] += p.res_scale * r4.y;
+                        o[4 * j + 2] += p.res_scale * r4.z; o[4 * j + 3] += p.res_scale * r4.w;
+                    }
+                    // the residual buffer is free again: fetch the next chunk's tile into it
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0 && ch + 1 < NCH && gn0 + 32 < p.N) {
+                        mbar_expect_tx(rbar, 4096);
+                        tma_load_4d(rbuf, &tmR, rbar, gn0 + 32, gm0, 0, c.z);
+                    }
+                }
+                if (p.tma_mode == 1) {
+                    uint8_t* orow = obuf + b * 4096 + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(orow + ((j ^ (lane & 7)) << 4)) =
+                            make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                } else {
+                    uint8_t* orow = obuf + b * 4096 + lane * 64;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint4 pk;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * j + 0], o[8 * j + 1]);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * j + 2], o[8 * j + 3]);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * j + 4], o[8 * j + 5]);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * j + 6], o[8 * j + 7]);
+                        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(orow + ((j ^ ((lane >> 1) & 3)) << 4)) = pk;
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (active) tma_store_4d(&tmC, obuf + b * 4096, gn0, gm0, zi, zo);
+                    tma_store_commit();
+                }
+                ++cnt;
+            }
+            if (!ok) break;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            ++it;
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 3); }
     } else {
-        // ---------------------------------------------------------------- epilogue
+        // ------------------------------------------- epilogue, generic (any alignment)
         const int q = warp & 3;                        // TMEM lane quarter this warp may read
-        float* stg = staging + (warp - 2) * 32 * STAGE_LD;
+        const int half = (warp - 2) >> 2;              // warps w and w+4 share a quarter: even / odd chunks
+        float* stg = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(staging) + (warp - 2) * Cfg::EPI_WARP_BYTES);
         const int r_sub = lane >> 3;                   // 0..3
         const int cg = lane & 7;                       // 0..7 -> columns 4*cg..4*cg+3
         int it = 0;
@@ -218,7 +353,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
 
 #pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
+            for (int ch = half; ch < BN / 32; ch += 2) {
                 uint32_t v[32];
                 if (have_acc) {
                     tmem_ld32(t_row + (uint32_t)(ch * 32), v);
@@ -381,6 +516,32 @@ static int make_map(CUtensorMap* map, const bf16* ptr, long long inner, long lon
     return 0;
 }
 
+// 4-D view (columns, rows, inner batch, outer batch) of an output or residual matrix with a
+// 32 x 32 element box: 128-byte rows for float32 (128B swizzle), 64-byte rows for bf16 (64B swizzle).
+static int make_map_out(CUtensorMap* map, const void* ptr, int elem_bytes, long long cols, long long rows,
+                        long long ld, long long inner, long long stride_in, long long outer, long long stride_out) {
+    EncodeTiledFn enc = get_encode_fn();
+    TB_CHECK(enc != nullptr, "cuTensorMapEncodeTiled entry point not available");
+    const cuuint64_t row_bytes = (cuuint64_t)ld * elem_bytes;
+    cuuint64_t s_in = inner > 1 ? (cuuint64_t)stride_in * elem_bytes : row_bytes * (cuuint64_t)rows;
+    cuuint64_t s_out = outer > 1 ? (cuuint64_t)stride_out * elem_bytes : row_bytes * (cuuint64_t)rows;
+    if (s_in == 0) s_in = 16;
+    if (s_out == 0) s_out = 16;
+    cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[3] = {row_bytes, s_in, s_out};
+    cuuint32_t box[4] = {32u, 32u, 1u, 1u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = enc(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     elem_bytes == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (output) failed with code %d (cols=%lld rows=%lld ld=%lld)",
+             (int)r, cols, rows, ld);
+    return 0;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
     if (a.bn == 64 || a.bn == 128) return a.bn;
     if (a.N <= 64) return 64;
@@ -407,7 +568,8 @@ int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
 
 template <int BN>
 static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, const CUtensorMap& tmA,
-                       const CUtensorMap& tmB, cudaStream_t stream) {
+                       const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmR,
+                       cudaStream_t stream) {
     using Cfg = GemmCfg<BN>;
     static bool attr_set[64] = {false};
     if (!attr_set[ctx->device & 63]) {
@@ -418,7 +580,7 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
     const long long total = (long long)p.batch * p.splits * p.mt * p.nt;
     int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     if (grid < 1) grid = 1;
-    gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, p);
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     (void)a;
@@ -470,10 +632,52 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
                                  (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);
         const double in_bytes = 2.0 * a.batch * ((double)a.M * a.K + (double)a.K * a.N) *
                                 (a.causal == CAUSAL_K_PREFIX || a.causal == CAUSAL_K_SUFFIX ? 0.75 : 1.0);
-        prof_mark(ctx, "gemm_bf16", 2.0 * macs, in_bytes + out_bytes, stream);
+        if (ctx->prof_on) {
+            char tag[128];
+            static const char* kn[3] = {"NN", "NT", "TN"};
+            snprintf(tag, sizeof(tag), "gemm_bf16:%s:%dx%dx%d:b%d:s%d:c%d:bn%d", kn[(int)a.kind], a.M, a.N, a.K,
+                     a.batch, splits, (int)a.causal, bn);
+            prof_mark(ctx, prof_intern(tag), 2.0 * macs, in_bytes + out_bytes, stream);
+        }
     }
-    if (bn == 64) TB_TRY(launch_impl<64>(ctx, a, p, tmA, tmB, stream));
-    else          TB_TRY(launch_impl<128>(ctx, a, p, tmA, tmB, stream));
+    // Tile stores by TMA when the output (and the residual / previous C) is 16-byte addressable
+    CUtensorMap tmC, tmR;
+    memset(&tmC, 0, sizeof(tmC));
+    memset(&tmR, 0, sizeof(tmR));
+    p.tma_mode = 0; p.tma_res = 0; p.res_scale = 0.0f;
+    p.bias_vec = p.bias && aligned16(p.bias);
+    {
+        const bool one_out = (p.C32 != nullptr) != (p.C16 != nullptr);
+        const int es = p.C32 ? 4 : 2;
+        const void* cptr = p.C32 ? (const void*)p.C32 : (const void*)p.C16;
+        const long long ld = p.C32 ? p.ldc32 : p.ldc16;
+        const long long so = p.C32 ? p.strideC32 : p.strideC16;
+        const long long si = p.C32 ? p.strideC32_in : p.strideC16_in;
+        const long long nz = (long long)p.batch * p.splits;
+        const bool has_res = p.residual != nullptr;
+        const bool has_beta = p.C32 != nullptr && p.beta != 0.0f;
+        // TMA stores work in 16-byte units: a row end that is not on such a boundary would spill
+        // zeros into the next few elements, so it needs the caller's word that those are padding
+        const bool row_end_ok = ((long long)p.N * es) % 16 == 0 || a.pad_cols_writable;
+        bool ok = one_out && row_end_ok && aligned16(cptr) && (ld * es) % 16 == 0 && (so * es) % 16 == 0 && (si * es) % 16 == 0 &&
+                  nz % p.c_inner == 0 && !getenv("TB_GEMM_GENERIC_EPILOGUE");
+        if (has_res && has_beta) ok = false;
+        if ((has_res || has_beta) && (p.C32 == nullptr || p.c_inner > 1)) ok = false;
+        if (has_res && !(aligned16(p.residual) && (p.ldr * 4) % 16 == 0 && (p.strideR * 4) % 16 == 0)) ok = false;
+        if (ok) {
+            TB_TRY(make_map_out(&tmC, cptr, es, p.N, p.M, ld, p.c_inner, si, nz / p.c_inner, so));
+            if (has_res) {
+                TB_TRY(make_map_out(&tmR, p.residual, 4, p.N, p.M, p.ldr, 1, 0, p.batch, p.strideR));
+                p.tma_res = 1; p.res_scale = 1.0f;
+            } else if (has_beta) {
+                tmR = tmC;
+                p.tma_res = 1; p.res_scale = p.beta;
+            }
+            p.tma_mode = p.C32 ? 1 : 2;
+        }
+    }
+    if (bn == 64) TB_TRY(launch_impl<64>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
+    else          TB_TRY(launch_impl<128>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
 
     if (splits > 1) {
         TB_CHECK(a.residual == nullptr, "split-K GEMM does not take a residual operand");

@@ -170,7 +170,7 @@ int forward(TbTrainer* g, bool want_grad) {
     {   // logits = nf @ E^T (tied head): gpu_train.c:378
         GemmArgs a;
         a.kind = GEMM_NT; a.A = g->nf; a.B = P16(g, 0); a.M = N; a.N = V; a.K = D; a.lda = D; a.ldb = D;
-        a.C32 = g->logits; a.ldc32 = g->Vp; a.splits = 1;
+        a.C32 = g->logits; a.ldc32 = g->Vp; a.splits = 1; a.pad_cols_writable = true;
         TB_TRY(gemm(g, a));
     }
     TB_TRY(launch_cross_entropy(c, g->logits, g->targets, g->loss_rows, want_grad ? g->dlogits : nullptr, N, V, g->Vp,
