@@ -148,6 +148,9 @@ def run_ours(args):
     grads_view = torch.as_tensor(DevView(g.device_ptr(GRADS), g.total), device="cuda") if world > 1 else None
     step = DataParallelStep(g, grads_view, layer_buckets(*g.param_layout()), world, dist if world > 1 else None)
     opt = AdamState(LR, BETA1, BETA2, ADAM_EPS)
+    # the trainer issues its work on a stream of its own; time and order everything on that stream
+    ext = torch.cuda.ExternalStream(g.stream_ptr())
+    torch.cuda.set_stream(ext)
 
     n_batches = 4
     stream = zipf_ids(n_batches * B * T + 1, V, seed=1 + 1000 * rank)
@@ -199,7 +202,7 @@ def run_ours(args):
     # ---- per-kernel timing of one step (CUDA events in front of every launch)
     lib.profile_begin()
     step.resident(opt, MAX_NORM)
-    prof = lib.profile_end()
+    prof = lib.profile_end(g.stream_ptr())
     torch.cuda.synchronize()
 
     tokens_per_step = B * T * world

@@ -153,6 +153,10 @@ int tb_trainer_upload(TbTrainer* g, int which, const float* h_flat);
 int tb_trainer_download(TbTrainer* g, int which, float* h_flat);
 /* Device address of a flat buffer (for a collective over the gradients). */
 void* tb_trainer_device_ptr(TbTrainer* g, int which);
+/* The cudaStream_t all of this trainer's work is issued on: the one given to tb_trainer_create,
+ * or a stream of the trainer's own when that was NULL (the step is replayed from CUDA graphs,
+ * which cannot be captured on the default stream). */
+void* tb_trainer_stream(TbTrainer* g);
 
 /* gpu_trainer_forward_backward (model/gpu_train.h:114): zeroes the gradients, runs forward and
  * backward on host ids/targets [B*T], returns the mean loss (mean inside a sequence, then over

@@ -53,10 +53,13 @@ int launch_embed_fwd(DeviceCtx* ctx, const float* E, const uint32_t* ids, float*
 
 // One block per run of equal tokens (rows pre-sorted by token, ties by position): thread j
 // adds the rows of the run in ascending position, then adds the sum to dE[token, j].
+// The grid has one block per row; blocks past the number of runs (read from device memory, so
+// that the launch shape does not depend on the batch) return at once.
 __global__ void embed_bwd_kernel(const float* __restrict__ dx, const uint32_t* __restrict__ order,
                                  const uint32_t* __restrict__ seg_start, const uint32_t* __restrict__ seg_token,
-                                 float* __restrict__ dE, int D) {
-    const int seg = blockIdx.x;
+                                 const uint32_t* __restrict__ nseg, float* __restrict__ dE, int D) {
+    const uint32_t seg = blockIdx.x;
+    if (seg >= *nseg) return;
     const uint32_t r0 = seg_start[seg], r1 = seg_start[seg + 1];
     const long long tok = seg_token[seg];
     for (int j = threadIdx.x; j < D; j += blockDim.x) {
@@ -67,11 +70,11 @@ __global__ void embed_bwd_kernel(const float* __restrict__ dx, const uint32_t* _
 }
 
 int launch_embed_bwd(DeviceCtx* ctx, const float* dx, const uint32_t* order, const uint32_t* seg_start,
-                     const uint32_t* seg_token, int nseg, float* dE, int D, cudaStream_t st) {
-    if (nseg <= 0) return 0;
+                     const uint32_t* seg_token, const uint32_t* nseg, int rows, float* dE, int D, cudaStream_t st) {
+    if (rows <= 0) return 0;
     const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : 64);
     prof_mark(ctx, "embed_bwd", 0.0, 0.0, st);
-    embed_bwd_kernel<<<nseg, threads, 0, st>>>(dx, order, seg_start, seg_token, dE, D);
+    embed_bwd_kernel<<<rows, threads, 0, st>>>(dx, order, seg_start, seg_token, nseg, dE, D);
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -129,6 +132,122 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
             wtmp[o] = dyr[j] * xr[j] * r;
         }
     }
+}
+
+// Same row math, plus the norm-weight gradient dw[j] += sum_rows dy*x*r without the [rows, cols]
+// temporary: each warp keeps its rows' column sums in registers, the block adds its warps in warp
+// order, writes one partial row, and the block that draws the last ticket adds the partials in
+// block order.  NC = ceil(cols / 32) columns per lane.
+template <int NC>
+__global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                      const float* __restrict__ rinv, const float* __restrict__ dy,
+                                      float* __restrict__ dx, bf16* __restrict__ dx16, float* __restrict__ dw,
+                                      float* __restrict__ partial, unsigned int* __restrict__ ticket, int rows,
+                                      int cols, int accumulate) {
+    extern __shared__ float sh_part[];      // [warps][cols]
+    __shared__ int is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wpb = blockDim.x >> 5;
+    float acc[NC];
+#pragma unroll
+    for (int k = 0; k < NC; ++k) acc[k] = 0.0f;
+    for (long long row = (long long)blockIdx.x * wpb + warp; row < rows; row += (long long)gridDim.x * wpb) {
+        const float* xr = x + row * cols;
+        const float* dyr = dy + row * cols;
+        const float r = rinv[row];
+        float xv[NC], dv[NC];
+        float S = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NC; ++k) {
+            const int j = lane + 32 * k;
+            xv[k] = j < cols ? xr[j] : 0.0f;
+            dv[k] = j < cols ? dyr[j] : 0.0f;
+            S += j < cols ? dv[k] * w[j] * xv[k] : 0.0f;
+        }
+        S = warp_sum(S);
+        const float kk = (r * r * r) / (float)cols;
+#pragma unroll
+        for (int k = 0; k < NC; ++k) {
+            const int j = lane + 32 * k;
+            if (j < cols) {
+                const long long o = row * cols + j;
+                float v = w[j] * r * dv[k] - kk * xv[k] * S;
+                if (accumulate) v += dx[o];
+                dx[o] = v;
+                dx16[o] = __float2bfloat16_rn(v);
+                acc[k] += dv[k] * xv[k] * r;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NC; ++k) {
+        const int j = lane + 32 * k;
+        if (j < cols) sh_part[warp * cols + j] = acc[k];
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+        float t = sh_part[j];
+        for (int k = 1; k < wpb; ++k) t += sh_part[k * cols + j];
+        partial[(long long)blockIdx.x * cols + j] = t;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1u) == gridDim.x - 1u);
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        // warp p adds the partial rows p, p+8, p+16, ... of each column in that order; then the
+        // eight sub-sums of a column are added in warp order
+        const unsigned int nb = gridDim.x;
+        for (int j0 = 0; j0 < cols; j0 += 32) {
+            const int j = j0 + lane;
+            float t = 0.0f;
+            if (j < cols) {
+                unsigned int b = warp;
+                for (; b + 3 * wpb < nb; b += 4 * wpb) {
+                    const float v0 = __ldcg(&partial[(long long)b * cols + j]);
+                    const float v1 = __ldcg(&partial[(long long)(b + wpb) * cols + j]);
+                    const float v2 = __ldcg(&partial[(long long)(b + 2 * wpb) * cols + j]);
+                    const float v3 = __ldcg(&partial[(long long)(b + 3 * wpb) * cols + j]);
+                    t += v0; t += v1; t += v2; t += v3;
+                }
+                for (; b < nb; b += wpb) t += __ldcg(&partial[(long long)b * cols + j]);
+            }
+            if (j < cols) sh_part[warp * cols + j] = t;
+        }
+        __syncthreads();
+        for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+            float t = sh_part[j];
+            for (int k = 1; k < wpb; ++k) t += sh_part[k * cols + j];
+            dw[j] += t;
+        }
+        if (threadIdx.x == 0) *ticket = 0u;
+    }
+}
+
+constexpr int kNormBwdBlocks = 296;      // partial rows of the fused norm-weight gradient
+
+size_t rmsnorm_bwd_scratch_floats(int cols) { return 64 + (size_t)kNormBwdBlocks * cols; }
+
+int launch_rmsnorm_bwd_dw(DeviceCtx* ctx, const float* x, const float* w, const float* rinv, const float* dy,
+                          float* dx, bf16* dx16, float* dw, float* scratch, int rows, int cols, int accumulate,
+                          cudaStream_t st) {
+    TB_CHECK(cols <= 1024, "fused RMSNorm backward supports at most 1024 columns (got %d)", cols);
+    int blocks = (rows + 7) / 8;
+    if (blocks > kNormBwdBlocks) blocks = kNormBwdBlocks;
+    if (blocks > 2 * ctx->sm_count) blocks = 2 * ctx->sm_count;
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch);
+    float* partial = scratch + 64;
+    const size_t smem = (size_t)8 * cols * sizeof(float);
+    prof_mark(ctx, "rmsnorm_bwd", 0.0, 0.0, st);
+    if (cols <= 384)
+        rmsnorm_bwd_dw_kernel<12><<<blocks, 256, smem, st>>>(x, w, rinv, dy, dx, dx16, dw, partial, ticket, rows, cols,
+                                                              accumulate);
+    else
+        rmsnorm_bwd_dw_kernel<32><<<blocks, 256, smem, st>>>(x, w, rinv, dy, dx, dx16, dw, partial, ticket, rows, cols,
+                                                              accumulate);
+    TB_LAUNCHED(ctx);
+    return 0;
 }
 
 int launch_rmsnorm_bwd(DeviceCtx* ctx, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
@@ -307,19 +426,31 @@ int launch_heads_split(DeviceCtx* ctx, const bf16* dout, bf16* dO, int B, int T,
 
 // --------------------------------------------------------------------- SwiGLU
 // h = g * sigmoid(g) * u with g = gu[:, :F], u = gu[:, F:]   (model/feedforward.c:9-14)
-__global__ void swiglu_fwd_kernel(const float* __restrict__ gu, bf16* __restrict__ h, long long total, int F) {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+__global__ void swiglu_fwd_kernel(const float* __restrict__ gu, bf16* __restrict__ h, long long total4, int F) {
+    const int F4 = F >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4;
          i += (long long)gridDim.x * blockDim.x) {
-        const long long n = i / F;
-        const int j = (int)(i % F);
-        const float g = gu[n * 2 * F + j], u = gu[n * 2 * F + F + j];
-        const float sg = 1.0f / (1.0f + expf(-g));
-        h[i] = __float2bfloat16_rn(g * sg * u);
+        const long long n = i / F4;
+        const int j = (int)(i % F4) << 2;
+        const float4 g = *reinterpret_cast<const float4*>(gu + n * 2 * F + j);
+        const float4 u = *reinterpret_cast<const float4*>(gu + n * 2 * F + F + j);
+        const float gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w};
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float sg = 1.0f / (1.0f + expf(-gg[e]));
+            o[e] = gg[e] * sg * uu[e];
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(h + n * F + j) = pk;
     }
 }
 
 int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F, cudaStream_t st) {
-    const long long total = (long long)rows * F;
+    TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
+    const long long total = (long long)rows * (F / 4);
     prof_mark(ctx, "swiglu_fwd", 0.0, 0.0, st);
     swiglu_fwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(gu, h, total, F);
     TB_LAUNCHED(ctx);
@@ -328,22 +459,37 @@ int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F,
 
 // dg = dh*u*(sg + g*sg*(1-sg)),  du = dh*g*sg
 __global__ void swiglu_bwd_kernel(const float* __restrict__ gu, const float* __restrict__ dh,
-                                  bf16* __restrict__ dgu, long long total, int F) {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+                                  bf16* __restrict__ dgu, long long total4, int F) {
+    const int F4 = F >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4;
          i += (long long)gridDim.x * blockDim.x) {
-        const long long n = i / F;
-        const int j = (int)(i % F);
-        const float g = gu[n * 2 * F + j], u = gu[n * 2 * F + F + j];
-        const float sg = 1.0f / (1.0f + expf(-g));
-        const float d = dh[i];
-        const float dsilu = d * u;
-        dgu[n * 2 * F + j] = __float2bfloat16_rn(dsilu * sg + dsilu * g * sg * (1.0f - sg));
-        dgu[n * 2 * F + F + j] = __float2bfloat16_rn(d * g * sg);
+        const long long n = i / F4;
+        const int j = (int)(i % F4) << 2;
+        const float4 g = *reinterpret_cast<const float4*>(gu + n * 2 * F + j);
+        const float4 u = *reinterpret_cast<const float4*>(gu + n * 2 * F + F + j);
+        const float4 d4 = *reinterpret_cast<const float4*>(dh + n * F + j);
+        const float gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+        float og[4], ou[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float sg = 1.0f / (1.0f + expf(-gg[e]));
+            const float dsilu = dd[e] * uu[e];
+            og[e] = dsilu * sg + dsilu * gg[e] * sg * (1.0f - sg);
+            ou[e] = dd[e] * gg[e] * sg;
+        }
+        __nv_bfloat162 a = __floats2bfloat162_rn(og[0], og[1]), b = __floats2bfloat162_rn(og[2], og[3]);
+        __nv_bfloat162 c = __floats2bfloat162_rn(ou[0], ou[1]), d = __floats2bfloat162_rn(ou[2], ou[3]);
+        uint2 pg, pu;
+        pg.x = *reinterpret_cast<uint32_t*>(&a); pg.y = *reinterpret_cast<uint32_t*>(&b);
+        pu.x = *reinterpret_cast<uint32_t*>(&c); pu.y = *reinterpret_cast<uint32_t*>(&d);
+        *reinterpret_cast<uint2*>(dgu + n * 2 * F + j) = pg;
+        *reinterpret_cast<uint2*>(dgu + n * 2 * F + F + j) = pu;
     }
 }
 
 int launch_swiglu_bwd(DeviceCtx* ctx, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t st) {
-    const long long total = (long long)rows * F;
+    TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
+    const long long total = (long long)rows * (F / 4);
     prof_mark(ctx, "swiglu_bwd", 0.0, 0.0, st);
     swiglu_bwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(gu, dh, dgu, total, F);
     TB_LAUNCHED(ctx);
@@ -388,10 +534,55 @@ __global__ void cross_entropy_kernel(const float* __restrict__ logits, const uin
     }
 }
 
+// One read of the row: 1024 threads hold up to 32 logits each in registers (V <= 32768).
+__global__ void __launch_bounds__(1024, 1)
+cross_entropy_row_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
+                         float* __restrict__ loss_rows, bf16* __restrict__ dlogits, int V, long long ld,
+                         float grad_scale) {
+    __shared__ float sh[32];
+    const long long row = blockIdx.x;
+    const float* z = logits + row * ld;
+    const int t = (int)targets[row];
+    float v[32];
+    float mx = -3.0e38f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        const int j = threadIdx.x + k * 1024;
+        v[k] = j < V ? z[j] : -3.0e38f;
+        mx = fmaxf(mx, v[k]);
+    }
+    mx = block_reduce(mx, sh, true);
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        const int j = threadIdx.x + k * 1024;
+        v[k] = j < V ? expf(v[k] - mx) : 0.0f;
+        sum += v[k];
+    }
+    sum = block_reduce(sum, sh, false);
+    if (threadIdx.x == 0) loss_rows[row] = (float)log((double)sum) + mx - z[t];
+    if (dlogits) {
+        const float inv = 1.0f / sum;
+        bf16* d = dlogits + row * ld;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            const int j = threadIdx.x + k * 1024;
+            if (j < V) {
+                float p = v[k] * inv;
+                if (j == t) p -= 1.0f;
+                d[j] = __float2bfloat16_rn(p * grad_scale);
+            }
+        }
+    }
+}
+
 int launch_cross_entropy(DeviceCtx* ctx, const float* logits, const uint32_t* targets, float* loss_rows,
                          bf16* dlogits, int rows, int V, long long ld, float grad_scale, cudaStream_t st) {
     prof_mark(ctx, "cross_entropy", 0.0, 0.0, st);
-    cross_entropy_kernel<<<rows, 512, 0, st>>>(logits, targets, loss_rows, dlogits, V, ld, grad_scale);
+    if (V > 4096 && V <= 32768)
+        cross_entropy_row_kernel<<<rows, 1024, 0, st>>>(logits, targets, loss_rows, dlogits, V, ld, grad_scale);
+    else
+        cross_entropy_kernel<<<rows, 512, 0, st>>>(logits, targets, loss_rows, dlogits, V, ld, grad_scale);
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -401,16 +592,24 @@ int launch_cross_entropy(DeviceCtx* ctx, const float* logits, const uint32_t* ta
 // stage 2: out[c] += partial[0][c] + partial[1][c] + ... in chunk order.
 constexpr int kColsumChunks = 64;
 
-size_t colsum_partial_floats(int cols) { return (size_t)kColsumChunks * cols; }
+// scratch of a column sum: kTicketWords ticket words (one per 32-column group; they must start at
+// zero and every launch leaves them at zero) followed by the partial sums [chunks][cols]
+constexpr int kTicketWords = 256;
+size_t colsum_partial_floats(int cols) { return (size_t)kTicketWords + (size_t)kColsumChunks * cols; }
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
 
+// One launch: every block writes the partial of its row chunk, takes a ticket, and the block that
+// draws the last ticket of a 32-column group adds that group's partials in chunk order.  The
+// ticket only decides WHO does the final sum, never its order, so the result is reproducible.
 template <typename T>
-__global__ void colsum_stage1_kernel(const T* __restrict__ in, float* __restrict__ partial, int rows, int cols) {
+__global__ void colsum_kernel(const T* __restrict__ in, float* __restrict__ out, float* __restrict__ partial,
+                              unsigned int* __restrict__ tickets, int rows, int cols) {
     __shared__ float part[8][33];
+    __shared__ int is_last;
     const int tx = threadIdx.x, ty = threadIdx.y;
     const int c = blockIdx.x * 32 + tx;
     const int chunk = blockIdx.y;
@@ -427,24 +626,43 @@ __global__ void colsum_stage1_kernel(const T* __restrict__ in, float* __restrict
         for (int k = 1; k < 8; ++k) t += part[k][tx];
         partial[(long long)chunk * cols + c] = t;
     }
-}
-
-__global__ void colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
-    float t = partial[c];
-    for (int k = 1; k < kColsumChunks; ++k) t += partial[(long long)k * cols + c];
-    out[c] += t;
+    __threadfence();
+    __syncthreads();
+    if (tx == 0 && ty == 0) is_last = (atomicAdd(&tickets[blockIdx.x], 1u) == (unsigned)kColsumChunks - 1u);
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        // lane ty adds chunks 8*ty .. 8*ty+7 in order, then lane 0 adds the eight sub-sums in order
+        float t = 0.0f;
+        if (c < cols) {
+            constexpr int per_lane = kColsumChunks / 8;
+            float v[per_lane];
+#pragma unroll
+            for (int k = 0; k < per_lane; ++k) v[k] = __ldcg(&partial[(long long)(ty * per_lane + k) * cols + c]);
+            t = v[0];
+#pragma unroll
+            for (int k = 1; k < per_lane; ++k) t += v[k];
+        }
+        __syncthreads();
+        part[ty][tx] = t;
+        __syncthreads();
+        if (ty == 0 && c < cols) {
+            float u = part[0][tx];
+#pragma unroll
+            for (int k = 1; k < 8; ++k) u += part[k][tx];
+            out[c] += u;
+        }
+        if (tx == 0 && ty == 0) tickets[blockIdx.x] = 0u;     // ready for the next launch
+    }
 }
 
 template <typename T>
 static int colsum_impl(DeviceCtx* ctx, const T* in, float* out, float* partial, int rows, int cols, cudaStream_t st) {
+    TB_CHECK((cols + 31) / 32 <= kTicketWords, "column sum supports at most %d columns", kTicketWords * 32);
     dim3 grid((cols + 31) / 32, kColsumChunks), block(32, 8);
-    prof_mark(ctx, "colsum_stage1", 0.0, 0.0, st);
-    colsum_stage1_kernel<T><<<grid, block, 0, st>>>(in, partial, rows, cols);
-    TB_LAUNCHED(ctx);
-    prof_mark(ctx, "colsum_stage2", 0.0, 0.0, st);
-    colsum_stage2_kernel<<<(cols + 127) / 128, 128, 0, st>>>(partial, out, cols);
+    unsigned int* tickets = reinterpret_cast<unsigned int*>(partial);
+    prof_mark(ctx, "colsum", 0.0, 0.0, st);
+    colsum_kernel<T><<<grid, block, 0, st>>>(in, out, partial + kTicketWords, tickets, rows, cols);
     TB_LAUNCHED(ctx);
     return 0;
 }

@@ -15,6 +15,11 @@ int launch_rmsnorm_fwd(DeviceCtx*, const float* x, const float* w, bf16* out, fl
 // dx (+)= rmsnorm backward; dx16 = bf16(dx); wtmp[n,j] = dy*x*r (summed over rows by colsum)
 int launch_rmsnorm_bwd(DeviceCtx*, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
                        bf16* dx16, float* wtmp, int rows, int cols, int accumulate, cudaStream_t);
+// the same with the norm-weight gradient fused: dw[j] += sum_rows dy*x*r (fixed order);
+// scratch needs rmsnorm_bwd_scratch_floats(cols) floats whose first 64 words start at zero
+size_t rmsnorm_bwd_scratch_floats(int cols);
+int launch_rmsnorm_bwd_dw(DeviceCtx*, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
+                          bf16* dx16, float* dw, float* scratch, int rows, int cols, int accumulate, cudaStream_t);
 int launch_rope_split(DeviceCtx*, const float* qkv, const float* cos_t, const float* sin_t, bf16* Q, bf16* K, bf16* V,
                       int B, int T, int H, int hd, cudaStream_t);
 int launch_rope_merge_bwd(DeviceCtx*, const float* dQ, const float* dK, const float* dV, const float* cos_t,
@@ -31,13 +36,14 @@ int launch_swiglu_bwd(DeviceCtx*, const float* gu, const float* dh, bf16* dgu, i
 // logits [rows, ld] fp32 -> loss_rows, dlogits bf16 [rows, ld] = (softmax - onehot) * grad_scale
 int launch_cross_entropy(DeviceCtx*, const float* logits, const uint32_t* targets, float* loss_rows, bf16* dlogits,
                          int rows, int V, long long ld, float grad_scale, cudaStream_t);
-// out[c] += sum_r in[r,c]; in is fp32 or bf16; partial needs colsum_partial_floats(cols) floats
+// out[c] += sum_r in[r,c]; in is fp32 or bf16; partial needs colsum_partial_floats(cols) floats, zeroed once
 size_t colsum_partial_floats(int cols);
 int launch_colsum_f32(DeviceCtx*, const float* in, float* out, float* partial, int rows, int cols, cudaStream_t);
 int launch_colsum_bf16(DeviceCtx*, const bf16* in, float* out, float* partial, int rows, int cols, cudaStream_t);
 // dE[token] += sum of dx rows of that token, rows taken in ascending position order
+// (nseg = number of token runs, in device memory; rows = launch size = number of rows)
 int launch_embed_bwd(DeviceCtx*, const float* dx, const uint32_t* order, const uint32_t* seg_start,
-                     const uint32_t* seg_token, int nseg, float* dE, int D, cudaStream_t);
+                     const uint32_t* seg_token, const uint32_t* nseg, int rows, float* dE, int D, cudaStream_t);
 constexpr int kNormBlocks = 1024;
 int launch_sumsq_partial(DeviceCtx*, const float* x, long long n, float* partial, cudaStream_t);
 // scalars[0] = norm (as float), scalars[1] = min(1, max_norm / norm) (1 when max_norm <= 0); norm64 = norm

@@ -19,6 +19,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -60,6 +61,7 @@ struct TbTrainer {
     float *dQ = nullptr, *dK = nullptr, *dV = nullptr;
     bf16 *dres16 = nullptr, *dgu = nullptr, *datt = nullptr, *dO = nullptr, *dS = nullptr, *dqkv = nullptr;
     float* colsum_partial = nullptr;
+    float* norm_scratch = nullptr;
     float* splitk_ws = nullptr; size_t splitk_floats = 0;
 
     uint32_t *ids = nullptr, *targets = nullptr, *order = nullptr, *seg_start = nullptr, *seg_token = nullptr;
@@ -70,7 +72,15 @@ struct TbTrainer {
     uint32_t *h_ids = nullptr, *h_targets = nullptr, *h_seg = nullptr;
     float* h_loss_rows = nullptr; double* h_norm = nullptr;
     int nseg = 0;
+    uint32_t* nseg_dev = nullptr;
     std::vector<void*> allocs;
+
+    // CUDA graphs: each segment of the step (forward, head backward, one layer's backward, ...) is
+    // run eagerly once, captured on its second use and replayed afterwards.
+    struct Segment { int state = 0; cudaGraphExec_t exec = nullptr; long long launches = 0; };
+    std::vector<Segment> segments;
+    bool graphs_on = true;
+    bool owns_stream = false;
 };
 
 namespace {
@@ -195,8 +205,8 @@ int backward_head(TbTrainer* g) {
         a.C32 = g->dn; a.ldc32 = D; a.splits = 1;
         TB_TRY(gemm(g, a));
     }
-    TB_TRY(launch_rmsnorm_bwd(c, g->x_final, P32(g, p_final), g->rf, g->dn, g->dres, g->dres16, g->wtmp, N, D, 0, st));
-    TB_TRY(launch_colsum_f32(c, g->wtmp, G32(g, p_final), g->colsum_partial, N, D, st));
+    TB_TRY(launch_rmsnorm_bwd_dw(c, g->x_final, P32(g, p_final), g->rf, g->dn, g->dres, g->dres16, G32(g, p_final),
+                                 g->norm_scratch, N, D, 0, st));
     return 0;
 }
 
@@ -216,9 +226,8 @@ int backward_layer(TbTrainer* g, int l) {
     TB_TRY(linear_dw(g, a.n2, g->dgu, G32(g, pidx(l, PK_WGU)), N, 2 * F, D));
     TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
     TB_TRY(linear_dx(g, g->dgu, P16(g, pidx(l, PK_WGU)), g->dn, nullptr, N, 2 * F, D));
-    TB_TRY(launch_rmsnorm_bwd(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.r2, g->dn, g->dres, g->dres16, g->wtmp, N, D, 1,
-                              st));
-    TB_TRY(launch_colsum_f32(c, g->wtmp, G32(g, pidx(l, PK_FFN_NORM)), g->colsum_partial, N, D, st));
+    TB_TRY(launch_rmsnorm_bwd_dw(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.r2, g->dn, g->dres, g->dres16,
+                                 G32(g, pidx(l, PK_FFN_NORM)), g->norm_scratch, N, D, 1, st));
 
     // ---- attention: x2 = x + (att @ Wo + bo); dres = dx2
     TB_TRY(linear_dw(g, a.att, g->dres16, G32(g, pidx(l, PK_WO)), N, D, D));
@@ -258,15 +267,44 @@ int backward_layer(TbTrainer* g, int l) {
     TB_TRY(linear_dw(g, a.n1, g->dqkv, G32(g, pidx(l, PK_WQKV)), N, 3 * D, D));
     TB_TRY(launch_colsum_bf16(c, g->dqkv, G32(g, pidx(l, PK_BQKV)), g->colsum_partial, N, 3 * D, st));
     TB_TRY(linear_dx(g, g->dqkv, P16(g, pidx(l, PK_WQKV)), g->dn, nullptr, N, 3 * D, D));
-    TB_TRY(launch_rmsnorm_bwd(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.r1, g->dn, g->dres, g->dres16, g->wtmp, N, D,
-                              1, st));
-    TB_TRY(launch_colsum_f32(c, g->wtmp, G32(g, pidx(l, PK_ATTN_NORM)), g->colsum_partial, N, D, st));
+    TB_TRY(launch_rmsnorm_bwd_dw(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.r1, g->dn, g->dres, g->dres16,
+                                 G32(g, pidx(l, PK_ATTN_NORM)), g->norm_scratch, N, D, 1, st));
     return 0;
 }
 
 int backward_embed(TbTrainer* g) {
-    return launch_embed_bwd(g->ctx, g->dres, g->order, g->seg_start, g->seg_token, g->nseg, G32(g, 0), g->D,
-                            g->stream);
+    return launch_embed_bwd(g->ctx, g->dres, g->order, g->seg_start, g->seg_token, g->nseg_dev, g->N, G32(g, 0),
+                            g->D, g->stream);
+}
+
+enum { SEG_FWD_TRAIN = 0, SEG_FWD_EVAL, SEG_HEAD_BWD, SEG_EMBED_BWD, SEG_ZERO, SEG_LAYER0 };
+
+// Runs `body` (a fixed sequence of launches on g->stream): eagerly the first time, under stream
+// capture the second time, as a graph launch from then on.
+template <typename Body>
+int run_segment(TbTrainer* g, int id, Body body) {
+    if (!g->graphs_on || g->ctx->prof_on) return body();
+    if ((int)g->segments.size() <= id) g->segments.resize(id + 1);
+    TbTrainer::Segment& s = g->segments[id];
+    if (s.state == 0) { s.state = 1; return body(); }
+    if (s.state == 1) {
+        const long long before = g->ctx->launches;
+        TB_CUDA(cudaStreamBeginCapture(g->stream, cudaStreamCaptureModeRelaxed));
+        const int rc = body();
+        cudaGraph_t graph = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(g->stream, &graph);
+        if (rc != 0) { if (graph) cudaGraphDestroy(graph); return rc; }
+        TB_CUDA(e);
+        s.launches = g->ctx->launches - before;
+        TB_CUDA(cudaGraphInstantiate(&s.exec, graph, 0));
+        cudaGraphDestroy(graph);
+        s.state = 2;
+        TB_CUDA(cudaGraphLaunch(s.exec, g->stream));
+        return 0;
+    }
+    TB_CUDA(cudaGraphLaunch(s.exec, g->stream));
+    g->ctx->launches += s.launches;
+    return 0;
 }
 
 // Stages ids/targets through pinned memory and starts their copy to the device.
@@ -306,6 +344,8 @@ int stage_segments(TbTrainer* g) {
     TB_CUDA(cudaMemcpyAsync(g->order, order, N * b, cudaMemcpyHostToDevice, g->stream));
     TB_CUDA(cudaMemcpyAsync(g->seg_start, seg_start, (nseg + 1) * b, cudaMemcpyHostToDevice, g->stream));
     TB_CUDA(cudaMemcpyAsync(g->seg_token, seg_token, nseg * b, cudaMemcpyHostToDevice, g->stream));
+    g->h_seg[3 * N + 1] = (uint32_t)nseg;
+    TB_CUDA(cudaMemcpyAsync(g->nseg_dev, g->h_seg + 3 * N + 1, b, cudaMemcpyHostToDevice, g->stream));
     return 0;
 }
 
@@ -351,6 +391,12 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
     TB_TRY(get_ctx(&g->ctx));
     g->device = g->ctx->device;
     g->stream = static_cast<cudaStream_t>(stream);
+    if (g->stream == nullptr) {
+        // the legacy default stream cannot be captured into a graph: work on a stream of our own
+        TB_CUDA(cudaStreamCreateWithFlags(&g->stream, cudaStreamNonBlocking));
+        g->owns_stream = true;
+    }
+    g->graphs_on = getenv("TB_NO_GRAPH") == nullptr;
     g->V = V; g->D = D; g->H = H; g->L = L; g->F = F; g->T = T; g->B = B; g->N = B * T; g->hd = D / H;
     g->Vp = round_up(V, 8);
     g->Tp = round_up(T, 8);
@@ -392,7 +438,14 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
     TB_TRY(dalloc(g, &g->dQ, N * D)); TB_TRY(dalloc(g, &g->dK, N * D)); TB_TRY(dalloc(g, &g->dV, N * D));
     TB_TRY(dalloc(g, &g->dres16, N * D)); TB_TRY(dalloc(g, &g->dgu, N * 2 * F)); TB_TRY(dalloc(g, &g->datt, N * D));
     TB_TRY(dalloc(g, &g->dO, N * D)); TB_TRY(dalloc(g, &g->dS, BHT * Tp)); TB_TRY(dalloc(g, &g->dqkv, N * 3 * D));
-    TB_TRY(dalloc(g, &g->colsum_partial, colsum_partial_floats(std::max(3 * D, 2 * F))));
+    TB_CHECK(D <= 1024, "d_model up to 1024 is supported (got %d)", D);
+    {
+        const size_t nc = colsum_partial_floats(std::max(3 * D, 2 * F)), nn = rmsnorm_bwd_scratch_floats(D);
+        TB_TRY(dalloc(g, &g->colsum_partial, nc));
+        TB_TRY(dalloc(g, &g->norm_scratch, nn));
+        TB_CUDA(cudaMemset(g->colsum_partial, 0, nc * 4));     // ticket words start at zero
+        TB_CUDA(cudaMemset(g->norm_scratch, 0, nn * 4));
+    }
     // dS and P rows are read by whole 128-tiles: start them from zero so never-written tails are finite
     TB_CUDA(cudaMemset(g->dS, 0, BHT * Tp * 2));
     for (int l = 0; l < L; ++l) TB_CUDA(cudaMemset(g->layers[l].P, 0, BHT * Tp * 2));
@@ -408,11 +461,12 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
 
     TB_TRY(dalloc(g, &g->ids, N)); TB_TRY(dalloc(g, &g->targets, N)); TB_TRY(dalloc(g, &g->order, N));
     TB_TRY(dalloc(g, &g->seg_start, N + 1)); TB_TRY(dalloc(g, &g->seg_token, N));
+    TB_TRY(dalloc(g, &g->nseg_dev, 1));
     TB_TRY(dalloc(g, &g->loss_rows, N));
     TB_TRY(dalloc(g, &g->norm_partial, (size_t)kNormBlocks)); TB_TRY(dalloc(g, &g->scalars, 4));
     TB_TRY(dalloc(g, &g->norm64, 1));
     TB_CUDA(cudaMallocHost(&g->h_ids, N * 4)); TB_CUDA(cudaMallocHost(&g->h_targets, N * 4));
-    TB_CUDA(cudaMallocHost(&g->h_seg, (3 * N + 2) * 4)); TB_CUDA(cudaMallocHost(&g->h_loss_rows, N * 4));
+    TB_CUDA(cudaMallocHost(&g->h_seg, (3 * N + 4) * 4)); TB_CUDA(cudaMallocHost(&g->h_loss_rows, N * 4));
     TB_CUDA(cudaMallocHost(&g->h_norm, sizeof(double)));
 
     // RoPE tables [T, hd/2] (model/rope.c:4-18), built on the host in float32
@@ -438,6 +492,8 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
 int tb_trainer_destroy(TbTrainer* g) {
     if (!g) return 0;
     cudaDeviceSynchronize();
+    for (auto& sgm : g->segments) if (sgm.exec) cudaGraphExecDestroy(sgm.exec);
+    if (g->owns_stream) cudaStreamDestroy(g->stream);
     for (void* p : g->allocs) cudaFree(p);
     cudaFreeHost(g->h_ids); cudaFreeHost(g->h_targets); cudaFreeHost(g->h_seg);
     cudaFreeHost(g->h_loss_rows); cudaFreeHost(g->h_norm);
@@ -488,10 +544,13 @@ int tb_trainer_zero_grads(TbTrainer* g) {
     return 0;
 }
 
+void* tb_trainer_stream(TbTrainer* g) { return g->stream; }
+
 int tb_trainer_forward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, int want_grad) {
     TB_CUDA(cudaSetDevice(g->device));
     TB_TRY(stage_inputs(g, h_ids, h_targets));
-    TB_TRY(forward(g, want_grad != 0));
+    const bool wg = want_grad != 0;
+    TB_TRY(run_segment(g, wg ? SEG_FWD_TRAIN : SEG_FWD_EVAL, [&]() { return forward(g, wg); }));
     if (want_grad) TB_TRY(stage_segments(g));
     return 0;
 }
@@ -508,16 +567,17 @@ int tb_trainer_step_resident(TbTrainer* g, uint64_t t, float lr, float beta1, fl
                              float max_norm) {
     TB_CHECK(g->nseg > 0, "tb_trainer_step_resident: call tb_trainer_set_inputs first");
     TB_TRY(tb_trainer_zero_grads(g));
-    TB_TRY(forward(g, true));
-    TB_TRY(backward_head(g));
-    for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
-    TB_TRY(backward_embed(g));
+    TB_TRY(tb_trainer_forward_resident(g, 1));
+    TB_TRY(tb_trainer_backward_head(g));
+    for (int l = g->L - 1; l >= 0; --l) TB_TRY(tb_trainer_backward_layer(g, l));
+    TB_TRY(tb_trainer_backward_embed(g));
     return tb_trainer_clip_adam_async(g, t, lr, beta1, beta2, eps, max_norm, 1.0f);
 }
 
 int tb_trainer_forward_resident(TbTrainer* g, int want_grad) {
     TB_CHECK(g->nseg > 0, "tb_trainer_forward_resident: call tb_trainer_set_inputs first");
-    return forward(g, want_grad != 0);
+    const bool wg = want_grad != 0;
+    return run_segment(g, wg ? SEG_FWD_TRAIN : SEG_FWD_EVAL, [&]() { return forward(g, wg); });
 }
 
 int tb_trainer_last_norm(TbTrainer* g, double* norm_out) {
@@ -526,21 +586,25 @@ int tb_trainer_last_norm(TbTrainer* g, double* norm_out) {
     return 0;
 }
 
-int tb_trainer_backward_head(TbTrainer* g) { return backward_head(g); }
+int tb_trainer_backward_head(TbTrainer* g) {
+    return run_segment(g, SEG_HEAD_BWD, [&]() { return backward_head(g); });
+}
 int tb_trainer_backward_layer(TbTrainer* g, int layer) {
     TB_CHECK(layer >= 0 && layer < g->L, "layer %d out of range", layer);
-    return backward_layer(g, layer);
+    return run_segment(g, SEG_LAYER0 + layer, [&]() { return backward_layer(g, layer); });
 }
-int tb_trainer_backward_embed(TbTrainer* g) { return backward_embed(g); }
+int tb_trainer_backward_embed(TbTrainer* g) {
+    return run_segment(g, SEG_EMBED_BWD, [&]() { return backward_embed(g); });
+}
 int tb_trainer_read_loss(TbTrainer* g, float* loss_out) { return read_loss(g, loss_out); }
 
 int tb_trainer_forward_backward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, float* loss_out) {
     TB_CUDA(cudaSetDevice(g->device));
     TB_TRY(tb_trainer_zero_grads(g));
     TB_TRY(tb_trainer_forward(g, h_ids, h_targets, 1));
-    TB_TRY(backward_head(g));
-    for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
-    TB_TRY(backward_embed(g));
+    TB_TRY(tb_trainer_backward_head(g));
+    for (int l = g->L - 1; l >= 0; --l) TB_TRY(tb_trainer_backward_layer(g, l));
+    TB_TRY(tb_trainer_backward_embed(g));
     return read_loss(g, loss_out);
 }
 
@@ -581,9 +645,9 @@ int tb_trainer_train_step(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h
     TB_CUDA(cudaSetDevice(g->device));
     TB_TRY(tb_trainer_zero_grads(g));
     TB_TRY(tb_trainer_forward(g, h_ids, h_targets, 1));
-    TB_TRY(backward_head(g));
-    for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
-    TB_TRY(backward_embed(g));
+    TB_TRY(tb_trainer_backward_head(g));
+    for (int l = g->L - 1; l >= 0; --l) TB_TRY(tb_trainer_backward_layer(g, l));
+    TB_TRY(tb_trainer_backward_embed(g));
     TB_TRY(tb_trainer_clip_adam_async(g, t, lr, beta1, beta2, eps, max_norm, 1.0f));
     TB_TRY(read_loss(g, loss_out));
     if (norm_out) *norm_out = *g->h_norm;

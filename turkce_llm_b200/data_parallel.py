@@ -55,6 +55,11 @@ class DataParallelStep:
         self.L = trainer.cfg[3]
         if not check_buckets(buckets, trainer.total):
             raise ValueError("gradient buckets do not tile the flat buffer")
+        self.stream = None
+        if world > 1:
+            # collectives must be ordered against the trainer's own stream: make it torch's current one
+            import torch
+            self.stream = torch.cuda.ExternalStream(trainer.stream_ptr())
 
     def _reduce(self, name, handles):
         if self.world > 1:
@@ -73,16 +78,31 @@ class DataParallelStep:
         for h in handles:
             h.wait()          # orders the optimiser after the collectives on the compute stream
 
+    def _on_stream(self):
+        import contextlib
+        if self.stream is None:
+            return contextlib.nullcontext()
+        import torch
+        return torch.cuda.stream(self.stream)
+
     def resident(self, opt, max_norm):
         """Step on the inputs already on the device (set_inputs); nothing crosses PCIe."""
+        with self._on_stream():
+            self._resident(opt, max_norm)
+
+    def host(self, ids, targets, opt, max_norm):
+        """Step on host token buffers; returns (mean loss over ranks, gradient norm)."""
+        with self._on_stream():
+            return self._host(ids, targets, opt, max_norm)
+
+    def _resident(self, opt, max_norm):
         g = self.g
         g.zero_grads()
         g.forward_resident(True)
         self._backward()
         g.clip_adam_async(opt, max_norm, 1.0 / self.world)
 
-    def host(self, ids, targets, opt, max_norm):
-        """Step on host token buffers; returns (mean loss over ranks, gradient norm)."""
+    def _host(self, ids, targets, opt, max_norm):
         g = self.g
         g.zero_grads()
         g.forward(ids, targets, True)

@@ -69,6 +69,10 @@ class GpuTrainer:
     def device_ptr(self, which):
         return int(self._lib.tb_trainer_device_ptr(self.h, which))
 
+    def stream_ptr(self):
+        """cudaStream_t (as an integer) all of this trainer's work is issued on."""
+        return int(self._lib.tb_trainer_stream(self.h) or 0)
+
     # gpu_trainer_forward_backward
     def forward_backward(self, ids, targets):
         ids, pi = _u32(ids)

@@ -46,6 +46,7 @@ SIGNATURES = {
     "tb_trainer_upload": (_i, [_vp, _i, _vp]),
     "tb_trainer_download": (_i, [_vp, _i, _vp]),
     "tb_trainer_device_ptr": (_vp, [_vp, _i]),
+    "tb_trainer_stream": (_vp, [_vp]),
     "tb_trainer_forward_backward": (_i, [_vp, _vp, _vp, C.POINTER(_f)]),
     "tb_trainer_eval_loss": (_i, [_vp, _vp, _vp, C.POINTER(_f)]),
     "tb_trainer_grad_norm": (_i, [_vp, C.POINTER(C.c_double)]),
