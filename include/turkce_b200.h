@@ -128,6 +128,24 @@ int tb_gemm_bf16_splitk_static(int kind, const void* d_A, const void* d_B, int M
 int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld_src, int64_t ld_dst,
                  int batch, int64_t stride_src, int64_t stride_dst, void* stream);
 
+/* ---- fused causal attention ---------------------------------------------------- */
+
+/* The per-head attention contractions of the reference's GPU trainer in one kernel: QK^T
+ * (k_bf16_gemm_nt), causal softmax (k_attn_softmax_fwd), P V (k_bf16_gemm_nn) and k_heads_merge
+ * (model/gpu_train.c:346-358; cuda/train_kernels.cu:631-651, :667-678).
+ * d_Q, d_K, d_V: bf16 [B*H, T, hd] with RoPE applied (the output layout of k_qkv_rope_split),
+ * hd <= 64 and a multiple of 8.  d_att: bf16 [B*T, H*hd] (heads merged).  d_lse: float [B*H, T],
+ * log of the row's sum of exponentials, kept for the backward pass in place of P [B,H,T,T]. */
+int tb_attention_fwd(const void* d_Q, const void* d_K, const void* d_V, void* d_att, float* d_lse, int B, int H, int T,
+                     int hd, float scale, void* stream);
+/* Backward of the same chain: k_heads_split, the dV / dP / dQ / dK products and
+ * k_attn_softmax_bwd (model/gpu_train.c:435-455; cuda/train_kernels.cu:655-664, :681-692).
+ * d_att, d_datt: bf16 [B*T, H*hd] (forward output and its gradient); d_delta: float scratch
+ * [B*H, T]; d_dQ, d_dK, d_dV: float [B*H, T, hd] (gradients of the rotated Q, K and of V). */
+int tb_attention_bwd(const void* d_Q, const void* d_K, const void* d_V, const void* d_att, const void* d_datt,
+                     const float* d_lse, float* d_delta, float* d_dQ, float* d_dK, float* d_dV, int B, int H, int T,
+                     int hd, float scale, void* stream);
+
 /* ---- GPU-resident trainer ---------------------------------------------------- */
 
 /* GpuTrainer (model/gpu_train.h:51-80).  Parameters, gradients and Adam state are flat

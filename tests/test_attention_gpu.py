@@ -1,0 +1,95 @@
+"""Fused causal attention (tb_attention_fwd / tb_attention_bwd) against the CPU oracle's
+scores -> mask -> softmax -> P V chain and its backward (model/attention.c:32-60;
+model/gpu_train.c:435-455), through the C ABI.  Metric: max|got-want| / max|want|."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_to_maxabs
+from oracle.pyoracle import BF16, FP32
+
+pytestmark = pytest.mark.gpu
+
+TOL_FWD = 1e-2        # bf16 P and V operands; P is rounded against the running maximum
+TOL_BWD = 2e-2        # the BF16-mode bound
+
+
+def make_qkv(oracle, B, H, T, hd, seed):
+    rng = np.random.default_rng(seed)
+    q, k, v = (oracle.round(rng.standard_normal((B * H, T, hd)).astype(np.float32), BF16) for _ in range(3))
+    return q, k, v
+
+
+def dev16(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda().to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("dims", [(1, 2, 12, 16), (2, 2, 200, 32), (1, 3, 320, 64), (1, 2, 1024, 64), (2, 1, 130, 8)])
+def test_attention_fwd_bwd_matches_oracle(tb, oracle, dims):
+    B, H, T, hd = dims
+    D = H * hd
+    scale = float(1.0 / np.sqrt(np.float32(hd)))
+    q, k, v = make_qkv(oracle, B, H, T, hd, 3)
+    Q, K, V = dev16(q), dev16(k), dev16(v)
+    att = torch.full((B * T, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    lse = torch.zeros(B * H, T, device="cuda")
+    tb.attention_fwd(Q, K, V, att, lse, B, H, T, hd, scale)
+    tb.sync_check()
+    O, P = oracle.attention_fwd(q, k, v, scale, mode=BF16, want_P=True)
+    want = oracle.heads_merge(O, B, T, H, hd)
+    got = att.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert rel_to_maxabs(got, want) <= TOL_FWD
+    assert rel_to_maxabs(got, oracle.heads_merge(oracle.attention_fwd(q, k, v, scale, mode=FP32), B, T, H, hd)) <= 2e-2
+    # log-sum-exp of the masked, scaled scores
+    S = np.einsum("zid,zjd->zij", q.astype(np.float64), k.astype(np.float64)) * scale
+    S = np.where(np.tril(np.ones((T, T), bool))[None], S, -np.inf)
+    want_lse = np.log(np.exp(S - S.max(-1, keepdims=True)).sum(-1)) + S.max(-1)
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 1e-3
+
+    rng = np.random.default_rng(4)
+    datt = oracle.round(rng.standard_normal((B * T, D)).astype(np.float32), BF16)
+    dQ, dK, dV = (torch.full((B * H, T, hd), float("nan"), device="cuda") for _ in range(3))
+    delta = torch.zeros(B * H, T, device="cuda")
+    tb.attention_bwd(Q, K, V, att, dev16(datt), lse, delta, dQ, dK, dV, B, H, T, hd, scale)
+    tb.sync_check()
+    dO = oracle.heads_split(datt, B, T, H, hd)
+    wq, wk, wv = oracle.attention_bwd(q, k, v, dO, scale, mode=BF16)
+    for got_t, want_a, name in ((dQ, wq, "dQ"), (dK, wk, "dK"), (dV, wv, "dV")):
+        g = got_t.cpu().numpy()
+        assert np.isfinite(g).all(), name
+        assert rel_to_maxabs(g, want_a) <= TOL_BWD, name
+
+
+def test_attention_properties_at_benchmark_size(tb):
+    """B=16, H=6, T=1024, hd=64 (the attention configuration of the benchmark): rows of P sum to 1
+    (V = 1 gives O = 1), and a change in later keys/values leaves earlier outputs bit-identical."""
+    B, H, T, hd = 16, 6, 1024, 64
+    D = H * hd
+    scale = 0.125
+    g = torch.Generator(device="cuda").manual_seed(2)
+    Q = torch.randn(B * H, T, hd, device="cuda", generator=g).to(torch.bfloat16)
+    K = torch.randn(B * H, T, hd, device="cuda", generator=g).to(torch.bfloat16)
+    V = torch.ones(B * H, T, hd, device="cuda", dtype=torch.bfloat16)
+    att = torch.zeros(B * T, D, device="cuda", dtype=torch.bfloat16)
+    lse = torch.zeros(B * H, T, device="cuda")
+    tb.attention_fwd(Q, K, V, att, lse, B, H, T, hd, scale)
+    tb.sync_check()
+    assert (att.float() - 1.0).abs().max().item() <= 1e-2
+    V = torch.randn(B * H, T, hd, device="cuda", generator=g).to(torch.bfloat16)
+    a1 = torch.zeros_like(att)
+    tb.attention_fwd(Q, K, V, a1, lse, B, H, T, hd, scale)
+    K2, V2 = K.clone(), V.clone()
+    K2[:, 700:] = 3.0
+    V2[:, 700:] = -2.0
+    a2 = torch.zeros_like(att)
+    tb.attention_fwd(Q, K2, V2, a2, lse, B, H, T, hd, scale)
+    tb.sync_check()
+    a1 = a1.view(B, T, D)
+    a2 = a2.view(B, T, D)
+    assert torch.equal(a1[:, :700], a2[:, :700])
+    assert not torch.equal(a1[:, 700:], a2[:, 700:])
+    a3 = torch.zeros_like(att)
+    tb.attention_fwd(Q, K, V, a3, lse, B, H, T, hd, scale)
+    tb.sync_check()
+    assert torch.equal(a3.view(B, T, D), a1)          # bitwise reproducible

@@ -52,7 +52,7 @@ int tb_profile_begin(void) {
     DeviceCtx* ctx;
     TB_TRY(get_ctx(&ctx));
     if (ctx->prof) {
-        for (auto& r : *ctx->prof) cudaEventDestroy(r.ev);
+        for (auto& r : *ctx->prof) { cudaEventDestroy(r.ev); if (r.ev_end) cudaEventDestroy(r.ev_end); }
         ctx->prof->clear();
     }
     ctx->prof_on = true;
@@ -75,7 +75,7 @@ int tb_profile_end(void* stream, char* out, int cap) {
     auto& v = *ctx->prof;
     for (size_t i = 0; i < v.size(); ++i) {
         float ms = 0.f;
-        cudaEvent_t next = (i + 1 < v.size()) ? v[i + 1].ev : last;
+        cudaEvent_t next = v[i].ev_end ? v[i].ev_end : ((i + 1 < v.size()) ? v[i + 1].ev : last);
         if (cudaEventElapsedTime(&ms, v[i].ev, next) != cudaSuccess) ms = 0.f;
         Agg& a = agg[v[i].tag];
         a.n++; a.ms += ms; a.flops += v[i].flops; a.bytes += v[i].bytes;
@@ -87,7 +87,7 @@ int tb_profile_end(void* stream, char* out, int cap) {
                  kv.second.flops, kv.second.bytes);
         text += line;
     }
-    for (auto& r : v) cudaEventDestroy(r.ev);
+    for (auto& r : v) { cudaEventDestroy(r.ev); if (r.ev_end) cudaEventDestroy(r.ev_end); }
     v.clear();
     cudaEventDestroy(last);
     strncpy(out, text.c_str(), (size_t)cap - 1);
@@ -138,6 +138,26 @@ int tb_gemm_bf16(int kind, const void* d_A, const void* d_B, int M, int N, int K
     a.causal = static_cast<CausalMode>(causal);
     a.splits = splits; a.bn = tile_n;
     return launch_gemm_bf16(ctx, a, S(stream));
+}
+
+int tb_attention_fwd(const void* d_Q, const void* d_K, const void* d_V, void* d_att, float* d_lse, int B, int H, int T,
+                     int hd, float scale, void* stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    return launch_attention_fwd(ctx, static_cast<const bf16*>(d_Q), static_cast<const bf16*>(d_K),
+                                static_cast<const bf16*>(d_V), static_cast<bf16*>(d_att), d_lse, B, H, T, hd, scale,
+                                S(stream));
+}
+
+int tb_attention_bwd(const void* d_Q, const void* d_K, const void* d_V, const void* d_att, const void* d_datt,
+                     const float* d_lse, float* d_delta, float* d_dQ, float* d_dK, float* d_dV, int B, int H, int T,
+                     int hd, float scale, void* stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    return launch_attention_bwd(ctx, static_cast<const bf16*>(d_Q), static_cast<const bf16*>(d_K),
+                                static_cast<const bf16*>(d_V), static_cast<const bf16*>(d_att),
+                                static_cast<const bf16*>(d_datt), d_lse, d_delta, d_dQ, d_dK, d_dV, B, H, T, hd, scale,
+                                S(stream));
 }
 
 // Packs both float32 operands to bf16 in scratch memory, then runs the bf16 GEMM.

@@ -1,0 +1,738 @@
+// Fused causal attention for sm_100a: S = Q K^T and O = P V on tcgen05 tensor cores with the
+// score tile kept in TMEM, the softmax done in registers and P handed to the second product
+// through shared memory -- the [T, T] score and probability matrices never exist in HBM.
+//
+// Replaces the reference's chain k_bf16_gemm_nt (QK^T) -> k_attn_softmax_fwd -> k_bf16_gemm_nn
+// (P V) -> k_heads_merge and its backward counterpart (model/gpu_train.c:346-358, :435-455;
+// cuda/train_kernels.cu:631-692), which stores P [B,H,T,T] in float32 per layer.
+//
+// Semantics are the reference's (model/attention.c:32-60): scores * 1/sqrt(hd), keys after the
+// query excluded, softmax over the row, times V.  The reference adds -1e9 to the excluded scores;
+// after exp in float32 that is exactly 0, so excluding them is the same function.  The softmax is
+// evaluated block-wise with a running maximum (the result is the same softmax; rounding of P to
+// bf16 happens against the running maximum instead of the final one).
+//
+// Layouts: Q, K, V bf16 [B*H, T, hd] (RoPE already applied), hd <= 64 and a multiple of 8 (rows
+// are padded to 64 columns with zeros by the TMA loads).  Output bf16 [B*T, H*hd] (heads merged)
+// plus the row-wise log-sum-exp, which is all the backward pass needs to rebuild P.
+#include "common.h"
+#include "ptx.cuh"
+
+#include <cstdlib>
+
+namespace tb {
+
+constexpr int ATT_BM = 128;       // queries per CTA
+constexpr int ATT_BN = 128;       // keys per step
+constexpr int ATT_HD = 64;        // padded head dimension
+constexpr int TILE_BYTES = 128 * 64 * 2;   // one [128, 64] bf16 tile, 128-byte rows
+
+// K-major operand tile [rows, 64] (128-byte rows, 128B swizzle): advance 32 bytes per K=16
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_addr, int k16) {
+    return umma_desc_sw128(tile_addr + k16 * 32, 16, 1024);
+}
+// the same tile read as an MN-major operand (64 MN elements contiguous, K = rows): 16 rows per K=16
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_addr, int k16, uint32_t lbo) {
+    return umma_desc_sw128(tile_addr + k16 * 2048, lbo, 1024);
+}
+
+// 2^x on the special-function unit (one instruction; 2^-inf = 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// 32 consecutive values of row r -> bf16 in a [128 x 128] operand stored as two [128 x 64] tiles
+__device__ __forceinline__ void store_chunk_bf16(uint8_t* tiles, int r, int c, const float (&x)[32]) {
+    uint8_t* row = tiles + (c >> 1) * TILE_BYTES + r * 128;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint4 pk;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(x[8 * g + 0], x[8 * g + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(x[8 * g + 2], x[8 * g + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(x[8 * g + 4], x[8 * g + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(x[8 * g + 6], x[8 * g + 7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        const int chunk = (c & 1) * 4 + g;
+        *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) = pk;
+    }
+}
+
+struct AttFwdParams {
+    int T, H, hd, D;
+    int nq;                 // query blocks per head
+    float scale_log2;       // 1/sqrt(hd) * log2(e)
+    bf16* att;              // [B*T, D]
+    float* lse;             // [B*H, T]
+    int* err;
+};
+
+// ------------------------------------------------------------------------------------ forward
+// CTA = 6 warps: TMA producer, MMA issuer (owns TMEM: S 128 columns + O-step 64 columns), four
+// softmax warps (thread = query row).  Two CTAs fit per SM, so one CTA's tensor-core work
+// overlaps the other's exponentials.
+__global__ void __launch_bounds__(192, 2)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const AttFwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint8_t* sQ = smem;                          // 16 KB
+    uint8_t* sK = smem + TILE_BYTES;             // 2 x 16 KB
+    uint8_t* sV = smem + 3 * TILE_BYTES;         // 2 x 16 KB
+    uint8_t* sP = smem + 5 * TILE_BYTES;         // 2 x 16 KB: keys 0-63 | keys 64-127
+    // the request is exactly 1 KB + 7 tiles (two CTAs per SM): the barriers go behind the tiles when
+    // the alignment pad leaves room there (the usual case: pad 0), else into the pad itself
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pad <= 768u ? smem + 7 * TILE_BYTES : smem_raw);
+    uint64_t* q_full = bars;          // 1
+    uint64_t* k_full = bars + 1;      // 2
+    uint64_t* v_full = bars + 3;      // 2
+    uint64_t* kv_empty = bars + 5;    // 2
+    uint64_t* s_full = bars + 7;
+    uint64_t* s_free = bars + 8;
+    uint64_t* p_full = bars + 9;
+    uint64_t* o_full = bars + 10;
+    uint64_t* o_free = bars + 11;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = p.nq - 1 - (int)blockIdx.x;       // heavy (late) query blocks first
+    const int bh = blockIdx.y;
+    const int q0 = qb * ATT_BM;
+    const int nkv = qb + 1;                           // key blocks 0..qb
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        mbar_init(s_full, 1); mbar_init(s_free, 4); mbar_init(p_full, 4); mbar_init(o_full, 1); mbar_init(o_free, 4);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tS = tmem_base, tO = tmem_base + 128;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(q_full, TILE_BYTES);
+            tma_load_3d(sQ, &tmQ, q_full, 0, q0, bh);
+            for (int j = 0; j < nkv && ok; ++j) {
+                const int s = j & 1;
+                if (!mbar_wait(&kv_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                mbar_expect_tx(&k_full[s], TILE_BYTES);
+                tma_load_3d(sK + s * TILE_BYTES, &tmK, &k_full[s], 0, j * ATT_BN, bh);
+                mbar_expect_tx(&v_full[s], TILE_BYTES);
+                tma_load_3d(sV + s * TILE_BYTES, &tmV, &v_full[s], 0, j * ATT_BN, bh);
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 11); }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(1u, 0u, 0u, ATT_BM, ATT_BN);     // Q K^T: both K-major
+            const uint32_t idesc_o = umma_idesc(1u, 0u, 1u, ATT_BM, ATT_HD);     // P V: V is MN-major
+            const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            for (int j = 0; j < nkv && ok; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = (uint32_t)((j >> 1) & 1), pj = (uint32_t)(j & 1);
+                if (!mbar_wait(&k_full[s], ph, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(s_free, pj ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t aK = smem_u32(sK + s * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < ATT_HD / 16; ++k)
+                    umma_bf16(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(s_full);
+                if (!mbar_wait(p_full, pj, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(o_free, pj ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t aV = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < ATT_BN / 16; ++k)
+                    umma_bf16(tO, kmajor_desc(aP + (k >> 2) * TILE_BYTES, k & 3), mnmajor_desc(aV, k, TILE_BYTES),
+                              idesc_o, k > 0 ? 1u : 0u);
+                umma_commit(o_full);
+                umma_commit(&kv_empty[s]);
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 12); }
+        }
+    } else {
+        const int q = warp & 3;
+        const int r = q * 32 + lane;                 // row of the tile = TMEM lane
+        const int qi = q0 + r;                       // query position
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        float m = -INFINITY, l = 0.0f;
+        float O[ATT_HD];
+#pragma unroll
+        for (int d = 0; d < ATT_HD; ++d) O[d] = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < nkv && ok; ++j) {
+            const uint32_t pj = (uint32_t)(j & 1);
+            if (!mbar_wait(s_full, pj, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const bool diag = (j == qb);
+            const int k0 = j * ATT_BN;
+            // pass 1: row maximum of the allowed scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tS + lane_base + c * 32, v);
+                tmem_ld_wait();
+                if (diag) {
+                    const int lim = qi - (k0 + c * 32);        // columns e <= lim are allowed
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, e <= lim ? __uint_as_float(v[e]) : -INFINITY);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2)
+                        mx = fmaxf(mx, fmaxf(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
+                }
+            }
+            const float m_new = fmaxf(m, mx * p.scale_log2);
+            const float alpha = fast_exp2(m - m_new);        // 0 on the first block (m = -inf)
+            l *= alpha;
+            // pass 2: p = 2^(s*c - m), row sum, bf16 P into shared memory (K-major, 128B swizzle)
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tS + lane_base + c * 32, v);
+                tmem_ld_wait();
+                float pv[32];
+                if (diag) {
+                    const int lim = qi - (k0 + c * 32);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        pv[e] = e <= lim ? fast_exp2(__uint_as_float(v[e]) * p.scale_log2 - m_new) : 0.0f;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) pv[e] = fast_exp2(__uint_as_float(v[e]) * p.scale_log2 - m_new);
+                }
+                float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+                for (int e = 0; e < 32; e += 4) { l0 += pv[e]; l1 += pv[e + 1]; l2 += pv[e + 2]; l3 += pv[e + 3]; }
+                l += (l0 + l1) + (l2 + l3);
+                store_chunk_bf16(sP, r, c, pv);
+            }
+            tc_fence_before();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(s_free); mbar_arrive(p_full); }
+            // accumulate this step's P V into the running output
+            if (!mbar_wait(o_full, pj, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tO + lane_base + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) O[c * 32 + e] = O[c * 32 + e] * alpha + __uint_as_float(v[e]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_free);
+            m = m_new;
+        }
+        if (ok && qi < p.T) {
+            const float inv = 1.0f / l;
+            const int b = bh / p.H, h = bh % p.H;
+            bf16* orow = p.att + ((long long)b * p.T + qi) * p.D + h * p.hd;
+#pragma unroll
+            for (int d = 0; d < ATT_HD; d += 8) {
+                if (d >= p.hd) break;
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(O[d + 0] * inv, O[d + 1] * inv);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(O[d + 2] * inv, O[d + 3] * inv);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(O[d + 4] * inv, O[d + 5] * inv);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(O[d + 6] * inv, O[d + 7] * inv);
+                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(orow + d) = pk;
+            }
+            p.lse[(long long)bh * p.T + qi] = (m + log2f(l)) * 0.6931471805599453f;
+        }
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 13); }
+    }
+
+    __syncwarp();
+    if (*abort_flag) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
+// ----------------------------------------------------------------------------------- backward
+// With P rebuilt from the saved log-sum-exp (P = exp(S*scale - lse)) the backward is, per head,
+//   dV = P^T dO,  dP = dO V^T,  dS = P * (dP - delta) * scale,  dQ = dS K,  dK = dS^T Q,
+// delta[i] = <dO_i, O_i>  (the reference's k_attn_softmax_bwd row dot <dP, P>, since O = P V).
+// Two kernels keep every sum in a fixed order without atomics: one owns a key block and walks the
+// query blocks below the diagonal (dK, dV), the other owns a query block and walks its key blocks
+// (dQ); both recompute S and dP on the tensor cores.
+
+__global__ void attention_delta_kernel(const bf16* __restrict__ att, const bf16* __restrict__ datt,
+                                       float* __restrict__ delta, int B, int T, int H, int hd) {
+    const long long total = (long long)B * T * H;
+    const int D = H * hd;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int h = (int)(i % H);
+        const long long n = i / H;
+        const int t = (int)(n % T);
+        const long long b = n / T;
+        const bf16* o = att + n * D + h * hd;
+        const bf16* d = datt + n * D + h * hd;
+        float s = 0.0f;
+        for (int k = 0; k < hd; k += 8) {
+            const uint4 ov = *reinterpret_cast<const uint4*>(o + k);
+            const uint4 dv = *reinterpret_cast<const uint4*>(d + k);
+            const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(o2[e]), c = __bfloat1622float2(d2[e]);
+                s += a.x * c.x;
+                s += a.y * c.y;
+            }
+        }
+        delta[(b * H + h) * T + t] = s;
+    }
+}
+
+struct AttBwdParams {
+    int T, H, hd;
+    int nq;
+    float scale, scale_log2;
+    const float* lse;       // [B*H, T]
+    const float* delta;     // [B*H, T]
+    float* dQ; float* dK; float* dV;     // [B*H, T, hd]
+    int* err;
+};
+
+constexpr int ATT_BWD_THREADS = 320;     // TMA warp, MMA warp, 8 compute warps
+
+// dK, dV of one key block: walks the query blocks qb = kb .. nq-1.
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
+attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                          const AttBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint8_t* sK = smem;
+    uint8_t* sV = smem + TILE_BYTES;
+    uint8_t* sQ = smem + 2 * TILE_BYTES;      // 2 stages
+    uint8_t* sdO = smem + 4 * TILE_BYTES;     // 2 stages
+    uint8_t* sP = smem + 6 * TILE_BYTES;      // [128 q, 128 keys] as two tiles
+    uint8_t* sdS = smem + 8 * TILE_BYTES;     // same
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 10 * TILE_BYTES);
+    uint64_t* kv_full = bars;          // 1
+    uint64_t* qdo_full = bars + 1;     // 2
+    uint64_t* qdo_empty = bars + 3;    // 2
+    uint64_t* sdp_full = bars + 5;
+    uint64_t* sdp_free = bars + 6;     // 8 arrivals
+    uint64_t* pds_full = bars + 7;     // 8 arrivals
+    uint64_t* pds_free = bars + 8;
+    uint64_t* acc_full = bars + 9;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kb = blockIdx.x;                 // early key blocks have the most query blocks: they start first
+    const int bh = blockIdx.y;
+    const int b = bh / p.H, h = bh % p.H;
+    const int k0 = kb * ATT_BN;
+    const int niter = p.nq - kb;
+
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+        mbar_init(sdp_full, 1); mbar_init(sdp_free, 8); mbar_init(pds_full, 8); mbar_init(pds_free, 1);
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 320;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+            tma_load_3d(sK, &tmK, kv_full, 0, k0, bh);
+            tma_load_3d(sV, &tmV, kv_full, 0, k0, bh);
+            for (int it = 0; it < niter && ok; ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(&qdo_empty[s], (uint32_t)((it >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                const int q0 = (kb + it) * ATT_BM;
+                mbar_expect_tx(&qdo_full[s], 2 * TILE_BYTES);
+                tma_load_3d(sQ + s * TILE_BYTES, &tmQ, &qdo_full[s], 0, q0, bh);
+                tma_load_4d(sdO + s * TILE_BYTES, &tmdO, &qdo_full[s], 0, q0, h, b);
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 21); }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t id_s = umma_idesc(1u, 0u, 0u, 128, 128);      // Q K^T, dO V^T
+            const uint32_t id_t = umma_idesc(1u, 1u, 1u, 128, 64);       // P^T dO, dS^T Q: both MN-major
+            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), adS = smem_u32(sdS);
+            bool ok = mbar_wait(kv_full, 0, abort_flag);
+            for (int it = 0; it < niter && ok; ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (uint32_t)((it >> 1) & 1), pi = (uint32_t)(it & 1);
+                const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), adO = smem_u32(sdO + s * TILE_BYTES);
+                if (!mbar_wait(&qdo_full[s], ph, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(sdp_free, pi ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_bf16(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), id_s, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_bf16(tdP, kmajor_desc(adO, k), kmajor_desc(aV, k), id_s, k > 0 ? 1u : 0u);
+                umma_commit(sdp_full);
+                if (!mbar_wait(pds_full, pi, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    umma_bf16(tdV, mnmajor_desc(aP, k, TILE_BYTES), mnmajor_desc(adO, k, TILE_BYTES), id_t,
+                              (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    umma_bf16(tdK, mnmajor_desc(adS, k, TILE_BYTES), mnmajor_desc(aQ, k, TILE_BYTES), id_t,
+                              (it > 0 || k > 0) ? 1u : 0u);
+                umma_commit(pds_free);
+                umma_commit(&qdo_empty[s]);
+            }
+            if (ok) umma_commit(acc_full);
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 22); }
+        }
+    } else {
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;             // which 64 key columns this warp handles
+        const int r = q * 32 + lane;                  // query row inside the block
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        bool ok = true;
+        for (int it = 0; it < niter && ok; ++it) {
+            const uint32_t pi = (uint32_t)(it & 1);
+            const int qb = kb + it;
+            const int qi = qb * ATT_BM + r;
+            const bool valid = qi < p.T;
+            const bool diag = (qb == kb);
+            const float lse2 = valid ? p.lse[(long long)bh * p.T + qi] * 1.4426950408889634f : INFINITY;
+            const float dl = valid ? p.delta[(long long)bh * p.T + qi] : 0.0f;
+            if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(pds_free, pi ^ 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = half * 2 + cc;
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tS + lane_base + c * 32, sv);
+                tmem_ld32(tdP + lane_base + c * 32, dv);
+                tmem_ld_wait();
+                float P[32], dS[32];
+                // rows past T get lse2 = +inf below, i.e. P = 0; the diagonal block masks keys after the query
+                const int lim = diag ? qi - (k0 + c * 32) : 32;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    float pe = fast_exp2(__uint_as_float(sv[e]) * p.scale_log2 - lse2);
+                    if (diag) pe = e <= lim ? pe : 0.0f;
+                    P[e] = pe;
+                    dS[e] = pe * (__uint_as_float(dv[e]) - dl) * p.scale;
+                }
+                store_chunk_bf16(sP, r, c, P);
+                store_chunk_bf16(sdS, r, c, dS);
+            }
+            tc_fence_before();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(sdp_free); mbar_arrive(pds_full); }
+        }
+        if (ok) {
+            if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            const int kj = k0 + r;                    // key row of the accumulators
+            uint32_t v[32], w[32];
+            tmem_ld32(tdV + lane_base + half * 32, v);
+            tmem_ld32(tdK + lane_base + half * 32, w);
+            tmem_ld_wait();
+            if (kj < p.T) {
+                float* dv = p.dV + ((long long)bh * p.T + kj) * p.hd;
+                float* dk = p.dK + ((long long)bh * p.T + kj) * p.hd;
+#pragma unroll
+                for (int e = 0; e < 32; e += 4) {
+                    const int d = half * 32 + e;
+                    if (d < p.hd) {
+                        *reinterpret_cast<float4*>(dv + d) = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                                                          __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                        *reinterpret_cast<float4*>(dk + d) = make_float4(__uint_as_float(w[e]), __uint_as_float(w[e + 1]),
+                                                                          __uint_as_float(w[e + 2]), __uint_as_float(w[e + 3]));
+                    }
+                }
+            }
+        }
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 23); }
+    }
+
+    __syncwarp();
+    if (*abort_flag) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// dQ of one query block: walks its key blocks kb = 0 .. qb.
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
+attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                        const AttBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint8_t* sQ = smem;
+    uint8_t* sdO = smem + TILE_BYTES;
+    uint8_t* sK = smem + 2 * TILE_BYTES;      // 2 stages
+    uint8_t* sV = smem + 4 * TILE_BYTES;      // 2 stages
+    uint8_t* sdS = smem + 6 * TILE_BYTES;     // [128 q, 128 keys] as two tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 8 * TILE_BYTES);
+    uint64_t* qdo_full = bars;         // 1
+    uint64_t* kv_full = bars + 1;      // 2
+    uint64_t* kv_empty = bars + 3;     // 2
+    uint64_t* sdp_full = bars + 5;
+    uint64_t* sdp_free = bars + 6;     // 8
+    uint64_t* ds_full = bars + 7;      // 8
+    uint64_t* ds_free = bars + 8;
+    uint64_t* acc_full = bars + 9;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = p.nq - 1 - (int)blockIdx.x;
+    const int bh = blockIdx.y;
+    const int b = bh / p.H, h = bh % p.H;
+    const int q0 = qb * ATT_BM;
+    const int niter = qb + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(qdo_full, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        mbar_init(sdp_full, 1); mbar_init(sdp_free, 8); mbar_init(ds_full, 8); mbar_init(ds_free, 1);
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
+            tma_load_3d(sQ, &tmQ, qdo_full, 0, q0, bh);
+            tma_load_4d(sdO, &tmdO, qdo_full, 0, q0, h, b);
+            for (int it = 0; it < niter && ok; ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(&kv_empty[s], (uint32_t)((it >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+                tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, it * ATT_BN, bh);
+                tma_load_3d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, it * ATT_BN, bh);
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 31); }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t id_s = umma_idesc(1u, 0u, 0u, 128, 128);
+            const uint32_t id_q = umma_idesc(1u, 0u, 1u, 128, 64);       // dS (K-major) x K block (MN-major)
+            const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), adS = smem_u32(sdS);
+            bool ok = mbar_wait(qdo_full, 0, abort_flag);
+            for (int it = 0; it < niter && ok; ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (uint32_t)((it >> 1) & 1), pi = (uint32_t)(it & 1);
+                const uint32_t aK = smem_u32(sK + s * TILE_BYTES), aV = smem_u32(sV + s * TILE_BYTES);
+                if (!mbar_wait(&kv_full[s], ph, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(sdp_free, pi ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_bf16(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), id_s, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_bf16(tdP, kmajor_desc(adO, k), kmajor_desc(aV, k), id_s, k > 0 ? 1u : 0u);
+                umma_commit(sdp_full);
+                if (!mbar_wait(ds_full, pi, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    umma_bf16(tdQ, kmajor_desc(adS + (k >> 2) * TILE_BYTES, k & 3), mnmajor_desc(aK, k, TILE_BYTES), id_q,
+                              (it > 0 || k > 0) ? 1u : 0u);
+                umma_commit(ds_free);
+                umma_commit(&kv_empty[s]);
+            }
+            if (ok) umma_commit(acc_full);
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 32); }
+        }
+    } else {
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int r = q * 32 + lane;
+        const int qi = q0 + r;
+        const bool valid = qi < p.T;
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        const float lse2 = valid ? p.lse[(long long)bh * p.T + qi] * 1.4426950408889634f : INFINITY;
+        const float dl = valid ? p.delta[(long long)bh * p.T + qi] : 0.0f;
+        bool ok = true;
+        for (int it = 0; it < niter && ok; ++it) {
+            const uint32_t pi = (uint32_t)(it & 1);
+            const bool diag = (it == qb);
+            const int k0 = it * ATT_BN;
+            if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(ds_free, pi ^ 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = half * 2 + cc;
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tS + lane_base + c * 32, sv);
+                tmem_ld32(tdP + lane_base + c * 32, dv);
+                tmem_ld_wait();
+                float dS[32];
+                const int lim = diag ? qi - (k0 + c * 32) : 32;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    float pe = fast_exp2(__uint_as_float(sv[e]) * p.scale_log2 - lse2);
+                    if (diag) pe = e <= lim ? pe : 0.0f;
+                    dS[e] = pe * (__uint_as_float(dv[e]) - dl) * p.scale;
+                }
+                store_chunk_bf16(sdS, r, c, dS);
+            }
+            tc_fence_before();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(sdp_free); mbar_arrive(ds_full); }
+        }
+        if (ok) {
+            if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            uint32_t v[32];
+            tmem_ld32(tdQ + lane_base + half * 32, v);
+            tmem_ld_wait();
+            if (valid) {
+                float* dq = p.dQ + ((long long)bh * p.T + qi) * p.hd;
+#pragma unroll
+                for (int e = 0; e < 32; e += 4) {
+                    const int d = half * 32 + e;
+                    if (d < p.hd)
+                        *reinterpret_cast<float4*>(dq + d) = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                                                          __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                }
+            }
+        }
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 33); }
+    }
+
+    __syncwarp();
+    if (*abort_flag) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+constexpr int ATT_DKDV_SMEM = 1024 + 10 * TILE_BYTES + 256;
+constexpr int ATT_DQ_SMEM = 1024 + 8 * TILE_BYTES + 256;
+
+int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, const bf16* att,
+                         const bf16* datt, const float* lse, float* delta, float* dQ, float* dK, float* dV, int B,
+                         int H, int T, int hd, float scale, cudaStream_t stream) {
+    TB_CHECK(hd > 0 && hd <= ATT_HD && hd % 8 == 0, "fused attention needs head_dim <= 64 and a multiple of 8 (got %d)", hd);
+    TB_CHECK(B > 0 && H > 0 && T > 0, "attention dims must be positive");
+    const int BH = B * H, D = H * hd;
+    CUtensorMap tmQ, tmK, tmV, tmdO;
+    TB_TRY(make_operand_map(&tmQ, Q, hd, T, hd, BH, (long long)T * hd, 128));
+    TB_TRY(make_operand_map(&tmK, K, hd, T, hd, BH, (long long)T * hd, 128));
+    TB_TRY(make_operand_map(&tmV, V, hd, T, hd, BH, (long long)T * hd, 128));
+    TB_TRY(make_operand_map4(&tmdO, datt, hd, T, D, H, hd, B, (long long)T * D, 128));
+    AttBwdParams p;
+    p.T = T; p.H = H; p.hd = hd; p.nq = (T + ATT_BM - 1) / ATT_BM;
+    p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+    p.lse = lse; p.delta = delta; p.dQ = dQ; p.dK = dK; p.dV = dV; p.err = ctx->d_err;
+    static bool attr_set[64] = {false};
+    if (!attr_set[ctx->device & 63]) {
+        TB_CUDA(cudaFuncSetAttribute(attention_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_DKDV_SMEM));
+        TB_CUDA(cudaFuncSetAttribute(attention_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_DQ_SMEM));
+        attr_set[ctx->device & 63] = true;
+    }
+    {
+        const long long total = (long long)B * T * H;
+        long long blocks = (total + 255) / 256;
+        if (blocks > 16LL * ctx->sm_count) blocks = 16LL * ctx->sm_count;
+        prof_mark(ctx, "attention_delta", 0.0, 0.0, stream);
+        attention_delta_kernel<<<(int)blocks, 256, 0, stream>>>(att, datt, delta, B, T, H, hd);
+        TB_CUDA(cudaGetLastError());
+        ctx->launches++;
+        prof_close(ctx, stream);
+    }
+    dim3 grid(p.nq, BH);
+    const double tri = (double)BH * T * (double)T * hd;      // one lower-triangular product = tri flops
+    prof_mark(ctx, "attention_bwd_dkdv", 4.0 * tri, (double)BH * T * hd * (2.0 * 4 + 8.0), stream);
+    attention_bwd_dkdv_kernel<<<grid, ATT_BWD_THREADS, ATT_DKDV_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
+    TB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    prof_close(ctx, stream);
+    prof_mark(ctx, "attention_bwd_dq", 3.0 * tri, (double)BH * T * hd * (2.0 * 4 + 4.0), stream);
+    attention_bwd_dq_kernel<<<grid, ATT_BWD_THREADS, ATT_DQ_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
+    TB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    prof_close(ctx, stream);
+    return 0;
+}
+
+constexpr int ATT_FWD_SMEM = 1024 + 7 * TILE_BYTES;
+
+int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, bf16* att, float* lse, int B,
+                         int H, int T, int hd, float scale, cudaStream_t stream) {
+    TB_CHECK(hd > 0 && hd <= ATT_HD && hd % 8 == 0, "fused attention needs head_dim <= 64 and a multiple of 8 (got %d)", hd);
+    TB_CHECK(B > 0 && H > 0 && T > 0, "attention dims must be positive");
+    const int BH = B * H;
+    CUtensorMap tmQ, tmK, tmV;
+    TB_TRY(make_operand_map(&tmQ, Q, hd, T, hd, BH, (long long)T * hd, ATT_BM));
+    TB_TRY(make_operand_map(&tmK, K, hd, T, hd, BH, (long long)T * hd, ATT_BN));
+    TB_TRY(make_operand_map(&tmV, V, hd, T, hd, BH, (long long)T * hd, ATT_BN));
+    AttFwdParams p;
+    p.T = T; p.H = H; p.hd = hd; p.D = H * hd;
+    p.nq = (T + ATT_BM - 1) / ATT_BM;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.att = att; p.lse = lse; p.err = ctx->d_err;
+    static bool attr_set[64] = {false};
+    if (!attr_set[ctx->device & 63]) {
+        TB_CUDA(cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_FWD_SMEM));
+        attr_set[ctx->device & 63] = true;
+    }
+    dim3 grid(p.nq, BH);
+    // algorithmic work: the lower triangle of two products of 2*T*T*hd flops each
+    prof_mark(ctx, "attention_fwd", 2.0 * (double)BH * T * (double)T * hd, (double)BH * T * hd * 2.0 * 4.0, stream);
+    attention_fwd_kernel<<<grid, 192, ATT_FWD_SMEM, stream>>>(tmQ, tmK, tmV, p);
+    TB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    prof_close(ctx, stream);
+    return 0;
+}
+
+}  // namespace tb

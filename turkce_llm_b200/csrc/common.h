@@ -42,9 +42,9 @@ const char* last_error();
         if (_r != 0) return _r;   \
     } while (0)
 
-// ---- optional per-launch timing: an event is recorded in front of every launch; the time
-// to the next mark on the same stream is attributed to that launch (idle gaps included).
-struct ProfRec { const char* tag; cudaEvent_t ev; double flops; double bytes; };
+// ---- optional per-launch timing: one event in front of a launch (prof_mark) and one behind it
+// (prof_close); the difference is the kernel's own time even when the host is the bottleneck.
+struct ProfRec { const char* tag; cudaEvent_t ev; cudaEvent_t ev_end; double flops; double bytes; };
 
 // ---- per-device context
 struct DeviceCtx {
@@ -60,6 +60,8 @@ struct DeviceCtx {
 
 // Records a timing mark when profiling is on (no-op otherwise).
 void prof_mark(DeviceCtx* ctx, const char* tag, double flops, double bytes, cudaStream_t stream);
+// Records the closing event of the last mark (no-op when profiling is off).
+void prof_close(DeviceCtx* ctx, cudaStream_t stream);
 // Returns a pointer that stays valid for the life of the process (for composed tags).
 const char* prof_intern(const char* text);
 
@@ -96,7 +98,7 @@ struct GemmArgs {
     float alpha = 1.0f, beta = 0.0f;        // beta applies to the previous contents of C32
     CausalMode causal = CAUSAL_NONE;
     int splits = 0;                         // 0 = choose; >1 uses scratch for fixed-order partial sums
-    int bn = 0;                             // 0 = choose tile width (64 or 128)
+    int bn = 0;                             // 0 = choose tile width (64, 128 or 192)
     bool pad_cols_writable = false;         // columns N .. round_up(N, 16 bytes) of each output row are padding
 };
 
@@ -105,6 +107,21 @@ int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream);
 int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, size_t workspace_floats,
                         cudaStream_t stream);
 int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn);
+// TMA map over a bf16 matrix seen as (inner, rows, batch) with a 64-element x box_rows box, 128B swizzle
+int make_operand_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld, int batch,
+                     long long batch_stride, int box_rows);
+// the same over a 4-level view (inner, rows, batch0, batch1) -- e.g. one head of a [B*T, H*hd] matrix
+int make_operand_map4(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld,
+                      long long n0, long long stride0, long long n1, long long stride1, int box_rows);
+
+// ---- fused causal attention (attention.cu); Q, K, V bf16 [B*H, T, hd] (hd <= 64, multiple of 8)
+// forward: att bf16 [B*T, H*hd] (heads merged), lse float [B*H, T] (natural-log sum of exponentials)
+int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, bf16* att, float* lse, int B,
+                         int H, int T, int hd, float scale, cudaStream_t stream);
+// backward: datt bf16 [B*T, H*hd] -> dQ, dK, dV float [B*H, T, hd]; delta is float scratch [B*H, T]
+int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, const bf16* att,
+                         const bf16* datt, const float* lse, float* delta, float* dQ, float* dK, float* dV, int B,
+                         int H, int T, int hd, float scale, cudaStream_t stream);
 
 // ---- operand packing (pack.cu): float32 [rows, cols] (ld) -> bf16 [rows, cols] (ld_out), batched
 int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int cols, long long ld_src,

@@ -77,10 +77,18 @@ void prof_mark(DeviceCtx* ctx, const char* tag, double flops, double bytes, cuda
     if (!ctx->prof_on) return;
     if (!ctx->prof) ctx->prof = new std::vector<ProfRec>();
     ProfRec r;
-    r.tag = tag; r.flops = flops; r.bytes = bytes;
+    r.tag = tag; r.flops = flops; r.bytes = bytes; r.ev_end = nullptr;
     if (cudaEventCreate(&r.ev) != cudaSuccess) return;
     cudaEventRecord(r.ev, stream);
     ctx->prof->push_back(r);
+}
+
+void prof_close(DeviceCtx* ctx, cudaStream_t stream) {
+    if (!ctx->prof_on || !ctx->prof || ctx->prof->empty()) return;
+    ProfRec& r = ctx->prof->back();
+    if (r.ev_end != nullptr) return;
+    if (cudaEventCreate(&r.ev_end) != cudaSuccess) { r.ev_end = nullptr; return; }
+    cudaEventRecord(r.ev_end, stream);
 }
 
 int check_device_error(DeviceCtx* ctx, cudaStream_t stream) {

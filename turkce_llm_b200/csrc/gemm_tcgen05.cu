@@ -38,14 +38,14 @@ template <int BN> struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 128) ? 4 : 5;
+    static constexpr int STAGES = (BN == 192) ? 3 : (BN == 128) ? 4 : 5;
     // per epilogue warp: 2 output buffers + 1 residual buffer of 32 rows x 128 B (TMA path);
     // the generic path uses the front of the same region (32 x 36 floats per warp)
     static constexpr int EPI_WARP_BYTES = 3 * 4096;
     static constexpr int STAGING_BYTES = EPI_WARPS * EPI_WARP_BYTES;
     static constexpr int BAR_BYTES = 512;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN;   // 128 or 256: powers of two >= 32
+    static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;   // power of two
 };
 
 struct GemmParams {
@@ -495,8 +495,14 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 3-D view (inner, rows, batch) of a bf16 matrix with a 64-element (128-byte) inner box.
+int make_operand_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld, int batch,
+                     long long batch_stride, int box_rows);
 static int make_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld,
                     int batch, long long batch_stride, int box_rows) {
+    return make_operand_map(map, ptr, inner, rows, ld, batch, batch_stride, box_rows);
+}
+int make_operand_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld,
+                     int batch, long long batch_stride, int box_rows) {
     EncodeTiledFn enc = get_encode_fn();
     TB_CHECK(enc != nullptr, "cuTensorMapEncodeTiled entry point not available");
     TB_CHECK((reinterpret_cast<uintptr_t>(ptr) & 15u) == 0, "GEMM operand must be 16-byte aligned");
@@ -513,6 +519,26 @@ static int make_map(CUtensorMap* map, const bf16* ptr, long long inner, long lon
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (inner=%lld rows=%lld ld=%lld batch=%d)",
              (int)r, inner, rows, ld, batch);
+    return 0;
+}
+
+int make_operand_map4(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld,
+                      long long n0, long long stride0, long long n1, long long stride1, int box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    TB_CHECK(enc != nullptr, "cuTensorMapEncodeTiled entry point not available");
+    TB_CHECK((reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && (ld * 2) % 16 == 0 && (stride0 * 2) % 16 == 0 &&
+                 (stride1 * 2) % 16 == 0,
+             "attention operand must be 16-byte aligned with strides that are multiples of 8 elements");
+    cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)n0, (cuuint64_t)n1};
+    cuuint64_t s0 = n0 > 1 ? (cuuint64_t)stride0 * 2 : (cuuint64_t)ld * 2 * (cuuint64_t)rows;
+    cuuint64_t s1 = n1 > 1 ? (cuuint64_t)stride1 * 2 : (cuuint64_t)ld * 2 * (cuuint64_t)rows;
+    cuuint64_t strides[3] = {(cuuint64_t)ld * 2, s0, s1};
+    cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, 1u, 1u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<bf16*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (4-D operand) failed with code %d", (int)r);
     return 0;
 }
 
@@ -543,15 +569,25 @@ static int make_map_out(CUtensorMap* map, const void* ptr, int elem_bytes, long 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
-    if (a.bn == 64 || a.bn == 128) return a.bn;
+    if (a.bn == 64 || a.bn == 128 || a.bn == 192) return a.bn;
     if (a.N <= 64) return 64;
-    // time ~ waves * tile width; the narrow tile pays ~15% for re-reading A
     const long long mt = (a.M + BM - 1) / BM;
     const long long t128 = mt * ((a.N + 127) / 128) * a.batch;
-    const long long t64 = mt * ((a.N + 63) / 64) * a.batch;
-    const long long w128 = (t128 + ctx->sm_count - 1) / ctx->sm_count;
-    const long long w64 = (t64 + ctx->sm_count - 1) / ctx->sm_count;
-    return (double)w64 * 64.0 * 1.15 < (double)w128 * 128.0 ? 64 : 128;
+    if (t128 * 2 <= ctx->sm_count && a.K >= 16 * BK) return 128;      // split-K will fill the machine
+    // time ~ waves x tile width x a factor for how often a tile re-reads its operands from L2
+    // (flops per operand byte: 43 for 128x64, 64 for 128x128, 77 for 128x192)
+    const int widths[3] = {64, 128, 192};
+    const double factor[3] = {1.30, 1.00, 0.95};
+    int best = 128;
+    double best_cost = 1e30;
+    for (int i = 0; i < 3; ++i) {
+        const long long tiles = mt * ((a.N + widths[i] - 1) / widths[i]) * a.batch;
+        const long long waves = (tiles + ctx->sm_count - 1) / ctx->sm_count;
+        const double cost = (double)waves * widths[i] * factor[i];
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = widths[i]; }
+    }
+    if (a.causal != CAUSAL_NONE && best == 192) best = 128;     // the causal tile rules assume 64 | 128 columns
+    return best;
 }
 
 int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
@@ -583,6 +619,7 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
     gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, p);
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
+    prof_close(ctx, stream);
     (void)a;
     return 0;
 }
@@ -625,21 +662,6 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
               p.strideC16_in % 4 == 0;
     p.vecr = p.residual && (reinterpret_cast<uintptr_t>(p.residual) % 16 == 0) && p.ldr % 4 == 0 && p.strideR % 4 == 0;
 
-    {
-        // algorithmic work: the causal products touch only the lower triangle (half the MACs)
-        const double macs = (double)a.M * a.N * a.K * a.batch * (a.causal != CAUSAL_NONE ? 0.5 : 1.0);
-        const double out_bytes = (double)a.M * a.N * a.batch * ((a.C32 ? 4.0 : 0.0) + (a.C16 ? 2.0 : 0.0)) *
-                                 (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);
-        const double in_bytes = 2.0 * a.batch * ((double)a.M * a.K + (double)a.K * a.N) *
-                                (a.causal == CAUSAL_K_PREFIX || a.causal == CAUSAL_K_SUFFIX ? 0.75 : 1.0);
-        if (ctx->prof_on) {
-            char tag[128];
-            static const char* kn[3] = {"NN", "NT", "TN"};
-            snprintf(tag, sizeof(tag), "gemm_bf16:%s:%dx%dx%d:b%d:s%d:c%d:bn%d", kn[(int)a.kind], a.M, a.N, a.K,
-                     a.batch, splits, (int)a.causal, bn);
-            prof_mark(ctx, prof_intern(tag), 2.0 * macs, in_bytes + out_bytes, stream);
-        }
-    }
     // Tile stores by TMA when the output (and the residual / previous C) is 16-byte addressable
     CUtensorMap tmC, tmR;
     memset(&tmC, 0, sizeof(tmC));
@@ -676,8 +698,24 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
             p.tma_mode = p.C32 ? 1 : 2;
         }
     }
-    if (bn == 64) TB_TRY(launch_impl<64>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
-    else          TB_TRY(launch_impl<128>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
+    {
+        // algorithmic work: the causal products touch only the lower triangle (half the MACs)
+        const double macs = (double)a.M * a.N * a.K * a.batch * (a.causal != CAUSAL_NONE ? 0.5 : 1.0);
+        const double out_bytes = (double)a.M * a.N * a.batch * ((a.C32 ? 4.0 : 0.0) + (a.C16 ? 2.0 : 0.0)) *
+                                 (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);
+        const double in_bytes = 2.0 * a.batch * ((double)a.M * a.K + (double)a.K * a.N) *
+                                (a.causal == CAUSAL_K_PREFIX || a.causal == CAUSAL_K_SUFFIX ? 0.75 : 1.0);
+        if (ctx->prof_on) {
+            char tag[128];
+            static const char* kn[3] = {"NN", "NT", "TN"};
+            snprintf(tag, sizeof(tag), "gemm_bf16:%s:%dx%dx%d:b%d:s%d:c%d:bn%d", kn[(int)a.kind], a.M, a.N, a.K,
+                     a.batch, splits, (int)a.causal, bn);
+            prof_mark(ctx, prof_intern(tag), 2.0 * macs, in_bytes + out_bytes, stream);
+        }
+    }
+    if (bn == 64)       TB_TRY(launch_impl<64>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
+    else if (bn == 192) TB_TRY(launch_impl<192>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
+    else                TB_TRY(launch_impl<128>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
 
     if (splits > 1) {
         TB_CHECK(a.residual == nullptr, "split-K GEMM does not take a residual operand");
@@ -690,6 +728,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
                                                        a.strideC32, a.strideC16, a.beta, a.bias);
         TB_CUDA(cudaGetLastError());
         ctx->launches++;
+        prof_close(ctx, stream);
     }
     return 0;
 }

@@ -57,6 +57,7 @@ int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int 
     pack_bf16_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst, vec);
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
+    prof_close(ctx, stream);
     return 0;
 }
 

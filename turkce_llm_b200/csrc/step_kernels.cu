@@ -18,6 +18,7 @@ static inline int grid_for(long long work, int block, const DeviceCtx* ctx, int 
     do {                            \
         TB_CUDA(cudaGetLastError()); \
         (ctx)->launches++;          \
+        prof_close((ctx), st);      \
     } while (0)
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -142,15 +143,17 @@ template <int NC>
 __global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                       const float* __restrict__ rinv, const float* __restrict__ dy,
                                       float* __restrict__ dx, bf16* __restrict__ dx16, float* __restrict__ dw,
-                                      float* __restrict__ partial, unsigned int* __restrict__ ticket, int rows,
-                                      int cols, int accumulate) {
+                                      float* __restrict__ db, float* __restrict__ partial,
+                                      unsigned int* __restrict__ ticket, int rows, int cols, int accumulate) {
     extern __shared__ float sh_part[];      // [warps][cols]
     __shared__ int is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wpb = blockDim.x >> 5;
-    float acc[NC];
+    // every partial row is [norm-weight sums | column sums of dx], 2*cols floats
+    const int pc = 2 * cols;
+    float acc[NC], accb[NC];
 #pragma unroll
-    for (int k = 0; k < NC; ++k) acc[k] = 0.0f;
+    for (int k = 0; k < NC; ++k) { acc[k] = 0.0f; accb[k] = 0.0f; }
     for (long long row = (long long)blockIdx.x * wpb + warp; row < rows; row += (long long)gridDim.x * wpb) {
         const float* xr = x + row * cols;
         const float* dyr = dy + row * cols;
@@ -176,76 +179,91 @@ __global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* 
                 dx[o] = v;
                 dx16[o] = __float2bfloat16_rn(v);
                 acc[k] += dv[k] * xv[k] * r;
+                accb[k] += v;
             }
         }
     }
 #pragma unroll
     for (int k = 0; k < NC; ++k) {
         const int j = lane + 32 * k;
-        if (j < cols) sh_part[warp * cols + j] = acc[k];
+        if (j < cols) { sh_part[warp * pc + j] = acc[k]; sh_part[warp * pc + cols + j] = accb[k]; }
     }
     __syncthreads();
-    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+    for (int j = threadIdx.x; j < pc; j += blockDim.x) {
         float t = sh_part[j];
-        for (int k = 1; k < wpb; ++k) t += sh_part[k * cols + j];
-        partial[(long long)blockIdx.x * cols + j] = t;
+        for (int k = 1; k < wpb; ++k) t += sh_part[k * pc + j];
+        partial[(long long)blockIdx.x * pc + j] = t;
+    }
+    // two-level fixed-order sum of the partial rows: blocks form groups of 32; the block that draws
+    // a group's last ticket adds that group's rows in block order, and the group finisher that
+    // draws the last second-level ticket adds the group sums in group order
+    const unsigned int nb = gridDim.x;
+    const unsigned int group = blockIdx.x >> 5, ngroups = (nb + 31u) >> 5;
+    const unsigned int gsize = min(32u, nb - (group << 5));
+    float* gpartial = partial + (long long)nb * pc;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = (atomicAdd(&ticket[1 + group], 1u) == gsize - 1u);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int j = threadIdx.x; j < pc; j += blockDim.x) {
+        float v[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+            v[k] = (unsigned)k < gsize ? __ldcg(&partial[(long long)((group << 5) + k) * pc + j]) : 0.0f;
+        float t = v[0];
+#pragma unroll
+        for (int k = 1; k < 32; ++k) t += v[k];
+        gpartial[(long long)group * pc + j] = t;
     }
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1u) == gridDim.x - 1u);
-    __syncthreads();
-    if (is_last) {
-        __threadfence();
-        // warp p adds the partial rows p, p+8, p+16, ... of each column in that order; then the
-        // eight sub-sums of a column are added in warp order
-        const unsigned int nb = gridDim.x;
-        for (int j0 = 0; j0 < cols; j0 += 32) {
-            const int j = j0 + lane;
-            float t = 0.0f;
-            if (j < cols) {
-                unsigned int b = warp;
-                for (; b + 3 * wpb < nb; b += 4 * wpb) {
-                    const float v0 = __ldcg(&partial[(long long)b * cols + j]);
-                    const float v1 = __ldcg(&partial[(long long)(b + wpb) * cols + j]);
-                    const float v2 = __ldcg(&partial[(long long)(b + 2 * wpb) * cols + j]);
-                    const float v3 = __ldcg(&partial[(long long)(b + 3 * wpb) * cols + j]);
-                    t += v0; t += v1; t += v2; t += v3;
-                }
-                for (; b < nb; b += wpb) t += __ldcg(&partial[(long long)b * cols + j]);
-            }
-            if (j < cols) sh_part[warp * cols + j] = t;
-        }
-        __syncthreads();
-        for (int j = threadIdx.x; j < cols; j += blockDim.x) {
-            float t = sh_part[j];
-            for (int k = 1; k < wpb; ++k) t += sh_part[k * cols + j];
-            dw[j] += t;
-        }
-        if (threadIdx.x == 0) *ticket = 0u;
+    if (threadIdx.x == 0) {
+        ticket[1 + group] = 0u;
+        is_last = (atomicAdd(&ticket[0], 1u) == ngroups - 1u);
     }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int j = threadIdx.x; j < pc; j += blockDim.x) {
+        float v[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] = (unsigned)k < ngroups ? __ldcg(&gpartial[(long long)k * pc + j]) : 0.0f;
+        float t = v[0];
+#pragma unroll
+        for (int k = 1; k < 32; ++k) t += v[k];
+        if (j < cols) dw[j] += t;
+        else if (db) db[j - cols] += t;
+    }
+    if (threadIdx.x == 0) ticket[0] = 0u;
 }
 
-constexpr int kNormBwdBlocks = 296;      // partial rows of the fused norm-weight gradient
+constexpr int kNormBwdBlocks = 1024;     // partial rows of the fused norm-weight gradient
 
-size_t rmsnorm_bwd_scratch_floats(int cols) { return 64 + (size_t)kNormBwdBlocks * cols; }
+size_t rmsnorm_bwd_scratch_floats(int cols) { return 64 + (size_t)(kNormBwdBlocks + 32) * cols * 2; }
 
 int launch_rmsnorm_bwd_dw(DeviceCtx* ctx, const float* x, const float* w, const float* rinv, const float* dy,
-                          float* dx, bf16* dx16, float* dw, float* scratch, int rows, int cols, int accumulate,
-                          cudaStream_t st) {
+                          float* dx, bf16* dx16, float* dw, float* db, float* scratch, int rows, int cols,
+                          int accumulate, cudaStream_t st) {
     TB_CHECK(cols <= 1024, "fused RMSNorm backward supports at most 1024 columns (got %d)", cols);
+    static bool attr_set = false;
+    if (!attr_set && cols > 384) {
+        TB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_dw_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
+        attr_set = true;
+    }
     int blocks = (rows + 7) / 8;
     if (blocks > kNormBwdBlocks) blocks = kNormBwdBlocks;
-    if (blocks > 2 * ctx->sm_count) blocks = 2 * ctx->sm_count;
     unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch);
     float* partial = scratch + 64;
-    const size_t smem = (size_t)8 * cols * sizeof(float);
+    const size_t smem = (size_t)8 * 2 * cols * sizeof(float);
     prof_mark(ctx, "rmsnorm_bwd", 0.0, 0.0, st);
     if (cols <= 384)
-        rmsnorm_bwd_dw_kernel<12><<<blocks, 256, smem, st>>>(x, w, rinv, dy, dx, dx16, dw, partial, ticket, rows, cols,
-                                                              accumulate);
+        rmsnorm_bwd_dw_kernel<12><<<blocks, 256, smem, st>>>(x, w, rinv, dy, dx, dx16, dw, db, partial, ticket, rows,
+                                                              cols, accumulate);
     else
-        rmsnorm_bwd_dw_kernel<32><<<blocks, 256, smem, st>>>(x, w, rinv, dy, dx, dx16, dw, partial, ticket, rows, cols,
-                                                              accumulate);
+        rmsnorm_bwd_dw_kernel<32><<<blocks, 256, smem, st>>>(x, w, rinv, dy, dx, dx16, dw, db, partial, ticket, rows,
+                                                              cols, accumulate);
     TB_LAUNCHED(ctx);
     return 0;
 }

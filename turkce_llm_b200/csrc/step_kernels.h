@@ -15,11 +15,13 @@ int launch_rmsnorm_fwd(DeviceCtx*, const float* x, const float* w, bf16* out, fl
 // dx (+)= rmsnorm backward; dx16 = bf16(dx); wtmp[n,j] = dy*x*r (summed over rows by colsum)
 int launch_rmsnorm_bwd(DeviceCtx*, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
                        bf16* dx16, float* wtmp, int rows, int cols, int accumulate, cudaStream_t);
-// the same with the norm-weight gradient fused: dw[j] += sum_rows dy*x*r (fixed order);
-// scratch needs rmsnorm_bwd_scratch_floats(cols) floats whose first 64 words start at zero
+// the same with two column sums fused (fixed order): the norm-weight gradient dw[j] += sum_rows dy*x*r
+// and, when db is given, db[j] += sum_rows dx[row, j] (the bias gradient of the layer that produced
+// this residual stream).  scratch needs rmsnorm_bwd_scratch_floats(cols) floats, first 64 words zero.
 size_t rmsnorm_bwd_scratch_floats(int cols);
 int launch_rmsnorm_bwd_dw(DeviceCtx*, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
-                          bf16* dx16, float* dw, float* scratch, int rows, int cols, int accumulate, cudaStream_t);
+                          bf16* dx16, float* dw, float* db, float* scratch, int rows, int cols, int accumulate,
+                          cudaStream_t);
 int launch_rope_split(DeviceCtx*, const float* qkv, const float* cos_t, const float* sin_t, bf16* Q, bf16* K, bf16* V,
                       int B, int T, int H, int hd, cudaStream_t);
 int launch_rope_merge_bwd(DeviceCtx*, const float* dQ, const float* dK, const float* dV, const float* cos_t,

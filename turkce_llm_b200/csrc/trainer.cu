@@ -31,7 +31,8 @@ enum { PK_ATTN_NORM = 0, PK_WQKV, PK_BQKV, PK_WO, PK_BO, PK_FFN_NORM, PK_WGU, PK
 
 struct LayerActs {
     float* x_in;  bf16* n1; float* r1;
-    bf16 *Q, *K, *V, *P, *att;
+    bf16 *Q, *K, *V, *P, *att;     // P [BH,T,T] only on the unfused attention path
+    float* lse;                    // [BH,T] on the fused path
     float* x2;    bf16* n2; float* r2;
     float* gu;    bf16* h;
 };
@@ -80,6 +81,8 @@ struct TbTrainer {
     struct Segment { int state = 0; cudaGraphExec_t exec = nullptr; long long launches = 0; };
     std::vector<Segment> segments;
     bool graphs_on = true;
+    bool fused_attention = true;   // head_dim <= 64: scores stay on chip
+    float* att_delta = nullptr;
     bool owns_stream = false;
 };
 
@@ -149,22 +152,26 @@ int forward(TbTrainer* g, bool want_grad) {
         TB_TRY(linear_fwd(g, a.n1, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, N,
                           3 * D, D));
         TB_TRY(launch_rope_split(c, g->qkv, g->cos_t, g->sin_t, a.Q, a.K, a.V, B, T, H, hd, st));
-        {   // S = Q K^T per (batch, head), lower-triangular tiles only
-            GemmArgs s;
-            s.kind = GEMM_NT; s.A = a.Q; s.B = a.K; s.M = T; s.N = T; s.K = hd; s.lda = hd; s.ldb = hd;
-            s.batch = BH; s.strideA = sThd; s.strideB = sThd;
-            s.C32 = g->S; s.ldc32 = Tp; s.strideC32 = sTT;
-            s.causal = CAUSAL_SKIP_UPPER; s.splits = 1;
-            TB_TRY(gemm(g, s));
-        }
-        TB_TRY(launch_attn_softmax_fwd(c, g->S, a.P, BH, T, Tp, g->scale, st));
-        {   // att[b*T+t, h*hd+d] = sum_j P[j] V[j,d], written straight into the merged layout
-            GemmArgs o;
-            o.kind = GEMM_NN; o.A = a.P; o.B = a.V; o.M = T; o.N = hd; o.K = T; o.lda = Tp; o.ldb = hd;
-            o.batch = BH; o.strideA = sTT; o.strideB = sThd;
-            o.C16 = a.att; o.ldc16 = D; o.c_inner = H; o.strideC16 = (long long)T * D; o.strideC16_in = hd;
-            o.causal = CAUSAL_K_PREFIX; o.splits = 1;
-            TB_TRY(gemm(g, o));
+        if (g->fused_attention) {
+            TB_TRY(launch_attention_fwd(c, a.Q, a.K, a.V, a.att, a.lse, B, H, T, hd, g->scale, st));
+        } else {
+            {   // S = Q K^T per (batch, head), lower-triangular tiles only
+                GemmArgs s;
+                s.kind = GEMM_NT; s.A = a.Q; s.B = a.K; s.M = T; s.N = T; s.K = hd; s.lda = hd; s.ldb = hd;
+                s.batch = BH; s.strideA = sThd; s.strideB = sThd;
+                s.C32 = g->S; s.ldc32 = Tp; s.strideC32 = sTT;
+                s.causal = CAUSAL_SKIP_UPPER; s.splits = 1;
+                TB_TRY(gemm(g, s));
+            }
+            TB_TRY(launch_attn_softmax_fwd(c, g->S, a.P, BH, T, Tp, g->scale, st));
+            {   // att[b*T+t, h*hd+d] = sum_j P[j] V[j,d], written straight into the merged layout
+                GemmArgs o;
+                o.kind = GEMM_NN; o.A = a.P; o.B = a.V; o.M = T; o.N = hd; o.K = T; o.lda = Tp; o.ldb = hd;
+                o.batch = BH; o.strideA = sTT; o.strideB = sThd;
+                o.C16 = a.att; o.ldc16 = D; o.c_inner = H; o.strideC16 = (long long)T * D; o.strideC16_in = hd;
+                o.causal = CAUSAL_K_PREFIX; o.splits = 1;
+                TB_TRY(gemm(g, o));
+            }
         }
         TB_TRY(linear_fwd(g, a.att, P16(g, pidx(l, PK_WO)), P32(g, pidx(l, PK_BO)), a.x_in, a.x2, nullptr, N, D, D));
         TB_TRY(launch_rmsnorm_fwd(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.n2, a.r2, N, D, g->eps, st));
@@ -205,8 +212,9 @@ int backward_head(TbTrainer* g) {
         a.C32 = g->dn; a.ldc32 = D; a.splits = 1;
         TB_TRY(gemm(g, a));
     }
+    // dres (the gradient of the last layer's output) also yields that layer's b_down gradient
     TB_TRY(launch_rmsnorm_bwd_dw(c, g->x_final, P32(g, p_final), g->rf, g->dn, g->dres, g->dres16, G32(g, p_final),
-                                 g->norm_scratch, N, D, 0, st));
+                                 g->L > 0 ? G32(g, pidx(g->L - 1, PK_BDOWN)) : nullptr, g->norm_scratch, N, D, 0, st));
     return 0;
 }
 
@@ -220,19 +228,23 @@ int backward_layer(TbTrainer* g, int l) {
 
     // ---- FFN: x3 = x2 + (h @ Wd + bd); dres = dx3
     TB_TRY(linear_dw(g, a.h, g->dres16, G32(g, pidx(l, PK_WDOWN)), N, D, F));
-    TB_TRY(launch_colsum_f32(c, g->dres, G32(g, pidx(l, PK_BDOWN)), g->colsum_partial, N, D, st));
+    // (b_down's gradient, the column sum of dres, was produced together with dres)
     TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WDOWN)), g->dh, nullptr, N, D, F));
     TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->dgu, N, F, st));
     TB_TRY(linear_dw(g, a.n2, g->dgu, G32(g, pidx(l, PK_WGU)), N, 2 * F, D));
     TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
     TB_TRY(linear_dx(g, g->dgu, P16(g, pidx(l, PK_WGU)), g->dn, nullptr, N, 2 * F, D));
     TB_TRY(launch_rmsnorm_bwd_dw(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.r2, g->dn, g->dres, g->dres16,
-                                 G32(g, pidx(l, PK_FFN_NORM)), g->norm_scratch, N, D, 1, st));
+                                 G32(g, pidx(l, PK_FFN_NORM)), G32(g, pidx(l, PK_BO)), g->norm_scratch, N, D, 1, st));
 
     // ---- attention: x2 = x + (att @ Wo + bo); dres = dx2
     TB_TRY(linear_dw(g, a.att, g->dres16, G32(g, pidx(l, PK_WO)), N, D, D));
-    TB_TRY(launch_colsum_f32(c, g->dres, G32(g, pidx(l, PK_BO)), g->colsum_partial, N, D, st));
+    // (bo's gradient came with dres as well)
     TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WO)), nullptr, g->datt, N, D, D));
+    if (g->fused_attention) {
+        TB_TRY(launch_attention_bwd(c, a.Q, a.K, a.V, a.att, g->datt, a.lse, g->att_delta, g->dQ, g->dK, g->dV, B, H, T,
+                                    hd, g->scale, st));
+    } else {
     TB_TRY(launch_heads_split(c, g->datt, g->dO, B, T, H, hd, st));
     {   // dV = P^T dO
         GemmArgs v;
@@ -263,12 +275,14 @@ int backward_layer(TbTrainer* g, int l) {
         k.C32 = g->dK; k.ldc32 = hd; k.strideC32 = sThd; k.causal = CAUSAL_K_SUFFIX; k.splits = 1;
         TB_TRY(gemm(g, k));
     }
+    }
     TB_TRY(launch_rope_merge_bwd(c, g->dQ, g->dK, g->dV, g->cos_t, g->sin_t, g->dqkv, B, T, H, hd, st));
     TB_TRY(linear_dw(g, a.n1, g->dqkv, G32(g, pidx(l, PK_WQKV)), N, 3 * D, D));
     TB_TRY(launch_colsum_bf16(c, g->dqkv, G32(g, pidx(l, PK_BQKV)), g->colsum_partial, N, 3 * D, st));
     TB_TRY(linear_dx(g, g->dqkv, P16(g, pidx(l, PK_WQKV)), g->dn, nullptr, N, 3 * D, D));
     TB_TRY(launch_rmsnorm_bwd_dw(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.r1, g->dn, g->dres, g->dres16,
-                                 G32(g, pidx(l, PK_ATTN_NORM)), g->norm_scratch, N, D, 1, st));
+                                 G32(g, pidx(l, PK_ATTN_NORM)), l > 0 ? G32(g, pidx(l - 1, PK_BDOWN)) : nullptr,
+                                 g->norm_scratch, N, D, 1, st));
     return 0;
 }
 
@@ -397,6 +411,7 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         g->owns_stream = true;
     }
     g->graphs_on = getenv("TB_NO_GRAPH") == nullptr;
+    g->fused_attention = (D / H) <= 64 && getenv("TB_NO_FUSED_ATTENTION") == nullptr;
     g->V = V; g->D = D; g->H = H; g->L = L; g->F = F; g->T = T; g->B = B; g->N = B * T; g->hd = D / H;
     g->Vp = round_up(V, 8);
     g->Tp = round_up(T, 8);
@@ -426,18 +441,26 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         LayerActs& a = g->layers[l];
         TB_TRY(dalloc(g, &a.x_in, N * D)); TB_TRY(dalloc(g, &a.n1, N * D)); TB_TRY(dalloc(g, &a.r1, N));
         TB_TRY(dalloc(g, &a.Q, N * D)); TB_TRY(dalloc(g, &a.K, N * D)); TB_TRY(dalloc(g, &a.V, N * D));
-        TB_TRY(dalloc(g, &a.P, BHT * Tp)); TB_TRY(dalloc(g, &a.att, N * D));
+        if (g->fused_attention) { a.P = nullptr; TB_TRY(dalloc(g, &a.lse, BHT)); }
+        else { a.lse = nullptr; TB_TRY(dalloc(g, &a.P, BHT * Tp)); }
+        TB_TRY(dalloc(g, &a.att, N * D));
         TB_TRY(dalloc(g, &a.x2, N * D)); TB_TRY(dalloc(g, &a.n2, N * D)); TB_TRY(dalloc(g, &a.r2, N));
         TB_TRY(dalloc(g, &a.gu, N * 2 * F)); TB_TRY(dalloc(g, &a.h, N * F));
     }
     TB_TRY(dalloc(g, &g->x_final, N * D)); TB_TRY(dalloc(g, &g->nf, N * D)); TB_TRY(dalloc(g, &g->rf, N));
     TB_TRY(dalloc(g, &g->logits, N * g->Vp)); TB_TRY(dalloc(g, &g->dlogits, N * g->Vp));
-    TB_TRY(dalloc(g, &g->qkv, N * 3 * D)); TB_TRY(dalloc(g, &g->S, BHT * Tp)); TB_TRY(dalloc(g, &g->dP, BHT * Tp));
+    TB_TRY(dalloc(g, &g->qkv, N * 3 * D));
+    if (g->fused_attention) {
+        TB_TRY(dalloc(g, &g->att_delta, BHT));
+    } else {
+        TB_TRY(dalloc(g, &g->S, BHT * Tp)); TB_TRY(dalloc(g, &g->dP, BHT * Tp));
+    }
     TB_TRY(dalloc(g, &g->dn, N * D)); TB_TRY(dalloc(g, &g->dres, N * D)); TB_TRY(dalloc(g, &g->wtmp, N * D));
     TB_TRY(dalloc(g, &g->dh, N * F));
     TB_TRY(dalloc(g, &g->dQ, N * D)); TB_TRY(dalloc(g, &g->dK, N * D)); TB_TRY(dalloc(g, &g->dV, N * D));
     TB_TRY(dalloc(g, &g->dres16, N * D)); TB_TRY(dalloc(g, &g->dgu, N * 2 * F)); TB_TRY(dalloc(g, &g->datt, N * D));
-    TB_TRY(dalloc(g, &g->dO, N * D)); TB_TRY(dalloc(g, &g->dS, BHT * Tp)); TB_TRY(dalloc(g, &g->dqkv, N * 3 * D));
+    TB_TRY(dalloc(g, &g->dqkv, N * 3 * D));
+    if (!g->fused_attention) { TB_TRY(dalloc(g, &g->dO, N * D)); TB_TRY(dalloc(g, &g->dS, BHT * Tp)); }
     TB_CHECK(D <= 1024, "d_model up to 1024 is supported (got %d)", D);
     {
         const size_t nc = colsum_partial_floats(std::max(3 * D, 2 * F)), nn = rmsnorm_bwd_scratch_floats(D);
@@ -447,8 +470,10 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         TB_CUDA(cudaMemset(g->norm_scratch, 0, nn * 4));
     }
     // dS and P rows are read by whole 128-tiles: start them from zero so never-written tails are finite
-    TB_CUDA(cudaMemset(g->dS, 0, BHT * Tp * 2));
-    for (int l = 0; l < L; ++l) TB_CUDA(cudaMemset(g->layers[l].P, 0, BHT * Tp * 2));
+    if (!g->fused_attention) {
+        TB_CUDA(cudaMemset(g->dS, 0, BHT * Tp * 2));
+        for (int l = 0; l < L; ++l) TB_CUDA(cudaMemset(g->layers[l].P, 0, BHT * Tp * 2));
+    }
 
     // split-K partials for the weight-gradient GEMMs: the largest is [D, 2F] or [D, 3D] or [F, D]
     {

@@ -37,6 +37,8 @@ SIGNATURES = {
                           _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _i64,
                           _f, _f, _i, _i, _i, _vp]),
     "tb_gemm_bf16_splitk_static": (_i, [_i, _vp, _vp, _i, _i, _i, _i64, _i64, _vp, _i64, _vp, _f, _f, _i, _i, _vp]),
+    "tb_attention_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
+    "tb_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
     "tb_trainer_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "tb_trainer_destroy": (_i, [_vp]),
@@ -163,6 +165,15 @@ def gemm_bf16_splitk_static(kind, A, B, M, N, K, lda, ldb, C32, ldc32, bias=None
     """Split-K GEMM whose scratch is built into the library image: allocates nothing (see the header)."""
     check(load().tb_gemm_bf16_splitk_static(kind, _ptr(A), _ptr(B), M, N, K, lda, ldb, _ptr(C32), ldc32, _ptr(bias),
                                             alpha, beta, splits, 1 if wait else 0, _stream()))
+
+
+def attention_fwd(Q, K, V, att, lse, B, H, T, hd, scale):
+    check(load().tb_attention_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(att), _ptr(lse), B, H, T, hd, scale, _stream()))
+
+
+def attention_bwd(Q, K, V, att, datt, lse, delta, dQ, dK, dV, B, H, T, hd, scale):
+    check(load().tb_attention_bwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(att), _ptr(datt), _ptr(lse), _ptr(delta),
+                                  _ptr(dQ), _ptr(dK), _ptr(dV), B, H, T, hd, scale, _stream()))
 
 
 def pack_bf16(src, dst, rows, cols, ld_src, ld_dst, batch=1, s_src=0, s_dst=0):
