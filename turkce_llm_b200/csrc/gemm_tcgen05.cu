@@ -452,26 +452,59 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
-// Adds split-K partials in split order: out = sum_s part[s] (+ beta * out), float4-wide.
+// Adds split-K partials in split order: out = sum_s part[s] (+ bias) (+ beta * out).  Loads of four
+// splits are issued together; the additions stay in split order.
+template <int VEC>
 __global__ void reduce_splits_kernel(const float* __restrict__ part, float* __restrict__ out,
                                      bf16* __restrict__ out16, int M, int N, long long ldc32, long long ldc16,
                                      int splits, long long strideC32, long long strideC16, float beta,
                                      const float* __restrict__ bias) {
     const long long per = (long long)M * N;
     const int z = blockIdx.y;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per;
-         i += (long long)gridDim.x * blockDim.x) {
+    const long long nvec = per / VEC;
+    for (long long iv = (long long)blockIdx.x * blockDim.x + threadIdx.x; iv < nvec;
+         iv += (long long)gridDim.x * blockDim.x) {
+        const long long i = iv * VEC;
         const int r = (int)(i / N), cidx = (int)(i % N);
         const float* src = part + ((long long)z * splits) * per + i;
-        float s = src[0];
-        for (int k = 1; k < splits; ++k) s += src[(long long)k * per];
-        if (bias) s += bias[cidx];
-        if (out) {
-            float* o = out + (long long)z * strideC32 + (long long)r * ldc32 + cidx;
-            if (beta != 0.0f) s += beta * *o;
-            *o = s;
+        float s[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) s[e] = 0.0f;
+        int k = 0;
+        for (; k + 4 <= splits; k += 4) {
+            float v[4][VEC];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (VEC == 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(src + (long long)(k + u) * per);
+                    v[u][0] = t.x; v[u][1 % VEC] = t.y; v[u][2 % VEC] = t.z; v[u][3 % VEC] = t.w;
+                } else {
+                    v[u][0] = src[(long long)(k + u) * per];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) s[e] += v[u][e];
         }
-        if (out16) out16[(long long)z * strideC16 + (long long)r * ldc16 + cidx] = __float2bfloat16_rn(s);
+        for (; k < splits; ++k) {
+            if (VEC == 4) {
+                const float4 t = *reinterpret_cast<const float4*>(src + (long long)k * per);
+                s[0] += t.x; s[1 % VEC] += t.y; s[2 % VEC] += t.z; s[3 % VEC] += t.w;
+            } else {
+                s[0] += src[(long long)k * per];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            if (bias) s[e] += bias[cidx + e];
+            if (out) {
+                float* o = out + (long long)z * strideC32 + (long long)r * ldc32 + cidx + e;
+                if (beta != 0.0f) s[e] += beta * *o;
+                *o = s[e];
+            }
+            if (out16) out16[(long long)z * strideC16 + (long long)r * ldc16 + cidx + e] = __float2bfloat16_rn(s[e]);
+        }
     }
 }
 
@@ -720,12 +753,19 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     if (splits > 1) {
         TB_CHECK(a.residual == nullptr, "split-K GEMM does not take a residual operand");
         const long long per = (long long)a.M * a.N;
-        int blocks = (int)((per + 255) / 256);
-        if (blocks > 4 * ctx->sm_count) blocks = 4 * ctx->sm_count;
+        const bool vec4 = a.N % 4 == 0;      // a float4 never straddles a row; partial slabs are 16-byte aligned
+        const long long nvec = vec4 ? per / 4 : per;
+        int blocks = (int)((nvec + 255) / 256);
+        if (blocks > 8 * ctx->sm_count) blocks = 8 * ctx->sm_count;
+        if (blocks < 1) blocks = 1;
         dim3 grid(blocks, a.batch);
         prof_mark(ctx, "splitk_reduce", 0.0, (double)(splits + 2) * per * a.batch * 4.0, stream);
-        reduce_splits_kernel<<<grid, 256, 0, stream>>>(ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits,
-                                                       a.strideC32, a.strideC16, a.beta, a.bias);
+        if (vec4)
+            reduce_splits_kernel<4><<<grid, 256, 0, stream>>>(ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits,
+                                                              a.strideC32, a.strideC16, a.beta, a.bias);
+        else
+            reduce_splits_kernel<1><<<grid, 256, 0, stream>>>(ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits,
+                                                              a.strideC32, a.strideC16, a.beta, a.bias);
         TB_CUDA(cudaGetLastError());
         ctx->launches++;
         prof_close(ctx, stream);

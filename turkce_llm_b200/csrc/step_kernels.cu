@@ -158,15 +158,19 @@ __global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* 
         const float* xr = x + row * cols;
         const float* dyr = dy + row * cols;
         const float r = rinv[row];
-        float xv[NC], dv[NC];
+        float xv[NC], dv[NC], wv[NC], ov[NC];
         float S = 0.0f;
 #pragma unroll
         for (int k = 0; k < NC; ++k) {
             const int j = lane + 32 * k;
-            xv[k] = j < cols ? xr[j] : 0.0f;
-            dv[k] = j < cols ? dyr[j] : 0.0f;
-            S += j < cols ? dv[k] * w[j] * xv[k] : 0.0f;
+            const bool in = j < cols;
+            xv[k] = in ? xr[j] : 0.0f;
+            dv[k] = in ? dyr[j] : 0.0f;
+            wv[k] = in ? w[j] : 0.0f;
+            ov[k] = (in && accumulate) ? dx[row * cols + j] : 0.0f;
         }
+#pragma unroll
+        for (int k = 0; k < NC; ++k) S += dv[k] * wv[k] * xv[k];
         S = warp_sum(S);
         const float kk = (r * r * r) / (float)cols;
 #pragma unroll
@@ -174,8 +178,7 @@ __global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* 
             const int j = lane + 32 * k;
             if (j < cols) {
                 const long long o = row * cols + j;
-                float v = w[j] * r * dv[k] - kk * xv[k] * S;
-                if (accumulate) v += dx[o];
+                const float v = wv[k] * r * dv[k] - kk * xv[k] * S + ov[k];
                 dx[o] = v;
                 dx16[o] = __float2bfloat16_rn(v);
                 acc[k] += dv[k] * xv[k] * r;
@@ -623,26 +626,47 @@ template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfl
 // One launch: every block writes the partial of its row chunk, takes a ticket, and the block that
 // draws the last ticket of a 32-column group adds that group's partials in chunk order.  The
 // ticket only decides WHO does the final sum, never its order, so the result is reproducible.
+// Column sums of a [rows, cols] matrix, out[c] += sum_r in[r, c], in one launch.  A block owns 64
+// columns (thread = 2 adjacent columns) x one chunk of rows; it writes the partial of its chunk,
+// takes a ticket, and the block that draws the last ticket of a column group adds that group's
+// partials in chunk order.  The ticket only decides WHO does the final sum, never its order.
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const bf16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
 template <typename T>
 __global__ void colsum_kernel(const T* __restrict__ in, float* __restrict__ out, float* __restrict__ partial,
                               unsigned int* __restrict__ tickets, int rows, int cols) {
-    __shared__ float part[8][33];
+    __shared__ float2 part[8][33];
     __shared__ int is_last;
     const int tx = threadIdx.x, ty = threadIdx.y;
-    const int c = blockIdx.x * 32 + tx;
+    const int c = blockIdx.x * 64 + 2 * tx;          // cols is even (checked by the launcher)
     const int chunk = blockIdx.y;
     const int per = (rows + kColsumChunks - 1) / kColsumChunks;
     const int r0 = chunk * per, r1 = min(rows, r0 + per);
-    float s = 0.0f;
-    if (c < cols)
-        for (int r = r0 + ty; r < r1; r += 8) s += to_f32<T>(in[(long long)r * cols + c]);
+    float2 s = make_float2(0.0f, 0.0f);
+    if (c < cols) {
+        int r = r0 + ty;
+        for (; r + 24 < r1; r += 32) {               // four independent loads in flight
+            const float2 a = load2(in + (long long)r * cols + c);
+            const float2 b = load2(in + (long long)(r + 8) * cols + c);
+            const float2 d = load2(in + (long long)(r + 16) * cols + c);
+            const float2 e = load2(in + (long long)(r + 24) * cols + c);
+            s.x += a.x; s.y += a.y; s.x += b.x; s.y += b.y; s.x += d.x; s.y += d.y; s.x += e.x; s.y += e.y;
+        }
+        for (; r < r1; r += 8) {
+            const float2 a = load2(in + (long long)r * cols + c);
+            s.x += a.x; s.y += a.y;
+        }
+    }
     part[ty][tx] = s;
     __syncthreads();
     if (ty == 0 && c < cols) {
-        float t = part[0][tx];
+        float2 t = part[0][tx];
 #pragma unroll
-        for (int k = 1; k < 8; ++k) t += part[k][tx];
-        partial[(long long)chunk * cols + c] = t;
+        for (int k = 1; k < 8; ++k) { t.x += part[k][tx].x; t.y += part[k][tx].y; }
+        *reinterpret_cast<float2*>(&partial[(long long)chunk * cols + c]) = t;
     }
     __threadfence();
     __syncthreads();
@@ -651,24 +675,26 @@ __global__ void colsum_kernel(const T* __restrict__ in, float* __restrict__ out,
     if (is_last) {
         __threadfence();
         // lane ty adds chunks 8*ty .. 8*ty+7 in order, then lane 0 adds the eight sub-sums in order
-        float t = 0.0f;
+        float2 t = make_float2(0.0f, 0.0f);
         if (c < cols) {
             constexpr int per_lane = kColsumChunks / 8;
-            float v[per_lane];
+            float2 v[per_lane];
 #pragma unroll
-            for (int k = 0; k < per_lane; ++k) v[k] = __ldcg(&partial[(long long)(ty * per_lane + k) * cols + c]);
+            for (int k = 0; k < per_lane; ++k)
+                v[k] = __ldcg(reinterpret_cast<const float2*>(&partial[(long long)(ty * per_lane + k) * cols + c]));
             t = v[0];
 #pragma unroll
-            for (int k = 1; k < per_lane; ++k) t += v[k];
+            for (int k = 1; k < per_lane; ++k) { t.x += v[k].x; t.y += v[k].y; }
         }
         __syncthreads();
         part[ty][tx] = t;
         __syncthreads();
         if (ty == 0 && c < cols) {
-            float u = part[0][tx];
+            float2 u = part[0][tx];
 #pragma unroll
-            for (int k = 1; k < 8; ++k) u += part[k][tx];
-            out[c] += u;
+            for (int k = 1; k < 8; ++k) { u.x += part[k][tx].x; u.y += part[k][tx].y; }
+            out[c] += u.x;
+            out[c + 1] += u.y;
         }
         if (tx == 0 && ty == 0) tickets[blockIdx.x] = 0u;     // ready for the next launch
     }
@@ -676,8 +702,9 @@ __global__ void colsum_kernel(const T* __restrict__ in, float* __restrict__ out,
 
 template <typename T>
 static int colsum_impl(DeviceCtx* ctx, const T* in, float* out, float* partial, int rows, int cols, cudaStream_t st) {
-    TB_CHECK((cols + 31) / 32 <= kTicketWords, "column sum supports at most %d columns", kTicketWords * 32);
-    dim3 grid((cols + 31) / 32, kColsumChunks), block(32, 8);
+    TB_CHECK((cols + 63) / 64 <= kTicketWords, "column sum supports at most %d columns", kTicketWords * 64);
+    TB_CHECK(cols % 2 == 0, "column sum needs an even number of columns (got %d)", cols);
+    dim3 grid((cols + 63) / 64, kColsumChunks), block(32, 8);
     unsigned int* tickets = reinterpret_cast<unsigned int*>(partial);
     prof_mark(ctx, "colsum", 0.0, 0.0, st);
     colsum_kernel<T><<<grid, block, 0, st>>>(in, out, partial + kTicketWords, tickets, rows, cols);
