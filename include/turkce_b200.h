@@ -24,7 +24,10 @@ extern "C" {
 #define TB_GEMM_NT 1   /* A [M,K] lda, B [N,K] ldb */
 #define TB_GEMM_TN 2   /* A [K,M] lda, B [K,N] ldb */
 
-/* operand precision of the tensor-core product; accumulation is always FP32 */
+/* operand precision of the tensor-core product; accumulation is always FP32.
+ * BF16: operands rounded to bf16 (kind::f16).  TF32: float32 operands read as tf32 (kind::tf32).
+ * FP32: each operand split into two tf32-exact pieces and multiplied as hi*hi + hi*lo + lo*hi
+ * (three TF32 products in one accumulator): about 2^-20 relative error, for the <= 1e-5 bound. */
 #define TB_PREC_BF16 0
 #define TB_PREC_TF32 1
 #define TB_PREC_FP32 2

@@ -54,6 +54,68 @@ def test_gemm_f32_matches_oracle(tb, oracle, kind, shape):
     assert rel_to_maxabs(got, want32) <= TOL_BF16_MODE
 
 
+TOL_TF32_MODE = 5e-3
+TOL_FP32_MODE = 1e-5
+
+
+@pytest.mark.parametrize("kind", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("shape", [(4, 5, 3), (127, 129, 65), (200, 100, 72), (300, 260, 520), (1024, 384, 384),
+                                   (512, 1152, 384)])
+def test_tf32_and_fp32_modes(tb, oracle, kind, shape):
+    """TF32 mode: <= 5e-3 against the float32 oracle and <= 2e-5 against the oracle on tf32-truncated
+    operands.  FP32 mode (three tf32 products): <= 1e-5 against the float64 product."""
+    from oracle.pyoracle import TF32
+    M, N, K = shape
+    k = KINDS[kind]
+    rng = np.random.default_rng(hash((kind, shape, 1)) % (1 << 31))
+    (ar, ac), (br, bc) = stored_shapes(k, M, N, K)
+    A = rng.standard_normal((ar, ac)).astype(np.float32)
+    B = (rng.standard_normal((br, bc)) * 0.02).astype(np.float32)
+    want32 = oracle.gemm(k // 2, k % 2, A, B, M, N, K, mode=FP32).reshape(M, N)
+    want_tf = oracle.gemm(k // 2, k % 2, A, B, M, N, K, mode=TF32).reshape(M, N)
+    truth = oracle.gemm_f64(k // 2, k % 2, A, B, M, N, K)
+    C = torch.full((M, N), float("nan"), device="cuda")
+    tb.gemm_f32(k, dev(A), dev(B), C, M, N, K, ac, bc, N, precision=tb.PREC_TF32)
+    tb.sync_check()
+    got = C.cpu().numpy()
+    assert rel_to_maxabs(got, want_tf) <= TOL_SAME_OPERANDS
+    assert rel_to_maxabs(got, want32) <= TOL_TF32_MODE
+    C = torch.full((M, N), float("nan"), device="cuda")
+    tb.gemm_f32(k, dev(A), dev(B), C, M, N, K, ac, bc, N, precision=tb.PREC_FP32)
+    tb.sync_check()
+    got = C.cpu().numpy()
+    assert rel_to_maxabs(got, truth) <= TOL_FP32_MODE
+    assert rel_to_maxabs(got, want32) <= TOL_FP32_MODE
+
+
+def test_modes_with_bias_residual_batch(tb, oracle):
+    """Strided, batched, alpha/beta and bias+residual forms in the TF32 and FP32 modes."""
+    rng = np.random.default_rng(33)
+    M, N, K, batch = 70, 52, 40, 3
+    lda, ldb, ldc = 44, 56, 60
+    sA, sB, sC = M * lda + 4, K * ldb + 8, M * ldc + 4
+    A = rng.standard_normal(batch * sA).astype(np.float32)
+    B = rng.standard_normal(batch * sB).astype(np.float32)
+    C0 = rng.standard_normal(batch * sC).astype(np.float32)
+    want = oracle.gemm(0, 0, A, B, M, N, K, lda, ldb, ldc, batch, sA, sB, sC, alpha=0.5, beta=2.0, C_in=C0)
+    for prec, tol in ((tb.PREC_TF32, TOL_TF32_MODE), (tb.PREC_FP32, TOL_FP32_MODE)):
+        C = dev(C0.copy())
+        tb.gemm_f32(0, dev(A), dev(B), C, M, N, K, lda, ldb, ldc, batch, sA, sB, sC, alpha=0.5, beta=2.0, precision=prec)
+        tb.sync_check()
+        assert rel_to_maxabs(C.cpu().numpy(), want) <= tol
+    M, N, K = 260, 96, 384
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    want = oracle.gemm_bias(A, B, bias, res)
+    for prec, tol in ((tb.PREC_TF32, TOL_TF32_MODE), (tb.PREC_FP32, TOL_FP32_MODE)):
+        C = torch.zeros(M, N, device="cuda")
+        tb.gemm_bias_f32(dev(A), dev(B), dev(bias), dev(res), C, M, N, K, precision=prec)
+        tb.sync_check()
+        assert rel_to_maxabs(C.cpu().numpy(), want) <= tol
+
+
 def test_known_answer_vectors(tb):
     ka = json.load(open(golden_path("matmul_known_answers.json")))
     for name in ("test_tensor_2x2", "test_cuda_4x3x5"):
@@ -245,4 +307,4 @@ def test_rejects_bad_arguments(tb):
     with pytest.raises(tb.TbError):
         tb.gemm_bf16(0, A, A, 0, 8, 8, 8, 8, C32=C, ldc32=8)       # empty problem
     with pytest.raises(tb.TbError):
-        tb.gemm_f32(0, C, C, C, 8, 8, 8, 8, 8, 8, precision=tb.PREC_FP32)   # not built: must not fall back silently
+        tb.gemm_f32(0, C, C, C, 8, 8, 8, 8, 8, 8, precision=7)             # unknown precision mode

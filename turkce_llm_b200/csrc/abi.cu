@@ -160,7 +160,16 @@ int tb_attention_bwd(const void* d_Q, const void* d_K, const void* d_V, const vo
                                 S(stream));
 }
 
-// Packs both float32 operands to bf16 in scratch memory, then runs the bf16 GEMM.
+// GEMM on float32 matrices in the reference's storage format.
+//   BF16: both operands are packed to bf16 in scratch memory, then the bf16 GEMM runs;
+//   TF32: the float32 operands go to the tensor cores as they are (kind::tf32 reads the top 19 bits);
+//         an operand whose rows are not 16-byte addressable is first copied with a padded leading dimension;
+//   FP32: each operand is split into tf32-exact pieces hi + lo and the product is evaluated as
+//         hi*hi + hi*lo + lo*hi in one TF32 GEMM over a 3x longer K (error ~2^-20 of the result).
+static inline bool tma_ok_f32(const float* p, long long ld, int batch, long long stride) {
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && ld % 4 == 0 && (batch == 1 || stride % 4 == 0);
+}
+
 static int gemm_f32_impl(int kind, const float* A, const float* B, float* C, int M, int N, int K,
                          long long lda, long long ldb, long long ldc, int batch, long long sA, long long sB,
                          long long sC, float alpha, float beta, const float* bias, const float* residual,
@@ -168,35 +177,71 @@ static int gemm_f32_impl(int kind, const float* A, const float* B, float* C, int
     DeviceCtx* ctx;
     TB_TRY(get_ctx(&ctx));
     TB_CHECK(kind >= 0 && kind <= 2, "unknown GEMM kind %d", kind);
-    TB_CHECK(precision == TB_PREC_BF16, "precision %d is not built yet: only TB_PREC_BF16 runs", precision);
+    TB_CHECK(precision >= TB_PREC_BF16 && precision <= TB_PREC_FP32, "unknown precision %d", precision);
     TB_CHECK(M > 0 && N > 0 && K > 0 && batch > 0, "GEMM dims must be positive");
     // stored shapes
     const int a_rows = (kind == TB_GEMM_TN) ? K : M, a_cols = (kind == TB_GEMM_TN) ? M : K;
     const int b_rows = (kind == TB_GEMM_NT) ? N : K, b_cols = (kind == TB_GEMM_NT) ? K : N;
-    const long long a_ld = round_up(a_cols, 8), b_ld = round_up(b_cols, 8);
-    const long long a_stride = (long long)a_rows * a_ld, b_stride = (long long)b_rows * b_ld;
-    const size_t a_bytes = round_up((size_t)a_stride * batch * 2, 256);
-    const size_t b_bytes = round_up((size_t)b_stride * batch * 2, 256);
 
     GemmArgs g;
     g.kind = static_cast<GemmKind>(kind);
-    g.M = M; g.N = N; g.K = K; g.lda = a_ld; g.ldb = b_ld;
-    g.batch = batch; g.strideA = a_stride; g.strideB = b_stride;
+    g.M = M; g.N = N; g.K = K;
+    g.batch = batch;
     g.C32 = C; g.ldc32 = ldc; g.strideC32 = sC;
     g.bias = bias; g.residual = residual; g.ldr = ldc; g.strideR = sC;
     g.alpha = alpha; g.beta = beta;
-    const int bn = (N <= 64) ? 64 : 128;
-    g.bn = 0;
-    int splits = residual ? 1 : choose_splits(ctx, g, bn);
+
+    if (precision == TB_PREC_BF16) {
+        const long long a_ld = round_up(a_cols, 8), b_ld = round_up(b_cols, 8);
+        const long long a_stride = (long long)a_rows * a_ld, b_stride = (long long)b_rows * b_ld;
+        const size_t a_bytes = round_up((size_t)a_stride * batch * 2, 256);
+        const size_t b_bytes = round_up((size_t)b_stride * batch * 2, 256);
+        g.lda = a_ld; g.ldb = b_ld; g.strideA = a_stride; g.strideB = b_stride;
+        const int splits = residual ? 1 : choose_splits(ctx, g, (N <= 64) ? 64 : 128);
+        g.splits = splits;
+        const size_t ws_floats = splits > 1 ? (size_t)splits * batch * M * N : 0;
+        TB_TRY(ensure_scratch(ctx, a_bytes + b_bytes + ws_floats * sizeof(float)));
+        bf16* pa = static_cast<bf16*>(ctx->scratch);
+        bf16* pb = reinterpret_cast<bf16*>(static_cast<char*>(ctx->scratch) + a_bytes);
+        float* ws = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + a_bytes + b_bytes);
+        TB_TRY(launch_pack_bf16(ctx, A, pa, a_rows, a_cols, lda, a_ld, batch, sA, a_stride, stream));
+        TB_TRY(launch_pack_bf16(ctx, B, pb, b_rows, b_cols, ldb, b_ld, batch, sB, b_stride, stream));
+        g.A = pa; g.B = pb;
+        return launch_gemm_bf16_ws(ctx, g, ws, ws_floats, stream);
+    }
+
+    g.tf32 = true;
+    const bool split3 = precision == TB_PREC_FP32;
+    // shapes of the operands the TF32 GEMM sees
+    const bool a_cat_cols = kind != TB_GEMM_TN;      // A stored [M,K]: the three pieces sit side by side
+    const bool b_cat_cols = kind == TB_GEMM_NT;      // B stored [N,K]
+    const int a_rows2 = split3 && !a_cat_cols ? 3 * a_rows : a_rows, a_cols2 = split3 && a_cat_cols ? 3 * a_cols : a_cols;
+    const int b_rows2 = split3 && !b_cat_cols ? 3 * b_rows : b_rows, b_cols2 = split3 && b_cat_cols ? 3 * b_cols : b_cols;
+    const bool a_inplace = !split3 && tma_ok_f32(A, lda, batch, sA);
+    const bool b_inplace = !split3 && tma_ok_f32(B, ldb, batch, sB);
+    const long long a_ld = a_inplace ? lda : round_up(a_cols2, 4), b_ld = b_inplace ? ldb : round_up(b_cols2, 4);
+    const long long a_stride = a_inplace ? sA : (long long)a_rows2 * a_ld;
+    const long long b_stride = b_inplace ? sB : (long long)b_rows2 * b_ld;
+    const size_t a_bytes = a_inplace ? 0 : round_up((size_t)a_stride * batch * 4, 256);
+    const size_t b_bytes = b_inplace ? 0 : round_up((size_t)b_stride * batch * 4, 256);
+    if (split3) g.K = 3 * K;
+    g.lda = a_ld; g.ldb = b_ld; g.strideA = a_stride; g.strideB = b_stride;
+    const int splits = residual ? 1 : choose_splits(ctx, g, (N <= 64) ? 64 : 128);
     g.splits = splits;
     const size_t ws_floats = splits > 1 ? (size_t)splits * batch * M * N : 0;
     TB_TRY(ensure_scratch(ctx, a_bytes + b_bytes + ws_floats * sizeof(float)));
-    bf16* pa = static_cast<bf16*>(ctx->scratch);
-    bf16* pb = reinterpret_cast<bf16*>(static_cast<char*>(ctx->scratch) + a_bytes);
+    float* pa = static_cast<float*>(ctx->scratch);
+    float* pb = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + a_bytes);
     float* ws = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + a_bytes + b_bytes);
-    TB_TRY(launch_pack_bf16(ctx, A, pa, a_rows, a_cols, lda, a_ld, batch, sA, a_stride, stream));
-    TB_TRY(launch_pack_bf16(ctx, B, pb, b_rows, b_cols, ldb, b_ld, batch, sB, b_stride, stream));
-    g.A = pa; g.B = pb;
+    if (split3) {
+        TB_TRY(launch_split3_f32(ctx, A, pa, a_rows, a_cols, lda, a_ld, a_cat_cols ? 1 : 0, 0, batch, sA, a_stride, stream));
+        TB_TRY(launch_split3_f32(ctx, B, pb, b_rows, b_cols, ldb, b_ld, b_cat_cols ? 1 : 0, 1, batch, sB, b_stride, stream));
+    } else {
+        if (!a_inplace) TB_TRY(launch_copy_f32(ctx, A, pa, a_rows, a_cols, lda, a_ld, batch, sA, a_stride, stream));
+        if (!b_inplace) TB_TRY(launch_copy_f32(ctx, B, pb, b_rows, b_cols, ldb, b_ld, batch, sB, b_stride, stream));
+    }
+    g.A = a_inplace ? static_cast<const void*>(A) : pa;
+    g.B = b_inplace ? static_cast<const void*>(B) : pb;
     return launch_gemm_bf16_ws(ctx, g, ws, ws_floats, stream);
 }
 

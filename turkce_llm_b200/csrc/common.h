@@ -83,8 +83,8 @@ enum CausalMode {
 
 struct GemmArgs {
     GemmKind kind = GEMM_NN;
-    const bf16* A = nullptr;   // NN/NT: [M,K] lda   TN: [K,M] lda
-    const bf16* B = nullptr;   // NN/TN: [K,N] ldb   NT: [N,K] ldb
+    const void* A = nullptr;   // NN/NT: [M,K] lda   TN: [K,M] lda   (bf16, or float32 when tf32 is set)
+    const void* B = nullptr;   // NN/TN: [K,N] ldb   NT: [N,K] ldb
     int M = 0, N = 0, K = 0;
     long long lda = 0, ldb = 0;
     int batch = 1;
@@ -99,6 +99,7 @@ struct GemmArgs {
     CausalMode causal = CAUSAL_NONE;
     int splits = 0;                         // 0 = choose; >1 uses scratch for fixed-order partial sums
     int bn = 0;                             // 0 = choose tile width (64, 128 or 192)
+    bool tf32 = false;                      // operands are float32 in memory and enter the tensor cores as tf32
     bool pad_cols_writable = false;         // columns N .. round_up(N, 16 bytes) of each output row are padding
 };
 
@@ -123,7 +124,17 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
                          const bf16* datt, const float* lse, float* delta, float* dQ, float* dK, float* dV, int B,
                          int H, int T, int hd, float scale, cudaStream_t stream);
 
-// ---- operand packing (pack.cu): float32 [rows, cols] (ld) -> bf16 [rows, cols] (ld_out), batched
+// ---- operand packing (pack.cu)
+// float32 [rows, cols] -> float32 copy with another leading dimension (makes a matrix TMA-addressable)
+int launch_copy_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, int cols, long long ld_src,
+                    long long ld_dst, int batch, long long stride_src, long long stride_dst, cudaStream_t stream);
+// float32 x -> three tf32-exact pieces for the 3xTF32 product: hi = x truncated to tf32, lo = x - hi.
+// along_cols: dst [rows, 3*cols] = [p0 | p1 | p2], else dst [3*rows, cols] = [p0 ; p1 ; p2];
+// pattern 0: (hi, hi, lo)   pattern 1: (hi, lo, hi)
+int launch_split3_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, int cols, long long ld_src,
+                      long long ld_dst, int along_cols, int pattern, int batch, long long stride_src,
+                      long long stride_dst, cudaStream_t stream);
+// float32 [rows, cols] (ld) -> bf16 [rows, cols] (ld_out), batched
 int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int cols, long long ld_src,
                      long long ld_dst, int batch, long long stride_src, long long stride_dst, cudaStream_t stream);
 

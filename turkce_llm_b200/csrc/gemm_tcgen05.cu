@@ -28,15 +28,16 @@
 namespace tb {
 
 constexpr int BM = 128;
-constexpr int BK = 64;              // bf16 elements = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
+constexpr int BK = 64;              // bf16 elements of one 128-byte swizzle row
+constexpr int BK_TF32 = 32;         // float32 elements of one 128-byte swizzle row (kind::tf32 operands)
+constexpr int ROW_BYTES = 128;
 constexpr int NUM_THREADS = 320;      // TMA warp, MMA warp, 8 epilogue warps
 constexpr int EPI_WARPS = 8;
 constexpr int STAGE_LD = 36;        // floats per staging row (32 + 4 pad: conflict-free float4 access)
 
 template <int BN> struct GemmCfg {
-    static constexpr int A_BYTES = BM * BK * 2;
-    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int A_BYTES = BM * ROW_BYTES;      // one K slice: 128-byte rows for either operand type
+    static constexpr int B_BYTES = BN * ROW_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN == 192) ? 3 : (BN == 128) ? 4 : 5;
     // per epilogue warp: 2 output buffers + 1 residual buffer of 32 rows x 128 B (TMA path);
@@ -70,7 +71,7 @@ struct GemmParams {
 
 struct TileCoord { int z, s, m0, n0, kb0, kb1; bool skip; };
 
-template <int BN>
+template <int BN, int BKE>
 __device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t) {
     TileCoord c;
     const int n_idx = t % p.nt; t /= p.nt;
@@ -79,7 +80,7 @@ __device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t) {
     c.z = t / p.splits;
     c.m0 = m_idx * BM;
     c.n0 = n_idx * BN;
-    const int kb_total = (p.K + BK - 1) / BK;
+    const int kb_total = (p.K + BKE - 1) / BKE;
     const int kb_per = (kb_total + p.splits - 1) / p.splits;
     c.kb0 = c.s * kb_per;
     c.kb1 = min(kb_total, c.kb0 + kb_per);
@@ -87,21 +88,27 @@ __device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t) {
     if (p.causal == CAUSAL_SKIP_UPPER) {
         c.skip = c.n0 > c.m0 + BM - 1;
     } else if (p.causal == CAUSAL_K_PREFIX) {
-        c.kb1 = min(c.kb1, (c.m0 + BM + BK - 1) / BK);
+        c.kb1 = min(c.kb1, (c.m0 + BM + BKE - 1) / BKE);
     } else if (p.causal == CAUSAL_K_SUFFIX) {
-        c.kb0 = max(c.kb0, c.m0 / BK);
+        c.kb0 = max(c.kb0, c.m0 / BKE);
     }
     if (c.kb1 < c.kb0) c.kb1 = c.kb0;   // empty range: the accumulator is treated as zero
     return c;
 }
 
-template <int BN>
+// TF32 = true: float32 operands in shared memory, kind::tf32 (the tensor core reads the top 19 bits),
+// K slices of 32 elements; everything else is shared with the bf16 path.
+template <int BN, bool TF32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  const GemmParams p) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
+    constexpr int BKE = TF32 ? BK_TF32 : BK;           // elements per K slice
+    constexpr int MNW = TF32 ? 32 : 64;                // elements per 128-byte row of an MN-major box
+    constexpr int MN_BOX_BYTES = BKE * ROW_BYTES;      // one MN-major box: BKE rows of 128 bytes
+    constexpr int MN_STEP = (TF32 ? 8 : 16) * ROW_BYTES;   // rows consumed by one UMMA (K = 8 or 16)
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -146,7 +153,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const TileCoord c = tile_of<BN>(p, t);
+                const TileCoord c = tile_of<BN, BKE>(p, t);
                 if (c.skip) continue;
                 for (int kb = c.kb0; kb < c.kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -154,17 +161,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     uint8_t* sB = sA + Cfg::A_BYTES;
                     mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
                     if (!p.a_mn) {
-                        tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, c.m0, c.z);
-                    } else {
-                        tma_load_3d(sA, &tmA, &full_bar[stage], c.m0, kb * BK, c.z);
-                        tma_load_3d(sA + 64 * BK * 2, &tmA, &full_bar[stage], c.m0 + 64, kb * BK, c.z);
-                    }
-                    if (!p.b_mn) {
-                        tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, c.n0, c.z);
+                        tma_load_3d(sA, &tmA, &full_bar[stage], kb * BKE, c.m0, c.z);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_3d(sB + j * 64 * BK * 2, &tmB, &full_bar[stage], c.n0 + j * 64, kb * BK, c.z);
+                        for (int j = 0; j < BM / MNW; ++j)
+                            tma_load_3d(sA + j * MN_BOX_BYTES, &tmA, &full_bar[stage], c.m0 + j * MNW, kb * BKE, c.z);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_3d(sB, &tmB, &full_bar[stage], kb * BKE, c.n0, c.z);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / MNW; ++j)
+                            tma_load_3d(sB + j * MN_BOX_BYTES, &tmB, &full_bar[stage], c.n0 + j * MNW, kb * BKE, c.z);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -174,12 +182,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(1u, (uint32_t)p.a_mn, (uint32_t)p.b_mn, BM, BN);
+            const uint32_t idesc = umma_idesc(TF32 ? 2u : 1u, (uint32_t)p.a_mn, (uint32_t)p.b_mn, BM, BN);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const TileCoord c = tile_of<BN>(p, t);
+                const TileCoord c = tile_of<BN, BKE>(p, t);
                 if (c.skip) continue;
                 const int buf = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -192,12 +200,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const uint32_t a_addr = smem_u32(stage_base + stage * Cfg::STAGE_BYTES);
                     const uint32_t b_addr = a_addr + Cfg::A_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t a_desc = p.a_mn ? umma_desc_sw128(a_addr + k * 2048, 64 * BK * 2, 1024)
-                                                       : umma_desc_sw128(a_addr + k * 32, 16, 1024);
-                        const uint64_t b_desc = p.b_mn ? umma_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
-                                                       : umma_desc_sw128(b_addr + k * 32, 16, 1024);
-                        umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < 4; ++k) {          // 4 UMMAs of 32 bytes of K per 128-byte slice
+                        const uint64_t a_desc = !p.a_mn ? umma_desc_sw128(a_addr + k * 32, 16, 1024)
+                                                : TF32  ? umma_desc_mn32(a_addr + k * MN_STEP, MN_BOX_BYTES)
+                                                        : umma_desc_sw128(a_addr + k * MN_STEP, MN_BOX_BYTES, 1024);
+                        const uint64_t b_desc = !p.b_mn ? umma_desc_sw128(b_addr + k * 32, 16, 1024)
+                                                : TF32  ? umma_desc_mn32(b_addr + k * MN_STEP, MN_BOX_BYTES)
+                                                        : umma_desc_sw128(b_addr + k * MN_STEP, MN_BOX_BYTES, 1024);
+                        if (TF32) umma_tf32(d_tmem, a_desc, b_desc, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                        else      umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -226,7 +237,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            const TileCoord c = tile_of<BN>(p, t);
+            const TileCoord c = tile_of<BN, BKE>(p, t);
             if (c.skip) continue;
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -338,7 +349,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            const TileCoord c = tile_of<BN>(p, t);
+            const TileCoord c = tile_of<BN, BKE>(p, t);
             if (c.skip) continue;
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -530,26 +541,31 @@ static EncodeTiledFn get_encode_fn() {
 // 3-D view (inner, rows, batch) of a bf16 matrix with a 64-element (128-byte) inner box.
 int make_operand_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld, int batch,
                      long long batch_stride, int box_rows);
-static int make_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld,
-                    int batch, long long batch_stride, int box_rows) {
-    return make_operand_map(map, ptr, inner, rows, ld, batch, batch_stride, box_rows);
-}
+static int make_operand_map_es(CUtensorMap* map, const void* ptr, int es, long long inner, long long rows,
+                               long long ld, int batch, long long batch_stride, int box_rows, bool mn_major = false);
 int make_operand_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld,
                      int batch, long long batch_stride, int box_rows) {
+    return make_operand_map_es(map, ptr, 2, inner, rows, ld, batch, batch_stride, box_rows);
+}
+// es = 2: bf16, 64-element rows; es = 4: float32 (read as tf32), 32-element rows
+static int make_operand_map_es(CUtensorMap* map, const void* ptr, int es, long long inner, long long rows,
+                               long long ld, int batch, long long batch_stride, int box_rows, bool mn_major) {
     EncodeTiledFn enc = get_encode_fn();
     TB_CHECK(enc != nullptr, "cuTensorMapEncodeTiled entry point not available");
     TB_CHECK((reinterpret_cast<uintptr_t>(ptr) & 15u) == 0, "GEMM operand must be 16-byte aligned");
-    TB_CHECK((ld * 2) % 16 == 0, "GEMM operand leading dimension must be a multiple of 8 bf16 elements (got %lld)", ld);
-    TB_CHECK(batch == 1 || (batch_stride * 2) % 16 == 0, "GEMM batch stride must be a multiple of 8 elements");
+    TB_CHECK((ld * es) % 16 == 0, "GEMM operand leading dimension must be a multiple of 16 bytes (got %lld elements of %d bytes)",
+             ld, es);
+    TB_CHECK(batch == 1 || (batch_stride * es) % 16 == 0, "GEMM batch stride must be a multiple of 16 bytes");
     cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch};
-    cuuint64_t bs = batch > 1 ? (cuuint64_t)batch_stride * 2 : (cuuint64_t)rows * (cuuint64_t)ld * 2;
+    cuuint64_t bs = batch > 1 ? (cuuint64_t)batch_stride * es : (cuuint64_t)rows * (cuuint64_t)ld * es;
     if (bs == 0) bs = 16;
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, bs};
-    cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * es, bs};
+    cuuint32_t box[3] = {(cuuint32_t)(ROW_BYTES / es), (cuuint32_t)box_rows, 1u};
     cuuint32_t estr[3] = {1u, 1u, 1u};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<bf16*>(ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = enc(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     (es == 4 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (inner=%lld rows=%lld ld=%lld batch=%d)",
              (int)r, inner, rows, ld, batch);
     return 0;
@@ -606,7 +622,7 @@ static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
     if (a.N <= 64) return 64;
     const long long mt = (a.M + BM - 1) / BM;
     const long long t128 = mt * ((a.N + 127) / 128) * a.batch;
-    if (t128 * 2 <= ctx->sm_count && a.K >= 16 * BK) return 128;      // split-K will fill the machine
+    if (t128 * 2 <= ctx->sm_count && a.K >= 16 * (a.tf32 ? BK_TF32 : BK)) return 128;      // split-K will fill the machine
     // time ~ waves x tile width x a factor for how often a tile re-reads its operands from L2
     // (flops per operand byte: 43 for 128x64, 64 for 128x128, 77 for 128x192)
     const int widths[3] = {64, 128, 192};
@@ -626,7 +642,8 @@ static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
 int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
     if (a.causal != CAUSAL_NONE) return 1;
     const long long tiles = (long long)((a.M + BM - 1) / BM) * ((a.N + bn - 1) / bn) * a.batch;
-    const int kb_total = (a.K + BK - 1) / BK;
+    const int bke = a.tf32 ? BK_TF32 : BK;
+    const int kb_total = (a.K + bke - 1) / bke;
     if (tiles * 2 > ctx->sm_count || kb_total < 16) return 1;
     int s = (int)(ctx->sm_count / tiles);
     if (s > kb_total / 4) s = kb_total / 4;     // at least 4 K slices per split
@@ -635,21 +652,21 @@ int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
     return (kb_total + kb_per - 1) / kb_per;     // no empty split
 }
 
-template <int BN>
+template <int BN, bool TF32>
 static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, const CUtensorMap& tmA,
                        const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmR,
                        cudaStream_t stream) {
     using Cfg = GemmCfg<BN>;
     static bool attr_set[64] = {false};
     if (!attr_set[ctx->device & 63]) {
-        TB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
         attr_set[ctx->device & 63] = true;
     }
     const long long total = (long long)p.batch * p.splits * p.mt * p.nt;
     int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     if (grid < 1) grid = 1;
-    gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, p);
+    gemm_bf16_kernel<BN, TF32><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, p);
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -664,10 +681,12 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     const int a_mn = (a.kind == GEMM_TN) ? 1 : 0;
     const int b_mn = (a.kind == GEMM_NT) ? 0 : 1;
     CUtensorMap tmA, tmB;
-    if (!a_mn) TB_TRY(make_map(&tmA, a.A, a.K, a.M, a.lda, a.batch, a.strideA, BM));
-    else       TB_TRY(make_map(&tmA, a.A, a.M, a.K, a.lda, a.batch, a.strideA, BK));
-    if (!b_mn) TB_TRY(make_map(&tmB, a.B, a.K, a.N, a.ldb, a.batch, a.strideB, bn));
-    else       TB_TRY(make_map(&tmB, a.B, a.N, a.K, a.ldb, a.batch, a.strideB, BK));
+    const int es = a.tf32 ? 4 : 2;
+    const int bke = a.tf32 ? BK_TF32 : BK;
+    if (!a_mn) TB_TRY(make_operand_map_es(&tmA, a.A, es, a.K, a.M, a.lda, a.batch, a.strideA, BM));
+    else       TB_TRY(make_operand_map_es(&tmA, a.A, es, a.M, a.K, a.lda, a.batch, a.strideA, bke, true));
+    if (!b_mn) TB_TRY(make_operand_map_es(&tmB, a.B, es, a.K, a.N, a.ldb, a.batch, a.strideB, bn));
+    else       TB_TRY(make_operand_map_es(&tmB, a.B, es, a.N, a.K, a.ldb, a.batch, a.strideB, bke, true));
 
     GemmParams p;
     p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch; p.splits = splits;
@@ -741,14 +760,20 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
         if (ctx->prof_on) {
             char tag[128];
             static const char* kn[3] = {"NN", "NT", "TN"};
-            snprintf(tag, sizeof(tag), "gemm_bf16:%s:%dx%dx%d:b%d:s%d:c%d:bn%d", kn[(int)a.kind], a.M, a.N, a.K,
-                     a.batch, splits, (int)a.causal, bn);
+            snprintf(tag, sizeof(tag), "%s:%s:%dx%dx%d:b%d:s%d:c%d:bn%d", a.tf32 ? "gemm_tf32" : "gemm_bf16",
+                     kn[(int)a.kind], a.M, a.N, a.K, a.batch, splits, (int)a.causal, bn);
             prof_mark(ctx, prof_intern(tag), 2.0 * macs, in_bytes + out_bytes, stream);
         }
     }
-    if (bn == 64)       TB_TRY(launch_impl<64>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
-    else if (bn == 192) TB_TRY(launch_impl<192>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
-    else                TB_TRY(launch_impl<128>(ctx, a, p, tmA, tmB, tmC, tmR, stream));
+    if (a.tf32) {
+        if (bn == 64)       TB_TRY((launch_impl<64, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        else if (bn == 192) TB_TRY((launch_impl<192, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        else                TB_TRY((launch_impl<128, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+    } else {
+        if (bn == 64)       TB_TRY((launch_impl<64, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        else if (bn == 192) TB_TRY((launch_impl<192, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        else                TB_TRY((launch_impl<128, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+    }
 
     if (splits > 1) {
         TB_CHECK(a.residual == nullptr, "split-K GEMM does not take a residual operand");

@@ -61,4 +61,76 @@ int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int 
     return 0;
 }
 
+__global__ void copy_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols,
+                                long long ld_src, long long ld_dst, long long stride_src, long long stride_dst) {
+    const float* s = src + (long long)blockIdx.z * stride_src;
+    float* d = dst + (long long)blockIdx.z * stride_dst;
+    const long long total = (long long)rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols;
+        const int c = (int)(i % cols);
+        d[r * ld_dst + c] = s[r * ld_src + c];
+    }
+}
+
+int launch_copy_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, int cols, long long ld_src,
+                    long long ld_dst, int batch, long long stride_src, long long stride_dst, cudaStream_t stream) {
+    TB_CHECK(rows > 0 && cols > 0 && batch > 0, "copy: empty matrix");
+    long long blocks = ((long long)rows * cols + 255) / 256;
+    if (blocks > 8LL * ctx->sm_count) blocks = 8LL * ctx->sm_count;
+    dim3 grid((unsigned)blocks, 1, (unsigned)batch);
+    prof_mark(ctx, "copy_f32", 0.0, (double)rows * cols * batch * 8.0, stream);
+    copy_f32_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst);
+    TB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    prof_close(ctx, stream);
+    return 0;
+}
+
+// hi keeps the 19 bits a tf32 operand has (sign, 8 exponent, 10 mantissa); lo = x - hi is exact in
+// float32 and itself enters the tensor core truncated to tf32, which loses about 2^-21 of x.
+__global__ void split3_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols,
+                                  long long ld_src, long long ld_dst, int along_cols, int pattern,
+                                  long long stride_src, long long stride_dst) {
+    const float* s = src + (long long)blockIdx.z * stride_src;
+    float* d = dst + (long long)blockIdx.z * stride_dst;
+    const long long total = (long long)rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols;
+        const int c = (int)(i % cols);
+        const float x = s[r * ld_src + c];
+        const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+        const float lo = x - hi;
+        const float p1 = pattern == 0 ? hi : lo;
+        const float p2 = pattern == 0 ? lo : hi;
+        if (along_cols) {
+            d[r * ld_dst + c] = hi;
+            d[r * ld_dst + cols + c] = p1;
+            d[r * ld_dst + 2LL * cols + c] = p2;
+        } else {
+            d[r * ld_dst + c] = hi;
+            d[(r + rows) * ld_dst + c] = p1;
+            d[(r + 2LL * rows) * ld_dst + c] = p2;
+        }
+    }
+}
+
+int launch_split3_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, int cols, long long ld_src,
+                      long long ld_dst, int along_cols, int pattern, int batch, long long stride_src,
+                      long long stride_dst, cudaStream_t stream) {
+    TB_CHECK(rows > 0 && cols > 0 && batch > 0, "split: empty matrix");
+    long long blocks = ((long long)rows * cols + 255) / 256;
+    if (blocks > 8LL * ctx->sm_count) blocks = 8LL * ctx->sm_count;
+    dim3 grid((unsigned)blocks, 1, (unsigned)batch);
+    prof_mark(ctx, "split3_f32", 0.0, (double)rows * cols * batch * 16.0, stream);
+    split3_f32_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst, along_cols, pattern, stride_src,
+                                                stride_dst);
+    TB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    prof_close(ctx, stream);
+    return 0;
+}
+
 }  // namespace tb

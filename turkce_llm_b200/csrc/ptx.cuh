@@ -170,14 +170,24 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // K-major tile  (rows x 64 bf16, rows 128 B apart): SBO = 1024 (8-row group), LBO unused.
 // MN-major tile (64 MN-elements x k rows of 128 B): SBO = 1024 (8-k group),
 //   LBO = byte distance between consecutive 64-element MN blocks.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= 1ull << 46;
-    d |= 2ull << 61;
+    d |= static_cast<uint64_t>(layout_type) << 61;
     return d;
+}
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return umma_desc(smem_addr, lbo_bytes, sbo_bytes, 2u);
+}
+// MN-major tile of 32-bit elements: the only layout the tensor core accepts is the 128-byte swizzle
+// with 32-byte atoms (layout type 1; TMA mode SWIZZLE_128B_ATOM_32B): 32 MN-elements (128 B) x groups
+// of 4 K rows, SBO = 512 bytes between K groups, LBO = bytes between 32-wide MN blocks.
+__device__ __forceinline__ uint64_t umma_desc_mn32(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return umma_desc(smem_addr, lbo_bytes, 512u, 1u);
 }
 
 // Instruction descriptor for kind::f16 / kind::tf32 with FP32 accumulation.
