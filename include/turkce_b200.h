@@ -221,6 +221,30 @@ int tb_trainer_forward_resident(TbTrainer* g, int want_grad);
 /* Gradient norm computed by the last tb_trainer_clip_adam_async (waits for the stream). */
 int tb_trainer_last_norm(TbTrainer* g, double* norm_out);
 
+/* ---- decoding with a KV cache --------------------------------------------------- */
+
+/* The reference generates by re-running lm_forward over the whole window for every new token
+ * (training/generate.c:186-212, training/chat.c:139-165) and has no KV cache; this engine computes
+ * the same last-row logits incrementally.  Greedy choice (argmax; the reference samples with a
+ * temperature, training/generate.c:57-73, which stays the caller's business through
+ * tb_decoder_read_logits).  max_seqs sequences are decoded in lockstep, each with room for max_len
+ * positions; the parameters are the trainer's flat float32 layout. */
+typedef struct TbDecoder TbDecoder;
+int tb_decoder_create(TbDecoder** out, int V, int D, int H, int L, int F, int max_seqs, int max_len, float eps,
+                      void* stream);
+int tb_decoder_destroy(TbDecoder* g);
+int64_t tb_decoder_total_scalars(const TbDecoder* g);
+int tb_decoder_upload(TbDecoder* g, const float* h_flat);
+/* h_ids: [max_seqs, prompt_len] prompt tokens; fills the cache and chooses the first new token. */
+int tb_decoder_prefill(TbDecoder* g, const uint32_t* h_ids, int prompt_len);
+/* n more tokens per sequence; asynchronous (one CUDA-graph launch per token). */
+int tb_decoder_generate(TbDecoder* g, int n);
+/* h_out: [max_seqs, count], the first `count` generated tokens of every sequence (waits). */
+int tb_decoder_read_tokens(TbDecoder* g, uint32_t* h_out, int count);
+/* h_logits: [max_seqs, V], the logits the most recent token was chosen from (waits). */
+int tb_decoder_read_logits(TbDecoder* g, float* h_logits);
+void* tb_decoder_stream(TbDecoder* g);
+
 #ifdef __cplusplus
 }
 #endif

@@ -259,7 +259,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
                 *reinterpret_cast<uint4*>(orow + d) = pk;
             }
-            p.lse[(long long)bh * p.T + qi] = (m + log2f(l)) * 0.6931471805599453f;
+            if (p.lse) p.lse[(long long)bh * p.T + qi] = (m + log2f(l)) * 0.6931471805599453f;
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 13); }
     }
@@ -707,14 +707,15 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
 constexpr int ATT_FWD_SMEM = 1024 + 7 * TILE_BYTES;
 
 int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, bf16* att, float* lse, int B,
-                         int H, int T, int hd, float scale, cudaStream_t stream) {
+                         int H, int T, int hd, float scale, cudaStream_t stream, long long kv_rows_per_head) {
     TB_CHECK(hd > 0 && hd <= ATT_HD && hd % 8 == 0, "fused attention needs head_dim <= 64 and a multiple of 8 (got %d)", hd);
     TB_CHECK(B > 0 && H > 0 && T > 0, "attention dims must be positive");
     const int BH = B * H;
     CUtensorMap tmQ, tmK, tmV;
     TB_TRY(make_operand_map(&tmQ, Q, hd, T, hd, BH, (long long)T * hd, ATT_BM));
-    TB_TRY(make_operand_map(&tmK, K, hd, T, hd, BH, (long long)T * hd, ATT_BN));
-    TB_TRY(make_operand_map(&tmV, V, hd, T, hd, BH, (long long)T * hd, ATT_BN));
+    const long long kv_rows = kv_rows_per_head > 0 ? kv_rows_per_head : T;      // a KV cache has room for more rows
+    TB_TRY(make_operand_map(&tmK, K, hd, T, hd, BH, kv_rows * hd, ATT_BN));
+    TB_TRY(make_operand_map(&tmV, V, hd, T, hd, BH, kv_rows * hd, ATT_BN));
     AttFwdParams p;
     p.T = T; p.H = H; p.hd = hd; p.D = H * hd;
     p.nq = (T + ATT_BM - 1) / ATT_BM;

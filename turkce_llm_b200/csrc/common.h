@@ -117,8 +117,9 @@ int make_operand_map4(CUtensorMap* map, const bf16* ptr, long long inner, long l
 
 // ---- fused causal attention (attention.cu); Q, K, V bf16 [B*H, T, hd] (hd <= 64, multiple of 8)
 // forward: att bf16 [B*T, H*hd] (heads merged), lse float [B*H, T] (natural-log sum of exponentials)
+// (lse may be NULL; kv_rows_per_head > T when K and V live in a KV cache with that many rows per head)
 int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, bf16* att, float* lse, int B,
-                         int H, int T, int hd, float scale, cudaStream_t stream);
+                         int H, int T, int hd, float scale, cudaStream_t stream, long long kv_rows_per_head = 0);
 // backward: datt bf16 [B*T, H*hd] -> dQ, dK, dV float [B*H, T, hd]; delta is float scratch [B*H, T]
 int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, const bf16* att,
                          const bf16* datt, const float* lse, float* delta, float* dQ, float* dK, float* dV, int B,

@@ -283,7 +283,7 @@ int launch_rmsnorm_bwd(DeviceCtx* ctx, const float* x, const float* w, const flo
 // qkv [B*T, 3D] -> Q, K rotated on interleaved pairs (2k, 2k+1), V copied; all [B,H,T,hd] bf16
 __global__ void rope_split_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
                                   const float* __restrict__ sin_t, bf16* __restrict__ Q, bf16* __restrict__ K,
-                                  bf16* __restrict__ V, int B, int T, int H, int hd) {
+                                  bf16* __restrict__ V, int B, int T, int H, int hd, int kv_cap) {
     const int half = hd >> 1;
     const int D = H * hd;
     const long long total = (long long)B * T * H * half;
@@ -299,21 +299,22 @@ __global__ void rope_split_kernel(const float* __restrict__ qkv, const float* __
         const int c0 = h * hd + 2 * k;
         const float c = cos_t[t * half + k], s = sin_t[t * half + k];
         const long long o = ((b * H + h) * T + t) * hd + 2 * k;
+        const long long okv = ((b * H + h) * (long long)kv_cap + t) * hd + 2 * k;     // K/V rows have room for kv_cap positions
         const float2 q = *reinterpret_cast<const float2*>(row + c0);
         const float2 kk = *reinterpret_cast<const float2*>(row + D + c0);
         const float2 v = *reinterpret_cast<const float2*>(row + 2 * D + c0);
         *reinterpret_cast<__nv_bfloat162*>(Q + o) = __floats2bfloat162_rn(q.x * c - q.y * s, q.x * s + q.y * c);
-        *reinterpret_cast<__nv_bfloat162*>(K + o) = __floats2bfloat162_rn(kk.x * c - kk.y * s, kk.x * s + kk.y * c);
-        *reinterpret_cast<__nv_bfloat162*>(V + o) = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162*>(K + okv) = __floats2bfloat162_rn(kk.x * c - kk.y * s, kk.x * s + kk.y * c);
+        *reinterpret_cast<__nv_bfloat162*>(V + okv) = __floats2bfloat162_rn(v.x, v.y);
     }
 }
 
 int launch_rope_split(DeviceCtx* ctx, const float* qkv, const float* cos_t, const float* sin_t, bf16* Q, bf16* K,
-                      bf16* V, int B, int T, int H, int hd, cudaStream_t st) {
+                      bf16* V, int B, int T, int H, int hd, int kv_cap, cudaStream_t st) {
     TB_CHECK(hd % 2 == 0, "head dim must be even");
     const long long total = (long long)B * T * H * (hd / 2);
     prof_mark(ctx, "rope_split", 0.0, 0.0, st);
-    rope_split_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(qkv, cos_t, sin_t, Q, K, V, B, T, H, hd);
+    rope_split_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(qkv, cos_t, sin_t, Q, K, V, B, T, H, hd, kv_cap);
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -353,6 +354,181 @@ int launch_rope_merge_bwd(DeviceCtx* ctx, const float* dQ, const float* dK, cons
     const long long total = (long long)B * T * H * (hd / 2);
     prof_mark(ctx, "rope_merge_bwd", 0.0, 0.0, st);
     rope_merge_bwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(dQ, dK, dV, cos_t, sin_t, dqkv, B, T, H, hd);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+__device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max);
+
+// ------------------------------------------------------- decode (one new token per sequence)
+// qkv [S, 3D] of the new tokens at position *pos: rotated q -> Q [S, H, hd] (float32), rotated k and
+// v -> the KV cache [S, H, cap, hd] (bf16) at row *pos.
+__global__ void rope_decode_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, float* __restrict__ Q, bf16* __restrict__ Kc,
+                                   bf16* __restrict__ Vc, const int* __restrict__ pos, int S, int H, int hd, int cap) {
+    const int half = hd >> 1, D = H * hd;
+    const int t = *pos;
+    const int total = S * H * half;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int k = i % half;
+        const int h = (i / half) % H;
+        const int sq = i / (half * H);
+        const float* row = qkv + (long long)sq * 3 * D;
+        const int c0 = h * hd + 2 * k;
+        const float c = cos_t[t * half + k], sn = sin_t[t * half + k];
+        const float2 q = *reinterpret_cast<const float2*>(row + c0);
+        const float2 kk = *reinterpret_cast<const float2*>(row + D + c0);
+        const float2 v = *reinterpret_cast<const float2*>(row + 2 * D + c0);
+        *reinterpret_cast<float2*>(Q + ((long long)sq * H + h) * hd + 2 * k) = make_float2(q.x * c - q.y * sn, q.x * sn + q.y * c);
+        const long long o = (((long long)sq * H + h) * cap + t) * hd + 2 * k;
+        *reinterpret_cast<__nv_bfloat162*>(Kc + o) = __floats2bfloat162_rn(kk.x * c - kk.y * sn, kk.x * sn + kk.y * c);
+        *reinterpret_cast<__nv_bfloat162*>(Vc + o) = __floats2bfloat162_rn(v.x, v.y);
+    }
+}
+
+int launch_rope_decode(DeviceCtx* ctx, const float* qkv, const float* cos_t, const float* sin_t, float* Q, bf16* Kc,
+                       bf16* Vc, const int* pos, int S, int H, int hd, int cap, cudaStream_t st) {
+    const int total = S * H * (hd / 2);
+    prof_mark(ctx, "rope_decode", 0.0, 0.0, st);
+    rope_decode_kernel<<<grid_for(total, 128, ctx), 128, 0, st>>>(qkv, cos_t, sin_t, Q, Kc, Vc, pos, S, H, hd, cap);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// One block per (sequence, head): scores of the new query against cache rows 0..*pos, softmax, P V.
+// The same function as a full causal forward restricted to its last row (model/attention.c:55-60).
+__global__ void attn_decode_kernel(const float* __restrict__ Q, const bf16* __restrict__ Kc,
+                                   const bf16* __restrict__ Vc, bf16* __restrict__ att, const int* __restrict__ pos,
+                                   int H, int hd, int cap, float scale) {
+    extern __shared__ float sh[];            // q [hd] | p [cap] | red [32] | part [2][hd]
+    float* q = sh;
+    float* p = sh + hd;
+    float* red = p + cap;
+    float* part = red + 32;
+    const int h = blockIdx.x, sq = blockIdx.y;
+    const int L = *pos + 1;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const bf16* Kb = Kc + ((long long)sq * H + h) * cap * hd;
+    const bf16* Vb = Vc + ((long long)sq * H + h) * cap * hd;
+    for (int d = tid; d < hd; d += nt) q[d] = Q[((long long)sq * H + h) * hd + d];
+    __syncthreads();
+    float mx = -3.0e38f;
+    for (int l = tid; l < L; l += nt) {
+        const bf16* kr = Kb + (long long)l * hd;
+        float s = 0.0f;
+        for (int d = 0; d < hd; d += 8) {
+            const uint4 kv = *reinterpret_cast<const uint4*>(kr + d);
+            const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(k2[e]);
+                s += q[d + 2 * e] * f.x;
+                s += q[d + 2 * e + 1] * f.y;
+            }
+        }
+        s *= scale;
+        p[l] = s;
+        mx = fmaxf(mx, s);
+    }
+    mx = block_reduce(mx, red, true);
+    float sum = 0.0f;
+    for (int l = tid; l < L; l += nt) {
+        const float e = expf(p[l] - mx);
+        p[l] = e;
+        sum += e;
+    }
+    sum = block_reduce(sum, red, false);
+    // output: thread (g, d) adds keys g, g+G, ... for dimension d; the G partial sums are added in order
+    const int G = min(nt / hd, 2);           // one or two groups of hd threads share the keys
+    const int g = tid / hd, d = tid % hd;
+    float acc = 0.0f;
+    if (g < G)
+        for (int l = g; l < L; l += G) acc += p[l] * __bfloat162float(Vb[(long long)l * hd + d]);
+    if (g < G) part[g * hd + d] = acc;
+    __syncthreads();
+    if (g == 0) {
+        float o = part[d];
+        if (G > 1) o += part[hd + d];
+        att[(long long)sq * (H * hd) + h * hd + d] = __float2bfloat16_rn(o / sum);
+    }
+}
+
+int launch_attn_decode(DeviceCtx* ctx, const float* Q, const bf16* Kc, const bf16* Vc, bf16* att, const int* pos, int S,
+                       int H, int hd, int cap, float scale, cudaStream_t st) {
+    TB_CHECK(hd <= 128 && hd % 8 == 0, "decode attention needs head_dim <= 128 and a multiple of 8");
+    int threads = (2 * hd + 31) / 32 * 32;   // two key groups of hd threads
+    if (threads < 64) threads = 64;
+    const size_t smem = (size_t)(hd + cap + 32 + 2 * hd) * sizeof(float);
+    TB_CHECK(smem <= 48 * 1024, "KV cache capacity %d too large for the decode attention kernel", cap);
+    dim3 grid(H, S);
+    prof_mark(ctx, "attn_decode", 0.0, 0.0, st);
+    attn_decode_kernel<<<grid, threads, smem, st>>>(Q, Kc, Vc, att, pos, H, hd, cap, scale);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// out[i, :] = in[idx(i), :] for the last position of every sequence: idx(i) = i*T + T-1
+__global__ void gather_last_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int S, int T, int D) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < S * D; i += gridDim.x * blockDim.x) {
+        const int sq = i / D, j = i % D;
+        out[i] = in[((long long)sq * T + T - 1) * D + j];
+    }
+}
+
+int launch_gather_last_rows(DeviceCtx* ctx, const float* in, float* out, int S, int T, int D, cudaStream_t st) {
+    prof_mark(ctx, "gather_last_rows", 0.0, 0.0, st);
+    gather_last_rows_kernel<<<grid_for((long long)S * D, 256, ctx), 256, 0, st>>>(in, out, S, T, D);
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+// Greedy choice: tok[s] = argmax_j logits[s, j] (lowest index on ties), also stored as generated
+// token number state[1] of sequence s.  state = {position of the next token, tokens generated}.
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, uint32_t* __restrict__ tok,
+                                   uint32_t* __restrict__ out, const int* __restrict__ state, int V, long long ld,
+                                   int out_ld) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const int sq = blockIdx.x;
+    const float* z = logits + (long long)sq * ld;
+    float best = -3.0e38f;
+    int idx = 0x7fffffff;
+    for (int j = threadIdx.x; j < V; j += blockDim.x) {
+        const float v = z[j];
+        if (v > best || (v == best && j < idx)) { best = v; idx = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+        tok[sq] = (uint32_t)idx;
+        if (out) out[(long long)sq * out_ld + state[1]] = (uint32_t)idx;
+    }
+}
+
+// after a step: one more token generated; the position advances once the token has been fed
+__global__ void advance_state_kernel(int* __restrict__ state, int advance_pos) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        state[1] += 1;
+        if (advance_pos) state[0] += 1;
+    }
+}
+
+int launch_argmax_rows(DeviceCtx* ctx, const float* logits, uint32_t* tok, uint32_t* out, int* state, int S, int V,
+                       long long ld, int out_ld, int advance_pos, cudaStream_t st) {
+    prof_mark(ctx, "argmax_rows", 0.0, 0.0, st);
+    argmax_rows_kernel<<<S, 1024, 0, st>>>(logits, tok, out, state, V, ld, out_ld);
+    TB_LAUNCHED(ctx);
+    prof_mark(ctx, "advance_state", 0.0, 0.0, st);
+    advance_state_kernel<<<1, 32, 0, st>>>(state, advance_pos);
     TB_LAUNCHED(ctx);
     return 0;
 }

@@ -22,8 +22,18 @@ size_t rmsnorm_bwd_scratch_floats(int cols);
 int launch_rmsnorm_bwd_dw(DeviceCtx*, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
                           bf16* dx16, float* dw, float* db, float* scratch, int rows, int cols, int accumulate,
                           cudaStream_t);
+// Q [B,H,T,hd]; K, V [B,H,kv_cap,hd] (kv_cap = T for the trainer, the cache capacity for prefill)
 int launch_rope_split(DeviceCtx*, const float* qkv, const float* cos_t, const float* sin_t, bf16* Q, bf16* K, bf16* V,
-                      int B, int T, int H, int hd, cudaStream_t);
+                      int B, int T, int H, int hd, int kv_cap, cudaStream_t);
+// ---- decode with a KV cache [S, H, cap, hd] (bf16); *pos is the position of the new token
+int launch_rope_decode(DeviceCtx*, const float* qkv, const float* cos_t, const float* sin_t, float* Q, bf16* Kc,
+                       bf16* Vc, const int* pos, int S, int H, int hd, int cap, cudaStream_t);
+int launch_attn_decode(DeviceCtx*, const float* Q, const bf16* Kc, const bf16* Vc, bf16* att, const int* pos, int S,
+                       int H, int hd, int cap, float scale, cudaStream_t);
+int launch_gather_last_rows(DeviceCtx*, const float* in, float* out, int S, int T, int D, cudaStream_t);
+// state = {position of the next token, tokens generated so far} in device memory
+int launch_argmax_rows(DeviceCtx*, const float* logits, uint32_t* tok, uint32_t* out, int* state, int S, int V,
+                       long long ld, int out_ld, int advance_pos, cudaStream_t);
 int launch_rope_merge_bwd(DeviceCtx*, const float* dQ, const float* dK, const float* dV, const float* cos_t,
                           const float* sin_t, bf16* dqkv, int B, int T, int H, int hd, cudaStream_t);
 // S [BH*T rows, leading dimension ld >= T] fp32 (entries j<=i valid) -> P bf16, same shape

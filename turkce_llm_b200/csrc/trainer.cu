@@ -151,7 +151,7 @@ int forward(TbTrainer* g, bool want_grad) {
         TB_TRY(launch_rmsnorm_fwd(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.n1, a.r1, N, D, g->eps, st));
         TB_TRY(linear_fwd(g, a.n1, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, N,
                           3 * D, D));
-        TB_TRY(launch_rope_split(c, g->qkv, g->cos_t, g->sin_t, a.Q, a.K, a.V, B, T, H, hd, st));
+        TB_TRY(launch_rope_split(c, g->qkv, g->cos_t, g->sin_t, a.Q, a.K, a.V, B, T, H, hd, T, st));
         if (g->fused_attention) {
             TB_TRY(launch_attention_fwd(c, a.Q, a.K, a.V, a.att, a.lse, B, H, T, hd, g->scale, st));
         } else {

@@ -40,6 +40,15 @@ SIGNATURES = {
     "tb_attention_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
+    "tb_decoder_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "tb_decoder_destroy": (_i, [_vp]),
+    "tb_decoder_total_scalars": (_i64, [_vp]),
+    "tb_decoder_upload": (_i, [_vp, _vp]),
+    "tb_decoder_prefill": (_i, [_vp, _vp, _i]),
+    "tb_decoder_generate": (_i, [_vp, _i]),
+    "tb_decoder_read_tokens": (_i, [_vp, _vp, _i]),
+    "tb_decoder_read_logits": (_i, [_vp, _vp]),
+    "tb_decoder_stream": (_vp, [_vp]),
     "tb_trainer_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "tb_trainer_destroy": (_i, [_vp]),
     "tb_trainer_total_scalars": (_i64, [_vp]),

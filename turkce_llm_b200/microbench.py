@@ -2,6 +2,7 @@
 
     python -m turkce_llm_b200.microbench gemm M N K kind [iters] [out=f32|bf16] [tile_n] [splits]
     python -m turkce_llm_b200.microbench attention B H T hd [iters]
+    python -m turkce_llm_b200.microbench decode S prompt_len new_tokens      (33.49M-parameter model)
 
 kind: 0 = NN, 1 = NT, 2 = TN.  Prints the mean device time per launch (CUDA events) and the
 algorithmic throughput.
@@ -35,9 +36,19 @@ def gemm(M, N, K, kind, iters=20, out="f32", tile_n=0, splits=1):
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / iters
-    print("gemm kind=%d %dx%dx%d out=%s tile_n=%d splits=%d: %.2f us  %.1f TFLOP/s"
-          % (kind, M, N, K, out, tile_n, splits, us, 2.0 * M * N * K / us / 1e6), flush=True)
-    return us
+    # the kernel's own time: events directly around each launch (not stretched by host launch cost)
+    lib.profile_begin()
+    for _ in range(iters):
+        run()
+    prof = lib.profile_end(torch.cuda.current_stream().cuda_stream)
+    kus = sum(v["ms"] for k, v in prof.items() if k.startswith("gemm_")) * 1e3 / iters
+    a_bytes, b_bytes = 2.0 * M * K, 2.0 * K * N
+    c_bytes = M * N * (4.0 if out == "f32" else 2.0)
+    print("gemm kind=%d %dx%dx%d out=%s tile_n=%d splits=%d: %.2f us per call, kernel %.2f us = %.1f TFLOP/s, "
+          "%.0f GB/s of operand+result bytes"
+          % (kind, M, N, K, out, tile_n, splits, us, kus, 2.0 * M * N * K / kus / 1e6,
+             (a_bytes + b_bytes + c_bytes) / kus / 1e3), flush=True)
+    return kus
 
 
 def attention(B, H, T, hd, iters=10):
@@ -71,6 +82,41 @@ def attention(B, H, T, hd, iters=10):
     return f_us, b_us
 
 
+def decode(S, prompt_len, n_new):
+    """Batched greedy decoding of the 33.49M-parameter decoder with a KV cache (random bf16 weights)."""
+    import numpy as np
+    from .decode import Decoder
+    V, D, H, L, F = 31769, 384, 6, 12, 1024
+    dec = Decoder(V, D, H, L, F, S, prompt_len + n_new + 1)
+    rng = np.random.default_rng(3)
+    dec.upload((rng.standard_normal(dec.total) * 0.02).astype(np.float32))
+    w = 1.0 / np.arange(1, V + 1, dtype=np.float64) ** 1.1
+    cdf = np.cumsum(w / w.sum())
+    prompts = np.minimum(np.searchsorted(cdf, rng.random((S, prompt_len))), V - 1).astype(np.uint32)
+    st = torch.cuda.ExternalStream(dec.stream_ptr())
+    dec.prefill(prompts)
+    dec.generate(3)                      # eager step, capture, first replay
+    dec.tokens(4)
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    with torch.cuda.stream(st):
+        e[0].record()
+        dec.prefill(prompts)
+        e[1].record()
+        dec.generate(n_new - 1)
+        e[2].record()
+    toks = dec.tokens(n_new)
+    pre_ms = e[0].elapsed_time(e[1])
+    gen_ms = e[1].elapsed_time(e[2])
+    step_us = gen_ms * 1e3 / (n_new - 1)
+    weight_mb = 2.0 * (12 * 1769472 + 12199296) / 1e6
+    print("decode S=%d prompt=%d new=%d: prefill %.2f ms (%.0f tokens/s), %.1f us per step = %.0f tokens/s, "
+          "weights streamed at %.0f GB/s; first tokens %s"
+          % (S, prompt_len, n_new, pre_ms, S * prompt_len / pre_ms * 1e3, step_us, S / step_us * 1e6,
+             weight_mb / step_us * 1e3, toks[0, :4].tolist()), flush=True)
+    dec.destroy()
+    return pre_ms, step_us
+
+
 def main(argv):
     if len(argv) >= 5 and argv[0] == "gemm":
         M, N, K, kind = (int(x) for x in argv[1:5])
@@ -79,6 +125,8 @@ def main(argv):
         tile_n = int(argv[7]) if len(argv) > 7 else 0
         splits = int(argv[8]) if len(argv) > 8 else 1
         gemm(M, N, K, kind, iters, out, tile_n, splits)
+    elif len(argv) >= 4 and argv[0] == "decode":
+        decode(int(argv[1]), int(argv[2]), int(argv[3]))
     elif len(argv) >= 5 and argv[0] == "attention":
         B, H, T, hd = (int(x) for x in argv[1:5])
         attention(B, H, T, hd, int(argv[5]) if len(argv) > 5 else 10)
