@@ -117,6 +117,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                 // everything above is independent of earlier kernels' results
     const uint32_t tS = tmem_base, tO = tmem_base + 128;
 
     if (warp == 0) {
@@ -132,6 +133,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 mbar_expect_tx(&v_full[s], TILE_BYTES);
                 tma_load_3d(sV + s * TILE_BYTES, &tmV, &v_full[s], 0, j * ATT_BN, bh);
             }
+            pdl_launch_dependents_now();     // all loads issued: the next kernel may start its prologue
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 11); }
         }
     } else if (warp == 1) {
@@ -281,6 +283,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
 __global__ void attention_delta_kernel(const bf16* __restrict__ att, const bf16* __restrict__ datt,
                                        float* __restrict__ delta, int B, int T, int H, int hd) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long total = (long long)B * T * H;
     const int D = H * hd;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -366,6 +370,7 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                 // everything above is independent of earlier kernels' results
     const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 320;
 
     if (warp == 0) {
@@ -382,6 +387,7 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 tma_load_3d(sQ + s * TILE_BYTES, &tmQ, &qdo_full[s], 0, q0, bh);
                 tma_load_4d(sdO + s * TILE_BYTES, &tmdO, &qdo_full[s], 0, q0, h, b);
             }
+            pdl_launch_dependents_now();     // all loads issued: the next kernel may start its prologue
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 21); }
         }
     } else if (warp == 1) {
@@ -540,6 +546,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                 // everything above is independent of earlier kernels' results
     const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256;
 
     if (warp == 0) {
@@ -555,6 +562,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                 tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, it * ATT_BN, bh);
                 tma_load_3d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, it * ATT_BN, bh);
             }
+            pdl_launch_dependents_now();     // all loads issued: the next kernel may start its prologue
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 31); }
         }
     } else if (warp == 1) {
@@ -684,7 +692,7 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
         long long blocks = (total + 255) / 256;
         if (blocks > 16LL * ctx->sm_count) blocks = 16LL * ctx->sm_count;
         prof_mark(ctx, "attention_delta", 0.0, 0.0, stream);
-        attention_delta_kernel<<<(int)blocks, 256, 0, stream>>>(att, datt, delta, B, T, H, hd);
+        TB_CUDA(launch_kernel(attention_delta_kernel, dim3((int)blocks), dim3(256), 0, stream, att, datt, delta, B, T, H, hd));
         TB_CUDA(cudaGetLastError());
         ctx->launches++;
         prof_close(ctx, stream);
@@ -692,12 +700,12 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     dim3 grid(p.nq, BH);
     const double tri = (double)BH * T * (double)T * hd;      // one lower-triangular product = tri flops
     prof_mark(ctx, "attention_bwd_dkdv", 4.0 * tri, (double)BH * T * hd * (2.0 * 4 + 8.0), stream);
-    attention_bwd_dkdv_kernel<<<grid, ATT_BWD_THREADS, ATT_DKDV_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
+    TB_CUDA(launch_kernel(attention_bwd_dkdv_kernel, dim3(grid), dim3(ATT_BWD_THREADS), ATT_DKDV_SMEM, stream, tmQ, tmK, tmV, tmdO, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
     prof_mark(ctx, "attention_bwd_dq", 3.0 * tri, (double)BH * T * hd * (2.0 * 4 + 4.0), stream);
-    attention_bwd_dq_kernel<<<grid, ATT_BWD_THREADS, ATT_DQ_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
+    TB_CUDA(launch_kernel(attention_bwd_dq_kernel, dim3(grid), dim3(ATT_BWD_THREADS), ATT_DQ_SMEM, stream, tmQ, tmK, tmV, tmdO, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -729,7 +737,7 @@ int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     dim3 grid(p.nq, BH);
     // algorithmic work: the lower triangle of two products of 2*T*T*hd flops each
     prof_mark(ctx, "attention_fwd", 2.0 * (double)BH * T * (double)T * hd, (double)BH * T * hd * 2.0 * 4.0, stream);
-    attention_fwd_kernel<<<grid, 192, ATT_FWD_SMEM, stream>>>(tmQ, tmK, tmV, p);
+    TB_CUDA(launch_kernel(attention_fwd_kernel, dim3(grid), dim3(192), ATT_FWD_SMEM, stream, tmQ, tmK, tmV, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);

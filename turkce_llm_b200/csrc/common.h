@@ -141,4 +141,36 @@ int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int 
 
 static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
 
+// ---- launches with programmatic dependent launch: the next kernel of the stream may be scheduled
+// and run its prologue while this one drains; every kernel of this library therefore executes
+// pdl_wait() before it touches global memory (a no-op for a launch without the attribute).
+int pdl_mode();     // 0 off, 1 every launch, 2 only launches with >= 64 KB of dynamic shared memory
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    const int mode = pdl_mode();
+    const bool pdl = mode == 1 || (mode == 2 && smem >= 65536);
+    cfg.attrs = pdl ? attr : nullptr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+// waits until every kernel this launch depends on has completed and its writes are visible
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// lets the next kernel of the stream start launching
+__device__ __forceinline__ void pdl_launch_dependents_now() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+#ifndef TB_PDL_STEP_LATE
+    pdl_launch_dependents_now();
+#endif
+}
+#endif
+
 }  // namespace tb

@@ -6,6 +6,7 @@
 #include "common.h"
 
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <set>
@@ -64,6 +65,15 @@ int ensure_scratch(DeviceCtx* ctx, size_t bytes) {
     TB_CUDA(cudaMalloc(&ctx->scratch, want));
     ctx->scratch_bytes = want;
     return 0;
+}
+
+int pdl_mode() {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* e = getenv("TB_PDL");
+        mode = getenv("TB_NO_PDL") ? 0 : (e ? atoi(e) : 2);
+    }
+    return mode;
 }
 
 const char* prof_intern(const char* text) {

@@ -129,7 +129,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int lane = threadIdx.x & 31;
     const int total_tiles = p.batch * p.splits * p.mt * p.nt;
 
+    // Prologue: nothing here reads or writes memory an earlier kernel of the stream produces, so it
+    // may overlap that kernel's tail (programmatic dependent launch); pdl_wait() below is the fence.
     if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        if (p.tma_mode) tma_prefetch_desc(&tmC);
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], EPI_WARPS); }
         for (int i = 0; i < EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
@@ -144,12 +149,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            tma_prefetch_desc(&tmA);
-            tma_prefetch_desc(&tmB);
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -177,6 +181,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
+            pdl_launch_dependents_now();     // all loads issued: the next kernel may start its prologue
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 1); }
         }
     } else if (warp == 1) {
@@ -337,7 +342,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
             ++it;
         }
-        if (lane == 0) tma_store_wait_all<0>();
+        if (lane == 0) tma_store_wait_read<0>();
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 3); }
     } else {
         // ------------------------------------------- epilogue, generic (any alignment)
@@ -470,6 +475,8 @@ __global__ void reduce_splits_kernel(const float* __restrict__ part, float* __re
                                      bf16* __restrict__ out16, int M, int N, long long ldc32, long long ldc16,
                                      int splits, long long strideC32, long long strideC16, float beta,
                                      const float* __restrict__ bias) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long per = (long long)M * N;
     const int z = blockIdx.y;
     const long long nvec = per / VEC;
@@ -666,7 +673,7 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
     const long long total = (long long)p.batch * p.splits * p.mt * p.nt;
     int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     if (grid < 1) grid = 1;
-    gemm_bf16_kernel<BN, TF32><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, p);
+    TB_CUDA(launch_kernel((gemm_bf16_kernel<BN, TF32>), dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, stream, tmA, tmB, tmC, tmR, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -786,11 +793,9 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
         dim3 grid(blocks, a.batch);
         prof_mark(ctx, "splitk_reduce", 0.0, (double)(splits + 2) * per * a.batch * 4.0, stream);
         if (vec4)
-            reduce_splits_kernel<4><<<grid, 256, 0, stream>>>(ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits,
-                                                              a.strideC32, a.strideC16, a.beta, a.bias);
+            TB_CUDA(launch_kernel((reduce_splits_kernel<4>), dim3(grid), dim3(256), 0, stream, ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits, a.strideC32, a.strideC16, a.beta, a.bias));
         else
-            reduce_splits_kernel<1><<<grid, 256, 0, stream>>>(ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits,
-                                                              a.strideC32, a.strideC16, a.beta, a.bias);
+            TB_CUDA(launch_kernel((reduce_splits_kernel<1>), dim3(grid), dim3(256), 0, stream, ws, a.C32, a.C16, a.M, a.N, a.ldc32, a.ldc16, splits, a.strideC32, a.strideC16, a.beta, a.bias));
         TB_CUDA(cudaGetLastError());
         ctx->launches++;
         prof_close(ctx, stream);

@@ -12,6 +12,8 @@ namespace tb {
 __global__ void pack_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst, int rows, int cols,
                                  long long ld_src, long long ld_dst, long long stride_src, long long stride_dst,
                                  int vec) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int z = blockIdx.z;
     const float* s = src + (long long)z * stride_src;
     bf16* d = dst + (long long)z * stride_dst;
@@ -54,7 +56,7 @@ int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int 
     if (blocks < 1) blocks = 1;
     dim3 grid((unsigned)blocks, 1, (unsigned)batch);
     prof_mark(ctx, "pack_bf16", 0.0, (double)rows * cols * batch * 6.0, stream);
-    pack_bf16_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst, vec);
+    TB_CUDA(launch_kernel(pack_bf16_kernel, dim3(grid), dim3(256), 0, stream, src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst, vec));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -63,6 +65,8 @@ int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int 
 
 __global__ void copy_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols,
                                 long long ld_src, long long ld_dst, long long stride_src, long long stride_dst) {
+    pdl_wait();
+    pdl_launch_dependents();
     const float* s = src + (long long)blockIdx.z * stride_src;
     float* d = dst + (long long)blockIdx.z * stride_dst;
     const long long total = (long long)rows * cols;
@@ -81,7 +85,7 @@ int launch_copy_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, int 
     if (blocks > 8LL * ctx->sm_count) blocks = 8LL * ctx->sm_count;
     dim3 grid((unsigned)blocks, 1, (unsigned)batch);
     prof_mark(ctx, "copy_f32", 0.0, (double)rows * cols * batch * 8.0, stream);
-    copy_f32_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst);
+    TB_CUDA(launch_kernel(copy_f32_kernel, dim3(grid), dim3(256), 0, stream, src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -93,6 +97,8 @@ int launch_copy_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, int 
 __global__ void split3_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols,
                                   long long ld_src, long long ld_dst, int along_cols, int pattern,
                                   long long stride_src, long long stride_dst) {
+    pdl_wait();
+    pdl_launch_dependents();
     const float* s = src + (long long)blockIdx.z * stride_src;
     float* d = dst + (long long)blockIdx.z * stride_dst;
     const long long total = (long long)rows * cols;
@@ -125,8 +131,7 @@ int launch_split3_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, in
     if (blocks > 8LL * ctx->sm_count) blocks = 8LL * ctx->sm_count;
     dim3 grid((unsigned)blocks, 1, (unsigned)batch);
     prof_mark(ctx, "split3_f32", 0.0, (double)rows * cols * batch * 16.0, stream);
-    split3_f32_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst, along_cols, pattern, stride_src,
-                                                stride_dst);
+    TB_CUDA(launch_kernel(split3_f32_kernel, dim3(grid), dim3(256), 0, stream, src, dst, rows, cols, ld_src, ld_dst, along_cols, pattern, stride_src, stride_dst));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);

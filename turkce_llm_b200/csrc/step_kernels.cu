@@ -35,6 +35,8 @@ __device__ __forceinline__ float warp_max(float v) {
 // ------------------------------------------------------------------ embedding
 __global__ void embed_fwd_kernel(const float* __restrict__ E, const uint32_t* __restrict__ ids,
                                  float* __restrict__ x, long long total, int D) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const long long n = i / D;
@@ -47,35 +49,68 @@ int launch_embed_fwd(DeviceCtx* ctx, const float* E, const uint32_t* ids, float*
                      cudaStream_t st) {
     const long long total = (long long)rows * D;
     prof_mark(ctx, "embed_fwd", 0.0, 0.0, st);
-    embed_fwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(E, ids, x, total, D);
+    TB_CUDA(launch_kernel(embed_fwd_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, E, ids, x, total, D));
     TB_LAUNCHED(ctx);
     return 0;
 }
 
-// One block per run of equal tokens (rows pre-sorted by token, ties by position): thread j
-// adds the rows of the run in ascending position, then adds the sum to dE[token, j].
-// The grid has one block per row; blocks past the number of runs (read from device memory, so
+// Embedding gradient.  The host sorts the rows by token (ties by position) and cuts every run of
+// equal tokens into chunks of at most kEmbedChunk rows; one block per chunk adds its rows in
+// ascending position.  A run of one chunk adds straight into dE[token]; a longer run (a frequent
+// token) parks each chunk's sum in `partial`, and the block that takes the run's last ticket adds
+// the chunk sums in chunk order, so the result does not depend on which block finishes last.
+// meta[3c..3c+2] = {first partial slot of the run or 0xffffffff, chunk index in the run, chunks in the run}.
+// The grid has one block per row; blocks past the number of chunks (read from device memory, so
 // that the launch shape does not depend on the batch) return at once.
 __global__ void embed_bwd_kernel(const float* __restrict__ dx, const uint32_t* __restrict__ order,
                                  const uint32_t* __restrict__ seg_start, const uint32_t* __restrict__ seg_token,
-                                 const uint32_t* __restrict__ nseg, float* __restrict__ dE, int D) {
+                                 const uint32_t* __restrict__ meta, const uint32_t* __restrict__ nseg,
+                                 float* __restrict__ partial, unsigned int* __restrict__ tickets,
+                                 float* __restrict__ dE, int D) {
+    pdl_wait();
+    pdl_launch_dependents();
     const uint32_t seg = blockIdx.x;
     if (seg >= *nseg) return;
+    __shared__ uint32_t rows[kEmbedChunk];
+    __shared__ int is_last;
     const uint32_t r0 = seg_start[seg], r1 = seg_start[seg + 1];
+    const int n = (int)(r1 - r0);
     const long long tok = seg_token[seg];
+    const uint32_t slot0 = meta[3 * seg], idx = meta[3 * seg + 1], count = meta[3 * seg + 2];
+    if ((int)threadIdx.x < n) rows[threadIdx.x] = order[r0 + threadIdx.x];
+    __syncthreads();
+    float* dst = slot0 == 0xffffffffu ? dE + tok * D : partial + (long long)(slot0 + idx) * D;
     for (int j = threadIdx.x; j < D; j += blockDim.x) {
         float acc = 0.0f;
-        for (uint32_t r = r0; r < r1; ++r) acc += dx[(long long)order[r] * D + j];
+        for (int r = 0; r < n; ++r) acc += dx[(long long)rows[r] * D + j];
+        if (slot0 == 0xffffffffu) dst[j] += acc; else dst[j] = acc;
+    }
+    if (slot0 == 0xffffffffu) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(&tickets[slot0], 1u);
+        is_last = (t == count - 1u);
+        if (is_last) tickets[slot0] = 0u;              // ready for the next step
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int j = threadIdx.x; j < D; j += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t c = 0; c < count; ++c) acc += __ldcg(partial + (long long)(slot0 + c) * D + j);
         dE[tok * D + j] += acc;
     }
 }
 
 int launch_embed_bwd(DeviceCtx* ctx, const float* dx, const uint32_t* order, const uint32_t* seg_start,
-                     const uint32_t* seg_token, const uint32_t* nseg, int rows, float* dE, int D, cudaStream_t st) {
+                     const uint32_t* seg_token, const uint32_t* meta, const uint32_t* nseg, int rows, float* partial,
+                     unsigned int* tickets, float* dE, int D, cudaStream_t st) {
     if (rows <= 0) return 0;
     const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : 64);
     prof_mark(ctx, "embed_bwd", 0.0, 0.0, st);
-    embed_bwd_kernel<<<rows, threads, 0, st>>>(dx, order, seg_start, seg_token, nseg, dE, D);
+    TB_CUDA(launch_kernel(embed_bwd_kernel, dim3(rows), dim3(threads), 0, st, dx, order, seg_start, seg_token, meta,
+                          nseg, partial, tickets, dE, D));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -84,6 +119,8 @@ int launch_embed_bwd(DeviceCtx* ctx, const float* dx, const uint32_t* order, con
 // y = x * r * w,  r = 1/sqrt(mean(x^2) + eps)   (model/model_ops.c; eps inside the root)
 __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                    bf16* __restrict__ out, float* __restrict__ rinv, int rows, int cols, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
@@ -103,7 +140,7 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
 int launch_rmsnorm_fwd(DeviceCtx* ctx, const float* x, const float* w, bf16* out, float* rinv, int rows, int cols,
                        float eps, cudaStream_t st) {
     prof_mark(ctx, "rmsnorm_fwd", 0.0, 0.0, st);
-    rmsnorm_fwd_kernel<<<grid_for(rows, 8, ctx), 256, 0, st>>>(x, w, out, rinv, rows, cols, eps);
+    TB_CUDA(launch_kernel(rmsnorm_fwd_kernel, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, out, rinv, rows, cols, eps));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -113,6 +150,8 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
                                    const float* __restrict__ rinv, const float* __restrict__ dy,
                                    float* __restrict__ dx, bf16* __restrict__ dx16, float* __restrict__ wtmp,
                                    int rows, int cols, int accumulate) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
@@ -145,6 +184,8 @@ __global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* 
                                       float* __restrict__ dx, bf16* __restrict__ dx16, float* __restrict__ dw,
                                       float* __restrict__ db, float* __restrict__ partial,
                                       unsigned int* __restrict__ ticket, int rows, int cols, int accumulate) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float sh_part[];      // [warps][cols]
     __shared__ int is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -262,11 +303,9 @@ int launch_rmsnorm_bwd_dw(DeviceCtx* ctx, const float* x, const float* w, const 
     const size_t smem = (size_t)8 * 2 * cols * sizeof(float);
     prof_mark(ctx, "rmsnorm_bwd", 0.0, 0.0, st);
     if (cols <= 384)
-        rmsnorm_bwd_dw_kernel<12><<<blocks, 256, smem, st>>>(x, w, rinv, dy, dx, dx16, dw, db, partial, ticket, rows,
-                                                              cols, accumulate);
+        TB_CUDA(launch_kernel((rmsnorm_bwd_dw_kernel<12>), dim3(blocks), dim3(256), smem, st, x, w, rinv, dy, dx, dx16, dw, db, partial, ticket, rows, cols, accumulate));
     else
-        rmsnorm_bwd_dw_kernel<32><<<blocks, 256, smem, st>>>(x, w, rinv, dy, dx, dx16, dw, db, partial, ticket, rows,
-                                                              cols, accumulate);
+        TB_CUDA(launch_kernel((rmsnorm_bwd_dw_kernel<32>), dim3(blocks), dim3(256), smem, st, x, w, rinv, dy, dx, dx16, dw, db, partial, ticket, rows, cols, accumulate));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -274,7 +313,7 @@ int launch_rmsnorm_bwd_dw(DeviceCtx* ctx, const float* x, const float* w, const 
 int launch_rmsnorm_bwd(DeviceCtx* ctx, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
                        bf16* dx16, float* wtmp, int rows, int cols, int accumulate, cudaStream_t st) {
     prof_mark(ctx, "rmsnorm_bwd", 0.0, 0.0, st);
-    rmsnorm_bwd_kernel<<<grid_for(rows, 8, ctx), 256, 0, st>>>(x, w, rinv, dy, dx, dx16, wtmp, rows, cols, accumulate);
+    TB_CUDA(launch_kernel(rmsnorm_bwd_kernel, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, rinv, dy, dx, dx16, wtmp, rows, cols, accumulate));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -284,6 +323,8 @@ int launch_rmsnorm_bwd(DeviceCtx* ctx, const float* x, const float* w, const flo
 __global__ void rope_split_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
                                   const float* __restrict__ sin_t, bf16* __restrict__ Q, bf16* __restrict__ K,
                                   bf16* __restrict__ V, int B, int T, int H, int hd, int kv_cap) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int half = hd >> 1;
     const int D = H * hd;
     const long long total = (long long)B * T * H * half;
@@ -314,7 +355,7 @@ int launch_rope_split(DeviceCtx* ctx, const float* qkv, const float* cos_t, cons
     TB_CHECK(hd % 2 == 0, "head dim must be even");
     const long long total = (long long)B * T * H * (hd / 2);
     prof_mark(ctx, "rope_split", 0.0, 0.0, st);
-    rope_split_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(qkv, cos_t, sin_t, Q, K, V, B, T, H, hd, kv_cap);
+    TB_CUDA(launch_kernel(rope_split_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, qkv, cos_t, sin_t, Q, K, V, B, T, H, hd, kv_cap));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -324,6 +365,8 @@ __global__ void rope_merge_bwd_kernel(const float* __restrict__ dQ, const float*
                                       const float* __restrict__ dV, const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t, bf16* __restrict__ dqkv, int B, int T, int H,
                                       int hd) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int half = hd >> 1;
     const int D = H * hd;
     const long long total = (long long)B * T * H * half;
@@ -353,7 +396,7 @@ int launch_rope_merge_bwd(DeviceCtx* ctx, const float* dQ, const float* dK, cons
                           const float* sin_t, bf16* dqkv, int B, int T, int H, int hd, cudaStream_t st) {
     const long long total = (long long)B * T * H * (hd / 2);
     prof_mark(ctx, "rope_merge_bwd", 0.0, 0.0, st);
-    rope_merge_bwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(dQ, dK, dV, cos_t, sin_t, dqkv, B, T, H, hd);
+    TB_CUDA(launch_kernel(rope_merge_bwd_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, dQ, dK, dV, cos_t, sin_t, dqkv, B, T, H, hd));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -366,6 +409,8 @@ __device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max);
 __global__ void rope_decode_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
                                    const float* __restrict__ sin_t, float* __restrict__ Q, bf16* __restrict__ Kc,
                                    bf16* __restrict__ Vc, const int* __restrict__ pos, int S, int H, int hd, int cap) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int half = hd >> 1, D = H * hd;
     const int t = *pos;
     const int total = S * H * half;
@@ -390,7 +435,7 @@ int launch_rope_decode(DeviceCtx* ctx, const float* qkv, const float* cos_t, con
                        bf16* Vc, const int* pos, int S, int H, int hd, int cap, cudaStream_t st) {
     const int total = S * H * (hd / 2);
     prof_mark(ctx, "rope_decode", 0.0, 0.0, st);
-    rope_decode_kernel<<<grid_for(total, 128, ctx), 128, 0, st>>>(qkv, cos_t, sin_t, Q, Kc, Vc, pos, S, H, hd, cap);
+    TB_CUDA(launch_kernel(rope_decode_kernel, dim3(grid_for(total, 128, ctx)), dim3(128), 0, st, qkv, cos_t, sin_t, Q, Kc, Vc, pos, S, H, hd, cap));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -400,6 +445,8 @@ int launch_rope_decode(DeviceCtx* ctx, const float* qkv, const float* cos_t, con
 __global__ void attn_decode_kernel(const float* __restrict__ Q, const bf16* __restrict__ Kc,
                                    const bf16* __restrict__ Vc, bf16* __restrict__ att, const int* __restrict__ pos,
                                    int H, int hd, int cap, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float sh[];            // q [hd] | p [cap] | red [32] | part [2][hd]
     float* q = sh;
     float* p = sh + hd;
@@ -462,13 +509,15 @@ int launch_attn_decode(DeviceCtx* ctx, const float* Q, const bf16* Kc, const bf1
     TB_CHECK(smem <= 48 * 1024, "KV cache capacity %d too large for the decode attention kernel", cap);
     dim3 grid(H, S);
     prof_mark(ctx, "attn_decode", 0.0, 0.0, st);
-    attn_decode_kernel<<<grid, threads, smem, st>>>(Q, Kc, Vc, att, pos, H, hd, cap, scale);
+    TB_CUDA(launch_kernel(attn_decode_kernel, dim3(grid), dim3(threads), smem, st, Q, Kc, Vc, att, pos, H, hd, cap, scale));
     TB_LAUNCHED(ctx);
     return 0;
 }
 
 // out[i, :] = in[idx(i), :] for the last position of every sequence: idx(i) = i*T + T-1
 __global__ void gather_last_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int S, int T, int D) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < S * D; i += gridDim.x * blockDim.x) {
         const int sq = i / D, j = i % D;
         out[i] = in[((long long)sq * T + T - 1) * D + j];
@@ -477,7 +526,7 @@ __global__ void gather_last_rows_kernel(const float* __restrict__ in, float* __r
 
 int launch_gather_last_rows(DeviceCtx* ctx, const float* in, float* out, int S, int T, int D, cudaStream_t st) {
     prof_mark(ctx, "gather_last_rows", 0.0, 0.0, st);
-    gather_last_rows_kernel<<<grid_for((long long)S * D, 256, ctx), 256, 0, st>>>(in, out, S, T, D);
+    TB_CUDA(launch_kernel(gather_last_rows_kernel, dim3(grid_for((long long)S * D, 256, ctx)), dim3(256), 0, st, in, out, S, T, D));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -487,6 +536,8 @@ int launch_gather_last_rows(DeviceCtx* ctx, const float* in, float* out, int S, 
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, uint32_t* __restrict__ tok,
                                    uint32_t* __restrict__ out, const int* __restrict__ state, int V, long long ld,
                                    int out_ld) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float bv[32];
     __shared__ int bi[32];
     const int sq = blockIdx.x;
@@ -516,6 +567,8 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, uint32_t* _
 
 // after a step: one more token generated; the position advances once the token has been fed
 __global__ void advance_state_kernel(int* __restrict__ state, int advance_pos) {
+    pdl_wait();
+    pdl_launch_dependents();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         state[1] += 1;
         if (advance_pos) state[0] += 1;
@@ -525,10 +578,10 @@ __global__ void advance_state_kernel(int* __restrict__ state, int advance_pos) {
 int launch_argmax_rows(DeviceCtx* ctx, const float* logits, uint32_t* tok, uint32_t* out, int* state, int S, int V,
                        long long ld, int out_ld, int advance_pos, cudaStream_t st) {
     prof_mark(ctx, "argmax_rows", 0.0, 0.0, st);
-    argmax_rows_kernel<<<S, 1024, 0, st>>>(logits, tok, out, state, V, ld, out_ld);
+    TB_CUDA(launch_kernel(argmax_rows_kernel, dim3(S), dim3(1024), 0, st, logits, tok, out, state, V, ld, out_ld));
     TB_LAUNCHED(ctx);
     prof_mark(ctx, "advance_state", 0.0, 0.0, st);
-    advance_state_kernel<<<1, 32, 0, st>>>(state, advance_pos);
+    TB_CUDA(launch_kernel(advance_state_kernel, dim3(1), dim3(32), 0, st, state, advance_pos));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -540,6 +593,8 @@ int launch_argmax_rows(DeviceCtx* ctx, const float* logits, uint32_t* tok, uint3
 // 128-wide tile that holds the diagonal: the following GEMMs read whole tiles up to there.
 __global__ void attn_softmax_fwd_kernel(const float* __restrict__ S, bf16* __restrict__ P, long long rows, int T,
                                         long long ld, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
@@ -563,7 +618,7 @@ int launch_attn_softmax_fwd(DeviceCtx* ctx, const float* S, bf16* P, int BH, int
                             cudaStream_t st) {
     const long long rows = (long long)BH * T;
     prof_mark(ctx, "attn_softmax_fwd", 0.0, 0.0, st);
-    attn_softmax_fwd_kernel<<<grid_for(rows, 8, ctx, 32), 256, 0, st>>>(S, P, rows, T, ld, scale);
+    TB_CUDA(launch_kernel(attn_softmax_fwd_kernel, dim3(grid_for(rows, 8, ctx, 32)), dim3(256), 0, st, S, P, rows, T, ld, scale));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -571,6 +626,8 @@ int launch_attn_softmax_fwd(DeviceCtx* ctx, const float* S, bf16* P, int BH, int
 // dS = P * (dP - <dP, P>) * scale   (softmax backward then the score scale)
 __global__ void attn_softmax_bwd_kernel(const bf16* __restrict__ P, const float* __restrict__ dP,
                                         bf16* __restrict__ dS, long long rows, int T, long long ld, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
@@ -592,7 +649,7 @@ int launch_attn_softmax_bwd(DeviceCtx* ctx, const bf16* P, const float* dP, bf16
                             float scale, cudaStream_t st) {
     const long long rows = (long long)BH * T;
     prof_mark(ctx, "attn_softmax_bwd", 0.0, 0.0, st);
-    attn_softmax_bwd_kernel<<<grid_for(rows, 8, ctx, 32), 256, 0, st>>>(P, dP, dS, rows, T, ld, scale);
+    TB_CUDA(launch_kernel(attn_softmax_bwd_kernel, dim3(grid_for(rows, 8, ctx, 32)), dim3(256), 0, st, P, dP, dS, rows, T, ld, scale));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -600,6 +657,8 @@ int launch_attn_softmax_bwd(DeviceCtx* ctx, const bf16* P, const float* dP, bf16
 // dout [B*T, H*hd] -> dO [B,H,T,hd]
 __global__ void heads_split_kernel(const bf16* __restrict__ dout, bf16* __restrict__ dO, int B, int T, int H,
                                    int hd) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long total = (long long)B * T * H * hd;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -616,7 +675,7 @@ __global__ void heads_split_kernel(const bf16* __restrict__ dout, bf16* __restri
 int launch_heads_split(DeviceCtx* ctx, const bf16* dout, bf16* dO, int B, int T, int H, int hd, cudaStream_t st) {
     const long long total = (long long)B * T * H * hd;
     prof_mark(ctx, "heads_split", 0.0, 0.0, st);
-    heads_split_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(dout, dO, B, T, H, hd);
+    TB_CUDA(launch_kernel(heads_split_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, dout, dO, B, T, H, hd));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -624,6 +683,8 @@ int launch_heads_split(DeviceCtx* ctx, const bf16* dout, bf16* dO, int B, int T,
 // --------------------------------------------------------------------- SwiGLU
 // h = g * sigmoid(g) * u with g = gu[:, :F], u = gu[:, F:]   (model/feedforward.c:9-14)
 __global__ void swiglu_fwd_kernel(const float* __restrict__ gu, bf16* __restrict__ h, long long total4, int F) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int F4 = F >> 2;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4;
          i += (long long)gridDim.x * blockDim.x) {
@@ -649,7 +710,7 @@ int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F,
     TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
     const long long total = (long long)rows * (F / 4);
     prof_mark(ctx, "swiglu_fwd", 0.0, 0.0, st);
-    swiglu_fwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(gu, h, total, F);
+    TB_CUDA(launch_kernel(swiglu_fwd_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, h, total, F));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -657,6 +718,8 @@ int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F,
 // dg = dh*u*(sg + g*sg*(1-sg)),  du = dh*g*sg
 __global__ void swiglu_bwd_kernel(const float* __restrict__ gu, const float* __restrict__ dh,
                                   bf16* __restrict__ dgu, long long total4, int F) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int F4 = F >> 2;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4;
          i += (long long)gridDim.x * blockDim.x) {
@@ -688,7 +751,7 @@ int launch_swiglu_bwd(DeviceCtx* ctx, const float* gu, const float* dh, bf16* dg
     TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
     const long long total = (long long)rows * (F / 4);
     prof_mark(ctx, "swiglu_bwd", 0.0, 0.0, st);
-    swiglu_bwd_kernel<<<grid_for(total, 256, ctx), 256, 0, st>>>(gu, dh, dgu, total, F);
+    TB_CUDA(launch_kernel(swiglu_bwd_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, dh, dgu, total, F));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -709,6 +772,8 @@ __device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
 __global__ void cross_entropy_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
                                      float* __restrict__ loss_rows, bf16* __restrict__ dlogits, int V, long long ld,
                                      float grad_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float sh[32];
     const long long row = blockIdx.x;
     const float* z = logits + row * ld;
@@ -736,6 +801,8 @@ __global__ void __launch_bounds__(1024, 1)
 cross_entropy_row_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
                          float* __restrict__ loss_rows, bf16* __restrict__ dlogits, int V, long long ld,
                          float grad_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float sh[32];
     const long long row = blockIdx.x;
     const float* z = logits + row * ld;
@@ -777,9 +844,9 @@ int launch_cross_entropy(DeviceCtx* ctx, const float* logits, const uint32_t* ta
                          bf16* dlogits, int rows, int V, long long ld, float grad_scale, cudaStream_t st) {
     prof_mark(ctx, "cross_entropy", 0.0, 0.0, st);
     if (V > 4096 && V <= 32768)
-        cross_entropy_row_kernel<<<rows, 1024, 0, st>>>(logits, targets, loss_rows, dlogits, V, ld, grad_scale);
+        TB_CUDA(launch_kernel(cross_entropy_row_kernel, dim3(rows), dim3(1024), 0, st, logits, targets, loss_rows, dlogits, V, ld, grad_scale));
     else
-        cross_entropy_kernel<<<rows, 512, 0, st>>>(logits, targets, loss_rows, dlogits, V, ld, grad_scale);
+        TB_CUDA(launch_kernel(cross_entropy_kernel, dim3(rows), dim3(512), 0, st, logits, targets, loss_rows, dlogits, V, ld, grad_scale));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -814,6 +881,8 @@ __device__ __forceinline__ float2 load2(const bf16* p) {
 template <typename T>
 __global__ void colsum_kernel(const T* __restrict__ in, float* __restrict__ out, float* __restrict__ partial,
                               unsigned int* __restrict__ tickets, int rows, int cols) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float2 part[8][33];
     __shared__ int is_last;
     const int tx = threadIdx.x, ty = threadIdx.y;
@@ -883,7 +952,7 @@ static int colsum_impl(DeviceCtx* ctx, const T* in, float* out, float* partial, 
     dim3 grid((cols + 63) / 64, kColsumChunks), block(32, 8);
     unsigned int* tickets = reinterpret_cast<unsigned int*>(partial);
     prof_mark(ctx, "colsum", 0.0, 0.0, st);
-    colsum_kernel<T><<<grid, block, 0, st>>>(in, out, partial + kTicketWords, tickets, rows, cols);
+    TB_CUDA(launch_kernel((colsum_kernel<T>), dim3(grid), dim3(block), 0, st, in, out, partial + kTicketWords, tickets, rows, cols));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -899,6 +968,8 @@ int launch_colsum_bf16(DeviceCtx* ctx, const bf16* in, float* out, float* partia
 
 // ------------------------------------------------------- gradient norm, Adam
 __global__ void sumsq_partial_kernel(const float* __restrict__ x, long long n, float* __restrict__ partial) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float sh[32];
     float s = 0.0f;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -910,18 +981,30 @@ __global__ void sumsq_partial_kernel(const float* __restrict__ x, long long n, f
 
 int launch_sumsq_partial(DeviceCtx* ctx, const float* x, long long n, float* partial, cudaStream_t st) {
     prof_mark(ctx, "sumsq_partial", 0.0, 0.0, st);
-    sumsq_partial_kernel<<<kNormBlocks, 256, 0, st>>>(x, n, partial);
+    TB_CUDA(launch_kernel(sumsq_partial_kernel, dim3(kNormBlocks), dim3(256), 0, st, x, n, partial));
     TB_LAUNCHED(ctx);
     return 0;
 }
 
-// The reference sums the block partials on the host in float64 (model/gpu_train.c:508-511);
-// one device thread does the same sum so the step needs no host round trip.
+// The reference sums the block partials on the host in float64 (model/gpu_train.c:508-511); one
+// warp does that sum here so the step needs no host round trip: each lane adds a contiguous run of
+// partials, then a fixed shuffle tree combines the lanes (same order every run).
 __global__ void clip_scale_kernel(const float* __restrict__ partial, float max_norm, float* __restrict__ scalars,
                                   double* __restrict__ norm64) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+    constexpr int PER = kNormBlocks / 32;
+    static_assert(kNormBlocks % 32 == 0, "one contiguous run of partials per lane");
+    float v[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) v[i] = partial[threadIdx.x * PER + i];
     double ss = 0.0;
-    for (int i = 0; i < kNormBlocks; ++i) ss += (double)partial[i];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) ss += (double)v[i];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (threadIdx.x != 0) return;
     const double norm = sqrt(ss);
     *norm64 = norm;
     scalars[0] = (float)norm;
@@ -931,7 +1014,7 @@ __global__ void clip_scale_kernel(const float* __restrict__ partial, float max_n
 int launch_clip_scale(DeviceCtx* ctx, const float* partial, float max_norm, float* scalars, double* norm64,
                       cudaStream_t st) {
     prof_mark(ctx, "clip_scale", 0.0, 0.0, st);
-    clip_scale_kernel<<<1, 32, 0, st>>>(partial, max_norm, scalars, norm64);
+    TB_CUDA(launch_kernel(clip_scale_kernel, dim3(1), dim3(32), 0, st, partial, max_norm, scalars, norm64));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -941,6 +1024,8 @@ int launch_clip_scale(DeviceCtx* ctx, const float* partial, float max_norm, floa
 __global__ void adam_kernel(float* __restrict__ p, bf16* __restrict__ p16, const float* __restrict__ g,
                             float* __restrict__ m, float* __restrict__ v, long long n, float lr, float b1, float b2,
                             float eps, float bc1, float bc2, float grad_scale, const float* __restrict__ dev_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     const float gs = dev_scale ? grad_scale * dev_scale[1] : grad_scale;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (long long)gridDim.x * blockDim.x) {
@@ -961,8 +1046,7 @@ int launch_adam(DeviceCtx* ctx, float* p, bf16* p16, const float* g, float* m, f
                 float b1, float b2, float eps, float bc1, float bc2, float grad_scale, const float* dev_scale,
                 cudaStream_t st) {
     prof_mark(ctx, "adam", 0.0, 0.0, st);
-    adam_kernel<<<grid_for(n, 256, ctx, 32), 256, 0, st>>>(p, p16, g, m, v, n, lr, b1, b2, eps, bc1, bc2, grad_scale,
-                                                            dev_scale);
+    TB_CUDA(launch_kernel(adam_kernel, dim3(grid_for(n, 256, ctx, 32)), dim3(256), 0, st, p, p16, g, m, v, n, lr, b1, b2, eps, bc1, bc2, grad_scale, dev_scale));
     TB_LAUNCHED(ctx);
     return 0;
 }

@@ -52,10 +52,15 @@ int launch_cross_entropy(DeviceCtx*, const float* logits, const uint32_t* target
 size_t colsum_partial_floats(int cols);
 int launch_colsum_f32(DeviceCtx*, const float* in, float* out, float* partial, int rows, int cols, cudaStream_t);
 int launch_colsum_bf16(DeviceCtx*, const bf16* in, float* out, float* partial, int rows, int cols, cudaStream_t);
-// dE[token] += sum of dx rows of that token, rows taken in ascending position order
-// (nseg = number of token runs, in device memory; rows = launch size = number of rows)
+// dE[token] += sum of dx rows of that token.  Rows sorted by token; each run cut into chunks of at most
+// kEmbedChunk rows (seg_start/seg_token per chunk, meta = {first partial slot | 0xffffffff, chunk index,
+// chunks in run}); nseg = number of chunks, in device memory; rows = launch size = number of rows.
+// partial: embed_partial_slots(rows) * D floats; tickets: embed_partial_slots(rows) words, zero.
+constexpr int kEmbedChunk = 16;
+inline int embed_partial_slots(int rows) { return 2 * (rows / kEmbedChunk) + 2; }
 int launch_embed_bwd(DeviceCtx*, const float* dx, const uint32_t* order, const uint32_t* seg_start,
-                     const uint32_t* seg_token, const uint32_t* nseg, int rows, float* dE, int D, cudaStream_t);
+                     const uint32_t* seg_token, const uint32_t* meta, const uint32_t* nseg, int rows, float* partial,
+                     unsigned int* tickets, float* dE, int D, cudaStream_t);
 constexpr int kNormBlocks = 1024;
 int launch_sumsq_partial(DeviceCtx*, const float* x, long long n, float* partial, cudaStream_t);
 // scalars[0] = norm (as float), scalars[1] = min(1, max_norm / norm) (1 when max_norm <= 0); norm64 = norm

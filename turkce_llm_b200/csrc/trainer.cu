@@ -65,7 +65,10 @@ struct TbTrainer {
     float* norm_scratch = nullptr;
     float* splitk_ws = nullptr; size_t splitk_floats = 0;
 
-    uint32_t *ids = nullptr, *targets = nullptr, *order = nullptr, *seg_start = nullptr, *seg_token = nullptr;
+    uint32_t *ids = nullptr, *targets = nullptr;
+    uint32_t *order = nullptr, *seg_start = nullptr, *seg_token = nullptr, *seg_meta = nullptr;   // one buffer
+    float* embed_partial = nullptr;
+    unsigned int* embed_tickets = nullptr;
     float *loss_rows = nullptr, *cos_t = nullptr, *sin_t = nullptr;
     float* norm_partial = nullptr; float* scalars = nullptr; double* norm64 = nullptr;
 
@@ -287,7 +290,8 @@ int backward_layer(TbTrainer* g, int l) {
 }
 
 int backward_embed(TbTrainer* g) {
-    return launch_embed_bwd(g->ctx, g->dres, g->order, g->seg_start, g->seg_token, g->nseg_dev, g->N, G32(g, 0),
+    return launch_embed_bwd(g->ctx, g->dres, g->order, g->seg_start, g->seg_token, g->seg_meta, g->nseg_dev, g->N,
+                            g->embed_partial, g->embed_tickets, G32(g, 0),
                             g->D, g->stream);
 }
 
@@ -333,7 +337,9 @@ int stage_inputs(TbTrainer* g, const uint32_t* ids, const uint32_t* targets) {
     return 0;
 }
 
-// Rows grouped by token (ties in ascending position) for the embedding gradient.
+// Rows grouped by token (ties in ascending position) for the embedding gradient; runs of one token
+// are cut into chunks of kEmbedChunk rows (see embed_bwd_kernel).  One pinned buffer, one copy:
+// [order N][chunk start N+1][chunk token N][chunk meta 3N][number of chunks 1].
 int stage_segments(TbTrainer* g) {
     const int N = g->N;
     std::vector<uint64_t> keys(N);
@@ -342,24 +348,32 @@ int stage_segments(TbTrainer* g) {
     uint32_t* order = g->h_seg;
     uint32_t* seg_start = g->h_seg + N;
     uint32_t* seg_token = g->h_seg + 2 * N + 1;
+    uint32_t* meta = g->h_seg + 3 * N + 1;
+    for (int i = 0; i < N; ++i) order[i] = (uint32_t)(keys[i] & 0xffffffffu);
     int nseg = 0;
-    for (int i = 0; i < N; ++i) {
-        order[i] = (uint32_t)(keys[i] & 0xffffffffu);
+    uint32_t slot = 0;
+    for (int i = 0; i < N;) {
         const uint32_t tok = (uint32_t)(keys[i] >> 32);
-        if (i == 0 || tok != (uint32_t)(keys[i - 1] >> 32)) {
-            seg_start[nseg] = (uint32_t)i;
+        int j = i;
+        while (j < N && (uint32_t)(keys[j] >> 32) == tok) ++j;
+        const uint32_t chunks = (uint32_t)((j - i + kEmbedChunk - 1) / kEmbedChunk);
+        for (uint32_t c = 0; c < chunks; ++c) {
+            seg_start[nseg] = (uint32_t)(i + (int)c * kEmbedChunk);
             seg_token[nseg] = tok;
+            meta[3 * nseg] = chunks > 1 ? slot : 0xffffffffu;
+            meta[3 * nseg + 1] = c;
+            meta[3 * nseg + 2] = chunks;
             ++nseg;
         }
+        if (chunks > 1) slot += chunks;
+        i = j;
     }
-    seg_start[nseg] = (uint32_t)N;
+    TB_CHECK((int)slot <= embed_partial_slots(N), "embedding gradient: %u partial slots exceed the buffer", slot);
+    for (int i = nseg; i <= N; ++i) seg_start[i] = (uint32_t)N;
     g->nseg = nseg;
-    const size_t b = sizeof(uint32_t);
-    TB_CUDA(cudaMemcpyAsync(g->order, order, N * b, cudaMemcpyHostToDevice, g->stream));
-    TB_CUDA(cudaMemcpyAsync(g->seg_start, seg_start, (nseg + 1) * b, cudaMemcpyHostToDevice, g->stream));
-    TB_CUDA(cudaMemcpyAsync(g->seg_token, seg_token, nseg * b, cudaMemcpyHostToDevice, g->stream));
-    g->h_seg[3 * N + 1] = (uint32_t)nseg;
-    TB_CUDA(cudaMemcpyAsync(g->nseg_dev, g->h_seg + 3 * N + 1, b, cudaMemcpyHostToDevice, g->stream));
+    g->h_seg[6 * N + 1] = (uint32_t)nseg;
+    TB_CUDA(cudaMemcpyAsync(g->order, g->h_seg, (size_t)(6 * N + 2) * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                            g->stream));
     return 0;
 }
 
@@ -484,14 +498,18 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         TB_TRY(dalloc(g, &g->splitk_ws, g->splitk_floats));
     }
 
-    TB_TRY(dalloc(g, &g->ids, N)); TB_TRY(dalloc(g, &g->targets, N)); TB_TRY(dalloc(g, &g->order, N));
-    TB_TRY(dalloc(g, &g->seg_start, N + 1)); TB_TRY(dalloc(g, &g->seg_token, N));
-    TB_TRY(dalloc(g, &g->nseg_dev, 1));
+    TB_TRY(dalloc(g, &g->ids, N)); TB_TRY(dalloc(g, &g->targets, N)); 
+    TB_TRY(dalloc(g, &g->order, 6 * N + 2));          // order | chunk start | chunk token | chunk meta | count
+    g->seg_start = g->order + N; g->seg_token = g->order + 2 * N + 1; g->seg_meta = g->order + 3 * N + 1;
+    g->nseg_dev = g->order + 6 * N + 1;
+    TB_TRY(dalloc(g, &g->embed_partial, (size_t)embed_partial_slots((int)N) * D));
+    TB_TRY(dalloc(g, &g->embed_tickets, (size_t)embed_partial_slots((int)N)));
+    TB_CUDA(cudaMemset(g->embed_tickets, 0, (size_t)embed_partial_slots((int)N) * sizeof(unsigned int)));
     TB_TRY(dalloc(g, &g->loss_rows, N));
     TB_TRY(dalloc(g, &g->norm_partial, (size_t)kNormBlocks)); TB_TRY(dalloc(g, &g->scalars, 4));
     TB_TRY(dalloc(g, &g->norm64, 1));
     TB_CUDA(cudaMallocHost(&g->h_ids, N * 4)); TB_CUDA(cudaMallocHost(&g->h_targets, N * 4));
-    TB_CUDA(cudaMallocHost(&g->h_seg, (3 * N + 4) * 4)); TB_CUDA(cudaMallocHost(&g->h_loss_rows, N * 4));
+    TB_CUDA(cudaMallocHost(&g->h_seg, (6 * N + 4) * 4)); TB_CUDA(cudaMallocHost(&g->h_loss_rows, N * 4));
     TB_CUDA(cudaMallocHost(&g->h_norm, sizeof(double)));
 
     // RoPE tables [T, hd/2] (model/rope.c:4-18), built on the host in float32
