@@ -131,6 +131,17 @@ int tb_gemm_bf16_splitk_static(int kind, const void* d_A, const void* d_B, int M
 int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld_src, int64_t ld_dst,
                  int batch, int64_t stride_src, int64_t stride_dst, void* stream);
 
+/* Decode-time LM head with the greedy choice fused: d_tok[s] = argmax_v <X[s,:], E[v,:]> (lowest index
+ * on ties) for 1 <= S <= 64 rows of X [S, K] bf16 against the tied embedding table E [V, K] bf16, K a
+ * multiple of 64.  The [S, V] logits (lm_forward's last rows, model/lm_model.c:72-81, whose argmax
+ * model/generate.c:204-206 takes when sampling is off) are not written unless d_logits is given
+ * (float32 [S, ld_logits]).  E is streamed from HBM exactly once; uses the library scratch buffer.
+ * table_is_stable != 0 promises that no earlier work still running on the stream writes E (weights
+ * during generation): the kernel then starts streaming E while that work finishes.  Calls that can
+ * overlap on the GPU (different streams) must not share a device: they share one ticket word. */
+int tb_lmhead_argmax_bf16(const void* d_X, const void* d_E, int S, int V, int K, uint32_t* d_tok, float* d_logits,
+                          int64_t ld_logits, int table_is_stable, void* stream);
+
 /* ---- fused causal attention ---------------------------------------------------- */
 
 /* The per-head attention contractions of the reference's GPU trainer in one kernel: QK^T

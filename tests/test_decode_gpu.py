@@ -81,3 +81,37 @@ def test_generate_in_one_call_equals_stepwise(tb, oracle):
         outs.append(dec.tokens(n_new))
         dec.destroy()
     assert np.array_equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("shape", [(64, 31769, 384), (5, 300, 64), (64, 1000, 128), (17, 40000, 384), (64, 2049, 1024)])
+def test_fused_lmhead_argmax_matches_oracle(tb, oracle, shape):
+    """tb_lmhead_argmax_bf16 against the oracle's BF16-mode product (operands rounded to bf16, float32
+    accumulation): the optional logits within the BF16 bound, the token equal to the argmax of those
+    logits, and equal to the oracle's choice wherever its top-2 margin is clear of the rounding noise."""
+    import torch
+    from turkce_llm_b200 import lib
+    S, V, K = shape
+    rng = np.random.default_rng(11)
+    X = rng.standard_normal((S, K)).astype(np.float32)
+    E = (rng.standard_normal((V, K)) * 0.05).astype(np.float32)
+    from oracle import pyoracle
+    want = oracle.gemm(0, 1, X, E, S, V, K, mode=pyoracle.BF16).reshape(S, V)      # X . E^T, operands rounded to bf16
+    x16 = torch.from_numpy(X).cuda().to(torch.bfloat16)
+    e16 = torch.from_numpy(E).cuda().to(torch.bfloat16)
+    tok = torch.full((S,), -1, device="cuda", dtype=torch.int32)
+    ld = V + 3
+    logits = torch.zeros(S, ld, device="cuda")
+    lib.lmhead_argmax_bf16(x16, e16, tok, logits, ld)
+    tok2 = torch.full((S,), -1, device="cuda", dtype=torch.int32)
+    lib.lmhead_argmax_bf16(x16, e16, tok2)                 # the product path: no logits written
+    lib.sync_check()
+    got = logits[:, :V].cpu().numpy()
+    assert np.all(logits[:, V:].cpu().numpy() == 0.0)       # nothing written past column V
+    assert rel_to_maxabs(got, want) <= 2e-2
+    t = tok.cpu().numpy()
+    assert np.array_equal(t, tok2.cpu().numpy())
+    assert np.array_equal(t, got.argmax(1))                 # lowest index on ties, like numpy
+    srt = np.sort(want, axis=1)
+    clear = (srt[:, -1] - srt[:, -2]) > 4e-2 * np.abs(want).max()
+    assert clear.sum() > 0
+    assert np.array_equal(t[clear], want.argmax(1)[clear])

@@ -42,6 +42,10 @@ struct TbDecoder {
     bf16 *n = nullptr, *att = nullptr, *h = nullptr, *Q = nullptr;
     uint32_t *ids = nullptr, *tok = nullptr, *out = nullptr;
     int* pos = nullptr;
+    bool fused_head = false;                   // LM head with the greedy choice fused (no logits in HBM)
+    float* head_val = nullptr; uint32_t* head_idx = nullptr;   // per-CTA winners of the fused head
+    unsigned int* head_ticket = nullptr;
+    int head_rows = 0;                         // rows of g->n the most recent head() normalised
     float *cos_t = nullptr, *sin_t = nullptr;
     uint32_t* h_pinned = nullptr;
     float* splitk_ws = nullptr; size_t splitk_floats = 0;
@@ -89,14 +93,23 @@ int layer_tail(TbDecoder* g, int l, int rows) {
     return 0;
 }
 
+// logits [rows, Vp] of the normalised rows in g->n (tied LM head)
+int head_logits(TbDecoder* g, int rows) {
+    GemmArgs a;
+    a.kind = GEMM_NT; a.A = g->n; a.B = P16(g, 0); a.M = rows; a.N = g->V; a.K = g->D; a.lda = g->D; a.ldb = g->D;
+    a.C32 = g->logits; a.ldc32 = g->Vp; a.splits = 1; a.pad_cols_writable = true;
+    return launch_gemm_bf16_ws(g->ctx, a, g->splitk_ws, g->splitk_floats, g->stream);
+}
+
 // final norm of `rows` rows of src, tied LM head, greedy choice
 int head(TbDecoder* g, const float* src, int rows, int advance_pos) {
     DeviceCtx* c = g->ctx; cudaStream_t st = g->stream;
     TB_TRY(launch_rmsnorm_fwd(c, src, P32(g, pidx(g->L, 0)), g->n, g->r, rows, g->D, g->eps, st));
-    GemmArgs a;
-    a.kind = GEMM_NT; a.A = g->n; a.B = P16(g, 0); a.M = rows; a.N = g->V; a.K = g->D; a.lda = g->D; a.ldb = g->D;
-    a.C32 = g->logits; a.ldc32 = g->Vp; a.splits = 1; a.pad_cols_writable = true;
-    TB_TRY(launch_gemm_bf16_ws(c, a, g->splitk_ws, g->splitk_floats, st));
+    g->head_rows = rows;
+    if (g->fused_head)
+        return launch_lmhead_argmax(c, g->n, P16(g, 0), rows, g->V, g->D, true, g->head_val, g->head_idx, g->head_ticket,
+                                    g->tok, g->out, g->pos, g->cap, advance_pos, nullptr, 0, st);
+    TB_TRY(head_logits(g, rows));
     return launch_argmax_rows(c, g->logits, g->tok, g->out, g->pos, rows, g->V, g->Vp, g->cap, advance_pos, st);
 }
 
@@ -150,6 +163,12 @@ int tb_decoder_create(TbDecoder** out, int V, int D, int H, int L, int F, int ma
     TB_TRY(dalloc(g, &g->x, N * D)); TB_TRY(dalloc(g, &g->x2, N * D)); TB_TRY(dalloc(g, &g->qkv, N * 3 * D));
     TB_TRY(dalloc(g, &g->gu, N * 2 * F)); TB_TRY(dalloc(g, &g->r, N)); TB_TRY(dalloc(g, &g->xl, S * D));
     TB_TRY(dalloc(g, &g->logits, S * g->Vp)); TB_TRY(dalloc(g, &g->qdec, S * D));
+    g->fused_head = getenv("TB_NO_FUSED_LMHEAD") == nullptr && lmhead_argmax_supported(g->ctx, (int)S, V, D);
+    if (g->fused_head) {
+        const size_t n = (size_t)lmhead_argmax_ctas(g->ctx, (int)S, V, D) * 64;
+        TB_TRY(dalloc(g, &g->head_val, n)); TB_TRY(dalloc(g, &g->head_idx, n));
+        TB_TRY(dalloc(g, &g->head_ticket, 1)); TB_CUDA(cudaMemset(g->head_ticket, 0, sizeof(unsigned int)));
+    }
     TB_TRY(dalloc(g, &g->n, N * D)); TB_TRY(dalloc(g, &g->att, N * D)); TB_TRY(dalloc(g, &g->h, N * F));
     TB_TRY(dalloc(g, &g->Q, N * D));
     TB_TRY(dalloc(g, &g->ids, N)); TB_TRY(dalloc(g, &g->tok, S)); TB_TRY(dalloc(g, &g->out, N));
@@ -268,8 +287,12 @@ int tb_decoder_read_tokens(TbDecoder* g, uint32_t* h_out, int count) {
     return 0;
 }
 
-// Logits [S, V] of the most recent step (for parity tests).
+// Logits [S, V] of the most recent step (for parity tests).  The fused head never stores them:
+// they are formed here, on request, from the step's normalised hidden states.
 int tb_decoder_read_logits(TbDecoder* g, float* h_logits) {
+    TB_CHECK(g->head_rows > 0, "tb_decoder_read_logits: no step has run yet");
+    if (g->fused_head) TB_TRY(head_logits(g, g->head_rows));
+    TB_CUDA(cudaStreamSynchronize(g->stream));
     TB_TRY(check_device_error(g->ctx, g->stream));
     std::vector<float> tmp((size_t)g->S * g->Vp);
     TB_CUDA(cudaMemcpy(tmp.data(), g->logits, tmp.size() * 4, cudaMemcpyDeviceToHost));

@@ -40,6 +40,7 @@ SIGNATURES = {
     "tb_attention_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
+    "tb_lmhead_argmax_bf16": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i64, _i, _vp]),
     "tb_decoder_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "tb_decoder_destroy": (_i, [_vp]),
     "tb_decoder_total_scalars": (_i64, [_vp]),
@@ -183,6 +184,16 @@ def attention_fwd(Q, K, V, att, lse, B, H, T, hd, scale):
 def attention_bwd(Q, K, V, att, datt, lse, delta, dQ, dK, dV, B, H, T, hd, scale):
     check(load().tb_attention_bwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(att), _ptr(datt), _ptr(lse), _ptr(delta),
                                   _ptr(dQ), _ptr(dK), _ptr(dV), B, H, T, hd, scale, _stream()))
+
+
+def lmhead_argmax_bf16(x16, e16, tok, logits=None, ld_logits=0, table_is_stable=False):
+    """tok[s] = argmax_v <x16[s], e16[v]> (bf16 device tensors [S, K], [V, K]; tok int32/uint32 [S]);
+    logits: optional float32 [S, ld_logits] that receives the products; table_is_stable: e16 is not
+    being written by earlier work of the stream (the kernel may then start reading it early)."""
+    S, K = x16.shape
+    V = e16.shape[0]
+    check(load().tb_lmhead_argmax_bf16(_ptr(x16), _ptr(e16), S, V, K, _ptr(tok), _ptr(logits), ld_logits,
+                                       1 if table_is_stable else 0, _stream()))
 
 
 def pack_bf16(src, dst, rows, cols, ld_src, ld_dst, batch=1, s_src=0, s_dst=0):

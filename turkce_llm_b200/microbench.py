@@ -3,6 +3,7 @@
     python -m turkce_llm_b200.microbench gemm M N K kind [iters] [out=f32|bf16] [tile_n] [splits]
     python -m turkce_llm_b200.microbench attention B H T hd [iters]
     python -m turkce_llm_b200.microbench decode S prompt_len new_tokens      (33.49M-parameter model)
+    python -m turkce_llm_b200.microbench lmhead S [V] [K] [iters] [copies]   (decode LM head, fused argmax)
 
 kind: 0 = NN, 1 = NT, 2 = TN.  Prints the mean device time per launch (CUDA events) and the
 algorithmic throughput.
@@ -12,6 +13,29 @@ import sys
 import torch
 
 from . import lib
+
+
+def graph_time_us(run, iters, replays=5):
+    """Device time per call with the host out of the picture: `iters` calls captured into one CUDA
+    graph on a side stream, the graph replayed and timed with events (mean over the replays)."""
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(st):
+        run(0)                                   # everything lazily set up before the capture
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(iters):
+                run(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (iters * replays)
 
 
 def gemm(M, N, K, kind, iters=20, out="f32", tile_n=0, splits=1):
@@ -42,6 +66,8 @@ def gemm(M, N, K, kind, iters=20, out="f32", tile_n=0, splits=1):
         run()
     prof = lib.profile_end(torch.cuda.current_stream().cuda_stream)
     kus = sum(v["ms"] for k, v in prof.items() if k.startswith("gemm_")) * 1e3 / iters
+    gus = graph_time_us(lambda i: run(), iters)
+    print("  in a CUDA graph (no host launch cost): %.2f us per call = %.1f TFLOP/s" % (gus, 2.0 * M * N * K / gus / 1e6))
     a_bytes, b_bytes = 2.0 * M * K, 2.0 * K * N
     c_bytes = M * N * (4.0 if out == "f32" else 2.0)
     print("gemm kind=%d %dx%dx%d out=%s tile_n=%d splits=%d: %.2f us per call, kernel %.2f us = %.1f TFLOP/s, "
@@ -117,6 +143,41 @@ def decode(S, prompt_len, n_new):
     return pre_ms, step_us
 
 
+def lmhead(S, V=31769, K=384, iters=40, copies=8):
+    """Decode-time LM head [S, K] x [V, K]^T with fused argmax.  `copies` tables are used in turn so
+    that every launch streams its table from HBM (8 x 24.4 MB is larger than the 126 MB L2)."""
+    lib.init(0)
+    X = torch.randn(S, K, device="cuda").to(torch.bfloat16)
+    Es = [(torch.randn(V, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    tok = torch.zeros(S, device="cuda", dtype=torch.int32)
+    for i in range(copies):
+        lib.lmhead_argmax_bf16(X, Es[i], tok)
+    lib.sync_check()
+    want = (X.float() @ Es[copies - 1].float().t()).argmax(1).to(torch.int32)
+    agree = int((want == tok).sum())
+    # back to back on one stream: the next launch's prologue overlaps this launch's tail, as in a decode step
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        lib.lmhead_argmax_bf16(X, Es[i % copies], tok)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    lib.profile_begin()
+    for i in range(iters):
+        lib.lmhead_argmax_bf16(X, Es[i % copies], tok)
+    prof = lib.profile_end(torch.cuda.current_stream().cuda_stream)
+    kus = prof["lmhead_argmax"]["ms"] * 1e3 / iters
+    nbytes = 2.0 * V * K + 2.0 * S * K
+    gus = graph_time_us(lambda i: lib.lmhead_argmax_bf16(X, Es[i % copies], tok), iters)
+    sus = graph_time_us(lambda i: lib.lmhead_argmax_bf16(X, Es[i % copies], tok, table_is_stable=True), iters)
+    print("lmhead S=%d V=%d K=%d: in a CUDA graph %.2f us per call = %.0f GB/s of table+input bytes "
+          "(%.2f us = %.0f GB/s when the table may be read before the previous kernel ends); eager %.2f us per call, "
+          "events around each launch %.2f us; tokens agree with torch on %d of %d"
+          % (S, V, K, gus, nbytes / gus / 1e3, sus, nbytes / sus / 1e3, us, kus, agree, S), flush=True)
+    return gus
+
+
 def main(argv):
     if len(argv) >= 5 and argv[0] == "gemm":
         M, N, K, kind = (int(x) for x in argv[1:5])
@@ -125,6 +186,8 @@ def main(argv):
         tile_n = int(argv[7]) if len(argv) > 7 else 0
         splits = int(argv[8]) if len(argv) > 8 else 1
         gemm(M, N, K, kind, iters, out, tile_n, splits)
+    elif len(argv) >= 2 and argv[0] == "lmhead":
+        lmhead(*(int(x) for x in argv[1:6]))
     elif len(argv) >= 4 and argv[0] == "decode":
         decode(int(argv[1]), int(argv[2]), int(argv[3]))
     elif len(argv) >= 5 and argv[0] == "attention":
