@@ -125,13 +125,9 @@ int tb_lmhead_argmax_bf16(const void* d_X, const void* d_E, int n_seqs, int V, i
              "tb_lmhead_argmax_bf16: needs 1 <= S <= 64 and K a multiple of 64 small enough for one slice of E per SM "
              "(got S=%d V=%d K=%d); use tb_gemm_bf16 for other shapes", n_seqs, V, K);
     TB_CHECK(d_logits == nullptr || ld_logits >= V, "tb_lmhead_argmax_bf16: ld_logits < V");
-    const size_t n = (size_t)lmhead_argmax_ctas(ctx, n_seqs, V, K) * 64;
-    TB_TRY(ensure_scratch(ctx, n * 8));
-    float* val = static_cast<float*>(ctx->scratch);
-    uint32_t* idx = reinterpret_cast<uint32_t*>(val + n);
     return launch_lmhead_argmax(ctx, static_cast<const bf16*>(d_X), static_cast<const bf16*>(d_E), n_seqs, V, K,
-                                table_is_stable != 0,
-                                val, idx, ctx->d_tickets, d_tok, nullptr, nullptr, 0, 0, d_logits, ld_logits, S(stream));
+                                table_is_stable != 0, ctx->d_best, ctx->d_tickets, d_tok, nullptr, nullptr, 0, 0,
+                                d_logits, ld_logits, S(stream));
 }
 
 int tb_gemm_bf16(int kind, const void* d_A, const void* d_B, int M, int N, int K,

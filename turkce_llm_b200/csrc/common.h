@@ -53,6 +53,7 @@ struct DeviceCtx {
     int* d_err = nullptr;
     // device error word written by kernels whose bounded waits ran out
     unsigned int* d_tickets = nullptr;   // 32 zeroed words behind the error word, for single-launch tickets
+    unsigned long long* d_best = nullptr; // 64 zeroed words for the fused LM head's packed maxima
     void* scratch = nullptr;       // growable scratch (operand packing, split-K partials)
     size_t scratch_bytes = 0;
     long long launches = 0;        // kernels launched by this library on this device
@@ -139,16 +140,16 @@ int launch_split3_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, in
                       long long stride_dst, cudaStream_t stream);
 // float32 [rows, cols] (ld) -> bf16 [rows, cols] (ld_out), batched
 // Decode-time LM head with fused greedy choice (lmhead_decode.cu): tok[s] = argmax_v <X[s,:], E[v,:]>,
-// S <= 64 rows of X [S, K] bf16, E [V, K] bf16; part_val/part_idx hold lmhead_argmax_ctas() * 64 entries,
-// ticket is one zeroed word that no concurrent launch shares.  table_is_stable: E is not written by
+// S <= 64 rows of X [S, K] bf16, E [V, K] bf16; best (64 words) and ticket (1 word) are zeroed device
+// memory that no concurrent launch shares (the kernel leaves them zero).  table_is_stable: E is not written by
 // earlier work of the stream, so its loads may start before that work has finished.
 // Also stores the token as out[s, state[1]] and advances state = {position, generated} like launch_argmax_rows
 // (out and state may be NULL).  logits (optional, [S, ld_logits] float32) receives the full products.
 bool lmhead_argmax_supported(const DeviceCtx* ctx, int S, int V, int K);
 int lmhead_argmax_ctas(const DeviceCtx* ctx, int S, int V, int K);
 int launch_lmhead_argmax(DeviceCtx* ctx, const bf16* X, const bf16* E, int S, int V, int K, bool table_is_stable,
-                         float* part_val, uint32_t* part_idx, unsigned int* ticket, uint32_t* tok, uint32_t* out,
-                         int* state, int out_ld, int advance_pos, float* logits, long long ld_logits, cudaStream_t st);
+                         unsigned long long* best, unsigned int* ticket, uint32_t* tok, uint32_t* out, int* state,
+                         int out_ld, int advance_pos, float* logits, long long ld_logits, cudaStream_t st);
 
 int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int cols, long long ld_src,
                      long long ld_dst, int batch, long long stride_src, long long stride_dst, cudaStream_t stream);

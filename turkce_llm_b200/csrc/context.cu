@@ -41,9 +41,10 @@ int get_ctx(DeviceCtx** out) {
             TB_CHECK(prop.major == 10, "this library is built for sm_100a only; device %d is sm_%d%d", dev, prop.major,
                      prop.minor);
             c->sm_count = prop.multiProcessorCount;
-            TB_CUDA(cudaMalloc(&c->d_err, 64 * sizeof(int)));
-            TB_CUDA(cudaMemset(c->d_err, 0, 64 * sizeof(int)));
+            TB_CUDA(cudaMalloc(&c->d_err, 1024));
+            TB_CUDA(cudaMemset(c->d_err, 0, 1024));
             c->d_tickets = reinterpret_cast<unsigned int*>(c->d_err + 32);
+            c->d_best = reinterpret_cast<unsigned long long*>(c->d_err + 64);
             c->scratch = nullptr;
             c->scratch_bytes = 0;
             c->launches = 0;

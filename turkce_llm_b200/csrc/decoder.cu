@@ -43,7 +43,7 @@ struct TbDecoder {
     uint32_t *ids = nullptr, *tok = nullptr, *out = nullptr;
     int* pos = nullptr;
     bool fused_head = false;                   // LM head with the greedy choice fused (no logits in HBM)
-    float* head_val = nullptr; uint32_t* head_idx = nullptr;   // per-CTA winners of the fused head
+    unsigned long long* head_best = nullptr;   // packed per-sequence maxima of the fused head (zero between launches)
     unsigned int* head_ticket = nullptr;
     int head_rows = 0;                         // rows of g->n the most recent head() normalised
     float *cos_t = nullptr, *sin_t = nullptr;
@@ -107,7 +107,7 @@ int head(TbDecoder* g, const float* src, int rows, int advance_pos) {
     TB_TRY(launch_rmsnorm_fwd(c, src, P32(g, pidx(g->L, 0)), g->n, g->r, rows, g->D, g->eps, st));
     g->head_rows = rows;
     if (g->fused_head)
-        return launch_lmhead_argmax(c, g->n, P16(g, 0), rows, g->V, g->D, true, g->head_val, g->head_idx, g->head_ticket,
+        return launch_lmhead_argmax(c, g->n, P16(g, 0), rows, g->V, g->D, true, g->head_best, g->head_ticket,
                                     g->tok, g->out, g->pos, g->cap, advance_pos, nullptr, 0, st);
     TB_TRY(head_logits(g, rows));
     return launch_argmax_rows(c, g->logits, g->tok, g->out, g->pos, rows, g->V, g->Vp, g->cap, advance_pos, st);
@@ -165,8 +165,7 @@ int tb_decoder_create(TbDecoder** out, int V, int D, int H, int L, int F, int ma
     TB_TRY(dalloc(g, &g->logits, S * g->Vp)); TB_TRY(dalloc(g, &g->qdec, S * D));
     g->fused_head = getenv("TB_NO_FUSED_LMHEAD") == nullptr && lmhead_argmax_supported(g->ctx, (int)S, V, D);
     if (g->fused_head) {
-        const size_t n = (size_t)lmhead_argmax_ctas(g->ctx, (int)S, V, D) * 64;
-        TB_TRY(dalloc(g, &g->head_val, n)); TB_TRY(dalloc(g, &g->head_idx, n));
+        TB_TRY(dalloc(g, &g->head_best, 64)); TB_CUDA(cudaMemset(g->head_best, 0, 64 * sizeof(unsigned long long)));
         TB_TRY(dalloc(g, &g->head_ticket, 1)); TB_CUDA(cudaMemset(g->head_ticket, 0, sizeof(unsigned int)));
     }
     TB_TRY(dalloc(g, &g->n, N * D)); TB_TRY(dalloc(g, &g->att, N * D)); TB_TRY(dalloc(g, &g->h, N * F));

@@ -11,9 +11,10 @@
 // of its TMA loads at once (so every SM has its full share of the table in flight from the first
 // microsecond), multiplies the slice -- as the M = 128 operand -- by the 64 hidden states on the
 // tensor cores (tcgen05, accumulator [128 vocabulary rows x 64 sequences] in TMEM), turns the
-// accumulator through shared memory and scans it per sequence.  Per-CTA winners go to a small
-// buffer; lmhead_pick_kernel combines them (lowest index wins ties, as the unfused argmax does),
-// stores the tokens and advances the decoder's position state.
+// accumulator through shared memory and scans it per sequence.  Each CTA's winners go into one
+// packed 64-bit maximum per sequence in global memory (order-independent: the largest value wins,
+// among equals the lowest index, as the unfused argmax does); the CTA that finishes last (a ticket)
+// publishes the tokens, advances the decoder's position state and clears the maxima.
 #include "common.h"
 #include "ptx.cuh"
 
@@ -33,8 +34,7 @@ constexpr int LH_MAX_KBLOCKS = 64;
 struct LmHeadParams {
     int V, S, kblocks, rows_per_cta, box_rows;
     int early_table;          // the table is not written by earlier kernels of the stream: load it before the fence
-    float* part_val;          // [ctas, 64]
-    uint32_t* part_idx;       // [ctas, 64]
+    unsigned long long* best; // [64] packed (value key, ~index) maxima over the CTAs; zero between launches
     unsigned int* ticket;     // zero between launches
     uint32_t* tok;            // [S]
     uint32_t* out;            // optional [S, out_ld]: generated tokens
@@ -180,6 +180,9 @@ lmhead_argmax_kernel(const __grid_constant__ CUtensorMap tmE, const __grid_const
     __syncthreads();
 
     // ---- this CTA's winners (segments hold ascending row ranges: strict > keeps the lowest row on ties)
+    // go into one packed maximum per sequence: value as an order-preserving key in the high word, the
+    // complemented index in the low word, so the largest value wins and among equals the lowest index
+    // -- whatever order the CTAs arrive in
     if (threadIdx.x < LH_SEQ) {
         const int s = threadIdx.x;
         float best = red_val[s];
@@ -189,8 +192,9 @@ lmhead_argmax_kernel(const __grid_constant__ CUtensorMap tmE, const __grid_const
             const float v = red_val[seg * LH_SEQ + s];
             if (v > best) { best = v; row = red_row[seg * LH_SEQ + s]; }
         }
-        p.part_val[(size_t)blockIdx.x * LH_SEQ + s] = best;
-        p.part_idx[(size_t)blockIdx.x * LH_SEQ + s] = (uint32_t)row0 + row;
+        const uint32_t b = __float_as_uint(best + 0.0f);                       // -0 -> +0
+        const uint32_t key = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+        atomicMax(p.best + s, ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - ((uint32_t)row0 + row)));
         __threadfence();
     }
     __syncthreads();
@@ -203,43 +207,17 @@ lmhead_argmax_kernel(const __grid_constant__ CUtensorMap tmE, const __grid_const
     if (!*is_last) return;
     __threadfence();
 
-    // ---- the last CTA to finish picks per sequence over all CTAs' winners (lowest index on ties)
-    {
-        const int s = threadIdx.x & (LH_SEQ - 1), sub = threadIdx.x >> 6;      // 4 threads per sequence
-        constexpr int PER = 40;                                                 // covers 160 CTAs without a loop
-        const int ctas = (int)gridDim.x;
-        float best = -3.0e38f;
-        uint32_t idx = 0xffffffffu;
-        for (int base = 0; base < ctas; base += 4 * PER) {
-            float v[PER];
-            uint32_t ix[PER];
-#pragma unroll
-            for (int j = 0; j < PER; ++j) {
-                const int c = base + 4 * j + sub;
-                const bool in = c < ctas;
-                v[j] = in ? __ldcg(p.part_val + (size_t)c * LH_SEQ + s) : -3.0e38f;
-                ix[j] = in ? __ldcg(p.part_idx + (size_t)c * LH_SEQ + s) : 0xffffffffu;
-            }
-#pragma unroll
-            for (int j = 0; j < PER; ++j)
-                if (v[j] > best || (v[j] == best && ix[j] < idx)) { best = v[j]; idx = ix[j]; }
-        }
-        red_val[sub * LH_SEQ + s] = best;
-        red_row[sub * LH_SEQ + s] = idx;
-    }
-    __syncthreads();
+    // ---- the last CTA to finish publishes the choices and clears the maxima for the next launch
     const int generated = p.state != nullptr ? p.state[1] : 0;
-    if (threadIdx.x < p.S) {
+    if (threadIdx.x < LH_SEQ) {
         const int s = threadIdx.x;
-        float best = red_val[s];
-        uint32_t idx = red_row[s];
-        for (int sub = 1; sub < 4; ++sub) {
-            const float v = red_val[sub * LH_SEQ + s];
-            const uint32_t i = red_row[sub * LH_SEQ + s];
-            if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+        const unsigned long long packed = __ldcg(p.best + s);
+        p.best[s] = 0ull;
+        if (s < p.S) {
+            const uint32_t idx = 0xffffffffu - (uint32_t)(packed & 0xffffffffull);
+            p.tok[s] = idx;
+            if (p.out != nullptr) p.out[(long long)s * p.out_ld + generated] = idx;
         }
-        p.tok[s] = idx;
-        if (p.out != nullptr) p.out[(long long)s * p.out_ld + generated] = idx;
     }
     __syncthreads();
     if (threadIdx.x == 0 && p.state != nullptr) {
@@ -289,8 +267,8 @@ int lmhead_argmax_ctas(const DeviceCtx* ctx, int S, int V, int K) {
 }
 
 int launch_lmhead_argmax(DeviceCtx* ctx, const bf16* X, const bf16* E, int S, int V, int K, bool table_is_stable,
-                         float* part_val, uint32_t* part_idx, unsigned int* ticket, uint32_t* tok, uint32_t* out,
-                         int* state, int out_ld, int advance_pos, float* logits, long long ld_logits, cudaStream_t st) {
+                         unsigned long long* best, unsigned int* ticket, uint32_t* tok, uint32_t* out, int* state,
+                         int out_ld, int advance_pos, float* logits, long long ld_logits, cudaStream_t st) {
     LmHeadPlan pl;
     TB_CHECK(plan(ctx, S, V, K, &pl), "fused LM head: unsupported shape S=%d V=%d K=%d", S, V, K);
     CUtensorMap tmE, tmX;
@@ -299,7 +277,7 @@ int launch_lmhead_argmax(DeviceCtx* ctx, const bf16* X, const bf16* E, int S, in
     LmHeadParams p;
     p.V = V; p.S = S; p.kblocks = pl.kblocks; p.rows_per_cta = pl.rows_per_cta; p.box_rows = pl.box_rows;
     p.early_table = table_is_stable ? 1 : 0;
-    p.part_val = part_val; p.part_idx = part_idx; p.ticket = ticket; p.tok = tok; p.out = out; p.state = state;
+    p.best = best; p.ticket = ticket; p.tok = tok; p.out = out; p.state = state;
     p.out_ld = out_ld; p.advance_pos = advance_pos;
     p.logits = logits; p.ld_logits = ld_logits; p.err = ctx->d_err;
     static bool attr_set[64] = {false};
