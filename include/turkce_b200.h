@@ -131,6 +131,14 @@ int tb_gemm_bf16_splitk_static(int kind, const void* d_A, const void* d_B, int M
 int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld_src, int64_t ld_dst,
                  int batch, int64_t stride_src, int64_t stride_dst, void* stream);
 
+/* Gate|up projection of the SwiGLU feed-forward with the activation fused into the GEMM epilogue:
+ * [g | u] = X[M,K] . W[K,2F] + bias[2F] (gate columns [0,F), up columns [F,2F)), H[M,F] = silu(g) * u.
+ * Replaces bf16_gemm_bias (model/gpu_train.c:364) followed by k_swiglu_fwd (cuda/train_kernels.cu:695-707;
+ * CPU definition model/feedforward.c:9-14) without the float32 [M,2F] projection in HBM.  X, W bf16 row-major;
+ * H bf16 [M,F]; GU (optional, bf16 [M,2F]) keeps g and u for the backward pass.  F must be a multiple of 64. */
+int tb_gemm_swiglu_bf16(const void* d_X, const void* d_W, const float* d_bias, int M, int F, int K, void* d_H,
+                        void* d_GU, void* stream);
+
 /* Decode-time LM head with the greedy choice fused: d_tok[s] = argmax_v <X[s,:], E[v,:]> (lowest index
  * on ties) for 1 <= S <= 64 rows of X [S, K] bf16 against the tied embedding table E [V, K] bf16, K a
  * multiple of 64.  The [S, V] logits (lm_forward's last rows, model/lm_model.c:72-81, whose argmax

@@ -308,3 +308,40 @@ def test_rejects_bad_arguments(tb):
         tb.gemm_bf16(0, A, A, 0, 8, 8, 8, 8, C32=C, ldc32=8)       # empty problem
     with pytest.raises(tb.TbError):
         tb.gemm_f32(0, C, C, C, 8, 8, 8, 8, 8, 8, precision=7)             # unknown precision mode
+
+
+@pytest.mark.parametrize("shape", [(8192, 1024, 384), (200, 64, 72), (64, 128, 384), (333, 192, 96)])
+def test_gemm_swiglu_epilogue(tb, oracle, shape):
+    """tb_gemm_swiglu_bf16 against the oracle's two steps: the BF16-mode gate|up projection with bias
+    (bf16_gemm_bias) and swiglu_fwd on it.  h and the kept gate|up are bf16, so the bound is the BF16
+    mode's plus one bf16 rounding of the result."""
+    import torch
+    from oracle import pyoracle
+    from turkce_llm_b200 import lib
+    M, F, K = shape
+    rng = np.random.default_rng(21)
+    X = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, 2 * F)) * 0.05).astype(np.float32)
+    bias = (rng.standard_normal(2 * F) * 0.1).astype(np.float32)
+    gu_want = oracle.gemm_bias(X, W, bias, None, mode=pyoracle.BF16)
+    h_want = oracle.swiglu_fwd(gu_want)
+    x16 = torch.from_numpy(X).cuda().to(torch.bfloat16)
+    w16 = torch.from_numpy(W).cuda().to(torch.bfloat16)
+    b = torch.from_numpy(bias).cuda()
+    h16 = torch.full((M, F), 7.0, device="cuda", dtype=torch.bfloat16)
+    gu16 = torch.full((M, 2 * F), 7.0, device="cuda", dtype=torch.bfloat16)
+    lib.gemm_swiglu_bf16(x16, w16, b, h16, gu16)
+    h_only = torch.full((M, F), 7.0, device="cuda", dtype=torch.bfloat16)
+    lib.gemm_swiglu_bf16(x16, w16, b, h_only, None)
+    lib.sync_check()
+    assert rel_to_maxabs(gu16.float().cpu().numpy(), gu_want) <= 2e-2
+    assert rel_to_maxabs(h16.float().cpu().numpy(), h_want) <= 2e-2
+    assert torch.equal(h16, h_only)
+    # bit-for-bit the same as the unfused route on the device: float32 projection, then bf16 SwiGLU of it
+    gu32 = torch.empty(M, 2 * F, device="cuda")
+    lib.gemm_bf16(0, x16, w16, M, 2 * F, K, K, 2 * F, C32=gu32, ldc32=2 * F, bias=b, splits=1)
+    lib.sync_check()
+    g, u = gu32[:, :F], gu32[:, F:]
+    assert torch.equal(gu16, gu32.to(torch.bfloat16))
+    h_ref = (g * (1.0 / (1.0 + torch.exp(-g))) * u)
+    assert rel_to_maxabs(h16.float().cpu().numpy(), h_ref.cpu().numpy()) <= 1e-2

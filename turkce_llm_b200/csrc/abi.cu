@@ -116,6 +116,21 @@ int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld
                             stride_dst, S(stream));
 }
 
+int tb_gemm_swiglu_bf16(const void* d_X, const void* d_W, const float* d_bias, int M, int F, int K, void* d_H,
+                        void* d_GU, void* stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    TB_CHECK(d_X && d_W && d_H, "tb_gemm_swiglu_bf16: NULL operand");
+    TB_CHECK(M > 0 && K > 0 && F > 0 && F % 64 == 0 && K % 8 == 0,
+             "tb_gemm_swiglu_bf16: d_ff must be a multiple of 64 and K a multiple of 8 (got F=%d K=%d)", F, K);
+    GemmArgs a;
+    a.kind = GEMM_NN; a.A = d_X; a.B = d_W; a.M = M; a.N = 2 * F; a.K = K; a.lda = K; a.ldb = 2 * F;
+    a.bias = d_bias; a.splits = 1;
+    a.swiglu_h = static_cast<bf16*>(d_H); a.ldh = F;
+    a.swiglu_gu = static_cast<bf16*>(d_GU); a.ldgu = 2 * F;
+    return launch_gemm_bf16(ctx, a, S(stream));
+}
+
 int tb_lmhead_argmax_bf16(const void* d_X, const void* d_E, int n_seqs, int V, int K, uint32_t* d_tok, float* d_logits,
                           int64_t ld_logits, int table_is_stable, void* stream) {
     DeviceCtx* ctx;

@@ -104,6 +104,12 @@ struct GemmArgs {
     int bn = 0;                             // 0 = choose tile width (64, 128 or 192)
     bool tf32 = false;                      // operands are float32 in memory and enter the tensor cores as tf32
     bool pad_cols_writable = false;         // columns N .. round_up(N, 16 bytes) of each output row are padding
+    // Fused SwiGLU epilogue (kind NN, N = 2F with gate columns [0,F) and up columns [F,2F), F % 64 == 0):
+    // h[M,F] = silu(g) * u with g, u = the product (+bias) -- the activation the reference computes in
+    // k_swiglu_fwd from the stored projection (cuda/train_kernels.cu:695-707).  Each tile pairs 64 gate
+    // columns with their 64 up columns.  swiglu_gu (optional, bf16 [M,2F]) keeps g and u for the backward pass.
+    bf16* swiglu_h = nullptr;  long long ldh = 0;
+    bf16* swiglu_gu = nullptr; long long ldgu = 0;
 };
 
 int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream);

@@ -87,8 +87,15 @@ int layer_tail(TbDecoder* g, int l, int rows) {
     const int D = g->D, F = g->F;
     TB_TRY(linear(g, g->att, P16(g, pidx(l, PK_WO)), P32(g, pidx(l, PK_BO)), g->x, g->x2, rows, D, D));
     TB_TRY(launch_rmsnorm_fwd(c, g->x2, P32(g, pidx(l, PK_FFN_NORM)), g->n, g->r, rows, D, g->eps, st));
-    TB_TRY(linear(g, g->n, P16(g, pidx(l, PK_WGU)), P32(g, pidx(l, PK_BGU)), nullptr, g->gu, rows, 2 * F, D));
-    TB_TRY(launch_swiglu_fwd(c, g->gu, g->h, rows, F, st));
+    if (F % 64 == 0 && getenv("TB_NO_FUSED_SWIGLU") == nullptr) {
+        GemmArgs s;       // h = silu(gate) * up in the projection's epilogue; gate|up themselves are not kept
+        s.kind = GEMM_NN; s.A = g->n; s.B = P16(g, pidx(l, PK_WGU)); s.M = rows; s.N = 2 * F; s.K = D; s.lda = D;
+        s.ldb = 2 * F; s.bias = P32(g, pidx(l, PK_BGU)); s.splits = 1; s.swiglu_h = g->h; s.ldh = F;
+        TB_TRY(launch_gemm_bf16_ws(c, s, g->splitk_ws, g->splitk_floats, st));
+    } else {
+        TB_TRY(linear(g, g->n, P16(g, pidx(l, PK_WGU)), P32(g, pidx(l, PK_BGU)), nullptr, g->gu, rows, 2 * F, D));
+        TB_TRY(launch_swiglu_fwd(c, g->gu, g->h, rows, F, st));
+    }
     TB_TRY(linear(g, g->h, P16(g, pidx(l, PK_WDOWN)), P32(g, pidx(l, PK_BDOWN)), g->x2, g->x, rows, D, F));
     return 0;
 }

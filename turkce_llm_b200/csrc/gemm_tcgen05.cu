@@ -62,7 +62,10 @@ struct GemmParams {
     const float* residual; long long ldr, strideR;
     float alpha, beta;
     int vec32, vec16, vecr;     // 16-byte (8-byte for bf16) vector access allowed
-    int tma_mode;               // 0: generic epilogue; 1: fp32 tile stores by TMA; 2: bf16 tile stores by TMA
+    int tma_mode;               // 0: generic epilogue; 1: fp32 tile stores by TMA; 2: bf16 tile stores by TMA;
+                                // 3: SwiGLU (tmC = h [M,F] bf16, tmR = gate|up [M,2F] bf16 when keep_gu)
+    int pair_off;               // mode 3: F; tile columns [0,BN/2) are gate columns n0/2.., [BN/2,BN) up columns F + n0/2..
+    int keep_gu;
     int tma_res;                // TMA path: add res_scale * (tile of tmR) -- the residual, or the old C for beta
     float res_scale;
     int bias_vec;               // bias pointer is 16-byte aligned
@@ -175,8 +178,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         tma_load_3d(sB, &tmB, &full_bar[stage], kb * BKE, c.n0, c.z);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / MNW; ++j)
-                            tma_load_3d(sB + j * MN_BOX_BYTES, &tmB, &full_bar[stage], c.n0 + j * MNW, kb * BKE, c.z);
+                        for (int j = 0; j < BN / MNW; ++j) {
+                            int n = c.n0 + j * MNW;
+                            if (p.tma_mode == 3)       // paired tile: first half gate columns, second half their up columns
+                                n = (c.n0 >> 1) + (j < BN / MNW / 2 ? j * MNW : p.pair_off + (j - BN / MNW / 2) * MNW);
+                            tma_load_3d(sB + j * MN_BOX_BYTES, &tmB, &full_bar[stage], n, kb * BKE, c.z);
+                        }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -251,6 +258,68 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int zo = zc / p.c_inner, zi = zc % p.c_inner;
             const int gm0 = c.m0 + q * 32;
             const bool rows_in = gm0 < p.M;
+            if (p.tma_mode == 3) {
+                // SwiGLU: this warp owns 32 rows x 32 hidden units: gate in accumulator columns half*32..,
+                // up in columns BN/2 + half*32..; h = silu(g) * u leaves as bf16, g and u (bf16) on request
+                if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 32);
+                uint32_t gr[32], ur[32];
+                tmem_ld32(t_row, gr);
+                tmem_ld32(t_row + (uint32_t)(BN / 2), ur);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);       // the accumulator is in registers now
+                const int hj0 = (c.n0 >> 1) + half * 32;            // first hidden unit of this warp's chunk
+                float gv[32], uv[32], hv[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) { gv[j] = __uint_as_float(gr[j]); uv[j] = __uint_as_float(ur[j]); }
+                if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        gv[j] += __ldg(p.bias + hj0 + j);
+                        uv[j] += __ldg(p.bias + p.pair_off + hj0 + j);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float sg = 1.0f / (1.0f + expf(-gv[j]));
+                    hv[j] = gv[j] * sg * uv[j];
+                }
+                if (lane == 0) tma_store_wait_read<0>();            // the previous tile's stores have left the buffers
+                __syncwarp();
+                auto stage_bf16 = [&](uint8_t* base, const float (&o)[32]) {
+                    uint8_t* orow = base + lane * 64;               // 32 x 64 B, 64B swizzle
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint4 pk;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * j + 0], o[8 * j + 1]);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * j + 2], o[8 * j + 3]);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * j + 4], o[8 * j + 5]);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * j + 6], o[8 * j + 7]);
+                        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(orow + ((j ^ ((lane >> 1) & 3)) << 4)) = pk;
+                    }
+                };
+                stage_bf16(obuf, hv);
+                if (p.keep_gu) { stage_bf16(obuf + 4096, gv); stage_bf16(rbuf, uv); }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (rows_in) {
+                        tma_store_4d(&tmC, obuf, hj0, gm0, 0, 0);
+                        if (p.keep_gu) {
+                            tma_store_4d(&tmR, obuf + 4096, hj0, gm0, 0, 0);
+                            tma_store_4d(&tmR, rbuf, p.pair_off + hj0, gm0, 0, 0);
+                        }
+                    }
+                    tma_store_commit();
+                }
+                ++it;
+                continue;
+            }
             const int col0 = c.n0 + half * (BN / 2);
             if (p.tma_res && lane == 0 && rows_in && col0 < p.N) {
                 mbar_expect_tx(rbar, 4096);
@@ -625,6 +694,7 @@ static int make_map_out(CUtensorMap* map, const void* ptr, int elem_bytes, long 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
+    if (a.swiglu_h) return 128;              // the paired gate/up tile
     if (a.bn == 64 || a.bn == 128 || a.bn == 192) return a.bn;
     if (a.N <= 64) return 64;
     const long long mt = (a.M + BM - 1) / BM;
@@ -684,7 +754,15 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
 static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, float* ws, cudaStream_t stream) {
     TB_CHECK(a.M > 0 && a.N > 0 && a.K > 0 && a.batch > 0, "GEMM dims must be positive (M=%d N=%d K=%d batch=%d)",
              a.M, a.N, a.K, a.batch);
-    TB_CHECK(a.A && a.B && (a.C32 || a.C16), "GEMM needs A, B and at least one output");
+    TB_CHECK(a.A && a.B && (a.C32 || a.C16 || a.swiglu_h), "GEMM needs A, B and at least one output");
+    const bool swiglu = a.swiglu_h != nullptr;
+    if (swiglu) {
+        TB_CHECK(a.kind == GEMM_NN && !a.tf32 && a.batch == 1 && bn == 128 && splits == 1 && a.N % 128 == 0 &&
+                     a.residual == nullptr && a.alpha == 1.0f && a.beta == 0.0f && !a.C32 && !a.C16 && a.causal == CAUSAL_NONE,
+                 "fused SwiGLU GEMM: needs a plain NN bf16 product with N = 2F, F a multiple of 64 (got N=%d)", a.N);
+        TB_CHECK(aligned16(a.swiglu_h) && a.ldh % 8 == 0 && (!a.swiglu_gu || (aligned16(a.swiglu_gu) && a.ldgu % 8 == 0)),
+                 "fused SwiGLU GEMM: outputs must be 16-byte aligned with leading dimensions that are multiples of 8");
+    }
     const int a_mn = (a.kind == GEMM_TN) ? 1 : 0;
     const int b_mn = (a.kind == GEMM_NT) ? 0 : 1;
     CUtensorMap tmA, tmB;
@@ -726,8 +804,15 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     memset(&tmC, 0, sizeof(tmC));
     memset(&tmR, 0, sizeof(tmR));
     p.tma_mode = 0; p.tma_res = 0; p.res_scale = 0.0f;
+    p.pair_off = 0; p.keep_gu = 0;
     p.bias_vec = p.bias && aligned16(p.bias);
-    {
+    if (swiglu) {
+        const int F = a.N / 2;
+        TB_TRY(make_map_out(&tmC, a.swiglu_h, 2, F, a.M, a.ldh, 1, 0, 1, 0));
+        if (a.swiglu_gu) TB_TRY(make_map_out(&tmR, a.swiglu_gu, 2, a.N, a.M, a.ldgu, 1, 0, 1, 0));
+        else tmR = tmC;
+        p.tma_mode = 3; p.pair_off = F; p.keep_gu = a.swiglu_gu ? 1 : 0;
+    } else {
         const bool one_out = (p.C32 != nullptr) != (p.C16 != nullptr);
         const int es = p.C32 ? 4 : 2;
         const void* cptr = p.C32 ? (const void*)p.C32 : (const void*)p.C16;
@@ -760,15 +845,16 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     {
         // algorithmic work: the causal products touch only the lower triangle (half the MACs)
         const double macs = (double)a.M * a.N * a.K * a.batch * (a.causal != CAUSAL_NONE ? 0.5 : 1.0);
-        const double out_bytes = (double)a.M * a.N * a.batch * ((a.C32 ? 4.0 : 0.0) + (a.C16 ? 2.0 : 0.0)) *
-                                 (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);
+        const double out_bytes = swiglu ? (double)a.M * a.N * (a.swiglu_gu ? 3.0 : 1.0)
+                                        : (double)a.M * a.N * a.batch * ((a.C32 ? 4.0 : 0.0) + (a.C16 ? 2.0 : 0.0)) *
+                                              (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);
         const double in_bytes = 2.0 * a.batch * ((double)a.M * a.K + (double)a.K * a.N) *
                                 (a.causal == CAUSAL_K_PREFIX || a.causal == CAUSAL_K_SUFFIX ? 0.75 : 1.0);
         if (ctx->prof_on) {
             char tag[128];
             static const char* kn[3] = {"NN", "NT", "TN"};
-            snprintf(tag, sizeof(tag), "%s:%s:%dx%dx%d:b%d:s%d:c%d:bn%d", a.tf32 ? "gemm_tf32" : "gemm_bf16",
-                     kn[(int)a.kind], a.M, a.N, a.K, a.batch, splits, (int)a.causal, bn);
+            snprintf(tag, sizeof(tag), "%s:%s:%dx%dx%d:b%d:s%d:c%d:bn%d%s", a.tf32 ? "gemm_tf32" : "gemm_bf16",
+                     kn[(int)a.kind], a.M, a.N, a.K, a.batch, splits, (int)a.causal, bn, swiglu ? ":swiglu" : "");
             prof_mark(ctx, prof_intern(tag), 2.0 * macs, in_bytes + out_bytes, stream);
         }
     }
@@ -806,7 +892,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
 int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual || a.c_inner > 1) splits = 1;
+    if (a.residual || a.c_inner > 1 || a.swiglu_h) splits = 1;
     float* ws = nullptr;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N * sizeof(float);
@@ -820,7 +906,7 @@ int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, siz
                         cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual || a.c_inner > 1) splits = 1;
+    if (a.residual || a.c_inner > 1 || a.swiglu_h) splits = 1;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N;
         TB_CHECK(workspace != nullptr && workspace_floats >= need,

@@ -716,7 +716,25 @@ int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F,
 }
 
 // dg = dh*u*(sg + g*sg*(1-sg)),  du = dh*g*sg
-__global__ void swiglu_bwd_kernel(const float* __restrict__ gu, const float* __restrict__ dh,
+template <typename TG> struct Load4;
+template <> struct Load4<float> {
+    static __device__ __forceinline__ void at(const float* p, float (&o)[4]) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    }
+};
+template <> struct Load4<bf16> {
+    static __device__ __forceinline__ void at(const bf16* p, float (&o)[4]) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+        o[0] = __low2float(lo); o[1] = __high2float(lo); o[2] = __low2float(hi); o[3] = __high2float(hi);
+    }
+};
+
+// TG = float: the stored projection; TG = bf16: the copy the fused SwiGLU GEMM epilogue keeps
+template <typename TG>
+__global__ void swiglu_bwd_kernel(const TG* __restrict__ gu, const float* __restrict__ dh,
                                   bf16* __restrict__ dgu, long long total4, int F) {
     pdl_wait();
     pdl_launch_dependents();
@@ -725,10 +743,11 @@ __global__ void swiglu_bwd_kernel(const float* __restrict__ gu, const float* __r
          i += (long long)gridDim.x * blockDim.x) {
         const long long n = i / F4;
         const int j = (int)(i % F4) << 2;
-        const float4 g = *reinterpret_cast<const float4*>(gu + n * 2 * F + j);
-        const float4 u = *reinterpret_cast<const float4*>(gu + n * 2 * F + F + j);
+        float gg[4], uu[4];
+        Load4<TG>::at(gu + n * 2 * F + j, gg);
+        Load4<TG>::at(gu + n * 2 * F + F + j, uu);
         const float4 d4 = *reinterpret_cast<const float4*>(dh + n * F + j);
-        const float gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+        const float dd[4] = {d4.x, d4.y, d4.z, d4.w};
         float og[4], ou[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -751,7 +770,16 @@ int launch_swiglu_bwd(DeviceCtx* ctx, const float* gu, const float* dh, bf16* dg
     TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
     const long long total = (long long)rows * (F / 4);
     prof_mark(ctx, "swiglu_bwd", 0.0, 0.0, st);
-    TB_CUDA(launch_kernel(swiglu_bwd_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, dh, dgu, total, F));
+    TB_CUDA(launch_kernel(swiglu_bwd_kernel<float>, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, dh, dgu, total, F));
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
+int launch_swiglu_bwd_bf16(DeviceCtx* ctx, const bf16* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t st) {
+    TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
+    const long long total = (long long)rows * (F / 4);
+    prof_mark(ctx, "swiglu_bwd", 0.0, 0.0, st);
+    TB_CUDA(launch_kernel(swiglu_bwd_kernel<bf16>, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, dh, dgu, total, F));
     TB_LAUNCHED(ctx);
     return 0;
 }

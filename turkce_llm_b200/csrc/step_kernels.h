@@ -45,6 +45,8 @@ int launch_attn_softmax_bwd(DeviceCtx*, const bf16* P, const float* dP, bf16* dS
 int launch_heads_split(DeviceCtx*, const bf16* dout, bf16* dO, int B, int T, int H, int hd, cudaStream_t);
 int launch_swiglu_fwd(DeviceCtx*, const float* gu, bf16* h, int rows, int F, cudaStream_t);
 int launch_swiglu_bwd(DeviceCtx*, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t);
+// the same with gate|up kept in bf16 by the fused SwiGLU GEMM epilogue
+int launch_swiglu_bwd_bf16(DeviceCtx*, const bf16* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t);
 // logits [rows, ld] fp32 -> loss_rows, dlogits bf16 [rows, ld] = (softmax - onehot) * grad_scale
 int launch_cross_entropy(DeviceCtx*, const float* logits, const uint32_t* targets, float* loss_rows, bf16* dlogits,
                          int rows, int V, long long ld, float grad_scale, cudaStream_t);

@@ -34,7 +34,8 @@ struct LayerActs {
     bf16 *Q, *K, *V, *P, *att;     // P [BH,T,T] only on the unfused attention path
     float* lse;                    // [BH,T] on the fused path
     float* x2;    bf16* n2; float* r2;
-    float* gu;    bf16* h;
+    float* gu;    bf16* h;   // gu: gate|up projection (unfused SwiGLU path)
+    bf16* gu16;              // gate|up in bf16, written by the fused SwiGLU GEMM epilogue
 };
 
 }  // namespace
@@ -85,6 +86,7 @@ struct TbTrainer {
     std::vector<Segment> segments;
     bool graphs_on = true;
     bool fused_attention = true;   // head_dim <= 64: scores stay on chip
+    bool fused_swiglu = true;      // d_ff % 64 == 0: silu(gate) * up formed in the gate|up GEMM's epilogue
     float* att_delta = nullptr;
     bool owns_stream = false;
 };
@@ -178,9 +180,18 @@ int forward(TbTrainer* g, bool want_grad) {
         }
         TB_TRY(linear_fwd(g, a.att, P16(g, pidx(l, PK_WO)), P32(g, pidx(l, PK_BO)), a.x_in, a.x2, nullptr, N, D, D));
         TB_TRY(launch_rmsnorm_fwd(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.n2, a.r2, N, D, g->eps, st));
-        TB_TRY(linear_fwd(g, a.n2, P16(g, pidx(l, PK_WGU)), P32(g, pidx(l, PK_BGU)), nullptr, a.gu, nullptr, N, 2 * F,
-                          D));
-        TB_TRY(launch_swiglu_fwd(c, a.gu, a.h, N, F, st));
+        if (g->fused_swiglu) {
+            // gate|up projection with h = silu(gate) * up formed in the GEMM epilogue; gate|up kept in bf16
+            GemmArgs s;
+            s.kind = GEMM_NN; s.A = a.n2; s.B = P16(g, pidx(l, PK_WGU)); s.M = N; s.N = 2 * F; s.K = D; s.lda = D;
+            s.ldb = 2 * F; s.bias = P32(g, pidx(l, PK_BGU)); s.splits = 1;
+            s.swiglu_h = a.h; s.ldh = F; s.swiglu_gu = a.gu16; s.ldgu = 2 * F;
+            TB_TRY(gemm(g, s));
+        } else {
+            TB_TRY(linear_fwd(g, a.n2, P16(g, pidx(l, PK_WGU)), P32(g, pidx(l, PK_BGU)), nullptr, a.gu, nullptr, N,
+                              2 * F, D));
+            TB_TRY(launch_swiglu_fwd(c, a.gu, a.h, N, F, st));
+        }
         TB_TRY(linear_fwd(g, a.h, P16(g, pidx(l, PK_WDOWN)), P32(g, pidx(l, PK_BDOWN)), a.x2, x_out, nullptr, N, D,
                           F));
     }
@@ -233,7 +244,8 @@ int backward_layer(TbTrainer* g, int l) {
     TB_TRY(linear_dw(g, a.h, g->dres16, G32(g, pidx(l, PK_WDOWN)), N, D, F));
     // (b_down's gradient, the column sum of dres, was produced together with dres)
     TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WDOWN)), g->dh, nullptr, N, D, F));
-    TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->dgu, N, F, st));
+    if (g->fused_swiglu) TB_TRY(launch_swiglu_bwd_bf16(c, a.gu16, g->dh, g->dgu, N, F, st));
+    else TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->dgu, N, F, st));
     TB_TRY(linear_dw(g, a.n2, g->dgu, G32(g, pidx(l, PK_WGU)), N, 2 * F, D));
     TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
     TB_TRY(linear_dx(g, g->dgu, P16(g, pidx(l, PK_WGU)), g->dn, nullptr, N, 2 * F, D));
@@ -426,6 +438,7 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
     }
     g->graphs_on = getenv("TB_NO_GRAPH") == nullptr;
     g->fused_attention = (D / H) <= 64 && getenv("TB_NO_FUSED_ATTENTION") == nullptr;
+    g->fused_swiglu = F % 64 == 0 && getenv("TB_NO_FUSED_SWIGLU") == nullptr;
     g->V = V; g->D = D; g->H = H; g->L = L; g->F = F; g->T = T; g->B = B; g->N = B * T; g->hd = D / H;
     g->Vp = round_up(V, 8);
     g->Tp = round_up(T, 8);
@@ -459,7 +472,10 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         else { a.lse = nullptr; TB_TRY(dalloc(g, &a.P, BHT * Tp)); }
         TB_TRY(dalloc(g, &a.att, N * D));
         TB_TRY(dalloc(g, &a.x2, N * D)); TB_TRY(dalloc(g, &a.n2, N * D)); TB_TRY(dalloc(g, &a.r2, N));
-        TB_TRY(dalloc(g, &a.gu, N * 2 * F)); TB_TRY(dalloc(g, &a.h, N * F));
+        a.gu = nullptr; a.gu16 = nullptr;
+        if (g->fused_swiglu) TB_TRY(dalloc(g, &a.gu16, N * 2 * F));
+        else TB_TRY(dalloc(g, &a.gu, N * 2 * F));
+        TB_TRY(dalloc(g, &a.h, N * F));
     }
     TB_TRY(dalloc(g, &g->x_final, N * D)); TB_TRY(dalloc(g, &g->nf, N * D)); TB_TRY(dalloc(g, &g->rf, N));
     TB_TRY(dalloc(g, &g->logits, N * g->Vp)); TB_TRY(dalloc(g, &g->dlogits, N * g->Vp));

@@ -40,6 +40,7 @@ SIGNATURES = {
     "tb_attention_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
+    "tb_gemm_swiglu_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "tb_lmhead_argmax_bf16": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i64, _i, _vp]),
     "tb_decoder_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "tb_decoder_destroy": (_i, [_vp]),
@@ -184,6 +185,13 @@ def attention_fwd(Q, K, V, att, lse, B, H, T, hd, scale):
 def attention_bwd(Q, K, V, att, datt, lse, delta, dQ, dK, dV, B, H, T, hd, scale):
     check(load().tb_attention_bwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(att), _ptr(datt), _ptr(lse), _ptr(delta),
                                   _ptr(dQ), _ptr(dK), _ptr(dV), B, H, T, hd, scale, _stream()))
+
+
+def gemm_swiglu_bf16(x16, w16, bias, h16, gu16=None):
+    """h16[M,F] = silu(g) * u with [g | u] = x16[M,K] @ w16[K,2F] + bias[2F]; gu16 (optional bf16 [M,2F]) keeps g, u."""
+    M, K = x16.shape
+    F = w16.shape[1] // 2
+    check(load().tb_gemm_swiglu_bf16(_ptr(x16), _ptr(w16), _ptr(bias), M, F, K, _ptr(h16), _ptr(gu16), _stream()))
 
 
 def lmhead_argmax_bf16(x16, e16, tok, logits=None, ld_logits=0, table_is_stable=False):
