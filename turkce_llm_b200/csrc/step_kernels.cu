@@ -176,18 +176,16 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
 
 // Same row math, plus the norm-weight gradient dw[j] += sum_rows dy*x*r without the [rows, cols]
 // temporary: each warp keeps its rows' column sums in registers, the block adds its warps in warp
-// order, writes one partial row, and the block that draws the last ticket adds the partials in
-// block order.  NC = ceil(cols / 32) columns per lane.
+// order and writes one partial row; norm_partial_sum_kernel then adds the partial rows in block
+// order.  NC = ceil(cols / 32) columns per lane.
 template <int NC>
 __global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                       const float* __restrict__ rinv, const float* __restrict__ dy,
-                                      float* __restrict__ dx, bf16* __restrict__ dx16, float* __restrict__ dw,
-                                      float* __restrict__ db, float* __restrict__ partial,
-                                      unsigned int* __restrict__ ticket, int rows, int cols, int accumulate) {
+                                      float* __restrict__ dx, bf16* __restrict__ dx16,
+                                      float* __restrict__ partial, int rows, int cols, int accumulate) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float sh_part[];      // [warps][cols]
-    __shared__ int is_last;
+    extern __shared__ float sh_part[];      // [warps][2 * cols]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wpb = blockDim.x >> 5;
     // every partial row is [norm-weight sums | column sums of dx], 2*cols floats
@@ -238,52 +236,39 @@ __global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* 
         for (int k = 1; k < wpb; ++k) t += sh_part[k * pc + j];
         partial[(long long)blockIdx.x * pc + j] = t;
     }
-    // two-level fixed-order sum of the partial rows: blocks form groups of 32; the block that draws
-    // a group's last ticket adds that group's rows in block order, and the group finisher that
-    // draws the last second-level ticket adds the group sums in group order
-    const unsigned int nb = gridDim.x;
-    const unsigned int group = blockIdx.x >> 5, ngroups = (nb + 31u) >> 5;
-    const unsigned int gsize = min(32u, nb - (group << 5));
-    float* gpartial = partial + (long long)nb * pc;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) is_last = (atomicAdd(&ticket[1 + group], 1u) == gsize - 1u);
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    for (int j = threadIdx.x; j < pc; j += blockDim.x) {
-        float v[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k)
-            v[k] = (unsigned)k < gsize ? __ldcg(&partial[(long long)((group << 5) + k) * pc + j]) : 0.0f;
-        float t = v[0];
-#pragma unroll
-        for (int k = 1; k < 32; ++k) t += v[k];
-        gpartial[(long long)group * pc + j] = t;
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        ticket[1 + group] = 0u;
-        is_last = (atomicAdd(&ticket[0], 1u) == ngroups - 1u);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    for (int j = threadIdx.x; j < pc; j += blockDim.x) {
-        float v[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) v[k] = (unsigned)k < ngroups ? __ldcg(&gpartial[(long long)k * pc + j]) : 0.0f;
-        float t = v[0];
-#pragma unroll
-        for (int k = 1; k < 32; ++k) t += v[k];
-        if (j < cols) dw[j] += t;
-        else if (db) db[j - cols] += t;
-    }
-    if (threadIdx.x == 0) ticket[0] = 0u;
 }
 
-constexpr int kNormBwdBlocks = 1024;     // partial rows of the fused norm-weight gradient
+// dw[j] += sum over the partial rows (block order), db likewise: one block per 32 columns, each
+// warp adds up to 32 consecutive partial rows (all loads in flight at once), warp 0 adds the warps.
+__global__ void norm_partial_sum_kernel(const float* __restrict__ partial, int nb, int pc, int cols,
+                                        float* __restrict__ dw, float* __restrict__ db) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float sh[32][33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int j = blockIdx.x * 32 + lane;
+    const int per = (nb + nw - 1) / nw;              // <= 32 by the launch
+    float v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        const int r = warp * per + k;
+        v[k] = (k < per && r < nb && j < pc) ? __ldcg(&partial[(long long)r * pc + j]) : 0.0f;
+    }
+    float t = v[0];
+#pragma unroll
+    for (int k = 1; k < 32; ++k) t += v[k];
+    sh[warp][lane] = t;
+    __syncthreads();
+    if (warp == 0 && j < pc) {
+        float s = sh[0][lane];
+        for (int k = 1; k < nw; ++k) s += sh[k][lane];
+        if (j < cols) dw[j] += s;
+        else if (db) db[j - cols] += s;
+    }
+}
+
+constexpr int kNormBwdBlocks = 512;      // partial rows of the fused norm-weight gradient
+constexpr int kNormBwdWarps = 16;        // rows in flight per block
 
 size_t rmsnorm_bwd_scratch_floats(int cols) { return 64 + (size_t)(kNormBwdBlocks + 32) * cols * 2; }
 
@@ -291,21 +276,28 @@ int launch_rmsnorm_bwd_dw(DeviceCtx* ctx, const float* x, const float* w, const 
                           float* dx, bf16* dx16, float* dw, float* db, float* scratch, int rows, int cols,
                           int accumulate, cudaStream_t st) {
     TB_CHECK(cols <= 1024, "fused RMSNorm backward supports at most 1024 columns (got %d)", cols);
-    static bool attr_set = false;
-    if (!attr_set && cols > 384) {
-        TB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_dw_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
-        attr_set = true;
+    const int warps = cols <= 384 ? kNormBwdWarps : 8;       // the wide variant holds whole rows in 255 registers
+    const size_t smem = (size_t)warps * 2 * cols * sizeof(float);
+    static bool attr_set[64] = {false};
+    if (!attr_set[ctx->device & 63]) {
+        TB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_dw_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kNormBwdWarps * 2 * 384 * (int)sizeof(float)));
+        TB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_dw_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     8 * 2 * 1024 * (int)sizeof(float)));
+        attr_set[ctx->device & 63] = true;
     }
-    int blocks = (rows + 7) / 8;
+    int blocks = (rows + warps - 1) / warps;
     if (blocks > kNormBwdBlocks) blocks = kNormBwdBlocks;
-    unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch);
     float* partial = scratch + 64;
-    const size_t smem = (size_t)8 * 2 * cols * sizeof(float);
+    const int pc = 2 * cols;
     prof_mark(ctx, "rmsnorm_bwd", 0.0, 0.0, st);
     if (cols <= 384)
-        TB_CUDA(launch_kernel((rmsnorm_bwd_dw_kernel<12>), dim3(blocks), dim3(256), smem, st, x, w, rinv, dy, dx, dx16, dw, db, partial, ticket, rows, cols, accumulate));
+        TB_CUDA(launch_kernel((rmsnorm_bwd_dw_kernel<12>), dim3(blocks), dim3(32 * warps), smem, st, x, w, rinv, dy, dx, dx16, partial, rows, cols, accumulate));
     else
-        TB_CUDA(launch_kernel((rmsnorm_bwd_dw_kernel<32>), dim3(blocks), dim3(256), smem, st, x, w, rinv, dy, dx, dx16, dw, db, partial, ticket, rows, cols, accumulate));
+        TB_CUDA(launch_kernel((rmsnorm_bwd_dw_kernel<32>), dim3(blocks), dim3(32 * warps), smem, st, x, w, rinv, dy, dx, dx16, partial, rows, cols, accumulate));
+    TB_LAUNCHED(ctx);
+    prof_mark(ctx, "rmsnorm_bwd_sum", 0.0, 0.0, st);
+    TB_CUDA(launch_kernel(norm_partial_sum_kernel, dim3((pc + 31) / 32), dim3(32 * ((blocks + 31) / 32)), 0, st, (const float*)partial, blocks, pc, cols, dw, db));
     TB_LAUNCHED(ctx);
     return 0;
 }
