@@ -70,9 +70,10 @@ struct AttFwdParams {
 };
 
 // ------------------------------------------------------------------------------------ forward
-// CTA = 6 warps: TMA producer, MMA issuer (owns TMEM: S 128 columns + O-step 64 columns), four
-// softmax warps (thread = query row).  Two CTAs fit per SM, so one CTA's tensor-core work
-// overlaps the other's exponentials.
+// CTA = 6 warps: TMA producer, MMA issuer (owns TMEM: two score buffers of 64 key columns and two
+// P V buffers of 64 head-dim columns), four softmax warps (thread = query row).  Keys are taken in
+// half blocks of 64 and the steps are software-pipelined: while the softmax warps work on half block
+// i, the tensor core computes the scores of i+1 and P V of i-1.  Two CTAs fit per SM on top of that.
 __global__ void __launch_bounds__(192, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const AttFwdParams p) {
@@ -88,15 +89,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint64_t* bars = reinterpret_cast<uint64_t*>(pad <= 768u ? smem + 7 * TILE_BYTES : smem_raw);
     uint64_t* q_full = bars;          // 1
-    uint64_t* k_full = bars + 1;      // 2
+    uint64_t* k_full = bars + 1;      // 2: K tile of 128 keys in stage s
     uint64_t* v_full = bars + 3;      // 2
     uint64_t* kv_empty = bars + 5;    // 2
-    uint64_t* s_full = bars + 7;
-    uint64_t* s_free = bars + 8;
-    uint64_t* p_full = bars + 9;
-    uint64_t* o_full = bars + 10;
-    uint64_t* o_free = bars + 11;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint64_t* s_full = bars + 7;      // 2: score buffer b holds Q K^T of a 64-key half block
+    uint64_t* s_free = bars + 9;      // 2
+    uint64_t* p_full = bars + 11;     // 2: probability buffer b written
+    uint64_t* o_full = bars + 13;     // 2: P V of a half block landed in output buffer b
+    uint64_t* o_free = bars + 15;     // 2
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,7 +109,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); }
-        mbar_init(s_full, 1); mbar_init(s_free, 4); mbar_init(p_full, 4); mbar_init(o_full, 1); mbar_init(o_free, 4);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); mbar_init(&p_full[i], 4);
+            mbar_init(&o_full[i], 1); mbar_init(&o_free[i], 4);
+        }
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -118,7 +122,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();                 // everything above is independent of earlier kernels' results
+    // TMEM: two score buffers of 64 key columns, two output buffers of 64 head-dim columns
     const uint32_t tS = tmem_base, tO = tmem_base + 128;
+    const int nsub = 2 * nkv;                         // 64-key half blocks
 
     if (warp == 0) {
         if (lane == 0) {
@@ -138,32 +144,42 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc_s = umma_idesc(1u, 0u, 0u, ATT_BM, ATT_BN);     // Q K^T: both K-major
+            // Half blocks of 64 keys, software-pipelined: the scores of half block i+2 are issued as soon
+            // as the softmax warps have drained buffer i&1, so the tensor core works on Q K^T (i+1, i+2)
+            // and P V (i-1) while the softmax of i runs -- no step waits for a full round trip.
+            const uint32_t idesc_s = umma_idesc(1u, 0u, 0u, ATT_BM, 64);         // Q K^T: both K-major
             const uint32_t idesc_o = umma_idesc(1u, 0u, 1u, ATT_BM, ATT_HD);     // P V: V is MN-major
             const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
             bool ok = mbar_wait(q_full, 0, abort_flag);
-            for (int j = 0; j < nkv && ok; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = (uint32_t)((j >> 1) & 1), pj = (uint32_t)(j & 1);
-                if (!mbar_wait(&k_full[s], ph, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(s_free, pj ^ 1u, abort_flag)) { ok = false; break; }
+            auto issue_scores = [&](int i) -> bool {
+                const int j = i >> 1, st = j & 1, b = i & 1;
+                if (b == 0 && !mbar_wait(&k_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
+                if (!mbar_wait(&s_free[b], (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t aK = smem_u32(sK + s * TILE_BYTES);
+                const uint32_t aK = smem_u32(sK + st * TILE_BYTES) + (uint32_t)b * 8192u;    // keys 64b.. of the tile
 #pragma unroll
                 for (int k = 0; k < ATT_HD / 16; ++k)
-                    umma_bf16(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), idesc_s, k > 0 ? 1u : 0u);
-                umma_commit(s_full);
-                if (!mbar_wait(p_full, pj, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(o_free, pj ^ 1u, abort_flag)) { ok = false; break; }
+                    umma_bf16(tS + (uint32_t)(b * 64), kmajor_desc(aQ, k), kmajor_desc(aK, k), idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(&s_full[b]);
+                return true;
+            };
+            if (ok) ok = issue_scores(0);
+            if (ok && nsub > 1) ok = issue_scores(1);
+            for (int i = 0; i < nsub && ok; ++i) {
+                const int j = i >> 1, st = j & 1, b = i & 1;
+                const uint32_t par = (uint32_t)((i >> 1) & 1);
+                if (!mbar_wait(&p_full[b], par, abort_flag)) { ok = false; break; }
+                if (b == 0 && !mbar_wait(&v_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&o_free[b], par ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t aV = smem_u32(sV + s * TILE_BYTES);
+                const uint32_t aV = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < ATT_BN / 16; ++k)
-                    umma_bf16(tO, kmajor_desc(aP + (k >> 2) * TILE_BYTES, k & 3), mnmajor_desc(aV, k, TILE_BYTES),
-                              idesc_o, k > 0 ? 1u : 0u);
-                umma_commit(o_full);
-                umma_commit(&kv_empty[s]);
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tO + (uint32_t)(b * 64), kmajor_desc(aP + b * TILE_BYTES, k),
+                              mnmajor_desc(aV, b * 4 + k, TILE_BYTES), idesc_o, k > 0 ? 1u : 0u);
+                umma_commit(&o_full[b]);
+                if (b == 1) umma_commit(&kv_empty[st]);          // both halves of the K/V tile are consumed
+                if (i + 2 < nsub) ok = issue_scores(i + 2);
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 12); }
         }
@@ -177,74 +193,83 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int d = 0; d < ATT_HD; ++d) O[d] = 0.0f;
         bool ok = true;
-        for (int j = 0; j < nkv && ok; ++j) {
-            const uint32_t pj = (uint32_t)(j & 1);
-            if (!mbar_wait(s_full, pj, abort_flag)) { ok = false; break; }
+        float alpha_prev = 0.0f;                     // rescale factor of the half block whose P V is still due
+        // adds P V of half block i (output buffer i&1) into the running output: O = O * alpha_i + P_i V_i
+        uint32_t va[32], vb[32];                     // one half block's scores (or one P V result) per row
+        auto accumulate = [&](int i, float alpha) -> bool {
+            const int b = i & 1;
+            if (!mbar_wait(&o_full[b], (uint32_t)((i >> 1) & 1), abort_flag)) return false;
             tc_fence_after();
-            const bool diag = (j == qb);
-            const int k0 = j * ATT_BN;
-            // pass 1: row maximum of the allowed scores
+            tmem_ld32(tO + lane_base + (uint32_t)(b * 64), va);
+            tmem_ld32(tO + lane_base + (uint32_t)(b * 64 + 32), vb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                O[e] = O[e] * alpha + __uint_as_float(va[e]);
+                O[32 + e] = O[32 + e] * alpha + __uint_as_float(vb[e]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free[b]);
+            return true;
+        };
+        for (int i = 0; i < nsub && ok; ++i) {
+            const int b = i & 1;
+            if (!mbar_wait(&s_full[b], (uint32_t)((i >> 1) & 1), abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const bool diag = ((i >> 1) == qb);
+            const int k0 = (i >> 1) * ATT_BN + b * 64;
+            const uint32_t ts = tS + lane_base + (uint32_t)(b * 64);
+            // all 64 scores of the row in one TMEM round trip; the registers are reused for the probabilities
+            tmem_ld32(ts, va);
+            tmem_ld32(ts + 32, vb);
+            tmem_ld_wait();
+            const int lim = diag ? qi - k0 : 64;               // columns e <= lim are allowed
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tS + lane_base + c * 32, v);
-                tmem_ld_wait();
-                if (diag) {
-                    const int lim = qi - (k0 + c * 32);        // columns e <= lim are allowed
+            if (diag) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, e <= lim ? __uint_as_float(v[e]) : -INFINITY);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2)
-                        mx = fmaxf(mx, fmaxf(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
+                for (int e = 0; e < 32; ++e) {
+                    mx = fmaxf(mx, e <= lim ? __uint_as_float(va[e]) : -INFINITY);
+                    mx = fmaxf(mx, e + 32 <= lim ? __uint_as_float(vb[e]) : -INFINITY);
                 }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(va[e]), __uint_as_float(vb[e])));
             }
             const float m_new = fmaxf(m, mx * p.scale_log2);
             const float alpha = fast_exp2(m - m_new);        // 0 on the first block (m = -inf)
             l *= alpha;
-            // pass 2: p = 2^(s*c - m), row sum, bf16 P into shared memory (K-major, 128B swizzle)
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tS + lane_base + c * 32, v);
-                tmem_ld_wait();
-                float pv[32];
-                if (diag) {
-                    const int lim = qi - (k0 + c * 32);
+            // p = 2^(s*c - m), row sum, bf16 P into shared memory (K-major, 128B swizzle)
+            float pa[32], pb[32];
+            if (diag) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        pv[e] = e <= lim ? fast_exp2(__uint_as_float(v[e]) * p.scale_log2 - m_new) : 0.0f;
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) pv[e] = fast_exp2(__uint_as_float(v[e]) * p.scale_log2 - m_new);
+                for (int e = 0; e < 32; ++e) {
+                    pa[e] = e <= lim ? fast_exp2(__uint_as_float(va[e]) * p.scale_log2 - m_new) : 0.0f;
+                    pb[e] = e + 32 <= lim ? fast_exp2(__uint_as_float(vb[e]) * p.scale_log2 - m_new) : 0.0f;
                 }
-                float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+            } else {
 #pragma unroll
-                for (int e = 0; e < 32; e += 4) { l0 += pv[e]; l1 += pv[e + 1]; l2 += pv[e + 2]; l3 += pv[e + 3]; }
-                l += (l0 + l1) + (l2 + l3);
-                store_chunk_bf16(sP, r, c, pv);
+                for (int e = 0; e < 32; ++e) {
+                    pa[e] = fast_exp2(__uint_as_float(va[e]) * p.scale_log2 - m_new);
+                    pb[e] = fast_exp2(__uint_as_float(vb[e]) * p.scale_log2 - m_new);
+                }
             }
+            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) { l0 += pa[e]; l1 += pa[e + 1]; l2 += pb[e]; l3 += pb[e + 1]; }
+            l += (l0 + l1) + (l2 + l3);
+            store_chunk_bf16(sP, r, 2 * b, pa);
+            store_chunk_bf16(sP, r, 2 * b + 1, pb);
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(s_free); mbar_arrive(p_full); }
-            // accumulate this step's P V into the running output
-            if (!mbar_wait(o_full, pj, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tO + lane_base + c * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) O[c * 32 + e] = O[c * 32 + e] * alpha + __uint_as_float(v[e]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_free);
+            if (lane == 0) { mbar_arrive(&s_free[b]); mbar_arrive(&p_full[b]); }
+            // the previous half block's P V has had this whole softmax to finish: add it now
+            if (i > 0) ok = accumulate(i - 1, alpha_prev);
+            alpha_prev = alpha;
             m = m_new;
         }
+        if (ok) ok = accumulate(nsub - 1, alpha_prev);
         if (ok && qi < p.T) {
             const float inv = 1.0f / l;
             const int b = bh / p.H, h = bh % p.H;
