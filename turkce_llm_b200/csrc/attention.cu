@@ -421,18 +421,27 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             const uint32_t id_t = umma_idesc(1u, 1u, 1u, 128, 64);       // P^T dO, dS^T Q: both MN-major
             const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), adS = smem_u32(sdS);
             bool ok = mbar_wait(kv_full, 0, abort_flag);
-            for (int it = 0; it < niter && ok; ++it) {
+            // S = Q K^T and dP = dO V^T of query block `it`; may run ahead of the accumulation of it-1
+            // because the compute warps free the two score tiles as soon as they hold them in registers
+            auto issue_sdp = [&](int it) -> bool {
                 const int s = it & 1;
-                const uint32_t ph = (uint32_t)((it >> 1) & 1), pi = (uint32_t)(it & 1);
                 const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), adO = smem_u32(sdO + s * TILE_BYTES);
-                if (!mbar_wait(&qdo_full[s], ph, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(sdp_free, pi ^ 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&qdo_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) return false;
+                if (!mbar_wait(sdp_free, (uint32_t)(it & 1) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), id_s, k > 0 ? 1u : 0u);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(tdP, kmajor_desc(adO, k), kmajor_desc(aV, k), id_s, k > 0 ? 1u : 0u);
                 umma_commit(sdp_full);
+                return true;
+            };
+            if (ok) ok = issue_sdp(0);
+            for (int it = 0; it < niter && ok; ++it) {
+                const int s = it & 1;
+                const uint32_t pi = (uint32_t)(it & 1);
+                const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), adO = smem_u32(sdO + s * TILE_BYTES);
+                if (it + 1 < niter && !issue_sdp(it + 1)) { ok = false; break; }
                 if (!mbar_wait(pds_full, pi, abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
@@ -464,32 +473,48 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             const float lse2 = valid ? p.lse[(long long)bh * p.T + qi] * 1.4426950408889634f : INFINITY;
             const float dl = valid ? p.delta[(long long)bh * p.T + qi] : 0.0f;
             if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
-            if (!mbar_wait(pds_free, pi ^ 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
-#pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {
-                const int c = half * 2 + cc;
-                uint32_t sv[32], dv[32];
-                tmem_ld32(tS + lane_base + c * 32, sv);
-                tmem_ld32(tdP + lane_base + c * 32, dv);
-                tmem_ld_wait();
-                float P[32], dS[32];
-                // rows past T get lse2 = +inf below, i.e. P = 0; the diagonal block masks keys after the query
-                const int lim = diag ? qi - (k0 + c * 32) : 32;
+            // this thread's 64 scores and 64 dP values in one TMEM round trip, then the tiles are free
+            uint32_t sv0[32], sv1[32], dv0[32], dv1[32];
+            tmem_ld32(tS + lane_base + (half * 2) * 32, sv0);
+            tmem_ld32(tS + lane_base + (half * 2 + 1) * 32, sv1);
+            tmem_ld32(tdP + lane_base + (half * 2) * 32, dv0);
+            tmem_ld32(tdP + lane_base + (half * 2 + 1) * 32, dv1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sdp_free);
+            // rows past T get lse2 = +inf, i.e. P = 0; the diagonal block masks keys after the query
+            float P[32], dS[32];
+            {
+                const int lim = diag ? qi - (k0 + (half * 2) * 32) : 32;
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    float pe = fast_exp2(__uint_as_float(sv[e]) * p.scale_log2 - lse2);
+                    float pe = fast_exp2(__uint_as_float(sv0[e]) * p.scale_log2 - lse2);
                     if (diag) pe = e <= lim ? pe : 0.0f;
                     P[e] = pe;
-                    dS[e] = pe * (__uint_as_float(dv[e]) - dl) * p.scale;
+                    dS[e] = pe * (__uint_as_float(dv0[e]) - dl) * p.scale;
                 }
-                store_chunk_bf16(sP, r, c, P);
-                store_chunk_bf16(sdS, r, c, dS);
             }
+            if (!mbar_wait(pds_free, pi ^ 1u, abort_flag)) { ok = false; break; }     // previous P, dS consumed
+            store_chunk_bf16(sP, r, half * 2, P);
+            store_chunk_bf16(sdS, r, half * 2, dS);
+            {
+                const int lim = diag ? qi - (k0 + (half * 2 + 1) * 32) : 32;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    float pe = fast_exp2(__uint_as_float(sv1[e]) * p.scale_log2 - lse2);
+                    if (diag) pe = e <= lim ? pe : 0.0f;
+                    P[e] = pe;
+                    dS[e] = pe * (__uint_as_float(dv1[e]) - dl) * p.scale;
+                }
+            }
+            store_chunk_bf16(sP, r, half * 2 + 1, P);
+            store_chunk_bf16(sdS, r, half * 2 + 1, dS);
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(sdp_free); mbar_arrive(pds_full); }
+            if (lane == 0) mbar_arrive(pds_full);
         }
         if (ok) {
             if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
@@ -596,18 +621,26 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             const uint32_t id_q = umma_idesc(1u, 0u, 1u, 128, 64);       // dS (K-major) x K block (MN-major)
             const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), adS = smem_u32(sdS);
             bool ok = mbar_wait(qdo_full, 0, abort_flag);
-            for (int it = 0; it < niter && ok; ++it) {
+            // S and dP of key block `it`; may run ahead of dQ += dS K of it-1 (see the dK/dV kernel)
+            auto issue_sdp = [&](int it) -> bool {
                 const int s = it & 1;
-                const uint32_t ph = (uint32_t)((it >> 1) & 1), pi = (uint32_t)(it & 1);
                 const uint32_t aK = smem_u32(sK + s * TILE_BYTES), aV = smem_u32(sV + s * TILE_BYTES);
-                if (!mbar_wait(&kv_full[s], ph, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(sdp_free, pi ^ 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&kv_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) return false;
+                if (!mbar_wait(sdp_free, (uint32_t)(it & 1) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), id_s, k > 0 ? 1u : 0u);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(tdP, kmajor_desc(adO, k), kmajor_desc(aV, k), id_s, k > 0 ? 1u : 0u);
                 umma_commit(sdp_full);
+                return true;
+            };
+            if (ok) ok = issue_sdp(0);
+            for (int it = 0; it < niter && ok; ++it) {
+                const int s = it & 1;
+                const uint32_t pi = (uint32_t)(it & 1);
+                const uint32_t aK = smem_u32(sK + s * TILE_BYTES);
+                if (it + 1 < niter && !issue_sdp(it + 1)) { ok = false; break; }
                 if (!mbar_wait(ds_full, pi, abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
@@ -635,29 +668,42 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             const bool diag = (it == qb);
             const int k0 = it * ATT_BN;
             if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
-            if (!mbar_wait(ds_free, pi ^ 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
-#pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {
-                const int c = half * 2 + cc;
-                uint32_t sv[32], dv[32];
-                tmem_ld32(tS + lane_base + c * 32, sv);
-                tmem_ld32(tdP + lane_base + c * 32, dv);
-                tmem_ld_wait();
-                float dS[32];
-                const int lim = diag ? qi - (k0 + c * 32) : 32;
+            uint32_t sv0[32], sv1[32], dv0[32], dv1[32];
+            tmem_ld32(tS + lane_base + (half * 2) * 32, sv0);
+            tmem_ld32(tS + lane_base + (half * 2 + 1) * 32, sv1);
+            tmem_ld32(tdP + lane_base + (half * 2) * 32, dv0);
+            tmem_ld32(tdP + lane_base + (half * 2 + 1) * 32, dv1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sdp_free);                  // the score tiles live in registers now
+            float dS[32];
+            {
+                const int lim = diag ? qi - (k0 + (half * 2) * 32) : 32;
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    float pe = fast_exp2(__uint_as_float(sv[e]) * p.scale_log2 - lse2);
+                    float pe = fast_exp2(__uint_as_float(sv0[e]) * p.scale_log2 - lse2);
                     if (diag) pe = e <= lim ? pe : 0.0f;
-                    dS[e] = pe * (__uint_as_float(dv[e]) - dl) * p.scale;
+                    dS[e] = pe * (__uint_as_float(dv0[e]) - dl) * p.scale;
                 }
-                store_chunk_bf16(sdS, r, c, dS);
             }
+            if (!mbar_wait(ds_free, pi ^ 1u, abort_flag)) { ok = false; break; }      // previous dS consumed
+            store_chunk_bf16(sdS, r, half * 2, dS);
+            {
+                const int lim = diag ? qi - (k0 + (half * 2 + 1) * 32) : 32;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    float pe = fast_exp2(__uint_as_float(sv1[e]) * p.scale_log2 - lse2);
+                    if (diag) pe = e <= lim ? pe : 0.0f;
+                    dS[e] = pe * (__uint_as_float(dv1[e]) - dl) * p.scale;
+                }
+            }
+            store_chunk_bf16(sdS, r, half * 2 + 1, dS);
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(sdp_free); mbar_arrive(ds_full); }
+            if (lane == 0) mbar_arrive(ds_full);
         }
         if (ok) {
             if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
