@@ -195,6 +195,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(TF32 ? 2u : 1u, (uint32_t)p.a_mn, (uint32_t)p.b_mn, BM, BN);
+            // Shared-memory descriptors are built once: the descriptor of stage 0, the step between stages
+            // and the step between the four UMMAs of a K slice are all that changes (the start address sits
+            // in the low 14 bits, in 16-byte units, and never carries out of them below 256 KB).  One thread
+            // issues every UMMA of the CTA, so its instruction count per UMMA bounds the tensor pipe.
+            const uint32_t a_addr0 = smem_u32(stage_base);
+            const uint32_t b_addr0 = a_addr0 + Cfg::A_BYTES;
+            const uint64_t a_desc0 = !p.a_mn ? umma_desc_sw128(a_addr0, 16, 1024)
+                                     : TF32  ? umma_desc_mn32(a_addr0, MN_BOX_BYTES)
+                                             : umma_desc_sw128(a_addr0, MN_BOX_BYTES, 1024);
+            const uint64_t b_desc0 = !p.b_mn ? umma_desc_sw128(b_addr0, 16, 1024)
+                                     : TF32  ? umma_desc_mn32(b_addr0, MN_BOX_BYTES)
+                                             : umma_desc_sw128(b_addr0, MN_BOX_BYTES, 1024);
+            const uint64_t a_kstep = (uint64_t)((!p.a_mn ? 32 : MN_STEP) >> 4);
+            const uint64_t b_kstep = (uint64_t)((!p.b_mn ? 32 : MN_STEP) >> 4);
+            constexpr uint64_t STAGE_STEP = (uint64_t)(Cfg::STAGE_BYTES >> 4);
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
@@ -209,21 +225,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int kb = c.kb0; kb < c.kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(stage_base + stage * Cfg::STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + Cfg::A_BYTES;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {          // 4 UMMAs of 32 bytes of K per 128-byte slice
-                        const uint64_t a_desc = !p.a_mn ? umma_desc_sw128(a_addr + k * 32, 16, 1024)
-                                                : TF32  ? umma_desc_mn32(a_addr + k * MN_STEP, MN_BOX_BYTES)
-                                                        : umma_desc_sw128(a_addr + k * MN_STEP, MN_BOX_BYTES, 1024);
-                        const uint64_t b_desc = !p.b_mn ? umma_desc_sw128(b_addr + k * 32, 16, 1024)
-                                                : TF32  ? umma_desc_mn32(b_addr + k * MN_STEP, MN_BOX_BYTES)
-                                                        : umma_desc_sw128(b_addr + k * MN_STEP, MN_BOX_BYTES, 1024);
-                        if (TF32) umma_tf32(d_tmem, a_desc, b_desc, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
-                        else      umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                        if (TF32) umma_tf32(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                        else      umma_bf16(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    a_desc += STAGE_STEP; b_desc += STAGE_STEP;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; a_desc = a_desc0; b_desc = b_desc0; }
                 }
                 if (!ok) break;
                 umma_commit(&acc_full[buf]);          // accumulator complete
