@@ -27,14 +27,19 @@ constexpr int ATT_BN = 128;       // keys per step
 constexpr int ATT_HD = 64;        // padded head dimension
 constexpr int TILE_BYTES = 128 * 64 * 2;   // one [128, 64] bf16 tile, 128-byte rows
 
+// Shared-memory descriptors are built once per tile, outside the issue loops (one thread issues every
+// UMMA of the CTA, so each instruction it spends per UMMA delays the tensor pipe); the loops only add
+// to the start-address field (low 14 bits, 16-byte units; never carries below 256 KB).
 // K-major operand tile [rows, 64] (128-byte rows, 128B swizzle): advance 32 bytes per K=16
-__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_addr, int k16) {
-    return umma_desc_sw128(tile_addr + k16 * 32, 16, 1024);
+__device__ __forceinline__ uint64_t kmajor_tile(uint32_t tile_addr) { return umma_desc_sw128(tile_addr, 16, 1024); }
+// the same tile read as an MN-major operand (64 MN elements contiguous, K = rows): 16 rows per K=16;
+// lbo = bytes between consecutive 64-wide MN blocks
+__device__ __forceinline__ uint64_t mnmajor_tile(uint32_t tile_addr, uint32_t lbo) {
+    return umma_desc_sw128(tile_addr, lbo, 1024);
 }
-// the same tile read as an MN-major operand (64 MN elements contiguous, K = rows): 16 rows per K=16
-__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_addr, int k16, uint32_t lbo) {
-    return umma_desc_sw128(tile_addr + k16 * 2048, lbo, 1024);
-}
+constexpr uint64_t KSTEP = 32 >> 4;          // descriptor units per K=16 step of a K-major tile
+constexpr uint64_t MNSTEP = 2048 >> 4;       // ... of an MN-major tile (16 rows of 128 bytes)
+constexpr uint64_t TILESTEP = (128 * 64 * 2) >> 4;   // one [128, 64] bf16 tile
 
 // 2^x on the special-function unit (one instruction; 2^-inf = 0)
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -149,17 +154,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             // and P V (i-1) while the softmax of i runs -- no step waits for a full round trip.
             const uint32_t idesc_s = umma_idesc(1u, 0u, 0u, ATT_BM, 64);         // Q K^T: both K-major
             const uint32_t idesc_o = umma_idesc(1u, 0u, 1u, ATT_BM, ATT_HD);     // P V: V is MN-major
-            const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+            const uint64_t dQ = kmajor_tile(smem_u32(sQ)), dK0 = kmajor_tile(smem_u32(sK)), dP0 = kmajor_tile(smem_u32(sP));
+            const uint64_t dV0 = mnmajor_tile(smem_u32(sV), TILE_BYTES);
             bool ok = mbar_wait(q_full, 0, abort_flag);
             auto issue_scores = [&](int i) -> bool {
                 const int j = i >> 1, st = j & 1, b = i & 1;
                 if (b == 0 && !mbar_wait(&k_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
                 if (!mbar_wait(&s_free[b], (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t aK = smem_u32(sK + st * TILE_BYTES) + (uint32_t)b * 8192u;    // keys 64b.. of the tile
+                const uint64_t dK = dK0 + (uint64_t)st * TILESTEP + (uint64_t)b * (TILESTEP / 2);   // keys 64b.. of the tile
 #pragma unroll
                 for (int k = 0; k < ATT_HD / 16; ++k)
-                    umma_bf16(tS + (uint32_t)(b * 64), kmajor_desc(aQ, k), kmajor_desc(aK, k), idesc_s, k > 0 ? 1u : 0u);
+                    umma_bf16(tS + (uint32_t)(b * 64), dQ + k * KSTEP, dK + k * KSTEP, idesc_s, k > 0 ? 1u : 0u);
                 umma_commit(&s_full[b]);
                 return true;
             };
@@ -172,11 +178,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 if (b == 0 && !mbar_wait(&v_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) { ok = false; break; }
                 if (!mbar_wait(&o_free[b], par ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t aV = smem_u32(sV + st * TILE_BYTES);
+                const uint64_t dP = dP0 + (uint64_t)b * TILESTEP;
+                const uint64_t dV = dV0 + (uint64_t)st * TILESTEP + (uint64_t)b * (4 * MNSTEP);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    umma_bf16(tO + (uint32_t)(b * 64), kmajor_desc(aP + b * TILE_BYTES, k),
-                              mnmajor_desc(aV, b * 4 + k, TILE_BYTES), idesc_o, k > 0 ? 1u : 0u);
+                    umma_bf16(tO + (uint32_t)(b * 64), dP + k * KSTEP, dV + k * MNSTEP, idesc_o, k > 0 ? 1u : 0u);
                 umma_commit(&o_full[b]);
                 if (b == 1) umma_commit(&kv_empty[st]);          // both halves of the K/V tile are consumed
                 if (i + 2 < nsub) ok = issue_scores(i + 2);
@@ -419,20 +425,23 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         if (lane == 0) {
             const uint32_t id_s = umma_idesc(1u, 0u, 0u, 128, 128);      // Q K^T, dO V^T
             const uint32_t id_t = umma_idesc(1u, 1u, 1u, 128, 64);       // P^T dO, dS^T Q: both MN-major
-            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), adS = smem_u32(sdS);
+            const uint64_t dKk = kmajor_tile(smem_u32(sK)), dVk = kmajor_tile(smem_u32(sV));
+            const uint64_t dPm = mnmajor_tile(smem_u32(sP), TILE_BYTES), ddSm = mnmajor_tile(smem_u32(sdS), TILE_BYTES);
+            const uint64_t dQk0 = kmajor_tile(smem_u32(sQ)), ddOk0 = kmajor_tile(smem_u32(sdO));
+            const uint64_t dQm0 = mnmajor_tile(smem_u32(sQ), TILE_BYTES), ddOm0 = mnmajor_tile(smem_u32(sdO), TILE_BYTES);
             bool ok = mbar_wait(kv_full, 0, abort_flag);
             // S = Q K^T and dP = dO V^T of query block `it`; may run ahead of the accumulation of it-1
             // because the compute warps free the two score tiles as soon as they hold them in registers
             auto issue_sdp = [&](int it) -> bool {
                 const int s = it & 1;
-                const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), adO = smem_u32(sdO + s * TILE_BYTES);
+                const uint64_t dQk = dQk0 + (uint64_t)s * TILESTEP, ddOk = ddOk0 + (uint64_t)s * TILESTEP;
                 if (!mbar_wait(&qdo_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) return false;
                 if (!mbar_wait(sdp_free, (uint32_t)(it & 1) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), id_s, k > 0 ? 1u : 0u);
+                for (int k = 0; k < 4; ++k) umma_bf16(tS, dQk + k * KSTEP, dKk + k * KSTEP, id_s, k > 0 ? 1u : 0u);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tdP, kmajor_desc(adO, k), kmajor_desc(aV, k), id_s, k > 0 ? 1u : 0u);
+                for (int k = 0; k < 4; ++k) umma_bf16(tdP, ddOk + k * KSTEP, dVk + k * KSTEP, id_s, k > 0 ? 1u : 0u);
                 umma_commit(sdp_full);
                 return true;
             };
@@ -440,18 +449,16 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             for (int it = 0; it < niter && ok; ++it) {
                 const int s = it & 1;
                 const uint32_t pi = (uint32_t)(it & 1);
-                const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), adO = smem_u32(sdO + s * TILE_BYTES);
+                const uint64_t dQm = dQm0 + (uint64_t)s * TILESTEP, ddOm = ddOm0 + (uint64_t)s * TILESTEP;
                 if (it + 1 < niter && !issue_sdp(it + 1)) { ok = false; break; }
                 if (!mbar_wait(pds_full, pi, abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                    umma_bf16(tdV, mnmajor_desc(aP, k, TILE_BYTES), mnmajor_desc(adO, k, TILE_BYTES), id_t,
-                              (it > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16(tdV, dPm + k * MNSTEP, ddOm + k * MNSTEP, id_t, (it > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                    umma_bf16(tdK, mnmajor_desc(adS, k, TILE_BYTES), mnmajor_desc(aQ, k, TILE_BYTES), id_t,
-                              (it > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16(tdK, ddSm + k * MNSTEP, dQm + k * MNSTEP, id_t, (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(pds_free);
                 umma_commit(&qdo_empty[s]);
             }
@@ -619,19 +626,21 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         if (lane == 0) {
             const uint32_t id_s = umma_idesc(1u, 0u, 0u, 128, 128);
             const uint32_t id_q = umma_idesc(1u, 0u, 1u, 128, 64);       // dS (K-major) x K block (MN-major)
-            const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), adS = smem_u32(sdS);
+            const uint64_t dQk = kmajor_tile(smem_u32(sQ)), ddOk = kmajor_tile(smem_u32(sdO)), ddSk = kmajor_tile(smem_u32(sdS));
+            const uint64_t dKk0 = kmajor_tile(smem_u32(sK)), dVk0 = kmajor_tile(smem_u32(sV));
+            const uint64_t dKm0 = mnmajor_tile(smem_u32(sK), TILE_BYTES);
             bool ok = mbar_wait(qdo_full, 0, abort_flag);
             // S and dP of key block `it`; may run ahead of dQ += dS K of it-1 (see the dK/dV kernel)
             auto issue_sdp = [&](int it) -> bool {
                 const int s = it & 1;
-                const uint32_t aK = smem_u32(sK + s * TILE_BYTES), aV = smem_u32(sV + s * TILE_BYTES);
+                const uint64_t dKk = dKk0 + (uint64_t)s * TILESTEP, dVk = dVk0 + (uint64_t)s * TILESTEP;
                 if (!mbar_wait(&kv_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) return false;
                 if (!mbar_wait(sdp_free, (uint32_t)(it & 1) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), id_s, k > 0 ? 1u : 0u);
+                for (int k = 0; k < 4; ++k) umma_bf16(tS, dQk + k * KSTEP, dKk + k * KSTEP, id_s, k > 0 ? 1u : 0u);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tdP, kmajor_desc(adO, k), kmajor_desc(aV, k), id_s, k > 0 ? 1u : 0u);
+                for (int k = 0; k < 4; ++k) umma_bf16(tdP, ddOk + k * KSTEP, dVk + k * KSTEP, id_s, k > 0 ? 1u : 0u);
                 umma_commit(sdp_full);
                 return true;
             };
@@ -639,13 +648,13 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             for (int it = 0; it < niter && ok; ++it) {
                 const int s = it & 1;
                 const uint32_t pi = (uint32_t)(it & 1);
-                const uint32_t aK = smem_u32(sK + s * TILE_BYTES);
+                const uint64_t dKm = dKm0 + (uint64_t)s * TILESTEP;
                 if (it + 1 < niter && !issue_sdp(it + 1)) { ok = false; break; }
                 if (!mbar_wait(ds_full, pi, abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                    umma_bf16(tdQ, kmajor_desc(adS + (k >> 2) * TILE_BYTES, k & 3), mnmajor_desc(aK, k, TILE_BYTES), id_q,
+                    umma_bf16(tdQ, ddSk + (uint64_t)(k >> 2) * TILESTEP + (uint64_t)(k & 3) * KSTEP, dKm + k * MNSTEP, id_q,
                               (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(ds_free);
                 umma_commit(&kv_empty[s]);
