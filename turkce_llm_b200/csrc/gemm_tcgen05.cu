@@ -64,6 +64,9 @@ struct GemmParams {
     int vec32, vec16, vecr;     // 16-byte (8-byte for bf16) vector access allowed
     int tma_mode;               // 0: generic epilogue; 1: fp32 tile stores by TMA; 2: bf16 tile stores by TMA;
                                 // 3: SwiGLU (tmC = h [M,F] bf16, tmR = gate|up [M,2F] bf16 when keep_gu)
+                                // 4: softmax statistics only (cross-entropy pass 1), nothing stored
+    int ce_mode;                // 2: bf16 tile stores carry (exp(z - lse[row]) - onehot) * ce_scale
+    const uint32_t* ce_targets; float* ce_stats; float* ce_ztarget; const float* ce_lse; float ce_scale;
     int pair_off;               // mode 3: F; tile columns [0,BN/2) are gate columns n0/2.., [BN/2,BN) up columns F + n0/2..
     int keep_gu;
     int tma_res;                // TMA path: add res_scale * (tile of tmR) -- the residual, or the old C for beta
@@ -137,7 +140,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
-        if (p.tma_mode) tma_prefetch_desc(&tmC);
+        if (p.tma_mode != 0 && p.tma_mode != 4) tma_prefetch_desc(&tmC);
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], EPI_WARPS); }
         for (int i = 0; i < EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
@@ -267,6 +270,61 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int zo = zc / p.c_inner, zi = zc % p.c_inner;
             const int gm0 = c.m0 + q * 32;
             const bool rows_in = gm0 < p.M;
+            if (p.tma_mode == 4) {
+                // Cross-entropy pass 1: running max and sum of exponentials of this warp's 32 rows over its
+                // half of the tile's columns (online update per 32-column chunk); nothing leaves but the pair
+                if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                constexpr float LOG2E = 1.4426950408889634f;
+                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
+                const int row = gm0 + lane;
+                const int tgt = row < p.M ? (int)__ldg(p.ce_targets + row) : -1;
+                float m_run = -INFINITY, s_run = 0.0f, zt = 0.0f;
+                bool has_t = false;
+#pragma unroll 1
+                for (int ch = 0; ch < NCH; ++ch) {
+                    const int gn0 = c.n0 + half * (BN / 2) + ch * 32;
+                    if (gn0 >= p.N) break;
+                    uint32_t v[32];
+                    tmem_ld32(t_row + (uint32_t)(ch * 32), v);
+                    tmem_ld_wait();
+                    float cm = -INFINITY;
+                    if (gn0 + 32 <= p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) cm = fmaxf(cm, __uint_as_float(v[j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) cm = fmaxf(cm, gn0 + j < p.N ? __uint_as_float(v[j]) : -INFINITY);
+                    }
+                    if (tgt >= gn0 && tgt < gn0 + 32) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (gn0 + j == tgt) zt = __uint_as_float(v[j]);
+                        has_t = true;
+                    }
+                    const float m_new = fmaxf(m_run, cm);
+                    const float mb = m_new * LOG2E;
+                    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        s0 += gn0 + j     < p.N ? ex2_approx(__uint_as_float(v[j])     * LOG2E - mb) : 0.0f;
+                        s1 += gn0 + j + 1 < p.N ? ex2_approx(__uint_as_float(v[j + 1]) * LOG2E - mb) : 0.0f;
+                        s2 += gn0 + j + 2 < p.N ? ex2_approx(__uint_as_float(v[j + 2]) * LOG2E - mb) : 0.0f;
+                        s3 += gn0 + j + 3 < p.N ? ex2_approx(__uint_as_float(v[j + 3]) * LOG2E - mb) : 0.0f;
+                    }
+                    s_run = s_run * ex2_approx((m_run - m_new) * LOG2E) + ((s0 + s1) + (s2 + s3));
+                    m_run = m_new;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (row < p.M) {
+                    float2* dst = reinterpret_cast<float2*>(p.ce_stats) + ((size_t)((c.n0 / BN) * 2 + half) * p.M + row);
+                    *dst = make_float2(m_run, s_run);           // (-inf, 0) for a half with no column inside N
+                    if (has_t) p.ce_ztarget[row] = zt;
+                }
+                ++it;
+                continue;
+            }
             if (p.tma_mode == 3) {
                 // SwiGLU: this warp owns 32 rows x 32 hidden units: gate in accumulator columns half*32..,
                 // up in columns BN/2 + half*32..; h = silu(g) * u leaves as bf16, g and u (bf16) on request
@@ -384,6 +442,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (lane == 0 && ch + 1 < NCH && gn0 + 32 < p.N) {
                         mbar_expect_tx(rbar, 4096);
                         tma_load_4d(rbuf, &tmR, rbar, gn0 + 32, gm0, 0, c.z);
+                    }
+                }
+                if (p.ce_mode == 2) {
+                    // cross-entropy pass 2: the logits turn into their gradient before they are stored
+                    constexpr float LOG2E = 1.4426950408889634f;
+                    const int row = gm0 + lane;
+                    const float lb = row < p.M ? __ldg(p.ce_lse + row) * LOG2E : 0.0f;
+                    const int tgt = row < p.M ? (int)__ldg(p.ce_targets + row) : -1;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float pr = gn0 + j < p.N ? ex2_approx(o[j] * LOG2E - lb) : 0.0f;
+                        if (gn0 + j == tgt) pr -= 1.0f;
+                        o[j] = pr * p.ce_scale;
                     }
                 }
                 if (p.tma_mode == 1) {
@@ -704,6 +775,7 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 
 static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
     if (a.swiglu_h) return 128;              // the paired gate/up tile
+    if (a.ce_mode != 0) return 192;          // the statistics are laid out per 192-column tile
     if (a.bn == 64 || a.bn == 128 || a.bn == 192) return a.bn;
     if (a.N <= 64) return 64;
     const long long mt = (a.M + BM - 1) / BM;
@@ -763,7 +835,14 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
 static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, float* ws, cudaStream_t stream) {
     TB_CHECK(a.M > 0 && a.N > 0 && a.K > 0 && a.batch > 0, "GEMM dims must be positive (M=%d N=%d K=%d batch=%d)",
              a.M, a.N, a.K, a.batch);
-    TB_CHECK(a.A && a.B && (a.C32 || a.C16 || a.swiglu_h), "GEMM needs A, B and at least one output");
+    TB_CHECK(a.A && a.B && (a.C32 || a.C16 || a.swiglu_h || a.ce_mode == 1), "GEMM needs A, B and at least one output");
+    if (a.ce_mode != 0) {
+        TB_CHECK(a.kind == GEMM_NT && !a.tf32 && a.batch == 1 && bn == 192 && splits == 1 && a.alpha == 1.0f &&
+                     a.beta == 0.0f && !a.bias && !a.residual && !a.C32 && !a.swiglu_h && a.causal == CAUSAL_NONE && a.ce_targets,
+                 "fused cross-entropy GEMM: needs a plain NT bf16 product with 192-column tiles and the targets");
+        if (a.ce_mode == 1) TB_CHECK(a.ce_stats && a.ce_ztarget && !a.C16, "cross-entropy pass 1 writes statistics only");
+        else TB_CHECK(a.ce_mode == 2 && a.ce_lse && a.C16, "cross-entropy pass 2 needs the row log-sum-exp and a bf16 output");
+    }
     const bool swiglu = a.swiglu_h != nullptr;
     if (swiglu) {
         TB_CHECK(a.kind == GEMM_NN && !a.tf32 && a.batch == 1 && bn == 128 && splits == 1 && a.N % 128 == 0 &&
@@ -814,8 +893,12 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     memset(&tmR, 0, sizeof(tmR));
     p.tma_mode = 0; p.tma_res = 0; p.res_scale = 0.0f;
     p.pair_off = 0; p.keep_gu = 0;
+    p.ce_mode = a.ce_mode; p.ce_targets = a.ce_targets; p.ce_stats = a.ce_stats; p.ce_ztarget = a.ce_ztarget;
+    p.ce_lse = a.ce_lse; p.ce_scale = a.ce_scale;
     p.bias_vec = p.bias && aligned16(p.bias);
-    if (swiglu) {
+    if (a.ce_mode == 1) {
+        p.tma_mode = 4;
+    } else if (swiglu) {
         const int F = a.N / 2;
         TB_TRY(make_map_out(&tmC, a.swiglu_h, 2, F, a.M, a.ldh, 1, 0, 1, 0));
         if (a.swiglu_gu) TB_TRY(make_map_out(&tmR, a.swiglu_gu, 2, a.N, a.M, a.ldgu, 1, 0, 1, 0));
@@ -839,6 +922,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
         if (has_res && has_beta) ok = false;
         if ((has_res || has_beta) && (p.C32 == nullptr || p.c_inner > 1)) ok = false;
         if (has_res && !(aligned16(p.residual) && (p.ldr * 4) % 16 == 0 && (p.strideR * 4) % 16 == 0)) ok = false;
+        TB_CHECK(ok || a.ce_mode == 0, "fused cross-entropy GEMM: the bf16 output must be 16-byte aligned with padded rows");
         if (ok) {
             TB_TRY(make_map_out(&tmC, cptr, es, p.N, p.M, ld, p.c_inner, si, nz / p.c_inner, so));
             if (has_res) {
@@ -854,7 +938,8 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     {
         // algorithmic work: the causal products touch only the lower triangle (half the MACs)
         const double macs = (double)a.M * a.N * a.K * a.batch * (a.causal != CAUSAL_NONE ? 0.5 : 1.0);
-        const double out_bytes = swiglu ? (double)a.M * a.N * (a.swiglu_gu ? 3.0 : 1.0)
+        const double out_bytes = a.ce_mode == 1 ? 16.0 * a.M * ((a.N + 191) / 192)
+                                 : swiglu      ? (double)a.M * a.N * (a.swiglu_gu ? 3.0 : 1.0)
                                         : (double)a.M * a.N * a.batch * ((a.C32 ? 4.0 : 0.0) + (a.C16 ? 2.0 : 0.0)) *
                                               (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);
         const double in_bytes = 2.0 * a.batch * ((double)a.M * a.K + (double)a.K * a.N) *
@@ -863,8 +948,9 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
             char tag[128];
             static const char* kn[3] = {"NN", "NT", "TN"};
             snprintf(tag, sizeof(tag), "%s:%s:%dx%dx%d:b%d:s%d:c%d:bn%d%s", a.tf32 ? "gemm_tf32" : "gemm_bf16",
-                     kn[(int)a.kind], a.M, a.N, a.K, a.batch, splits, (int)a.causal, bn, swiglu ? ":swiglu" : "");
-            prof_mark(ctx, prof_intern(tag), 2.0 * macs, in_bytes + out_bytes, stream);
+                     kn[(int)a.kind], a.M, a.N, a.K, a.batch, splits, (int)a.causal, bn, swiglu ? ":swiglu" : a.ce_mode == 1 ? ":ce_stats" : a.ce_mode == 2 ? ":ce_grad" : "");
+            // the second cross-entropy pass repeats pass 1's product: its flops are not algorithmic work
+            prof_mark(ctx, prof_intern(tag), a.ce_mode == 2 ? 0.0 : 2.0 * macs, in_bytes + out_bytes, stream);
         }
     }
     if (a.tf32) {
@@ -901,7 +987,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
 int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual || a.c_inner > 1 || a.swiglu_h) splits = 1;
+    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0) splits = 1;
     float* ws = nullptr;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N * sizeof(float);
@@ -915,7 +1001,7 @@ int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, siz
                         cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual || a.c_inner > 1 || a.swiglu_h) splits = 1;
+    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0) splits = 1;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N;
         TB_CHECK(workspace != nullptr && workspace_floats >= need,

@@ -78,6 +78,13 @@ __device__ __forceinline__ void tc_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// 2^x on the special-function unit (one instruction; 2^-inf = 0; relative error about 2^-22)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // --------------------------------------------------------------------- TMA
 // Plain tiled loads into this CTA's shared memory; completion is signalled on an
 // mbarrier of the same CTA.  x is the innermost coordinate and must be a multiple

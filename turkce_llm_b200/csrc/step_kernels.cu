@@ -860,6 +860,55 @@ cross_entropy_row_kernel(const float* __restrict__ logits, const uint32_t* __res
     }
 }
 
+// Second half of the cross-entropy fused into the LM-head GEMM: the GEMM epilogue leaves, per row, `parts`
+// pairs (max, sum exp(z - max)) over column ranges; their combination is the row's log-sum-exp, and
+// loss = lse - z[target] (model/loss.c:31-73).  32 rows per block, 8 threads per row each taking every
+// 8th pair in order, combined in thread order.
+__global__ void ce_combine_kernel(const float2* __restrict__ stats, int parts, int rows,
+                                  const float* __restrict__ ztarget, float* __restrict__ lse_out,
+                                  float* __restrict__ loss_rows) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float shm[8][33], shs[8][33];
+    const int rl = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int row = blockIdx.x * 32 + rl;
+    float m = -INFINITY, s = 0.0f;
+    if (row < rows) {
+        for (int t = g; t < parts; t += 8) {
+            const float2 v = stats[(size_t)t * rows + row];
+            if (v.x > -INFINITY) {
+                const float mn = fmaxf(m, v.x);
+                s = s * expf(m - mn) + v.y * expf(v.x - mn);
+                m = mn;
+            }
+        }
+    }
+    shm[g][rl] = m; shs[g][rl] = s;
+    __syncthreads();
+    if (g == 0 && row < rows) {
+        for (int k = 1; k < 8; ++k) {
+            const float mk = shm[k][rl], sk = shs[k][rl];
+            if (mk > -INFINITY) {
+                const float mn = fmaxf(m, mk);
+                s = s * expf(m - mn) + sk * expf(mk - mn);
+                m = mn;
+            }
+        }
+        const float lse = (float)log((double)s) + m;
+        lse_out[row] = lse;
+        loss_rows[row] = lse - ztarget[row];
+    }
+}
+
+int launch_ce_combine(DeviceCtx* ctx, const float* stats, int parts, int rows, const float* ztarget, float* lse,
+                      float* loss_rows, cudaStream_t st) {
+    prof_mark(ctx, "ce_combine", 0.0, 0.0, st);
+    TB_CUDA(launch_kernel(ce_combine_kernel, dim3((rows + 31) / 32), dim3(256), 0, st,
+                          reinterpret_cast<const float2*>(stats), parts, rows, ztarget, lse, loss_rows));
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
 int launch_cross_entropy(DeviceCtx* ctx, const float* logits, const uint32_t* targets, float* loss_rows,
                          bf16* dlogits, int rows, int V, long long ld, float grad_scale, cudaStream_t st) {
     prof_mark(ctx, "cross_entropy", 0.0, 0.0, st);

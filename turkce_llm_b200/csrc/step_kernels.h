@@ -48,6 +48,10 @@ int launch_swiglu_bwd(DeviceCtx*, const float* gu, const float* dh, bf16* dgu, i
 // the same with gate|up kept in bf16 by the fused SwiGLU GEMM epilogue
 int launch_swiglu_bwd_bf16(DeviceCtx*, const bf16* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t);
 // logits [rows, ld] fp32 -> loss_rows, dlogits bf16 [rows, ld] = (softmax - onehot) * grad_scale
+// combines the per-tile softmax statistics of the fused LM-head GEMM (GemmArgs::ce_mode 1):
+// lse[row] and loss_rows[row] = lse - ztarget[row]; stats is [parts][rows] pairs (max, sum exp)
+int launch_ce_combine(DeviceCtx*, const float* stats, int parts, int rows, const float* ztarget, float* lse,
+                      float* loss_rows, cudaStream_t);
 int launch_cross_entropy(DeviceCtx*, const float* logits, const uint32_t* targets, float* loss_rows, bf16* dlogits,
                          int rows, int V, long long ld, float grad_scale, cudaStream_t);
 // out[c] += sum_r in[r,c]; in is fp32 or bf16; partial needs colsum_partial_floats(cols) floats, zeroed once

@@ -57,7 +57,8 @@ struct TbTrainer {
 
     std::vector<LayerActs> layers;
     float* x_final = nullptr; bf16* nf = nullptr; float* rf = nullptr;
-    float* logits = nullptr; bf16* dlogits = nullptr;
+    float* logits = nullptr; bf16* dlogits = nullptr;   // logits only exist without the fused cross-entropy
+    float *ce_stats = nullptr, *ce_zt = nullptr, *ce_lse = nullptr;
 
     float *qkv = nullptr, *S = nullptr, *dP = nullptr, *dn = nullptr, *dres = nullptr, *wtmp = nullptr, *dh = nullptr;
     float *dQ = nullptr, *dK = nullptr, *dV = nullptr;
@@ -86,6 +87,7 @@ struct TbTrainer {
     std::vector<Segment> segments;
     bool graphs_on = true;
     bool fused_attention = true;   // head_dim <= 64: scores stay on chip
+    bool fused_ce = true;          // cross-entropy inside the LM-head GEMM epilogues: no [N, V] logits
     bool fused_swiglu = true;      // d_ff % 64 == 0: silu(gate) * up formed in the gate|up GEMM's epilogue
     float* att_delta = nullptr;
     bool owns_stream = false;
@@ -198,6 +200,25 @@ int forward(TbTrainer* g, bool want_grad) {
 
     const long long p_final = pidx(g->L, 0);
     TB_TRY(launch_rmsnorm_fwd(c, g->x_final, P32(g, p_final), g->nf, g->rf, N, D, g->eps, st));
+    if (g->fused_ce) {
+        // logits = nf @ E^T (tied head, gpu_train.c:378) never reach HBM: pass 1 keeps per-tile softmax
+        // statistics and the target logit, their combination is the loss; pass 2 forms the product again
+        // and stores (softmax - onehot) / N directly (gpu_train.c:381)
+        GemmArgs a;
+        a.kind = GEMM_NT; a.A = g->nf; a.B = P16(g, 0); a.M = N; a.N = V; a.K = D; a.lda = D; a.ldb = D;
+        a.splits = 1; a.bn = 192; a.ce_targets = g->targets;
+        GemmArgs s1 = a;
+        s1.ce_mode = 1; s1.ce_stats = g->ce_stats; s1.ce_ztarget = g->ce_zt;
+        TB_TRY(gemm(g, s1));
+        TB_TRY(launch_ce_combine(c, g->ce_stats, 2 * ((V + 191) / 192), N, g->ce_zt, g->ce_lse, g->loss_rows, st));
+        if (want_grad) {
+            GemmArgs s2 = a;
+            s2.ce_mode = 2; s2.ce_lse = g->ce_lse; s2.ce_scale = 1.0f / (float)N;
+            s2.C16 = g->dlogits; s2.ldc16 = g->Vp; s2.pad_cols_writable = true;
+            TB_TRY(gemm(g, s2));
+        }
+        return 0;
+    }
     {   // logits = nf @ E^T (tied head): gpu_train.c:378
         GemmArgs a;
         a.kind = GEMM_NT; a.A = g->nf; a.B = P16(g, 0); a.M = N; a.N = V; a.K = D; a.lda = D; a.ldb = D;
@@ -478,7 +499,14 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         TB_TRY(dalloc(g, &a.h, N * F));
     }
     TB_TRY(dalloc(g, &g->x_final, N * D)); TB_TRY(dalloc(g, &g->nf, N * D)); TB_TRY(dalloc(g, &g->rf, N));
-    TB_TRY(dalloc(g, &g->logits, N * g->Vp)); TB_TRY(dalloc(g, &g->dlogits, N * g->Vp));
+    g->fused_ce = getenv("TB_NO_FUSED_CE") == nullptr;
+    if (g->fused_ce) {
+        TB_TRY(dalloc(g, &g->ce_stats, (size_t)2 * ((V + 191) / 192) * N * 2));
+        TB_TRY(dalloc(g, &g->ce_zt, N)); TB_TRY(dalloc(g, &g->ce_lse, N));
+    } else {
+        TB_TRY(dalloc(g, &g->logits, N * g->Vp));
+    }
+    TB_TRY(dalloc(g, &g->dlogits, N * g->Vp));
     TB_TRY(dalloc(g, &g->qkv, N * 3 * D));
     if (g->fused_attention) {
         TB_TRY(dalloc(g, &g->att_delta, BHT));
