@@ -350,8 +350,42 @@ struct AttBwdParams {
     const float* lse;       // [B*H, T]
     const float* delta;     // [B*H, T]
     float* dQ; float* dK; float* dV;     // [B*H, T, hd]
+    // merged output (optional, replaces dQ/dK/dV): dqkv bf16 [B*T, 3*H*hd] with the inverse rotation of
+    // the position embedding applied to dQ and dK on the way out (the reference's k_qkv_rope_merge_bwd,
+    // cuda/train_kernels.cu:600-626); cos_t/sin_t are the [T, hd/2] tables
+    bf16* dqkv; const float* cos_t; const float* sin_t;
     int* err;
 };
+
+// 32 consecutive head-dim values of one row -> bf16 at dst, optionally through the inverse rotation of the
+// interleaved pairs (2k, 2k+1): out = (a*c + b*s, -a*s + b*c).  d0 = first head-dim index of the 32.
+__device__ __forceinline__ void store_row_bf16(bf16* dst, const uint32_t (&v)[32], int d0, int hd, const float* cs,
+                                               const float* sn) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 8) {
+        if (d0 + e >= hd) break;
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(v[e + j]);
+        if (cs != nullptr) {
+            const float4 c4 = *reinterpret_cast<const float4*>(cs + ((d0 + e) >> 1));
+            const float4 s4 = *reinterpret_cast<const float4*>(sn + ((d0 + e) >> 1));
+            const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float a = o[2 * j], b = o[2 * j + 1];
+                o[2 * j] = a * cc[j] + b * ss[j];
+                o[2 * j + 1] = -a * ss[j] + b * cc[j];
+            }
+        }
+        uint4 pk;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(o[0], o[1]), h1 = __floats2bfloat162_rn(o[2], o[3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(o[4], o[5]), h3 = __floats2bfloat162_rn(o[6], o[7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(dst + e) = pk;
+    }
+}
 
 constexpr int ATT_BWD_THREADS = 320;     // TMA warp, MMA warp, 8 compute warps
 
@@ -533,7 +567,13 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             tmem_ld32(tdV + lane_base + half * 32, v);
             tmem_ld32(tdK + lane_base + half * 32, w);
             tmem_ld_wait();
-            if (kj < p.T) {
+            if (kj < p.T && p.dqkv != nullptr) {
+                const int D = p.H * p.hd;
+                bf16* row = p.dqkv + ((long long)b * p.T + kj) * 3 * D + h * p.hd + half * 32;
+                const int hh = p.hd >> 1;
+                store_row_bf16(row + D, w, half * 32, p.hd, p.cos_t + (long long)kj * hh, p.sin_t + (long long)kj * hh);
+                store_row_bf16(row + 2 * D, v, half * 32, p.hd, nullptr, nullptr);
+            } else if (kj < p.T) {
                 float* dv = p.dV + ((long long)bh * p.T + kj) * p.hd;
                 float* dk = p.dK + ((long long)bh * p.T + kj) * p.hd;
 #pragma unroll
@@ -722,7 +762,12 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             uint32_t v[32];
             tmem_ld32(tdQ + lane_base + half * 32, v);
             tmem_ld_wait();
-            if (valid) {
+            if (valid && p.dqkv != nullptr) {
+                const int D = p.H * p.hd;
+                const int hh = p.hd >> 1;
+                store_row_bf16(p.dqkv + ((long long)b * p.T + qi) * 3 * D + h * p.hd + half * 32, v, half * 32, p.hd,
+                               p.cos_t + (long long)qi * hh, p.sin_t + (long long)qi * hh);
+            } else if (valid) {
                 float* dq = p.dQ + ((long long)bh * p.T + qi) * p.hd;
 #pragma unroll
                 for (int e = 0; e < 32; e += 4) {
@@ -748,8 +793,11 @@ constexpr int ATT_DQ_SMEM = 1024 + 8 * TILE_BYTES + 256;
 
 int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, const bf16* att,
                          const bf16* datt, const float* lse, float* delta, float* dQ, float* dK, float* dV, int B,
-                         int H, int T, int hd, float scale, cudaStream_t stream) {
+                         int H, int T, int hd, float scale, cudaStream_t stream, bf16* dqkv, const float* cos_t,
+                         const float* sin_t) {
     TB_CHECK(hd > 0 && hd <= ATT_HD && hd % 8 == 0, "fused attention needs head_dim <= 64 and a multiple of 8 (got %d)", hd);
+    TB_CHECK(dqkv != nullptr ? (cos_t && sin_t && (reinterpret_cast<uintptr_t>(dqkv) & 15u) == 0) : (dQ && dK && dV),
+             "attention backward needs either dQ, dK, dV or the merged output with the rotation tables");
     TB_CHECK(B > 0 && H > 0 && T > 0, "attention dims must be positive");
     const int BH = B * H, D = H * hd;
     CUtensorMap tmQ, tmK, tmV, tmdO;
@@ -761,6 +809,7 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     p.T = T; p.H = H; p.hd = hd; p.nq = (T + ATT_BM - 1) / ATT_BM;
     p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
     p.lse = lse; p.delta = delta; p.dQ = dQ; p.dK = dK; p.dV = dV; p.err = ctx->d_err;
+    p.dqkv = dqkv; p.cos_t = cos_t; p.sin_t = sin_t;
     static bool attr_set[64] = {false};
     if (!attr_set[ctx->device & 63]) {
         TB_CUDA(cudaFuncSetAttribute(attention_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_DKDV_SMEM));

@@ -278,8 +278,9 @@ int backward_layer(TbTrainer* g, int l) {
     // (bo's gradient came with dres as well)
     TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WO)), nullptr, g->datt, N, D, D));
     if (g->fused_attention) {
-        TB_TRY(launch_attention_bwd(c, a.Q, a.K, a.V, a.att, g->datt, a.lse, g->att_delta, g->dQ, g->dK, g->dV, B, H, T,
-                                    hd, g->scale, st));
+        // dQ, dK, dV leave the kernels rotated back and merged as bf16 dqkv [N, 3D]
+        TB_TRY(launch_attention_bwd(c, a.Q, a.K, a.V, a.att, g->datt, a.lse, g->att_delta, nullptr, nullptr, nullptr, B,
+                                    H, T, hd, g->scale, st, g->dqkv, g->cos_t, g->sin_t));
     } else {
     TB_TRY(launch_heads_split(c, g->datt, g->dO, B, T, H, hd, st));
     {   // dV = P^T dO
@@ -311,8 +312,8 @@ int backward_layer(TbTrainer* g, int l) {
         k.C32 = g->dK; k.ldc32 = hd; k.strideC32 = sThd; k.causal = CAUSAL_K_SUFFIX; k.splits = 1;
         TB_TRY(gemm(g, k));
     }
-    }
     TB_TRY(launch_rope_merge_bwd(c, g->dQ, g->dK, g->dV, g->cos_t, g->sin_t, g->dqkv, B, T, H, hd, st));
+    }
     TB_TRY(linear_dw(g, a.n1, g->dqkv, G32(g, pidx(l, PK_WQKV)), N, 3 * D, D));
     TB_TRY(launch_colsum_bf16(c, g->dqkv, G32(g, pidx(l, PK_BQKV)), g->colsum_partial, N, 3 * D, st));
     TB_TRY(linear_dx(g, g->dqkv, P16(g, pidx(l, PK_WQKV)), g->dn, nullptr, N, 3 * D, D));
