@@ -116,6 +116,13 @@ struct GemmArgs {
     //   ce_mode 1: per row and per 96-column tile half, max and sum of exp(z - max) -> ce_stats
     //              [2 * ceil(N/192)][M] float2, and the target's logit -> ce_ztarget[M]
     //   ce_mode 2: the product is formed again and leaves as C16 = (exp(z - ce_lse[row]) - onehot) * ce_scale
+    // QKV projection with the position embedding fused (kind NN, N = 3*H*hd, hd 32 or 64, T % 32 == 0, M = B*T):
+    // instead of the float32 [M, 3D] projection and k_qkv_rope_split (cuda/train_kernels.cu:573-597), the
+    // epilogue rotates the interleaved pairs of the q and k columns with the [T, hd/2] tables and stores
+    // bf16 tiles straight into rope_qkv = [3][B][H][T][hd] (Q, K, V of equal size, back to back)
+    bf16* rope_qkv = nullptr;
+    const float* rope_cos = nullptr; const float* rope_sin = nullptr;
+    int rope_T = 0, rope_H = 0, rope_hd = 0;
     int ce_mode = 0;
     const uint32_t* ce_targets = nullptr;
     float* ce_stats = nullptr;

@@ -65,6 +65,8 @@ struct GemmParams {
     int tma_mode;               // 0: generic epilogue; 1: fp32 tile stores by TMA; 2: bf16 tile stores by TMA;
                                 // 3: SwiGLU (tmC = h [M,F] bf16, tmR = gate|up [M,2F] bf16 when keep_gu)
                                 // 4: softmax statistics only (cross-entropy pass 1), nothing stored
+                                // 5: bf16 tiles into [3][B][H][T][hd] with q, k rotated (tmC is a 5-D map)
+    const float* rope_cos; const float* rope_sin; int rope_T, rope_H, rope_hd;
     int ce_mode;                // 2: bf16 tile stores carry (exp(z - lse[row]) - onehot) * ce_scale
     const uint32_t* ce_targets; float* ce_stats; float* ce_ztarget; const float* ce_lse; float ce_scale;
     int pair_off;               // mode 3: F; tile columns [0,BN/2) are gate columns n0/2.., [BN/2,BN) up columns F + n0/2..
@@ -351,7 +353,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    const float sg = 1.0f / (1.0f + expf(-gv[j]));
+                    // sigmoid from ex2.approx and an approximate reciprocal (relative error ~1e-6, far below bf16's)
+                    const float sg = __fdividef(1.0f, 1.0f + ex2_approx(-gv[j] * 1.4426950408889634f));
                     hv[j] = gv[j] * sg * uv[j];
                 }
                 if (lane == 0) tma_store_wait_read<0>();            // the previous tile's stores have left the buffers
@@ -388,6 +391,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 continue;
             }
             const int col0 = c.n0 + half * (BN / 2);
+            // mode 5: position of this thread's row, and of the 32-row chunk, inside its sequence (once per tile)
+            const int rope_D = p.rope_H * p.rope_hd, rope_shift = p.rope_hd == 64 ? 6 : 5;
+            int rope_b = 0, rope_t0 = 0, rope_t = 0;
+            if (p.tma_mode == 5) { rope_b = gm0 / p.rope_T; rope_t0 = gm0 - rope_b * p.rope_T; rope_t = rope_t0 + lane; }
             if (p.tma_res && lane == 0 && rows_in && col0 < p.N) {
                 mbar_expect_tx(rbar, 4096);
                 tma_load_4d(rbuf, &tmR, rbar, col0, gm0, 0, c.z);
@@ -444,6 +451,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         tma_load_4d(rbuf, &tmR, rbar, gn0 + 32, gm0, 0, c.z);
                     }
                 }
+                if (p.tma_mode == 5) {
+                    // position embedding on the q and k columns: pairs (2k, 2k+1) of a head rotate by the
+                    // angle of (position, k); this chunk is 32 consecutive head-dim values of one head
+                    if (gn0 < 2 * rope_D) {
+                        const int d0 = (gn0 - (gn0 >= rope_D ? rope_D : 0)) & (p.rope_hd - 1);
+                        const long long off = (long long)rope_t * (p.rope_hd >> 1) + (d0 >> 1);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.rope_cos + off) + j);
+                            const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.rope_sin + off) + j);
+                            const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float a0 = o[8 * j + 2 * i], b0 = o[8 * j + 2 * i + 1];
+                                o[8 * j + 2 * i] = a0 * cc[i] - b0 * ss[i];
+                                o[8 * j + 2 * i + 1] = a0 * ss[i] + b0 * cc[i];
+                            }
+                        }
+                    }
+                }
                 if (p.ce_mode == 2) {
                     // cross-entropy pass 2: the logits turn into their gradient before they are stored
                     constexpr float LOG2E = 1.4426950408889634f;
@@ -480,7 +507,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                    if (active) tma_store_4d(&tmC, obuf + b * 4096, gn0, gm0, zi, zo);
+                    if (active && p.tma_mode == 5) {
+                        const int which = gn0 >= 2 * rope_D ? 2 : (gn0 >= rope_D ? 1 : 0);
+                        const int cin = gn0 - which * rope_D;
+                        tma_store_5d(&tmC, obuf + b * 4096, cin & (p.rope_hd - 1), rope_t0, cin >> rope_shift, rope_b, which);
+                    } else if (active) {
+                        tma_store_4d(&tmC, obuf + b * 4096, gn0, gm0, zi, zo);
+                    }
                     tma_store_commit();
                 }
                 ++cnt;
@@ -835,7 +868,15 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
 static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, float* ws, cudaStream_t stream) {
     TB_CHECK(a.M > 0 && a.N > 0 && a.K > 0 && a.batch > 0, "GEMM dims must be positive (M=%d N=%d K=%d batch=%d)",
              a.M, a.N, a.K, a.batch);
-    TB_CHECK(a.A && a.B && (a.C32 || a.C16 || a.swiglu_h || a.ce_mode == 1), "GEMM needs A, B and at least one output");
+    TB_CHECK(a.A && a.B && (a.C32 || a.C16 || a.swiglu_h || a.ce_mode == 1 || a.rope_qkv),
+             "GEMM needs A, B and at least one output");
+    if (a.rope_qkv) {
+        TB_CHECK(a.kind == GEMM_NN && !a.tf32 && a.batch == 1 && splits == 1 && a.alpha == 1.0f && a.beta == 0.0f &&
+                     !a.residual && !a.C32 && !a.C16 && !a.swiglu_h && a.ce_mode == 0 && a.causal == CAUSAL_NONE &&
+                     a.rope_cos && a.rope_sin && (a.rope_hd == 32 || a.rope_hd == 64) && a.rope_T > 0 &&
+                     a.rope_T % 32 == 0 && a.M % a.rope_T == 0 && a.N == 3 * a.rope_H * a.rope_hd && aligned16(a.rope_qkv),
+                 "fused QKV + position-embedding GEMM: needs a plain NN bf16 product with N = 3*H*hd, hd 32 or 64, T %% 32 == 0");
+    }
     if (a.ce_mode != 0) {
         TB_CHECK(a.kind == GEMM_NT && !a.tf32 && a.batch == 1 && bn == 192 && splits == 1 && a.alpha == 1.0f &&
                      a.beta == 0.0f && !a.bias && !a.residual && !a.C32 && !a.swiglu_h && a.causal == CAUSAL_NONE && a.ce_targets,
@@ -896,8 +937,22 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     p.ce_mode = a.ce_mode; p.ce_targets = a.ce_targets; p.ce_stats = a.ce_stats; p.ce_ztarget = a.ce_ztarget;
     p.ce_lse = a.ce_lse; p.ce_scale = a.ce_scale;
     p.bias_vec = p.bias && aligned16(p.bias);
+    p.rope_cos = a.rope_cos; p.rope_sin = a.rope_sin; p.rope_T = a.rope_T; p.rope_H = a.rope_H; p.rope_hd = a.rope_hd;
     if (a.ce_mode == 1) {
         p.tma_mode = 4;
+    } else if (a.rope_qkv) {
+        EncodeTiledFn enc = get_encode_fn();
+        TB_CHECK(enc != nullptr, "cuTensorMapEncodeTiled entry point not available");
+        const cuuint64_t hd = (cuuint64_t)a.rope_hd, T = (cuuint64_t)a.rope_T, H = (cuuint64_t)a.rope_H, Bn = (cuuint64_t)(a.M / a.rope_T);
+        cuuint64_t dims[5] = {hd, T, H, Bn, 3};
+        cuuint64_t strides[4] = {hd * 2, T * hd * 2, H * T * hd * 2, Bn * H * T * hd * 2};
+        cuuint32_t box[5] = {32u, 32u, 1u, 1u, 1u};
+        cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+        CUresult r = enc(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, a.rope_qkv, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (QKV output) failed with code %d", (int)r);
+        p.tma_mode = 5;
     } else if (swiglu) {
         const int F = a.N / 2;
         TB_TRY(make_map_out(&tmC, a.swiglu_h, 2, F, a.M, a.ldh, 1, 0, 1, 0));
@@ -938,7 +993,8 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     {
         // algorithmic work: the causal products touch only the lower triangle (half the MACs)
         const double macs = (double)a.M * a.N * a.K * a.batch * (a.causal != CAUSAL_NONE ? 0.5 : 1.0);
-        const double out_bytes = a.ce_mode == 1 ? 16.0 * a.M * ((a.N + 191) / 192)
+        const double out_bytes = a.rope_qkv ? 2.0 * a.M * a.N
+                                 : a.ce_mode == 1 ? 16.0 * a.M * ((a.N + 191) / 192)
                                  : swiglu      ? (double)a.M * a.N * (a.swiglu_gu ? 3.0 : 1.0)
                                         : (double)a.M * a.N * a.batch * ((a.C32 ? 4.0 : 0.0) + (a.C16 ? 2.0 : 0.0)) *
                                               (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);
@@ -948,7 +1004,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
             char tag[128];
             static const char* kn[3] = {"NN", "NT", "TN"};
             snprintf(tag, sizeof(tag), "%s:%s:%dx%dx%d:b%d:s%d:c%d:bn%d%s", a.tf32 ? "gemm_tf32" : "gemm_bf16",
-                     kn[(int)a.kind], a.M, a.N, a.K, a.batch, splits, (int)a.causal, bn, swiglu ? ":swiglu" : a.ce_mode == 1 ? ":ce_stats" : a.ce_mode == 2 ? ":ce_grad" : "");
+                     kn[(int)a.kind], a.M, a.N, a.K, a.batch, splits, (int)a.causal, bn, swiglu ? ":swiglu" : a.rope_qkv ? ":rope" : a.ce_mode == 1 ? ":ce_stats" : a.ce_mode == 2 ? ":ce_grad" : "");
             // the second cross-entropy pass repeats pass 1's product: its flops are not algorithmic work
             prof_mark(ctx, prof_intern(tag), a.ce_mode == 2 ? 0.0 : 2.0 * macs, in_bytes + out_bytes, stream);
         }
@@ -987,7 +1043,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
 int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0) splits = 1;
+    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0 || a.rope_qkv) splits = 1;
     float* ws = nullptr;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N * sizeof(float);
@@ -1001,7 +1057,7 @@ int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, siz
                         cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0) splits = 1;
+    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0 || a.rope_qkv) splits = 1;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N;
         TB_CHECK(workspace != nullptr && workspace_floats >= need,

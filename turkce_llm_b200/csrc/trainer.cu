@@ -87,6 +87,7 @@ struct TbTrainer {
     std::vector<Segment> segments;
     bool graphs_on = true;
     bool fused_attention = true;   // head_dim <= 64: scores stay on chip
+    bool fused_rope = true;        // T % 32 == 0, head_dim 32 or 64: rotation and head split in the QKV GEMM epilogue
     bool fused_ce = true;          // cross-entropy inside the LM-head GEMM epilogues: no [N, V] logits
     bool fused_swiglu = true;      // d_ff % 64 == 0: silu(gate) * up formed in the gate|up GEMM's epilogue
     float* att_delta = nullptr;
@@ -156,9 +157,18 @@ int forward(TbTrainer* g, bool want_grad) {
         LayerActs& a = g->layers[l];
         float* x_out = (l + 1 < g->L) ? g->layers[l + 1].x_in : g->x_final;
         TB_TRY(launch_rmsnorm_fwd(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.n1, a.r1, N, D, g->eps, st));
-        TB_TRY(linear_fwd(g, a.n1, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, N,
-                          3 * D, D));
-        TB_TRY(launch_rope_split(c, g->qkv, g->cos_t, g->sin_t, a.Q, a.K, a.V, B, T, H, hd, T, st));
+        if (g->fused_rope) {
+            // QKV projection; q and k rotated and all three stored per head as bf16 by the GEMM epilogue
+            GemmArgs s;
+            s.kind = GEMM_NN; s.A = a.n1; s.B = P16(g, pidx(l, PK_WQKV)); s.M = N; s.N = 3 * D; s.K = D; s.lda = D;
+            s.ldb = 3 * D; s.bias = P32(g, pidx(l, PK_BQKV)); s.splits = 1;
+            s.rope_qkv = a.Q; s.rope_cos = g->cos_t; s.rope_sin = g->sin_t; s.rope_T = T; s.rope_H = H; s.rope_hd = hd;
+            TB_TRY(gemm(g, s));
+        } else {
+            TB_TRY(linear_fwd(g, a.n1, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, N,
+                              3 * D, D));
+            TB_TRY(launch_rope_split(c, g->qkv, g->cos_t, g->sin_t, a.Q, a.K, a.V, B, T, H, hd, T, st));
+        }
         if (g->fused_attention) {
             TB_TRY(launch_attention_fwd(c, a.Q, a.K, a.V, a.att, a.lse, B, H, T, hd, g->scale, st));
         } else {
@@ -461,6 +471,7 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
     g->graphs_on = getenv("TB_NO_GRAPH") == nullptr;
     g->fused_attention = (D / H) <= 64 && getenv("TB_NO_FUSED_ATTENTION") == nullptr;
     g->fused_swiglu = F % 64 == 0 && getenv("TB_NO_FUSED_SWIGLU") == nullptr;
+    g->fused_rope = T % 32 == 0 && (D / H == 32 || D / H == 64) && getenv("TB_NO_FUSED_ROPE") == nullptr;
     g->V = V; g->D = D; g->H = H; g->L = L; g->F = F; g->T = T; g->B = B; g->N = B * T; g->hd = D / H;
     g->Vp = round_up(V, 8);
     g->Tp = round_up(T, 8);
@@ -489,7 +500,8 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
     for (int l = 0; l < L; ++l) {
         LayerActs& a = g->layers[l];
         TB_TRY(dalloc(g, &a.x_in, N * D)); TB_TRY(dalloc(g, &a.n1, N * D)); TB_TRY(dalloc(g, &a.r1, N));
-        TB_TRY(dalloc(g, &a.Q, N * D)); TB_TRY(dalloc(g, &a.K, N * D)); TB_TRY(dalloc(g, &a.V, N * D));
+        TB_TRY(dalloc(g, &a.Q, 3 * N * D));          // Q, K, V back to back: one 5-D store map covers them
+        a.K = a.Q + N * D; a.V = a.K + N * D;
         if (g->fused_attention) { a.P = nullptr; TB_TRY(dalloc(g, &a.lse, BHT)); }
         else { a.lse = nullptr; TB_TRY(dalloc(g, &a.P, BHT * Tp)); }
         TB_TRY(dalloc(g, &a.att, N * D));
