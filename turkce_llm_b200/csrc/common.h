@@ -101,7 +101,7 @@ struct GemmArgs {
     float alpha = 1.0f, beta = 0.0f;        // beta applies to the previous contents of C32
     CausalMode causal = CAUSAL_NONE;
     int splits = 0;                         // 0 = choose; >1 uses scratch for fixed-order partial sums
-    int bn = 0;                             // 0 = choose tile width (64, 128 or 192)
+    int bn = 0;                             // 0 = choose tile width (64, 128 or 192; 256 = a CTA pair on a 256 x 256 tile)
     bool tf32 = false;                      // operands are float32 in memory and enter the tensor cores as tf32
     bool pad_cols_writable = false;         // columns N .. round_up(N, 16 bytes) of each output row are padding
     // Fused SwiGLU epilogue (kind NN, N = 2F with gate columns [0,F) and up columns [F,2F), F % 64 == 0):
@@ -189,19 +189,34 @@ static inline long long round_up(long long x, long long m) { return (x + m - 1) 
 // pdl_wait() before it touches global memory (a no-op for a launch without the attribute).
 int pdl_mode();     // 0 off, 1 every launch, 2 only launches with >= 64 KB of dynamic shared memory
 
+// cluster_x > 1: thread-block clusters of that many CTAs along x (the grid must be a multiple of it)
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t stream, int cluster_x, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    const int mode = pdl_mode();
+    if (mode == 1 || (mode == 2 && smem >= 65536)) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster_x; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = n ? attr : nullptr;
+    cfg.numAttrs = (unsigned)n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  Args&&... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    const int mode = pdl_mode();
-    const bool pdl = mode == 1 || (mode == 2 && smem >= 65536);
-    cfg.attrs = pdl ? attr : nullptr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    return launch_kernel_cluster(kernel, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
 }
 
 #ifdef __CUDACC__

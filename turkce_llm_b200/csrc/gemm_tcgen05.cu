@@ -35,11 +35,14 @@ constexpr int NUM_THREADS = 320;      // TMA warp, MMA warp, 8 epilogue warps
 constexpr int EPI_WARPS = 8;
 constexpr int STAGE_LD = 36;        // floats per staging row (32 + 4 pad: conflict-free float4 access)
 
-template <int BN> struct GemmCfg {
+// PAIR: two CTAs of a cluster share a 256 x BN tile (cta_group::2): each loads its own 128 rows of A and
+// BN/2 columns of B, so a CTA's shared-memory traffic per output element drops by BN/(128 + BN/2)/(BN/(128+BN)).
+template <int BN, bool PAIR = false> struct GemmCfg {
+    static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN;   // columns of B this CTA loads
     static constexpr int A_BYTES = BM * ROW_BYTES;      // one K slice: 128-byte rows for either operand type
-    static constexpr int B_BYTES = BN * ROW_BYTES;
+    static constexpr int B_BYTES = BN_LOCAL * ROW_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 192) ? 3 : (BN == 128) ? 4 : 5;
+    static constexpr int STAGES = PAIR ? 4 : (BN == 192) ? 3 : (BN == 128) ? 4 : 5;
     // per epilogue warp: 2 output buffers + 1 residual buffer of 32 rows x 128 B (TMA path);
     // the generic path uses the front of the same region (32 x 36 floats per warp)
     static constexpr int EPI_WARP_BYTES = 3 * 4096;
@@ -79,14 +82,14 @@ struct GemmParams {
 
 struct TileCoord { int z, s, m0, n0, kb0, kb1; bool skip; };
 
-template <int BN, int BKE>
-__device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t) {
+template <int BN, int BKE, int TILE_M = BM>
+__device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t, int row_off = 0) {
     TileCoord c;
     const int n_idx = t % p.nt; t /= p.nt;
     const int m_idx = t % p.mt; t /= p.mt;
     c.s = t % p.splits;
     c.z = t / p.splits;
-    c.m0 = m_idx * BM;
+    c.m0 = m_idx * TILE_M + row_off;
     c.n0 = n_idx * BN;
     const int kb_total = (p.K + BKE - 1) / BKE;
     const int kb_per = (kb_total + p.splits - 1) / p.splits;
@@ -106,13 +109,21 @@ __device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t) {
 
 // TF32 = true: float32 operands in shared memory, kind::tf32 (the tensor core reads the top 19 bits),
 // K slices of 32 elements; everything else is shared with the bf16 path.
-template <int BN, bool TF32>
+template <int BN, bool TF32, bool PAIR = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  const GemmParams p) {
-    using Cfg = GemmCfg<BN>;
+    static_assert(!(PAIR && TF32), "CTA pairs are built for bf16 operands only");
+    using Cfg = GemmCfg<BN, PAIR>;
     constexpr int STAGES = Cfg::STAGES;
+    constexpr int BNL = Cfg::BN_LOCAL;
+    constexpr int TILE_M = PAIR ? 2 * BM : BM;
+    // PAIR: rank in the CTA pair; rank 0 issues the UMMAs and owns the barriers the loads are counted on
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const int row_off = (int)rank * BM;
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int nworkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     constexpr int BKE = TF32 ? BK_TF32 : BK;           // elements per K slice
     constexpr int MNW = TF32 ? 32 : 64;                // elements per 128-byte row of an MN-major box
     constexpr int MN_BOX_BYTES = BKE * ROW_BYTES;      // one MN-major box: BKE rows of 128 bytes
@@ -144,17 +155,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tma_prefetch_desc(&tmB);
         if (p.tma_mode != 0 && p.tma_mode != 4) tma_prefetch_desc(&tmC);
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], EPI_WARPS); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], PAIR ? 2 * EPI_WARPS : EPI_WARPS); }
         for (int i = 0; i < EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-        tmem_relinquish();
+        if (PAIR) { tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish_pair(); }
+        else      { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync();          // both CTAs' barriers exist before either signals the other's
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
@@ -164,32 +176,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const TileCoord c = tile_of<BN, BKE>(p, t);
+            for (int t = worker; t < total_tiles && ok; t += nworkers) {
+                const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
                 if (c.skip) continue;
                 for (int kb = c.kb0; kb < c.kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     uint8_t* sA = stage_base + stage * Cfg::STAGE_BYTES;
                     uint8_t* sB = sA + Cfg::A_BYTES;
-                    mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                    // PAIR: both CTAs' bytes are counted on rank 0's barrier, which alone arms it
+                    if (!PAIR) mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                    else if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
+                    auto load = [&](void* dst, const CUtensorMap* map, int x, int y, int z) {
+                        if (PAIR) tma_load_3d_pair(dst, map, &full_bar[stage], x, y, z);
+                        else tma_load_3d(dst, map, &full_bar[stage], x, y, z);
+                    };
                     if (!p.a_mn) {
-                        tma_load_3d(sA, &tmA, &full_bar[stage], kb * BKE, c.m0, c.z);
+                        load(sA, &tmA, kb * BKE, c.m0, c.z);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BM / MNW; ++j)
-                            tma_load_3d(sA + j * MN_BOX_BYTES, &tmA, &full_bar[stage], c.m0 + j * MNW, kb * BKE, c.z);
+                        for (int j = 0; j < BM / MNW; ++j) load(sA + j * MN_BOX_BYTES, &tmA, c.m0 + j * MNW, kb * BKE, c.z);
                     }
+                    const int nb0 = c.n0 + (int)rank * BNL;          // first B column this CTA loads
                     if (!p.b_mn) {
-                        tma_load_3d(sB, &tmB, &full_bar[stage], kb * BKE, c.n0, c.z);
+                        load(sB, &tmB, kb * BKE, nb0, c.z);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / MNW; ++j) {
-                            int n = c.n0 + j * MNW;
-                            if (p.tma_mode == 3)       // paired tile: first half gate columns, second half their up columns
-                                n = (c.n0 >> 1) + (j < BN / MNW / 2 ? j * MNW : p.pair_off + (j - BN / MNW / 2) * MNW);
-                            tma_load_3d(sB + j * MN_BOX_BYTES, &tmB, &full_bar[stage], n, kb * BKE, c.z);
+                        for (int j = 0; j < BNL / MNW; ++j) {
+                            int n = nb0 + j * MNW;
+                            if (p.tma_mode == 3) {     // paired tile: first half gate columns, second half their up columns
+                                const int jj = (int)rank * (BNL / MNW) + j;      // box index inside the whole tile
+                                n = (c.n0 >> 1) + (jj < BN / MNW / 2 ? jj * MNW : p.pair_off + (jj - BN / MNW / 2) * MNW);
+                            }
+                            load(sB + j * MN_BOX_BYTES, &tmB, n, kb * BKE, c.z);
                         }
                     }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (PAIR && ok) {
+                // every release of a stage must have arrived (from rank 0's commits) before this CTA may exit
+                for (int i = 0; i < STAGES && ok; ++i) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) ok = false;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -197,9 +224,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 1); }
         }
     } else if (warp == 1) {
-        // -------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc(TF32 ? 2u : 1u, (uint32_t)p.a_mn, (uint32_t)p.b_mn, BM, BN);
+        // -------------------------------------------------------------- MMA issuer (PAIR: rank 0 for both CTAs)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc(TF32 ? 2u : 1u, (uint32_t)p.a_mn, (uint32_t)p.b_mn, TILE_M, BN);
             // Shared-memory descriptors are built once: the descriptor of stage 0, the step between stages
             // and the step between the four UMMAs of a K slice are all that changes (the start address sits
             // in the low 14 bits, in 16-byte units, and never carries out of them below 256 KB).  One thread
@@ -219,8 +246,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const TileCoord c = tile_of<BN, BKE>(p, t);
+            for (int t = worker; t < total_tiles && ok; t += nworkers) {
+                const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
                 if (c.skip) continue;
                 const int buf = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -232,15 +259,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {          // 4 UMMAs of 32 bytes of K per 128-byte slice
-                        if (TF32) umma_tf32(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
-                        else      umma_bf16(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                        if (TF32)      umma_tf32(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                        else if (PAIR) umma_bf16_pair(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                        else           umma_bf16(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
                     }
-                    umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
+                    if (PAIR) umma_commit_pair(&empty_bar[stage]);   // stage reusable (in both CTAs) once these MMAs have read it
+                    else      umma_commit(&empty_bar[stage]);
                     a_desc += STAGE_STEP; b_desc += STAGE_STEP;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; a_desc = a_desc0; b_desc = b_desc0; }
                 }
                 if (!ok) break;
-                umma_commit(&acc_full[buf]);          // accumulator complete
+                if (PAIR) umma_commit_pair(&acc_full[buf]);      // accumulator complete (each CTA reads its own 128 rows)
+                else      umma_commit(&acc_full[buf]);
                 ++it;
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 2); }
@@ -262,8 +292,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t rphase = 0;
         int it = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            const TileCoord c = tile_of<BN, BKE>(p, t);
+        for (int t = worker; t < total_tiles && ok; t += nworkers) {
+            const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
             if (c.skip) continue;
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -318,7 +348,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (lane == 0) { if (PAIR) mbar_arrive_leader(&acc_empty[buf]); else mbar_arrive(&acc_empty[buf]); }
                 if (row < p.M) {
                     float2* dst = reinterpret_cast<float2*>(p.ce_stats) + ((size_t)((c.n0 / BN) * 2 + half) * p.M + row);
                     *dst = make_float2(m_run, s_run);           // (-inf, 0) for a half with no column inside N
@@ -328,64 +358,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 continue;
             }
             if (p.tma_mode == 3) {
-                // SwiGLU: this warp owns 32 rows x 32 hidden units: gate in accumulator columns half*32..,
-                // up in columns BN/2 + half*32..; h = silu(g) * u leaves as bf16, g and u (bf16) on request
+                // SwiGLU: this warp owns 32 rows x BN/4 hidden units: gate in accumulator columns half*BN/4..,
+                // up in columns BN/2 + half*BN/4..; h = silu(g) * u leaves as bf16, g and u (bf16) on request
                 if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 32);
-                uint32_t gr[32], ur[32];
-                tmem_ld32(t_row, gr);
-                tmem_ld32(t_row + (uint32_t)(BN / 2), ur);
-                tmem_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);       // the accumulator is in registers now
-                const int hj0 = (c.n0 >> 1) + half * 32;            // first hidden unit of this warp's chunk
-                float gv[32], uv[32], hv[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) { gv[j] = __uint_as_float(gr[j]); uv[j] = __uint_as_float(ur[j]); }
-                if (p.bias) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        gv[j] += __ldg(p.bias + hj0 + j);
-                        uv[j] += __ldg(p.bias + p.pair_off + hj0 + j);
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 128; ++ch) {
+                    const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) +
+                                           (uint32_t)(buf * BN + half * (BN / 4) + ch * 32);
+                    uint32_t gr[32], ur[32];
+                    tmem_ld32(t_row, gr);
+                    tmem_ld32(t_row + (uint32_t)(BN / 2), ur);
+                    tmem_ld_wait();
+                    if (ch == BN / 128 - 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) { if (PAIR) mbar_arrive_leader(&acc_empty[buf]); else mbar_arrive(&acc_empty[buf]); }
                     }
-                }
+                    const int hj0 = (c.n0 >> 1) + half * (BN / 4) + ch * 32;     // first hidden unit of this chunk
+                    float gv[32], uv[32], hv[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    // sigmoid from ex2.approx and an approximate reciprocal (relative error ~1e-6, far below bf16's)
-                    const float sg = __fdividef(1.0f, 1.0f + ex2_approx(-gv[j] * 1.4426950408889634f));
-                    hv[j] = gv[j] * sg * uv[j];
-                }
-                if (lane == 0) tma_store_wait_read<0>();            // the previous tile's stores have left the buffers
-                __syncwarp();
-                auto stage_bf16 = [&](uint8_t* base, const float (&o)[32]) {
-                    uint8_t* orow = base + lane * 64;               // 32 x 64 B, 64B swizzle
+                    for (int j = 0; j < 32; ++j) { gv[j] = __uint_as_float(gr[j]); uv[j] = __uint_as_float(ur[j]); }
+                    if (p.bias) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint4 pk;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * j + 0], o[8 * j + 1]);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * j + 2], o[8 * j + 3]);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * j + 4], o[8 * j + 5]);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * j + 6], o[8 * j + 7]);
-                        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                        *reinterpret_cast<uint4*>(orow + ((j ^ ((lane >> 1) & 3)) << 4)) = pk;
-                    }
-                };
-                stage_bf16(obuf, hv);
-                if (p.keep_gu) { stage_bf16(obuf + 4096, gv); stage_bf16(rbuf, uv); }
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) {
-                    if (rows_in) {
-                        tma_store_4d(&tmC, obuf, hj0, gm0, 0, 0);
-                        if (p.keep_gu) {
-                            tma_store_4d(&tmR, obuf + 4096, hj0, gm0, 0, 0);
-                            tma_store_4d(&tmR, rbuf, p.pair_off + hj0, gm0, 0, 0);
+                        for (int j = 0; j < 32; ++j) {
+                            gv[j] += __ldg(p.bias + hj0 + j);
+                            uv[j] += __ldg(p.bias + p.pair_off + hj0 + j);
                         }
                     }
-                    tma_store_commit();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        // sigmoid from ex2.approx and an approximate reciprocal (relative error ~1e-6, far below bf16's)
+                        const float sg = __fdividef(1.0f, 1.0f + ex2_approx(-gv[j] * 1.4426950408889634f));
+                        hv[j] = gv[j] * sg * uv[j];
+                    }
+                    if (lane == 0) tma_store_wait_read<0>();            // the previous chunk's stores have left the buffers
+                    __syncwarp();
+                    auto stage_bf16 = [&](uint8_t* base, const float (&o)[32]) {
+                        uint8_t* orow = base + lane * 64;               // 32 x 64 B, 64B swizzle
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 pk;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * j + 0], o[8 * j + 1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * j + 2], o[8 * j + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * j + 4], o[8 * j + 5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * j + 6], o[8 * j + 7]);
+                            pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(orow + ((j ^ ((lane >> 1) & 3)) << 4)) = pk;
+                        }
+                    };
+                    stage_bf16(obuf, hv);
+                    if (p.keep_gu) { stage_bf16(obuf + 4096, gv); stage_bf16(rbuf, uv); }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rows_in) {
+                            tma_store_4d(&tmC, obuf, hj0, gm0, 0, 0);
+                            if (p.keep_gu) {
+                                tma_store_4d(&tmR, obuf + 4096, hj0, gm0, 0, 0);
+                                tma_store_4d(&tmR, rbuf, p.pair_off + hj0, gm0, 0, 0);
+                            }
+                        }
+                        tma_store_commit();
+                    }
                 }
                 ++it;
                 continue;
@@ -521,7 +557,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!ok) break;
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) { if (PAIR) mbar_arrive_leader(&acc_empty[buf]); else mbar_arrive(&acc_empty[buf]); }
             ++it;
         }
         if (lane == 0) tma_store_wait_read<0>();
@@ -535,8 +571,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int cg = lane & 7;                       // 0..7 -> columns 4*cg..4*cg+3
         int it = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            const TileCoord c = tile_of<BN, BKE>(p, t);
+        for (int t = worker; t < total_tiles && ok; t += nworkers) {
+            const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
             if (c.skip) continue;
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -629,7 +665,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) { if (PAIR) mbar_arrive_leader(&acc_empty[buf]); else mbar_arrive(&acc_empty[buf]); }
             ++it;
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 3); }
@@ -644,9 +680,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync();          // the other CTA has read its accumulators and needs none of this CTA's barriers any more
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+        if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+        else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
 }
 
@@ -807,9 +845,9 @@ static int make_map_out(CUtensorMap* map, const void* ptr, int elem_bytes, long 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
-    if (a.swiglu_h) return 128;              // the paired gate/up tile
-    if (a.ce_mode != 0) return 192;          // the statistics are laid out per 192-column tile
-    if (a.bn == 64 || a.bn == 128 || a.bn == 192) return a.bn;
+    if (a.swiglu_h) return a.bn == 256 && a.N % 256 == 0 ? 256 : 128;     // the paired gate/up tile
+    if (a.ce_mode != 0) return a.bn == 256 ? 256 : 192;     // the statistics are laid out per tile of this width
+    if (a.bn == 64 || a.bn == 128 || a.bn == 192 || a.bn == 256) return a.bn;
     if (a.N <= 64) return 64;
     const long long mt = (a.M + BM - 1) / BM;
     const long long t128 = mt * ((a.N + 127) / 128) * a.batch;
@@ -843,21 +881,28 @@ int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
     return (kb_total + kb_per - 1) / kb_per;     // no empty split
 }
 
-template <int BN, bool TF32>
+template <int BN, bool TF32, bool PAIR = false>
 static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, const CUtensorMap& tmA,
                        const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmR,
                        cudaStream_t stream) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, PAIR>;
     static bool attr_set[64] = {false};
     if (!attr_set[ctx->device & 63]) {
-        TB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, TF32, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
         attr_set[ctx->device & 63] = true;
     }
     const long long total = (long long)p.batch * p.splits * p.mt * p.nt;
-    int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
-    if (grid < 1) grid = 1;
-    TB_CUDA(launch_kernel((gemm_bf16_kernel<BN, TF32>), dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, stream, tmA, tmB, tmC, tmR, p));
+    int grid;
+    if (PAIR) {
+        const long long pairs = ctx->sm_count / 2;
+        grid = 2 * (int)(total < pairs ? total : pairs);      // one cluster of two CTAs per tile in flight
+    } else {
+        grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+    }
+    if (grid < 1) grid = PAIR ? 2 : 1;
+    TB_CUDA(launch_kernel_cluster((gemm_bf16_kernel<BN, TF32, PAIR>), dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES,
+                                  stream, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -878,7 +923,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
                  "fused QKV + position-embedding GEMM: needs a plain NN bf16 product with N = 3*H*hd, hd 32 or 64, T %% 32 == 0");
     }
     if (a.ce_mode != 0) {
-        TB_CHECK(a.kind == GEMM_NT && !a.tf32 && a.batch == 1 && bn == 192 && splits == 1 && a.alpha == 1.0f &&
+        TB_CHECK(a.kind == GEMM_NT && !a.tf32 && a.batch == 1 && (bn == 192 || bn == 256) && splits == 1 && a.alpha == 1.0f &&
                      a.beta == 0.0f && !a.bias && !a.residual && !a.C32 && !a.swiglu_h && a.causal == CAUSAL_NONE && a.ce_targets,
                  "fused cross-entropy GEMM: needs a plain NT bf16 product with 192-column tiles and the targets");
         if (a.ce_mode == 1) TB_CHECK(a.ce_stats && a.ce_ztarget && !a.C16, "cross-entropy pass 1 writes statistics only");
@@ -886,7 +931,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     }
     const bool swiglu = a.swiglu_h != nullptr;
     if (swiglu) {
-        TB_CHECK(a.kind == GEMM_NN && !a.tf32 && a.batch == 1 && bn == 128 && splits == 1 && a.N % 128 == 0 &&
+        TB_CHECK(a.kind == GEMM_NN && !a.tf32 && a.batch == 1 && (bn == 128 || bn == 256) && splits == 1 && a.N % bn == 0 &&
                      a.residual == nullptr && a.alpha == 1.0f && a.beta == 0.0f && !a.C32 && !a.C16 && a.causal == CAUSAL_NONE,
                  "fused SwiGLU GEMM: needs a plain NN bf16 product with N = 2F, F a multiple of 64 (got N=%d)", a.N);
         TB_CHECK(aligned16(a.swiglu_h) && a.ldh % 8 == 0 && (!a.swiglu_gu || (aligned16(a.swiglu_gu) && a.ldgu % 8 == 0)),
@@ -899,12 +944,17 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     const int bke = a.tf32 ? BK_TF32 : BK;
     if (!a_mn) TB_TRY(make_operand_map_es(&tmA, a.A, es, a.K, a.M, a.lda, a.batch, a.strideA, BM));
     else       TB_TRY(make_operand_map_es(&tmA, a.A, es, a.M, a.K, a.lda, a.batch, a.strideA, bke, true));
-    if (!b_mn) TB_TRY(make_operand_map_es(&tmB, a.B, es, a.K, a.N, a.ldb, a.batch, a.strideB, bn));
+    const bool pair = bn == 256;
+    if (pair)
+        TB_CHECK(!a.tf32 && a.batch == 1 && a.causal == CAUSAL_NONE && a.c_inner <= 1,
+                 "256-wide CTA-pair tiles take one plain bf16 product (no batch, no causal mode)");
+    if (!b_mn) TB_TRY(make_operand_map_es(&tmB, a.B, es, a.K, a.N, a.ldb, a.batch, a.strideB, pair ? bn / 2 : bn));
     else       TB_TRY(make_operand_map_es(&tmB, a.B, es, a.N, a.K, a.ldb, a.batch, a.strideB, bke, true));
 
     GemmParams p;
     p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch; p.splits = splits;
-    p.mt = (a.M + BM - 1) / BM; p.nt = (a.N + bn - 1) / bn;
+    p.mt = pair ? (a.M + 2 * BM - 1) / (2 * BM) : (a.M + BM - 1) / BM;      // a pair owns 256 rows
+    p.nt = (a.N + bn - 1) / bn;
     p.a_mn = a_mn; p.b_mn = b_mn; p.causal = (int)a.causal;
     p.err = ctx->d_err;
     if (splits > 1) {
@@ -1009,7 +1059,9 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
             prof_mark(ctx, prof_intern(tag), a.ce_mode == 2 ? 0.0 : 2.0 * macs, in_bytes + out_bytes, stream);
         }
     }
-    if (a.tf32) {
+    if (pair) {
+        TB_TRY((launch_impl<256, false, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+    } else if (a.tf32) {
         if (bn == 64)       TB_TRY((launch_impl<64, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
         else if (bn == 192) TB_TRY((launch_impl<192, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
         else                TB_TRY((launch_impl<128, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
