@@ -220,7 +220,7 @@ def test_bf16_entry_tiles_splits_outputs(tb, oracle, kind):
     C0 = rng.standard_normal((M, N)).astype(np.float32)
     want = oracle.gemm(k // 2, k % 2, A, B, M, N, K, lda, ldb, N, beta=1.0, C_in=C0).reshape(M, N) + bias
     results = []
-    for tile_n, splits in ((128, 1), (64, 1), (192, 1), (128, 8), (64, 5), (192, 3), (0, 0)):
+    for tile_n, splits in ((128, 1), (64, 1), (192, 1), (256, 1), (128, 8), (64, 5), (192, 3), (256, 4), (0, 0)):
         C = dev(C0.copy())
         C16 = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
         tb.gemm_bf16(k, A16, B16, M, N, K, lda, ldb, C32=C, ldc32=N, C16=C16, ldc16=N, bias=dev(bias), beta=1.0,

@@ -110,11 +110,11 @@ struct GemmArgs {
     // columns with their 64 up columns.  swiglu_gu (optional, bf16 [M,2F]) keeps g and u for the backward pass.
     bf16* swiglu_h = nullptr;  long long ldh = 0;
     bf16* swiglu_gu = nullptr; long long ldgu = 0;
-    // Cross-entropy fused into the LM-head product (kind NT, bn = 192, no other output), so that the
+    // Cross-entropy fused into the LM-head product (kind NT, bn = 192 or 256, no other output), so that the
     // [M, N] logits never exist in HBM (the reference writes them and k_cross_entropy reads them back,
     // model/gpu_train.c:378-381, cuda/train_kernels.cu:742-775).
-    //   ce_mode 1: per row and per 96-column tile half, max and sum of exp(z - max) -> ce_stats
-    //              [2 * ceil(N/192)][M] float2, and the target's logit -> ce_ztarget[M]
+    //   ce_mode 1: per row and per half tile (bn/2 columns), max and sum of exp(z - max) -> ce_stats
+    //              [2 * ceil(N/bn)][M] float2, and the target's logit -> ce_ztarget[M]
     //   ce_mode 2: the product is formed again and leaves as C16 = (exp(z - ce_lse[row]) - onehot) * ce_scale
     // QKV projection with the position embedding fused (kind NN, N = 3*H*hd, hd 32 or 64, T % 32 == 0, M = B*T):
     // instead of the float32 [M, 3D] projection and k_qkv_rope_split (cuda/train_kernels.cu:573-597), the

@@ -845,23 +845,37 @@ static int make_map_out(CUtensorMap* map, const void* ptr, int elem_bytes, long 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
-    if (a.swiglu_h) return a.bn == 256 && a.N % 256 == 0 ? 256 : 128;     // the paired gate/up tile
+    // time ~ waves x tile width x a factor for how often a tile re-reads its operands from L2
+    // (flops per operand byte: 43 for 128x64, 64 for 128x128, 77 for 128x192, 128 for a CTA pair on 256x256).
+    // 256 = a CTA pair on a 256 x 256 tile: per output element a CTA pulls 0.6x the operand bytes of a
+    // 128 x 192 tile through its L2 port (the limit of the main loop); its waves are counted in CTA pairs.
+    const bool pair_ok = !a.tf32 && a.batch == 1 && a.causal == CAUSAL_NONE && a.c_inner <= 1 && a.M >= 512 &&
+                         getenv("TB_GEMM_NO_PAIR") == nullptr;
+    const long long mt = (a.M + BM - 1) / BM;
+    auto cost_of = [&](int width) -> double {
+        static const double factor[4] = {1.30, 1.00, 0.95, 0.70};
+        if (width == 256) {
+            const long long tiles = ((a.M + 2 * BM - 1) / (2 * BM)) * ((a.N + 255) / 256);
+            const long long pairs = ctx->sm_count / 2;
+            // a narrow output wastes part of the second 256-wide column of tiles; only a long K loop pays for that
+            const double narrow = (a.N < 512 && a.K < 4096) ? 1.15 : 1.0;
+            return (double)((tiles + pairs - 1) / pairs) * 256 * factor[3] * narrow;
+        }
+        const long long tiles = mt * ((a.N + width - 1) / width) * a.batch;
+        return (double)((tiles + ctx->sm_count - 1) / ctx->sm_count) * width * factor[width / 64 - 1];
+    };
+    if (a.swiglu_h)      // paired gate/up tile: 128 wide, or 256 wide on a CTA pair
+        return ((a.bn == 256 || (a.bn == 0 && pair_ok && cost_of(256) < cost_of(128))) && a.N % 256 == 0) ? 256 : 128;
     if (a.ce_mode != 0) return a.bn == 256 ? 256 : 192;     // the statistics are laid out per tile of this width
     if (a.bn == 64 || a.bn == 128 || a.bn == 192 || a.bn == 256) return a.bn;
     if (a.N <= 64) return 64;
-    const long long mt = (a.M + BM - 1) / BM;
     const long long t128 = mt * ((a.N + 127) / 128) * a.batch;
     if (t128 * 2 <= ctx->sm_count && a.K >= 16 * (a.tf32 ? BK_TF32 : BK)) return 128;      // split-K will fill the machine
-    // time ~ waves x tile width x a factor for how often a tile re-reads its operands from L2
-    // (flops per operand byte: 43 for 128x64, 64 for 128x128, 77 for 128x192)
-    const int widths[3] = {64, 128, 192};
-    const double factor[3] = {1.30, 1.00, 0.95};
+    const int widths[4] = {64, 128, 192, 256};
     int best = 128;
     double best_cost = 1e30;
-    for (int i = 0; i < 3; ++i) {
-        const long long tiles = mt * ((a.N + widths[i] - 1) / widths[i]) * a.batch;
-        const long long waves = (tiles + ctx->sm_count - 1) / ctx->sm_count;
-        const double cost = (double)waves * widths[i] * factor[i];
+    for (int i = 0; i < (pair_ok ? 4 : 3); ++i) {
+        const double cost = cost_of(widths[i]);
         if (cost < best_cost - 1e-9) { best_cost = cost; best = widths[i]; }
     }
     if (a.causal != CAUSAL_NONE && best == 192) best = 128;     // the causal tile rules assume 64 | 128 columns
@@ -870,11 +884,13 @@ static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
 
 int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
     if (a.causal != CAUSAL_NONE) return 1;
-    const long long tiles = (long long)((a.M + BM - 1) / BM) * ((a.N + bn - 1) / bn) * a.batch;
+    const int tile_m = bn == 256 ? 2 * BM : BM;                     // a CTA pair owns 256 rows
+    const int workers = bn == 256 ? ctx->sm_count / 2 : ctx->sm_count;
+    const long long tiles = (long long)((a.M + tile_m - 1) / tile_m) * ((a.N + bn - 1) / bn) * a.batch;
     const int bke = a.tf32 ? BK_TF32 : BK;
     const int kb_total = (a.K + bke - 1) / bke;
-    if (tiles * 2 > ctx->sm_count || kb_total < 16) return 1;
-    int s = (int)(ctx->sm_count / tiles);
+    if (tiles * 2 > workers || kb_total < 16) return 1;
+    int s = (int)(workers / tiles);
     if (s > kb_total / 4) s = kb_total / 4;     // at least 4 K slices per split
     if (s < 1) s = 1;
     const int kb_per = (kb_total + s - 1) / s;

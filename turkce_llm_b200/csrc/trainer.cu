@@ -105,6 +105,8 @@ int dalloc(TbTrainer* g, T** p, size_t count) {
     return 0;
 }
 
+constexpr int kCeTile = 256;      // tile width of the LM-head products with the fused cross-entropy (a CTA pair)
+
 inline long long pidx(int layer, int k) { return 1 + 10LL * layer + k; }
 inline float* P32(TbTrainer* g, long long i) { return g->params + g->offsets[i]; }
 inline bf16* P16(TbTrainer* g, long long i) { return g->params16 + g->offsets[i]; }
@@ -216,11 +218,11 @@ int forward(TbTrainer* g, bool want_grad) {
         // and stores (softmax - onehot) / N directly (gpu_train.c:381)
         GemmArgs a;
         a.kind = GEMM_NT; a.A = g->nf; a.B = P16(g, 0); a.M = N; a.N = V; a.K = D; a.lda = D; a.ldb = D;
-        a.splits = 1; a.bn = 192; a.ce_targets = g->targets;
+        a.splits = 1; a.bn = kCeTile; a.ce_targets = g->targets;
         GemmArgs s1 = a;
         s1.ce_mode = 1; s1.ce_stats = g->ce_stats; s1.ce_ztarget = g->ce_zt;
         TB_TRY(gemm(g, s1));
-        TB_TRY(launch_ce_combine(c, g->ce_stats, 2 * ((V + 191) / 192), N, g->ce_zt, g->ce_lse, g->loss_rows, st));
+        TB_TRY(launch_ce_combine(c, g->ce_stats, 2 * ((V + kCeTile - 1) / kCeTile), N, g->ce_zt, g->ce_lse, g->loss_rows, st));
         if (want_grad) {
             GemmArgs s2 = a;
             s2.ce_mode = 2; s2.ce_lse = g->ce_lse; s2.ce_scale = 1.0f / (float)N;
@@ -514,7 +516,7 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
     TB_TRY(dalloc(g, &g->x_final, N * D)); TB_TRY(dalloc(g, &g->nf, N * D)); TB_TRY(dalloc(g, &g->rf, N));
     g->fused_ce = getenv("TB_NO_FUSED_CE") == nullptr;
     if (g->fused_ce) {
-        TB_TRY(dalloc(g, &g->ce_stats, (size_t)2 * ((V + 191) / 192) * N * 2));
+        TB_TRY(dalloc(g, &g->ce_stats, (size_t)2 * ((V + kCeTile - 1) / kCeTile) * N * 2));
         TB_TRY(dalloc(g, &g->ce_zt, N)); TB_TRY(dalloc(g, &g->ce_lse, N));
     } else {
         TB_TRY(dalloc(g, &g->logits, N * g->Vp));
