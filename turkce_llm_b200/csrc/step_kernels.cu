@@ -776,6 +776,71 @@ int launch_swiglu_bwd_bf16(DeviceCtx* ctx, const bf16* gu, const float* dh, bf16
     return 0;
 }
 
+// The same backward with the bias gradient of the gate|up projection (column sums of dgu, the reference's
+// k_colsum_acc on it, cuda/train_kernels.cu:518-531) taken on the way: a thread owns four hidden units (four
+// gate and four up columns) and walks its block's rows, so the eight column sums stay in its registers; each
+// block leaves one partial row [2F] (sums of the bf16-rounded values, exactly what a column sum of dgu would
+// add) and norm_partial_sum_kernel adds the partial rows in block order.
+__global__ void swiglu_bwd_colsum_kernel(const bf16* __restrict__ gu, const float* __restrict__ dh,
+                                         bf16* __restrict__ dgu, float* __restrict__ partial, int rows, int F) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int rows_per = (rows + gridDim.x - 1) / gridDim.x;
+    const int r0 = blockIdx.x * rows_per, r1 = min(rows, r0 + rows_per);
+    for (int j = threadIdx.x * 4; j < F; j += blockDim.x * 4) {
+        float sg_[4] = {0.f, 0.f, 0.f, 0.f}, su_[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+        for (int n = r0; n < r1; ++n) {
+            float gg[4], uu[4];
+            Load4<bf16>::at(gu + (long long)n * 2 * F + j, gg);
+            Load4<bf16>::at(gu + (long long)n * 2 * F + F + j, uu);
+            const float4 d4 = *reinterpret_cast<const float4*>(dh + (long long)n * F + j);
+            const float dd[4] = {d4.x, d4.y, d4.z, d4.w};
+            bf16 og[4], ou[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float sg = 1.0f / (1.0f + expf(-gg[e]));
+                const float dsilu = dd[e] * uu[e];
+                og[e] = __float2bfloat16_rn(dsilu * sg + dsilu * gg[e] * sg * (1.0f - sg));
+                ou[e] = __float2bfloat16_rn(dd[e] * gg[e] * sg);
+                sg_[e] += __bfloat162float(og[e]);
+                su_[e] += __bfloat162float(ou[e]);
+            }
+            uint2 pg, pu;
+            __nv_bfloat162 a = __halves2bfloat162(og[0], og[1]), b = __halves2bfloat162(og[2], og[3]);
+            __nv_bfloat162 c = __halves2bfloat162(ou[0], ou[1]), d = __halves2bfloat162(ou[2], ou[3]);
+            pg.x = *reinterpret_cast<uint32_t*>(&a); pg.y = *reinterpret_cast<uint32_t*>(&b);
+            pu.x = *reinterpret_cast<uint32_t*>(&c); pu.y = *reinterpret_cast<uint32_t*>(&d);
+            *reinterpret_cast<uint2*>(dgu + (long long)n * 2 * F + j) = pg;
+            *reinterpret_cast<uint2*>(dgu + (long long)n * 2 * F + F + j) = pu;
+        }
+        float* prow = partial + (long long)blockIdx.x * 2 * F;
+        *reinterpret_cast<float4*>(prow + j) = make_float4(sg_[0], sg_[1], sg_[2], sg_[3]);
+        *reinterpret_cast<float4*>(prow + F + j) = make_float4(su_[0], su_[1], su_[2], su_[3]);
+    }
+}
+
+size_t swiglu_bwd_scratch_floats(int F) { return 64 + (size_t)kNormBwdBlocks * 2 * F; }
+
+int launch_swiglu_bwd_colsum(DeviceCtx* ctx, const bf16* gu, const float* dh, bf16* dgu, float* dbias,
+                             float* scratch, int rows, int F, cudaStream_t st) {
+    TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
+    int blocks = rows < kNormBwdBlocks ? rows : kNormBwdBlocks;
+    float* partial = scratch + 64;
+    const int threads = F / 4 >= 256 ? 256 : ((F / 4 + 31) / 32) * 32;
+    prof_mark(ctx, "swiglu_bwd", 0.0, 0.0, st);
+    TB_CUDA(launch_kernel(swiglu_bwd_colsum_kernel, dim3(blocks), dim3(threads), 0, st, gu, dh, dgu, partial, rows, F));
+    TB_LAUNCHED(ctx);
+    // blocks past the last row leave no partial row: only ceil(rows / rows_per) rows are valid
+    const int rows_per = (rows + blocks - 1) / blocks;
+    const int nb = (rows + rows_per - 1) / rows_per;
+    prof_mark(ctx, "colsum_partials", 0.0, 0.0, st);
+    TB_CUDA(launch_kernel(norm_partial_sum_kernel, dim3((2 * F + 31) / 32), dim3(32 * ((nb + 31) / 32)), 0, st,
+                          (const float*)partial, nb, 2 * F, 2 * F, dbias, (float*)nullptr));
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
 // -------------------------------------------------------------- cross-entropy
 __device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;

@@ -47,6 +47,11 @@ int launch_swiglu_fwd(DeviceCtx*, const float* gu, bf16* h, int rows, int F, cud
 int launch_swiglu_bwd(DeviceCtx*, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t);
 // the same with gate|up kept in bf16 by the fused SwiGLU GEMM epilogue
 int launch_swiglu_bwd_bf16(DeviceCtx*, const bf16* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t);
+// ... and with the gate|up bias gradient (dbias[2F] += column sums of dgu) produced on the way;
+// scratch holds swiglu_bwd_scratch_floats(F) floats
+size_t swiglu_bwd_scratch_floats(int F);
+int launch_swiglu_bwd_colsum(DeviceCtx*, const bf16* gu, const float* dh, bf16* dgu, float* dbias, float* scratch,
+                             int rows, int F, cudaStream_t);
 // logits [rows, ld] fp32 -> loss_rows, dlogits bf16 [rows, ld] = (softmax - onehot) * grad_scale
 // combines the per-tile softmax statistics of the fused LM-head GEMM (GemmArgs::ce_mode 1):
 // lse[row] and loss_rows[row] = lse - ztarget[row]; stats is [parts][rows] pairs (max, sum exp)

@@ -65,6 +65,7 @@ struct TbTrainer {
     bf16 *dres16 = nullptr, *dgu = nullptr, *datt = nullptr, *dO = nullptr, *dS = nullptr, *dqkv = nullptr;
     float* colsum_partial = nullptr;
     float* norm_scratch = nullptr;
+    float* swiglu_scratch = nullptr;
     float* splitk_ws = nullptr; size_t splitk_floats = 0;
 
     uint32_t *ids = nullptr, *targets = nullptr;
@@ -277,10 +278,12 @@ int backward_layer(TbTrainer* g, int l) {
     TB_TRY(linear_dw(g, a.h, g->dres16, G32(g, pidx(l, PK_WDOWN)), N, D, F));
     // (b_down's gradient, the column sum of dres, was produced together with dres)
     TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WDOWN)), g->dh, nullptr, N, D, F));
-    if (g->fused_swiglu) TB_TRY(launch_swiglu_bwd_bf16(c, a.gu16, g->dh, g->dgu, N, F, st));
+    // (fused path: the gate|up bias gradient, the column sums of dgu, comes out of the same kernel)
+    if (g->fused_swiglu)
+        TB_TRY(launch_swiglu_bwd_colsum(c, a.gu16, g->dh, g->dgu, G32(g, pidx(l, PK_BGU)), g->swiglu_scratch, N, F, st));
     else TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->dgu, N, F, st));
     TB_TRY(linear_dw(g, a.n2, g->dgu, G32(g, pidx(l, PK_WGU)), N, 2 * F, D));
-    TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
+    if (!g->fused_swiglu) TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
     TB_TRY(linear_dx(g, g->dgu, P16(g, pidx(l, PK_WGU)), g->dn, nullptr, N, 2 * F, D));
     TB_TRY(launch_rmsnorm_bwd_dw(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.r2, g->dn, g->dres, g->dres16,
                                  G32(g, pidx(l, PK_FFN_NORM)), G32(g, pidx(l, PK_BO)), g->norm_scratch, N, D, 1, st));
@@ -539,6 +542,7 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         const size_t nc = colsum_partial_floats(std::max(3 * D, 2 * F)), nn = rmsnorm_bwd_scratch_floats(D);
         TB_TRY(dalloc(g, &g->colsum_partial, nc));
         TB_TRY(dalloc(g, &g->norm_scratch, nn));
+        TB_TRY(dalloc(g, &g->swiglu_scratch, swiglu_bwd_scratch_floats(F)));
         TB_CUDA(cudaMemset(g->colsum_partial, 0, nc * 4));     // ticket words start at zero
         TB_CUDA(cudaMemset(g->norm_scratch, 0, nn * 4));
     }
