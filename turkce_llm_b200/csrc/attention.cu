@@ -106,8 +106,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qb = p.nq - 1 - (int)blockIdx.x;       // heavy (late) query blocks first
-    const int bh = blockIdx.y;
+    // blocks are handed out x fastest: all heads' heaviest (last) query block first, the lightest last,
+    // so the long CTAs start together and the short ones fill the tail
+    const int qb = p.nq - 1 - (int)blockIdx.y;
+    const int bh = blockIdx.x;
     const int q0 = qb * ATT_BM;
     const int nkv = qb + 1;                           // key blocks 0..qb
 
@@ -387,7 +389,9 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, const uint32_t (&v)[32
     }
 }
 
-constexpr int ATT_BWD_THREADS = 320;     // TMA warp, MMA warp, 8 compute warps
+constexpr int ATT_BWD_THREADS = 352;     // TMA warp, score-MMA warp, 8 compute warps, gradient-MMA warp
+// (two issuing threads on different schedulers: one thread cannot issue a block's 24 UMMAs as fast as the
+//  tensor pipe retires them while eight compute warps compete for the same issue slots)
 
 // dK, dV of one key block: walks the query blocks qb = kb .. nq-1.
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
@@ -416,8 +420,8 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kb = blockIdx.x;                 // early key blocks have the most query blocks: they start first
-    const int bh = blockIdx.y;
+    const int kb = blockIdx.y;                 // early key blocks have the most query blocks: all heads' first
+    const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh % p.H;
     const int k0 = kb * ATT_BN;
     const int niter = p.nq - kb;
@@ -458,11 +462,8 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t id_s = umma_idesc(1u, 0u, 0u, 128, 128);      // Q K^T, dO V^T
-            const uint32_t id_t = umma_idesc(1u, 1u, 1u, 128, 64);       // P^T dO, dS^T Q: both MN-major
             const uint64_t dKk = kmajor_tile(smem_u32(sK)), dVk = kmajor_tile(smem_u32(sV));
-            const uint64_t dPm = mnmajor_tile(smem_u32(sP), TILE_BYTES), ddSm = mnmajor_tile(smem_u32(sdS), TILE_BYTES);
             const uint64_t dQk0 = kmajor_tile(smem_u32(sQ)), ddOk0 = kmajor_tile(smem_u32(sdO));
-            const uint64_t dQm0 = mnmajor_tile(smem_u32(sQ), TILE_BYTES), ddOm0 = mnmajor_tile(smem_u32(sdO), TILE_BYTES);
             bool ok = mbar_wait(kv_full, 0, abort_flag);
             // S = Q K^T and dP = dO V^T of query block `it`; may run ahead of the accumulation of it-1
             // because the compute warps free the two score tiles as soon as they hold them in registers
@@ -480,12 +481,21 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 return true;
             };
             if (ok) ok = issue_sdp(0);
+            for (int it = 0; it + 1 < niter && ok; ++it) ok = issue_sdp(it + 1);
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 22); }
+        }
+    } else if (warp == 10) {
+        // second issuer: dV += P^T dO and dK += dS^T Q once the compute warps have written P and dS
+        if (lane == 0) {
+            const uint32_t id_t = umma_idesc(1u, 1u, 1u, 128, 64);       // both operands MN-major
+            const uint64_t dPm = mnmajor_tile(smem_u32(sP), TILE_BYTES), ddSm = mnmajor_tile(smem_u32(sdS), TILE_BYTES);
+            const uint64_t dQm0 = mnmajor_tile(smem_u32(sQ), TILE_BYTES), ddOm0 = mnmajor_tile(smem_u32(sdO), TILE_BYTES);
+            bool ok = true;
             for (int it = 0; it < niter && ok; ++it) {
                 const int s = it & 1;
-                const uint32_t pi = (uint32_t)(it & 1);
                 const uint64_t dQm = dQm0 + (uint64_t)s * TILESTEP, ddOm = ddOm0 + (uint64_t)s * TILESTEP;
-                if (it + 1 < niter && !issue_sdp(it + 1)) { ok = false; break; }
-                if (!mbar_wait(pds_full, pi, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&qdo_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) { ok = false; break; }
+                if (!mbar_wait(pds_full, (uint32_t)(it & 1), abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
@@ -494,10 +504,12 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 for (int k = 0; k < 8; ++k)
                     umma_bf16(tdK, ddSm + k * MNSTEP, dQm + k * MNSTEP, id_t, (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(pds_free);
+                // S and dP of this block (the other issuer's) completed before the compute warps could sign
+                // pds_full, so this commit covers every read of the stage
                 umma_commit(&qdo_empty[s]);
             }
             if (ok) umma_commit(acc_full);
-            if (!ok) { *abort_flag = 1; atomicExch(p.err, 22); }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 24); }
         }
     } else {
         const int q = warp & 3;
@@ -505,14 +517,23 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         const int r = q * 32 + lane;                  // query row inside the block
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         bool ok = true;
+        // the row's log-sum-exp and delta of the NEXT query block are fetched while this one is worked on
+        float lse_next = INFINITY, dl_next = 0.0f;
+        {
+            const int qi0 = kb * ATT_BM + r;
+            if (qi0 < p.T) { lse_next = p.lse[(long long)bh * p.T + qi0] * 1.4426950408889634f; dl_next = p.delta[(long long)bh * p.T + qi0]; }
+        }
         for (int it = 0; it < niter && ok; ++it) {
             const uint32_t pi = (uint32_t)(it & 1);
             const int qb = kb + it;
             const int qi = qb * ATT_BM + r;
-            const bool valid = qi < p.T;
             const bool diag = (qb == kb);
-            const float lse2 = valid ? p.lse[(long long)bh * p.T + qi] * 1.4426950408889634f : INFINITY;
-            const float dl = valid ? p.delta[(long long)bh * p.T + qi] : 0.0f;
+            const float lse2 = lse_next, dl = dl_next;            // +inf for rows past T: P = 0
+            lse_next = INFINITY; dl_next = 0.0f;
+            if (it + 1 < niter && qi + ATT_BM < p.T) {
+                lse_next = p.lse[(long long)bh * p.T + qi + ATT_BM] * 1.4426950408889634f;
+                dl_next = p.delta[(long long)bh * p.T + qi + ATT_BM];
+            }
             if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
             tc_fence_after();
             // this thread's 64 scores and 64 dP values in one TMEM round trip, then the tiles are free
@@ -624,8 +645,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qb = p.nq - 1 - (int)blockIdx.x;
-    const int bh = blockIdx.y;
+    const int qb = p.nq - 1 - (int)blockIdx.y;       // heaviest query blocks of all heads first
+    const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh % p.H;
     const int q0 = qb * ATT_BM;
     const int niter = qb + 1;
@@ -665,10 +686,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t id_s = umma_idesc(1u, 0u, 0u, 128, 128);
-            const uint32_t id_q = umma_idesc(1u, 0u, 1u, 128, 64);       // dS (K-major) x K block (MN-major)
-            const uint64_t dQk = kmajor_tile(smem_u32(sQ)), ddOk = kmajor_tile(smem_u32(sdO)), ddSk = kmajor_tile(smem_u32(sdS));
+            const uint64_t dQk = kmajor_tile(smem_u32(sQ)), ddOk = kmajor_tile(smem_u32(sdO));
             const uint64_t dKk0 = kmajor_tile(smem_u32(sK)), dVk0 = kmajor_tile(smem_u32(sV));
-            const uint64_t dKm0 = mnmajor_tile(smem_u32(sK), TILE_BYTES);
             bool ok = mbar_wait(qdo_full, 0, abort_flag);
             // S and dP of key block `it`; may run ahead of dQ += dS K of it-1 (see the dK/dV kernel)
             auto issue_sdp = [&](int it) -> bool {
@@ -685,22 +704,31 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                 return true;
             };
             if (ok) ok = issue_sdp(0);
+            for (int it = 0; it + 1 < niter && ok; ++it) ok = issue_sdp(it + 1);
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 32); }
+        }
+    } else if (warp == 10) {
+        // second issuer: dQ += dS K once the compute warps have written dS
+        if (lane == 0) {
+            const uint32_t id_q = umma_idesc(1u, 0u, 1u, 128, 64);       // dS (K-major) x K block (MN-major)
+            const uint64_t ddSk = kmajor_tile(smem_u32(sdS));
+            const uint64_t dKm0 = mnmajor_tile(smem_u32(sK), TILE_BYTES);
+            bool ok = true;
             for (int it = 0; it < niter && ok; ++it) {
                 const int s = it & 1;
-                const uint32_t pi = (uint32_t)(it & 1);
                 const uint64_t dKm = dKm0 + (uint64_t)s * TILESTEP;
-                if (it + 1 < niter && !issue_sdp(it + 1)) { ok = false; break; }
-                if (!mbar_wait(ds_full, pi, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&kv_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) { ok = false; break; }
+                if (!mbar_wait(ds_full, (uint32_t)(it & 1), abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                     umma_bf16(tdQ, ddSk + (uint64_t)(k >> 2) * TILESTEP + (uint64_t)(k & 3) * KSTEP, dKm + k * MNSTEP, id_q,
                               (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(ds_free);
-                umma_commit(&kv_empty[s]);
+                umma_commit(&kv_empty[s]);       // S, dP of this block completed before ds_full could be signed
             }
             if (ok) umma_commit(acc_full);
-            if (!ok) { *abort_flag = 1; atomicExch(p.err, 32); }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 34); }
         }
     } else {
         const int q = warp & 3;
@@ -826,7 +854,7 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
         ctx->launches++;
         prof_close(ctx, stream);
     }
-    dim3 grid(p.nq, BH);
+    dim3 grid(BH, p.nq);
     const double tri = (double)BH * T * (double)T * hd;      // one lower-triangular product = tri flops
     prof_mark(ctx, "attention_bwd_dkdv", 4.0 * tri, (double)BH * T * hd * (2.0 * 4 + 8.0), stream);
     TB_CUDA(launch_kernel(attention_bwd_dkdv_kernel, dim3(grid), dim3(ATT_BWD_THREADS), ATT_DKDV_SMEM, stream, tmQ, tmK, tmV, tmdO, p));
@@ -863,7 +891,7 @@ int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
         TB_CUDA(cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_FWD_SMEM));
         attr_set[ctx->device & 63] = true;
     }
-    dim3 grid(p.nq, BH);
+    dim3 grid(BH, p.nq);
     // algorithmic work: the lower triangle of two products of 2*T*T*hd flops each
     prof_mark(ctx, "attention_fwd", 2.0 * (double)BH * T * (double)T * hd, (double)BH * T * hd * 2.0 * 4.0, stream);
     TB_CUDA(launch_kernel(attention_fwd_kernel, dim3(grid), dim3(192), ATT_FWD_SMEM, stream, tmQ, tmK, tmV, p));
