@@ -439,7 +439,7 @@ __global__ void attn_decode_kernel(const float* __restrict__ Q, const bf16* __re
                                    int H, int hd, int cap, float scale) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float sh[];            // q [hd] | p [cap] | red [32] | part [2][hd]
+    extern __shared__ float sh[];            // q [hd] | p [cap] | red [32] | part [groups][hd]
     float* q = sh;
     float* p = sh + hd;
     float* red = p + cap;
@@ -477,27 +477,38 @@ __global__ void attn_decode_kernel(const float* __restrict__ Q, const bf16* __re
         sum += e;
     }
     sum = block_reduce(sum, red, false);
-    // output: thread (g, d) adds keys g, g+G, ... for dimension d; the G partial sums are added in order
-    const int G = min(nt / hd, 2);           // one or two groups of hd threads share the keys
-    const int g = tid / hd, d = tid % hd;
-    float acc = 0.0f;
-    if (g < G)
-        for (int l = g; l < L; l += G) acc += p[l] * __bfloat162float(Vb[(long long)l * hd + d]);
-    if (g < G) part[g * hd + d] = acc;
+    // output: thread (g, c) adds keys g, g+G, ... for head dims 4c..4c+3 (one 8-byte load per key); the G
+    // partial sums are added in group order
+    const int C = hd >> 2;                   // threads per key group
+    const int G = nt / C;
+    const int g = tid / C, c4 = (tid % C) * 4;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (g < G) {
+        for (int l = g; l < L; l += G) {
+            const uint2 v = *reinterpret_cast<const uint2*>(Vb + (long long)l * hd + c4);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            const float w = p[l];
+            a0 += w * lo.x; a1 += w * lo.y; a2 += w * hi.x; a3 += w * hi.y;
+        }
+        float* dst = part + g * hd + c4;
+        dst[0] = a0; dst[1] = a1; dst[2] = a2; dst[3] = a3;
+    }
     __syncthreads();
-    if (g == 0) {
-        float o = part[d];
-        if (G > 1) o += part[hd + d];
-        att[(long long)sq * (H * hd) + h * hd + d] = __float2bfloat16_rn(o / sum);
+    if (tid < hd) {
+        float o = part[tid];
+        for (int k = 1; k < G; ++k) o += part[k * hd + tid];
+        att[(long long)sq * (H * hd) + h * hd + tid] = __float2bfloat16_rn(o / sum);
     }
 }
 
 int launch_attn_decode(DeviceCtx* ctx, const float* Q, const bf16* Kc, const bf16* Vc, bf16* att, const int* pos, int S,
                        int H, int hd, int cap, float scale, cudaStream_t st) {
     TB_CHECK(hd <= 128 && hd % 8 == 0, "decode attention needs head_dim <= 128 and a multiple of 8");
-    int threads = (2 * hd + 31) / 32 * 32;   // two key groups of hd threads
-    if (threads < 64) threads = 64;
-    const size_t smem = (size_t)(hd + cap + 32 + 2 * hd) * sizeof(float);
+    TB_CHECK(hd % 4 == 0, "decode attention needs a head_dim that is a multiple of 4");
+    const int threads = 256 / (hd / 4) * (hd / 4) >= 64 ? 256 / (hd / 4) * (hd / 4) : 64;     // whole key groups of hd/4 threads
+    const int groups = threads / (hd / 4);
+    const size_t smem = (size_t)(hd + cap + 32 + groups * hd) * sizeof(float);
     TB_CHECK(smem <= 48 * 1024, "KV cache capacity %d too large for the decode attention kernel", cap);
     dim3 grid(H, S);
     prof_mark(ctx, "attn_decode", 0.0, 0.0, st);
