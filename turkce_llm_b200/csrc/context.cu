@@ -41,6 +41,12 @@ int get_ctx(DeviceCtx** out) {
             TB_CHECK(prop.major == 10, "this library is built for sm_100a only; device %d is sm_%d%d", dev, prop.major,
                      prop.minor);
             c->sm_count = prop.multiProcessorCount;
+            // TB_SM_RESERVE=n: the persistent kernels (one CTA per SM) leave n SMs free, e.g. for the
+            // communication kernels of a data-parallel run, whose CTAs would otherwise hold up whole GEMMs
+            if (const char* e = getenv("TB_SM_RESERVE")) {
+                const int n = atoi(e);
+                if (n > 0 && n < c->sm_count - 8) c->sm_count -= n;
+            }
             TB_CUDA(cudaMalloc(&c->d_err, 1024));
             TB_CUDA(cudaMemset(c->d_err, 0, 1024));
             c->d_tickets = reinterpret_cast<unsigned int*>(c->d_err + 32);
