@@ -344,7 +344,7 @@ int backward_embed(TbTrainer* g) {
                             g->D, g->stream);
 }
 
-enum { SEG_FWD_TRAIN = 0, SEG_FWD_EVAL, SEG_HEAD_BWD, SEG_EMBED_BWD, SEG_ZERO, SEG_LAYER0 };
+enum { SEG_FWD_TRAIN = 0, SEG_FWD_EVAL, SEG_HEAD_BWD, SEG_EMBED_BWD, SEG_ZERO, SEG_STEP, SEG_LAYER0 };
 
 // Runs `body` (a fixed sequence of launches on g->stream): eagerly the first time, under stream
 // capture the second time, as a graph launch from then on.
@@ -672,11 +672,15 @@ int tb_trainer_set_inputs(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h
 int tb_trainer_step_resident(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
                              float max_norm) {
     TB_CHECK(g->nseg > 0, "tb_trainer_step_resident: call tb_trainer_set_inputs first");
-    TB_TRY(tb_trainer_zero_grads(g));
-    TB_TRY(tb_trainer_forward_resident(g, 1));
-    TB_TRY(tb_trainer_backward_head(g));
-    for (int l = g->L - 1; l >= 0; --l) TB_TRY(tb_trainer_backward_layer(g, l));
-    TB_TRY(tb_trainer_backward_embed(g));
+    // zeroing, forward and the whole backward are one graph (a single-GPU step has no reason to stop between
+    // layers); the optimiser's scalars change every step, so clip + Adam stay ordinary launches
+    TB_TRY(run_segment(g, SEG_STEP, [&]() {
+        TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->total * 4, g->stream));
+        TB_TRY(forward(g, true));
+        TB_TRY(backward_head(g));
+        for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
+        return backward_embed(g);
+    }));
     return tb_trainer_clip_adam_async(g, t, lr, beta1, beta2, eps, max_norm, 1.0f);
 }
 
