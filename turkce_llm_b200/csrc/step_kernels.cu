@@ -137,10 +137,52 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
     }
 }
 
+// the same with 16-byte loads and 8-byte stores (cols % 4 == 0, cols <= 4 * 32 * NV)
+template <int NV>
+__global__ void rmsnorm_fwd_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                       bf16* __restrict__ out, float* __restrict__ rinv, int rows, int cols, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows;
+         row += (long long)gridDim.x * wpb) {
+        const float* xr = x + row * cols;
+        float4 xv[NV];
+        float ss = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int j = 4 * (lane + 32 * k);
+            xv[k] = j < cols ? *reinterpret_cast<const float4*>(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
+        }
+        ss = warp_sum(ss);
+        const float ms = ss / (float)cols;
+        const float r = 1.0f / (float)sqrt((double)(ms + eps));
+        if (lane == 0) rinv[row] = r;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int j = 4 * (lane + 32 * k);
+            if (j < cols) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + j);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(xv[k].x * r * wv.x, xv[k].y * r * wv.y);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(xv[k].z * r * wv.z, xv[k].w * r * wv.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(out + row * cols + j) = pk;
+            }
+        }
+    }
+}
+
 int launch_rmsnorm_fwd(DeviceCtx* ctx, const float* x, const float* w, bf16* out, float* rinv, int rows, int cols,
                        float eps, cudaStream_t st) {
     prof_mark(ctx, "rmsnorm_fwd", 0.0, 0.0, st);
-    TB_CUDA(launch_kernel(rmsnorm_fwd_kernel, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, out, rinv, rows, cols, eps));
+    if (cols % 4 == 0 && cols <= 384 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 7u) == 0)
+        TB_CUDA(launch_kernel(rmsnorm_fwd_vec_kernel<3>, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, out, rinv, rows, cols, eps));
+    else
+        TB_CUDA(launch_kernel(rmsnorm_fwd_kernel, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, out, rinv, rows, cols, eps));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -238,6 +280,84 @@ __global__ void rmsnorm_bwd_dw_kernel(const float* __restrict__ x, const float* 
     }
 }
 
+// The same kernel with 16-byte accesses: lane owns columns 4*(lane + 32k) .. +3 (cols % 4 == 0), which cuts
+// the load/store instruction count by four -- the kernel is bound by memory requests, not by arithmetic.
+template <int NV>
+__global__ void rmsnorm_bwd_dw_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                          const float* __restrict__ rinv, const float* __restrict__ dy,
+                                          float* __restrict__ dx, bf16* __restrict__ dx16,
+                                          float* __restrict__ partial, int rows, int cols, int accumulate) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ float sh_part[];      // [warps][2 * cols]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wpb = blockDim.x >> 5;
+    const int pc = 2 * cols;
+    float4 acc[NV], accb[NV], wv[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int j = 4 * (lane + 32 * k);
+        acc[k] = make_float4(0.f, 0.f, 0.f, 0.f); accb[k] = acc[k];
+        wv[k] = j < cols ? *reinterpret_cast<const float4*>(w + j) : acc[k];
+    }
+    for (long long row = (long long)blockIdx.x * wpb + warp; row < rows; row += (long long)gridDim.x * wpb) {
+        const float* xr = x + row * cols;
+        const float* dyr = dy + row * cols;
+        float* dxr = dx + row * cols;
+        const float r = rinv[row];
+        float4 xv[NV], dv[NV], ov[NV];
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int j = 4 * (lane + 32 * k);
+            const bool in = j < cols;
+            xv[k] = in ? *reinterpret_cast<const float4*>(xr + j) : z;
+            dv[k] = in ? *reinterpret_cast<const float4*>(dyr + j) : z;
+            ov[k] = (in && accumulate) ? *reinterpret_cast<const float4*>(dxr + j) : z;
+        }
+        float S = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+            S += dv[k].x * wv[k].x * xv[k].x + dv[k].y * wv[k].y * xv[k].y + dv[k].z * wv[k].z * xv[k].z +
+                 dv[k].w * wv[k].w * xv[k].w;
+        S = warp_sum(S);
+        const float kk = (r * r * r) / (float)cols * S;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int j = 4 * (lane + 32 * k);
+            if (j < cols) {
+                float4 v;
+                v.x = wv[k].x * r * dv[k].x - kk * xv[k].x + ov[k].x;
+                v.y = wv[k].y * r * dv[k].y - kk * xv[k].y + ov[k].y;
+                v.z = wv[k].z * r * dv[k].z - kk * xv[k].z + ov[k].z;
+                v.w = wv[k].w * r * dv[k].w - kk * xv[k].w + ov[k].w;
+                *reinterpret_cast<float4*>(dxr + j) = v;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dx16 + row * cols + j) = pk;
+                acc[k].x += dv[k].x * xv[k].x * r; acc[k].y += dv[k].y * xv[k].y * r;
+                acc[k].z += dv[k].z * xv[k].z * r; acc[k].w += dv[k].w * xv[k].w * r;
+                accb[k].x += v.x; accb[k].y += v.y; accb[k].z += v.z; accb[k].w += v.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int j = 4 * (lane + 32 * k);
+        if (j < cols) {
+            *reinterpret_cast<float4*>(sh_part + warp * pc + j) = acc[k];
+            *reinterpret_cast<float4*>(sh_part + warp * pc + cols + j) = accb[k];
+        }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < pc; j += blockDim.x) {
+        float t = sh_part[j];
+        for (int k = 1; k < wpb; ++k) t += sh_part[k * pc + j];
+        partial[(long long)blockIdx.x * pc + j] = t;
+    }
+}
+
 // dw[j] += sum over the partial rows (block order), db likewise: one block per 32 columns, each
 // warp adds up to 32 consecutive partial rows (all loads in flight at once), warp 0 adds the warps.
 __global__ void norm_partial_sum_kernel(const float* __restrict__ partial, int nb, int pc, int cols,
@@ -282,6 +402,8 @@ int launch_rmsnorm_bwd_dw(DeviceCtx* ctx, const float* x, const float* w, const 
     if (!attr_set[ctx->device & 63]) {
         TB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_dw_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kNormBwdWarps * 2 * 384 * (int)sizeof(float)));
+        TB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_dw_vec_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kNormBwdWarps * 2 * 384 * (int)sizeof(float)));
         TB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_dw_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      8 * 2 * 1024 * (int)sizeof(float)));
         attr_set[ctx->device & 63] = true;
@@ -291,7 +413,9 @@ int launch_rmsnorm_bwd_dw(DeviceCtx* ctx, const float* x, const float* w, const 
     float* partial = scratch + 64;
     const int pc = 2 * cols;
     prof_mark(ctx, "rmsnorm_bwd", 0.0, 0.0, st);
-    if (cols <= 384)
+    if (cols % 4 == 0 && cols <= 384)
+        TB_CUDA(launch_kernel((rmsnorm_bwd_dw_vec_kernel<3>), dim3(blocks), dim3(32 * warps), smem, st, x, w, rinv, dy, dx, dx16, partial, rows, cols, accumulate));
+    else if (cols <= 384)
         TB_CUDA(launch_kernel((rmsnorm_bwd_dw_kernel<12>), dim3(blocks), dim3(32 * warps), smem, st, x, w, rinv, dy, dx, dx16, partial, rows, cols, accumulate));
     else
         TB_CUDA(launch_kernel((rmsnorm_bwd_dw_kernel<32>), dim3(blocks), dim3(32 * warps), smem, st, x, w, rinv, dy, dx, dx16, partial, rows, cols, accumulate));
