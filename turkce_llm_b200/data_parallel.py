@@ -5,10 +5,11 @@ The reference runs one sequence per CPU thread on a shadow model and then adds t
 gradients in a fixed order and divides by the worker count (dp_reduce_run, :102-117).  Here every
 rank holds a full replica on its own GPU, processes its own sequences, and the flat float32
 gradient buffer is summed over ranks with one all-reduce per bucket; the division by the number of
-ranks is folded into Adam's gradient scale.  A bucket is one layer's ten tensors (contiguous in the
-flat layout); it is reduced as soon as that layer's backward has been issued, so the transfer
-overlaps the backward of the layers below.  The tied embedding receives gradient both first (LM
-head) and last (token lookup), so its bucket goes last.
+ranks is folded into Adam's gradient scale.  By default the whole flat buffer is reduced by one
+collective after the backward pass (0.4 ms for 134 MB on 8 GPUs).  The bucketed variant -- a bucket is one
+layer's ten tensors (contiguous in the flat layout), reduced as soon as that layer's backward has been
+issued; the tied embedding receives gradient both first (LM head) and last (token lookup), so its bucket
+goes last -- is kept (TB_DP_MODE=overlap): it measures slower with the current GEMM kernels, see below.
 """
 from . import lib
 
@@ -55,6 +56,15 @@ class DataParallelStep:
         self.L = trainer.cfg[3]
         if not check_buckets(buckets, trainer.total):
             raise ValueError("gradient buckets do not tile the flat buffer")
+        # TB_DP_MODE: "end" (default: one all-reduce of the flat buffer after the backward pass), "overlap"
+        # (one all-reduce per layer bucket as soon as the layer's backward has been issued), "halves" (two
+        # collectives), or for diagnosis "none" (no all-reduce: wrong results, timing only).
+        # Measured on 8 B200 (6.10 / 6.40 / 6.16 ms per step against 5.70 ms without any all-reduce): the
+        # persistent GEMM kernels hand out their tiles statically, one CTA per SM, so a communication CTA that
+        # occupies an SM while a GEMM runs holds up that whole GEMM -- the collectives under the backward pass
+        # cost more than the 0.4 ms they hide.
+        import os
+        self.mode = os.environ.get("TB_DP_MODE", "end")
         self.stream = None
         if world > 1:
             # collectives must be ordered against the trainer's own stream: make it torch's current one
@@ -62,7 +72,7 @@ class DataParallelStep:
             self.stream = torch.cuda.ExternalStream(trainer.stream_ptr())
 
     def _reduce(self, name, handles):
-        if self.world > 1:
+        if self.world > 1 and self.mode == "overlap":
             lo, hi = self.buckets[name]
             handles.append(all_reduce_bucket(self.dist, self.grads, lo, hi))
 
@@ -70,11 +80,20 @@ class DataParallelStep:
         g, handles = self.g, []
         g.backward_head()
         self._reduce("final_norm", handles)
+        mid = self.L // 2
         for l in range(self.L - 1, -1, -1):
             g.backward_layer(l)
             self._reduce("layer%d" % l, handles)
+            if self.world > 1 and self.mode == "halves" and l == mid and mid > 0:
+                # layers mid..L-1 and the final norm are final: one collective for the upper part of the buffer
+                handles.append(all_reduce_bucket(self.dist, self.grads, self.buckets["layer%d" % mid][0], self.g.total))
         g.backward_embed()
         self._reduce("embedding", handles)
+        if self.world > 1 and self.mode == "end":       # one collective after the whole backward
+            handles.append(all_reduce_bucket(self.dist, self.grads, 0, self.g.total))
+        if self.world > 1 and self.mode == "halves":
+            hi = self.buckets["layer%d" % mid][0] if mid > 0 else self.g.total
+            handles.append(all_reduce_bucket(self.dist, self.grads, 0, hi))
         for h in handles:
             h.wait()          # orders the optimiser after the collectives on the compute stream
 
