@@ -24,6 +24,8 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <cstring>
 
 namespace tb {
 
@@ -752,7 +754,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static EncodeTiledFn get_encode_fn() {
+static EncodeTiledFn get_driver_encode_fn() {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
         void* p = nullptr;
@@ -764,6 +766,52 @@ static EncodeTiledFn get_encode_fn() {
     }
     return fn;
 }
+
+// Host-side cache of encoded tensor maps, keyed by everything that goes into one (address, extents, strides,
+// box, types): a training loop or a caller of the eager entry points presents the same few dozen matrices
+// again and again, and a map depends on nothing but those numbers, so a hit can never be stale.
+// Direct-mapped, 1024 entries, one mutex; a miss costs the driver call it replaces.
+struct MapKey {
+    uint64_t v[20];
+    bool operator==(const MapKey& o) const { return memcmp(v, o.v, sizeof(v)) == 0; }
+};
+struct MapEntry { MapKey key; CUtensorMap map; bool used; };
+static MapEntry g_map_cache[1024];
+static std::mutex g_map_mutex;
+
+static CUresult encode_cached(CUtensorMap* map, CUtensorMapDataType dtype, cuuint32_t rank, void* ptr,
+                              const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
+                              const cuuint32_t* estr, CUtensorMapInterleave il, CUtensorMapSwizzle sw,
+                              CUtensorMapL2promotion l2, CUtensorMapFloatOOBfill oob) {
+    EncodeTiledFn fn = get_driver_encode_fn();
+    if (fn == nullptr) return CUDA_ERROR_NOT_SUPPORTED;
+    if (rank > 5) return fn(map, dtype, rank, ptr, dims, strides, box, estr, il, sw, l2, oob);
+    MapKey k;
+    memset(&k, 0, sizeof(k));
+    k.v[0] = reinterpret_cast<uint64_t>(ptr);
+    k.v[1] = ((uint64_t)dtype << 40) | ((uint64_t)rank << 32) | ((uint64_t)il << 24) | ((uint64_t)sw << 16) |
+             ((uint64_t)l2 << 8) | (uint64_t)oob;
+    for (cuuint32_t i = 0; i < rank; ++i) {
+        k.v[2 + i] = dims[i];
+        k.v[12 + i] = ((uint64_t)box[i] << 32) | estr[i];
+        if (i + 1 < rank) k.v[7 + i] = strides[i];
+    }
+    uint64_t h = 1469598103934665603ull;
+    for (int i = 0; i < 20; ++i) { h ^= k.v[i]; h *= 1099511628211ull; }
+    MapEntry& e = g_map_cache[(h ^ (h >> 29)) & 1023u];
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        if (e.used && e.key == k) { *map = e.map; return CUDA_SUCCESS; }
+    }
+    const CUresult r = fn(map, dtype, rank, ptr, dims, strides, box, estr, il, sw, l2, oob);
+    if (r == CUDA_SUCCESS) {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        e.key = k; e.map = *map; e.used = true;
+    }
+    return r;
+}
+
+static EncodeTiledFn get_encode_fn() { return get_driver_encode_fn() ? &encode_cached : nullptr; }
 
 // 3-D view (inner, rows, batch) of a bf16 matrix with a 64-element (128-byte) inner box.
 int make_operand_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld, int batch,
