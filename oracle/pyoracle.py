@@ -51,6 +51,13 @@ def build_ref(ref_root):
     return REF_SO
 
 
+def build_ref_gpu(ref_root):
+    """Compile the reference's GPU-resident trainer where it lies into oracle/_ref/librefgpu.so, and its
+    cuda/train_kernels.cu into oracle/_ref/train_kernels.cubin (sm_100a); used on a GPU box only."""
+    subprocess.check_call(["make", "-C", HERE, "refgpu", "REF=" + ref_root], stdout=subprocess.DEVNULL,
+                          stderr=subprocess.DEVNULL)
+
+
 class ModelCfg(C.Structure):
     _fields_ = [("V", C.c_int), ("D", C.c_int), ("H", C.c_int), ("L", C.c_int),
                 ("F", C.c_int), ("T", C.c_int), ("B", C.c_int), ("eps", C.c_float)]

@@ -1,0 +1,114 @@
+"""The trainer at FULL size (33,490,176 parameters, batch 8 x 1024 tokens) against the reference's own
+GPU-resident trainer: model/gpu_train.c unmodified, with the reference's cuda/train_kernels.cu compiled
+for sm_100a, run in a child process (oracle/ref_gpu.py).  The CPU oracle needs hours per step at this size,
+so this is the only full-size check of the gradients and of the 200-step loss trajectory.
+
+Bounds: the reference's own trainer test (tests/test_gpu_train.c:119,128) for the single step; 1 % on every
+loss of the trajectory (the bound the task states)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from conftest import compare_tensor_bad, rel_to_maxabs
+
+pytestmark = pytest.mark.gpu
+
+FULL = (31769, 384, 6, 12, 1024, 1024, 8)       # V, D, H, L, F, T, B
+LOSS_TOL = 2e-2
+GRAD_TOL = 8e-2
+
+
+@pytest.fixture(scope="module")
+def refgpu():
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        pytest.skip("oracle/_ref/librefgpu.so / train_kernels.cubin not built on this machine")
+    return ref_gpu
+
+
+def start_weights(g, seed):
+    """N(0, 0.02) matrices, unit norm weights, zero biases: lm_init's distribution (model/lm_model.c:21-60)."""
+    rng = np.random.default_rng(seed)
+    p = (rng.standard_normal(g.total) * 0.02).astype(np.float32)
+    off, num = g.param_layout()
+    for i, (o, n) in enumerate(zip(off, num)):
+        k = (i - 1) % 10 if 0 < i < len(off) - 1 else -1
+        if i == len(off) - 1 or k in (0, 5):
+            p[o:o + n] = 1.0                     # attn_norm, ffn_norm, final_norm
+        elif k in (2, 4, 7, 9):
+            p[o:o + n] = 0.0                     # b_qkv, bo, b_gate_up, b_down
+    return p
+
+
+def zipf_stream(n, V, seed):
+    return (np.random.default_rng(seed).zipf(1.1, n) % V).astype(np.uint32)
+
+
+def test_full_size_step_matches_reference_gpu_trainer(tb, refgpu, tmp_path):
+    from turkce_llm_b200.gpu_train import GRADS, GpuTrainer
+    V, D, H, L, F, T, B = FULL
+    g = GpuTrainer(V, D, H, L, F, T, B, 1e-5)
+    p = start_weights(g, 21)
+    stream = zipf_stream(B * T + 1, V, 22)
+    ids, tgt = stream[:-1].copy(), stream[1:].copy()
+    np.save(tmp_path / "p.npy", p)
+    np.savez(tmp_path / "batch.npz", ids=ids, tgt=tgt)
+    r = refgpu.run_child(["step", "--cfg", *FULL, "--params", tmp_path / "p.npy", "--tokens", tmp_path / "batch.npz",
+                          "--grads-out", tmp_path / "g.npy", "--out", tmp_path / "step.json"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    want = json.load(open(tmp_path / "step.json"))
+    want_grads = np.load(tmp_path / "g.npy")
+
+    g.upload(p)
+    loss = g.forward_backward(ids, tgt)
+    norm = g.grad_norm()
+    got = g.download(GRADS)
+    assert abs(loss - want["loss"]) <= LOSS_TOL * abs(want["loss"]), (loss, want["loss"])
+    assert abs(norm - want["grad_norm"]) <= 2e-2 * want["grad_norm"], (norm, want["grad_norm"])
+    off, num = g.param_layout()
+    worst = 0.0
+    for i, (o, n) in enumerate(zip(off, num)):
+        a, b = got[o:o + n], want_grads[o:o + n]
+        assert compare_tensor_bad(a, b, GRAD_TOL) == 0, (i, rel_to_maxabs(a, b))
+        worst = max(worst, rel_to_maxabs(a, b))
+    print("full-size step: loss", loss, "reference", want["loss"], "worst gradient tensor error", worst)
+    g.destroy()
+
+
+def test_full_size_loss_trajectory_200_steps(tb, refgpu, ref, tmp_path):
+    """The reference's training loop (training/train_lm_gpu.c:212-223: warm-up schedule, windows drawn with
+    seed 2026 + step, clip at 1.0, scaled Adam) for 200 steps on both trainers from the same weights."""
+    from turkce_llm_b200.gpu_train import AdamState, GpuTrainer
+    V, D, H, L, F, T, B = FULL
+    steps, warmup, total, peak, lo = 200, 1000, 70000, 6e-4, 6e-5
+    g = GpuTrainer(V, D, H, L, F, T, B, 1e-5)
+    p = start_weights(g, 31)
+    tokens = zipf_stream(2_000_000, V, 32)       # stands in for the reference's private corpus
+    np.save(tmp_path / "p.npy", p)
+    np.save(tmp_path / "tok.npy", tokens)
+    r = refgpu.run_child(["trajectory", "--cfg", *FULL, "--params", tmp_path / "p.npy", "--tokens",
+                          tmp_path / "tok.npy", "--steps", steps, "--warmup", warmup, "--total-steps", total,
+                          "--peak-lr", peak, "--min-lr", lo, "--clip", 1.0, "--out", tmp_path / "traj.json"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    want = json.load(open(tmp_path / "traj.json"))
+
+    g.upload(p)
+    opt = AdamState(lr=peak)
+    worst = 0.0
+    losses = []
+    for step in range(steps):
+        opt.lr = float(np.float32(peak) * np.float32(step + 1) / np.float32(warmup))   # training/lr_schedule.c:7-9
+        ids, tgt = ref.sample_batch(tokens, T, B, 2026 + step)
+        loss, _ = g.train_step(ids, tgt, opt, max_norm=1.0)
+        losses.append(loss)
+        worst = max(worst, abs(loss - want["losses"][step]) / abs(want["losses"][step]))
+    out = os.environ.get("TB_TRAJECTORY_OUT")
+    if out:
+        json.dump({"losses": losses, "reference": want}, open(out, "w"))
+    print("trajectory: first", losses[0], want["losses"][0], "last", losses[-1], want["losses"][-1],
+          "worst relative difference", worst, "reference s/step", want["seconds_per_step"])
+    assert worst <= 1e-2, worst
+    assert losses[-1] < losses[0] - 1.0          # it actually trained
+    g.destroy()
