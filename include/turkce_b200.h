@@ -185,6 +185,8 @@ int tb_trainer_destroy(TbTrainer* g);
 int64_t tb_trainer_total_scalars(const TbTrainer* g);
 int tb_trainer_num_params(const TbTrainer* g);                       /* 10*L + 2 */
 int tb_trainer_param_layout(const TbTrainer* g, int64_t* offsets, int64_t* numels);
+/* The architecture and step shape the trainer was created with (any pointer may be NULL). */
+int tb_trainer_dims(const TbTrainer* g, int* V, int* D, int* H, int* L, int* F, int* T, int* B);
 
 /* `which` selects a flat buffer: 0 parameters, 1 gradients, 2 Adam m, 3 Adam v.
  * gpu_trainer_upload / gpu_trainer_upload_grads (model/gpu_train.h:97,103) */
@@ -239,6 +241,34 @@ int tb_trainer_step_resident(TbTrainer* g, uint64_t t, float lr, float beta1, fl
 int tb_trainer_forward_resident(TbTrainer* g, int want_grad);
 /* Gradient norm computed by the last tb_trainer_clip_adam_async (waits for the stream). */
 int tb_trainer_last_norm(TbTrainer* g, double* norm_out);
+
+/* ---- the training loop around the trainer (host code) ---------------------------- */
+
+/* gpu_trainer_sample_batch (model/gpu_train.h:108-109, model/gpu_train.c:296-307; the same windows as the
+ * CPU workers of training/data_parallel.c:73-77): sequence w of the batch starts at a position drawn from
+ * PCG32 seeded (seed_base * 1000003 + w, stream 99 + w), uniformly in [0, num_tokens - T - 1); targets are
+ * the ids shifted by one.  ids_out, targets_out: [B * T].  Host memory only. */
+int tb_sample_batch(const uint32_t* tokens, uint64_t num_tokens, int T, int B, uint64_t seed_base,
+                    uint32_t* ids_out, uint32_t* targets_out);
+/* lr_warmup_cosine (training/lr_schedule.c:6-15): peak * (step + 1) / warmup during warm-up, then a
+ * cosine from peak to min over the remaining steps. */
+float tb_lr_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_t total_steps, float peak_lr, float min_lr);
+/* checkpoint_save / checkpoint_load (training/checkpoint.h:6-12,30-41) on the trainer's device state, in the
+ * reference's "TRLM" version-1 file format, byte for byte: header, per tensor [ndim][shape][values], then,
+ * with_optimizer != 0, per tensor Adam m and v, then the step counter.  Save writes <path>.tmp and renames
+ * it; load validates the whole file against the model before it touches the trainer, and with_optimizer != 0
+ * requires the optimiser state to be in the file.  A checkpoint written by the reference loads here and
+ * the other way round. */
+int tb_checkpoint_save(const char* path, TbTrainer* g, int with_optimizer, uint64_t adam_t);
+int tb_checkpoint_load(const char* path, TbTrainer* g, int with_optimizer, uint64_t* adam_t_out);
+/* The loop of training/train_lm_gpu.c:212-223 for steps [start_step, start_step + num_steps): schedule,
+ * windows drawn with seed 2026 + step, forward, backward, global-norm clip at max_norm, Adam.  *adam_t is
+ * the optimiser's step counter (incremented per step).  The next step's windows are drawn on the host while
+ * the device runs the current step; ids travel through pinned memory; the loss read-back is the only host
+ * synchronisation of a step.  losses_out / norms_out: [num_steps] or NULL. */
+int tb_trainer_run(TbTrainer* g, const uint32_t* tokens, uint64_t num_tokens, uint32_t start_step, uint32_t num_steps,
+                   uint32_t warmup_steps, uint32_t total_steps, float peak_lr, float min_lr, float max_norm,
+                   float beta1, float beta2, float eps, uint64_t* adam_t, float* losses_out, double* norms_out);
 
 /* ---- decoding with a KV cache --------------------------------------------------- */
 

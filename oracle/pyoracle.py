@@ -304,6 +304,13 @@ class Ref:
         L.ref_lm_adam_step.argtypes = [C.c_void_p, C.c_float]
         L.ref_lm_adam_t.restype = u64
         L.ref_lm_adam_t.argtypes = [C.c_void_p]
+        L.ref_lm_set_adam_t.argtypes = [C.c_void_p, u64]
+        L.ref_lm_checkpoint_save.restype = C.c_int
+        L.ref_lm_checkpoint_save.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+        L.ref_lm_checkpoint_load.restype = C.c_int
+        L.ref_lm_checkpoint_load.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+        L.ref_lr_warmup_cosine.restype = C.c_float
+        L.ref_lr_warmup_cosine.argtypes = [u64, u64, u64, C.c_float, C.c_float]
         L.ref_lm_forward_logits.argtypes = [C.c_void_p, _u32p, C.c_uint32, u64, _f32p, u64]
         L.ref_attention_fwd_bwd.argtypes = [_f32p] * 6 + [C.c_uint32, u64, C.c_uint32, C.c_uint32] + [_f32p] * 6 + [u64]
         L.ref_ffn_fwd_bwd.argtypes = [_f32p] * 6 + [u64, C.c_uint32, C.c_uint32] + [_f32p] * 6 + [u64]
@@ -368,6 +375,9 @@ class Ref:
                                  _fp(out), _fp(dx), _fp(dwg), _fp(dbg), _fp(dwd), _fp(dbd), arena)
         return out, dx, dwg, dbg, dwd, dbd
 
+    def lr_warmup_cosine(self, step, warmup, total, peak, min_lr):
+        return float(self.lib.ref_lr_warmup_cosine(step, warmup, total, peak, min_lr))
+
     def sample_batch(self, tokens, T, B, seed_base):
         tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
         ids = np.zeros(B * T, dtype=np.uint32)
@@ -416,6 +426,18 @@ class RefLM:
 
     def adam_step(self, lr):
         self.ref.lib.ref_lm_adam_step(self.h, lr)
+
+    def adam_t(self):
+        return int(self.ref.lib.ref_lm_adam_t(self.h))
+
+    def set_adam_t(self, t):
+        self.ref.lib.ref_lm_set_adam_t(self.h, t)
+
+    def checkpoint_save(self, path, with_opt):
+        return bool(self.ref.lib.ref_lm_checkpoint_save(self.h, str(path).encode(), int(with_opt)))
+
+    def checkpoint_load(self, path, with_opt):
+        return bool(self.ref.lib.ref_lm_checkpoint_load(self.h, str(path).encode(), int(with_opt)))
 
     def forward_logits(self, ids, B, T, arena=4 << 30):
         ids = np.ascontiguousarray(ids, dtype=np.uint32)

@@ -25,6 +25,8 @@
 #include "model/gpu_ops.h"
 #include "training/adam.h"
 #include "training/data_parallel.h"
+#include "training/checkpoint.h"
+#include "training/lr_schedule.h"
 
 #include <stdlib.h>
 #include <string.h>
@@ -199,6 +201,23 @@ void ref_sample_batch(const u32* tokens, u64 num_tokens, u32 T, u32 B, u64 seed_
 
 void ref_lm_adam_step(RefLM* r, float lr) { r->opt.lr = lr; adam_step(&r->opt); }
 u64 ref_lm_adam_t(RefLM* r) { return r->opt.t; }
+void ref_lm_set_adam_t(RefLM* r, u64 t) { r->opt.t = t; }
+
+/* checkpoint_save / checkpoint_load: training/checkpoint.c:24-135.  Return the reference's bool32. */
+int ref_lm_checkpoint_save(RefLM* r, const char* path, int with_opt) {
+    return (int)checkpoint_save(path, r->params, r->np, with_opt ? &r->opt : NULL_PTR);
+}
+int ref_lm_checkpoint_load(RefLM* r, const char* path, int with_opt) {
+    Allocator scratch = allocator_create(ref_lm_total_scalars(r) * 3 * sizeof(f32) + (16ull << 20));
+    int ok = (int)checkpoint_load(&scratch, path, r->params, r->np, with_opt ? &r->opt : NULL_PTR);
+    allocator_destroy(&scratch);
+    return ok;
+}
+
+/* lr_warmup_cosine: training/lr_schedule.c:6-15 */
+float ref_lr_warmup_cosine(u64 step, u64 warmup, u64 total, float peak, float min_lr) {
+    return lr_warmup_cosine(step, warmup, total, peak, min_lr);
+}
 
 /* lm_forward (model/lm_model.c:62-82) on a batch of B stacked sequences;
  * writes logits [B*T, V].  Used as the decode oracle (full recompute). */

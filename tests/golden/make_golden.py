@@ -3,7 +3,7 @@
 Run where the reference checkout is available (it builds oracle/_ref/libref.so from the
 reference's unmodified sources, see oracle/Makefile):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [train_loop]
 
 Inputs come from numpy's seeded generator (reproducible anywhere), outputs from the reference:
 tensor_matmul2d / backward_matmul2d, causal_self_attention, swiglu_feedforward,
@@ -37,7 +37,44 @@ def gemm_inputs(seed, M, K, N):
     return X, W, dY
 
 
+def train_loop_fixtures(ref):
+    """Window sampling (model/gpu_train.c:296-307), learning-rate schedule (training/lr_schedule.c:6-15) and
+    the checkpoint file (training/checkpoint.c:24-74) of the reference's small end-to-end model."""
+    cases = []
+    for num_tokens, T, B, seed_base in [(4000, 12, 5, 2026), (100000, 128, 8, 2027), (2_000_000, 1024, 8, 2226),
+                                        (70, 64, 3, 5), (1 << 20, 256, 64, 123456789)]:
+        tokens = np.arange(num_tokens, dtype=np.uint32)          # ids[w*T] is then the window's start
+        ids, tgt = ref.sample_batch(tokens, T, B, seed_base)
+        assert np.array_equal(tgt, ids + 1)
+        cases.append({"num_tokens": num_tokens, "T": T, "B": B, "seed_base": seed_base,
+                      "starts": [int(x) for x in ids[::T]]})
+    sched = []
+    for step in [0, 1, 10, 999, 1000, 1001, 5000, 35000, 69999, 70000, 90000]:
+        sched.append({"step": step, "lr_bits": int(np.float32(ref.lr_warmup_cosine(step, 1000, 70000, 6e-4, 6e-5))
+                                                   .view(np.uint32))})
+    sched.append({"step": 3, "warmup": 0, "total": 10, "lr_bits": int(np.float32(
+        ref.lr_warmup_cosine(3, 0, 10, 1e-3, 1e-4)).view(np.uint32))})
+    g = np.load(os.path.join(HERE, "model_step_small.npz"))
+    V, D, H, L, F, T, Bn = [int(x) for x in g["dims"]]
+    lm = pyoracle.RefLM(ref, V, D, H, L, F, 1e-5, 1337, 1)
+    lm.set(0, g["params1"]); lm.set(2, g["adam_m"]); lm.set(3, g["adam_v"]); lm.set_adam_t(1)
+    digests = {}
+    for with_opt in (0, 1):
+        path = "/tmp/_golden_ckpt_%d.bin" % with_opt
+        assert lm.checkpoint_save(path, with_opt)
+        data = open(path, "rb").read()
+        digests["with_opt_%d" % with_opt] = {"bytes": len(data), "sha256": hashlib.sha256(data).hexdigest()}
+        os.remove(path)
+    lm.close()
+    json.dump({"windows": cases, "schedule": sched, "checkpoint_of_model_step_small": digests},
+              open(os.path.join(HERE, "train_loop.json"), "w"), indent=1)
+
+
 def main():
+    if len(sys.argv) > 2 and sys.argv[2] == "train_loop":
+        pyoracle.build_ref(sys.argv[1])
+        train_loop_fixtures(pyoracle.Ref())
+        return
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     pyoracle.build_ref(ref_root)
     ref = pyoracle.Ref()
@@ -131,6 +168,7 @@ def main():
     # ---- rope tables and host scalars
     c, s = ref.rope_tables(32, 16)
     np.savez_compressed(os.path.join(HERE, "rope_tables.npz"), cos=c, sin=s)
+    train_loop_fixtures(ref)
     print("golden fixtures written to", HERE)
 
 

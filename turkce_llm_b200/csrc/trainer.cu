@@ -610,6 +610,18 @@ int tb_trainer_destroy(TbTrainer* g) {
 int64_t tb_trainer_total_scalars(const TbTrainer* g) { return g->total; }
 int tb_trainer_num_params(const TbTrainer* g) { return (int)g->offsets.size(); }
 
+int tb_trainer_dims(const TbTrainer* g, int* V, int* D, int* H, int* L, int* F, int* T, int* B) {
+    TB_CHECK(g, "tb_trainer_dims: null trainer");
+    if (V) *V = g->V;
+    if (D) *D = g->D;
+    if (H) *H = g->H;
+    if (L) *L = g->L;
+    if (F) *F = g->F;
+    if (T) *T = g->T;
+    if (B) *B = g->B;
+    return 0;
+}
+
 int tb_trainer_param_layout(const TbTrainer* g, int64_t* offsets, int64_t* numels) {
     for (size_t i = 0; i < g->offsets.size(); ++i) { offsets[i] = g->offsets[i]; numels[i] = g->numels[i]; }
     return 0;

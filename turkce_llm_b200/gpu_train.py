@@ -156,3 +156,43 @@ class GpuTrainer:
         loss = C.c_float()
         lib.check(self._lib.tb_trainer_read_loss(self.h, C.byref(loss)))
         return loss.value
+
+    # ---- the loop around the trainer (training/train_lm_gpu.c:195-260)
+    def run(self, tokens, start_step, num_steps, opt, warmup_steps, total_steps, peak_lr, min_lr, max_norm=1.0):
+        """Steps [start_step, start_step + num_steps) of the reference's training loop; returns (losses, norms).
+        opt.t advances by num_steps."""
+        tokens, pt = _u32(tokens)
+        losses = np.empty(num_steps, dtype=np.float32)
+        norms = np.empty(num_steps, dtype=np.float64)
+        t = C.c_uint64(opt.t)
+        lib.check(self._lib.tb_trainer_run(self.h, pt, tokens.size, start_step, num_steps, warmup_steps, total_steps,
+                                           peak_lr, min_lr, max_norm, opt.beta1, opt.beta2, opt.eps, C.byref(t),
+                                           losses.ctypes.data, norms.ctypes.data))
+        opt.t = t.value
+        return losses, norms
+
+    def save_checkpoint(self, path, opt=None):
+        """checkpoint_save (training/checkpoint.h:30): the reference's TRLM file; opt adds Adam m, v and t."""
+        lib.check(self._lib.tb_checkpoint_save(str(path).encode(), self.h, int(opt is not None),
+                                               opt.t if opt is not None else 0))
+
+    def load_checkpoint(self, path, opt=None):
+        """checkpoint_load (training/checkpoint.h:41): raises and leaves the trainer untouched on any mismatch."""
+        t = C.c_uint64(0)
+        lib.check(self._lib.tb_checkpoint_load(str(path).encode(), self.h, int(opt is not None), C.byref(t)))
+        if opt is not None:
+            opt.t = t.value
+
+
+def sample_batch(tokens, T, B, seed_base):
+    """gpu_trainer_sample_batch (model/gpu_train.c:296-307): the B windows of one step and their targets."""
+    tokens, pt = _u32(tokens)
+    ids = np.empty(B * T, dtype=np.uint32)
+    tgt = np.empty(B * T, dtype=np.uint32)
+    lib.check(lib.load().tb_sample_batch(pt, tokens.size, T, B, seed_base, ids.ctypes.data, tgt.ctypes.data))
+    return ids, tgt
+
+
+def lr_warmup_cosine(step, warmup_steps, total_steps, peak_lr, min_lr):
+    """lr_warmup_cosine (training/lr_schedule.c:6-15)."""
+    return float(lib.load().tb_lr_warmup_cosine(step, warmup_steps, total_steps, peak_lr, min_lr))

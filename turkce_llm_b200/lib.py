@@ -77,6 +77,13 @@ SIGNATURES = {
     "tb_trainer_step_resident": (_i, [_vp, C.c_uint64, _f, _f, _f, _f, _f]),
     "tb_trainer_forward_resident": (_i, [_vp, _i]),
     "tb_trainer_last_norm": (_i, [_vp, C.POINTER(C.c_double)]),
+    "tb_trainer_dims": (_i, [_vp] + [C.POINTER(_i)] * 7),
+    "tb_sample_batch": (_i, [_vp, C.c_uint64, _i, _i, C.c_uint64, _vp, _vp]),
+    "tb_lr_warmup_cosine": (_f, [C.c_uint64, C.c_uint64, C.c_uint64, _f, _f]),
+    "tb_checkpoint_save": (_i, [C.c_char_p, _vp, _i, C.c_uint64]),
+    "tb_checkpoint_load": (_i, [C.c_char_p, _vp, _i, C.POINTER(C.c_uint64)]),
+    "tb_trainer_run": (_i, [_vp, _vp, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _f, _f, _f,
+                            _f, _f, _f, C.POINTER(C.c_uint64), _vp, _vp]),
 }
 
 _lib = None
