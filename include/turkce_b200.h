@@ -227,7 +227,8 @@ int tb_trainer_forward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_ta
 int tb_trainer_backward_head(TbTrainer* g);
 int tb_trainer_backward_layer(TbTrainer* g, int layer);
 int tb_trainer_backward_embed(TbTrainer* g);
-/* grad_scale multiplies the gradients before the norm is applied (1/world_size after a sum). */
+/* grad_scale multiplies the gradients before the norm is taken and clipped (1/world_size after a sum over
+ * ranks, 1/micro-batches after accumulation): the reported and clipped norm is that of the averaged gradients. */
 int tb_trainer_clip_adam_async(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
                                float max_norm, float grad_scale);
 int tb_trainer_read_loss(TbTrainer* g, float* loss_out);
@@ -250,6 +251,11 @@ int tb_trainer_last_norm(TbTrainer* g, double* norm_out);
  * the ids shifted by one.  ids_out, targets_out: [B * T].  Host memory only. */
 int tb_sample_batch(const uint32_t* tokens, uint64_t num_tokens, int T, int B, uint64_t seed_base,
                     uint32_t* ids_out, uint32_t* targets_out);
+/* Sequences [first_sequence, first_sequence + count) of the same step: what one rank of a data-parallel job
+ * draws.  A sequence's window depends on its index in the GLOBAL batch only (the reference's worker w,
+ * training/data_parallel.c:132-133), so the set of windows of a step does not depend on the number of ranks. */
+int tb_sample_batch_range(const uint32_t* tokens, uint64_t num_tokens, int T, int first_sequence, int count,
+                          uint64_t seed_base, uint32_t* ids_out, uint32_t* targets_out);
 /* lr_warmup_cosine (training/lr_schedule.c:6-15): peak * (step + 1) / warmup during warm-up, then a
  * cosine from peak to min over the remaining steps. */
 float tb_lr_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_t total_steps, float peak_lr, float min_lr);

@@ -67,3 +67,112 @@ def test_bucketed_all_reduce_is_the_mean_of_ranks(tmp_path):
     g1 = np.random.default_rng(101).standard_normal(total).astype(np.float32)
     want = (g0 + g1) * np.float32(0.5)
     assert np.array_equal(np.load(out), want)
+
+
+def test_shards_and_micro_batches_cover_the_global_batch():
+    from turkce_llm_b200.data_parallel import micro_batches, shard_sequences
+    import pytest
+    for G, world, micro in ((128, 8, 16), (128, 1, 16), (128, 4, 16), (28, 4, 7), (8, 2, 4)):
+        seen = []
+        for r in range(world):
+            first, count = shard_sequences(G, world, r)
+            for f, c in micro_batches(first, count, micro):
+                seen += list(range(f, f + c))
+        assert seen == list(range(G))
+    with pytest.raises(ValueError):
+        shard_sequences(10, 4, 0)
+    with pytest.raises(ValueError):
+        micro_batches(0, 10, 4)
+
+
+def test_windows_of_a_step_do_not_depend_on_the_number_of_ranks():
+    """Each rank draws its slice of the global batch; together they are the windows one worker would draw."""
+    from turkce_llm_b200.data_parallel import micro_batches, shard_sequences
+    from turkce_llm_b200.gpu_train import sample_batch
+    tokens = np.arange(300000, dtype=np.uint32)
+    T, G = 64, 32
+    whole = sample_batch(tokens, T, G, 2030)[0].reshape(G, T)
+    for world in (1, 2, 4, 8):
+        rows = []
+        for r in range(world):
+            for f, c in micro_batches(*shard_sequences(G, world, r), 4):
+                rows.append(sample_batch(tokens, T, c, 2030, first_sequence=f)[0].reshape(c, T))
+        assert np.array_equal(np.concatenate(rows), whole)
+
+
+class _FakeTrainer:
+    """Stands in for GpuTrainer on CPU: the 'gradient' of a micro-batch is a fixed function of its ids, added
+    into the flat buffer as the device kernels do; Adam is replaced by recording the scaled gradient."""
+
+    def __init__(self, total, L):
+        self.total, self.cfg = total, (0, 0, 0, L)
+        self.grads = torch.zeros(total)
+        self.applied = None
+        self._loss = 0.0
+
+    def stream_ptr(self):
+        return 0
+
+    def zero_grads(self):
+        self.grads.zero_()
+
+    def forward(self, ids, targets, want_grad):
+        self._ids = ids
+        self._loss = float(np.mean(ids))
+
+    def backward_head(self):
+        rng = np.random.default_rng(int(self._ids.sum()))
+        self.grads += torch.from_numpy(rng.standard_normal(self.total).astype(np.float32))
+
+    def backward_layer(self, l):
+        pass
+
+    def backward_embed(self):
+        pass
+
+    def clip_adam_async(self, opt, max_norm, grad_scale):
+        self.applied = self.grads * grad_scale
+
+    def read_loss(self):
+        return self._loss
+
+    def last_norm(self):
+        return float(self.applied.norm())
+
+
+def _micro(seq):
+    ids = np.full(8, seq, dtype=np.uint32)
+    return ids, ids
+
+
+def _accumulate_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from turkce_llm_b200 import data_parallel as dp
+    off, num = layout(50, 32, 2, 48)
+    total = int(off[-1] + num[-1])
+    g = _FakeTrainer(total, 2)
+
+    step = dp.DataParallelStep(g, g.grads, dp.layer_buckets(off, num), world, dist)
+    step.loss_device = "cpu"
+    first, count = dp.shard_sequences(8, world, rank)
+    batches = [_micro(f) for f, _ in dp.micro_batches(first, count, 1)]
+    loss, _ = step.host_accumulate(batches, None, 1.0)
+    if rank == 0:
+        np.save(out, np.concatenate([g.applied.numpy(), [loss]]))
+    dist.destroy_process_group()
+
+
+def test_accumulated_micro_batches_over_two_ranks_give_the_global_mean(tmp_path):
+    world = 2
+    out = str(tmp_path / "acc.npy")
+    mp.spawn(_accumulate_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    got = np.load(out)
+    off, num = layout(50, 32, 2, 48)
+    total = int(off[-1] + num[-1])
+    want = np.zeros(total, dtype=np.float64)
+    for seq in range(8):
+        want += np.random.default_rng(8 * seq).standard_normal(total).astype(np.float32)
+    assert np.allclose(got[:-1], want / 8, rtol=0, atol=2e-6)
+    assert abs(got[-1] - np.mean(np.arange(8))) < 1e-6

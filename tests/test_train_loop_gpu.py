@@ -145,3 +145,42 @@ def test_resume_from_checkpoint_is_bit_identical(tb, tmp_path):
     for w, x in zip((PARAMS, ADAM_M, ADAM_V), want):
         assert np.array_equal(c.download(w).view(np.uint32), x.view(np.uint32))
     c.destroy()
+
+
+def test_micro_batch_accumulation_equals_one_large_batch(tb):
+    """Two micro-batches of 4 sequences accumulated into one optimiser step against one batch of 8 sequences
+    (the fixed-global-batch mode of the data-parallel step): same mean loss and mean gradients up to the
+    summation order; a second run is bit-identical."""
+    from conftest import rel_to_maxabs
+    from turkce_llm_b200.data_parallel import DataParallelStep, layer_buckets, micro_batches, shard_sequences
+    from turkce_llm_b200.gpu_train import GRADS, PARAMS, AdamState, GpuTrainer, sample_batch
+    V, D, H, L, F, T = 500, 64, 2, 2, 128, 64
+    tokens = (np.random.default_rng(4).zipf(1.1, 20000) % V).astype(np.uint32)
+    big = GpuTrainer(V, D, H, L, F, T, 8, 1e-5)
+    p = (np.random.default_rng(5).standard_normal(big.total) * 0.05).astype(np.float32)
+    big.upload(p)
+    ids, tgt = sample_batch(tokens, T, 8, 2026)
+    loss_big = big.forward_backward(ids, tgt)
+    norm_big = big.grad_norm()
+    g_big = big.download(GRADS)
+    big.destroy()
+
+    results = []
+    for _ in range(2):
+        small = GpuTrainer(V, D, H, L, F, T, 4, 1e-5)
+        small.upload(p)
+        step = DataParallelStep(small, None, layer_buckets(*small.param_layout()), 1, None)
+        batches = [sample_batch(tokens, T, c, 2026, first_sequence=f)
+                   for f, c in micro_batches(*shard_sequences(8, 1, 0), 4)]
+        assert np.array_equal(np.concatenate([b[0] for b in batches]), ids)
+        opt = AdamState(lr=1e-3)
+        loss, norm = step.host_accumulate(batches, opt, max_norm=0.0)
+        results.append((loss, norm, small.download(GRADS), small.download(PARAMS)))
+        small.destroy()
+    loss, norm, g_sum, _ = results[0]
+    assert abs(loss - loss_big) <= 1e-5 * abs(loss_big)
+    assert rel_to_maxabs(g_sum * np.float32(0.5), g_big) <= 2e-3
+    assert abs(norm - np.sqrt(np.sum((g_sum.astype(np.float64) * 0.5) ** 2))) <= 1e-4 * norm
+    assert abs(norm - norm_big) <= 2e-3 * norm_big          # the clipped norm is that of the MEAN gradients
+    assert results[1][0] == loss and results[1][1] == norm
+    assert np.array_equal(results[0][3].view(np.uint32), results[1][3].view(np.uint32))

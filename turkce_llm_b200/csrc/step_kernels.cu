@@ -1263,8 +1263,8 @@ int launch_sumsq_partial(DeviceCtx* ctx, const float* x, long long n, float* par
 // The reference sums the block partials on the host in float64 (model/gpu_train.c:508-511); one
 // warp does that sum here so the step needs no host round trip: each lane adds a contiguous run of
 // partials, then a fixed shuffle tree combines the lanes (same order every run).
-__global__ void clip_scale_kernel(const float* __restrict__ partial, float max_norm, float* __restrict__ scalars,
-                                  double* __restrict__ norm64) {
+__global__ void clip_scale_kernel(const float* __restrict__ partial, float max_norm, float grad_scale,
+                                  float* __restrict__ scalars, double* __restrict__ norm64) {
     pdl_wait();
     pdl_launch_dependents();
     if (blockIdx.x != 0 || threadIdx.x >= 32) return;
@@ -1279,16 +1279,18 @@ __global__ void clip_scale_kernel(const float* __restrict__ partial, float max_n
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (threadIdx.x != 0) return;
-    const double norm = sqrt(ss);
+    // the norm that is clipped is that of the gradients Adam will see: after grad_scale (1 / ranks after a sum
+    // over ranks, 1 / micro-batches after accumulation), as the reference clips its averaged gradients
+    const double norm = sqrt(ss) * (double)grad_scale;
     *norm64 = norm;
     scalars[0] = (float)norm;
     scalars[1] = (max_norm > 0.0f && norm > (double)max_norm) ? (float)((double)max_norm / norm) : 1.0f;
 }
 
-int launch_clip_scale(DeviceCtx* ctx, const float* partial, float max_norm, float* scalars, double* norm64,
-                      cudaStream_t st) {
+int launch_clip_scale(DeviceCtx* ctx, const float* partial, float max_norm, float grad_scale, float* scalars,
+                      double* norm64, cudaStream_t st) {
     prof_mark(ctx, "clip_scale", 0.0, 0.0, st);
-    TB_CUDA(launch_kernel(clip_scale_kernel, dim3(1), dim3(32), 0, st, partial, max_norm, scalars, norm64));
+    TB_CUDA(launch_kernel(clip_scale_kernel, dim3(1), dim3(32), 0, st, partial, max_norm, grad_scale, scalars, norm64));
     TB_LAUNCHED(ctx);
     return 0;
 }

@@ -75,7 +75,8 @@ int launch_embed_bwd(DeviceCtx*, const float* dx, const uint32_t* order, const u
 constexpr int kNormBlocks = 1024;
 int launch_sumsq_partial(DeviceCtx*, const float* x, long long n, float* partial, cudaStream_t);
 // scalars[0] = norm (as float), scalars[1] = min(1, max_norm / norm) (1 when max_norm <= 0); norm64 = norm
-int launch_clip_scale(DeviceCtx*, const float* partial, float max_norm, float* scalars, double* norm64, cudaStream_t);
+int launch_clip_scale(DeviceCtx*, const float* partial, float max_norm, float grad_scale, float* scalars,
+                      double* norm64, cudaStream_t);
 // Adam; gradient is multiplied by grad_scale * (*dev_scale if given); writes the bf16 shadow copy too
 int launch_adam(DeviceCtx*, float* p, bf16* p16, const float* g, float* m, float* v, long long n, float lr, float b1,
                 float b2, float eps, float bc1, float bc2, float grad_scale, const float* dev_scale, cudaStream_t);

@@ -75,19 +75,25 @@ struct File {
 
 extern "C" {
 
-int tb_sample_batch(const uint32_t* tokens, uint64_t num_tokens, int T, int B, uint64_t seed_base,
-                    uint32_t* ids_out, uint32_t* targets_out) {
+int tb_sample_batch_range(const uint32_t* tokens, uint64_t num_tokens, int T, int first_sequence, int count,
+                          uint64_t seed_base, uint32_t* ids_out, uint32_t* targets_out) {
     TB_CHECK(tokens && ids_out && targets_out, "tb_sample_batch: null pointer");
-    TB_CHECK(T > 0 && B > 0 && num_tokens > (uint64_t)T + 1, "tb_sample_batch: %llu tokens cannot hold a window of %d + 1",
-             (unsigned long long)num_tokens, T);
+    TB_CHECK(T > 0 && count > 0 && first_sequence >= 0 && num_tokens > (uint64_t)T + 1,
+             "tb_sample_batch: %llu tokens cannot hold a window of %d + 1", (unsigned long long)num_tokens, T);
     const int64_t max_start = (int64_t)(num_tokens - (uint64_t)T - 1);
-    for (int w = 0; w < B; ++w) {
-        Pcg32 rng(seed_base * 1000003ull + (uint64_t)w, 99ull + (uint64_t)w);
+    for (int i = 0; i < count; ++i) {
+        const uint64_t w = (uint64_t)first_sequence + (uint64_t)i;
+        Pcg32 rng(seed_base * 1000003ull + w, 99ull + w);
         const int64_t start = rng.range(0, max_start);
-        std::memcpy(ids_out + (size_t)w * T, tokens + start, (size_t)T * sizeof(uint32_t));
-        std::memcpy(targets_out + (size_t)w * T, tokens + start + 1, (size_t)T * sizeof(uint32_t));
+        std::memcpy(ids_out + (size_t)i * T, tokens + start, (size_t)T * sizeof(uint32_t));
+        std::memcpy(targets_out + (size_t)i * T, tokens + start + 1, (size_t)T * sizeof(uint32_t));
     }
     return 0;
+}
+
+int tb_sample_batch(const uint32_t* tokens, uint64_t num_tokens, int T, int B, uint64_t seed_base,
+                    uint32_t* ids_out, uint32_t* targets_out) {
+    return tb_sample_batch_range(tokens, num_tokens, T, 0, B, seed_base, ids_out, targets_out);
 }
 
 float tb_lr_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_t total_steps, float peak_lr, float min_lr) {

@@ -738,7 +738,7 @@ int tb_trainer_eval_loss(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_
 
 int tb_trainer_grad_norm(TbTrainer* g, double* norm_out) {
     TB_TRY(launch_sumsq_partial(g->ctx, g->grads, g->total, g->norm_partial, g->stream));
-    TB_TRY(launch_clip_scale(g->ctx, g->norm_partial, 0.0f, g->scalars, g->norm64, g->stream));
+    TB_TRY(launch_clip_scale(g->ctx, g->norm_partial, 0.0f, 1.0f, g->scalars, g->norm64, g->stream));
     TB_CUDA(cudaMemcpyAsync(g->h_norm, g->norm64, sizeof(double), cudaMemcpyDeviceToHost, g->stream));
     TB_CUDA(cudaStreamSynchronize(g->stream));
     *norm_out = *g->h_norm;
@@ -757,7 +757,7 @@ int tb_trainer_clip_adam_async(TbTrainer* g, uint64_t t, float lr, float beta1, 
                                float max_norm, float grad_scale) {
     TB_CHECK(t >= 1, "Adam step counter starts at 1");
     TB_TRY(launch_sumsq_partial(g->ctx, g->grads, g->total, g->norm_partial, g->stream));
-    TB_TRY(launch_clip_scale(g->ctx, g->norm_partial, max_norm, g->scalars, g->norm64, g->stream));
+    TB_TRY(launch_clip_scale(g->ctx, g->norm_partial, max_norm, grad_scale, g->scalars, g->norm64, g->stream));
     TB_CUDA(cudaMemcpyAsync(g->h_norm, g->norm64, sizeof(double), cudaMemcpyDeviceToHost, g->stream));
     return adam_launch(g, t, lr, beta1, beta2, eps, grad_scale, g->scalars);
 }

@@ -39,6 +39,22 @@ def check_buckets(buckets, total):
     return pos == total
 
 
+def shard_sequences(global_batch, world, rank):
+    """(first sequence, count) of the global batch that `rank` processes: contiguous slices, as the reference
+    hands sequence w to worker w (training/data_parallel.c:126-135)."""
+    if global_batch % world != 0:
+        raise ValueError("a global batch of %d sequences does not divide over %d ranks" % (global_batch, world))
+    per = global_batch // world
+    return rank * per, per
+
+
+def micro_batches(first, count, micro):
+    """Cuts a rank's slice into micro-batches of `micro` sequences: [(first sequence, count), ...]."""
+    if count % micro != 0:
+        raise ValueError("%d sequences per rank do not divide into micro-batches of %d" % (count, micro))
+    return [(first + i, micro) for i in range(0, count, micro)]
+
+
 def all_reduce_bucket(dist, flat, lo, hi, async_op=True):
     """Sum of flat[lo:hi] over all ranks, in place."""
     return dist.all_reduce(flat[lo:hi], op=dist.ReduceOp.SUM, async_op=async_op)
@@ -66,7 +82,8 @@ class DataParallelStep:
         import os
         self.mode = os.environ.get("TB_DP_MODE", "end")
         self.stream = None
-        if world > 1:
+        self.loss_device = "cuda"      # where the ranks' losses are averaged (the host tests set "cpu")
+        if world > 1 and trainer.stream_ptr():
             # collectives must be ordered against the trainer's own stream: make it torch's current one
             import torch
             self.stream = torch.cuda.ExternalStream(trainer.stream_ptr())
@@ -76,8 +93,14 @@ class DataParallelStep:
             lo, hi = self.buckets[name]
             handles.append(all_reduce_bucket(self.dist, self.grads, lo, hi))
 
-    def _backward(self):
+    def _backward(self, reduce=True):
         g, handles = self.g, []
+        if not reduce:        # a micro-batch that is not the step's last: accumulate locally, no collective
+            g.backward_head()
+            for l in range(self.L - 1, -1, -1):
+                g.backward_layer(l)
+            g.backward_embed()
+            return
         g.backward_head()
         self._reduce("final_norm", handles)
         mid = self.L // 2
@@ -134,3 +157,28 @@ class DataParallelStep:
             self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
             loss = float(t.item()) / self.world
         return loss, g.last_norm()
+
+    def host_accumulate(self, batches, opt, max_norm):
+        """One optimiser step over several micro-batches [(ids, targets), ...] of this rank: the gradients of
+        the micro-batches add up in the flat buffer (every backward kernel accumulates, as the reference's do),
+        the ranks' sums are all-reduced once after the last micro-batch, and 1 / (world * micro-batches) is
+        folded into Adam's gradient scale -- the mean over the global batch, as data_parallel_step defines it
+        (training/data_parallel.c:102-117,150-162).  Returns (mean loss, gradient norm)."""
+        with self._on_stream():
+            g = self.g
+            g.zero_grads()
+            loss = 0.0
+            for i, (ids, targets) in enumerate(batches):
+                g.forward(ids, targets, True)
+                last = i + 1 == len(batches)
+                self._backward(reduce=last)
+                if not last:
+                    loss += g.read_loss()          # before the next forward overwrites the loss rows
+            g.clip_adam_async(opt, max_norm, 1.0 / (self.world * len(batches)))
+            loss = (loss + g.read_loss()) / len(batches)
+            if self.world > 1:
+                import torch
+                t = torch.tensor([loss], device=self.loss_device, dtype=torch.float32)
+                self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+                loss = float(t.item()) / self.world
+            return loss, g.last_norm()

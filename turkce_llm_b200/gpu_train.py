@@ -184,12 +184,14 @@ class GpuTrainer:
             opt.t = t.value
 
 
-def sample_batch(tokens, T, B, seed_base):
-    """gpu_trainer_sample_batch (model/gpu_train.c:296-307): the B windows of one step and their targets."""
+def sample_batch(tokens, T, B, seed_base, first_sequence=0):
+    """gpu_trainer_sample_batch (model/gpu_train.c:296-307): B windows of one step and their targets, starting at
+    sequence `first_sequence` of the global batch (a data-parallel rank draws its own slice)."""
     tokens, pt = _u32(tokens)
     ids = np.empty(B * T, dtype=np.uint32)
     tgt = np.empty(B * T, dtype=np.uint32)
-    lib.check(lib.load().tb_sample_batch(pt, tokens.size, T, B, seed_base, ids.ctypes.data, tgt.ctypes.data))
+    lib.check(lib.load().tb_sample_batch_range(pt, tokens.size, T, first_sequence, B, seed_base, ids.ctypes.data,
+                                               tgt.ctypes.data))
     return ids, tgt
 
 

@@ -79,6 +79,7 @@ SIGNATURES = {
     "tb_trainer_last_norm": (_i, [_vp, C.POINTER(C.c_double)]),
     "tb_trainer_dims": (_i, [_vp] + [C.POINTER(_i)] * 7),
     "tb_sample_batch": (_i, [_vp, C.c_uint64, _i, _i, C.c_uint64, _vp, _vp]),
+    "tb_sample_batch_range": (_i, [_vp, C.c_uint64, _i, _i, _i, C.c_uint64, _vp, _vp]),
     "tb_lr_warmup_cosine": (_f, [C.c_uint64, C.c_uint64, C.c_uint64, _f, _f]),
     "tb_checkpoint_save": (_i, [C.c_char_p, _vp, _i, C.c_uint64]),
     "tb_checkpoint_load": (_i, [C.c_char_p, _vp, _i, C.POINTER(C.c_uint64)]),
