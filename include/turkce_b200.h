@@ -256,6 +256,8 @@ int tb_sample_batch(const uint32_t* tokens, uint64_t num_tokens, int T, int B, u
  * training/data_parallel.c:132-133), so the set of windows of a step does not depend on the number of ranks. */
 int tb_sample_batch_range(const uint32_t* tokens, uint64_t num_tokens, int T, int first_sequence, int count,
                           uint64_t seed_base, uint32_t* ids_out, uint32_t* targets_out);
+/* n draws of pcg_uniform (runtime/prng.c:34-37) from the generator seeded (seed, seq): [0, 1) in steps of 2^-32. */
+int tb_pcg_uniform_fill(uint64_t seed, uint64_t seq, uint64_t n, double* out);
 /* lr_warmup_cosine (training/lr_schedule.c:6-15): peak * (step + 1) / warmup during warm-up, then a
  * cosine from peak to min over the remaining steps. */
 float tb_lr_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_t total_steps, float peak_lr, float min_lr);
@@ -280,9 +282,8 @@ int tb_trainer_run(TbTrainer* g, const uint32_t* tokens, uint64_t num_tokens, ui
 
 /* The reference generates by re-running lm_forward over the whole window for every new token
  * (training/generate.c:186-212, training/chat.c:139-165) and has no KV cache; this engine computes
- * the same last-row logits incrementally.  Greedy choice (argmax; the reference samples with a
- * temperature, training/generate.c:57-73, which stays the caller's business through
- * tb_decoder_read_logits).  max_seqs sequences are decoded in lockstep, each with room for max_len
+ * the same last-row logits incrementally.  The next token is the greedy choice (argmax) unless
+ * tb_decoder_set_sampling selects the reference's temperature sampling.  max_seqs sequences are decoded in lockstep, each with room for max_len
  * positions; the parameters are the trainer's flat float32 layout. */
 typedef struct TbDecoder TbDecoder;
 int tb_decoder_create(TbDecoder** out, int V, int D, int H, int L, int F, int max_seqs, int max_len, float eps,
@@ -292,6 +293,12 @@ int64_t tb_decoder_total_scalars(const TbDecoder* g);
 int tb_decoder_upload(TbDecoder* g, const float* h_flat);
 /* h_ids: [max_seqs, prompt_len] prompt tokens; fills the cache and chooses the first new token. */
 int tb_decoder_prefill(TbDecoder* g, const uint32_t* h_ids, int prompt_len);
+/* sample_next (training/generate.c:57-73): with temperature > 0 every next token (the prefill's included) is
+ * drawn from softmax(logits / temperature) by inverse CDF in ascending token order, float64 running sum.
+ * Sequence s uses the PCG32 stream (seed, seq + s), one pcg_uniform per generated token -- (4242, 7) is the
+ * reference generator's stream for its single sequence.  temperature <= 0 goes back to greedy.  Call before
+ * tb_decoder_prefill; the sampled head writes the [S, V] logits (the greedy head does not). */
+int tb_decoder_set_sampling(TbDecoder* g, float temperature, uint64_t seed, uint64_t seq);
 /* n more tokens per sequence; asynchronous (one CUDA-graph launch per token). */
 int tb_decoder_generate(TbDecoder* g, int n);
 /* h_out: [max_seqs, count], the first `count` generated tokens of every sequence (waits). */

@@ -115,3 +115,76 @@ def test_fused_lmhead_argmax_matches_oracle(tb, oracle, shape):
     clear = (srt[:, -1] - srt[:, -2]) > 4e-2 * np.abs(want).max()
     assert clear.sum() > 0
     assert np.array_equal(t[clear], want.argmax(1)[clear])
+
+
+def sample_next(logits, temperature, u):
+    """sample_next of the reference's generator (training/generate.c:57-73), restated: float32 exponentials of
+    (z - max) / temperature, float64 running sum in ascending token order, first index whose sum reaches u * total."""
+    z = logits.astype(np.float32)
+    e = np.exp((z - z.max()) / np.float32(temperature)).astype(np.float32)
+    c = np.cumsum(e.astype(np.float64))
+    j = int(np.searchsorted(c, u * c[-1], side="left"))
+    return min(j, z.size - 1), c
+
+
+@pytest.mark.parametrize("dims", [(97, 32, 2, 2, 48, 3, 5, 12), (31769, 64, 2, 1, 128, 4, 6, 10)])
+def test_temperature_sampling_follows_the_references_sampler(tb, oracle, dims):
+    """Every sampled token is the reference sampler's choice on the engine's own logits with the reference's
+    uniform draws (PCG32 stream (4242, 7 + s)); the logits themselves still match the oracle's full recompute."""
+    from turkce_llm_b200.decode import Decoder, pcg_uniform
+    V, D, H, L, F, S, prompt_len, n_new = dims
+    cap = prompt_len + n_new + 2
+    p = make_params(oracle, (V, D, H, L, F, 1, 1, 1e-5), 7)
+    dec = Decoder(V, D, H, L, F, S, cap)
+    dec.upload(p)
+    temperature = 0.85                                       # training/generate.c:52
+    dec.set_sampling(temperature, 4242, 7)
+    prompts = np.random.default_rng(8).integers(0, V, (S, prompt_len)).astype(np.uint32)
+    dec.prefill(prompts)
+    u = np.stack([pcg_uniform(4242, 7 + s, cap) for s in range(S)])
+    window = prompts.copy()
+    distinct = set()
+    for step in range(n_new):
+        if step > 0:
+            dec.generate(1)
+        logits = dec.logits()
+        tok = dec.tokens(step + 1)[:, step]
+        for s in range(S):
+            want, c = sample_next(logits[s], temperature, u[s, step])
+            if tok[s] != want:
+                # only a draw that lands within rounding of a boundary of the running sum may differ, by one
+                r = u[s, step] * c[-1]
+                assert abs(int(tok[s]) - want) == 1 and abs(c[min(tok[s], want)] - r) <= 1e-6 * c[-1], (step, s)
+            distinct.add(int(tok[s]))
+        if step == 0 and V < 1000:
+            T = window.shape[1]
+            _, _, full = oracle.model_forward_backward((V, D, H, L, F, T, S, 1e-5), p, window.reshape(-1),
+                                                       np.zeros(S * T, np.uint32), want_grads=False, want_logits=True)
+            assert rel_to_maxabs(logits, full.reshape(S, T, V)[:, -1, :]) <= 2e-2
+        window = np.concatenate([window, tok[:, None].astype(np.uint32)], axis=1)
+    assert len(distinct) > S                                  # it sampled, it did not collapse to one token
+    dec.destroy()
+
+
+def test_sampling_limits_and_reproducibility(tb, oracle):
+    """A vanishing temperature gives the greedy tokens; the same seed gives the same tokens, another seed does
+    not; switching back to temperature 0 restores the greedy engine."""
+    from turkce_llm_b200.decode import Decoder
+    V, D, H, L, F, S, prompt_len, n_new = 300, 64, 2, 2, 128, 4, 9, 16
+    p = make_params(oracle, (V, D, H, L, F, 1, 1, 1e-5), 9)
+    prompts = np.random.default_rng(10).integers(0, V, (S, prompt_len)).astype(np.uint32)
+    dec = Decoder(V, D, H, L, F, S, prompt_len + n_new + 2)
+    dec.upload(p)
+
+    def run(temperature, seed):
+        dec.set_sampling(temperature, seed, 7)
+        dec.prefill(prompts)
+        dec.generate(n_new - 1)
+        return dec.tokens(n_new)
+
+    greedy = run(0.0, 1)
+    assert np.array_equal(run(1e-4, 1), greedy)
+    a, b, c = run(0.85, 4242), run(0.85, 4242), run(0.85, 4243)
+    assert np.array_equal(a, b) and not np.array_equal(a, c) and not np.array_equal(a, greedy)
+    assert np.array_equal(run(0.0, 1), greedy)
+    dec.destroy()

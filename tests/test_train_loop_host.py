@@ -62,3 +62,16 @@ def test_lr_schedule_matches_reference_live(ref):
         assert abs(int(got.view(np.uint32)) - int(want.view(np.uint32))) <= 1, step
         exact += int(got == want)
     assert exact >= 0.99 * len(steps)
+
+
+def test_pcg_uniform_matches_reference(ref):
+    from turkce_llm_b200.decode import pcg_uniform
+    for seed, seq in ((4242, 7), (0, 0), (2**63 + 5, 2**40)):
+        assert np.array_equal(pcg_uniform(seed, seq, 1000), ref.uniform(1000, seed, seq))
+
+
+def test_pcg_uniform_known_values():
+    """The first draws of the reference generator's stream pcg_seed(4242, 7) (training/generate.c:181)."""
+    from turkce_llm_b200.decode import pcg_uniform
+    got = pcg_uniform(4242, 7, 4)
+    assert [int(x * 2**32) for x in got] == [1341512397, 1709436583, 702394695, 2554193518]

@@ -19,6 +19,8 @@
 #include <cstring>
 #include <vector>
 
+#include "pcg32.h"
+
 using namespace tb;
 
 namespace {
@@ -50,6 +52,8 @@ struct TbDecoder {
     uint32_t* h_pinned = nullptr;
     float* splitk_ws = nullptr; size_t splitk_floats = 0;
     int prompt_len = 0, generated = 0;
+    float temperature = 0.f;                   // > 0: temperature sampling with the uniforms in sample_u
+    double* sample_u = nullptr;                // [cap, S]: draw of sequence s for generated token i at i * S + s
     cudaGraphExec_t step_graph = nullptr;
     int step_state = 0;
     long long step_launches = 0;
@@ -113,6 +117,11 @@ int head(TbDecoder* g, const float* src, int rows, int advance_pos) {
     DeviceCtx* c = g->ctx; cudaStream_t st = g->stream;
     TB_TRY(launch_rmsnorm_fwd(c, src, P32(g, pidx(g->L, 0)), g->n, g->r, rows, g->D, g->eps, st));
     g->head_rows = rows;
+    if (g->temperature > 0.f) {
+        TB_TRY(head_logits(g, rows));
+        return launch_sample_rows(c, g->logits, g->sample_u, g->temperature, g->tok, g->out, g->pos, rows, g->V, g->Vp,
+                                  g->cap, advance_pos, st);
+    }
     if (g->fused_head)
         return launch_lmhead_argmax(c, g->n, P16(g, 0), rows, g->V, g->D, true, g->head_best, g->head_ticket,
                                     g->tok, g->out, g->pos, g->cap, advance_pos, nullptr, 0, st);
@@ -250,7 +259,30 @@ int tb_decoder_prefill(TbDecoder* g, const uint32_t* h_ids, int prompt_len) {
     return 0;
 }
 
-// Generates n more tokens per sequence (greedy); the tokens stay on the device until read.
+int tb_decoder_set_sampling(TbDecoder* g, float temperature, uint64_t seed, uint64_t seq) {
+    TB_CHECK(g, "tb_decoder_set_sampling: null decoder");
+    TB_CUDA(cudaSetDevice(g->device));
+    TB_CUDA(cudaStreamSynchronize(g->stream));
+    if (g->step_graph) {                       // the captured step holds the other head: capture again
+        cudaGraphExecDestroy(g->step_graph);
+        g->step_graph = nullptr;
+    }
+    g->step_state = 0;
+    g->temperature = temperature > 0.f ? temperature : 0.f;
+    if (g->temperature > 0.f) {
+        if (!g->sample_u) TB_TRY(dalloc(g, &g->sample_u, (size_t)g->cap * g->S));
+        TB_CHECK(g->logits, "tb_decoder_set_sampling: this decoder was created without a logits buffer");
+        std::vector<double> u((size_t)g->cap * g->S);
+        for (int s = 0; s < g->S; ++s) {
+            Pcg32 rng(seed, seq + (uint64_t)s);
+            for (int i = 0; i < g->cap; ++i) u[(size_t)i * g->S + s] = rng.uniform();
+        }
+        TB_CUDA(cudaMemcpy(g->sample_u, u.data(), u.size() * sizeof(double), cudaMemcpyHostToDevice));
+    }
+    return 0;
+}
+
+// Generates n more tokens per sequence (greedy or sampled); the tokens stay on the device until read.
 int tb_decoder_generate(TbDecoder* g, int n) {
     TB_CUDA(cudaSetDevice(g->device));
     TB_CHECK(g->generated >= 1, "tb_decoder_generate: call tb_decoder_prefill first");

@@ -718,6 +718,84 @@ int launch_argmax_rows(DeviceCtx* ctx, const float* logits, uint32_t* tok, uint3
     return 0;
 }
 
+// Temperature sampling, sample_next of the reference's generator (training/generate.c:57-73):
+// e_j = exp((z_j - max z) / temperature) in float32, r = u * sum_j e_j, the token is the first j whose running
+// sum (float64, ascending j) reaches r; the last index if none does.  One block per sequence; thread t owns the
+// contiguous columns [t * per, (t + 1) * per), so that the running sum is formed in ascending order: per-thread
+// sums in column order, an exclusive scan over the threads in thread order.  u[state[1] * S + s] is the uniform
+// draw of sequence s for generated token number state[1].
+__global__ void __launch_bounds__(1024, 1)
+sample_rows_kernel(const float* __restrict__ logits, const double* __restrict__ u, float temperature,
+                   uint32_t* __restrict__ tok, uint32_t* __restrict__ out, const int* __restrict__ state, int S, int V,
+                   long long ld, int out_ld) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float wmax[32];
+    __shared__ double wsum[32];
+    __shared__ int wfirst[32];
+    const int sq = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* z = logits + (long long)sq * ld;
+    float mx = -3.0e38f;
+    for (int j = tid; j < V; j += blockDim.x) mx = fmaxf(mx, z[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) wmax[warp] = mx;
+    __syncthreads();
+    mx = wmax[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, wmax[w]);
+
+    const int per = (V + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int j0 = min(tid * per, V), j1 = min(j0 + per, V);
+    double local = 0.0;
+    for (int j = j0; j < j1; ++j) local += (double)expf((z[j] - mx) / temperature);
+    // inclusive scan inside the warp, then the warps' totals in warp order
+    double incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    double before = 0.0, total = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+        if (w < warp) before += wsum[w];
+        total += wsum[w];
+    }
+    const double r = u[(long long)state[1] * S + sq] * total;
+    double c = before + (incl - local);
+    int first = 0x7fffffff;
+    if (c + local >= r || j1 == V) {          // the crossing can only lie in a chunk whose end reaches r
+        for (int j = j0; j < j1; ++j) {
+            c += (double)expf((z[j] - mx) / temperature);
+            if (c >= r) { first = j; break; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+    if (lane == 0) wfirst[warp] = first;
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) first = min(first, wfirst[w]);
+        if (first == 0x7fffffff) first = V - 1;
+        tok[sq] = (uint32_t)first;
+        if (out) out[(long long)sq * out_ld + state[1]] = (uint32_t)first;
+    }
+}
+
+int launch_sample_rows(DeviceCtx* ctx, const float* logits, const double* u, float temperature, uint32_t* tok,
+                       uint32_t* out, int* state, int S, int V, long long ld, int out_ld, int advance_pos,
+                       cudaStream_t st) {
+    prof_mark(ctx, "sample_rows", 0.0, 0.0, st);
+    TB_CUDA(launch_kernel(sample_rows_kernel, dim3(S), dim3(1024), 0, st, logits, u, temperature, tok, out,
+                          (const int*)state, S, V, ld, out_ld));
+    TB_LAUNCHED(ctx);
+    prof_mark(ctx, "advance_state", 0.0, 0.0, st);
+    TB_CUDA(launch_kernel(advance_state_kernel, dim3(1), dim3(32), 0, st, state, advance_pos));
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
 // ------------------------------------------------------------- causal softmax
 // Row i of a [T,T] score matrix: p_j = softmax_j(s_j * scale) over j <= i.  The reference adds
 // -1e9 to j > i (model/attention.c:11), which underflows to exactly 0 after exp in float32, so

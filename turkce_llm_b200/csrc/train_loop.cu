@@ -8,42 +8,12 @@
 #include <vector>
 
 #include "common.h"
+#include "pcg32.h"
 #include "turkce_b200.h"
 
 namespace {
 
-// PCG32 (O'Neill's pcg32: 64-bit LCG state, XSH-RR output), seeded and consumed as the reference does
-// (runtime/prng.c:10-32), so that a given (seed, stream) yields the same windows.
-struct Pcg32 {
-    uint64_t state, inc;
-    uint32_t next() {
-        const uint64_t old = state;
-        state = old * 6364136223846793005ull + inc;
-        const uint32_t x = (uint32_t)(((old >> 18u) ^ old) >> 27u);
-        const uint32_t rot = (uint32_t)(old >> 59u);
-        return (x >> rot) | (x << ((32u - rot) & 31u));
-    }
-    Pcg32(uint64_t seed, uint64_t seq) : state(0), inc((seq << 1u) | 1u) {
-        next();
-        state += seed;
-        next();
-    }
-    uint64_t next64() {
-        const uint64_t hi = next();
-        const uint64_t lo = next();
-        return (hi << 32) | lo;
-    }
-    // unbiased draw from [lo, hi): 64-bit values below (2^64 - range) mod range are rejected
-    // (runtime/prng.c:51-70)
-    int64_t range(int64_t lo, int64_t hi) {
-        const uint64_t r = (uint64_t)(hi - lo);
-        if (r == 0) return lo;
-        const uint64_t threshold = (0 - r) % r;
-        uint64_t v;
-        do v = next64(); while (v < threshold);
-        return lo + (int64_t)(v % r);
-    }
-};
+using tb::Pcg32;
 
 struct Dims { int V, D, H, L, F, T, B; };
 
@@ -94,6 +64,13 @@ int tb_sample_batch_range(const uint32_t* tokens, uint64_t num_tokens, int T, in
 int tb_sample_batch(const uint32_t* tokens, uint64_t num_tokens, int T, int B, uint64_t seed_base,
                     uint32_t* ids_out, uint32_t* targets_out) {
     return tb_sample_batch_range(tokens, num_tokens, T, 0, B, seed_base, ids_out, targets_out);
+}
+
+int tb_pcg_uniform_fill(uint64_t seed, uint64_t seq, uint64_t n, double* out) {
+    TB_CHECK(out || n == 0, "tb_pcg_uniform_fill: null pointer");
+    Pcg32 rng(seed, seq);
+    for (uint64_t i = 0; i < n; ++i) out[i] = rng.uniform();
+    return 0;
 }
 
 float tb_lr_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_t total_steps, float peak_lr, float min_lr) {

@@ -1,4 +1,4 @@
-"""Greedy decoding with a KV cache (host-side wrapper of the tb_decoder_* entry points).
+"""Greedy or temperature-sampled decoding with a KV cache (host-side wrapper of the tb_decoder_* entry points).
 
 The reference generates by re-running its full forward per token (training/generate.c:186-212);
 this wrapper keeps that calling shape -- prompts in, tokens out -- over the incremental engine."""
@@ -36,6 +36,11 @@ class Decoder:
             raise ValueError("expected %d scalars, got %d" % (self.total, flat.size))
         lib.check(self._lib.tb_decoder_upload(self.h, flat.ctypes.data))
 
+    def set_sampling(self, temperature, seed=4242, seq=7):
+        """sample_next of training/generate.c:57-73 with the reference generator's PCG32 stream per sequence
+        (seed, seq + s); temperature <= 0 selects the greedy choice again.  Call before prefill."""
+        lib.check(self._lib.tb_decoder_set_sampling(self.h, temperature, seed, seq))
+
     def prefill(self, prompts):
         prompts = np.ascontiguousarray(prompts, dtype=np.uint32)
         assert prompts.shape[0] == self.S
@@ -56,3 +61,10 @@ class Decoder:
 
     def stream_ptr(self):
         return int(self._lib.tb_decoder_stream(self.h) or 0)
+
+
+def pcg_uniform(seed, seq, n):
+    """n draws of the reference's pcg_uniform (runtime/prng.c:34-37) from the stream (seed, seq)."""
+    out = np.empty(n, dtype=np.float64)
+    lib.check(lib.load().tb_pcg_uniform_fill(seed, seq, n, out.ctypes.data))
+    return out

@@ -46,6 +46,7 @@ SIGNATURES = {
     "tb_decoder_destroy": (_i, [_vp]),
     "tb_decoder_total_scalars": (_i64, [_vp]),
     "tb_decoder_upload": (_i, [_vp, _vp]),
+    "tb_decoder_set_sampling": (_i, [_vp, _f, C.c_uint64, C.c_uint64]),
     "tb_decoder_prefill": (_i, [_vp, _vp, _i]),
     "tb_decoder_generate": (_i, [_vp, _i]),
     "tb_decoder_read_tokens": (_i, [_vp, _vp, _i]),
@@ -80,6 +81,7 @@ SIGNATURES = {
     "tb_trainer_dims": (_i, [_vp] + [C.POINTER(_i)] * 7),
     "tb_sample_batch": (_i, [_vp, C.c_uint64, _i, _i, C.c_uint64, _vp, _vp]),
     "tb_sample_batch_range": (_i, [_vp, C.c_uint64, _i, _i, _i, C.c_uint64, _vp, _vp]),
+    "tb_pcg_uniform_fill": (_i, [C.c_uint64, C.c_uint64, C.c_uint64, _vp]),
     "tb_lr_warmup_cosine": (_f, [C.c_uint64, C.c_uint64, C.c_uint64, _f, _f]),
     "tb_checkpoint_save": (_i, [C.c_char_p, _vp, _i, C.c_uint64]),
     "tb_checkpoint_load": (_i, [C.c_char_p, _vp, _i, C.POINTER(C.c_uint64)]),
