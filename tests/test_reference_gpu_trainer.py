@@ -15,7 +15,8 @@ from conftest import compare_tensor_bad, rel_to_maxabs
 
 pytestmark = pytest.mark.gpu
 
-FULL = (31769, 384, 6, 12, 1024, 1024, 8)       # V, D, H, L, F, T, B
+FULL = (31769, 384, 6, 12, 1024, 1024, 8)       # V, D, H, L, F, T, B: training/train_lm_gpu.c
+DEEP = (31769, 384, 6, 24, 1024, 1024, 14)      # the 24-layer model and batch of training/train_faz5.c:30-55
 LOSS_TOL = 2e-2
 GRAD_TOL = 8e-2
 
@@ -46,16 +47,17 @@ def zipf_stream(n, V, seed):
     return (np.random.default_rng(seed).zipf(1.1, n) % V).astype(np.uint32)
 
 
-def test_full_size_step_matches_reference_gpu_trainer(tb, refgpu, tmp_path):
+@pytest.mark.parametrize("shape", [FULL, DEEP], ids=["12_layers_batch_8", "24_layers_batch_14"])
+def test_full_size_step_matches_reference_gpu_trainer(tb, refgpu, tmp_path, shape):
     from turkce_llm_b200.gpu_train import GRADS, GpuTrainer
-    V, D, H, L, F, T, B = FULL
+    V, D, H, L, F, T, B = shape
     g = GpuTrainer(V, D, H, L, F, T, B, 1e-5)
     p = start_weights(g, 21)
     stream = zipf_stream(B * T + 1, V, 22)
     ids, tgt = stream[:-1].copy(), stream[1:].copy()
     np.save(tmp_path / "p.npy", p)
     np.savez(tmp_path / "batch.npz", ids=ids, tgt=tgt)
-    r = refgpu.run_child(["step", "--cfg", *FULL, "--params", tmp_path / "p.npy", "--tokens", tmp_path / "batch.npz",
+    r = refgpu.run_child(["step", "--cfg", *shape, "--params", tmp_path / "p.npy", "--tokens", tmp_path / "batch.npz",
                           "--grads-out", tmp_path / "g.npy", "--out", tmp_path / "step.json"])
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     want = json.load(open(tmp_path / "step.json"))

@@ -132,12 +132,18 @@ int head(TbDecoder* g, const float* src, int rows, int advance_pos) {
 int decode_step_body(TbDecoder* g) {
     DeviceCtx* c = g->ctx; cudaStream_t st = g->stream;
     const int S = g->S, D = g->D, H = g->H, hd = g->hd;
+    const bool split_rope = getenv("TB_DECODE_SPLIT_ROPE") != nullptr;    // the two-kernel form, for comparison
     TB_TRY(launch_embed_fwd(c, P32(g, 0), g->tok, g->x, S, D, st));
     for (int l = 0; l < g->L; ++l) {
         TB_TRY(launch_rmsnorm_fwd(c, g->x, P32(g, pidx(l, PK_ATTN_NORM)), g->n, g->r, S, D, g->eps, st));
         TB_TRY(linear(g, g->n, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, S, 3 * D, D));
-        TB_TRY(launch_rope_decode(c, g->qkv, g->cos_t, g->sin_t, g->qdec, g->Kc[l], g->Vc[l], g->pos, S, H, hd, g->cap, st));
-        TB_TRY(launch_attn_decode(c, g->qdec, g->Kc[l], g->Vc[l], g->att, g->pos, S, H, hd, g->cap, g->scale, st));
+        if (split_rope) {
+            TB_TRY(launch_rope_decode(c, g->qkv, g->cos_t, g->sin_t, g->qdec, g->Kc[l], g->Vc[l], g->pos, S, H, hd, g->cap, st));
+            TB_TRY(launch_attn_decode(c, g->qdec, g->Kc[l], g->Vc[l], g->att, g->pos, S, H, hd, g->cap, g->scale, st));
+        } else {
+            TB_TRY(launch_rope_attn_decode(c, g->qkv, g->cos_t, g->sin_t, g->Kc[l], g->Vc[l], g->att, g->pos, S, H, hd,
+                                           g->cap, g->scale, st));
+        }
         TB_TRY(layer_tail(g, l, S));
     }
     return head(g, g->x, S, 1);

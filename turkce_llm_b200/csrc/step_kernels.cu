@@ -646,6 +646,103 @@ int launch_attn_decode(DeviceCtx* ctx, const float* Q, const bf16* Kc, const bf1
     return 0;
 }
 
+// rope_decode_kernel and attn_decode_kernel in one launch: the block of (sequence, head) rotates its own slice of
+// the new token's q and k, appends k and v to its own cache rows (no other block reads them in this launch),
+// and attends over rows 0..*pos.  Kc and Vc are written and read here, so they are neither const nor restrict.
+__global__ void rope_attn_decode_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
+                                        const float* __restrict__ sin_t, bf16* Kc, bf16* Vc, bf16* __restrict__ att,
+                                        const int* __restrict__ pos, int H, int hd, int cap, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ float sh[];            // q [hd] | p [cap] | red [32] | part [groups][hd]
+    float* q = sh;
+    float* p = sh + hd;
+    float* red = p + cap;
+    float* part = red + 32;
+    const int h = blockIdx.x, sq = blockIdx.y;
+    const int t = *pos;
+    const int L = t + 1;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int half = hd >> 1, D = H * hd;
+    bf16* Kb = Kc + ((long long)sq * H + h) * cap * hd;
+    bf16* Vb = Vc + ((long long)sq * H + h) * cap * hd;
+    for (int k = tid; k < half; k += nt) {
+        const float* row = qkv + (long long)sq * 3 * D + h * hd + 2 * k;
+        const float c = cos_t[t * half + k], sn = sin_t[t * half + k];
+        const float2 qq = *reinterpret_cast<const float2*>(row);
+        const float2 kk = *reinterpret_cast<const float2*>(row + D);
+        const float2 v = *reinterpret_cast<const float2*>(row + 2 * D);
+        q[2 * k] = qq.x * c - qq.y * sn;
+        q[2 * k + 1] = qq.x * sn + qq.y * c;
+        const long long o = (long long)t * hd + 2 * k;
+        *reinterpret_cast<__nv_bfloat162*>(Kb + o) = __floats2bfloat162_rn(kk.x * c - kk.y * sn, kk.x * sn + kk.y * c);
+        *reinterpret_cast<__nv_bfloat162*>(Vb + o) = __floats2bfloat162_rn(v.x, v.y);
+    }
+    __syncthreads();                         // the new cache row is visible to the whole block
+    float mx = -3.0e38f;
+    for (int l = tid; l < L; l += nt) {
+        const bf16* kr = Kb + (long long)l * hd;
+        float s = 0.0f;
+        for (int d = 0; d < hd; d += 8) {
+            const uint4 kv = *reinterpret_cast<const uint4*>(kr + d);
+            const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(k2[e]);
+                s += q[d + 2 * e] * f.x;
+                s += q[d + 2 * e + 1] * f.y;
+            }
+        }
+        s *= scale;
+        p[l] = s;
+        mx = fmaxf(mx, s);
+    }
+    mx = block_reduce(mx, red, true);
+    float sum = 0.0f;
+    for (int l = tid; l < L; l += nt) {
+        const float e = expf(p[l] - mx);
+        p[l] = e;
+        sum += e;
+    }
+    sum = block_reduce(sum, red, false);
+    const int C = hd >> 2;
+    const int G = nt / C;
+    const int g = tid / C, c4 = (tid % C) * 4;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (g < G) {
+        for (int l = g; l < L; l += G) {
+            const uint2 v = *reinterpret_cast<const uint2*>(Vb + (long long)l * hd + c4);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            const float w = p[l];
+            a0 += w * lo.x; a1 += w * lo.y; a2 += w * hi.x; a3 += w * hi.y;
+        }
+        float* dst = part + g * hd + c4;
+        dst[0] = a0; dst[1] = a1; dst[2] = a2; dst[3] = a3;
+    }
+    __syncthreads();
+    if (tid < hd) {
+        float o = part[tid];
+        for (int k = 1; k < G; ++k) o += part[k * hd + tid];
+        att[(long long)sq * (H * hd) + h * hd + tid] = __float2bfloat16_rn(o / sum);
+    }
+}
+
+int launch_rope_attn_decode(DeviceCtx* ctx, const float* qkv, const float* cos_t, const float* sin_t, bf16* Kc, bf16* Vc,
+                            bf16* att, const int* pos, int S, int H, int hd, int cap, float scale, cudaStream_t st) {
+    TB_CHECK(hd <= 128 && hd % 8 == 0, "decode attention needs head_dim <= 128 and a multiple of 8");
+    const int threads = 256 / (hd / 4) * (hd / 4) >= 64 ? 256 / (hd / 4) * (hd / 4) : 64;
+    const int groups = threads / (hd / 4);
+    const size_t smem = (size_t)(hd + cap + 32 + groups * hd) * sizeof(float);
+    TB_CHECK(smem <= 48 * 1024, "KV cache capacity %d too large for the decode attention kernel", cap);
+    dim3 grid(H, S);
+    prof_mark(ctx, "rope_attn_decode", 0.0, 0.0, st);
+    TB_CUDA(launch_kernel(rope_attn_decode_kernel, dim3(grid), dim3(threads), smem, st, qkv, cos_t, sin_t, Kc, Vc, att, pos,
+                          H, hd, cap, scale));
+    TB_LAUNCHED(ctx);
+    return 0;
+}
+
 // out[i, :] = in[idx(i), :] for the last position of every sequence: idx(i) = i*T + T-1
 __global__ void gather_last_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int S, int T, int D) {
     pdl_wait();

@@ -32,6 +32,8 @@ int launch_attn_decode(DeviceCtx*, const float* Q, const bf16* Kc, const bf16* V
                        int H, int hd, int cap, float scale, cudaStream_t);
 int launch_gather_last_rows(DeviceCtx*, const float* in, float* out, int S, int T, int D, cudaStream_t);
 // state = {position of the next token, tokens generated so far} in device memory
+int launch_rope_attn_decode(DeviceCtx*, const float* qkv, const float* cos_t, const float* sin_t, bf16* Kc, bf16* Vc,
+                            bf16* att, const int* pos, int S, int H, int hd, int cap, float scale, cudaStream_t);
 int launch_sample_rows(DeviceCtx*, const float* logits, const double* u, float temperature, uint32_t* tok,
                        uint32_t* out, int* state, int S, int V, long long ld, int out_ld, int advance_pos, cudaStream_t);
 int launch_argmax_rows(DeviceCtx*, const float* logits, uint32_t* tok, uint32_t* out, int* state, int S, int V,
