@@ -166,6 +166,7 @@ int forward(TbTrainer* g, bool want_grad) {
             s.kind = GEMM_NN; s.A = a.n1; s.B = P16(g, pidx(l, PK_WQKV)); s.M = N; s.N = 3 * D; s.K = D; s.lda = D;
             s.ldb = 3 * D; s.bias = P32(g, pidx(l, PK_BQKV)); s.splits = 1;
             s.rope_qkv = a.Q; s.rope_cos = g->cos_t; s.rope_sin = g->sin_t; s.rope_T = T; s.rope_H = H; s.rope_hd = hd;
+            if (const char* e = getenv("TB_ROPE_BN")) s.bn = atoi(e);
             TB_TRY(gemm(g, s));
         } else {
             TB_TRY(linear_fwd(g, a.n1, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, N,
