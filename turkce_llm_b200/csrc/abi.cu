@@ -98,7 +98,7 @@ int tb_profile_end(void* stream, char* out, int cap) {
 int tb_alloc(void** d_ptr, uint64_t bytes) { TB_CUDA(cudaMalloc(d_ptr, bytes)); return 0; }
 int tb_free(void* d_ptr) { TB_CUDA(cudaFree(d_ptr)); return 0; }
 int tb_h2d(void* d_dst, const void* h_src, uint64_t bytes) {
-    TB_CUDA(cudaMemcpy(d_dst, h_src, bytes, cudaMemcpyHostToDevice));
+    TB_H2D_SYNC(d_dst, h_src, bytes);
     return 0;
 }
 int tb_d2h(void* h_dst, const void* d_src, uint64_t bytes) {
@@ -304,6 +304,8 @@ int tb_matmul_host(const float* h_A, const float* h_B, float* h_C, int M, int K,
             set_error("tb_matmul_host: host to device copy failed");
             rc = -1; break;
         }
+        // pageable copies may still be in flight on the legacy stream when cudaMemcpy returns
+        if (cudaStreamSynchronize(cudaStreamLegacy) != cudaSuccess) { set_error("tb_matmul_host: synchronisation failed"); rc = -1; break; }
         rc = gemm_f32_impl(TB_GEMM_NN, dA, dB, dC, M, N, K, K, N, N, 1, 0, 0, 0, 1.0f, 0.0f, nullptr, nullptr,
                            precision, nullptr);
         if (rc) break;

@@ -42,6 +42,16 @@ const char* last_error();
         if (_r != 0) return _r;   \
     } while (0)
 
+// cudaMemcpy from pageable host memory may return once the data sits in the driver's staging buffer, before
+// the DMA into device memory (ordered on the legacy default stream) has finished.  The work of this library runs
+// on non-blocking streams, which do not wait for that stream: wait for it here, so that a kernel launched right
+// after an upload never reads the old contents.
+#define TB_H2D_SYNC(dst, src, bytes)                                             \
+    do {                                                                         \
+        TB_CUDA(cudaMemcpy((dst), (src), (bytes), cudaMemcpyHostToDevice));      \
+        TB_CUDA(cudaStreamSynchronize(cudaStreamLegacy));                        \
+    } while (0)
+
 // ---- optional per-launch timing: one event in front of a launch (prof_mark) and one behind it
 // (prof_close); the difference is the kernel's own time even when the host is the bottleneck.
 struct ProfRec { const char* tag; cudaEvent_t ev; cudaEvent_t ev_end; double flops; double bytes; };

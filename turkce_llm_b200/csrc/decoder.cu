@@ -208,8 +208,8 @@ int tb_decoder_create(TbDecoder** out, int V, int D, int H, int L, int F, int ma
                 sn[(size_t)p * half + k] = sinf(angle);
             }
         TB_TRY(dalloc(g, &g->cos_t, ct.size())); TB_TRY(dalloc(g, &g->sin_t, sn.size()));
-        TB_CUDA(cudaMemcpy(g->cos_t, ct.data(), ct.size() * 4, cudaMemcpyHostToDevice));
-        TB_CUDA(cudaMemcpy(g->sin_t, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+        TB_H2D_SYNC(g->cos_t, ct.data(), ct.size() * 4);
+        TB_H2D_SYNC(g->sin_t, sn.data(), sn.size() * 4);
     }
     *out = g;
     return 0;
@@ -229,7 +229,7 @@ int64_t tb_decoder_total_scalars(const TbDecoder* g) { return g->total; }
 
 int tb_decoder_upload(TbDecoder* g, const float* h_flat) {
     TB_CUDA(cudaStreamSynchronize(g->stream));
-    TB_CUDA(cudaMemcpy(g->params, h_flat, (size_t)g->total * 4, cudaMemcpyHostToDevice));
+    TB_H2D_SYNC(g->params, h_flat, (size_t)g->total * 4);
     TB_CHECK(g->total < (1LL << 31), "model too large for the single-row pack");
     TB_TRY(launch_pack_bf16(g->ctx, g->params, g->params16, 1, (int)g->total, g->total, g->total, 1, 0, 0, g->stream));
     TB_CUDA(cudaStreamSynchronize(g->stream));
@@ -283,7 +283,7 @@ int tb_decoder_set_sampling(TbDecoder* g, float temperature, uint64_t seed, uint
             Pcg32 rng(seed, seq + (uint64_t)s);
             for (int i = 0; i < g->cap; ++i) u[(size_t)i * g->S + s] = rng.uniform();
         }
-        TB_CUDA(cudaMemcpy(g->sample_u, u.data(), u.size() * sizeof(double), cudaMemcpyHostToDevice));
+        TB_H2D_SYNC(g->sample_u, u.data(), u.size() * sizeof(double));
     }
     return 0;
 }

@@ -589,8 +589,8 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
                 sn[(size_t)pos * half + k] = sinf(angle);
             }
         TB_TRY(dalloc(g, &g->cos_t, ct.size())); TB_TRY(dalloc(g, &g->sin_t, sn.size()));
-        TB_CUDA(cudaMemcpy(g->cos_t, ct.data(), ct.size() * 4, cudaMemcpyHostToDevice));
-        TB_CUDA(cudaMemcpy(g->sin_t, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+        TB_H2D_SYNC(g->cos_t, ct.data(), ct.size() * 4);
+        TB_H2D_SYNC(g->sin_t, sn.data(), sn.size() * 4);
     }
     *out = g;
     return 0;
@@ -639,7 +639,7 @@ int tb_trainer_upload(TbTrainer* g, int which, const float* h_flat) {
     float* d = flat_ptr(g, which);
     TB_CHECK(d != nullptr, "tb_trainer_upload: unknown buffer %d", which);
     TB_CUDA(cudaStreamSynchronize(g->stream));
-    TB_CUDA(cudaMemcpy(d, h_flat, (size_t)g->total * 4, cudaMemcpyHostToDevice));
+    TB_H2D_SYNC(d, h_flat, (size_t)g->total * 4);
     if (which == 0) {
         // refresh the bf16 shadow copy the GEMMs read
         TB_CHECK(g->total < (1LL << 31), "model too large for the single-row pack");
