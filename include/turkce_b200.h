@@ -120,12 +120,20 @@ int tb_gemm_bf16(int kind, const void* d_A, const void* d_B, int M, int N, int K
  * order: bitwise reproducible).  wait != 0: the call waits for `stream` and returns non-zero if a
  * kernel gave up on a bounded wait; wait == 0: fully asynchronous.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
- * queries device attributes; make that first call before any stream capture begins.
+ * queries device attributes; make that first call before any stream capture begins.  (That set-up is
+ * guarded by a mutex: two host threads may make their first calls at the same time.)
  * All calls on a device share the one array and one status word: two calls whose kernels can
- * overlap on the GPU (different streams, no ordering between them) race on them. */
+ * overlap on the GPU (different streams, no ordering between them) race on them.  Every call clears the
+ * status word on its stream before it launches, so a caller that passes wait == 0 must read the word
+ * with tb_gemm_bf16_splitk_static_status before its next call, or a time-out goes unreported
+ * (tb_check reads a different word and allocates on first use). */
 int tb_gemm_bf16_splitk_static(int kind, const void* d_A, const void* d_B, int M, int N, int K,
                                int64_t lda, int64_t ldb, float* d_C32, int64_t ldc32,
                                const float* d_bias, float alpha, float beta, int splits, int wait, void* stream);
+
+/* No counterpart in the reference.  Waits for `stream` and returns non-zero if a kernel of an earlier
+ * tb_gemm_bf16_splitk_static call on this device gave up on a bounded wait.  Allocates nothing. */
+int tb_gemm_bf16_splitk_static_status(void* stream);
 
 /* float32 [rows, cols] (ld_src) -> bf16 [rows, cols] (ld_dst), `batch` matrices. */
 int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld_src, int64_t ld_dst,
@@ -138,6 +146,16 @@ int tb_pack_bf16(const float* d_src, void* d_dst, int rows, int cols, int64_t ld
  * H bf16 [M,F]; GU (optional, bf16 [M,2F]) keeps g and u for the backward pass.  F must be a multiple of 64. */
 int tb_gemm_swiglu_bf16(const void* d_X, const void* d_W, const float* d_bias, int M, int F, int K, void* d_H,
                         void* d_GU, void* stream);
+
+/* QKV projection with the position embedding and the head split fused into the GEMM epilogue:
+ * bf16_gemm_bias (model/gpu_train.c:338) followed by k_qkv_rope_split (model/gpu_train.c:339-343,
+ * cuda/train_kernels.cu:573-597; CPU definition model/attention.c:26-29,50-53 with model/rope.c:20-47).
+ *   qkv = X[B*T, D] . W[D, 3D] + bias[3D]   (D = H*hd; row n holds q | k | v of token n, head h at column h*hd)
+ * q and k are rotated pairwise ((2k, 2k+1) by the angle of (position, k), tables cos/sin [T, hd/2] float32),
+ * and all three leave as bf16 in d_QKV = [3][B][H][T][hd] (Q, K, V back to back, the layout tb_attention_fwd
+ * reads).  X, W bf16 row-major; hd 32 or 64; T a multiple of 32; tables 16-byte aligned. */
+int tb_gemm_qkv_rope_bf16(const void* d_X, const void* d_W, const float* d_bias, const float* d_cos, const float* d_sin,
+                          int B, int T, int H, int hd, void* d_QKV, void* stream);
 
 /* Decode-time LM head with the greedy choice fused: d_tok[s] = argmax_v <X[s,:], E[v,:]> (lowest index
  * on ties) for 1 <= S <= 64 rows of X [S, K] bf16 against the tied embedding table E [V, K] bf16, K a

@@ -93,3 +93,53 @@ def test_attention_properties_at_benchmark_size(tb):
     tb.attention_fwd(Q, K, V, a3, lse, B, H, T, hd, scale)
     tb.sync_check()
     assert torch.equal(a3.view(B, T, D), a1)          # bitwise reproducible
+
+
+def test_strided_qkv_projection_rope_then_attention_at_benchmark_size(tb, oracle):
+    """The attention configuration of the benchmark (B=16, H=6, T=1024, hd=64) from the reference's strided
+    layout: q, k, v are column slices of one [B*T, 3D] projection (model/attention.c:26-29,50-53).  The QKV GEMM
+    with the fused position embedding and head split is compared with the oracle's projection + k_qkv_rope_split
+    restatement (cuda/train_kernels.cu:573-597) on every element; fused attention forward and backward then run
+    on that output for all 96 heads and are compared with the oracle on a handful of them."""
+    import os
+    B, H, T, hd = 16, 6, 1024, 64
+    D, N = H * hd, B * T
+    scale = float(1.0 / np.sqrt(np.float32(hd)))
+    oracle.set_threads(min(os.cpu_count() or 8, 64))
+    rng = np.random.default_rng(2)
+    X = oracle.round(rng.standard_normal((N, D)).astype(np.float32), BF16)
+    W = oracle.round((rng.standard_normal((D, 3 * D)) / np.sqrt(D)).astype(np.float32), BF16)   # q, k, v ~ N(0, 1)
+    bias = (0.1 * rng.standard_normal(3 * D)).astype(np.float32)
+    cos_t, sin_t = oracle.rope_tables(T, hd)
+    qkv16 = torch.full((3, B, H, T, hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+    tb.gemm_qkv_rope_bf16(dev16(X), dev16(W), torch.from_numpy(bias).cuda(), torch.from_numpy(cos_t).cuda(),
+                          torch.from_numpy(sin_t).cuda(), B, T, H, hd, qkv16)
+    tb.sync_check()
+    want_qkv = oracle.gemm_bias(X, W, bias, None, mode=BF16)
+    wq, wk, wv = oracle.qkv_rope_split(want_qkv, B, T, H, hd)
+    got = qkv16.float().cpu().numpy().reshape(3, B * H, T, hd)
+    assert np.isfinite(got).all()
+    for g, w, name in zip(got, (wq, wk, wv), "QKV"):
+        assert rel_to_maxabs(g, w) <= 4e-3, name            # one bf16 rounding of the stored value (2^-9 of it)
+
+    # attention on the stored bf16 q, k, v: all heads on the device, a handful against the oracle
+    Q, K, V = qkv16[0].reshape(B * H, T, hd), qkv16[1].reshape(B * H, T, hd), qkv16[2].reshape(B * H, T, hd)
+    att = torch.full((N, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    lse = torch.zeros(B * H, T, device="cuda")
+    tb.attention_fwd(Q, K, V, att, lse, B, H, T, hd, scale)
+    datt = oracle.round(np.random.default_rng(5).standard_normal((N, D)).astype(np.float32), BF16)
+    dQ, dK, dV = (torch.full((B * H, T, hd), float("nan"), device="cuda") for _ in range(3))
+    delta = torch.zeros(B * H, T, device="cuda")
+    tb.attention_bwd(Q, K, V, att, dev16(datt), lse, delta, dQ, dK, dV, B, H, T, hd, scale)
+    tb.sync_check()
+    heads = [0, 17, 40, 63, 95]                                # (batch, head) = divmod(index, H)
+    q, k, v = (got[i][heads] for i in range(3))
+    O = oracle.attention_fwd(q, k, v, scale, mode=BF16)
+    att_h = att.float().cpu().numpy().reshape(B, T, H, hd)
+    dO = np.stack([datt.reshape(B, T, H, hd)[z // H, :, z % H, :] for z in heads])
+    wdq, wdk, wdv = oracle.attention_bwd(q, k, v, dO, scale, mode=BF16)
+    for i, z in enumerate(heads):
+        assert rel_to_maxabs(att_h[z // H, :, z % H, :], O[i]) <= TOL_FWD, z
+        for got_t, want_a, name in ((dQ, wdq, "dQ"), (dK, wdk, "dK"), (dV, wdv, "dV")):
+            assert rel_to_maxabs(got_t[z].cpu().numpy(), want_a[i]) <= TOL_BWD, (z, name)
+    assert torch.isfinite(att.float()).all() and all(torch.isfinite(t).all() for t in (dQ, dK, dV))

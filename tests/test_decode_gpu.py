@@ -62,6 +62,84 @@ def test_cached_decode_matches_full_recompute(tb, oracle, dims):
     dec.destroy()
 
 
+def test_full_size_cached_decode_matches_full_recompute(tb, oracle):
+    """The decode configuration of the benchmark at full size: the 33,490,176-parameter decoder (12 layers,
+    d_model 384, 6 heads, d_ff 1024, 31,769 tokens), 64 sequences with 128-token Zipf(1.1) prompts, 128 greedy
+    tokens, cache length up to 256.  The logits each token was chosen from are compared with the oracle's
+    full-recompute forward over the window (training/generate.c:186-212) after the prefill and at decode steps
+    1, 64 and 127, on eight of the 64 sequences (sequences are independent; the oracle's forward over all 64
+    windows would hold 2 GB of logits)."""
+    import os
+    from turkce_llm_b200.decode import Decoder
+    V, D, H, L, F, S, prompt_len, n_new = 31769, 384, 6, 12, 1024, 64, 128, 128
+    oracle.set_threads(min(os.cpu_count() or 8, 64))
+    rng = np.random.default_rng(3)
+    p = make_params(oracle, (V, D, H, L, F, 1, 1, 1e-5), 3)
+    w = 1.0 / np.arange(1, V + 1, dtype=np.float64) ** 1.1
+    cdf = np.cumsum(w / w.sum())
+    prompts = np.minimum(np.searchsorted(cdf, rng.random((S, prompt_len))), V - 1).astype(np.uint32)
+    dec = Decoder(V, D, H, L, F, S, prompt_len + n_new + 1)
+    dec.upload(p)
+    dec.prefill(prompts)
+    rows = [0, 9, 18, 27, 36, 45, 54, 63]
+    checks = {}
+    for step in (0, 1, 64, n_new - 1):
+        have = 1 if not checks else max(checks) + 1
+        if step + 1 > have:
+            dec.generate(step + 1 - have)
+        checks[step] = (dec.logits()[rows], dec.tokens(step + 1))
+    all_tokens = dec.tokens(n_new)
+    assert all_tokens.max() < V
+    dec.destroy()
+    for step, (got_logits, toks) in checks.items():
+        assert np.array_equal(toks, all_tokens[:, :step + 1])          # earlier tokens do not change later
+        window = np.concatenate([prompts[rows], toks[rows][:, :step]], axis=1)
+        T = window.shape[1]
+        assert T == prompt_len + step
+        _, _, logits = oracle.model_forward_backward((V, D, H, L, F, T, len(rows), 1e-5), p, window.reshape(-1),
+                                                     np.zeros(len(rows) * T, np.uint32), want_grads=False,
+                                                     want_logits=True)
+        want = logits.reshape(len(rows), T, V)[:, -1, :]
+        assert rel_to_maxabs(got_logits, want) <= 2e-2, step           # the BF16-mode bound
+        got_tok = toks[rows][:, step]
+        assert np.array_equal(got_tok, got_logits.argmax(1))
+        srt = np.sort(want, axis=1)
+        clear = (srt[:, -1] - srt[:, -2]) > 4e-2 * np.abs(want).max()
+        assert np.array_equal(got_tok[clear], want.argmax(1)[clear])
+
+
+def test_greedy_choice_stays_in_vocabulary_for_nan_and_inf_rows(tb):
+    """A row of logits that is all NaN or all -inf (diverged weights) must still give a token inside [0, V):
+    the token is fed back into the embedding lookup.  Both greedy paths: the fused LM head (NaN hidden states
+    make every product NaN) and the decoder's general path."""
+    import torch
+    from turkce_llm_b200 import lib
+    from turkce_llm_b200.decode import Decoder
+    S, V, K = 8, 3000, 128
+    x = torch.randn(S, K, device="cuda")
+    x[1] = float("nan")
+    x[3] = float("-inf")              # products of mixed sign: -inf and +inf sum to NaN
+    x[5] = 0.0
+    e16 = (torch.randn(V, K, device="cuda") * 0.05).to(torch.bfloat16)
+    tok = torch.full((S,), -1, device="cuda", dtype=torch.int32)
+    lib.lmhead_argmax_bf16(x.to(torch.bfloat16), e16, tok)
+    lib.sync_check()
+    t = tok.cpu().numpy()
+    assert ((t >= 0) & (t < V)).all(), t
+    assert t[5] == 0                   # all-equal row: lowest index
+    # a decoder whose weights are NaN: every step's token must stay a valid row of the embedding table
+    # (d_model 32 is below the fused head's smallest K, so this decoder takes the general argmax kernel)
+    V, D, H, L, F, S = 211, 32, 2, 2, 128, 4
+    dec = Decoder(V, D, H, L, F, S, 16)
+    p = np.full(dec.total, np.nan, np.float32)
+    dec.upload(p)
+    dec.prefill(np.zeros((S, 4), np.uint32))
+    dec.generate(6)
+    toks = dec.tokens(7)
+    assert toks.max() < V
+    dec.destroy()
+
+
 def test_generate_in_one_call_equals_stepwise(tb, oracle):
     """n graph-replayed steps in one call give the tokens of n single-step calls, bit for bit."""
     from turkce_llm_b200.decode import Decoder

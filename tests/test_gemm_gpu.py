@@ -173,13 +173,18 @@ def test_gemm_bias_residual(tb, oracle):
         assert rel_to_maxabs(C.cpu().numpy(), want) <= TOL_SAME_OPERANDS
 
 
+@pytest.mark.parametrize("precision", ["bf16", "tf32", "fp32"])
 @pytest.mark.parametrize("name", ["qkv", "out", "gate_up", "down"])
-def test_layer_gemms_fwd_dx_dw(tb, oracle, name):
-    """One layer's linear GEMMs at M = 4*256 tokens: forward, dX = dY W^T, dW = X^T dY
+def test_layer_gemms_fwd_dx_dw(tb, oracle, name, precision):
+    """One layer's linear GEMMs at M = 4*256 tokens: forward, dX = dY W^T, dW = X^T dY, in each of the three
+    operand precisions with its stated bound against the float32 oracle: 2e-2 (BF16), 5e-3 (TF32), 1e-5 (FP32)
     (the float32 oracle results are pinned to the reference by tests/golden/gemm_layer_digests.json)."""
     import os, sys
+    from oracle.pyoracle import TF32
     sys.path.insert(0, os.path.dirname(golden_path("x")))
     from make_golden import gemm_inputs
+    prec, mode_tol, same_mode = {"bf16": (tb.PREC_BF16, TOL_BF16_MODE, BF16), "tf32": (tb.PREC_TF32, TOL_TF32_MODE, TF32),
+                                 "fp32": (tb.PREC_FP32, TOL_FP32_MODE, None)}[precision]
     d = json.load(open(golden_path("gemm_layer_digests.json")))[name]
     M, K, N = d["M"], d["K"], d["N"]
     X, W, dY = gemm_inputs(d["seed"], M, K, N)
@@ -187,19 +192,25 @@ def test_layer_gemms_fwd_dx_dw(tb, oracle, name):
     C = torch.zeros(M, N, device="cuda")
     dX = torch.zeros(M, K, device="cuda")
     dW = torch.zeros(K, N, device="cuda")
-    tb.gemm_f32(0, dX_, dW_, C, M, N, K, K, N, N)
-    tb.gemm_f32(1, dY_, dW_, dX, M, K, N, N, N, K)
-    tb.gemm_f32(2, dX_, dY_, dW, K, N, M, K, N, N)
+    tb.gemm_f32(0, dX_, dW_, C, M, N, K, K, N, N, precision=prec)
+    tb.gemm_f32(1, dY_, dW_, dX, M, K, N, N, N, K, precision=prec)
+    tb.gemm_f32(2, dX_, dY_, dW, K, N, M, K, N, N, precision=prec)
     tb.sync_check()
     for got, (ta, tb_, A, B, m, n, k), key in (
             (C, (0, 0, X, W, M, N, K), "C"), (dX, (0, 1, dY, W, M, K, N), "dX"), (dW, (1, 0, X, dY, K, N, M), "dW")):
         got = got.cpu().numpy().reshape(-1)
         want32 = oracle.gemm(ta, tb_, A, B, m, n, k)
-        want16 = oracle.gemm(ta, tb_, A, B, m, n, k, mode=BF16)
         step = max(1, want32.size // 16)
         assert np.allclose(want32[::step][:16], d[key + "_sample"], rtol=0, atol=0)   # same oracle as the fixture
-        assert rel_to_maxabs(got, want16) <= TOL_SAME_OPERANDS, key
-        assert rel_to_maxabs(got, want32) <= TOL_BF16_MODE, key
+        if same_mode is not None:
+            want_same = oracle.gemm(ta, tb_, A, B, m, n, k, mode=same_mode)
+            assert rel_to_maxabs(got, want_same) <= TOL_SAME_OPERANDS, key
+        else:
+            # the float32 oracle itself carries the rounding of a sequential float32 sum over k (up to 1024
+            # terms); the float64 product is the truth the 1e-5 bound is stated against
+            truth = oracle.gemm_f64(ta, tb_, A, B, m, n, k).reshape(-1)
+            assert rel_to_maxabs(got, truth) <= TOL_FP32_MODE, key
+        assert rel_to_maxabs(got, want32) <= mode_tol, key
 
 
 @pytest.mark.parametrize("kind", ["NN", "NT", "TN"])

@@ -1,10 +1,11 @@
 """The allocation-free split-K GEMM (tb_gemm_bf16_splitk_static) against the regular entry point.
 
-Collected last on purpose: a run that stops at the first failure has then already run every other
-test.  The new entry point is called first, before anything has initialised the library on the
-device, because hosts that cannot allocate device memory will not have called tb_init either; it
-is then called a second time to show that the scratch array left over from the first call does
-not leak into the second result.
+This file is collected last, so a run that stops at the first failure has already run every other
+test.  The static entry point is called twice in a row on different problems: the scratch array keeps
+the first call's partial sums, and the second result must not see them.  When this file runs alone in
+a fresh process the static calls are also the first use of the library on the device (hosts that cannot
+allocate device memory will not have called tb_init either); after the other tests the library is
+already initialised, and the results must be the same.
 """
 import numpy as np
 import pytest
@@ -39,6 +40,13 @@ def test_static_scratch_entry_matches_regular_entry():
         lib.gemm_bf16_splitk_static(kind, A, B, M, N, K, lda, ldb, C, N, bias=bias, alpha=0.5, beta=1.0,
                                     splits=splits, wait=True)
         statics.append((kind, M, N, K, splits, A, B, lda, ldb, bias, C0, C))
+    # the asynchronous form: the caller reads the status word itself, without allocating
+    kind, M, N, K, splits, A, B, lda, ldb, bias, C0, C = statics[0]
+    C_async = C0.clone()
+    lib.gemm_bf16_splitk_static(kind, A, B, M, N, K, lda, ldb, C_async, N, bias=bias, alpha=0.5, beta=1.0,
+                                splits=splits, wait=False)
+    lib.gemm_bf16_splitk_static_status()
+    assert torch.equal(C_async, C)
     # only now the regular path (this initialises the library's own state and scratch on the device)
     lib.init(0)
     for kind, M, N, K, splits, A, B, lda, ldb, bias, C0, C in statics:

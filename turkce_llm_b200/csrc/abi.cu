@@ -131,6 +131,24 @@ int tb_gemm_swiglu_bf16(const void* d_X, const void* d_W, const float* d_bias, i
     return launch_gemm_bf16(ctx, a, S(stream));
 }
 
+int tb_gemm_qkv_rope_bf16(const void* d_X, const void* d_W, const float* d_bias, const float* d_cos, const float* d_sin,
+                          int B, int T, int H, int hd, void* d_QKV, void* stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    TB_CHECK(d_X && d_W && d_cos && d_sin && d_QKV, "tb_gemm_qkv_rope_bf16: NULL operand");
+    TB_CHECK(B > 0 && T > 0 && H > 0 && (hd == 32 || hd == 64) && T % 32 == 0,
+             "tb_gemm_qkv_rope_bf16: head_dim must be 32 or 64 and T a multiple of 32 (got T=%d hd=%d)", T, hd);
+    TB_CHECK((reinterpret_cast<uintptr_t>(d_cos) & 15u) == 0 && (reinterpret_cast<uintptr_t>(d_sin) & 15u) == 0,
+             "tb_gemm_qkv_rope_bf16: the angle tables must be 16-byte aligned");
+    const int D = H * hd;
+    GemmArgs a;
+    a.kind = GEMM_NN; a.A = d_X; a.B = d_W; a.M = B * T; a.N = 3 * D; a.K = D; a.lda = D; a.ldb = 3 * D;
+    a.bias = d_bias; a.splits = 1;
+    a.rope_qkv = static_cast<bf16*>(d_QKV); a.rope_cos = d_cos; a.rope_sin = d_sin;
+    a.rope_T = T; a.rope_H = H; a.rope_hd = hd;
+    return launch_gemm_bf16(ctx, a, S(stream));
+}
+
 int tb_lmhead_argmax_bf16(const void* d_X, const void* d_E, int n_seqs, int V, int K, uint32_t* d_tok, float* d_logits,
                           int64_t ld_logits, int table_is_stable, void* stream) {
     DeviceCtx* ctx;

@@ -114,7 +114,9 @@ int check_device_error(DeviceCtx* ctx, cudaStream_t stream) {
     TB_CUDA(cudaStreamSynchronize(stream));
     TB_CUDA(cudaMemcpy(&h, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost));
     if (h != 0) {
-        cudaMemset(ctx->d_err, 0, sizeof(int));
+        // the ticket words and packed maxima behind the error word go back to zero as well: a kernel that
+        // gave up may have left them half-way
+        cudaMemset(ctx->d_err, 0, 1024);
         const char* who = h == 1 ? "TMA producer" : h == 2 ? "MMA issuer" : h == 3 ? "epilogue" : "kernel";
         set_error("a kernel gave up on a bounded wait (%s, code %d); its output is invalid", who, h);
         return -3;

@@ -1156,10 +1156,21 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     return 0;
 }
 
+// Forms that cannot be split along K run unsplit: fused epilogues, a residual operand, and the causal modes
+// (a skipped tile writes no partial slab, and the causal k ranges are per tile).  A split count beyond the
+// number of K slices would leave empty splits.
+static int check_splits(const GemmArgs& a, int* splits) {
+    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0 || a.rope_qkv || a.causal != CAUSAL_NONE) *splits = 1;
+    const int bke = a.tf32 ? BK_TF32 : BK;
+    const int kb_total = (a.K + bke - 1) / bke;
+    TB_CHECK(*splits <= kb_total, "splits=%d exceeds the %d K slices of %d elements this product has", *splits, kb_total, bke);
+    return 0;
+}
+
 int launch_gemm_bf16(DeviceCtx* ctx, const GemmArgs& a, cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0 || a.rope_qkv) splits = 1;
+    TB_TRY(check_splits(a, &splits));
     float* ws = nullptr;
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N * sizeof(float);
@@ -1173,7 +1184,7 @@ int launch_gemm_bf16_ws(DeviceCtx* ctx, const GemmArgs& a, float* workspace, siz
                         cudaStream_t stream) {
     const int bn = pick_bn(ctx, a);
     int splits = a.splits > 0 ? a.splits : choose_splits(ctx, a, bn);
-    if (a.residual || a.c_inner > 1 || a.swiglu_h || a.ce_mode != 0 || a.rope_qkv) splits = 1;
+    TB_TRY(check_splits(a, &splits));
     if (splits > 1) {
         const size_t need = (size_t)splits * a.batch * a.M * a.N;
         TB_CHECK(workspace != nullptr && workspace_floats >= need,
@@ -1207,10 +1218,12 @@ struct StaticSetup {
     int sm_count = 0;
 };
 StaticSetup g_static_setup[64];
+std::mutex g_static_mutex;
 
 int static_setup(int dev, StaticSetup** out) {
     TB_CHECK(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
     StaticSetup* s = &g_static_setup[dev];
+    std::lock_guard<std::mutex> lock(g_static_mutex);     // two host threads may make the first call together
     if (!s->done) {
         void* p = nullptr;
         TB_CUDA(cudaGetSymbolAddress(&p, g_static_partials));
@@ -1277,5 +1290,18 @@ extern "C" int tb_gemm_bf16_splitk_static(int kind, const void* d_A, const void*
         TB_CUDA(cudaMemcpy(&h, s->status, sizeof(int), cudaMemcpyDeviceToHost));
         TB_CHECK(h == 0, "tb_gemm_bf16_splitk_static: a kernel gave up on a bounded wait (code %d); output invalid", h);
     }
+    return 0;
+}
+
+extern "C" int tb_gemm_bf16_splitk_static_status(void* stream) {
+    using namespace tb;
+    int dev = -1;
+    TB_CUDA(cudaGetDevice(&dev));
+    StaticSetup* s = nullptr;
+    TB_TRY(static_setup(dev, &s));
+    int h = 0;
+    TB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    TB_CUDA(cudaMemcpy(&h, s->status, sizeof(int), cudaMemcpyDeviceToHost));
+    TB_CHECK(h == 0, "tb_gemm_bf16_splitk_static: a kernel gave up on a bounded wait (code %d); output invalid", h);
     return 0;
 }

@@ -145,10 +145,12 @@ lmhead_argmax_kernel(const __grid_constant__ CUtensorMap tmE, const __grid_const
         }
     }
     tc_fence_before();
-    __syncthreads();
+    // a CTA whose wait ran out skips the scan but still takes its ticket below, so that the ticket word and
+    // the maxima are back at zero when the launch ends (the error word tells the host the tokens are invalid)
+    const int all_done = __syncthreads_and(done ? 1 : 0);
     if (warp == 1) tmem_dealloc(tmem_base, 128);
-    if (!done) return;
 
+    if (all_done) {
     // ---- per sequence: 4 threads scan a quarter of the rows each, four rows per load, in four
     // independent chains (row mod 4); every comparison prefers the lower row on equal values
     {
@@ -156,14 +158,18 @@ lmhead_argmax_kernel(const __grid_constant__ CUtensorMap tmE, const __grid_const
         const int seg_len = ((rows_here + 15) >> 4) << 2;              // multiple of 4 rows
         const int r0 = seg * seg_len, r1 = min(r0 + seg_len, rows_here);
         const float* src = stage + s * LH_STAGE_LD;
-        float bv[4] = {-3.0e38f, -3.0e38f, -3.0e38f, -3.0e38f};
-        int br[4] = {0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff};
+        // every chain starts on a row of this CTA with the lowest key, so that a sequence whose products are
+        // all NaN or -inf (diverged weights) still yields a token inside the vocabulary
+        float bv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        int br[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) br[j] = r0 + j < r1 ? r0 + j : (r0 < r1 ? r0 : 0);
         for (int r = r0; r < r1; r += 4) {
             const float4 v = *reinterpret_cast<const float4*>(src + r);
             const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                if (r + j < r1 && e[j] > bv[j]) { bv[j] = e[j]; br[j] = r + j; }
+                if (r + j < r1 && e[j] > bv[j]) { bv[j] = e[j]; br[j] = r + j; }      // false for NaN
         }
 #pragma unroll
         for (int j = 1; j < 4; ++j)
@@ -197,6 +203,7 @@ lmhead_argmax_kernel(const __grid_constant__ CUtensorMap tmE, const __grid_const
         atomicMax(p.best + s, ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - ((uint32_t)row0 + row)));
         __threadfence();
     }
+    }   // all_done
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned int t = atomicAdd(p.ticket, 1u);
@@ -214,7 +221,8 @@ lmhead_argmax_kernel(const __grid_constant__ CUtensorMap tmE, const __grid_const
         const unsigned long long packed = __ldcg(p.best + s);
         p.best[s] = 0ull;
         if (s < p.S) {
-            const uint32_t idx = 0xffffffffu - (uint32_t)(packed & 0xffffffffull);
+            uint32_t idx = 0xffffffffu - (uint32_t)(packed & 0xffffffffull);
+            if (idx >= (uint32_t)p.V) idx = 0u;      // only after an aborted launch: keep the fed-back token in range
             p.tok[s] = idx;
             if (p.out != nullptr) p.out[(long long)s * p.out_ld + generated] = idx;
         }

@@ -46,7 +46,7 @@ __global__ void embed_fwd_kernel(const float* __restrict__ E, const uint32_t* __
          i += (long long)gridDim.x * blockDim.x) {
         const long long n = i / D;
         const int j = (int)(i % D);
-        x[i] = E[(long long)ids[n] * D + j];
+        x[i] = E[(long long)ids[n] * D + j];     // ids are range-checked by whoever writes them (host or argmax)
     }
 }
 
@@ -771,10 +771,13 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, uint32_t* _
     __shared__ int bi[32];
     const int sq = blockIdx.x;
     const float* z = logits + (long long)sq * ld;
-    float best = -3.0e38f;
-    int idx = 0x7fffffff;
+    // a row of NaN or -inf logits (diverged weights) must still yield a token inside [0, V): the
+    // comparison key of such a value is the lowest one, and the search starts from this thread's first column
+    float best = -INFINITY;
+    int idx = threadIdx.x < V ? (int)threadIdx.x : 0;
     for (int j = threadIdx.x; j < V; j += blockDim.x) {
-        const float v = z[j];
+        float v = z[j];
+        if (!(v == v)) v = -INFINITY;
         if (v > best || (v == best && j < idx)) { best = v; idx = j; }
     }
 #pragma unroll

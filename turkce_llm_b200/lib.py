@@ -37,10 +37,12 @@ SIGNATURES = {
                           _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _i64,
                           _f, _f, _i, _i, _i, _vp]),
     "tb_gemm_bf16_splitk_static": (_i, [_i, _vp, _vp, _i, _i, _i, _i64, _i64, _vp, _i64, _vp, _f, _f, _i, _i, _vp]),
+    "tb_gemm_bf16_splitk_static_status": (_i, [_vp]),
     "tb_attention_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
     "tb_gemm_swiglu_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "tb_gemm_qkv_rope_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "tb_lmhead_argmax_bf16": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i64, _i, _vp]),
     "tb_decoder_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "tb_decoder_destroy": (_i, [_vp]),
@@ -188,6 +190,11 @@ def gemm_bf16_splitk_static(kind, A, B, M, N, K, lda, ldb, C32, ldc32, bias=None
                                             alpha, beta, splits, 1 if wait else 0, _stream()))
 
 
+def gemm_bf16_splitk_static_status():
+    """Waits for the current stream and raises if a static split-K call gave up on a bounded wait."""
+    check(load().tb_gemm_bf16_splitk_static_status(_stream()))
+
+
 def attention_fwd(Q, K, V, att, lse, B, H, T, hd, scale):
     check(load().tb_attention_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(att), _ptr(lse), B, H, T, hd, scale, _stream()))
 
@@ -202,6 +209,12 @@ def gemm_swiglu_bf16(x16, w16, bias, h16, gu16=None):
     M, K = x16.shape
     F = w16.shape[1] // 2
     check(load().tb_gemm_swiglu_bf16(_ptr(x16), _ptr(w16), _ptr(bias), M, F, K, _ptr(h16), _ptr(gu16), _stream()))
+
+
+def gemm_qkv_rope_bf16(x16, w16, bias, cos_t, sin_t, B, T, H, hd, qkv16):
+    """qkv16 [3, B, H, T, hd] bf16 = head-split, rotated (q, k) projection x16[B*T, D] @ w16[D, 3D] + bias."""
+    check(load().tb_gemm_qkv_rope_bf16(_ptr(x16), _ptr(w16), _ptr(bias), _ptr(cos_t), _ptr(sin_t), B, T, H, hd,
+                                       _ptr(qkv16), _stream()))
 
 
 def lmhead_argmax_bf16(x16, e16, tok, logits=None, ld_logits=0, table_is_stable=False):
