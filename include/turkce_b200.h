@@ -296,6 +296,38 @@ int tb_trainer_run(TbTrainer* g, const uint32_t* tokens, uint64_t num_tokens, ui
                    uint32_t warmup_steps, uint32_t total_steps, float peak_lr, float min_lr, float max_norm,
                    float beta1, float beta2, float eps, uint64_t* adam_t, float* losses_out, double* norms_out);
 
+/* ---- data parallelism over the GPUs of one box ----------------------------------------- */
+
+/* The multi-GPU extension of data_parallel_step (training/data_parallel.h:20-35, training/data_parallel.c:119-163).
+ * The reference hands one sequence to each CPU worker thread, adds the workers' gradients in a fixed order,
+ * divides by the worker count (dp_reduce_run, :102-117) and averages the workers' losses.  Here a worker is a
+ * rank: one process or host thread per GPU, each with its own TbTrainer (a full replica, created with the
+ * per-rank batch), and the flat float32 gradient buffers are summed over the ranks by NCCL over NVLink;
+ * 1 / ranks is folded into Adam's gradient scale, and every rank ends the step with bit-identical weights.
+ * NCCL is loaded at run time (libnccl.so.2, or the path in TB_NCCL_LIB); one rank alone needs no NCCL. */
+typedef struct TbDp TbDp;
+#define TB_DP_ALLREDUCE 0   /* one all-reduce of the flat gradient buffer (the loss rides in a spare slot) */
+#define TB_DP_SHARDED   1   /* reduce-scatter, Adam on this rank's 1/ranks slice, all-gather of the weights */
+/* Rank 0 calls this and hands the 128 bytes to every rank (through whatever channel launched them). */
+int tb_dp_unique_id(void* id_out_128_bytes);
+/* Collective over the ranks (creates the NCCL communicator); unique_id may be NULL when world == 1. */
+int tb_dp_create(TbDp** out, TbTrainer* g, const void* unique_id, int rank, int world, int mode);
+int tb_dp_destroy(TbDp* dp);
+int tb_dp_info(const TbDp* dp, int* rank, int* world, int* mode, int* nccl_version);
+/* One optimiser step: data_parallel_step + the clipped Adam step of the training loop
+ * (training/train_lm.c:184-194, training/train_lm_gpu.c:212-223).  h_ids / h_targets hold this rank's
+ * `micro_batches` batches of B * T tokens back to back; their gradients accumulate in the flat buffer (every
+ * backward kernel adds, as the reference's do), the ranks' sums are combined once, and
+ * 1 / (ranks * micro_batches) scales the gradients before the norm is taken and clipped at max_norm.
+ * loss_out: mean loss over all ranks and micro-batches; norm_out: the global gradient norm.  With one rank
+ * and one micro-batch the step equals tb_trainer_train_step bit for bit. */
+int tb_dp_step(TbDp* dp, const uint32_t* h_ids, const uint32_t* h_targets, int micro_batches, uint64_t t, float lr,
+               float beta1, float beta2, float eps, float max_norm, float* loss_out, double* norm_out);
+/* The same step on the device-resident inputs of tb_trainer_set_inputs: no host transfer, no host
+ * synchronisation; tb_dp_last_result waits for the stream and returns that step's loss and norm. */
+int tb_dp_step_resident(TbDp* dp, uint64_t t, float lr, float beta1, float beta2, float eps, float max_norm);
+int tb_dp_last_result(TbDp* dp, float* loss_out, double* norm_out);
+
 /* ---- decoding with a KV cache --------------------------------------------------- */
 
 /* The reference generates by re-running lm_forward over the whole window for every new token

@@ -16,6 +16,7 @@
 #include "../../include/turkce_b200.h"
 #include "common.h"
 #include "step_kernels.h"
+#include "trainer_internal.h"
 
 #include <algorithm>
 #include <cmath>
@@ -51,7 +52,7 @@ struct TbTrainer {
     float scale = 0.f;
 
     std::vector<long long> offsets, numels;
-    long long total = 0;
+    long long total = 0, padded = 0;
     float *params = nullptr, *grads = nullptr, *adam_m = nullptr, *adam_v = nullptr;
     bf16* params16 = nullptr;
 
@@ -78,6 +79,7 @@ struct TbTrainer {
     // pinned host staging
     uint32_t *h_ids = nullptr, *h_targets = nullptr, *h_seg = nullptr;
     float* h_loss_rows = nullptr; double* h_norm = nullptr;
+    cudaEvent_t staged = nullptr; bool staged_pending = false;   // behind the last copy out of the pinned buffers
     int nseg = 0;
     uint32_t* nseg_dev = nullptr;
     std::vector<void*> allocs;
@@ -380,10 +382,15 @@ int stage_inputs(TbTrainer* g, const uint32_t* ids, const uint32_t* targets) {
     const size_t bytes = (size_t)g->N * sizeof(uint32_t);
     for (int i = 0; i < g->N; ++i)
         TB_CHECK(ids[i] < (uint32_t)g->V && targets[i] < (uint32_t)g->V, "token id out of range at position %d", i);
+    // the pinned staging buffers are reused: the copies of the previous batch (micro-batches of one optimiser
+    // step follow each other without a host synchronisation) must have left them
+    if (g->staged_pending) { TB_CUDA(cudaEventSynchronize(g->staged)); g->staged_pending = false; }
     std::memcpy(g->h_ids, ids, bytes);
     std::memcpy(g->h_targets, targets, bytes);
     TB_CUDA(cudaMemcpyAsync(g->ids, g->h_ids, bytes, cudaMemcpyHostToDevice, g->stream));
     TB_CUDA(cudaMemcpyAsync(g->targets, g->h_targets, bytes, cudaMemcpyHostToDevice, g->stream));
+    TB_CUDA(cudaEventRecord(g->staged, g->stream));
+    g->staged_pending = true;
     return 0;
 }
 
@@ -424,6 +431,8 @@ int stage_segments(TbTrainer* g) {
     g->h_seg[6 * N + 1] = (uint32_t)nseg;
     TB_CUDA(cudaMemcpyAsync(g->order, g->h_seg, (size_t)(6 * N + 2) * sizeof(uint32_t), cudaMemcpyHostToDevice,
                             g->stream));
+    TB_CUDA(cudaEventRecord(g->staged, g->stream));
+    g->staged_pending = true;
     return 0;
 }
 
@@ -455,6 +464,18 @@ int adam_launch(TbTrainer* g, uint64_t t, float lr, float b1, float b2, float ep
 }
 
 }  // namespace
+
+namespace tb {
+int trainer_view(TbTrainer* g, TrainerView* v) {
+    TB_CHECK(g != nullptr && v != nullptr, "trainer_view: null argument");
+    v->ctx = g->ctx; v->stream = g->stream; v->device = g->device;
+    v->total = g->total; v->padded = g->padded;
+    v->params = g->params; v->grads = g->grads; v->adam_m = g->adam_m; v->adam_v = g->adam_v; v->params16 = g->params16;
+    v->loss_rows = g->loss_rows; v->B = g->B; v->T = g->T; v->L = g->L;
+    v->norm_partial = g->norm_partial; v->scalars = g->scalars; v->norm64 = g->norm64; v->h_norm = g->h_norm;
+    return 0;
+}
+}  // namespace tb
 
 extern "C" {
 
@@ -495,12 +516,15 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
 
     const size_t N = g->N, BHT = (size_t)B * H * T;
     const size_t Tp = (size_t)g->Tp;
-    TB_TRY(dalloc(g, &g->params, g->total)); TB_TRY(dalloc(g, &g->grads, g->total));
-    TB_TRY(dalloc(g, &g->adam_m, g->total)); TB_TRY(dalloc(g, &g->adam_v, g->total));
-    TB_TRY(dalloc(g, &g->params16, g->total));
-    TB_CUDA(cudaMemset(g->params, 0, g->total * 4)); TB_CUDA(cudaMemset(g->grads, 0, g->total * 4));
-    TB_CUDA(cudaMemset(g->adam_m, 0, g->total * 4)); TB_CUDA(cudaMemset(g->adam_v, 0, g->total * 4));
-    TB_CUDA(cudaMemset(g->params16, 0, g->total * 2));
+    // the flat buffers carry kFlatPad spare scalars behind the last parameter: the data-parallel step keeps
+    // the rank's loss there (so one collective sums gradients and loss) and rounds its per-rank slices up
+    g->padded = g->total + kFlatPad;
+    TB_TRY(dalloc(g, &g->params, g->padded)); TB_TRY(dalloc(g, &g->grads, g->padded));
+    TB_TRY(dalloc(g, &g->adam_m, g->padded)); TB_TRY(dalloc(g, &g->adam_v, g->padded));
+    TB_TRY(dalloc(g, &g->params16, g->padded));
+    TB_CUDA(cudaMemset(g->params, 0, g->padded * 4)); TB_CUDA(cudaMemset(g->grads, 0, g->padded * 4));
+    TB_CUDA(cudaMemset(g->adam_m, 0, g->padded * 4)); TB_CUDA(cudaMemset(g->adam_v, 0, g->padded * 4));
+    TB_CUDA(cudaMemset(g->params16, 0, g->padded * 2));
 
     g->layers.resize(L);
     for (int l = 0; l < L; ++l) {
@@ -575,6 +599,7 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
     TB_CUDA(cudaMallocHost(&g->h_ids, N * 4)); TB_CUDA(cudaMallocHost(&g->h_targets, N * 4));
     TB_CUDA(cudaMallocHost(&g->h_seg, (6 * N + 4) * 4)); TB_CUDA(cudaMallocHost(&g->h_loss_rows, N * 4));
     TB_CUDA(cudaMallocHost(&g->h_norm, sizeof(double)));
+    TB_CUDA(cudaEventCreateWithFlags(&g->staged, cudaEventDisableTiming));
 
     // RoPE tables [T, hd/2] (model/rope.c:4-18), built on the host in float32
     {
@@ -604,6 +629,7 @@ int tb_trainer_destroy(TbTrainer* g) {
     for (void* p : g->allocs) cudaFree(p);
     cudaFreeHost(g->h_ids); cudaFreeHost(g->h_targets); cudaFreeHost(g->h_seg);
     cudaFreeHost(g->h_loss_rows); cudaFreeHost(g->h_norm);
+    if (g->staged) cudaEventDestroy(g->staged);
     delete g;
     return 0;
 }
@@ -659,7 +685,7 @@ int tb_trainer_download(TbTrainer* g, int which, float* h_flat) {
 }
 
 int tb_trainer_zero_grads(TbTrainer* g) {
-    TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->total * 4, g->stream));
+    TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->padded * 4, g->stream));
     return 0;
 }
 
@@ -688,7 +714,7 @@ int tb_trainer_step_resident(TbTrainer* g, uint64_t t, float lr, float beta1, fl
     // zeroing, forward and the whole backward are one graph (a single-GPU step has no reason to stop between
     // layers); the optimiser's scalars change every step, so clip + Adam stay ordinary launches
     TB_TRY(run_segment(g, SEG_STEP, [&]() {
-        TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->total * 4, g->stream));
+        TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->padded * 4, g->stream));
         TB_TRY(forward(g, true));
         TB_TRY(backward_head(g));
         for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));

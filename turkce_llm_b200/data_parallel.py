@@ -3,14 +3,22 @@
 
 The reference runs one sequence per CPU thread on a shadow model and then adds the workers'
 gradients in a fixed order and divides by the worker count (dp_reduce_run, :102-117).  Here every
-rank holds a full replica on its own GPU, processes its own sequences, and the flat float32
-gradient buffer is summed over ranks with one all-reduce per bucket; the division by the number of
-ranks is folded into Adam's gradient scale.  By default the whole flat buffer is reduced by one
-collective after the backward pass (0.4 ms for 134 MB on 8 GPUs).  The bucketed variant -- a bucket is one
-layer's ten tensors (contiguous in the flat layout), reduced as soon as that layer's backward has been
-issued; the tied embedding receives gradient both first (LM head) and last (token lookup), so its bucket
-goes last -- is kept (TB_DP_MODE=overlap): it measures slower with the current GEMM kernels, see below.
+rank holds a full replica on its own GPU and processes its own sequences; the flat float32 gradient
+buffer is summed over the ranks and the division by the number of ranks is folded into Adam's
+gradient scale.
+
+`DataParallel` binds the library's own step (tb_dp_* in include/turkce_b200.h: NCCL called from the
+library).  `DataParallelStep` is the same sequence written over torch.distributed on the staged
+tb_trainer_* calls, with the choice of where the collectives go (TB_DP_MODE: one all-reduce after the
+backward pass, one per layer bucket as soon as the layer's backward has been issued, or two halves);
+a bucket is one layer's ten tensors (contiguous in the flat layout); the tied embedding receives
+gradient both first (LM head) and last (token lookup), so its bucket goes last.
 """
+import ctypes as C
+import os
+
+import numpy as np
+
 from . import lib
 
 
@@ -75,11 +83,6 @@ class DataParallelStep:
         # TB_DP_MODE: "end" (default: one all-reduce of the flat buffer after the backward pass), "overlap"
         # (one all-reduce per layer bucket as soon as the layer's backward has been issued), "halves" (two
         # collectives), or for diagnosis "none" (no all-reduce: wrong results, timing only).
-        # Measured on 8 B200 (6.10 / 6.40 / 6.16 ms per step against 5.70 ms without any all-reduce): the
-        # persistent GEMM kernels hand out their tiles statically, one CTA per SM, so a communication CTA that
-        # occupies an SM while a GEMM runs holds up that whole GEMM -- the collectives under the backward pass
-        # cost more than the 0.4 ms they hide.
-        import os
         self.mode = os.environ.get("TB_DP_MODE", "end")
         self.stream = None
         self.loss_device = "cuda"      # where the ranks' losses are averaged (the host tests set "cpu")
@@ -182,3 +185,74 @@ class DataParallelStep:
                 self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
                 loss = float(t.item()) / self.world
             return loss, g.last_norm()
+
+
+ALLREDUCE, SHARDED = 0, 1
+
+
+class DataParallel:
+    """The library's data-parallel step (tb_dp_*): one instance per rank, over that rank's GpuTrainer.
+
+    `dist` (torch.distributed, any backend) is used once, to hand rank 0's NCCL id to the other ranks;
+    every collective of a step is issued by the library itself on the trainer's stream."""
+
+    def __init__(self, trainer, rank=0, world=1, dist=None, mode=None):
+        self.g = trainer
+        self._lib = lib.load()
+        if mode is None:
+            mode = SHARDED if os.environ.get("TB_DP_MODE", "allreduce") == "sharded" else ALLREDUCE
+        uid = None
+        if world > 1:
+            buf = (C.c_ubyte * 128)()
+            if rank == 0:
+                lib.check(self._lib.tb_dp_unique_id(buf))
+            box = [bytes(buf)]
+            dist.broadcast_object_list(box, src=0)
+            uid = (C.c_ubyte * 128).from_buffer_copy(box[0])
+        h = C.c_void_p()
+        lib.check(self._lib.tb_dp_create(C.byref(h), trainer.h, uid, rank, world, mode))
+        self.h = h
+        self.rank, self.world, self.mode = rank, world, mode
+
+    def destroy(self):
+        if self.h:
+            self._lib.tb_dp_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+    def describe(self):
+        r, w, m, v = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+        lib.check(self._lib.tb_dp_info(self.h, C.byref(r), C.byref(w), C.byref(m), C.byref(v)))
+        how = "one rank: no collective" if w.value == 1 else (
+            "reduce-scatter + Adam on the rank's slice + all-gather of the float32 weights" if m.value == SHARDED
+            else "one all-reduce of the flat float32 gradient buffer after the backward pass")
+        return {"entry": "tb_dp_step (C, NCCL called by the library)", "combine": how, "nccl_version": v.value}
+
+    def step_host(self, ids, targets, opt, max_norm):
+        """One optimiser step on this rank's host token buffers; returns (mean loss over ranks, gradient norm)."""
+        return self.step_host_accumulate([(ids, targets)], opt, max_norm)
+
+    def step_host_accumulate(self, batches, opt, max_norm):
+        """One optimiser step over several micro-batches [(ids, targets), ...] of this rank."""
+        ids = np.ascontiguousarray(np.concatenate([np.asarray(b[0], dtype=np.uint32).reshape(-1) for b in batches]))
+        tgt = np.ascontiguousarray(np.concatenate([np.asarray(b[1], dtype=np.uint32).reshape(-1) for b in batches]))
+        opt.t += 1
+        loss, norm = C.c_float(), C.c_double()
+        lib.check(self._lib.tb_dp_step(self.h, ids.ctypes.data, tgt.ctypes.data, len(batches), opt.t, opt.lr,
+                                       opt.beta1, opt.beta2, opt.eps, max_norm, C.byref(loss), C.byref(norm)))
+        return loss.value, norm.value
+
+    def step_resident(self, opt, max_norm):
+        """One optimiser step on the inputs already on the device (GpuTrainer.set_inputs); asynchronous."""
+        opt.t += 1
+        lib.check(self._lib.tb_dp_step_resident(self.h, opt.t, opt.lr, opt.beta1, opt.beta2, opt.eps, max_norm))
+
+    def last_result(self):
+        loss, norm = C.c_float(), C.c_double()
+        lib.check(self._lib.tb_dp_last_result(self.h, C.byref(loss), C.byref(norm)))
+        return loss.value, norm.value

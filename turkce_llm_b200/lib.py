@@ -87,6 +87,13 @@ SIGNATURES = {
     "tb_lr_warmup_cosine": (_f, [C.c_uint64, C.c_uint64, C.c_uint64, _f, _f]),
     "tb_checkpoint_save": (_i, [C.c_char_p, _vp, _i, C.c_uint64]),
     "tb_checkpoint_load": (_i, [C.c_char_p, _vp, _i, C.POINTER(C.c_uint64)]),
+    "tb_dp_unique_id": (_i, [_vp]),
+    "tb_dp_create": (_i, [C.POINTER(_vp), _vp, _vp, _i, _i, _i]),
+    "tb_dp_destroy": (_i, [_vp]),
+    "tb_dp_info": (_i, [_vp] + [C.POINTER(_i)] * 4),
+    "tb_dp_step": (_i, [_vp, _vp, _vp, _i, C.c_uint64, _f, _f, _f, _f, _f, C.POINTER(_f), C.POINTER(C.c_double)]),
+    "tb_dp_step_resident": (_i, [_vp, C.c_uint64, _f, _f, _f, _f, _f]),
+    "tb_dp_last_result": (_i, [_vp, C.POINTER(_f), C.POINTER(C.c_double)]),
     "tb_trainer_run": (_i, [_vp, _vp, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _f, _f, _f,
                             _f, _f, _f, C.POINTER(C.c_uint64), _vp, _vp]),
 }
