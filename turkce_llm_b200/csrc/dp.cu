@@ -92,16 +92,33 @@ int load_nccl() {
     } while (0)
 
 // Mean loss of this rank's batch, in the order the host code uses (mean inside a sequence, then over the
-// sequences: model/gpu_train.c:478-487), written or added to *slot.  One thread per sequence, sequential sums.
+// sequences: model/gpu_train.c:478-487), written or added to *slot.  Each warp takes sequences in turn: its lanes
+// fetch 32 consecutive rows at a time (one coalesced load) and lane 0 adds them in row order, so the sum is the
+// sequential float32 sum of the host loop.
 __global__ void loss_mean_kernel(const float* __restrict__ loss_rows, int B, int T, float* __restrict__ slot, int accumulate) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ float per_seq[];
-    for (int b = threadIdx.x; b < B; b += blockDim.x) {
-        float s = 0.0f;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int b = warp; b < B; b += nwarps) {
         const float* r = loss_rows + (size_t)b * T;
-        for (int t = 0; t < T; ++t) s += r[t];
-        per_seq[b] = s / (float)T;
+        float s = 0.0f;
+        for (int t0 = 0; t0 < T; t0 += 128) {
+            float v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = t0 + k * 32 + lane < T ? r[t0 + k * 32 + lane] : 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int n = min(32, T - (t0 + k * 32));
+                if (n == 32) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) s += __shfl_sync(0xffffffffu, v[k], j);   // every lane forms the same sum
+                } else {
+                    for (int j = 0; j < n; ++j) s += __shfl_sync(0xffffffffu, v[k], j);
+                }
+            }
+        }
+        if (lane == 0) per_seq[b] = s / (float)T;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -163,7 +180,7 @@ int backward_all(TbDp* dp) {
 
 int mean_loss_to_slot(TbDp* dp, int accumulate) {
     const TrainerView& v = dp->v;
-    const int threads = v.B < 32 ? 32 : (v.B > 1024 ? 1024 : (v.B + 31) / 32 * 32);
+    const int threads = 32 * (v.B < 32 ? v.B : 32);          // one warp per sequence, up to 32 warps
     prof_mark(v.ctx, "loss_mean", 0.0, 0.0, v.stream);
     TB_CUDA(launch_kernel(loss_mean_kernel, dim3(1), dim3(threads), (size_t)v.B * sizeof(float), v.stream, v.loss_rows,
                           v.B, v.T, v.grads + v.total, accumulate));
