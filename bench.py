@@ -16,6 +16,7 @@ of the ids and the device->host read of the loss inside the timed region.  Besid
 timed regions, the line carries sub-records for the other benchmark configurations:
   c1  one layer's four linear GEMMs (forward, dX, dW) in the three operand precisions: device time,
       TFLOP/s, error against the CPU oracle, and the reference's own tensor_matmul2d on the host cores
+  tf32_step  the headline step with the linear-layer GEMMs in TF32 mode, with its own roofline
   c3  fused causal attention at B=16, H=6, T=1024, hd=64 (forward and backward)
   c4  batched decoding with a KV cache: 64 sequences, 128-token prompts, 128 greedy tokens
   c5  the data-parallel step with a fixed global batch of 128 x 1024 tokens (at every N)
@@ -340,7 +341,7 @@ def run_ours(args):
             result["c5"] = {k: c5[k] for k in ("value", "unit", "ms_per_step", "steps", "warmup", "scaling", "config",
                                                "final_loss", "grad_norm", "gpu_launches")}
         if rank == 0 and world == 1:
-            for name, fn in (("c1", bench_c1), ("c3", bench_c3), ("c4", bench_c4),
+            for name, fn in (("tf32_step", bench_tf32_step), ("c1", bench_c1), ("c3", bench_c3), ("c4", bench_c4),
                              ("reference_gpu_trainer", bench_reference_gpu_trainer),
                              ("cpu_baseline", cpu_baseline_port)):
                 try:
@@ -788,6 +789,58 @@ def bench_reference_gpu_trainer(steps=8):
                     "its own 26 kernels compiled by nvcc for sm_100a; %d steps (difference of a %d-step and a 2-step run)"
                     % (steps, 2 + steps),
             "first_loss": runs[1]["losses"][0]}
+
+
+def bench_tf32_step(steps=10):
+    """The same training step with the linear-layer GEMMs in TF32 mode (float32 weights and activations read by
+    the tensor cores as tf32): device-resident step time and the GEMM roofline against the TF32 peak.  No TF32 peak
+    has been measured on this pool, so the denominator is half the measured burst bf16 peak (the nominal ratio)."""
+    import torch
+    from turkce_llm_b200 import lib
+    from turkce_llm_b200.gpu_train import AdamState, GpuTrainer
+    V, D, H, L, F = (MODEL[k] for k in "VDHLF")
+    B, T = BATCH, CONTEXT
+    pk = peaks()
+    g = GpuTrainer(V, D, H, L, F, T, B, 1e-5, precision=lib.PREC_TF32)
+    g.upload(init_params(g.total, g.param_layout(), seed=0))
+    opt = AdamState(LR, BETA1, BETA2, ADAM_EPS)
+    stream = zipf_ids(B * T + 1, V, seed=1)
+    g.set_inputs(stream[:-1].copy(), stream[1:].copy())
+    st = torch.cuda.ExternalStream(g.stream_ptr())
+    with torch.cuda.stream(st):
+        for _ in range(4):
+            g.step_resident(opt, MAX_NORM)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            g.step_resident(opt, MAX_NORM)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        loss = g.read_loss()
+        torch.cuda._sleep(20_000_000)
+        lib.profile_begin()
+        g.step_resident(opt, MAX_NORM)
+        prof = lib.profile_end(g.stream_ptr())
+        torch.cuda.synchronize()
+    g.destroy()
+    gemm = {"launches": 0, "ms": 0.0, "flops": 0.0}
+    for name, v in prof.items():
+        if name.startswith("gemm_tf32"):
+            for k in gemm:
+                gemm[k] += v[k]
+    achieved = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] > 0 else None
+    peak = pk["burst"] / 2
+    return {"dtype": "tf32", "ms_per_step": round(ms, 3), "tokens_per_s": round(B * T / ms * 1e3), "steps": steps,
+            "loss_after": loss,
+            "workload": "the headline training step with TB_PREC_TF32: float32 operands as tf32 in every linear-layer "
+                        "GEMM (forward, dX, dW, LM head); attention core bf16",
+            "roofline": {"bound": "tensor", "kernel": "gemm_bf16_kernel<BN, TF32>", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak if achieved else None,
+                         "peak_source": "half of the %s burst bf16 peak (no TF32 peak measured on this pool)" % pk["src"],
+                         "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"],
+                         "algorithmic_gflop_per_step": gemm["flops"] / 1e9}}
 
 
 def cpu_baseline_port():

@@ -198,6 +198,12 @@ typedef struct TbTrainer TbTrainer;
  * an LMModel*, the weights through tb_trainer_upload.  d_model, d_ff and head_dim must be
  * multiples of 8.  All work of this trainer is issued on `stream`. */
 int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T, int B, float eps, void* stream);
+/* The same with the operand precision of the linear-layer GEMMs (forward, dX, dW and the LM head) chosen:
+ * TB_PREC_BF16 (what tb_trainer_create gives) or TB_PREC_TF32 -- float32 weights and activations read by the
+ * tensor cores as tf32 (kind::tf32), float32 accumulation; the attention core stays the fused bf16 kernel in
+ * both (the reference's attention products are bf16: model/gpu_train.c:346-353).  Other values are rejected. */
+int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, int T, int B, float eps, int precision,
+                           void* stream);
 /* gpu_trainer_destroy (model/gpu_train.h:93) */
 int tb_trainer_destroy(TbTrainer* g);
 int64_t tb_trainer_total_scalars(const TbTrainer* g);

@@ -192,6 +192,9 @@ int launch_lmhead_argmax(DeviceCtx* ctx, const bf16* X, const bf16* E, int S, in
 int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int cols, long long ld_src,
                      long long ld_dst, int batch, long long stride_src, long long stride_dst, cudaStream_t stream);
 
+// bf16 -> float32, n elements (n % 4 == 0)
+int launch_widen_bf16(DeviceCtx* ctx, const bf16* src, float* dst, long long n, cudaStream_t stream);
+
 static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
 
 // ---- launches with programmatic dependent launch: the next kernel of the stream may be scheduled

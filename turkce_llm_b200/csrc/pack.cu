@@ -139,3 +139,33 @@ int launch_split3_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, in
 }
 
 }  // namespace tb
+
+namespace tb {
+
+// bf16 -> float32 (exact): the TF32 mode of the trainer widens the outputs of the attention kernels, which
+// stay bf16, before they enter a float32-operand GEMM.  n must be a multiple of 4, pointers 16-byte aligned.
+__global__ void widen_bf16_kernel(const uint2* __restrict__ src, float4* __restrict__ dst, long long n4) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        const uint2 v = src[i];
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+        dst[i] = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+    }
+}
+
+int launch_widen_bf16(DeviceCtx* ctx, const bf16* src, float* dst, long long n, cudaStream_t stream) {
+    TB_CHECK(n > 0 && n % 4 == 0, "widen: element count must be a positive multiple of 4");
+    long long blocks = (n / 4 + 255) / 256;
+    if (blocks > 8LL * ctx->sm_count) blocks = 8LL * ctx->sm_count;
+    prof_mark(ctx, "widen_bf16", 0.0, (double)n * 6.0, stream);
+    TB_CUDA(launch_kernel(widen_bf16_kernel, dim3((unsigned)blocks), dim3(256), 0, stream,
+                          reinterpret_cast<const uint2*>(src), reinterpret_cast<float4*>(dst), n / 4));
+    TB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    prof_close(ctx, stream);
+    return 0;
+}
+
+}  // namespace tb

@@ -123,7 +123,8 @@ int launch_embed_bwd(DeviceCtx* ctx, const float* dx, const uint32_t* order, con
 // -------------------------------------------------------------------- RMSNorm
 // y = x * r * w,  r = 1/sqrt(mean(x^2) + eps)   (model/model_ops.c; eps inside the root)
 __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                   bf16* __restrict__ out, float* __restrict__ rinv, int rows, int cols, float eps) {
+                                   bf16* __restrict__ out, float* __restrict__ out32, float* __restrict__ rinv,
+                                   int rows, int cols, float eps) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -137,15 +138,19 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
         const float ms = ss / (float)cols;
         const float r = 1.0f / (float)sqrt((double)(ms + eps));
         if (lane == 0) rinv[row] = r;
-        bf16* orow = out + row * cols;
-        for (int i = lane; i < cols; i += 32) orow[i] = __float2bfloat16_rn(xr[i] * r * w[i]);
+        for (int i = lane; i < cols; i += 32) {
+            const float y = xr[i] * r * w[i];
+            if (out) out[row * cols + i] = __float2bfloat16_rn(y);
+            if (out32) out32[row * cols + i] = y;
+        }
     }
 }
 
 // the same with 16-byte loads and 8-byte stores (cols % 4 == 0, cols <= 4 * 32 * NV)
 template <int NV>
 __global__ void rmsnorm_fwd_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                       bf16* __restrict__ out, float* __restrict__ rinv, int rows, int cols, float eps) {
+                                       bf16* __restrict__ out, float* __restrict__ out32, float* __restrict__ rinv,
+                                       int rows, int cols, float eps) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -170,24 +175,28 @@ __global__ void rmsnorm_fwd_vec_kernel(const float* __restrict__ x, const float*
             const int j = 4 * (lane + 32 * k);
             if (j < cols) {
                 const float4 wv = *reinterpret_cast<const float4*>(w + j);
-                __nv_bfloat162 lo = __floats2bfloat162_rn(xv[k].x * r * wv.x, xv[k].y * r * wv.y);
-                __nv_bfloat162 hi = __floats2bfloat162_rn(xv[k].z * r * wv.z, xv[k].w * r * wv.w);
-                uint2 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(out + row * cols + j) = pk;
+                const float4 y = make_float4(xv[k].x * r * wv.x, xv[k].y * r * wv.y, xv[k].z * r * wv.z, xv[k].w * r * wv.w);
+                if (out) {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn(y.z, y.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(out + row * cols + j) = pk;
+                }
+                if (out32) *reinterpret_cast<float4*>(out32 + row * cols + j) = y;
             }
         }
     }
 }
 
 int launch_rmsnorm_fwd(DeviceCtx* ctx, const float* x, const float* w, bf16* out, float* rinv, int rows, int cols,
-                       float eps, cudaStream_t st) {
+                       float eps, cudaStream_t st, float* out32) {
     prof_mark(ctx, "rmsnorm_fwd", 0.0, 0.0, st);
     if (cols % 4 == 0 && cols <= 384 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0 &&
-        (reinterpret_cast<uintptr_t>(out) & 7u) == 0)
-        TB_CUDA(launch_kernel(rmsnorm_fwd_vec_kernel<3>, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, out, rinv, rows, cols, eps));
+        (reinterpret_cast<uintptr_t>(out) & 7u) == 0 && (reinterpret_cast<uintptr_t>(out32) & 15u) == 0)
+        TB_CUDA(launch_kernel(rmsnorm_fwd_vec_kernel<3>, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, out, out32, rinv, rows, cols, eps));
     else
-        TB_CUDA(launch_kernel(rmsnorm_fwd_kernel, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, out, rinv, rows, cols, eps));
+        TB_CUDA(launch_kernel(rmsnorm_fwd_kernel, dim3(grid_for(rows, 8, ctx)), dim3(256), 0, st, x, w, out, out32, rinv, rows, cols, eps));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -992,7 +1001,8 @@ int launch_heads_split(DeviceCtx* ctx, const bf16* dout, bf16* dO, int B, int T,
 
 // --------------------------------------------------------------------- SwiGLU
 // h = g * sigmoid(g) * u with g = gu[:, :F], u = gu[:, F:]   (model/feedforward.c:9-14)
-__global__ void swiglu_fwd_kernel(const float* __restrict__ gu, bf16* __restrict__ h, long long total4, int F) {
+__global__ void swiglu_fwd_kernel(const float* __restrict__ gu, bf16* __restrict__ h, float* __restrict__ h32,
+                                  long long total4, int F) {
     pdl_wait();
     pdl_launch_dependents();
     const int F4 = F >> 2;
@@ -1009,18 +1019,21 @@ __global__ void swiglu_fwd_kernel(const float* __restrict__ gu, bf16* __restrict
             const float sg = 1.0f / (1.0f + expf(-gg[e]));
             o[e] = gg[e] * sg * uu[e];
         }
-        __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
-        uint2 pk;
-        pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(h + n * F + j) = pk;
+        if (h) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(h + n * F + j) = pk;
+        }
+        if (h32) *reinterpret_cast<float4*>(h32 + n * F + j) = make_float4(o[0], o[1], o[2], o[3]);
     }
 }
 
-int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F, cudaStream_t st) {
+int launch_swiglu_fwd(DeviceCtx* ctx, const float* gu, bf16* h, int rows, int F, cudaStream_t st, float* h32) {
     TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
     const long long total = (long long)rows * (F / 4);
     prof_mark(ctx, "swiglu_fwd", 0.0, 0.0, st);
-    TB_CUDA(launch_kernel(swiglu_fwd_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, h, total, F));
+    TB_CUDA(launch_kernel(swiglu_fwd_kernel, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, h, h32, total, F));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -1045,7 +1058,7 @@ template <> struct Load4<bf16> {
 // TG = float: the stored projection; TG = bf16: the copy the fused SwiGLU GEMM epilogue keeps
 template <typename TG>
 __global__ void swiglu_bwd_kernel(const TG* __restrict__ gu, const float* __restrict__ dh,
-                                  bf16* __restrict__ dgu, long long total4, int F) {
+                                  bf16* __restrict__ dgu, float* __restrict__ dgu32, long long total4, int F) {
     pdl_wait();
     pdl_launch_dependents();
     const int F4 = F >> 2;
@@ -1066,21 +1079,28 @@ __global__ void swiglu_bwd_kernel(const TG* __restrict__ gu, const float* __rest
             og[e] = dsilu * sg + dsilu * gg[e] * sg * (1.0f - sg);
             ou[e] = dd[e] * gg[e] * sg;
         }
-        __nv_bfloat162 a = __floats2bfloat162_rn(og[0], og[1]), b = __floats2bfloat162_rn(og[2], og[3]);
-        __nv_bfloat162 c = __floats2bfloat162_rn(ou[0], ou[1]), d = __floats2bfloat162_rn(ou[2], ou[3]);
-        uint2 pg, pu;
-        pg.x = *reinterpret_cast<uint32_t*>(&a); pg.y = *reinterpret_cast<uint32_t*>(&b);
-        pu.x = *reinterpret_cast<uint32_t*>(&c); pu.y = *reinterpret_cast<uint32_t*>(&d);
-        *reinterpret_cast<uint2*>(dgu + n * 2 * F + j) = pg;
-        *reinterpret_cast<uint2*>(dgu + n * 2 * F + F + j) = pu;
+        if (dgu) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(og[0], og[1]), b = __floats2bfloat162_rn(og[2], og[3]);
+            __nv_bfloat162 c = __floats2bfloat162_rn(ou[0], ou[1]), d = __floats2bfloat162_rn(ou[2], ou[3]);
+            uint2 pg, pu;
+            pg.x = *reinterpret_cast<uint32_t*>(&a); pg.y = *reinterpret_cast<uint32_t*>(&b);
+            pu.x = *reinterpret_cast<uint32_t*>(&c); pu.y = *reinterpret_cast<uint32_t*>(&d);
+            *reinterpret_cast<uint2*>(dgu + n * 2 * F + j) = pg;
+            *reinterpret_cast<uint2*>(dgu + n * 2 * F + F + j) = pu;
+        }
+        if (dgu32) {
+            *reinterpret_cast<float4*>(dgu32 + n * 2 * F + j) = make_float4(og[0], og[1], og[2], og[3]);
+            *reinterpret_cast<float4*>(dgu32 + n * 2 * F + F + j) = make_float4(ou[0], ou[1], ou[2], ou[3]);
+        }
     }
 }
 
-int launch_swiglu_bwd(DeviceCtx* ctx, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t st) {
+int launch_swiglu_bwd(DeviceCtx* ctx, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t st,
+                      float* dgu32) {
     TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
     const long long total = (long long)rows * (F / 4);
     prof_mark(ctx, "swiglu_bwd", 0.0, 0.0, st);
-    TB_CUDA(launch_kernel(swiglu_bwd_kernel<float>, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, dh, dgu, total, F));
+    TB_CUDA(launch_kernel(swiglu_bwd_kernel<float>, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, dh, dgu, dgu32, total, F));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -1089,7 +1109,7 @@ int launch_swiglu_bwd_bf16(DeviceCtx* ctx, const bf16* gu, const float* dh, bf16
     TB_CHECK(F % 4 == 0, "d_ff must be a multiple of 4");
     const long long total = (long long)rows * (F / 4);
     prof_mark(ctx, "swiglu_bwd", 0.0, 0.0, st);
-    TB_CUDA(launch_kernel(swiglu_bwd_kernel<bf16>, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, dh, dgu, total, F));
+    TB_CUDA(launch_kernel(swiglu_bwd_kernel<bf16>, dim3(grid_for(total, 256, ctx)), dim3(256), 0, st, gu, dh, dgu, (float*)nullptr, total, F));
     TB_LAUNCHED(ctx);
     return 0;
 }
@@ -1173,8 +1193,8 @@ __device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
 
 // loss = log(sum exp(z - max)) + max - z[target];  dlogits = (softmax - onehot) * grad_scale
 __global__ void cross_entropy_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
-                                     float* __restrict__ loss_rows, bf16* __restrict__ dlogits, int V, long long ld,
-                                     float grad_scale) {
+                                     float* __restrict__ loss_rows, bf16* __restrict__ dlogits,
+                                     float* __restrict__ dlogits32, int V, long long ld, float grad_scale) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float sh[32];
@@ -1188,13 +1208,13 @@ __global__ void cross_entropy_kernel(const float* __restrict__ logits, const uin
     for (int j = threadIdx.x; j < V; j += blockDim.x) sum += expf(z[j] - mx);
     sum = block_reduce(sum, sh, false);
     if (threadIdx.x == 0) loss_rows[row] = (float)log((double)sum) + mx - z[t];
-    if (dlogits) {
+    if (dlogits || dlogits32) {
         const float inv = 1.0f / sum;
-        bf16* d = dlogits + row * ld;
         for (int j = threadIdx.x; j < V; j += blockDim.x) {
             float p = expf(z[j] - mx) * inv;
             if (j == t) p -= 1.0f;
-            d[j] = __float2bfloat16_rn(p * grad_scale);
+            if (dlogits) dlogits[row * ld + j] = __float2bfloat16_rn(p * grad_scale);
+            if (dlogits32) dlogits32[row * ld + j] = p * grad_scale;
         }
     }
 }
@@ -1202,8 +1222,8 @@ __global__ void cross_entropy_kernel(const float* __restrict__ logits, const uin
 // One read of the row: 1024 threads hold up to 32 logits each in registers (V <= 32768).
 __global__ void __launch_bounds__(1024, 1)
 cross_entropy_row_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
-                         float* __restrict__ loss_rows, bf16* __restrict__ dlogits, int V, long long ld,
-                         float grad_scale) {
+                         float* __restrict__ loss_rows, bf16* __restrict__ dlogits, float* __restrict__ dlogits32, int V,
+                         long long ld, float grad_scale) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float sh[32];
@@ -1228,16 +1248,16 @@ cross_entropy_row_kernel(const float* __restrict__ logits, const uint32_t* __res
     }
     sum = block_reduce(sum, sh, false);
     if (threadIdx.x == 0) loss_rows[row] = (float)log((double)sum) + mx - z[t];
-    if (dlogits) {
+    if (dlogits || dlogits32) {
         const float inv = 1.0f / sum;
-        bf16* d = dlogits + row * ld;
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
             const int j = threadIdx.x + k * 1024;
             if (j < V) {
                 float p = v[k] * inv;
                 if (j == t) p -= 1.0f;
-                d[j] = __float2bfloat16_rn(p * grad_scale);
+                if (dlogits) dlogits[row * ld + j] = __float2bfloat16_rn(p * grad_scale);
+                if (dlogits32) dlogits32[row * ld + j] = p * grad_scale;
             }
         }
     }
@@ -1293,12 +1313,13 @@ int launch_ce_combine(DeviceCtx* ctx, const float* stats, int parts, int rows, c
 }
 
 int launch_cross_entropy(DeviceCtx* ctx, const float* logits, const uint32_t* targets, float* loss_rows,
-                         bf16* dlogits, int rows, int V, long long ld, float grad_scale, cudaStream_t st) {
+                         bf16* dlogits, int rows, int V, long long ld, float grad_scale, cudaStream_t st,
+                         float* dlogits32) {
     prof_mark(ctx, "cross_entropy", 0.0, 0.0, st);
     if (V > 4096 && V <= 32768)
-        TB_CUDA(launch_kernel(cross_entropy_row_kernel, dim3(rows), dim3(1024), 0, st, logits, targets, loss_rows, dlogits, V, ld, grad_scale));
+        TB_CUDA(launch_kernel(cross_entropy_row_kernel, dim3(rows), dim3(1024), 0, st, logits, targets, loss_rows, dlogits, dlogits32, V, ld, grad_scale));
     else
-        TB_CUDA(launch_kernel(cross_entropy_kernel, dim3(rows), dim3(512), 0, st, logits, targets, loss_rows, dlogits, V, ld, grad_scale));
+        TB_CUDA(launch_kernel(cross_entropy_kernel, dim3(rows), dim3(512), 0, st, logits, targets, loss_rows, dlogits, dlogits32, V, ld, grad_scale));
     TB_LAUNCHED(ctx);
     return 0;
 }

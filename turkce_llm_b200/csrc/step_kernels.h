@@ -10,8 +10,9 @@
 namespace tb {
 
 int launch_embed_fwd(DeviceCtx*, const float* E, const uint32_t* ids, float* x, int rows, int D, cudaStream_t);
+// (out32, when given, receives the same values unrounded; out may then be NULL)
 int launch_rmsnorm_fwd(DeviceCtx*, const float* x, const float* w, bf16* out, float* rinv, int rows, int cols,
-                       float eps, cudaStream_t);
+                       float eps, cudaStream_t, float* out32 = nullptr);
 // dx (+)= rmsnorm backward; dx16 = bf16(dx); wtmp[n,j] = dy*x*r (summed over rows by colsum)
 int launch_rmsnorm_bwd(DeviceCtx*, const float* x, const float* w, const float* rinv, const float* dy, float* dx,
                        bf16* dx16, float* wtmp, int rows, int cols, int accumulate, cudaStream_t);
@@ -47,8 +48,10 @@ int launch_attn_softmax_fwd(DeviceCtx*, const float* S, bf16* P, int BH, int T, 
 int launch_attn_softmax_bwd(DeviceCtx*, const bf16* P, const float* dP, bf16* dS, int BH, int T, long long ld,
                             float scale, cudaStream_t);
 int launch_heads_split(DeviceCtx*, const bf16* dout, bf16* dO, int B, int T, int H, int hd, cudaStream_t);
-int launch_swiglu_fwd(DeviceCtx*, const float* gu, bf16* h, int rows, int F, cudaStream_t);
-int launch_swiglu_bwd(DeviceCtx*, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t);
+// (h32 / dgu32, when given, receive the float32 values; the bf16 output may then be NULL)
+int launch_swiglu_fwd(DeviceCtx*, const float* gu, bf16* h, int rows, int F, cudaStream_t, float* h32 = nullptr);
+int launch_swiglu_bwd(DeviceCtx*, const float* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t,
+                      float* dgu32 = nullptr);
 // the same with gate|up kept in bf16 by the fused SwiGLU GEMM epilogue
 int launch_swiglu_bwd_bf16(DeviceCtx*, const bf16* gu, const float* dh, bf16* dgu, int rows, int F, cudaStream_t);
 // ... and with the gate|up bias gradient (dbias[2F] += column sums of dgu) produced on the way;
@@ -62,7 +65,7 @@ int launch_swiglu_bwd_colsum(DeviceCtx*, const bf16* gu, const float* dh, bf16* 
 int launch_ce_combine(DeviceCtx*, const float* stats, int parts, int rows, const float* ztarget, float* lse,
                       float* loss_rows, cudaStream_t);
 int launch_cross_entropy(DeviceCtx*, const float* logits, const uint32_t* targets, float* loss_rows, bf16* dlogits,
-                         int rows, int V, long long ld, float grad_scale, cudaStream_t);
+                         int rows, int V, long long ld, float grad_scale, cudaStream_t, float* dlogits32 = nullptr);
 // out[c] += sum_r in[r,c]; in is fp32 or bf16; partial needs colsum_partial_floats(cols) floats, zeroed once
 size_t colsum_partial_floats(int cols);
 int launch_colsum_f32(DeviceCtx*, const float* in, float* out, float* partial, int rows, int cols, cudaStream_t);

@@ -31,6 +31,7 @@ namespace {
 enum { PK_ATTN_NORM = 0, PK_WQKV, PK_BQKV, PK_WO, PK_BO, PK_FFN_NORM, PK_WGU, PK_BGU, PK_WDOWN, PK_BDOWN };
 
 struct LayerActs {
+    float *n1_32 = nullptr, *n2_32 = nullptr, *h32 = nullptr;    // TF32 mode: float32 GEMM operands
     float* x_in;  bf16* n1; float* r1;
     bf16 *Q, *K, *V, *P, *att;     // P [BH,T,T] only on the unfused attention path
     float* lse;                    // [BH,T] on the fused path
@@ -93,6 +94,12 @@ struct TbTrainer {
     bool fused_rope = true;        // T % 32 == 0, head_dim 32 or 64: rotation and head split in the QKV GEMM epilogue
     bool fused_ce = true;          // cross-entropy inside the LM-head GEMM epilogues: no [N, V] logits
     bool fused_swiglu = true;      // d_ff % 64 == 0: silu(gate) * up formed in the gate|up GEMM's epilogue
+    // TF32 mode (TB_PREC_TF32): every linear-layer GEMM (forward, dX, dW, LM head) reads float32 operands as tf32
+    // (kind::tf32); weights are the float32 masters, activations and gradients that feed a GEMM are kept in float32.
+    // The attention core stays the fused bf16 kernel (the reference's attention products are bf16 as well);
+    // its outputs are widened.  The fused epilogues are those of the bf16 path and are switched off here.
+    bool tf32 = false;
+    float *nf32 = nullptr, *dlogits32 = nullptr, *dgu32 = nullptr, *dqkv32 = nullptr, *att32 = nullptr;
     float* att_delta = nullptr;
     bool owns_stream = false;
 };
@@ -119,33 +126,39 @@ int gemm(TbTrainer* g, GemmArgs& a) {
     return launch_gemm_bf16_ws(g->ctx, a, g->splitk_ws, g->splitk_floats, g->stream);
 }
 
-// C[M,N] = A[M,K] @ W[K,N] + bias (+ residual): the reference's bf16_gemm_bias (gpu_train.c:103-107)
-int linear_fwd(TbTrainer* g, const bf16* A, const bf16* W, const float* bias, const float* residual, float* C32,
+// C[M,N] = A[M,K] @ W[K,N] + bias (+ residual): the reference's bf16_gemm_bias (gpu_train.c:103-107).
+// Operands are bf16, or float32 read as tf32 in the TF32 mode.
+int linear_fwd(TbTrainer* g, const void* A, const void* W, const float* bias, const float* residual, float* C32,
                bf16* C16, int M, int N, int K) {
     GemmArgs a;
     a.kind = GEMM_NN; a.A = A; a.B = W; a.M = M; a.N = N; a.K = K; a.lda = K; a.ldb = N;
     a.C32 = C32; a.ldc32 = N; a.C16 = C16; a.ldc16 = N;
     a.bias = bias; a.residual = residual; a.ldr = N;
-    a.splits = 1;
+    a.splits = 1; a.tf32 = g->tf32;
     return gemm(g, a);
 }
 
 // dX[M,K] = dY[M,N] @ W[K,N]^T : the reference's bf16_gemm1(GEMM_NT) (gpu_train.c:419,427,434,463)
-int linear_dx(TbTrainer* g, const bf16* dY, const bf16* W, float* dX32, bf16* dX16, int M, int N, int K) {
+int linear_dx(TbTrainer* g, const void* dY, const void* W, float* dX32, bf16* dX16, int M, int N, int K) {
     GemmArgs a;
     a.kind = GEMM_NT; a.A = dY; a.B = W; a.M = M; a.N = K; a.K = N; a.lda = N; a.ldb = N;
     a.C32 = dX32; a.ldc32 = K; a.C16 = dX16; a.ldc16 = K;
-    a.splits = 1;
+    a.splits = 1; a.tf32 = g->tf32;
     return gemm(g, a);
 }
 
 // dW[K,N] += X[M,K]^T @ dY[M,N] : the reference's gemm1(GEMM_TN, beta=1) (gpu_train.c:417,425,432,461)
-int linear_dw(TbTrainer* g, const bf16* X, const bf16* dY, float* dW, int M, int N, int K) {
+int linear_dw(TbTrainer* g, const void* X, const void* dY, float* dW, int M, int N, int K) {
     GemmArgs a;
     a.kind = GEMM_TN; a.A = X; a.B = dY; a.M = K; a.N = N; a.K = M; a.lda = K; a.ldb = N;
     a.C32 = dW; a.ldc32 = N; a.beta = 1.0f;
-    a.splits = 0;
+    a.splits = 0; a.tf32 = g->tf32;
     return gemm(g, a);
+}
+
+// the weight matrix of parameter i as a GEMM operand: the bf16 shadow, or the float32 master in the TF32 mode
+inline const void* WOP(TbTrainer* g, long long i) {
+    return g->tf32 ? static_cast<const void*>(P32(g, i)) : static_cast<const void*>(P16(g, i));
 }
 
 int forward(TbTrainer* g, bool want_grad) {
@@ -161,7 +174,7 @@ int forward(TbTrainer* g, bool want_grad) {
     for (int l = 0; l < g->L; ++l) {
         LayerActs& a = g->layers[l];
         float* x_out = (l + 1 < g->L) ? g->layers[l + 1].x_in : g->x_final;
-        TB_TRY(launch_rmsnorm_fwd(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.n1, a.r1, N, D, g->eps, st));
+        TB_TRY(launch_rmsnorm_fwd(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.n1, a.r1, N, D, g->eps, st, a.n1_32));
         if (g->fused_rope) {
             // QKV projection; q and k rotated and all three stored per head as bf16 by the GEMM epilogue
             GemmArgs s;
@@ -171,8 +184,8 @@ int forward(TbTrainer* g, bool want_grad) {
             if (const char* e = getenv("TB_ROPE_BN")) s.bn = atoi(e);
             TB_TRY(gemm(g, s));
         } else {
-            TB_TRY(linear_fwd(g, a.n1, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, N,
-                              3 * D, D));
+            TB_TRY(linear_fwd(g, g->tf32 ? (const void*)a.n1_32 : (const void*)a.n1, WOP(g, pidx(l, PK_WQKV)),
+                              P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, N, 3 * D, D));
             TB_TRY(launch_rope_split(c, g->qkv, g->cos_t, g->sin_t, a.Q, a.K, a.V, B, T, H, hd, T, st));
         }
         if (g->fused_attention) {
@@ -196,8 +209,10 @@ int forward(TbTrainer* g, bool want_grad) {
                 TB_TRY(gemm(g, o));
             }
         }
-        TB_TRY(linear_fwd(g, a.att, P16(g, pidx(l, PK_WO)), P32(g, pidx(l, PK_BO)), a.x_in, a.x2, nullptr, N, D, D));
-        TB_TRY(launch_rmsnorm_fwd(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.n2, a.r2, N, D, g->eps, st));
+        if (g->tf32) TB_TRY(launch_widen_bf16(c, a.att, g->att32, (long long)N * D, st));
+        TB_TRY(linear_fwd(g, g->tf32 ? (const void*)g->att32 : (const void*)a.att, WOP(g, pidx(l, PK_WO)),
+                          P32(g, pidx(l, PK_BO)), a.x_in, a.x2, nullptr, N, D, D));
+        TB_TRY(launch_rmsnorm_fwd(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.n2, a.r2, N, D, g->eps, st, a.n2_32));
         if (g->fused_swiglu) {
             // gate|up projection with h = silu(gate) * up formed in the GEMM epilogue; gate|up kept in bf16
             GemmArgs s;
@@ -206,16 +221,16 @@ int forward(TbTrainer* g, bool want_grad) {
             s.swiglu_h = a.h; s.ldh = F; s.swiglu_gu = a.gu16; s.ldgu = 2 * F;
             TB_TRY(gemm(g, s));
         } else {
-            TB_TRY(linear_fwd(g, a.n2, P16(g, pidx(l, PK_WGU)), P32(g, pidx(l, PK_BGU)), nullptr, a.gu, nullptr, N,
-                              2 * F, D));
-            TB_TRY(launch_swiglu_fwd(c, a.gu, a.h, N, F, st));
+            TB_TRY(linear_fwd(g, g->tf32 ? (const void*)a.n2_32 : (const void*)a.n2, WOP(g, pidx(l, PK_WGU)),
+                              P32(g, pidx(l, PK_BGU)), nullptr, a.gu, nullptr, N, 2 * F, D));
+            TB_TRY(launch_swiglu_fwd(c, a.gu, g->tf32 ? nullptr : a.h, N, F, st, a.h32));
         }
-        TB_TRY(linear_fwd(g, a.h, P16(g, pidx(l, PK_WDOWN)), P32(g, pidx(l, PK_BDOWN)), a.x2, x_out, nullptr, N, D,
-                          F));
+        TB_TRY(linear_fwd(g, g->tf32 ? (const void*)a.h32 : (const void*)a.h, WOP(g, pidx(l, PK_WDOWN)),
+                          P32(g, pidx(l, PK_BDOWN)), a.x2, x_out, nullptr, N, D, F));
     }
 
     const long long p_final = pidx(g->L, 0);
-    TB_TRY(launch_rmsnorm_fwd(c, g->x_final, P32(g, p_final), g->nf, g->rf, N, D, g->eps, st));
+    TB_TRY(launch_rmsnorm_fwd(c, g->x_final, P32(g, p_final), g->nf, g->rf, N, D, g->eps, st, g->nf32));
     if (g->fused_ce) {
         // logits = nf @ E^T (tied head, gpu_train.c:378) never reach HBM: pass 1 keeps per-tile softmax
         // statistics and the target logit, their combination is the loss; pass 2 forms the product again
@@ -237,12 +252,13 @@ int forward(TbTrainer* g, bool want_grad) {
     }
     {   // logits = nf @ E^T (tied head): gpu_train.c:378
         GemmArgs a;
-        a.kind = GEMM_NT; a.A = g->nf; a.B = P16(g, 0); a.M = N; a.N = V; a.K = D; a.lda = D; a.ldb = D;
+        a.kind = GEMM_NT; a.A = g->tf32 ? (const void*)g->nf32 : (const void*)g->nf; a.B = WOP(g, 0);
+        a.M = N; a.N = V; a.K = D; a.lda = D; a.ldb = D; a.tf32 = g->tf32;
         a.C32 = g->logits; a.ldc32 = g->Vp; a.splits = 1; a.pad_cols_writable = true;
         TB_TRY(gemm(g, a));
     }
-    TB_TRY(launch_cross_entropy(c, g->logits, g->targets, g->loss_rows, want_grad ? g->dlogits : nullptr, N, V, g->Vp,
-                                1.0f / (float)N, st));
+    TB_TRY(launch_cross_entropy(c, g->logits, g->targets, g->loss_rows, (want_grad && !g->tf32) ? g->dlogits : nullptr, N, V,
+                                g->Vp, 1.0f / (float)N, st, (want_grad && g->tf32) ? g->dlogits32 : nullptr));
     return 0;
 }
 
@@ -253,13 +269,16 @@ int backward_head(TbTrainer* g) {
     const long long p_final = pidx(g->L, 0);
     {   // dE += dlogits^T @ nf  (gpu_train.c:403)
         GemmArgs a;
-        a.kind = GEMM_TN; a.A = g->dlogits; a.B = g->nf; a.M = V; a.N = D; a.K = N; a.lda = g->Vp; a.ldb = D;
+        a.kind = GEMM_TN; a.A = g->tf32 ? (const void*)g->dlogits32 : (const void*)g->dlogits;
+        a.B = g->tf32 ? (const void*)g->nf32 : (const void*)g->nf; a.tf32 = g->tf32;
+        a.M = V; a.N = D; a.K = N; a.lda = g->Vp; a.ldb = D;
         a.C32 = G32(g, 0); a.ldc32 = D; a.beta = 1.0f; a.splits = 1;
         TB_TRY(gemm(g, a));
     }
     {   // dnf = dlogits @ E  (gpu_train.c:404)
         GemmArgs a;
-        a.kind = GEMM_NN; a.A = g->dlogits; a.B = P16(g, 0); a.M = N; a.N = D; a.K = V; a.lda = g->Vp; a.ldb = D;
+        a.kind = GEMM_NN; a.A = g->tf32 ? (const void*)g->dlogits32 : (const void*)g->dlogits; a.B = WOP(g, 0);
+        a.tf32 = g->tf32; a.M = N; a.N = D; a.K = V; a.lda = g->Vp; a.ldb = D;
         a.C32 = g->dn; a.ldc32 = D; a.splits = 1;
         TB_TRY(gemm(g, a));
     }
@@ -277,24 +296,31 @@ int backward_layer(TbTrainer* g, int l) {
     const long long Tp = g->Tp, sTT = (long long)T * Tp, sThd = (long long)T * hd;
     LayerActs& a = g->layers[l];
 
+    // the gradient of the residual stream as a GEMM operand: bf16 copy, or the float32 buffer itself (TF32 mode)
+    const void* dres_op = g->tf32 ? (const void*)g->dres : (const void*)g->dres16;
     // ---- FFN: x3 = x2 + (h @ Wd + bd); dres = dx3
-    TB_TRY(linear_dw(g, a.h, g->dres16, G32(g, pidx(l, PK_WDOWN)), N, D, F));
+    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.h32 : (const void*)a.h, dres_op, G32(g, pidx(l, PK_WDOWN)), N, D, F));
     // (b_down's gradient, the column sum of dres, was produced together with dres)
-    TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WDOWN)), g->dh, nullptr, N, D, F));
+    TB_TRY(linear_dx(g, dres_op, WOP(g, pidx(l, PK_WDOWN)), g->dh, nullptr, N, D, F));
     // (fused path: the gate|up bias gradient, the column sums of dgu, comes out of the same kernel)
     if (g->fused_swiglu)
         TB_TRY(launch_swiglu_bwd_colsum(c, a.gu16, g->dh, g->dgu, G32(g, pidx(l, PK_BGU)), g->swiglu_scratch, N, F, st));
-    else TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->dgu, N, F, st));
-    TB_TRY(linear_dw(g, a.n2, g->dgu, G32(g, pidx(l, PK_WGU)), N, 2 * F, D));
-    if (!g->fused_swiglu) TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
-    TB_TRY(linear_dx(g, g->dgu, P16(g, pidx(l, PK_WGU)), g->dn, nullptr, N, 2 * F, D));
+    else TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->tf32 ? nullptr : g->dgu, N, F, st, g->dgu32));
+    const void* dgu_op = g->tf32 ? (const void*)g->dgu32 : (const void*)g->dgu;
+    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.n2_32 : (const void*)a.n2, dgu_op, G32(g, pidx(l, PK_WGU)), N, 2 * F, D));
+    if (!g->fused_swiglu) {
+        if (g->tf32) TB_TRY(launch_colsum_f32(c, g->dgu32, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
+        else TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
+    }
+    TB_TRY(linear_dx(g, dgu_op, WOP(g, pidx(l, PK_WGU)), g->dn, nullptr, N, 2 * F, D));
     TB_TRY(launch_rmsnorm_bwd_dw(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.r2, g->dn, g->dres, g->dres16,
                                  G32(g, pidx(l, PK_FFN_NORM)), G32(g, pidx(l, PK_BO)), g->norm_scratch, N, D, 1, st));
 
     // ---- attention: x2 = x + (att @ Wo + bo); dres = dx2
-    TB_TRY(linear_dw(g, a.att, g->dres16, G32(g, pidx(l, PK_WO)), N, D, D));
+    if (g->tf32) TB_TRY(launch_widen_bf16(c, a.att, g->att32, (long long)N * D, st));
+    TB_TRY(linear_dw(g, g->tf32 ? (const void*)g->att32 : (const void*)a.att, dres_op, G32(g, pidx(l, PK_WO)), N, D, D));
     // (bo's gradient came with dres as well)
-    TB_TRY(linear_dx(g, g->dres16, P16(g, pidx(l, PK_WO)), nullptr, g->datt, N, D, D));
+    TB_TRY(linear_dx(g, dres_op, WOP(g, pidx(l, PK_WO)), nullptr, g->datt, N, D, D));
     if (g->fused_attention) {
         // dQ, dK, dV leave the kernels rotated back and merged as bf16 dqkv [N, 3D]
         TB_TRY(launch_attention_bwd(c, a.Q, a.K, a.V, a.att, g->datt, a.lse, g->att_delta, nullptr, nullptr, nullptr, B,
@@ -332,9 +358,11 @@ int backward_layer(TbTrainer* g, int l) {
     }
     TB_TRY(launch_rope_merge_bwd(c, g->dQ, g->dK, g->dV, g->cos_t, g->sin_t, g->dqkv, B, T, H, hd, st));
     }
-    TB_TRY(linear_dw(g, a.n1, g->dqkv, G32(g, pidx(l, PK_WQKV)), N, 3 * D, D));
+    if (g->tf32) TB_TRY(launch_widen_bf16(c, g->dqkv, g->dqkv32, (long long)N * 3 * D, st));
+    const void* dqkv_op = g->tf32 ? (const void*)g->dqkv32 : (const void*)g->dqkv;
+    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.n1_32 : (const void*)a.n1, dqkv_op, G32(g, pidx(l, PK_WQKV)), N, 3 * D, D));
     TB_TRY(launch_colsum_bf16(c, g->dqkv, G32(g, pidx(l, PK_BQKV)), g->colsum_partial, N, 3 * D, st));
-    TB_TRY(linear_dx(g, g->dqkv, P16(g, pidx(l, PK_WQKV)), g->dn, nullptr, N, 3 * D, D));
+    TB_TRY(linear_dx(g, dqkv_op, WOP(g, pidx(l, PK_WQKV)), g->dn, nullptr, N, 3 * D, D));
     TB_TRY(launch_rmsnorm_bwd_dw(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.r1, g->dn, g->dres, g->dres16,
                                  G32(g, pidx(l, PK_ATTN_NORM)), l > 0 ? G32(g, pidx(l - 1, PK_BDOWN)) : nullptr,
                                  g->norm_scratch, N, D, 1, st));
@@ -480,7 +508,14 @@ int trainer_view(TbTrainer* g, TrainerView* v) {
 extern "C" {
 
 int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T, int B, float eps, void* stream) {
+    return tb_trainer_create_prec(out, V, D, H, L, F, T, B, eps, TB_PREC_BF16, stream);
+}
+
+int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, int T, int B, float eps, int precision,
+                           void* stream) {
     TB_CHECK(out != nullptr, "tb_trainer_create: out is NULL");
+    TB_CHECK(precision == TB_PREC_BF16 || precision == TB_PREC_TF32,
+             "the trainer runs its GEMMs in BF16 or TF32 mode (precision %d is not available: there is no fallback)", precision);
     TB_CHECK(V > 0 && D > 0 && H > 0 && L >= 0 && F > 0 && T > 0 && B > 0, "trainer dims must be positive");
     TB_CHECK(D % H == 0, "d_model %d not divisible by heads %d", D, H);
     TB_CHECK(D % 8 == 0 && F % 8 == 0 && (D / H) % 8 == 0,
@@ -495,10 +530,12 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         TB_CUDA(cudaStreamCreateWithFlags(&g->stream, cudaStreamNonBlocking));
         g->owns_stream = true;
     }
+    g->tf32 = precision == TB_PREC_TF32;
     g->graphs_on = getenv("TB_NO_GRAPH") == nullptr;
     g->fused_attention = (D / H) <= 64 && getenv("TB_NO_FUSED_ATTENTION") == nullptr;
-    g->fused_swiglu = F % 64 == 0 && getenv("TB_NO_FUSED_SWIGLU") == nullptr;
-    g->fused_rope = T % 32 == 0 && (D / H == 32 || D / H == 64) && getenv("TB_NO_FUSED_ROPE") == nullptr;
+    TB_CHECK(!g->tf32 || g->fused_attention, "the TF32 mode needs head_dim <= 64 (the attention core is the fused bf16 kernel)");
+    g->fused_swiglu = !g->tf32 && F % 64 == 0 && getenv("TB_NO_FUSED_SWIGLU") == nullptr;
+    g->fused_rope = !g->tf32 && T % 32 == 0 && (D / H == 32 || D / H == 64) && getenv("TB_NO_FUSED_ROPE") == nullptr;
     g->V = V; g->D = D; g->H = H; g->L = L; g->F = F; g->T = T; g->B = B; g->N = B * T; g->hd = D / H;
     g->Vp = round_up(V, 8);
     g->Tp = round_up(T, 8);
@@ -540,9 +577,17 @@ int tb_trainer_create(TbTrainer** out, int V, int D, int H, int L, int F, int T,
         if (g->fused_swiglu) TB_TRY(dalloc(g, &a.gu16, N * 2 * F));
         else TB_TRY(dalloc(g, &a.gu, N * 2 * F));
         TB_TRY(dalloc(g, &a.h, N * F));
+        if (g->tf32) {
+            TB_TRY(dalloc(g, &a.n1_32, N * D)); TB_TRY(dalloc(g, &a.n2_32, N * D)); TB_TRY(dalloc(g, &a.h32, N * F));
+        }
     }
     TB_TRY(dalloc(g, &g->x_final, N * D)); TB_TRY(dalloc(g, &g->nf, N * D)); TB_TRY(dalloc(g, &g->rf, N));
-    g->fused_ce = getenv("TB_NO_FUSED_CE") == nullptr;
+    g->fused_ce = !g->tf32 && getenv("TB_NO_FUSED_CE") == nullptr;
+    if (g->tf32) {
+        TB_TRY(dalloc(g, &g->nf32, N * D)); TB_TRY(dalloc(g, &g->dlogits32, N * g->Vp));
+        TB_TRY(dalloc(g, &g->dgu32, N * 2 * F)); TB_TRY(dalloc(g, &g->dqkv32, N * 3 * D)); TB_TRY(dalloc(g, &g->att32, N * D));
+        TB_CUDA(cudaMemset(g->dlogits32, 0, N * g->Vp * 4));      // the padding columns stay zero
+    }
     if (g->fused_ce) {
         TB_TRY(dalloc(g, &g->ce_stats, (size_t)2 * ((V + kCeTile - 1) / kCeTile) * N * 2));
         TB_TRY(dalloc(g, &g->ce_zt, N)); TB_TRY(dalloc(g, &g->ce_lse, N));

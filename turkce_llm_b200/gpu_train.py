@@ -25,11 +25,13 @@ def _u32(a):
 
 
 class GpuTrainer:
-    def __init__(self, V, D, H, L, F, T, B, eps=1e-5, device=0, stream=None):
+    def __init__(self, V, D, H, L, F, T, B, eps=1e-5, device=0, stream=None, precision=lib.PREC_BF16):
+        """precision: lib.PREC_BF16 or lib.PREC_TF32, the operand format of the linear-layer GEMMs."""
         self._lib = lib.load()
         lib.init(device)
         h = C.c_void_p()
-        lib.check(self._lib.tb_trainer_create(C.byref(h), V, D, H, L, F, T, B, eps, stream))
+        lib.check(self._lib.tb_trainer_create_prec(C.byref(h), V, D, H, L, F, T, B, eps, precision, stream))
+        self.precision = precision
         self.h = h
         self.cfg = (V, D, H, L, F, T, B, eps)
         self.total = int(self._lib.tb_trainer_total_scalars(self.h))

@@ -55,6 +55,7 @@ SIGNATURES = {
     "tb_decoder_read_logits": (_i, [_vp, _vp]),
     "tb_decoder_stream": (_vp, [_vp]),
     "tb_trainer_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "tb_trainer_create_prec": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "tb_trainer_destroy": (_i, [_vp]),
     "tb_trainer_total_scalars": (_i64, [_vp]),
     "tb_trainer_num_params": (_i, [_vp]),
