@@ -766,30 +766,42 @@ def bench_lmhead(S=64, V=31769, K=384, iters=40, copies=8):
 
 
 def bench_reference_gpu_trainer(steps=8):
-    """The reference's own GPU-resident trainer (model/gpu_train.c unmodified, its cuda/train_kernels.cu compiled
-    for sm_100a; the checker library oracle/_ref/librefgpu.so) on the same GPU and the same step, in a child
-    process: the kernels this library replaces, timed beside it."""
+    """The reference's own GPU-resident trainer (model/gpu_train.c unmodified; the checker library
+    oracle/_ref/librefgpu.so) on the same GPU and the same step, in a child process, twice: with its own 26 kernels
+    compiled for sm_100a (the kernels this library replaces), and with the module in which its GEMM entries are this
+    library's Driver-API cubin kernels (turkce_llm_b200/csrc/cubin/gemm_ref_abi.cu) and everything else is unchanged."""
     from oracle import ref_gpu
     if not ref_gpu.available():
         return {"unavailable": "oracle/_ref/librefgpu.so / train_kernels.cubin are not built on this machine"}
     V, D, H, L, F = (MODEL[k] for k in "VDHLF")
+    out_rec = {}
     with tempfile.TemporaryDirectory() as tmp:
         tok = os.path.join(tmp, "tokens.npy")
         out = os.path.join(tmp, "out.json")
         np.save(tok, zipf_ids(400_000, V, 1))
-        runs = []
-        for n in (2, 2 + steps):        # the difference of two runs leaves out context set-up and the first step
-            r = ref_gpu.run_child(["trajectory", "--cfg", V, D, H, L, F, CONTEXT, BATCH, "--tokens", tok, "--steps", n,
-                                   "--out", out], timeout=600)
-            if r.returncode != 0:
-                return {"error": (r.stderr or r.stdout)[-400:]}
-            runs.append(json.load(open(out)))
-    sec = (runs[1]["seconds"] - runs[0]["seconds"]) / steps
-    return {"ms_per_step": round(sec * 1e3, 2), "tokens_per_s": round(BATCH * CONTEXT / sec),
-            "what": "gpu_trainer_forward_backward + grad_norm + adam_step_scaled of the reference, batch 8 x 1024, "
-                    "its own 26 kernels compiled by nvcc for sm_100a; %d steps (difference of a %d-step and a 2-step run)"
-                    % (steps, 2 + steps),
-            "first_loss": runs[1]["losses"][0]}
+        for key, module in (("own_kernels", ref_gpu.REFGPU_CUBIN), ("with_this_librarys_gemm_cubin", ref_gpu.REFGPU_TB_CUBIN)):
+            if not os.path.exists(module):
+                out_rec[key] = {"unavailable": os.path.basename(module) + " is not built on this machine"}
+                continue
+            runs = []
+            for n in (2, 2 + steps):        # the difference of two runs leaves out context set-up and the first step
+                r = ref_gpu.run_child(["trajectory", "--module", module, "--cfg", V, D, H, L, F, CONTEXT, BATCH, "--tokens", tok,
+                                       "--steps", n, "--out", out], timeout=600)
+                if r.returncode != 0:
+                    runs = None
+                    out_rec[key] = {"error": (r.stderr or r.stdout)[-400:]}
+                    break
+                runs.append(json.load(open(out)))
+            if runs:
+                sec = (runs[1]["seconds"] - runs[0]["seconds"]) / steps
+                out_rec[key] = {"ms_per_step": round(sec * 1e3, 2), "tokens_per_s": round(BATCH * CONTEXT / sec),
+                                "first_loss": runs[1]["losses"][0], "loss_after_%d_steps" % (2 + steps): runs[1]["losses"][-1]}
+    out_rec["what"] = ("gpu_trainer_forward_backward + grad_norm + adam_step_scaled of the reference's unmodified host code, "
+                       "batch 8 x 1024; %d steps (difference of a %d-step and a 2-step run)" % (steps, 2 + steps))
+    if "ms_per_step" in out_rec.get("own_kernels", {}):
+        out_rec["ms_per_step"] = out_rec["own_kernels"]["ms_per_step"]
+        out_rec["tokens_per_s"] = out_rec["own_kernels"]["tokens_per_s"]
+    return out_rec
 
 
 def bench_tf32_step(steps=10):

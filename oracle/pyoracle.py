@@ -54,7 +54,7 @@ def build_ref(ref_root):
 def build_ref_gpu(ref_root):
     """Compile the reference's GPU-resident trainer where it lies into oracle/_ref/librefgpu.so, and its
     cuda/train_kernels.cu into oracle/_ref/train_kernels.cubin (sm_100a); used on a GPU box only."""
-    subprocess.check_call(["make", "-C", HERE, "refgpu", "REF=" + ref_root], stdout=subprocess.DEVNULL,
+    subprocess.check_call(["make", "-C", HERE, "refgpu", "refgpu_tb", "REF=" + ref_root], stdout=subprocess.DEVNULL,
                           stderr=subprocess.DEVNULL)
 
 

@@ -12,6 +12,11 @@ run as a CHILD PROCESS (`python -m oracle.ref_gpu <command> ...`) that touches n
               given token stream; writes losses, gradient norms and seconds per step
   step        one forward+backward from given weights on a given batch; writes loss, norm, gradients
   gemms       times the reference's GEMM kernels alone on the layer shapes of one training step
+  gemm        one GEMM launch of a named kernel of any module image through the reference's loader
+              (cuda_init / cuda_get_kernel / cuda_launch): inputs from an .npz, output to an .npy
+
+--module selects the module image the reference's loader reads (default: the reference's own kernels; the
+drop-in tests pass oracle/_ref/train_kernels_tb_gemm.cubin or turkce_llm_b200/turkce_b200_gemm.cubin).
 """
 import argparse
 import ctypes as C
@@ -25,6 +30,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 REFGPU_SO = os.path.join(HERE, "_ref", "librefgpu.so")
 REFGPU_CUBIN = os.path.join(HERE, "_ref", "train_kernels.cubin")
+# the reference's non-GEMM kernels + this library's GEMM entries under the reference's names, in one module
+REFGPU_TB_CUBIN = os.path.join(HERE, "_ref", "train_kernels_tb_gemm.cubin")
 
 
 def available():
@@ -38,7 +45,7 @@ def _ptr(a, t):
 class RefGpu:
     """gpu_trainer_* of the reference (model/gpu_train.h:86-125) behind oracle/ref_gpu_shim.c."""
 
-    def __init__(self, V, D, H, L, F, T, B, eps=1e-5, seed=1337, seq=1, arena_bytes=None):
+    def __init__(self, V, D, H, L, F, T, B, eps=1e-5, seed=1337, seq=1, arena_bytes=None, module=None):
         self.lib = lib = C.CDLL(REFGPU_SO)
         lib.refgpu_create.restype = C.c_void_p
         lib.refgpu_create.argtypes = [C.c_uint32] * 5 + [C.c_float, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32,
@@ -66,7 +73,7 @@ class RefGpu:
         if arena_bytes is None:
             # values + grads + adam m, v on the host mirror, loss rows, tables, slack
             arena_bytes = 4 * 4 * total + 64 * B * T + (64 << 20)
-        self.h = lib.refgpu_create(V, D, H, L, F, eps, seed, seq, B, T, REFGPU_CUBIN.encode(), arena_bytes)
+        self.h = lib.refgpu_create(V, D, H, L, F, eps, seed, seq, B, T, (module or REFGPU_CUBIN).encode(), arena_bytes)
         self.total = int(lib.refgpu_total_scalars(self.h))
         assert self.total == total
         self.B, self.T = B, T
@@ -112,7 +119,7 @@ class RefGpu:
 
 def cmd_trajectory(a):
     V, D, H, L, F, T, B = a.cfg
-    r = RefGpu(V, D, H, L, F, T, B, a.eps)
+    r = RefGpu(V, D, H, L, F, T, B, a.eps, module=a.module)
     if a.params:
         r.set(0, np.load(a.params))
     tokens = np.load(a.tokens)
@@ -128,7 +135,7 @@ def cmd_step(a):
     """One gpu_trainer_forward_backward from given weights on given ids/targets (an .npz with `ids`, `tgt`);
     writes the loss and gradient norm to --out and the flat gradients to --grads-out (.npy)."""
     V, D, H, L, F, T, B = a.cfg
-    r = RefGpu(V, D, H, L, F, T, B, a.eps)
+    r = RefGpu(V, D, H, L, F, T, B, a.eps, module=a.module)
     r.set(0, np.load(a.params))
     batch = np.load(a.tokens)
     loss = r.forward_backward(batch["ids"], batch["tgt"])
@@ -143,7 +150,7 @@ def cmd_gemms(a):
     """The reference's GEMM kernels alone on the shapes of one training step at B*T = a.tokens."""
     V, D, H, L, F, T, B = a.cfg
     N = B * T
-    r = RefGpu(V, D, H, 1, F, T, B, a.eps)   # one layer: the shapes do not depend on depth
+    r = RefGpu(V, D, H, 1, F, T, B, a.eps, module=a.module)   # one layer: the shapes do not depend on depth
     rows = []
 
     def add(name, sec, M, Nn, K, batch=1):
@@ -174,6 +181,33 @@ def cmd_gemms(a):
         json.dump({"tokens": N, "rows": rows}, f)
 
 
+def cmd_gemm(a):
+    """--tokens: an .npz with entry (str), form, A, B, C, optional bias / residual, and the integers M, N, K, lda,
+    ldb, ldc, sA, sB, sC, gx, gy, gz, bx, by, iters and floats alpha, beta.  Writes the result matrix to --out (.npy)
+    and, next to it, <out>.json with the seconds per launch."""
+    z = np.load(a.tokens, allow_pickle=False)
+    lib = C.CDLL(REFGPU_SO)
+    f32p = C.POINTER(C.c_float)
+    lib.refcuda_gemm.restype = C.c_double
+    lib.refcuda_gemm.argtypes = [C.c_char_p, C.c_char_p, C.c_int, f32p, C.c_uint64, f32p, C.c_uint64, f32p, f32p, f32p,
+                                 C.c_uint64] + [C.c_int32] * 6 + [C.c_int64] * 3 + [C.c_float] * 2 + [C.c_uint32] * 5 + [C.c_int]
+    A = np.ascontiguousarray(z["A"], dtype=np.float32).reshape(-1)
+    B = np.ascontiguousarray(z["B"], dtype=np.float32).reshape(-1)
+    Cm = np.ascontiguousarray(z["C"], dtype=np.float32).reshape(-1).copy()
+    bias = np.ascontiguousarray(z["bias"], dtype=np.float32) if "bias" in z else None
+    res = np.ascontiguousarray(z["residual"], dtype=np.float32).reshape(-1) if "residual" in z else None
+    i = lambda k: int(z[k])
+    sec = lib.refcuda_gemm((a.module or REFGPU_CUBIN).encode(), str(z["entry"]).encode(), i("form"),
+                           _ptr(A, C.c_float), A.size, _ptr(B, C.c_float), B.size,
+                           _ptr(bias, C.c_float) if bias is not None else None,
+                           _ptr(res, C.c_float) if res is not None else None, _ptr(Cm, C.c_float), Cm.size,
+                           i("M"), i("N"), i("K"), i("lda"), i("ldb"), i("ldc"), i("sA"), i("sB"), i("sC"),
+                           float(z["alpha"]), float(z["beta"]), i("gx"), i("gy"), i("gz"), i("bx"), i("by"), i("iters"))
+    np.save(a.out, Cm)
+    with open(a.out + ".json", "w") as f:
+        json.dump({"seconds_per_launch": float(sec)}, f)
+
+
 def run_child(args, timeout=1200):
     """Runs `python -m oracle.ref_gpu <args>` from the repository root; returns the completed process."""
     root = os.path.dirname(HERE)
@@ -183,7 +217,8 @@ def run_child(args, timeout=1200):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("command", choices=["trajectory", "step", "gemms"])
+    ap.add_argument("command", choices=["trajectory", "step", "gemms", "gemm"])
+    ap.add_argument("--module", default=None, help="module image for the reference's loader (default: its own kernels)")
     ap.add_argument("--cfg", type=int, nargs=7, metavar=("V", "D", "H", "L", "F", "T", "B"),
                     default=[31769, 384, 6, 12, 1024, 1024, 8])
     ap.add_argument("--eps", type=float, default=1e-5)
@@ -201,7 +236,7 @@ def main():
     a = ap.parse_args()
     if not available():
         raise SystemExit("oracle/_ref/librefgpu.so or train_kernels.cubin is not built (make -C oracle refgpu)")
-    {"trajectory": cmd_trajectory, "step": cmd_step, "gemms": cmd_gemms}[a.command](a)
+    {"trajectory": cmd_trajectory, "step": cmd_step, "gemms": cmd_gemms, "gemm": cmd_gemm}[a.command](a)
 
 
 if __name__ == "__main__":

@@ -201,3 +201,48 @@ double refgpu_time_gemm(RefGpu* r, int kind, int fp32_kernel, i32 M, i32 N, i32 
     cuda_free(A); cuda_free(B); cuda_free(C);
     return (t1 - t0) / (f64)iters;
 }
+
+/* One GEMM launch through the reference's unmodified loader, with ANY module image: cuda_init (module load with
+ * cuModuleLoadData, cuda/cuda_backend.c:56-107), cuda_get_kernel (:103-107), cuda_alloc / cuda_h2d, cuda_launch
+ * (cuLaunchKernel on the NULL stream with the reference's void** parameter convention, :150-153), cuda_d2h.  The
+ * caller gives the entry name, the host matrices and the launch geometry (the test computes it the way the reference's
+ * static helpers do, model/gpu_train.c:45-118, cuda/cuda_backend.c:141-148).
+ * form 0: the 14-parameter list of k_gemm_* / k_bf16_gemm_* (cuda/train_kernels.cu:187-188);
+ * form 1: k_bf16_gemm_nn_bias(A, B, bias, residual, C, M, N, K) (:226-228), bias / residual may be NULL;
+ * form 2: k_matmul(A, B, C, M, K, N) (cuda/kernels.cu:35).
+ * C holds the initial output (read when beta != 0) and receives the result.  iters > 1 repeats the launch and the
+ * function returns the seconds per launch of the repeated part (timer_now_seconds around cuda_sync), else 0. */
+double refcuda_gemm(const char* module_path, const char* entry, int form,
+                    const float* A, u64 nA, const float* B, u64 nB, const float* bias, const float* residual,
+                    float* C, u64 nC, i32 M, i32 N, i32 K, i32 lda, i32 ldb, i32 ldc,
+                    i64 sA, i64 sB, i64 sC, f32 alpha, f32 beta,
+                    u32 gx, u32 gy, u32 gz, u32 bx, u32 by, int iters) {
+    Allocator alloc = allocator_create(64ull << 20);
+    CudaCtx ctx = cuda_init(&alloc, module_path);
+    CUfunction f = cuda_get_kernel(&ctx, entry);
+    CUdeviceptr dA = cuda_alloc(nA * 4), dB = cuda_alloc(nB * 4), dC = cuda_alloc(nC * 4);
+    CUdeviceptr dbias = 0, dres = 0;
+    cuda_h2d(dA, A, nA * 4); cuda_h2d(dB, B, nB * 4); cuda_h2d(dC, C, nC * 4);
+    if (bias) { dbias = cuda_alloc((u64)N * 4); cuda_h2d(dbias, bias, (u64)N * 4); }
+    if (residual) { dres = cuda_alloc(nC * 4); cuda_h2d(dres, residual, nC * 4); }
+    void* args0[] = { &dA, &dB, &dC, &M, &N, &K, &lda, &ldb, &ldc, &sA, &sB, &sC, &alpha, &beta };
+    void* args1[] = { &dA, &dB, &dbias, &dres, &dC, &M, &N, &K };
+    void* args2[] = { &dA, &dB, &dC, &M, &K, &N };
+    void** args = form == 0 ? args0 : form == 1 ? args1 : args2;
+    cuda_launch(f, gx, gy, gz, bx, by, 1, 0, args);
+    cuda_sync();
+    cuda_d2h(C, dC, nC * 4);
+    double sec = 0.0;
+    if (iters > 1) {
+        f64 t0 = timer_now_seconds();
+        for (int i = 0; i < iters; i++) cuda_launch(f, gx, gy, gz, bx, by, 1, 0, args);
+        cuda_sync();
+        sec = (timer_now_seconds() - t0) / (f64)iters;
+    }
+    cuda_free(dA); cuda_free(dB); cuda_free(dC);
+    if (dbias) cuda_free(dbias);
+    if (dres) cuda_free(dres);
+    cuda_shutdown(&ctx);
+    allocator_destroy(&alloc);
+    return sec;
+}

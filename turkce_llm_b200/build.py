@@ -1,8 +1,10 @@
-"""Builds the sm_100a shared library in-tree with nvcc (no JIT cache, no torch extension).
+"""Builds the sm_100a shared library and the Driver-API cubin in-tree with nvcc (no JIT cache, no torch extension).
 
     python -m turkce_llm_b200.build [--force] [--verbose]
 
-Output: turkce_llm_b200/libturkce_b200.so.  nvcc cross-compiles without a GPU.
+Outputs: turkce_llm_b200/libturkce_b200.so (the C ABI of include/turkce_b200.h) and
+turkce_llm_b200/turkce_b200_gemm.cubin (the GEMM family under the reference's kernel names, for the reference's
+cuModuleLoadData loader).  nvcc cross-compiles without a GPU.
 """
 import os
 import subprocess
@@ -11,6 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libturkce_b200.so")
+CUBIN = os.path.join(HERE, "turkce_b200_gemm.cubin")
+CUBIN_SRC = os.path.join(CSRC, "cubin", "gemm_ref_abi.cu")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC_FLAGS = [
@@ -29,12 +33,25 @@ def _stale():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + \
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if os.path.isfile(os.path.join(CSRC, f))] + \
            [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def build_cubin(force=False, verbose=False):
+    """nvcc -cubin of the reference-ABI GEMM kernels (a module image for cuModuleLoadData)."""
+    deps = [CUBIN_SRC, os.path.join(CSRC, "ptx.cuh")]
+    if not force and os.path.exists(CUBIN) and all(os.path.getmtime(d) <= os.path.getmtime(CUBIN) for d in deps):
+        return CUBIN
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc, "-cubin", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17"] + \
+          (["-Xptxas", "-v"] if verbose else []) + ["-o", CUBIN, CUBIN_SRC]
+    subprocess.check_call(cmd)
+    return CUBIN
+
+
 def build(force=False, verbose=False):
+    build_cubin(force, verbose)
     if not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
