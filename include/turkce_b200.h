@@ -88,7 +88,10 @@ int tb_gemm_bias_f32(const float* d_A, const float* d_B, const float* d_bias, co
 
 /* gpu_matmul() behind node_matmul2d_gpu, and k_matmul (model/gpu_ops.c:118-160;
  * cuda/kernels.cu:35-65): host matrices in, host matrix out, copies included.
- * C[M,N] = A[M,K] @ B[K,N], all contiguous row-major float32 in host memory. */
+ * C[M,N] = A[M,K] @ B[K,N], all contiguous row-major float32 in host memory.
+ * Like the reference's worker slots (model/gpu_ops.c:31-46,78-102) every calling host thread keeps its own three
+ * device buffers per device, grown on demand and reused, so repeated calls allocate nothing; threads may call
+ * concurrently (the product itself is serialised per process: the library's scratch is one per device). */
 int tb_matmul_host(const float* h_A, const float* h_B, float* h_C, int M, int K, int N, int precision);
 
 /* ---- GEMM on bf16 device matrices (native format of this library) ----------- */

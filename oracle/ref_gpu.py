@@ -12,6 +12,7 @@ run as a CHILD PROCESS (`python -m oracle.ref_gpu <command> ...`) that touches n
               given token stream; writes losses, gradient norms and seconds per step
   step        one forward+backward from given weights on a given batch; writes loss, norm, gradients
   gemms       times the reference's GEMM kernels alone on the layer shapes of one training step
+  abi_in_context  the product library's tb_gemm_bias_f32 called inside the reference's own CUDA context
   gemm        one GEMM launch of a named kernel of any module image through the reference's loader
               (cuda_init / cuda_get_kernel / cuda_launch): inputs from an .npz, output to an .npy
 
@@ -208,6 +209,30 @@ def cmd_gemm(a):
         json.dump({"seconds_per_launch": float(sec)}, f)
 
 
+def cmd_abi_in_context(a):
+    """tb_gemm_bias_f32 of the product library called inside the context the reference's cuda_init created, on
+    buffers from the reference's cuda_alloc.  --tokens: an .npz with A, B, bias, residual; --params: path of
+    libturkce_b200.so.  Writes C to --out (.npy) and {"rc", "error"} to <out>.json."""
+    z = np.load(a.tokens)
+    lib = C.CDLL(REFGPU_SO)
+    f32p = C.POINTER(C.c_float)
+    lib.refcuda_call_tb_gemm_bias.restype = C.c_int
+    lib.refcuda_call_tb_gemm_bias.argtypes = [C.c_char_p, C.c_char_p, f32p, f32p, f32p, f32p, f32p, C.c_int32, C.c_int32,
+                                              C.c_int32, C.c_char_p, C.c_int]
+    A, B = (np.ascontiguousarray(z[k], dtype=np.float32) for k in ("A", "B"))
+    bias, res = (np.ascontiguousarray(z[k], dtype=np.float32) for k in ("bias", "residual"))
+    M, K = A.shape
+    N = B.shape[1]
+    out = np.zeros((M, N), dtype=np.float32)
+    err = C.create_string_buffer(1024)
+    rc = lib.refcuda_call_tb_gemm_bias((a.module or REFGPU_CUBIN).encode(), a.params.encode(), _ptr(A, C.c_float),
+                                       _ptr(B, C.c_float), _ptr(bias, C.c_float), _ptr(res, C.c_float), _ptr(out, C.c_float),
+                                       M, N, K, err, len(err))
+    np.save(a.out, out)
+    with open(a.out + ".json", "w") as f:
+        json.dump({"rc": int(rc), "error": err.value.decode("utf-8", "replace")}, f)
+
+
 def run_child(args, timeout=1200):
     """Runs `python -m oracle.ref_gpu <args>` from the repository root; returns the completed process."""
     root = os.path.dirname(HERE)
@@ -217,7 +242,7 @@ def run_child(args, timeout=1200):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("command", choices=["trajectory", "step", "gemms", "gemm"])
+    ap.add_argument("command", choices=["trajectory", "step", "gemms", "gemm", "abi_in_context"])
     ap.add_argument("--module", default=None, help="module image for the reference's loader (default: its own kernels)")
     ap.add_argument("--cfg", type=int, nargs=7, metavar=("V", "D", "H", "L", "F", "T", "B"),
                     default=[31769, 384, 6, 12, 1024, 1024, 8])
@@ -236,7 +261,8 @@ def main():
     a = ap.parse_args()
     if not available():
         raise SystemExit("oracle/_ref/librefgpu.so or train_kernels.cubin is not built (make -C oracle refgpu)")
-    {"trajectory": cmd_trajectory, "step": cmd_step, "gemms": cmd_gemms, "gemm": cmd_gemm}[a.command](a)
+    {"trajectory": cmd_trajectory, "step": cmd_step, "gemms": cmd_gemms, "gemm": cmd_gemm,
+     "abi_in_context": cmd_abi_in_context}[a.command](a)
 
 
 if __name__ == "__main__":

@@ -246,3 +246,39 @@ double refcuda_gemm(const char* module_path, const char* entry, int form,
     allocator_destroy(&alloc);
     return sec;
 }
+
+/* The C-ABI route inside the reference's own context: cuda_init creates a context with cuCtxCreate and makes it
+ * current (cuda/cuda_backend.c:56-107); the product library (libturkce_b200.so, CUDA runtime API) is then loaded and
+ * its float32 entry point tb_gemm_bias_f32 is called on CUdeviceptr values from cuda_alloc -- the call the binding
+ * stub of bf16_gemm_bias makes (model/gpu_train.c:103-107).  Returns the library's return code; tb_last_error's
+ * text is copied to err (cap bytes). */
+#include <dlfcn.h>
+#include <stdio.h>
+int refcuda_call_tb_gemm_bias(const char* module_path, const char* libtb_path, const float* A, const float* B,
+                              const float* bias, const float* residual, float* C, i32 M, i32 N, i32 K, char* err, int cap) {
+    Allocator alloc = allocator_create(64ull << 20);
+    CudaCtx ctx = cuda_init(&alloc, module_path);
+    void* h = dlopen(libtb_path, RTLD_NOW | RTLD_LOCAL);
+    if (!h) { snprintf(err, cap, "dlopen failed: %s", dlerror()); return -100; }
+    typedef int (*GemmBiasFn)(const float*, const float*, const float*, const float*, float*, int, int, int, int, void*);
+    typedef int (*CheckFn)(void*);
+    typedef const char* (*ErrFn)(void);
+    GemmBiasFn gemm_bias = (GemmBiasFn)dlsym(h, "tb_gemm_bias_f32");
+    CheckFn check_fn = (CheckFn)dlsym(h, "tb_check");
+    ErrFn last_error = (ErrFn)dlsym(h, "tb_last_error");
+    if (!gemm_bias || !check_fn || !last_error) { snprintf(err, cap, "symbols missing"); return -101; }
+    CUdeviceptr dA = cuda_alloc((u64)M * K * 4), dB = cuda_alloc((u64)K * N * 4), dC = cuda_alloc((u64)M * N * 4);
+    CUdeviceptr dbias = cuda_alloc((u64)N * 4), dres = cuda_alloc((u64)M * N * 4);
+    cuda_h2d(dA, A, (u64)M * K * 4); cuda_h2d(dB, B, (u64)K * N * 4);
+    cuda_h2d(dbias, bias, (u64)N * 4); cuda_h2d(dres, residual, (u64)M * N * 4);
+    int rc = gemm_bias((const float*)dA, (const float*)dB, (const float*)dbias, (const float*)dres, (float*)dC, M, N, K,
+                       0 /* TB_PREC_BF16 */, NULL);
+    if (rc == 0) rc = check_fn(NULL);
+    if (rc != 0) snprintf(err, cap, "%s", last_error());
+    cuda_sync();
+    if (rc == 0) cuda_d2h(C, dC, (u64)M * N * 4);
+    cuda_free(dA); cuda_free(dB); cuda_free(dC); cuda_free(dbias); cuda_free(dres);
+    cuda_shutdown(&ctx);
+    allocator_destroy(&alloc);
+    return rc;
+}

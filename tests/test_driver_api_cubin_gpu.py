@@ -155,3 +155,24 @@ def test_reference_trainer_runs_on_the_drop_in_gemm_kernels(refgpu, oracle, tmp_
     for i, (o, n) in enumerate(zip(off, sizes)):
         assert compare_tensor_bad(grads[o:o + n], want_grads[o:o + n], 8e-2) == 0, "parameter %d" % i
     assert abs(got["grad_norm"] - oracle.grad_norm(want_grads)) <= 2e-2 * oracle.grad_norm(want_grads)
+
+
+def test_c_abi_works_inside_the_references_own_context(refgpu, oracle, tmp_path):
+    """The other route of the boundary: the C ABI called from the reference's process.  The reference creates a
+    context of its own with cuCtxCreate and keeps it current (cuda/cuda_backend.c:56-107, cuda/cuda_backend.h:36-40);
+    the library (CUDA runtime API) must work in that context on the reference's CUdeviceptr buffers, as the binding
+    of bf16_gemm_bias (model/gpu_train.c:103-107) needs."""
+    rng = np.random.default_rng(9)
+    M, N, K = 300, 200, 384
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    np.savez(tmp_path / "in.npz", A=A, B=B, bias=bias, residual=res)
+    lib_path = os.path.join(ROOT, "turkce_llm_b200", "libturkce_b200.so")
+    r = refgpu.run_child(["abi_in_context", "--tokens", tmp_path / "in.npz", "--params", lib_path, "--out", tmp_path / "c.npy"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    info = json.load(open(str(tmp_path / "c.npy") + ".json"))
+    assert info["rc"] == 0, info
+    got = np.load(tmp_path / "c.npy")
+    assert rel_to_maxabs(got, oracle.gemm_bias(A, B, bias, res, mode=BF16)) <= 2e-5

@@ -356,3 +356,38 @@ def test_gemm_swiglu_epilogue(tb, oracle, shape):
     assert torch.equal(gu16, gu32.to(torch.bfloat16))
     h_ref = (g * (1.0 / (1.0 + torch.exp(-g))) * u)
     assert rel_to_maxabs(h16.float().cpu().numpy(), h_ref.cpu().numpy()) <= 1e-2
+
+
+def test_matmul_host_from_several_threads(tb, oracle):
+    """gpu_matmul is called from many worker threads at once in the reference's data-parallel step
+    (model/gpu_ops.c:78-134): every thread has its own buffers, results are unaffected by the others, and a
+    thread's repeated calls reuse its buffers (shapes shrink and grow)."""
+    import threading
+    rng = np.random.default_rng(77)
+    shapes = [(64, 48, 32), (200, 384, 130), (17, 5, 300), (128, 1024, 384)]
+    cases = []
+    for M, K, N in shapes:
+        A = rng.standard_normal((M, K)).astype(np.float32)
+        B = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+        cases.append((A, B, oracle.gemm(0, 0, A, B, M, N, K, mode=BF16).reshape(M, N)))
+    errors = []
+
+    def worker(order):
+        try:
+            for _ in range(3):
+                for i in order:
+                    A, B, want = cases[i]
+                    M, K = A.shape
+                    N = B.shape[1]
+                    out = np.zeros((M, N), np.float32)
+                    tb.matmul_host(A, B, out, M, K, N)
+                    if rel_to_maxabs(out, want) > TOL_SAME_OPERANDS:
+                        errors.append((i, rel_to_maxabs(out, want)))
+        except Exception as e:          # noqa: BLE001 -- reported by the assertion below
+            errors.append(repr(e))
+    threads = [threading.Thread(target=worker, args=(o,)) for o in ([0, 1, 2, 3], [3, 2, 1, 0], [1, 3, 0, 2], [2, 0, 3, 1])]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors

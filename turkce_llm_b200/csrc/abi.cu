@@ -4,6 +4,7 @@
 
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 
 using namespace tb;
@@ -306,36 +307,61 @@ int tb_gemm_bias_f32(const float* d_A, const float* d_B, const float* d_bias, co
                          precision, S(stream));
 }
 
+// gpu_matmul keeps three growable device buffers per worker slot and reuses them from call to call
+// (model/gpu_ops.c:31-46,118-160); the slot of a call is the calling thread's (gpu_ops_set_worker_id stores it in a
+// thread-local, :100-102).  Here every host thread that calls tb_matmul_host owns one such slot per device: buffers
+// grow on demand and live until the thread ends, so the steady state allocates nothing, and threads never share a
+// slot (no lock on the data path, as the reference's worker slots).
+namespace {
+struct MatmulSlot {
+    int device = -1;
+    float *dA = nullptr, *dB = nullptr, *dC = nullptr;
+    size_t capA = 0, capB = 0, capC = 0;
+    ~MatmulSlot() {
+        if (device < 0) return;
+        int cur = -1;
+        if (cudaGetDevice(&cur) != cudaSuccess) return;      // the runtime is already shutting down
+        cudaSetDevice(device);
+        cudaFree(dA); cudaFree(dB); cudaFree(dC);
+        cudaSetDevice(cur);
+    }
+};
+thread_local MatmulSlot t_slots[8];
+
+int grow(float** p, size_t* cap, size_t need) {
+    if (need <= *cap) return 0;
+    if (*p) TB_CUDA(cudaFree(*p));
+    *p = nullptr; *cap = 0;
+    const size_t want = need + need / 4;
+    TB_CUDA(cudaMalloc(p, want * sizeof(float)));
+    *cap = want;
+    return 0;
+}
+}  // namespace
+
 int tb_matmul_host(const float* h_A, const float* h_B, float* h_C, int M, int K, int N, int precision) {
     DeviceCtx* ctx;
     TB_TRY(get_ctx(&ctx));
     TB_CHECK(M > 0 && N > 0 && K > 0, "matmul dims must be positive");
     const size_t na = (size_t)M * K, nb = (size_t)K * N, nc = (size_t)M * N;
-    float *dA = nullptr, *dB = nullptr, *dC = nullptr;
-    TB_CUDA(cudaMalloc(&dA, na * 4));
-    TB_CUDA(cudaMalloc(&dB, nb * 4));
-    TB_CUDA(cudaMalloc(&dC, nc * 4));
-    int rc = 0;
-    do {
-        if (cudaMemcpy(dA, h_A, na * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
-            cudaMemcpy(dB, h_B, nb * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
-            set_error("tb_matmul_host: host to device copy failed");
-            rc = -1; break;
-        }
-        // pageable copies may still be in flight on the legacy stream when cudaMemcpy returns
-        if (cudaStreamSynchronize(cudaStreamLegacy) != cudaSuccess) { set_error("tb_matmul_host: synchronisation failed"); rc = -1; break; }
-        rc = gemm_f32_impl(TB_GEMM_NN, dA, dB, dC, M, N, K, K, N, N, 1, 0, 0, 0, 1.0f, 0.0f, nullptr, nullptr,
-                           precision, nullptr);
-        if (rc) break;
-        rc = check_device_error(ctx, nullptr);
-        if (rc) break;
-        if (cudaMemcpy(h_C, dC, nc * 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
-            set_error("tb_matmul_host: device to host copy failed");
-            rc = -1;
-        }
-    } while (0);
-    cudaFree(dA); cudaFree(dB); cudaFree(dC);
-    return rc;
+    MatmulSlot* slot = nullptr;
+    for (MatmulSlot& s : t_slots)
+        if (s.device == ctx->device || s.device < 0) { slot = &s; break; }
+    TB_CHECK(slot != nullptr, "tb_matmul_host: this thread already uses 8 devices");
+    slot->device = ctx->device;
+    TB_TRY(grow(&slot->dA, &slot->capA, na));
+    TB_TRY(grow(&slot->dB, &slot->capB, nb));
+    TB_TRY(grow(&slot->dC, &slot->capC, nc));
+    TB_H2D_SYNC(slot->dA, h_A, na * 4);
+    TB_H2D_SYNC(slot->dB, h_B, nb * 4);
+    // the library scratch (operand packing, split-K partials) is one per device: calls of different threads take turns
+    static std::mutex gemm_mutex;
+    std::lock_guard<std::mutex> lock(gemm_mutex);
+    TB_TRY(gemm_f32_impl(TB_GEMM_NN, slot->dA, slot->dB, slot->dC, M, N, K, K, N, N, 1, 0, 0, 0, 1.0f, 0.0f, nullptr,
+                         nullptr, precision, nullptr));
+    TB_TRY(check_device_error(ctx, nullptr));
+    TB_CUDA(cudaMemcpy(h_C, slot->dC, nc * 4, cudaMemcpyDeviceToHost));
+    return 0;
 }
 
 }  // extern "C"
