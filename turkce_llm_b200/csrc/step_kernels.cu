@@ -1351,40 +1351,73 @@ __device__ __forceinline__ float2 load2(const bf16* p) {
     return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
 }
 
-template <typename T>
+// eight adjacent columns of one row (16 bytes of bf16, 32 bytes of float32)
+__device__ __forceinline__ void load8(const float* p, float (&o)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&o)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+        o[2 * k] = f.x; o[2 * k + 1] = f.y;
+    }
+}
+
+// CW columns per thread (8 with 16-byte loads when cols % 8 == 0, else 2): a block owns 32 * CW columns x one
+// chunk of rows; lane ty walks rows r0 + ty, + 8, ... with four loads in flight.
+template <typename T, int CW>
 __global__ void colsum_kernel(const T* __restrict__ in, float* __restrict__ out, float* __restrict__ partial,
                               unsigned int* __restrict__ tickets, int rows, int cols) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ float2 part[8][33];
+    __shared__ float part[8][32 * CW + 1];
     __shared__ int is_last;
     const int tx = threadIdx.x, ty = threadIdx.y;
-    const int c = blockIdx.x * 64 + 2 * tx;          // cols is even (checked by the launcher)
+    const int c = (blockIdx.x * 32 + tx) * CW;        // cols is a multiple of CW (checked by the launcher)
     const int chunk = blockIdx.y;
     const int per = (rows + kColsumChunks - 1) / kColsumChunks;
     const int r0 = chunk * per, r1 = min(rows, r0 + per);
-    float2 s = make_float2(0.0f, 0.0f);
+    float s[CW];
+#pragma unroll
+    for (int e = 0; e < CW; ++e) s[e] = 0.0f;
+    auto fetch = [&](int r, float (&o)[CW]) {
+        if constexpr (CW == 8) {
+            load8(in + (long long)r * cols + c, o);
+        } else {
+            const float2 v = load2(in + (long long)r * cols + c);
+            o[0] = v.x; o[1] = v.y;
+        }
+    };
     if (c < cols) {
         int r = r0 + ty;
         for (; r + 24 < r1; r += 32) {               // four independent loads in flight
-            const float2 a = load2(in + (long long)r * cols + c);
-            const float2 b = load2(in + (long long)(r + 8) * cols + c);
-            const float2 d = load2(in + (long long)(r + 16) * cols + c);
-            const float2 e = load2(in + (long long)(r + 24) * cols + c);
-            s.x += a.x; s.y += a.y; s.x += b.x; s.y += b.y; s.x += d.x; s.y += d.y; s.x += e.x; s.y += e.y;
+            float a[CW], b[CW], d[CW], e4[CW];
+            fetch(r, a); fetch(r + 8, b); fetch(r + 16, d); fetch(r + 24, e4);
+#pragma unroll
+            for (int e = 0; e < CW; ++e) { s[e] += a[e]; s[e] += b[e]; s[e] += d[e]; s[e] += e4[e]; }
         }
         for (; r < r1; r += 8) {
-            const float2 a = load2(in + (long long)r * cols + c);
-            s.x += a.x; s.y += a.y;
+            float a[CW];
+            fetch(r, a);
+#pragma unroll
+            for (int e = 0; e < CW; ++e) s[e] += a[e];
         }
     }
-    part[ty][tx] = s;
-    __syncthreads();
-    if (ty == 0 && c < cols) {
-        float2 t = part[0][tx];
 #pragma unroll
-        for (int k = 1; k < 8; ++k) { t.x += part[k][tx].x; t.y += part[k][tx].y; }
-        *reinterpret_cast<float2*>(&partial[(long long)chunk * cols + c]) = t;
+    for (int e = 0; e < CW; ++e) part[ty][tx * CW + e] = s[e];
+    __syncthreads();
+    // the eight row-lanes of a column are added in lane order by one thread per column
+    for (int j = ty * 32 + tx; j < 32 * CW; j += 256) {
+        const int col = blockIdx.x * 32 * CW + j;
+        if (col < cols) {
+            float t = part[0][j];
+#pragma unroll
+            for (int k = 1; k < 8; ++k) t += part[k][j];
+            partial[(long long)chunk * cols + col] = t;
+        }
     }
     __threadfence();
     __syncthreads();
@@ -1392,27 +1425,18 @@ __global__ void colsum_kernel(const T* __restrict__ in, float* __restrict__ out,
     __syncthreads();
     if (is_last) {
         __threadfence();
-        // lane ty adds chunks 8*ty .. 8*ty+7 in order, then lane 0 adds the eight sub-sums in order
-        float2 t = make_float2(0.0f, 0.0f);
-        if (c < cols) {
-            constexpr int per_lane = kColsumChunks / 8;
-            float2 v[per_lane];
+        // the block that drew the last ticket of this column group adds the chunk partials in chunk order
+        for (int j = ty * 32 + tx; j < 32 * CW; j += 256) {
+            const int col = blockIdx.x * 32 * CW + j;
+            if (col < cols) {
+                float v[kColsumChunks];
 #pragma unroll
-            for (int k = 0; k < per_lane; ++k)
-                v[k] = __ldcg(reinterpret_cast<const float2*>(&partial[(long long)(ty * per_lane + k) * cols + c]));
-            t = v[0];
+                for (int k = 0; k < kColsumChunks; ++k) v[k] = __ldcg(&partial[(long long)k * cols + col]);
+                float t = v[0];
 #pragma unroll
-            for (int k = 1; k < per_lane; ++k) { t.x += v[k].x; t.y += v[k].y; }
-        }
-        __syncthreads();
-        part[ty][tx] = t;
-        __syncthreads();
-        if (ty == 0 && c < cols) {
-            float2 u = part[0][tx];
-#pragma unroll
-            for (int k = 1; k < 8; ++k) { u.x += part[k][tx].x; u.y += part[k][tx].y; }
-            out[c] += u.x;
-            out[c + 1] += u.y;
+                for (int k = 1; k < kColsumChunks; ++k) t += v[k];
+                out[col] += t;
+            }
         }
         if (tx == 0 && ty == 0) tickets[blockIdx.x] = 0u;     // ready for the next launch
     }
@@ -1422,10 +1446,16 @@ template <typename T>
 static int colsum_impl(DeviceCtx* ctx, const T* in, float* out, float* partial, int rows, int cols, cudaStream_t st) {
     TB_CHECK((cols + 63) / 64 <= kTicketWords, "column sum supports at most %d columns", kTicketWords * 64);
     TB_CHECK(cols % 2 == 0, "column sum needs an even number of columns (got %d)", cols);
-    dim3 grid((cols + 63) / 64, kColsumChunks), block(32, 8);
     unsigned int* tickets = reinterpret_cast<unsigned int*>(partial);
     prof_mark(ctx, "colsum", 0.0, 0.0, st);
-    TB_CUDA(launch_kernel((colsum_kernel<T>), dim3(grid), dim3(block), 0, st, in, out, partial + kTicketWords, tickets, rows, cols));
+    const bool wide = cols % 8 == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
+    if (wide) {
+        dim3 grid((cols + 255) / 256, kColsumChunks), block(32, 8);
+        TB_CUDA(launch_kernel((colsum_kernel<T, 8>), dim3(grid), dim3(block), 0, st, in, out, partial + kTicketWords, tickets, rows, cols));
+    } else {
+        dim3 grid((cols + 63) / 64, kColsumChunks), block(32, 8);
+        TB_CUDA(launch_kernel((colsum_kernel<T, 2>), dim3(grid), dim3(block), 0, st, in, out, partial + kTicketWords, tickets, rows, cols));
+    }
     TB_LAUNCHED(ctx);
     return 0;
 }
