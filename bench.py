@@ -692,7 +692,7 @@ def bench_c3():
             "timing": "device time per call inside a CUDA graph, 4 operand sets in rotation (252 MB > L2)"}
 
 
-def bench_c4():
+def bench_c4(S=64, prompt_len=128, n_new=128, with_lm_head=True):
     """Batched greedy decoding with a KV cache: 64 sequences, 128-token Zipf(1.1) prompts, 128 new tokens;
     random bf16 weights (seed 3).  HBM roofline: the step streams all weights once (66.9 MB) and the cache up to
     the current length (1.18 MB per position over all layers and sequences)."""
@@ -700,7 +700,6 @@ def bench_c4():
     from turkce_llm_b200 import lib
     from turkce_llm_b200.decode import Decoder
     V, D, H, L, F = (MODEL[k] for k in "VDHLF")
-    S, prompt_len, n_new = 64, 128, 128
     pk = peaks()
     dec = Decoder(V, D, H, L, F, S, prompt_len + n_new + 1)
     rng = np.random.default_rng(3)
@@ -729,13 +728,15 @@ def bench_c4():
     mean_len = prompt_len + (n_new - 1) / 2.0 + 1
     kv_bytes = S * L * 2 * mean_len * D * 2.0
     gbs = (weight_bytes + kv_bytes) / step_us / 1e3
-    rec = {"workload": "64 sequences, 128-token Zipf(1.1) prompts, 128 greedy tokens, cache length 128..256; bf16 weights, seed 3",
+    rec = {"workload": "%d sequences, %d-token Zipf(1.1) prompts, %d greedy tokens, cache length %d..%d; bf16 weights, seed 3"
+                       % (S, prompt_len, n_new, prompt_len, prompt_len + n_new),
            "prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(S * prompt_len / pre_ms * 1e3),
            "decode_us_per_step": round(step_us, 1), "decode_tokens_per_s": round(S / step_us * 1e6),
            "algorithmic_mb_per_step": {"weights": round(weight_bytes / 1e6, 1), "kv_cache_mean": round(kv_bytes / 1e6, 1)},
            "achieved_gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / pk["hbm"], 4),
            "launches_per_token": round(launches / n_new, 1), "first_tokens": toks[0, :4].tolist()}
-    rec["lm_head"] = bench_lmhead()
+    if with_lm_head:
+        rec["lm_head"] = bench_lmhead()
     return rec
 
 
@@ -1010,7 +1011,8 @@ def run_only(args):
         print("attention B=%d H=%d T=%d hd=%d: fwd %.1f us (%.1f TFLOP/s causal-useful)  bwd %.1f us (%.1f TFLOP/s)"
               % (B, H, T, hd, f_us, 2 * tri / f_us / 1e6, b_us, 5 * tri / b_us / 1e6), flush=True)
     elif args.only == "decode":
-        print(json.dumps(bench_c4()), flush=True)
+        nums = [int(x) for x in a[:3]]
+        print(json.dumps(bench_c4(*nums, with_lm_head=False)), flush=True)
     elif args.only == "lmhead":
         print(json.dumps(bench_lmhead(*(int(x) for x in a[:5]))), flush=True)
     return 0
