@@ -75,7 +75,9 @@ def main():
         pyoracle.build_ref(sys.argv[1])
         train_loop_fixtures(pyoracle.Ref())
         return
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <reference checkout> [train_loop]")
+    ref_root = sys.argv[1]
     pyoracle.build_ref(ref_root)
     ref = pyoracle.Ref()
 
