@@ -160,6 +160,18 @@ int tb_gemm_swiglu_bf16(const void* d_X, const void* d_W, const float* d_bias, i
 int tb_gemm_qkv_rope_bf16(const void* d_X, const void* d_W, const float* d_bias, const float* d_cos, const float* d_sin,
                           int B, int T, int H, int hd, void* d_QKV, void* stream);
 
+/* One linear layer of a decode step for S <= 64 sequences (the reference has no decode path: its generator re-runs
+ * lm_forward per token, training/generate.c:186-212; the products are the layer's projections, model/attention.c:26,67
+ * and model/feedforward.c:9-16, with model_ops.c's RMSNorm in front of the QKV and gate|up projections):
+ *   Y[S, N] = X[S, K] . W[K, N] + bias[N] (+ residual[S, N])             d_y32 float32
+ *   or, with d_h16 given (N = 2F): H[S, F] = silu(g + b_g) * (u + b_u)    d_h16 bf16, [g | u] = X W
+ * X is either bf16 (d_X16) or float32 rows (d_x32) that the kernel normalises itself: X = x * rsqrt(mean x^2 + eps) * w.
+ * W bf16 row-major; K a multiple of 64 up to 1024; N a multiple of 128 (F a multiple of 64).  A weight-streaming
+ * kernel: the slab of W a CTA needs is requested before the previous kernel of the stream has finished. */
+int tb_decode_linear(const void* d_X16, const float* d_x32, const float* d_norm_w, float eps, const void* d_W,
+                     const float* d_bias, const float* d_residual, float* d_y32, void* d_h16, int S, int N, int K,
+                     void* stream);
+
 /* Decode-time LM head with the greedy choice fused: d_tok[s] = argmax_v <X[s,:], E[v,:]> (lowest index
  * on ties) for 1 <= S <= 64 rows of X [S, K] bf16 against the tied embedding table E [V, K] bf16, K a
  * multiple of 64.  The [S, V] logits (lm_forward's last rows, model/lm_model.c:72-81, whose argmax

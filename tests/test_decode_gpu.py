@@ -28,8 +28,11 @@ def make_params(oracle, cfg, seed):
     return p
 
 
-@pytest.mark.parametrize("dims", [(97, 32, 2, 2, 48, 3, 5, 6), (300, 64, 2, 2, 128, 4, 140, 20)])
+@pytest.mark.parametrize("dims", [(97, 32, 2, 2, 48, 3, 5, 6), (300, 64, 2, 2, 128, 4, 140, 20),
+                                  (300, 128, 2, 2, 256, 5, 20, 12), (500, 256, 4, 3, 1024, 64, 9, 5)])
 def test_cached_decode_matches_full_recompute(tb, oracle, dims):
+    """(The last two shapes are also those the optional decode-step linear kernel supports, see
+    test_lean_decode_step_matches_general_step.)"""
     from turkce_llm_b200.decode import Decoder
     V, D, H, L, F, S, prompt_len, n_new = dims
     cap = prompt_len + n_new + 2
@@ -266,3 +269,70 @@ def test_sampling_limits_and_reproducibility(tb, oracle):
     assert np.array_equal(a, b) and not np.array_equal(a, c) and not np.array_equal(a, greedy)
     assert np.array_equal(run(0.0, 1), greedy)
     dec.destroy()
+
+
+@pytest.mark.parametrize("mode", ["norm_qkv", "out_residual", "norm_swiglu", "down_residual"])
+def test_decode_linear_entry_matches_oracle(tb, oracle, mode):
+    """tb_decode_linear -- the decode step's own linear kernel with the RMSNorm, the SwiGLU and the residual add fused
+    (model/model_ops.c's rmsnorm, model/feedforward.c:9-14, model/transformer_block.c:7-15) -- against the oracle's
+    separate steps on bf16-rounded operands, at the layer shapes of the 33.49M model and a ragged sequence count."""
+    import torch
+    from oracle.pyoracle import BF16
+    rng = np.random.default_rng(21)
+    D, F = 384, 1024
+    for S in (64, 37):
+        if mode == "norm_qkv":
+            K, N = D, 3 * D
+        elif mode == "out_residual":
+            K, N = D, D
+        elif mode == "norm_swiglu":
+            K, N = D, 2 * F
+        else:
+            K, N = F, D
+        x = rng.standard_normal((S, K)).astype(np.float32)
+        W = oracle.round((rng.standard_normal((K, N)) * 0.05).astype(np.float32), BF16)
+        bias = rng.standard_normal(N).astype(np.float32)
+        res = rng.standard_normal((S, N)).astype(np.float32)
+        w16 = torch.from_numpy(W).cuda().to(torch.bfloat16)
+        if mode.startswith("norm"):
+            nw = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+            xn, _ = oracle.rmsnorm_fwd(x, nw, 1e-5)
+            want = oracle.gemm_bias(oracle.round(xn, BF16), W, bias, None)
+            x_in = dict(x32=torch.from_numpy(x).cuda(), norm_w=torch.from_numpy(nw).cuda())
+        else:
+            xb = oracle.round(x, BF16)
+            want = oracle.gemm_bias(xb, W, bias, res)
+            x_in = dict(x16=torch.from_numpy(xb).cuda().to(torch.bfloat16), residual=torch.from_numpy(res).cuda())
+        if mode == "norm_swiglu":
+            h = torch.full((S, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+            tb.decode_linear(w16, S, N, K, bias=torch.from_numpy(bias).cuda(), h16=h, **x_in)
+            tb.sync_check()
+            got = h.float().cpu().numpy()
+            want = oracle.swiglu_fwd(want)
+            assert rel_to_maxabs(got, want) <= 6e-3, (mode, S)          # one bf16 rounding of the output
+        else:
+            y = torch.full((S, N), float("nan"), device="cuda")
+            tb.decode_linear(w16, S, N, K, bias=torch.from_numpy(bias).cuda(), y32=y, **x_in)
+            tb.sync_check()
+            # a normalised value that sits on a bf16 rounding boundary may round the other way than the oracle's
+            assert rel_to_maxabs(y.cpu().numpy(), want) <= (2e-3 if mode.startswith("norm") else 2e-5), (mode, S)
+
+
+def test_lean_decode_step_matches_general_step(tb, oracle, monkeypatch):
+    """TB_DECODE_LEAN=1 routes the decode step through tb_decode_linear's kernel: same tokens as the default step
+    wherever the logits' top-2 margin is clear, logits within the BF16-mode bound of each other."""
+    from turkce_llm_b200.decode import Decoder
+    V, D, H, L, F, S, prompt_len, n_new = 500, 256, 4, 3, 1024, 64, 9, 6
+    p = make_params(oracle, (V, D, H, L, F, 1, 1, 1e-5), 5)
+    prompts = np.random.default_rng(6).integers(0, V, (S, prompt_len)).astype(np.uint32)
+    outs = []
+    for lean in (False, True):
+        if lean:
+            monkeypatch.setenv("TB_DECODE_LEAN", "1")
+        dec = Decoder(V, D, H, L, F, S, prompt_len + n_new + 2)
+        dec.upload(p)
+        dec.prefill(prompts)
+        dec.generate(1)
+        outs.append(dec.logits())
+        dec.destroy()
+    assert rel_to_maxabs(outs[1], outs[0]) <= 2e-2

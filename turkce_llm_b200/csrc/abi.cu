@@ -150,6 +150,19 @@ int tb_gemm_qkv_rope_bf16(const void* d_X, const void* d_W, const float* d_bias,
     return launch_gemm_bf16(ctx, a, S(stream));
 }
 
+int tb_decode_linear(const void* d_X16, const float* d_x32, const float* d_norm_w, float eps, const void* d_W,
+                     const float* d_bias, const float* d_residual, float* d_y32, void* d_h16, int S, int N, int K,
+                     void* stream) {
+    DeviceCtx* ctx;
+    TB_TRY(get_ctx(&ctx));
+    TB_CHECK(d_W != nullptr, "tb_decode_linear: NULL weight matrix");
+    TB_CHECK(decode_linear_supported(S, N, K, d_h16 != nullptr),
+             "tb_decode_linear: needs 1 <= S <= 64, K a multiple of 64 up to 1024, N a multiple of 128 (d_ff a multiple of 64 "
+             "with the SwiGLU output); got S=%d N=%d K=%d -- use tb_gemm_bf16 for other shapes", S, N, K);
+    return launch_decode_linear(ctx, static_cast<const bf16*>(d_X16), d_x32, d_norm_w, eps, static_cast<const bf16*>(d_W),
+                                d_bias, d_residual, d_y32, static_cast<bf16*>(d_h16), S, N, K, static_cast<cudaStream_t>(stream));
+}
+
 int tb_lmhead_argmax_bf16(const void* d_X, const void* d_E, int n_seqs, int V, int K, uint32_t* d_tok, float* d_logits,
                           int64_t ld_logits, int table_is_stable, void* stream) {
     DeviceCtx* ctx;

@@ -189,6 +189,14 @@ int launch_lmhead_argmax(DeviceCtx* ctx, const bf16* X, const bf16* E, int S, in
                          unsigned long long* best, unsigned int* ticket, uint32_t* tok, uint32_t* out, int* state,
                          int out_ld, int advance_pos, float* logits, long long ld_logits, cudaStream_t st);
 
+// Linear layer of a decode step for S <= 64 rows (decode_linear.cu): y32 [S, N] = X W + bias (+ residual), or with
+// h16 given (N = 2F) h16 [S, F] = silu(gate) * up.  X is bf16 [S, K], or x32 float32 [S, K] with the RMSNorm
+// (norm_w, eps) fused in front.  W bf16 [K, N] row-major.  N % 128 == 0 (F % 64 == 0), K % 64 == 0, K <= 1024.
+bool decode_linear_supported(int S, int N, int K, bool swiglu);
+int launch_decode_linear(DeviceCtx* ctx, const bf16* X16, const float* x32, const float* norm_w, float eps, const bf16* W,
+                         const float* bias, const float* residual, float* y32, bf16* h16, int S, int N, int K,
+                         cudaStream_t st);
+
 int launch_pack_bf16(DeviceCtx* ctx, const float* src, bf16* dst, int rows, int cols, long long ld_src,
                      long long ld_dst, int batch, long long stride_src, long long stride_dst, cudaStream_t stream);
 

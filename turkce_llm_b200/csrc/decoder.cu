@@ -44,6 +44,7 @@ struct TbDecoder {
     bf16 *n = nullptr, *att = nullptr, *h = nullptr, *Q = nullptr;
     uint32_t *ids = nullptr, *tok = nullptr, *out = nullptr;
     int* pos = nullptr;
+    bool lean_step = false;                    // decode step on decode_linear_kernel (norm / SwiGLU / residual fused)
     bool fused_head = false;                   // LM head with the greedy choice fused (no logits in HBM)
     unsigned long long* head_best = nullptr;   // packed per-sequence maxima of the fused head (zero between launches)
     unsigned int* head_ticket = nullptr;
@@ -135,6 +136,21 @@ int decode_step_body(TbDecoder* g) {
     const bool split_rope = getenv("TB_DECODE_SPLIT_ROPE") != nullptr;    // the two-kernel form, for comparison
     TB_TRY(launch_embed_fwd(c, P32(g, 0), g->tok, g->x, S, D, st));
     for (int l = 0; l < g->L; ++l) {
+        if (g->lean_step) {
+            // five launches per layer: [RMSNorm + QKV] [rotary + cache append + attention] [out-projection + residual]
+            // [RMSNorm + gate|up + SwiGLU] [down + residual]
+            TB_TRY(launch_decode_linear(c, nullptr, g->x, P32(g, pidx(l, PK_ATTN_NORM)), g->eps, P16(g, pidx(l, PK_WQKV)),
+                                        P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, nullptr, S, 3 * D, D, st));
+            TB_TRY(launch_rope_attn_decode(c, g->qkv, g->cos_t, g->sin_t, g->Kc[l], g->Vc[l], g->att, g->pos, S, H, hd,
+                                           g->cap, g->scale, st));
+            TB_TRY(launch_decode_linear(c, g->att, nullptr, nullptr, 0.f, P16(g, pidx(l, PK_WO)), P32(g, pidx(l, PK_BO)),
+                                        g->x, g->x2, nullptr, S, D, D, st));
+            TB_TRY(launch_decode_linear(c, nullptr, g->x2, P32(g, pidx(l, PK_FFN_NORM)), g->eps, P16(g, pidx(l, PK_WGU)),
+                                        P32(g, pidx(l, PK_BGU)), nullptr, nullptr, g->h, S, 2 * g->F, D, st));
+            TB_TRY(launch_decode_linear(c, g->h, nullptr, nullptr, 0.f, P16(g, pidx(l, PK_WDOWN)), P32(g, pidx(l, PK_BDOWN)),
+                                        g->x2, g->x, nullptr, S, D, g->F, st));
+            continue;
+        }
         TB_TRY(launch_rmsnorm_fwd(c, g->x, P32(g, pidx(l, PK_ATTN_NORM)), g->n, g->r, S, D, g->eps, st));
         TB_TRY(linear(g, g->n, P16(g, pidx(l, PK_WQKV)), P32(g, pidx(l, PK_BQKV)), nullptr, g->qkv, S, 3 * D, D));
         if (split_rope) {
@@ -186,6 +202,13 @@ int tb_decoder_create(TbDecoder** out, int V, int D, int H, int L, int F, int ma
     TB_TRY(dalloc(g, &g->gu, N * 2 * F)); TB_TRY(dalloc(g, &g->r, N)); TB_TRY(dalloc(g, &g->xl, S * D));
     TB_TRY(dalloc(g, &g->logits, S * g->Vp)); TB_TRY(dalloc(g, &g->qdec, S * D));
     g->fused_head = getenv("TB_NO_FUSED_LMHEAD") == nullptr && lmhead_argmax_supported(g->ctx, (int)S, V, D);
+    // TB_DECODE_LEAN=1: the decode step on decode_linear_kernel (RMSNorm, SwiGLU and residual fused: 63 launches per
+    // token instead of 87).  Off by default: it measures slower (640-700 against 572 us per step of 64 sequences); a
+    // CTA that streams a whole 128-column slab by itself gets only 10-25 B/clk out of HBM, and the per-CTA RMSNorm
+    // prologue (3 us on 8 warps) sits on the critical path.
+    g->lean_step = getenv("TB_DECODE_LEAN") != nullptr && getenv("TB_DECODE_SPLIT_ROPE") == nullptr &&
+                   decode_linear_supported((int)S, 3 * D, D, false) && decode_linear_supported((int)S, D, D, false) &&
+                   decode_linear_supported((int)S, 2 * F, D, true) && decode_linear_supported((int)S, D, F, false) && D % 4 == 0;
     if (g->fused_head) {
         TB_TRY(dalloc(g, &g->head_best, 64)); TB_CUDA(cudaMemset(g->head_best, 0, 64 * sizeof(unsigned long long)));
         TB_TRY(dalloc(g, &g->head_ticket, 1)); TB_CUDA(cudaMemset(g->head_ticket, 0, sizeof(unsigned int)));

@@ -5,6 +5,8 @@
 // reductions instead of one 256-thread block per row with shared-memory trees.
 #include "step_kernels.h"
 
+#include <cstdlib>
+
 namespace tb {
 
 static inline int grid_for(long long work, int block, const DeviceCtx* ctx, int per_sm = 16) {

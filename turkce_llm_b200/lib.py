@@ -43,6 +43,7 @@ SIGNATURES = {
     "tb_pack_bf16": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i, _i64, _i64, _vp]),
     "tb_gemm_swiglu_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "tb_gemm_qkv_rope_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "tb_decode_linear": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "tb_lmhead_argmax_bf16": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i64, _i, _vp]),
     "tb_decoder_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "tb_decoder_destroy": (_i, [_vp]),
@@ -223,6 +224,12 @@ def gemm_qkv_rope_bf16(x16, w16, bias, cos_t, sin_t, B, T, H, hd, qkv16):
     """qkv16 [3, B, H, T, hd] bf16 = head-split, rotated (q, k) projection x16[B*T, D] @ w16[D, 3D] + bias."""
     check(load().tb_gemm_qkv_rope_bf16(_ptr(x16), _ptr(w16), _ptr(bias), _ptr(cos_t), _ptr(sin_t), B, T, H, hd,
                                        _ptr(qkv16), _stream()))
+
+
+def decode_linear(w16, S, N, K, x16=None, x32=None, norm_w=None, eps=1e-5, bias=None, residual=None, y32=None, h16=None):
+    """One decode-step linear layer (see tb_decode_linear): bf16 or float32-to-normalise input, float32 or SwiGLU output."""
+    check(load().tb_decode_linear(_ptr(x16), _ptr(x32), _ptr(norm_w), eps, _ptr(w16), _ptr(bias), _ptr(residual), _ptr(y32),
+                                  _ptr(h16), S, N, K, _stream()))
 
 
 def lmhead_argmax_bf16(x16, e16, tok, logits=None, ld_logits=0, table_is_stable=False):
