@@ -329,11 +329,15 @@ int tb_trainer_run(TbTrainer* g, const uint32_t* tokens, uint64_t num_tokens, ui
 typedef struct TbDp TbDp;
 #define TB_DP_ALLREDUCE 0   /* one all-reduce of the flat gradient buffer (the loss rides in a spare slot) */
 #define TB_DP_SHARDED   1   /* reduce-scatter, Adam on this rank's 1/ranks slice, all-gather of the weights */
+#define TB_DP_OVERLAP   2   /* the all-reduce in per-layer buckets on a side stream, under the rest of the backward pass */
 /* Rank 0 calls this and hands the 128 bytes to every rank (through whatever channel launched them). */
 int tb_dp_unique_id(void* id_out_128_bytes);
 /* Collective over the ranks (creates the NCCL communicator); unique_id may be NULL when world == 1. */
 int tb_dp_create(TbDp** out, TbTrainer* g, const void* unique_id, int rank, int world, int mode);
 int tb_dp_destroy(TbDp* dp);
+/* Host arithmetic of TB_DP_SHARDED: the slice [first, first + count) of the flat buffers that `rank` owns, and the
+ * chunk (scalars per rank in the reduce-scatter / all-gather, a multiple of 8).  The slices tile [0, total). */
+int tb_dp_slice(int64_t total, int world, int rank, int64_t* chunk, int64_t* first, int64_t* count);
 int tb_dp_info(const TbDp* dp, int* rank, int* world, int* mode, int* nccl_version);
 /* One optimiser step: data_parallel_step + the clipped Adam step of the training loop
  * (training/train_lm.c:184-194, training/train_lm_gpu.c:212-223).  h_ids / h_targets hold this rank's

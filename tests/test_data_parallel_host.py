@@ -176,3 +176,30 @@ def test_accumulated_micro_batches_over_two_ranks_give_the_global_mean(tmp_path)
         want += np.random.default_rng(8 * seq).standard_normal(total).astype(np.float32)
     assert np.allclose(got[:-1], want / 8, rtol=0, atol=2e-6)
     assert abs(got[-1] - np.mean(np.arange(8))) < 1e-6
+
+
+def test_sharded_optimiser_slices_tile_the_flat_buffer():
+    """tb_dp_slice (host arithmetic of the sharded mode, no GPU involved): the ranks' slices tile [0, total) in rank
+    order, every slice starts on a multiple of 8 scalars, and world * chunk stays inside the padded flat buffers
+    (1024 spare scalars behind the last parameter)."""
+    import ctypes as C
+    from turkce_llm_b200 import lib
+    L = lib.load()
+    for total in (33490176, 1000, 7, 8, 123457):
+        for world in (1, 2, 3, 4, 8, 16):
+            pos = 0
+            chunks = set()
+            for rank in range(world):
+                chunk, first, count = C.c_int64(), C.c_int64(), C.c_int64()
+                assert L.tb_dp_slice(total, world, rank, C.byref(chunk), C.byref(first), C.byref(count)) == 0
+                chunks.add(chunk.value)
+                assert first.value % 8 == 0 and chunk.value % 8 == 0
+                assert first.value == rank * chunk.value
+                if count.value:
+                    assert first.value == pos
+                    pos += count.value
+                assert count.value <= chunk.value
+            assert pos == total
+            assert len(chunks) == 1
+            assert world * chunks.pop() <= total + 1024
+    assert L.tb_dp_slice(100, 4, 4, None, None, None) != 0          # rank out of range

@@ -16,6 +16,10 @@
 //                    only, adds up its share of the squared norm, one two-scalar all-reduce (float64) combines the
 //                    norm and the loss, the rank runs Adam on its slice, and ncclAllGather returns the updated
 //                    float32 weights of all slices; the bf16 shadow weights are re-formed locally.
+//   TB_DP_OVERLAP    the all-reduce in per-layer buckets on a side stream while the layers below are still in backward
+//                    (a layer's ten tensors are contiguous in the flat buffer and final once its backward has run;
+//                    the final norm and the loss slot go first, the tied embedding, which receives gradient from the
+//                    LM head first and from the token lookup last, goes last); the optimiser waits for the last bucket.
 // Kernels of this library never touch another GPU's memory: all exchange is NCCL's.
 //
 // NCCL is looked up at run time (dlopen of libnccl.so.2, the copy the host process already has loaded if any),
@@ -33,6 +37,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 using namespace tb;
 
@@ -165,6 +170,9 @@ struct TbDp {
     int rank = 0, world = 1, mode = TB_DP_ALLREDUCE;
     ncclComm_t comm = nullptr;
     long long chunk = 0, lo = 0, own = 0;   // sharded mode: slice [lo, lo + own) of the flat buffers
+    cudaStream_t side = nullptr;            // overlap mode: the stream the bucket all-reduces run on
+    cudaEvent_t ev_ready = nullptr, ev_done = nullptr;
+    std::vector<long long> bucket_lo, bucket_hi;      // [0] final norm (+ loss slot), [1 + i] layer L-1-i, [L + 1] embedding
     double* d_pair = nullptr;               // {sum of squares, loss} for the two-scalar all-reduce
     double* h_pair = nullptr;               // pinned
     float* h_loss = nullptr;                // pinned
@@ -172,10 +180,33 @@ struct TbDp {
 
 namespace {
 
-int backward_all(TbDp* dp) {
+// overlap mode: bucket b is final on the trainer's stream now; reduce it on the side stream
+int reduce_bucket(TbDp* dp, size_t b) {
+    const TrainerView& v = dp->v;
+    TB_CUDA(cudaEventRecord(dp->ev_ready, v.stream));
+    TB_CUDA(cudaStreamWaitEvent(dp->side, dp->ev_ready, 0));
+    float* p = v.grads + dp->bucket_lo[b];
+    TB_NCCL(g_nccl.AllReduce(p, p, (size_t)(dp->bucket_hi[b] - dp->bucket_lo[b]), ncclFloat32, ncclSum, dp->comm, dp->side));
+    return 0;
+}
+
+// The backward pass of one batch.  reduce: this is the step's last micro-batch and the mode is TB_DP_OVERLAP.
+int backward_all(TbDp* dp, bool reduce = false) {
+    size_t b = 0;
     TB_TRY(tb_trainer_backward_head(dp->g));
-    for (int l = dp->v.L - 1; l >= 0; --l) TB_TRY(tb_trainer_backward_layer(dp->g, l));
-    return tb_trainer_backward_embed(dp->g);
+    if (reduce) TB_TRY(reduce_bucket(dp, b++));
+    for (int l = dp->v.L - 1; l >= 0; --l) {
+        TB_TRY(tb_trainer_backward_layer(dp->g, l));
+        if (reduce) TB_TRY(reduce_bucket(dp, b++));
+    }
+    TB_TRY(tb_trainer_backward_embed(dp->g));
+    if (reduce) {
+        TB_TRY(reduce_bucket(dp, b++));
+        // the optimiser (on the trainer's stream) waits for the last bucket
+        TB_CUDA(cudaEventRecord(dp->ev_done, dp->side));
+        TB_CUDA(cudaStreamWaitEvent(dp->v.stream, dp->ev_done, 0));
+    }
+    return 0;
 }
 
 int mean_loss_to_slot(TbDp* dp, int accumulate) {
@@ -195,8 +226,8 @@ int mean_loss_to_slot(TbDp* dp, int accumulate) {
 int combine_and_update(TbDp* dp, uint64_t t, float lr, float b1, float b2, float eps, float max_norm, int parts) {
     const TrainerView& v = dp->v;
     const float scale = 1.0f / ((float)dp->world * (float)parts);
-    if (dp->world == 1 || dp->mode == TB_DP_ALLREDUCE) {
-        if (dp->world > 1)      // gradients and the loss slot behind them in one collective
+    if (dp->world == 1 || dp->mode == TB_DP_ALLREDUCE || dp->mode == TB_DP_OVERLAP) {
+        if (dp->world > 1 && dp->mode == TB_DP_ALLREDUCE)      // gradients and the loss slot behind them in one collective
             TB_NCCL(g_nccl.AllReduce(v.grads, v.grads, (size_t)v.total + 1, ncclFloat32, ncclSum, dp->comm, v.stream));
         TB_TRY(tb_trainer_clip_adam_async(dp->g, t, lr, b1, b2, eps, max_norm, scale));
         TB_CUDA(cudaMemcpyAsync(dp->h_loss, v.grads + v.total, sizeof(float), cudaMemcpyDeviceToHost, v.stream));
@@ -254,10 +285,24 @@ int tb_dp_unique_id(void* id_out_128_bytes) {
     return 0;
 }
 
+int tb_dp_slice(int64_t total, int world, int rank, int64_t* chunk, int64_t* first, int64_t* count) {
+    TB_CHECK(total > 0 && world >= 1 && rank >= 0 && rank < world, "tb_dp_slice: rank %d of %d over %lld scalars", rank, world,
+             (long long)total);
+    // equal chunks of a multiple of 8 scalars (16-byte boundaries in float32 and in bf16); the last ranks' chunks may
+    // reach past the last parameter into the padding of the flat buffers, and own fewer (or no) parameters
+    const int64_t c = round_up((total + world - 1) / world, 8);
+    const int64_t lo = c * rank;
+    const int64_t hi = lo + c < total ? lo + c : total;
+    if (chunk) *chunk = c;
+    if (first) *first = lo;
+    if (count) *count = hi > lo ? hi - lo : 0;
+    return 0;
+}
+
 int tb_dp_create(TbDp** out, TbTrainer* g, const void* unique_id, int rank, int world, int mode) {
     TB_CHECK(out != nullptr && g != nullptr, "tb_dp_create: NULL argument");
     TB_CHECK(world >= 1 && rank >= 0 && rank < world, "tb_dp_create: rank %d of %d", rank, world);
-    TB_CHECK(mode == TB_DP_ALLREDUCE || mode == TB_DP_SHARDED, "tb_dp_create: unknown mode %d", mode);
+    TB_CHECK(mode == TB_DP_ALLREDUCE || mode == TB_DP_SHARDED || mode == TB_DP_OVERLAP, "tb_dp_create: unknown mode %d", mode);
     TbDp* dp = new TbDp();
     dp->g = g; dp->rank = rank; dp->world = world; dp->mode = mode;
     TB_TRY(trainer_view(g, &dp->v));
@@ -266,13 +311,26 @@ int tb_dp_create(TbDp** out, TbTrainer* g, const void* unique_id, int rank, int 
     TB_CUDA(cudaMallocHost(&dp->h_pair, 2 * sizeof(double)));
     TB_CUDA(cudaMalloc(&dp->d_pair, 2 * sizeof(double)));
     *dp->h_loss = 0.0f; dp->h_pair[0] = dp->h_pair[1] = 0.0;
-    // slices of the sharded mode: equal chunks of a multiple of 8 scalars (16-byte boundaries in float32 and bf16)
-    dp->chunk = round_up((dp->v.total + world - 1) / world, 8);
+    int64_t chunk = 0, lo = 0, own = 0;
+    TB_TRY(tb_dp_slice(dp->v.total, world, rank, &chunk, &lo, &own));
+    dp->chunk = chunk; dp->lo = lo; dp->own = own;
     TB_CHECK(dp->chunk * world <= dp->v.padded, "tb_dp_create: %d ranks need %lld scalars, the flat buffers hold %lld",
              world, dp->chunk * world, dp->v.padded);
-    dp->lo = dp->chunk * rank;
-    const long long hi = dp->lo + dp->chunk < dp->v.total ? dp->lo + dp->chunk : dp->v.total;
-    dp->own = hi > dp->lo ? hi - dp->lo : 0;
+    if (world > 1 && mode == TB_DP_OVERLAP) {
+        TB_CUDA(cudaStreamCreateWithFlags(&dp->side, cudaStreamNonBlocking));
+        TB_CUDA(cudaEventCreateWithFlags(&dp->ev_ready, cudaEventDisableTiming));
+        TB_CUDA(cudaEventCreateWithFlags(&dp->ev_done, cudaEventDisableTiming));
+        const int np = tb_trainer_num_params(g);
+        std::vector<int64_t> off(np), num(np);
+        TB_TRY(tb_trainer_param_layout(g, off.data(), num.data()));
+        const int L = dp->v.L;
+        dp->bucket_lo.push_back(off[np - 1]); dp->bucket_hi.push_back(dp->v.total + 1);      // final norm + the loss slot
+        for (int l = L - 1; l >= 0; --l) {
+            dp->bucket_lo.push_back(off[1 + 10 * l]);
+            dp->bucket_hi.push_back(l + 1 < L ? off[1 + 10 * (l + 1)] : off[np - 1]);
+        }
+        dp->bucket_lo.push_back(0); dp->bucket_hi.push_back(np > 1 ? off[1] : dp->v.total);
+    }
     if (world > 1) {
         TB_CHECK(unique_id != nullptr, "tb_dp_create: %d ranks need the 128-byte id from tb_dp_unique_id", world);
         TB_TRY(load_nccl());
@@ -288,7 +346,11 @@ int tb_dp_destroy(TbDp* dp) {
     if (!dp) return 0;
     cudaSetDevice(dp->v.device);
     cudaStreamSynchronize(dp->v.stream);
+    if (dp->side) cudaStreamSynchronize(dp->side);
     if (dp->comm) g_nccl.CommDestroy(dp->comm);
+    if (dp->side) cudaStreamDestroy(dp->side);
+    if (dp->ev_ready) cudaEventDestroy(dp->ev_ready);
+    if (dp->ev_done) cudaEventDestroy(dp->ev_done);
     cudaFreeHost(dp->h_loss); cudaFreeHost(dp->h_pair); cudaFree(dp->d_pair);
     delete dp;
     return 0;
@@ -314,10 +376,11 @@ int tb_dp_step(TbDp* dp, const uint32_t* h_ids, const uint32_t* h_targets, int m
     TB_CUDA(cudaSetDevice(v.device));
     const size_t n = (size_t)v.B * v.T;
     TB_TRY(tb_trainer_zero_grads(dp->g));          // also clears the loss slot
+    const bool overlap = dp->world > 1 && dp->mode == TB_DP_OVERLAP;
     for (int i = 0; i < micro_batches; ++i) {
         TB_TRY(tb_trainer_forward(dp->g, h_ids + i * n, h_targets + i * n, 1));
-        TB_TRY(backward_all(dp));
-        TB_TRY(mean_loss_to_slot(dp, 1));
+        TB_TRY(mean_loss_to_slot(dp, 1));          // the loss rows are final after the forward pass
+        TB_TRY(backward_all(dp, overlap && i + 1 == micro_batches));
     }
     TB_TRY(combine_and_update(dp, t, lr, beta1, beta2, eps, max_norm, micro_batches));
     return finish(dp, micro_batches, loss_out, norm_out);
@@ -328,8 +391,8 @@ int tb_dp_step_resident(TbDp* dp, uint64_t t, float lr, float beta1, float beta2
     TB_CUDA(cudaSetDevice(dp->v.device));
     TB_TRY(tb_trainer_zero_grads(dp->g));
     TB_TRY(tb_trainer_forward_resident(dp->g, 1));
-    TB_TRY(backward_all(dp));
     TB_TRY(mean_loss_to_slot(dp, 1));
+    TB_TRY(backward_all(dp, dp->world > 1 && dp->mode == TB_DP_OVERLAP));
     return combine_and_update(dp, t, lr, beta1, beta2, eps, max_norm, 1);
 }
 

@@ -187,7 +187,7 @@ class DataParallelStep:
             return loss, g.last_norm()
 
 
-ALLREDUCE, SHARDED = 0, 1
+ALLREDUCE, SHARDED, OVERLAP = 0, 1, 2
 
 
 class DataParallel:
@@ -200,7 +200,7 @@ class DataParallel:
         self.g = trainer
         self._lib = lib.load()
         if mode is None:
-            mode = SHARDED if os.environ.get("TB_DP_MODE", "allreduce") == "sharded" else ALLREDUCE
+            mode = {"sharded": SHARDED, "overlap": OVERLAP}.get(os.environ.get("TB_DP_MODE", "allreduce"), ALLREDUCE)
         uid = None
         if world > 1:
             buf = (C.c_ubyte * 128)()
@@ -230,6 +230,7 @@ class DataParallel:
         lib.check(self._lib.tb_dp_info(self.h, C.byref(r), C.byref(w), C.byref(m), C.byref(v)))
         how = "one rank: no collective" if w.value == 1 else (
             "reduce-scatter + Adam on the rank's slice + all-gather of the float32 weights" if m.value == SHARDED
+            else "all-reduce in per-layer buckets on a side stream under the backward pass" if m.value == OVERLAP
             else "one all-reduce of the flat float32 gradient buffer after the backward pass")
         return {"entry": "tb_dp_step (C, NCCL called by the library)", "combine": how, "nccl_version": v.value}
 

@@ -92,6 +92,7 @@ SIGNATURES = {
     "tb_dp_unique_id": (_i, [_vp]),
     "tb_dp_create": (_i, [C.POINTER(_vp), _vp, _vp, _i, _i, _i]),
     "tb_dp_destroy": (_i, [_vp]),
+    "tb_dp_slice": (_i, [_i64, _i, _i, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
     "tb_dp_info": (_i, [_vp] + [C.POINTER(_i)] * 4),
     "tb_dp_step": (_i, [_vp, _vp, _vp, _i, C.c_uint64, _f, _f, _f, _f, _f, C.POINTER(_f), C.POINTER(C.c_double)]),
     "tb_dp_step_resident": (_i, [_vp, C.c_uint64, _f, _f, _f, _f, _f]),
