@@ -48,6 +48,18 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Two float32 results per issue slot (fma.rn.f32x2 and friends, sm_100): the softmax warps of these kernels are
+// bound by instruction issue (about 2,000 cycles per 128 x 128 block for 64 scores per thread), not by a unit.
+__device__ __forceinline__ float2 pair_of(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+
+#ifdef TB_ATT_DEBUG
+__device__ long long g_att_dbg[2][1024][16];
+__device__ long long g_att_e[4];
+#define DBG_CLK() clock64()
+#else
+#define DBG_CLK() 0ll
+#endif
+
 // 32 consecutive values of row r -> bf16 in a [128 x 128] operand stored as two [128 x 64] tiles
 __device__ __forceinline__ void store_chunk_bf16(uint8_t* tiles, int r, int c, const float (&x)[32]) {
     uint8_t* row = tiles + (c >> 1) * TILE_BYTES + r * 128;
@@ -81,7 +93,8 @@ struct AttFwdParams {
 // i, the tensor core computes the scores of i+1 and P V of i-1.  Two CTAs fit per SM on top of that.
 __global__ void __launch_bounds__(192, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const AttFwdParams p) {
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                     const AttFwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -102,6 +115,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint64_t* p_full = bars + 11;     // 2: probability buffer b written
     uint64_t* o_full = bars + 13;     // 2: P V of a half block landed in output buffer b
     uint64_t* o_free = bars + 15;     // 2
+    uint64_t* out_full = bars + 18;   // 4 arrivals: the output tile is staged in shared memory
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -120,6 +134,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); mbar_init(&p_full[i], 4);
             mbar_init(&o_full[i], 1); mbar_init(&o_free[i], 4);
         }
+        mbar_init(out_full, 4);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -211,10 +226,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             tmem_ld32(tO + lane_base + (uint32_t)(b * 64), va);
             tmem_ld32(tO + lane_base + (uint32_t)(b * 64 + 32), vb);
             tmem_ld_wait();
+            const float2 al2 = make_float2(alpha, alpha);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                O[e] = O[e] * alpha + __uint_as_float(va[e]);
-                O[32 + e] = O[32 + e] * alpha + __uint_as_float(vb[e]);
+            for (int e = 0; e < 32; e += 2) {
+                const float2 o0 = __ffma2_rn(make_float2(O[e], O[e + 1]), al2, pair_of(va[e], va[e + 1]));
+                const float2 o1 = __ffma2_rn(make_float2(O[32 + e], O[33 + e]), al2, pair_of(vb[e], vb[e + 1]));
+                O[e] = o0.x; O[e + 1] = o0.y; O[32 + e] = o1.x; O[33 + e] = o1.y;
             }
             tc_fence_before();
             __syncwarp();
@@ -249,23 +266,22 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             l *= alpha;
             // p = 2^(s*c - m), row sum, bf16 P into shared memory (K-major, 128B swizzle)
             float pa[32], pb[32];
-            if (diag) {
+            const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_new, -m_new);
+            float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    pa[e] = e <= lim ? fast_exp2(__uint_as_float(va[e]) * p.scale_log2 - m_new) : 0.0f;
-                    pb[e] = e + 32 <= lim ? fast_exp2(__uint_as_float(vb[e]) * p.scale_log2 - m_new) : 0.0f;
+            for (int e = 0; e < 32; e += 2) {
+                const float2 xa = __ffma2_rn(pair_of(va[e], va[e + 1]), c2, nm2);
+                const float2 xb = __ffma2_rn(pair_of(vb[e], vb[e + 1]), c2, nm2);
+                pa[e] = fast_exp2(xa.x); pa[e + 1] = fast_exp2(xa.y);
+                pb[e] = fast_exp2(xb.x); pb[e + 1] = fast_exp2(xb.y);
+                if (diag) {
+                    pa[e] = e <= lim ? pa[e] : 0.0f;           pa[e + 1] = e + 1 <= lim ? pa[e + 1] : 0.0f;
+                    pb[e] = e + 32 <= lim ? pb[e] : 0.0f;      pb[e + 1] = e + 33 <= lim ? pb[e + 1] : 0.0f;
                 }
-            } else {
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    pa[e] = fast_exp2(__uint_as_float(va[e]) * p.scale_log2 - m_new);
-                    pb[e] = fast_exp2(__uint_as_float(vb[e]) * p.scale_log2 - m_new);
-                }
+                la = __fadd2_rn(la, make_float2(pa[e], pa[e + 1]));
+                lb = __fadd2_rn(lb, make_float2(pb[e], pb[e + 1]));
             }
-            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-            for (int e = 0; e < 32; e += 2) { l0 += pa[e]; l1 += pa[e + 1]; l2 += pb[e]; l3 += pb[e + 1]; }
-            l += (l0 + l1) + (l2 + l3);
+            l += (la.x + la.y) + (lb.x + lb.y);
             store_chunk_bf16(sP, r, 2 * b, pa);
             store_chunk_bf16(sP, r, 2 * b + 1, pb);
             tc_fence_before();
@@ -278,23 +294,37 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             m = m_new;
         }
         if (ok) ok = accumulate(nsub - 1, alpha_prev);
-        if (ok && qi < p.T) {
+        if (ok) {
+            // O / l as bf16 into the Q tile (every product has completed), one TMA store for the 128 rows: a thread per
+            // row storing to global memory directly touches 32 different rows per instruction
             const float inv = 1.0f / l;
             const int b = bh / p.H, h = bh % p.H;
-            bf16* orow = p.att + ((long long)b * p.T + qi) * p.D + h * p.hd;
+            if (qi < p.T) {
+                uint8_t* row = sQ + r * 128;
 #pragma unroll
-            for (int d = 0; d < ATT_HD; d += 8) {
-                if (d >= p.hd) break;
-                uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(O[d + 0] * inv, O[d + 1] * inv);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(O[d + 2] * inv, O[d + 3] * inv);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(O[d + 4] * inv, O[d + 5] * inv);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(O[d + 6] * inv, O[d + 7] * inv);
-                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(orow + d) = pk;
+                for (int d = 0; d < ATT_HD; d += 8) {
+                    if (d >= p.hd) break;
+                    uint4 pk;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(O[d + 0] * inv, O[d + 1] * inv);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(O[d + 2] * inv, O[d + 3] * inv);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(O[d + 4] * inv, O[d + 5] * inv);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(O[d + 6] * inv, O[d + 7] * inv);
+                    pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                    pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                    *reinterpret_cast<uint4*>(row + (((d >> 3) ^ (r & 7)) << 4)) = pk;
+                }
+                if (p.lse) p.lse[(long long)bh * p.T + qi] = (m + log2f(l)) * 0.6931471805599453f;
             }
-            if (p.lse) p.lse[(long long)bh * p.T + qi] = (m + log2f(l)) * 0.6931471805599453f;
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(out_full);
+            if (q == 0 && lane == 0) {
+                if (mbar_wait(out_full, 0, abort_flag)) {
+                    tma_store_4d(&tmO, sQ, 0, q0, h, b);          // rows past T are clipped
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                } else ok = false;
+            }
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 13); }
     }
@@ -359,19 +389,39 @@ struct AttBwdParams {
     int* err;
 };
 
-// 32 consecutive head-dim values of one row -> bf16 at dst, optionally through the inverse rotation of the
-// interleaved pairs (2k, 2k+1): out = (a*c + b*s, -a*s + b*c).  d0 = first head-dim index of the 32.
-__device__ __forceinline__ void store_row_bf16(bf16* dst, const uint32_t (&v)[32], int d0, int hd, const float* cs,
-                                               const float* sn) {
+// The rotation tables of one row for 32 consecutive head-dim values (16 pairs) starting at d0: fetched before the
+// wait for the accumulators, in one batch (loads placed between the stores of a row would each wait for the
+// store before them, since the compiler cannot tell the tables from the output).
+struct RopeRow { float4 c[4], s[4]; };
+__device__ __forceinline__ void load_rope_row(RopeRow& t, const float* cs, const float* sn, int d0, int hd) {
 #pragma unroll
-    for (int e = 0; e < 32; e += 8) {
+    for (int g = 0; g < 4; ++g) {
+        if (d0 + 8 * g < hd) {
+            t.c[g] = *reinterpret_cast<const float4*>(cs + ((d0 + 8 * g) >> 1));
+            t.s[g] = *reinterpret_cast<const float4*>(sn + ((d0 + 8 * g) >> 1));
+        } else {
+            t.c[g] = make_float4(1.f, 1.f, 1.f, 1.f);
+            t.s[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+}
+
+// 32 consecutive head-dim values of one row (first index d0), times mul, optionally through the inverse rotation of
+// the interleaved pairs (2k, 2k+1): out = (a*c + b*s, -a*s + b*c), as bf16 into row r of a [128 x 64] tile in shared
+// memory (128-byte rows, 128B swizzle), from where one TMA store writes the whole tile: a thread per row storing to global memory directly touches 32 different
+// rows per instruction (one 16-byte piece each), which took ~4,500 cycles per CTA.
+__device__ __forceinline__ void stage_row_bf16(uint8_t* tile, int r, const uint32_t (&v)[32], int d0, int hd,
+                                               const RopeRow* rot, float mul) {
+    uint8_t* row = tile + r * 128;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int e = 8 * g;
         if (d0 + e >= hd) break;
         float o[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(v[e + j]);
-        if (cs != nullptr) {
-            const float4 c4 = *reinterpret_cast<const float4*>(cs + ((d0 + e) >> 1));
-            const float4 s4 = *reinterpret_cast<const float4*>(sn + ((d0 + e) >> 1));
+        for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(v[e + j]) * mul;
+        if (rot != nullptr) {
+            const float4 c4 = rot->c[g], s4 = rot->s[g];
             const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -385,10 +435,44 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, const uint32_t (&v)[32
         __nv_bfloat162 h2 = __floats2bfloat162_rn(o[4], o[5]), h3 = __floats2bfloat162_rn(o[6], o[7]);
         pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
         pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(dst + e) = pk;
+        const int chunk = (d0 >> 3) + g;
+        *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) = pk;
     }
 }
 
+// 32 float32 values times mul into row r of a [128 x 32] float32 tile (128-byte rows, 128B swizzle) for a TMA store
+__device__ __forceinline__ void stage_row_f32(uint8_t* tile, int r, const uint32_t (&v)[32], float mul) {
+    uint8_t* row = tile + r * 128;
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+        *reinterpret_cast<float4*>(row + ((g ^ (r & 7)) << 4)) =
+            make_float4(__uint_as_float(v[4 * g]) * mul, __uint_as_float(v[4 * g + 1]) * mul,
+                        __uint_as_float(v[4 * g + 2]) * mul, __uint_as_float(v[4 * g + 3]) * mul);
+}
+
+// P = 2^(s*c - lse) and dS' = P * (dP - delta) of 32 scores of one row, two per instruction.  The factor 1/sqrt(hd)
+// of dS is applied to the accumulated dQ and dK instead (they are linear in dS).  lim: columns e <= lim are allowed.
+__device__ __forceinline__ void p_and_ds(const uint32_t (&sv)[32], const uint32_t (&dv)[32], float scale_log2, float lse2,
+                                         float dl, bool diag, int lim, float (&P)[32], float (&dS)[32]) {
+    const float2 c2 = make_float2(scale_log2, scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dl, -dl);
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+        const float2 x = __ffma2_rn(pair_of(sv[e], sv[e + 1]), c2, nl2);
+        float p0 = fast_exp2(x.x), p1 = fast_exp2(x.y);
+        if (diag) { p0 = e <= lim ? p0 : 0.0f; p1 = e + 1 <= lim ? p1 : 0.0f; }
+        const float2 d = __fmul2_rn(make_float2(p0, p1), __fadd2_rn(pair_of(dv[e], dv[e + 1]), nd2));
+        P[e] = p0; P[e + 1] = p1;
+        dS[e] = d.x; dS[e + 1] = d.y;
+    }
+}
+
+// Stages of the operand pair that changes per step (Q, dO in the dK/dV kernel; K, V in the dQ kernel).  With two, the
+// load of step i+1 can only start when step i-1 has been consumed, and its latency plus the score products (~1,700
+// cycles) exceed one step of the compute warps: they waited ~500 cycles per step.  With three it starts a step earlier.
+#ifndef ATT_BWD_STAGES
+#define ATT_BWD_STAGES 3
+#endif
+static_assert(ATT_BWD_STAGES >= 2 && ATT_BWD_STAGES <= 4, "barrier slots are laid out for up to four stages");
 constexpr int ATT_BWD_THREADS = 352;     // TMA warp, score-MMA warp, 8 compute warps, gradient-MMA warp
 // (two issuing threads on different schedulers: one thread cannot issue a block's 24 UMMAs as fast as the
 //  tensor pipe retires them while eight compute warps compete for the same issue slots)
@@ -397,26 +481,29 @@ constexpr int ATT_BWD_THREADS = 352;     // TMA warp, score-MMA warp, 8 compute 
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                          const __grid_constant__ CUtensorMap tmoK, const __grid_constant__ CUtensorMap tmoV,
                           const AttBwdParams p) {
+    const long long dbg_t0 = DBG_CLK();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     uint8_t* sK = smem;
     uint8_t* sV = smem + TILE_BYTES;
-    uint8_t* sQ = smem + 2 * TILE_BYTES;      // 2 stages
-    uint8_t* sdO = smem + 4 * TILE_BYTES;     // 2 stages
-    uint8_t* sP = smem + 6 * TILE_BYTES;      // [128 q, 128 keys] as two tiles
-    uint8_t* sdS = smem + 8 * TILE_BYTES;     // same
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 10 * TILE_BYTES);
+    uint8_t* sQ = smem + 2 * TILE_BYTES;                              // ATT_BWD_STAGES stages
+    uint8_t* sdO = smem + (2 + ATT_BWD_STAGES) * TILE_BYTES;          // ATT_BWD_STAGES stages
+    uint8_t* sP = smem + (2 + 2 * ATT_BWD_STAGES) * TILE_BYTES;       // [128 q, 128 keys] as two tiles
+    uint8_t* sdS = smem + (4 + 2 * ATT_BWD_STAGES) * TILE_BYTES;      // same
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (6 + 2 * ATT_BWD_STAGES) * TILE_BYTES);
     uint64_t* kv_full = bars;          // 1
-    uint64_t* qdo_full = bars + 1;     // 2
-    uint64_t* qdo_empty = bars + 3;    // 2
-    uint64_t* sdp_full = bars + 5;
-    uint64_t* sdp_free = bars + 6;     // 8 arrivals
-    uint64_t* pds_full = bars + 7;     // 8 arrivals
-    uint64_t* pds_free = bars + 8;
-    uint64_t* acc_full = bars + 9;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* qdo_full = bars + 1;     // ATT_BWD_STAGES
+    uint64_t* qdo_empty = bars + 5;    // ATT_BWD_STAGES
+    uint64_t* sdp_full = bars + 9;
+    uint64_t* sdp_free = bars + 10;    // 8 arrivals
+    uint64_t* pds_full = bars + 11;    // 8 arrivals
+    uint64_t* pds_free = bars + 12;
+    uint64_t* acc_full = bars + 13;
+    uint64_t* out_full = bars + 14;    // 8 arrivals: the output tile is staged in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -428,9 +515,9 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+        for (int i = 0; i < ATT_BWD_STAGES; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
         mbar_init(sdp_full, 1); mbar_init(sdp_free, 8); mbar_init(pds_full, 8); mbar_init(pds_free, 1);
-        mbar_init(acc_full, 1);
+        mbar_init(acc_full, 1); mbar_init(out_full, 8);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -449,8 +536,8 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             tma_load_3d(sK, &tmK, kv_full, 0, k0, bh);
             tma_load_3d(sV, &tmV, kv_full, 0, k0, bh);
             for (int it = 0; it < niter && ok; ++it) {
-                const int s = it & 1;
-                if (!mbar_wait(&qdo_empty[s], (uint32_t)((it >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                const int s = it % ATT_BWD_STAGES;
+                if (!mbar_wait(&qdo_empty[s], (uint32_t)((it / ATT_BWD_STAGES) & 1) ^ 1u, abort_flag)) { ok = false; break; }
                 const int q0 = (kb + it) * ATT_BM;
                 mbar_expect_tx(&qdo_full[s], 2 * TILE_BYTES);
                 tma_load_3d(sQ + s * TILE_BYTES, &tmQ, &qdo_full[s], 0, q0, bh);
@@ -468,9 +555,9 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             // S = Q K^T and dP = dO V^T of query block `it`; may run ahead of the accumulation of it-1
             // because the compute warps free the two score tiles as soon as they hold them in registers
             auto issue_sdp = [&](int it) -> bool {
-                const int s = it & 1;
+                const int s = it % ATT_BWD_STAGES;
                 const uint64_t dQk = dQk0 + (uint64_t)s * TILESTEP, ddOk = ddOk0 + (uint64_t)s * TILESTEP;
-                if (!mbar_wait(&qdo_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) return false;
+                if (!mbar_wait(&qdo_full[s], (uint32_t)((it / ATT_BWD_STAGES) & 1), abort_flag)) return false;
                 if (!mbar_wait(sdp_free, (uint32_t)(it & 1) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
@@ -492,9 +579,9 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             const uint64_t dQm0 = mnmajor_tile(smem_u32(sQ), TILE_BYTES), ddOm0 = mnmajor_tile(smem_u32(sdO), TILE_BYTES);
             bool ok = true;
             for (int it = 0; it < niter && ok; ++it) {
-                const int s = it & 1;
+                const int s = it % ATT_BWD_STAGES;
                 const uint64_t dQm = dQm0 + (uint64_t)s * TILESTEP, ddOm = ddOm0 + (uint64_t)s * TILESTEP;
-                if (!mbar_wait(&qdo_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&qdo_full[s], (uint32_t)((it / ATT_BWD_STAGES) & 1), abort_flag)) { ok = false; break; }
                 if (!mbar_wait(pds_full, (uint32_t)(it & 1), abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
@@ -517,6 +604,7 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         const int r = q * 32 + lane;                  // query row inside the block
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         bool ok = true;
+        long long dbg[16] = {0}; dbg[1] = DBG_CLK() - dbg_t0;
         // the row's log-sum-exp and delta of the NEXT query block are fetched while this one is worked on
         float lse_next = INFINITY, dl_next = 0.0f;
         {
@@ -534,8 +622,10 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 lse_next = p.lse[(long long)bh * p.T + qi + ATT_BM] * 1.4426950408889634f;
                 dl_next = p.delta[(long long)bh * p.T + qi + ATT_BM];
             }
+            const long long c_a = DBG_CLK();
             if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
             tc_fence_after();
+            const long long c_b = DBG_CLK();
             // this thread's 64 scores and 64 dP values in one TMEM round trip, then the tiles are free
             uint32_t sv0[32], sv1[32], dv0[32], dv1[32];
             tmem_ld32(tS + lane_base + (half * 2) * 32, sv0);
@@ -543,73 +633,97 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             tmem_ld32(tdP + lane_base + (half * 2) * 32, dv0);
             tmem_ld32(tdP + lane_base + (half * 2 + 1) * 32, dv1);
             tmem_ld_wait();
+            const long long c_c = DBG_CLK();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(sdp_free);
             // rows past T get lse2 = +inf, i.e. P = 0; the diagonal block masks keys after the query
             float P[32], dS[32];
-            {
-                const int lim = diag ? qi - (k0 + (half * 2) * 32) : 32;
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float pe = fast_exp2(__uint_as_float(sv0[e]) * p.scale_log2 - lse2);
-                    if (diag) pe = e <= lim ? pe : 0.0f;
-                    P[e] = pe;
-                    dS[e] = pe * (__uint_as_float(dv0[e]) - dl) * p.scale;
-                }
-            }
-            if (!mbar_wait(pds_free, pi ^ 1u, abort_flag)) { ok = false; break; }     // previous P, dS consumed
+            p_and_ds(sv0, dv0, p.scale_log2, lse2, dl, diag, diag ? qi - (k0 + (half * 2) * 32) : 32, P, dS);
+            const long long c_d = DBG_CLK();
+            if (!mbar_wait(pds_free, pi ^ 1u, abort_flag)) { ok = false; break; }
+            const long long c_e = DBG_CLK();     // previous P, dS consumed
             store_chunk_bf16(sP, r, half * 2, P);
             store_chunk_bf16(sdS, r, half * 2, dS);
-            {
-                const int lim = diag ? qi - (k0 + (half * 2 + 1) * 32) : 32;
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float pe = fast_exp2(__uint_as_float(sv1[e]) * p.scale_log2 - lse2);
-                    if (diag) pe = e <= lim ? pe : 0.0f;
-                    P[e] = pe;
-                    dS[e] = pe * (__uint_as_float(dv1[e]) - dl) * p.scale;
-                }
-            }
+            p_and_ds(sv1, dv1, p.scale_log2, lse2, dl, diag, diag ? qi - (k0 + (half * 2 + 1) * 32) : 32, P, dS);
             store_chunk_bf16(sP, r, half * 2 + 1, P);
             store_chunk_bf16(sdS, r, half * 2 + 1, dS);
+            const long long c_f = DBG_CLK();
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(pds_full);
+            const long long c_g = DBG_CLK();
+            dbg[2] += c_b - c_a; dbg[3] += c_c - c_b; dbg[4] += c_d - c_c; dbg[5] += c_e - c_d; dbg[6] += c_f - c_e; dbg[7] += c_g - c_f;
         }
+        const long long c_h = DBG_CLK();
+        const int kj = k0 + r;                        // key row of the accumulators
+        RopeRow rot;                                  // fetched while the last products finish
+        if (ok && kj < p.T && p.dqkv != nullptr)
+            load_rope_row(rot, p.cos_t + (long long)kj * (p.hd >> 1), p.sin_t + (long long)kj * (p.hd >> 1), half * 32, p.hd);
         if (ok) {
             if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
         }
+        const long long c_i = DBG_CLK();
         if (ok) {
             tc_fence_after();
-            const int kj = k0 + r;                    // key row of the accumulators
             uint32_t v[32], w[32];
             tmem_ld32(tdV + lane_base + half * 32, v);
             tmem_ld32(tdK + lane_base + half * 32, w);
             tmem_ld_wait();
-            if (kj < p.T && p.dqkv != nullptr) {
-                const int D = p.H * p.hd;
-                bf16* row = p.dqkv + ((long long)b * p.T + kj) * 3 * D + h * p.hd + half * 32;
-                const int hh = p.hd >> 1;
-                store_row_bf16(row + D, w, half * 32, p.hd, p.cos_t + (long long)kj * hh, p.sin_t + (long long)kj * hh);
-                store_row_bf16(row + 2 * D, v, half * 32, p.hd, nullptr, nullptr);
-            } else if (kj < p.T) {
-                float* dv = p.dV + ((long long)bh * p.T + kj) * p.hd;
-                float* dk = p.dK + ((long long)bh * p.T + kj) * p.hd;
-#pragma unroll
-                for (int e = 0; e < 32; e += 4) {
-                    const int d = half * 32 + e;
-                    if (d < p.hd) {
-                        *reinterpret_cast<float4*>(dv + d) = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
-                                                                          __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
-                        *reinterpret_cast<float4*>(dk + d) = make_float4(__uint_as_float(w[e]), __uint_as_float(w[e + 1]),
-                                                                          __uint_as_float(w[e + 2]), __uint_as_float(w[e + 3]));
-                    }
+            if (p.dqkv != nullptr) {
+                // the P and dS tiles are free (every product has completed): dK into the first, dV into the second
+                if (kj < p.T) {
+                    stage_row_bf16(sP, r, w, half * 32, p.hd, &rot, p.scale);
+                    stage_row_bf16(sP + TILE_BYTES, r, v, half * 32, p.hd, nullptr, 1.0f);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(out_full);
+                if (warp == 2 && lane == 0) {
+                    if (mbar_wait(out_full, 0, abort_flag)) {
+                        tma_store_4d(&tmoK, sP, 0, k0, h, b);              // rows past T are clipped
+                        tma_store_4d(&tmoV, sP + TILE_BYTES, 0, k0, h, b);
+                        tma_store_commit();
+                        tma_store_wait_read<0>();
+                    } else ok = false;
+                }
+            } else {
+                // separate float32 outputs [B*H, T, hd]: dK into the two P tiles (head-dim columns 0-31 | 32-63), dV
+                // into the two dS tiles; tmoK / tmoV are float32 maps here
+                const long long e0 = DBG_CLK();
+                if (kj < p.T && half * 32 < p.hd) {
+                    stage_row_f32(sP + half * TILE_BYTES, r, w, p.scale);
+                    stage_row_f32(sdS + half * TILE_BYTES, r, v, 1.0f);
+                }
+                const long long e1 = DBG_CLK();
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(out_full);
+                if (warp == 2 && lane == 0) {
+                    if (mbar_wait(out_full, 0, abort_flag)) {
+                        const long long e2 = DBG_CLK();
+                        for (int c = 0; c * 32 < p.hd; ++c) {
+                            tma_store_3d(&tmoK, sP + c * TILE_BYTES, c * 32, k0, bh);
+                            tma_store_3d(&tmoV, sdS + c * TILE_BYTES, c * 32, k0, bh);
+                        }
+                        tma_store_commit();
+                        tma_store_wait_read<0>();
+                        const long long e3 = DBG_CLK();
+                        dbg[12] = e0 - c_i; dbg[13] = e1 - e0; dbg[14] = e2 - e1; dbg[15] = e3 - e2;
+                    } else ok = false;
                 }
             }
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 23); }
+#ifdef TB_ATT_DEBUG
+        if (warp == 2 && lane == 0) {
+            const long long c_j = DBG_CLK();
+            dbg[8] = c_i - c_h; dbg[9] = c_j - c_i; dbg[0] = c_j - dbg_t0; dbg[10] = niter;
+            unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid)); dbg[11] = smid;
+            for (int i = 0; i < 16; ++i) g_att_dbg[0][blockIdx.y * gridDim.x + blockIdx.x][i] = dbg[i];
+        }
+#endif
     }
 
     __syncwarp();
@@ -623,25 +737,27 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                        const AttBwdParams p) {
+                        const __grid_constant__ CUtensorMap tmoQ, const AttBwdParams p) {
+    const long long dbg_t0 = DBG_CLK();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     uint8_t* sQ = smem;
     uint8_t* sdO = smem + TILE_BYTES;
-    uint8_t* sK = smem + 2 * TILE_BYTES;      // 2 stages
-    uint8_t* sV = smem + 4 * TILE_BYTES;      // 2 stages
-    uint8_t* sdS = smem + 6 * TILE_BYTES;     // [128 q, 128 keys] as two tiles
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 8 * TILE_BYTES);
+    uint8_t* sK = smem + 2 * TILE_BYTES;                              // ATT_BWD_STAGES stages
+    uint8_t* sV = smem + (2 + ATT_BWD_STAGES) * TILE_BYTES;           // ATT_BWD_STAGES stages
+    uint8_t* sdS = smem + (2 + 2 * ATT_BWD_STAGES) * TILE_BYTES;      // [128 q, 128 keys] as two tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (4 + 2 * ATT_BWD_STAGES) * TILE_BYTES);
     uint64_t* qdo_full = bars;         // 1
-    uint64_t* kv_full = bars + 1;      // 2
-    uint64_t* kv_empty = bars + 3;     // 2
-    uint64_t* sdp_full = bars + 5;
-    uint64_t* sdp_free = bars + 6;     // 8
-    uint64_t* ds_full = bars + 7;      // 8
-    uint64_t* ds_free = bars + 8;
-    uint64_t* acc_full = bars + 9;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* kv_full = bars + 1;      // ATT_BWD_STAGES
+    uint64_t* kv_empty = bars + 5;     // ATT_BWD_STAGES
+    uint64_t* sdp_full = bars + 9;
+    uint64_t* sdp_free = bars + 10;    // 8
+    uint64_t* ds_full = bars + 11;     // 8
+    uint64_t* ds_free = bars + 12;
+    uint64_t* acc_full = bars + 13;
+    uint64_t* out_full = bars + 14;    // 8 arrivals: the output tile is staged in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -653,9 +769,9 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
     if (threadIdx.x == 0) {
         mbar_init(qdo_full, 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        for (int i = 0; i < ATT_BWD_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
         mbar_init(sdp_full, 1); mbar_init(sdp_free, 8); mbar_init(ds_full, 8); mbar_init(ds_free, 1);
-        mbar_init(acc_full, 1);
+        mbar_init(acc_full, 1); mbar_init(out_full, 8);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -674,8 +790,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             tma_load_3d(sQ, &tmQ, qdo_full, 0, q0, bh);
             tma_load_4d(sdO, &tmdO, qdo_full, 0, q0, h, b);
             for (int it = 0; it < niter && ok; ++it) {
-                const int s = it & 1;
-                if (!mbar_wait(&kv_empty[s], (uint32_t)((it >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                const int s = it % ATT_BWD_STAGES;
+                if (!mbar_wait(&kv_empty[s], (uint32_t)((it / ATT_BWD_STAGES) & 1) ^ 1u, abort_flag)) { ok = false; break; }
                 mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
                 tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, it * ATT_BN, bh);
                 tma_load_3d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, it * ATT_BN, bh);
@@ -691,9 +807,9 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             bool ok = mbar_wait(qdo_full, 0, abort_flag);
             // S and dP of key block `it`; may run ahead of dQ += dS K of it-1 (see the dK/dV kernel)
             auto issue_sdp = [&](int it) -> bool {
-                const int s = it & 1;
+                const int s = it % ATT_BWD_STAGES;
                 const uint64_t dKk = dKk0 + (uint64_t)s * TILESTEP, dVk = dVk0 + (uint64_t)s * TILESTEP;
-                if (!mbar_wait(&kv_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) return false;
+                if (!mbar_wait(&kv_full[s], (uint32_t)((it / ATT_BWD_STAGES) & 1), abort_flag)) return false;
                 if (!mbar_wait(sdp_free, (uint32_t)(it & 1) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
@@ -715,9 +831,9 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             const uint64_t dKm0 = mnmajor_tile(smem_u32(sK), TILE_BYTES);
             bool ok = true;
             for (int it = 0; it < niter && ok; ++it) {
-                const int s = it & 1;
+                const int s = it % ATT_BWD_STAGES;
                 const uint64_t dKm = dKm0 + (uint64_t)s * TILESTEP;
-                if (!mbar_wait(&kv_full[s], (uint32_t)((it >> 1) & 1), abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&kv_full[s], (uint32_t)((it / ATT_BWD_STAGES) & 1), abort_flag)) { ok = false; break; }
                 if (!mbar_wait(ds_full, (uint32_t)(it & 1), abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
@@ -740,73 +856,89 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         const float lse2 = valid ? p.lse[(long long)bh * p.T + qi] * 1.4426950408889634f : INFINITY;
         const float dl = valid ? p.delta[(long long)bh * p.T + qi] : 0.0f;
         bool ok = true;
+        long long dbg[16] = {0}; dbg[1] = DBG_CLK() - dbg_t0;
         for (int it = 0; it < niter && ok; ++it) {
             const uint32_t pi = (uint32_t)(it & 1);
             const bool diag = (it == qb);
             const int k0 = it * ATT_BN;
+            const long long c_a = DBG_CLK();
             if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
             tc_fence_after();
+            const long long c_b = DBG_CLK();
             uint32_t sv0[32], sv1[32], dv0[32], dv1[32];
             tmem_ld32(tS + lane_base + (half * 2) * 32, sv0);
             tmem_ld32(tS + lane_base + (half * 2 + 1) * 32, sv1);
             tmem_ld32(tdP + lane_base + (half * 2) * 32, dv0);
             tmem_ld32(tdP + lane_base + (half * 2 + 1) * 32, dv1);
             tmem_ld_wait();
+            const long long c_c = DBG_CLK();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(sdp_free);                  // the score tiles live in registers now
-            float dS[32];
-            {
-                const int lim = diag ? qi - (k0 + (half * 2) * 32) : 32;
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float pe = fast_exp2(__uint_as_float(sv0[e]) * p.scale_log2 - lse2);
-                    if (diag) pe = e <= lim ? pe : 0.0f;
-                    dS[e] = pe * (__uint_as_float(dv0[e]) - dl) * p.scale;
-                }
-            }
-            if (!mbar_wait(ds_free, pi ^ 1u, abort_flag)) { ok = false; break; }      // previous dS consumed
+            float P[32], dS[32];       // P itself is not needed here (the compiler drops it)
+            p_and_ds(sv0, dv0, p.scale_log2, lse2, dl, diag, diag ? qi - (k0 + (half * 2) * 32) : 32, P, dS);
+            const long long c_d = DBG_CLK();
+            if (!mbar_wait(ds_free, pi ^ 1u, abort_flag)) { ok = false; break; }
+            const long long c_e = DBG_CLK();      // previous dS consumed
             store_chunk_bf16(sdS, r, half * 2, dS);
-            {
-                const int lim = diag ? qi - (k0 + (half * 2 + 1) * 32) : 32;
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float pe = fast_exp2(__uint_as_float(sv1[e]) * p.scale_log2 - lse2);
-                    if (diag) pe = e <= lim ? pe : 0.0f;
-                    dS[e] = pe * (__uint_as_float(dv1[e]) - dl) * p.scale;
-                }
-            }
+            p_and_ds(sv1, dv1, p.scale_log2, lse2, dl, diag, diag ? qi - (k0 + (half * 2 + 1) * 32) : 32, P, dS);
             store_chunk_bf16(sdS, r, half * 2 + 1, dS);
+            const long long c_f = DBG_CLK();
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_full);
+            const long long c_g = DBG_CLK();
+            dbg[2] += c_b - c_a; dbg[3] += c_c - c_b; dbg[4] += c_d - c_c; dbg[5] += c_e - c_d; dbg[6] += c_f - c_e; dbg[7] += c_g - c_f;
         }
+        const long long c_h = DBG_CLK();
+        RopeRow rot;                                  // fetched while the last product finishes
+        if (ok && valid && p.dqkv != nullptr)
+            load_rope_row(rot, p.cos_t + (long long)qi * (p.hd >> 1), p.sin_t + (long long)qi * (p.hd >> 1), half * 32, p.hd);
         if (ok) {
             if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
         }
+        const long long c_i = DBG_CLK();
         if (ok) {
             tc_fence_after();
             uint32_t v[32];
             tmem_ld32(tdQ + lane_base + half * 32, v);
             tmem_ld_wait();
-            if (valid && p.dqkv != nullptr) {
-                const int D = p.H * p.hd;
-                const int hh = p.hd >> 1;
-                store_row_bf16(p.dqkv + ((long long)b * p.T + qi) * 3 * D + h * p.hd + half * 32, v, half * 32, p.hd,
-                               p.cos_t + (long long)qi * hh, p.sin_t + (long long)qi * hh);
-            } else if (valid) {
-                float* dq = p.dQ + ((long long)bh * p.T + qi) * p.hd;
-#pragma unroll
-                for (int e = 0; e < 32; e += 4) {
-                    const int d = half * 32 + e;
-                    if (d < p.hd)
-                        *reinterpret_cast<float4*>(dq + d) = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
-                                                                          __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+            if (p.dqkv != nullptr) {
+                if (valid) stage_row_bf16(sdS, r, v, half * 32, p.hd, &rot, p.scale);      // the dS tiles are free
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(out_full);
+                if (warp == 2 && lane == 0) {
+                    if (mbar_wait(out_full, 0, abort_flag)) {
+                        tma_store_4d(&tmoQ, sdS, 0, q0, h, b);
+                        tma_store_commit();
+                        tma_store_wait_read<0>();
+                    } else ok = false;
+                }
+            } else {
+                if (valid && half * 32 < p.hd) stage_row_f32(sdS + half * TILE_BYTES, r, v, p.scale);    // float32 dQ [B*H, T, hd]
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(out_full);
+                if (warp == 2 && lane == 0) {
+                    if (mbar_wait(out_full, 0, abort_flag)) {
+                        for (int c = 0; c * 32 < p.hd; ++c) tma_store_3d(&tmoQ, sdS + c * TILE_BYTES, c * 32, q0, bh);
+                        tma_store_commit();
+                        tma_store_wait_read<0>();
+                    } else ok = false;
                 }
             }
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 33); }
+#ifdef TB_ATT_DEBUG
+        if (warp == 2 && lane == 0) {
+            const long long c_j = DBG_CLK();
+            dbg[8] = c_i - c_h; dbg[9] = c_j - c_i; dbg[0] = c_j - dbg_t0; dbg[10] = niter;
+            unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid)); dbg[11] = smid;
+            for (int i = 0; i < 16; ++i) g_att_dbg[1][blockIdx.y * gridDim.x + blockIdx.x][i] = dbg[i];
+        }
+#endif
     }
 
     __syncwarp();
@@ -816,8 +948,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-constexpr int ATT_DKDV_SMEM = 1024 + 10 * TILE_BYTES + 256;
-constexpr int ATT_DQ_SMEM = 1024 + 8 * TILE_BYTES + 256;
+constexpr int ATT_DKDV_SMEM = 1024 + (6 + 2 * ATT_BWD_STAGES) * TILE_BYTES + 256;
+constexpr int ATT_DQ_SMEM = 1024 + (4 + 2 * ATT_BWD_STAGES) * TILE_BYTES + 256;
 
 int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, const bf16* att,
                          const bf16* datt, const float* lse, float* delta, float* dQ, float* dK, float* dV, int B,
@@ -833,6 +965,17 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     TB_TRY(make_operand_map(&tmK, K, hd, T, hd, BH, (long long)T * hd, 128));
     TB_TRY(make_operand_map(&tmV, V, hd, T, hd, BH, (long long)T * hd, 128));
     TB_TRY(make_operand_map4(&tmdO, datt, hd, T, D, H, hd, B, (long long)T * D, 128));
+    // the merged output dqkv [B*T, 3D] as three (hd, T, H, B) views for the tile stores
+    CUtensorMap tmoQ = tmdO, tmoK = tmdO, tmoV = tmdO;
+    if (dqkv != nullptr) {
+        TB_TRY(make_operand_map4(&tmoQ, dqkv, hd, T, 3LL * D, H, hd, B, (long long)T * 3 * D, 128));
+        TB_TRY(make_operand_map4(&tmoK, dqkv + D, hd, T, 3LL * D, H, hd, B, (long long)T * 3 * D, 128));
+        TB_TRY(make_operand_map4(&tmoV, dqkv + 2 * D, hd, T, 3LL * D, H, hd, B, (long long)T * 3 * D, 128));
+    } else {
+        TB_TRY(make_operand_map_f32(&tmoQ, dQ, hd, T, hd, BH, (long long)T * hd, 128));
+        TB_TRY(make_operand_map_f32(&tmoK, dK, hd, T, hd, BH, (long long)T * hd, 128));
+        TB_TRY(make_operand_map_f32(&tmoV, dV, hd, T, hd, BH, (long long)T * hd, 128));
+    }
     AttBwdParams p;
     p.T = T; p.H = H; p.hd = hd; p.nq = (T + ATT_BM - 1) / ATT_BM;
     p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
@@ -857,12 +1000,12 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     dim3 grid(BH, p.nq);
     const double tri = (double)BH * T * (double)T * hd;      // one lower-triangular product = tri flops
     prof_mark(ctx, "attention_bwd_dkdv", 4.0 * tri, (double)BH * T * hd * (2.0 * 4 + 8.0), stream);
-    TB_CUDA(launch_kernel(attention_bwd_dkdv_kernel, dim3(grid), dim3(ATT_BWD_THREADS), ATT_DKDV_SMEM, stream, tmQ, tmK, tmV, tmdO, p));
+    TB_CUDA(launch_kernel(attention_bwd_dkdv_kernel, dim3(grid), dim3(ATT_BWD_THREADS), ATT_DKDV_SMEM, stream, tmQ, tmK, tmV, tmdO, tmoK, tmoV, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
     prof_mark(ctx, "attention_bwd_dq", 3.0 * tri, (double)BH * T * hd * (2.0 * 4 + 4.0), stream);
-    TB_CUDA(launch_kernel(attention_bwd_dq_kernel, dim3(grid), dim3(ATT_BWD_THREADS), ATT_DQ_SMEM, stream, tmQ, tmK, tmV, tmdO, p));
+    TB_CUDA(launch_kernel(attention_bwd_dq_kernel, dim3(grid), dim3(ATT_BWD_THREADS), ATT_DQ_SMEM, stream, tmQ, tmK, tmV, tmdO, tmoQ, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -881,6 +1024,8 @@ int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     const long long kv_rows = kv_rows_per_head > 0 ? kv_rows_per_head : T;      // a KV cache has room for more rows
     TB_TRY(make_operand_map(&tmK, K, hd, T, hd, BH, kv_rows * hd, ATT_BN));
     TB_TRY(make_operand_map(&tmV, V, hd, T, hd, BH, kv_rows * hd, ATT_BN));
+    CUtensorMap tmO;        // att [B*T, D] as (hd, T, H, B) for the tile store
+    TB_TRY(make_operand_map4(&tmO, att, hd, T, (long long)H * hd, H, hd, B, (long long)T * H * hd, ATT_BM));
     AttFwdParams p;
     p.T = T; p.H = H; p.hd = hd; p.D = H * hd;
     p.nq = (T + ATT_BM - 1) / ATT_BM;
@@ -894,7 +1039,7 @@ int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     dim3 grid(BH, p.nq);
     // algorithmic work: the lower triangle of two products of 2*T*T*hd flops each
     prof_mark(ctx, "attention_fwd", 2.0 * (double)BH * T * (double)T * hd, (double)BH * T * hd * 2.0 * 4.0, stream);
-    TB_CUDA(launch_kernel(attention_fwd_kernel, dim3(grid), dim3(192), ATT_FWD_SMEM, stream, tmQ, tmK, tmV, p));
+    TB_CUDA(launch_kernel(attention_fwd_kernel, dim3(grid), dim3(192), ATT_FWD_SMEM, stream, tmQ, tmK, tmV, tmO, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -902,3 +1047,9 @@ int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
 }
 
 }  // namespace tb
+
+#ifdef TB_ATT_DEBUG
+extern "C" int tb_debug_att_read(long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, tb::g_att_dbg, sizeof(tb::g_att_dbg));
+}
+#endif

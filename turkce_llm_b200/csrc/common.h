@@ -149,6 +149,9 @@ int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn);
 // TMA map over a bf16 matrix seen as (inner, rows, batch) with a 64-element x box_rows box, 128B swizzle
 int make_operand_map(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld, int batch,
                      long long batch_stride, int box_rows);
+// the same over a float32 matrix: 32-element x box_rows box
+int make_operand_map_f32(CUtensorMap* map, const float* ptr, long long inner, long long rows, long long ld, int batch,
+                         long long batch_stride, int box_rows);
 // the same over a 4-level view (inner, rows, batch0, batch1) -- e.g. one head of a [B*T, H*hd] matrix
 int make_operand_map4(CUtensorMap* map, const bf16* ptr, long long inner, long long rows, long long ld,
                       long long n0, long long stride0, long long n1, long long stride1, int box_rows);
