@@ -52,13 +52,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // bound by instruction issue (about 2,000 cycles per 128 x 128 block for 64 scores per thread), not by a unit.
 __device__ __forceinline__ float2 pair_of(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
 
-#ifdef TB_ATT_DEBUG
-__device__ long long g_att_dbg[2][1024][16];
-__device__ long long g_att_e[4];
-#define DBG_CLK() clock64()
-#else
-#define DBG_CLK() 0ll
-#endif
 
 // 32 consecutive values of row r -> bf16 in a [128 x 128] operand stored as two [128 x 64] tiles
 __device__ __forceinline__ void store_chunk_bf16(uint8_t* tiles, int r, int c, const float (&x)[32]) {
@@ -386,8 +379,14 @@ struct AttBwdParams {
     // the position embedding applied to dQ and dK on the way out (the reference's k_qkv_rope_merge_bwd,
     // cuda/train_kernels.cu:600-626); cos_t/sin_t are the [T, hd/2] tables
     bf16* dqkv; const float* cos_t; const float* sin_t;
+    // dS hand-off between the two kernels: the dK/dV kernel stores each [128 q x 128 keys] block of dS' = P * (dP - delta)
+    // (bf16, the 32 KB shared-memory image it feeds its own tensor-core product with) at block index
+    // bh * nq*(nq+1)/2 + qb*(qb+1)/2 + kb; the dQ kernel reads the blocks back and only forms dQ = sum_kb dS' K.
+    // (Recomputing S, dP and the exponentials there instead cost a second pass over the 2^x unit, the busiest one.)
+    bf16* ds;
     int* err;
 };
+constexpr int DS_BLOCK_BYTES = 2 * TILE_BYTES;
 
 // The rotation tables of one row for 32 consecutive head-dim values (16 pairs) starting at d0: fetched before the
 // wait for the accumulators, in one batch (loads placed between the stores of a row would each wait for the
@@ -466,13 +465,7 @@ __device__ __forceinline__ void p_and_ds(const uint32_t (&sv)[32], const uint32_
     }
 }
 
-// Stages of the operand pair that changes per step (Q, dO in the dK/dV kernel; K, V in the dQ kernel).  With two, the
-// load of step i+1 can only start when step i-1 has been consumed, and its latency plus the score products (~1,700
-// cycles) exceed one step of the compute warps: they waited ~500 cycles per step.  With three it starts a step earlier.
-#ifndef ATT_BWD_STAGES
-#define ATT_BWD_STAGES 3
-#endif
-static_assert(ATT_BWD_STAGES >= 2 && ATT_BWD_STAGES <= 4, "barrier slots are laid out for up to four stages");
+constexpr int ATT_BWD_STAGES = 2;       // stages of the (Q, dO) pair in the dK/dV kernel
 constexpr int ATT_BWD_THREADS = 352;     // TMA warp, score-MMA warp, 8 compute warps, gradient-MMA warp
 // (two issuing threads on different schedulers: one thread cannot issue a block's 24 UMMAs as fast as the
 //  tensor pipe retires them while eight compute warps compete for the same issue slots)
@@ -483,7 +476,6 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                           const __grid_constant__ CUtensorMap tmoK, const __grid_constant__ CUtensorMap tmoV,
                           const AttBwdParams p) {
-    const long long dbg_t0 = DBG_CLK();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -492,8 +484,8 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     uint8_t* sQ = smem + 2 * TILE_BYTES;                              // ATT_BWD_STAGES stages
     uint8_t* sdO = smem + (2 + ATT_BWD_STAGES) * TILE_BYTES;          // ATT_BWD_STAGES stages
     uint8_t* sP = smem + (2 + 2 * ATT_BWD_STAGES) * TILE_BYTES;       // [128 q, 128 keys] as two tiles
-    uint8_t* sdS = smem + (4 + 2 * ATT_BWD_STAGES) * TILE_BYTES;      // same
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (6 + 2 * ATT_BWD_STAGES) * TILE_BYTES);
+    uint8_t* sdS = smem + (4 + 2 * ATT_BWD_STAGES) * TILE_BYTES;      // same, two buffers (one is being stored to HBM)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (8 + 2 * ATT_BWD_STAGES) * TILE_BYTES);
     uint64_t* kv_full = bars;          // 1
     uint64_t* qdo_full = bars + 1;     // ATT_BWD_STAGES
     uint64_t* qdo_empty = bars + 5;    // ATT_BWD_STAGES
@@ -503,6 +495,7 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     uint64_t* pds_free = bars + 12;
     uint64_t* acc_full = bars + 13;
     uint64_t* out_full = bars + 14;    // 8 arrivals: the output tile is staged in shared memory
+    uint64_t* ds_stored = bars + 16;   // 2: the bulk store of dS buffer b has read it
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -518,6 +511,7 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         for (int i = 0; i < ATT_BWD_STAGES; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
         mbar_init(sdp_full, 1); mbar_init(sdp_free, 8); mbar_init(pds_full, 8); mbar_init(pds_free, 1);
         mbar_init(acc_full, 1); mbar_init(out_full, 8);
+        mbar_init(&ds_stored[0], 1); mbar_init(&ds_stored[1], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -575,7 +569,8 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         // second issuer: dV += P^T dO and dK += dS^T Q once the compute warps have written P and dS
         if (lane == 0) {
             const uint32_t id_t = umma_idesc(1u, 1u, 1u, 128, 64);       // both operands MN-major
-            const uint64_t dPm = mnmajor_tile(smem_u32(sP), TILE_BYTES), ddSm = mnmajor_tile(smem_u32(sdS), TILE_BYTES);
+            const uint64_t dPm = mnmajor_tile(smem_u32(sP), TILE_BYTES), ddSm0 = mnmajor_tile(smem_u32(sdS), TILE_BYTES);
+            const long long nblk = (long long)p.nq * (p.nq + 1) / 2;
             const uint64_t dQm0 = mnmajor_tile(smem_u32(sQ), TILE_BYTES), ddOm0 = mnmajor_tile(smem_u32(sdO), TILE_BYTES);
             bool ok = true;
             for (int it = 0; it < niter && ok; ++it) {
@@ -587,6 +582,7 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                     umma_bf16(tdV, dPm + k * MNSTEP, ddOm + k * MNSTEP, id_t, (it > 0 || k > 0) ? 1u : 0u);
+                const uint64_t ddSm = ddSm0 + (uint64_t)(it & 1) * (2 * TILESTEP);
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                     umma_bf16(tdK, ddSm + k * MNSTEP, dQm + k * MNSTEP, id_t, (it > 0 || k > 0) ? 1u : 0u);
@@ -594,8 +590,22 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 // S and dP of this block (the other issuer's) completed before the compute warps could sign
                 // pds_full, so this commit covers every read of the stage
                 umma_commit(&qdo_empty[s]);
+                if (it == niter - 1) umma_commit(acc_full);      // the epilogue need not wait for the store below
+                // the dS block leaves for the dQ kernel as it lies in shared memory; its buffer is written again two
+                // steps from now, and this thread has nothing else to do until the next block is ready.  Not before the
+                // products above have completed: a 32 KB read of shared memory beside them delays pds_free, which the
+                // compute warps need ~900 cycles after they sign pds_full
+                if (!mbar_wait(pds_free, (uint32_t)(it & 1), abort_flag)) { ok = false; break; }
+                {
+                    const int qb = kb + it;
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(p.ds) +
+                                   ((long long)bh * nblk + (long long)qb * (qb + 1) / 2 + kb) * DS_BLOCK_BYTES;
+                    bulk_store(dst, sdS + (it & 1) * DS_BLOCK_BYTES, DS_BLOCK_BYTES);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                    mbar_arrive(&ds_stored[it & 1]);
+                }
             }
-            if (ok) umma_commit(acc_full);
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 24); }
         }
     } else {
@@ -604,7 +614,6 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         const int r = q * 32 + lane;                  // query row inside the block
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         bool ok = true;
-        long long dbg[16] = {0}; dbg[1] = DBG_CLK() - dbg_t0;
         // the row's log-sum-exp and delta of the NEXT query block are fetched while this one is worked on
         float lse_next = INFINITY, dl_next = 0.0f;
         {
@@ -622,10 +631,8 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 lse_next = p.lse[(long long)bh * p.T + qi + ATT_BM] * 1.4426950408889634f;
                 dl_next = p.delta[(long long)bh * p.T + qi + ATT_BM];
             }
-            const long long c_a = DBG_CLK();
             if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const long long c_b = DBG_CLK();
             // this thread's 64 scores and 64 dP values in one TMEM round trip, then the tiles are free
             uint32_t sv0[32], sv1[32], dv0[32], dv1[32];
             tmem_ld32(tS + lane_base + (half * 2) * 32, sv0);
@@ -633,30 +640,25 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             tmem_ld32(tdP + lane_base + (half * 2) * 32, dv0);
             tmem_ld32(tdP + lane_base + (half * 2 + 1) * 32, dv1);
             tmem_ld_wait();
-            const long long c_c = DBG_CLK();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(sdp_free);
             // rows past T get lse2 = +inf, i.e. P = 0; the diagonal block masks keys after the query
             float P[32], dS[32];
             p_and_ds(sv0, dv0, p.scale_log2, lse2, dl, diag, diag ? qi - (k0 + (half * 2) * 32) : 32, P, dS);
-            const long long c_d = DBG_CLK();
-            if (!mbar_wait(pds_free, pi ^ 1u, abort_flag)) { ok = false; break; }
-            const long long c_e = DBG_CLK();     // previous P, dS consumed
+            if (!mbar_wait(pds_free, pi ^ 1u, abort_flag)) { ok = false; break; }     // previous P, dS consumed
+            uint8_t* sdS_it = sdS + pi * DS_BLOCK_BYTES;                                // and this buffer's block stored
+            if (!mbar_wait(&ds_stored[pi], (uint32_t)((it >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
             store_chunk_bf16(sP, r, half * 2, P);
-            store_chunk_bf16(sdS, r, half * 2, dS);
+            store_chunk_bf16(sdS_it, r, half * 2, dS);
             p_and_ds(sv1, dv1, p.scale_log2, lse2, dl, diag, diag ? qi - (k0 + (half * 2 + 1) * 32) : 32, P, dS);
             store_chunk_bf16(sP, r, half * 2 + 1, P);
-            store_chunk_bf16(sdS, r, half * 2 + 1, dS);
-            const long long c_f = DBG_CLK();
+            store_chunk_bf16(sdS_it, r, half * 2 + 1, dS);
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(pds_full);
-            const long long c_g = DBG_CLK();
-            dbg[2] += c_b - c_a; dbg[3] += c_c - c_b; dbg[4] += c_d - c_c; dbg[5] += c_e - c_d; dbg[6] += c_f - c_e; dbg[7] += c_g - c_f;
         }
-        const long long c_h = DBG_CLK();
         const int kj = k0 + r;                        // key row of the accumulators
         RopeRow rot;                                  // fetched while the last products finish
         if (ok && kj < p.T && p.dqkv != nullptr)
@@ -664,7 +666,6 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         if (ok) {
             if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
         }
-        const long long c_i = DBG_CLK();
         if (ok) {
             tc_fence_after();
             uint32_t v[32], w[32];
@@ -690,40 +691,27 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                 }
             } else {
                 // separate float32 outputs [B*H, T, hd]: dK into the two P tiles (head-dim columns 0-31 | 32-63), dV
-                // into the two dS tiles; tmoK / tmoV are float32 maps here
-                const long long e0 = DBG_CLK();
+                // into the two Q stages (a dS buffer may still be on its way out); tmoK / tmoV are float32 maps here
                 if (kj < p.T && half * 32 < p.hd) {
                     stage_row_f32(sP + half * TILE_BYTES, r, w, p.scale);
-                    stage_row_f32(sdS + half * TILE_BYTES, r, v, 1.0f);
+                    stage_row_f32(sQ + half * TILE_BYTES, r, v, 1.0f);
                 }
-                const long long e1 = DBG_CLK();
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(out_full);
                 if (warp == 2 && lane == 0) {
                     if (mbar_wait(out_full, 0, abort_flag)) {
-                        const long long e2 = DBG_CLK();
                         for (int c = 0; c * 32 < p.hd; ++c) {
                             tma_store_3d(&tmoK, sP + c * TILE_BYTES, c * 32, k0, bh);
-                            tma_store_3d(&tmoV, sdS + c * TILE_BYTES, c * 32, k0, bh);
+                            tma_store_3d(&tmoV, sQ + c * TILE_BYTES, c * 32, k0, bh);
                         }
                         tma_store_commit();
                         tma_store_wait_read<0>();
-                        const long long e3 = DBG_CLK();
-                        dbg[12] = e0 - c_i; dbg[13] = e1 - e0; dbg[14] = e2 - e1; dbg[15] = e3 - e2;
                     } else ok = false;
                 }
             }
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 23); }
-#ifdef TB_ATT_DEBUG
-        if (warp == 2 && lane == 0) {
-            const long long c_j = DBG_CLK();
-            dbg[8] = c_i - c_h; dbg[9] = c_j - c_i; dbg[0] = c_j - dbg_t0; dbg[10] = niter;
-            unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid)); dbg[11] = smid;
-            for (int i = 0; i < 16; ++i) g_att_dbg[0][blockIdx.y * gridDim.x + blockIdx.x][i] = dbg[i];
-        }
-#endif
     }
 
     __syncwarp();
@@ -733,31 +721,29 @@ attention_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-// dQ of one query block: walks its key blocks kb = 0 .. qb.
-__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
-attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                        const __grid_constant__ CUtensorMap tmoQ, const AttBwdParams p) {
-    const long long dbg_t0 = DBG_CLK();
+// dQ of one query block: dQ = scale * sum over its key blocks kb = 0 .. qb of dS'(qb, kb) K(kb), the dS' blocks read
+// back as the dK/dV kernel stored them.  No exponentials and no compute warps in the loop: a loader, a tensor-core
+// issuer and four epilogue warps (thread = query row); two stages of 48 KB, so two CTAs share an SM and the prologue
+// and epilogue of one hide behind the loop of the other.  Sums are formed in key-block order: fixed, no atomics.
+constexpr int ATT_DQ_THREADS = 192;
+constexpr int ATT_DQ_STAGES = 2;
+constexpr int ATT_DQ_STAGE_BYTES = DS_BLOCK_BYTES + TILE_BYTES;
+
+__global__ void __launch_bounds__(ATT_DQ_THREADS, 2)
+attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmoQ,
+                        const AttBwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
-    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-    uint8_t* sQ = smem;
-    uint8_t* sdO = smem + TILE_BYTES;
-    uint8_t* sK = smem + 2 * TILE_BYTES;                              // ATT_BWD_STAGES stages
-    uint8_t* sV = smem + (2 + ATT_BWD_STAGES) * TILE_BYTES;           // ATT_BWD_STAGES stages
-    uint8_t* sdS = smem + (2 + 2 * ATT_BWD_STAGES) * TILE_BYTES;      // [128 q, 128 keys] as two tiles
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (4 + 2 * ATT_BWD_STAGES) * TILE_BYTES);
-    uint64_t* qdo_full = bars;         // 1
-    uint64_t* kv_full = bars + 1;      // ATT_BWD_STAGES
-    uint64_t* kv_empty = bars + 5;     // ATT_BWD_STAGES
-    uint64_t* sdp_full = bars + 9;
-    uint64_t* sdp_free = bars + 10;    // 8
-    uint64_t* ds_full = bars + 11;     // 8
-    uint64_t* ds_free = bars + 12;
-    uint64_t* acc_full = bars + 13;
-    uint64_t* out_full = bars + 14;    // 8 arrivals: the output tile is staged in shared memory
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    // stage s: dS block (two [128 x 64] tiles) then the K tile.  The request is 1 KB + the stages: the barriers go
+    // behind the stages when the alignment pad leaves room there (the usual case: pad 0), else into the pad itself
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pad <= 768u ? smem + ATT_DQ_STAGES * ATT_DQ_STAGE_BYTES : smem_raw);
+    uint64_t* full = bars;             // ATT_DQ_STAGES
+    uint64_t* empty = bars + 2;        // ATT_DQ_STAGES
+    uint64_t* acc_full = bars + 4;
+    uint64_t* out_full = bars + 5;     // 4 arrivals
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -768,193 +754,120 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const int niter = qb + 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(qdo_full, 1);
-        for (int i = 0; i < ATT_BWD_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-        mbar_init(sdp_full, 1); mbar_init(sdp_free, 8); mbar_init(ds_full, 8); mbar_init(ds_free, 1);
-        mbar_init(acc_full, 1); mbar_init(out_full, 8);
+        for (int i = 0; i < ATT_DQ_STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        mbar_init(acc_full, 1); mbar_init(out_full, 4);
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, 64); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tdQ = *tmem_slot;
     pdl_wait();                 // everything above is independent of earlier kernels' results
-    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256;
 
     if (warp == 0) {
         if (lane == 0) {
             bool ok = true;
-            mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
-            tma_load_3d(sQ, &tmQ, qdo_full, 0, q0, bh);
-            tma_load_4d(sdO, &tmdO, qdo_full, 0, q0, h, b);
+            const long long nblk = (long long)p.nq * (p.nq + 1) / 2;
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ds) +
+                                 ((long long)bh * nblk + (long long)qb * (qb + 1) / 2) * DS_BLOCK_BYTES;
             for (int it = 0; it < niter && ok; ++it) {
-                const int s = it % ATT_BWD_STAGES;
-                if (!mbar_wait(&kv_empty[s], (uint32_t)((it / ATT_BWD_STAGES) & 1) ^ 1u, abort_flag)) { ok = false; break; }
-                mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-                tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, it * ATT_BN, bh);
-                tma_load_3d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, it * ATT_BN, bh);
+                const int s = it % ATT_DQ_STAGES;
+                if (!mbar_wait(&empty[s], (uint32_t)((it / ATT_DQ_STAGES) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                uint8_t* st = smem + s * ATT_DQ_STAGE_BYTES;
+                mbar_expect_tx(&full[s], ATT_DQ_STAGE_BYTES);
+                bulk_load(st, src + (long long)it * DS_BLOCK_BYTES, DS_BLOCK_BYTES, &full[s]);
+                tma_load_3d(st + DS_BLOCK_BYTES, &tmK, &full[s], 0, it * ATT_BN, bh);
             }
             pdl_launch_dependents_now();     // all loads issued: the next kernel may start its prologue
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 31); }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t id_s = umma_idesc(1u, 0u, 0u, 128, 128);
-            const uint64_t dQk = kmajor_tile(smem_u32(sQ)), ddOk = kmajor_tile(smem_u32(sdO));
-            const uint64_t dKk0 = kmajor_tile(smem_u32(sK)), dVk0 = kmajor_tile(smem_u32(sV));
-            bool ok = mbar_wait(qdo_full, 0, abort_flag);
-            // S and dP of key block `it`; may run ahead of dQ += dS K of it-1 (see the dK/dV kernel)
-            auto issue_sdp = [&](int it) -> bool {
-                const int s = it % ATT_BWD_STAGES;
-                const uint64_t dKk = dKk0 + (uint64_t)s * TILESTEP, dVk = dVk0 + (uint64_t)s * TILESTEP;
-                if (!mbar_wait(&kv_full[s], (uint32_t)((it / ATT_BWD_STAGES) & 1), abort_flag)) return false;
-                if (!mbar_wait(sdp_free, (uint32_t)(it & 1) ^ 1u, abort_flag)) return false;
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tS, dQk + k * KSTEP, dKk + k * KSTEP, id_s, k > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tdP, ddOk + k * KSTEP, dVk + k * KSTEP, id_s, k > 0 ? 1u : 0u);
-                umma_commit(sdp_full);
-                return true;
-            };
-            if (ok) ok = issue_sdp(0);
-            for (int it = 0; it + 1 < niter && ok; ++it) ok = issue_sdp(it + 1);
-            if (!ok) { *abort_flag = 1; atomicExch(p.err, 32); }
-        }
-    } else if (warp == 10) {
-        // second issuer: dQ += dS K once the compute warps have written dS
-        if (lane == 0) {
             const uint32_t id_q = umma_idesc(1u, 0u, 1u, 128, 64);       // dS (K-major) x K block (MN-major)
-            const uint64_t ddSk = kmajor_tile(smem_u32(sdS));
-            const uint64_t dKm0 = mnmajor_tile(smem_u32(sK), TILE_BYTES);
             bool ok = true;
             for (int it = 0; it < niter && ok; ++it) {
-                const int s = it % ATT_BWD_STAGES;
-                const uint64_t dKm = dKm0 + (uint64_t)s * TILESTEP;
-                if (!mbar_wait(&kv_full[s], (uint32_t)((it / ATT_BWD_STAGES) & 1), abort_flag)) { ok = false; break; }
-                if (!mbar_wait(ds_full, (uint32_t)(it & 1), abort_flag)) { ok = false; break; }
+                const int s = it % ATT_DQ_STAGES;
+                const uint32_t st = smem_u32(smem + s * ATT_DQ_STAGE_BYTES);
+                const uint64_t ddSk = kmajor_tile(st);
+                const uint64_t dKm = mnmajor_tile(st + DS_BLOCK_BYTES, TILE_BYTES);
+                if (!mbar_wait(&full[s], (uint32_t)((it / ATT_DQ_STAGES) & 1), abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                     umma_bf16(tdQ, ddSk + (uint64_t)(k >> 2) * TILESTEP + (uint64_t)(k & 3) * KSTEP, dKm + k * MNSTEP, id_q,
                               (it > 0 || k > 0) ? 1u : 0u);
-                umma_commit(ds_free);
-                umma_commit(&kv_empty[s]);       // S, dP of this block completed before ds_full could be signed
+                umma_commit(&empty[s]);
             }
             if (ok) umma_commit(acc_full);
-            if (!ok) { *abort_flag = 1; atomicExch(p.err, 34); }
+            if (!ok) { *abort_flag = 1; atomicExch(p.err, 32); }
         }
     } else {
         const int q = warp & 3;
-        const int half = (warp - 2) >> 2;
         const int r = q * 32 + lane;
         const int qi = q0 + r;
         const bool valid = qi < p.T;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        const float lse2 = valid ? p.lse[(long long)bh * p.T + qi] * 1.4426950408889634f : INFINITY;
-        const float dl = valid ? p.delta[(long long)bh * p.T + qi] : 0.0f;
         bool ok = true;
-        long long dbg[16] = {0}; dbg[1] = DBG_CLK() - dbg_t0;
-        for (int it = 0; it < niter && ok; ++it) {
-            const uint32_t pi = (uint32_t)(it & 1);
-            const bool diag = (it == qb);
-            const int k0 = it * ATT_BN;
-            const long long c_a = DBG_CLK();
-            if (!mbar_wait(sdp_full, pi, abort_flag)) { ok = false; break; }
+        RopeRow rot0, rot1;                           // fetched while the products run
+        if (valid && p.dqkv != nullptr) {
+            const float* cs = p.cos_t + (long long)qi * (p.hd >> 1);
+            const float* sn = p.sin_t + (long long)qi * (p.hd >> 1);
+            load_rope_row(rot0, cs, sn, 0, p.hd);
+            load_rope_row(rot1, cs, sn, 32, p.hd);
+        }
+        if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
+        if (ok) {
             tc_fence_after();
-            const long long c_b = DBG_CLK();
-            uint32_t sv0[32], sv1[32], dv0[32], dv1[32];
-            tmem_ld32(tS + lane_base + (half * 2) * 32, sv0);
-            tmem_ld32(tS + lane_base + (half * 2 + 1) * 32, sv1);
-            tmem_ld32(tdP + lane_base + (half * 2) * 32, dv0);
-            tmem_ld32(tdP + lane_base + (half * 2 + 1) * 32, dv1);
+            uint32_t v0[32], v1[32];
+            tmem_ld32(tdQ + lane_base, v0);
+            tmem_ld32(tdQ + lane_base + 32, v1);
             tmem_ld_wait();
-            const long long c_c = DBG_CLK();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sdp_free);                  // the score tiles live in registers now
-            float P[32], dS[32];       // P itself is not needed here (the compiler drops it)
-            p_and_ds(sv0, dv0, p.scale_log2, lse2, dl, diag, diag ? qi - (k0 + (half * 2) * 32) : 32, P, dS);
-            const long long c_d = DBG_CLK();
-            if (!mbar_wait(ds_free, pi ^ 1u, abort_flag)) { ok = false; break; }
-            const long long c_e = DBG_CLK();      // previous dS consumed
-            store_chunk_bf16(sdS, r, half * 2, dS);
-            p_and_ds(sv1, dv1, p.scale_log2, lse2, dl, diag, diag ? qi - (k0 + (half * 2 + 1) * 32) : 32, P, dS);
-            store_chunk_bf16(sdS, r, half * 2 + 1, dS);
-            const long long c_f = DBG_CLK();
-            tc_fence_before();
+            uint8_t* out = smem;                      // stage 0 is free: every product has completed
+            if (p.dqkv != nullptr) {
+                if (valid) {
+                    stage_row_bf16(out, r, v0, 0, p.hd, &rot0, p.scale);
+                    stage_row_bf16(out, r, v1, 32, p.hd, &rot1, p.scale);
+                }
+            } else if (valid) {                       // float32 dQ [B*H, T, hd]
+                stage_row_f32(out, r, v0, p.scale);
+                if (p.hd > 32) stage_row_f32(out + TILE_BYTES, r, v1, p.scale);
+            }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(ds_full);
-            const long long c_g = DBG_CLK();
-            dbg[2] += c_b - c_a; dbg[3] += c_c - c_b; dbg[4] += c_d - c_c; dbg[5] += c_e - c_d; dbg[6] += c_f - c_e; dbg[7] += c_g - c_f;
-        }
-        const long long c_h = DBG_CLK();
-        RopeRow rot;                                  // fetched while the last product finishes
-        if (ok && valid && p.dqkv != nullptr)
-            load_rope_row(rot, p.cos_t + (long long)qi * (p.hd >> 1), p.sin_t + (long long)qi * (p.hd >> 1), half * 32, p.hd);
-        if (ok) {
-            if (!mbar_wait(acc_full, 0, abort_flag)) ok = false;
-        }
-        const long long c_i = DBG_CLK();
-        if (ok) {
-            tc_fence_after();
-            uint32_t v[32];
-            tmem_ld32(tdQ + lane_base + half * 32, v);
-            tmem_ld_wait();
-            if (p.dqkv != nullptr) {
-                if (valid) stage_row_bf16(sdS, r, v, half * 32, p.hd, &rot, p.scale);      // the dS tiles are free
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(out_full);
-                if (warp == 2 && lane == 0) {
-                    if (mbar_wait(out_full, 0, abort_flag)) {
-                        tma_store_4d(&tmoQ, sdS, 0, q0, h, b);
-                        tma_store_commit();
-                        tma_store_wait_read<0>();
-                    } else ok = false;
-                }
-            } else {
-                if (valid && half * 32 < p.hd) stage_row_f32(sdS + half * TILE_BYTES, r, v, p.scale);    // float32 dQ [B*H, T, hd]
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(out_full);
-                if (warp == 2 && lane == 0) {
-                    if (mbar_wait(out_full, 0, abort_flag)) {
-                        for (int c = 0; c * 32 < p.hd; ++c) tma_store_3d(&tmoQ, sdS + c * TILE_BYTES, c * 32, q0, bh);
-                        tma_store_commit();
-                        tma_store_wait_read<0>();
-                    } else ok = false;
-                }
+            if (lane == 0) mbar_arrive(out_full);
+            if (q == 0 && lane == 0) {
+                if (mbar_wait(out_full, 0, abort_flag)) {
+                    if (p.dqkv != nullptr) tma_store_4d(&tmoQ, out, 0, q0, h, b);          // rows past T are clipped
+                    else for (int c = 0; c * 32 < p.hd; ++c) tma_store_3d(&tmoQ, out + c * TILE_BYTES, c * 32, q0, bh);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                } else ok = false;
             }
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 33); }
-#ifdef TB_ATT_DEBUG
-        if (warp == 2 && lane == 0) {
-            const long long c_j = DBG_CLK();
-            dbg[8] = c_i - c_h; dbg[9] = c_j - c_i; dbg[0] = c_j - dbg_t0; dbg[10] = niter;
-            unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid)); dbg[11] = smid;
-            for (int i = 0; i < 16; ++i) g_att_dbg[1][blockIdx.y * gridDim.x + blockIdx.x][i] = dbg[i];
-        }
-#endif
     }
 
     __syncwarp();
     if (*abort_flag) for (int i = 0; i < 64; ++i) __nanosleep(1000);
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tdQ, 64); }
 }
 
-constexpr int ATT_DKDV_SMEM = 1024 + (6 + 2 * ATT_BWD_STAGES) * TILE_BYTES + 256;
-constexpr int ATT_DQ_SMEM = 1024 + (4 + 2 * ATT_BWD_STAGES) * TILE_BYTES + 256;
+constexpr int ATT_DKDV_SMEM = 1024 + (8 + 2 * ATT_BWD_STAGES) * TILE_BYTES + 256;
+constexpr int ATT_DQ_SMEM = 1024 + ATT_DQ_STAGES * ATT_DQ_STAGE_BYTES;
+
+size_t attention_bwd_ds_bytes(int B, int H, int T) {
+    const long long nq = (T + ATT_BM - 1) / ATT_BM;
+    return (size_t)((long long)B * H * (nq * (nq + 1) / 2) * DS_BLOCK_BYTES);
+}
 
 int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, const bf16* att,
                          const bf16* datt, const float* lse, float* delta, float* dQ, float* dK, float* dV, int B,
                          int H, int T, int hd, float scale, cudaStream_t stream, bf16* dqkv, const float* cos_t,
-                         const float* sin_t) {
+                         const float* sin_t, bf16* ds_blocks) {
     TB_CHECK(hd > 0 && hd <= ATT_HD && hd % 8 == 0, "fused attention needs head_dim <= 64 and a multiple of 8 (got %d)", hd);
     TB_CHECK(dqkv != nullptr ? (cos_t && sin_t && (reinterpret_cast<uintptr_t>(dqkv) & 15u) == 0) : (dQ && dK && dV),
              "attention backward needs either dQ, dK, dV or the merged output with the rotation tables");
@@ -981,6 +894,12 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
     p.lse = lse; p.delta = delta; p.dQ = dQ; p.dK = dK; p.dV = dV; p.err = ctx->d_err;
     p.dqkv = dqkv; p.cos_t = cos_t; p.sin_t = sin_t;
+    if (ds_blocks == nullptr) {      // no caller-owned buffer for the dS blocks: the context's scratch
+        TB_TRY(ensure_scratch(ctx, attention_bwd_ds_bytes(B, H, T)));
+        ds_blocks = reinterpret_cast<bf16*>(ctx->scratch);
+    }
+    TB_CHECK((reinterpret_cast<uintptr_t>(ds_blocks) & 15u) == 0, "the dS block buffer must be 16-byte aligned");
+    p.ds = ds_blocks;
     static bool attr_set[64] = {false};
     if (!attr_set[ctx->device & 63]) {
         TB_CUDA(cudaFuncSetAttribute(attention_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_DKDV_SMEM));
@@ -1004,8 +923,8 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
-    prof_mark(ctx, "attention_bwd_dq", 3.0 * tri, (double)BH * T * hd * (2.0 * 4 + 4.0), stream);
-    TB_CUDA(launch_kernel(attention_bwd_dq_kernel, dim3(grid), dim3(ATT_BWD_THREADS), ATT_DQ_SMEM, stream, tmQ, tmK, tmV, tmdO, tmoQ, p));
+    prof_mark(ctx, "attention_bwd_dq", 1.0 * tri, (double)BH * T * hd * (2.0 * 4 + 4.0), stream);
+    TB_CUDA(launch_kernel(attention_bwd_dq_kernel, dim3(grid), dim3(ATT_DQ_THREADS), ATT_DQ_SMEM, stream, tmK, tmoQ, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
@@ -1048,8 +967,3 @@ int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
 
 }  // namespace tb
 
-#ifdef TB_ATT_DEBUG
-extern "C" int tb_debug_att_read(long long* host) {
-    return (int)cudaMemcpyFromSymbol(host, tb::g_att_dbg, sizeof(tb::g_att_dbg));
-}
-#endif

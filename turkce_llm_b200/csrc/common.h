@@ -165,9 +165,12 @@ int launch_attention_fwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
 int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf16* V, const bf16* att,
                          const bf16* datt, const float* lse, float* delta, float* dQ, float* dK, float* dV, int B,
                          int H, int T, int hd, float scale, cudaStream_t stream, bf16* dqkv = nullptr,
-                         const float* cos_t = nullptr, const float* sin_t = nullptr);
+                         const float* cos_t = nullptr, const float* sin_t = nullptr, bf16* ds_blocks = nullptr);
 // (dqkv given: the gradients leave merged as bf16 [B*T, 3*H*hd] with the inverse rotation of the position
-//  embedding applied to dQ and dK; dQ, dK, dV are then unused and may be NULL)
+//  embedding applied to dQ and dK; dQ, dK, dV are then unused and may be NULL.
+//  ds_blocks: attention_bwd_ds_bytes(B, H, T) bytes through which the dK/dV kernel hands the dS blocks to the dQ
+//  kernel (lower-triangular 128 x 128 blocks, bf16); NULL = the context's growable scratch)
+size_t attention_bwd_ds_bytes(int B, int H, int T);
 
 // ---- operand packing (pack.cu)
 // float32 [rows, cols] -> float32 copy with another leading dimension (makes a matrix TMA-addressable)

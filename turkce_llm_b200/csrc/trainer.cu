@@ -101,6 +101,7 @@ struct TbTrainer {
     bool tf32 = false;
     float *nf32 = nullptr, *dlogits32 = nullptr, *dgu32 = nullptr, *dqkv32 = nullptr, *att32 = nullptr;
     float* att_delta = nullptr;
+    bf16* att_ds = nullptr;        // dS blocks on their way from the dK/dV kernel to the dQ kernel
     bool owns_stream = false;
 };
 
@@ -324,7 +325,7 @@ int backward_layer(TbTrainer* g, int l) {
     if (g->fused_attention) {
         // dQ, dK, dV leave the kernels rotated back and merged as bf16 dqkv [N, 3D]
         TB_TRY(launch_attention_bwd(c, a.Q, a.K, a.V, a.att, g->datt, a.lse, g->att_delta, nullptr, nullptr, nullptr, B,
-                                    H, T, hd, g->scale, st, g->dqkv, g->cos_t, g->sin_t));
+                                    H, T, hd, g->scale, st, g->dqkv, g->cos_t, g->sin_t, g->att_ds));
     } else {
     TB_TRY(launch_heads_split(c, g->datt, g->dO, B, T, H, hd, st));
     {   // dV = P^T dO
@@ -598,6 +599,7 @@ int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, i
     TB_TRY(dalloc(g, &g->qkv, N * 3 * D));
     if (g->fused_attention) {
         TB_TRY(dalloc(g, &g->att_delta, BHT));
+        TB_TRY(dalloc(g, &g->att_ds, attention_bwd_ds_bytes(B, H, T) / sizeof(bf16)));
     } else {
         TB_TRY(dalloc(g, &g->S, BHT * Tp)); TB_TRY(dalloc(g, &g->dP, BHT * Tp));
     }
