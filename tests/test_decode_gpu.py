@@ -336,3 +336,38 @@ def test_lean_decode_step_matches_general_step(tb, oracle, monkeypatch):
         outs.append(dec.logits())
         dec.destroy()
     assert rel_to_maxabs(outs[1], outs[0]) <= 2e-2
+
+
+@pytest.mark.parametrize("dims", [(500, 256, 4, 3, 1024, 64, 9, 6), (300, 128, 2, 2, 256, 5, 20, 6),
+                                  (31769, 384, 6, 12, 1024, 64, 16, 4)])
+def test_one_kernel_decode_step_matches_launch_per_kernel_step(tb, oracle, monkeypatch, dims):
+    """The default decode step runs every layer in one cooperative kernel (three launches per token with the final
+    norm and the head); TB_DECODE_NO_MEGA=1 selects the launch-per-kernel step.  Same bf16 operands and the same
+    RMSNorm summation order, so the logits differ only by the accumulation order of the products."""
+    from turkce_llm_b200 import lib
+    from turkce_llm_b200.decode import Decoder
+    V, D, H, L, F, S, prompt_len, n_new = dims
+    p = make_params(oracle, (V, D, H, L, F, 1, 1, 1e-5), 5)
+    prompts = np.random.default_rng(6).integers(0, V, (S, prompt_len)).astype(np.uint32)
+    outs, toks, launches = [], [], []
+    for mega in (True, False):
+        if not mega:
+            monkeypatch.setenv("TB_DECODE_NO_MEGA", "1")
+        dec = Decoder(V, D, H, L, F, S, prompt_len + n_new + 2)
+        dec.upload(p)
+        dec.prefill(prompts)
+        dec.generate(1)                      # (the first step of a decoder runs outside a graph)
+        before = lib.launch_count()
+        dec.generate(n_new - 1)
+        launches.append((lib.launch_count() - before) // (n_new - 1))
+        outs.append(dec.logits())
+        toks.append(dec.tokens(n_new + 1))
+        dec.destroy()
+    assert launches[0] <= 4 and launches[1] > 5 * L, launches
+    # a sequence whose greedy choice fell the other way at a near-tie sees other inputs from then on: compare the rest
+    same_so_far = (toks[0][:, :-1] == toks[1][:, :-1]).all(axis=1)
+    assert same_so_far.mean() >= 0.8, same_so_far.mean()
+    assert rel_to_maxabs(outs[0][same_so_far], outs[1][same_so_far]) <= 1e-2
+    srt = np.sort(outs[1], axis=1)
+    clear = (srt[:, -1] - srt[:, -2]) > 2e-2 * np.abs(outs[1]).max()
+    assert np.array_equal(toks[0][same_so_far & clear, -1], toks[1][same_so_far & clear, -1])

@@ -172,6 +172,18 @@ int launch_attention_bwd(DeviceCtx* ctx, const bf16* Q, const bf16* K, const bf1
 //  kernel (lower-triangular 128 x 128 blocks, bf16); NULL = the context's growable scratch)
 size_t attention_bwd_ds_bytes(int B, int H, int T);
 
+// ---- the decode step of all layers as one cooperative kernel (decode_mega.cu)
+struct DecodeMega;
+bool decode_mega_supported(const DeviceCtx* ctx, int S, int D, int H, int F, int cap);
+int decode_mega_create(DeviceCtx* ctx, DecodeMega** out, int S, int D, int H, int F, int L, int cap, float eps, float scale);
+void decode_mega_destroy(DecodeMega* m);
+// slab copies of the weights + the per-layer pointer table; offsets = the flat parameter offsets (embedding first)
+int decode_mega_set_weights(DeviceCtx* ctx, DecodeMega* m, const float* params, const bf16* params16, const long long* offsets,
+                            bf16* const* Kc, bf16* const* Vc, cudaStream_t st);
+// x (float32 [S, D]) = the last layer's output for the tokens tok at position *pos; K and V rows appended to the caches
+int launch_decode_mega(DeviceCtx* ctx, DecodeMega* m, const uint32_t* tok, const int* pos, const float* cos_t, const float* sin_t,
+                       float* x, float* x2, float* qkv, bf16* att, bf16* h, cudaStream_t st);
+
 // ---- operand packing (pack.cu)
 // float32 [rows, cols] -> float32 copy with another leading dimension (makes a matrix TMA-addressable)
 int launch_copy_f32(DeviceCtx* ctx, const float* src, float* dst, int rows, int cols, long long ld_src,

@@ -44,6 +44,7 @@ struct TbDecoder {
     bf16 *n = nullptr, *att = nullptr, *h = nullptr, *Q = nullptr;
     uint32_t *ids = nullptr, *tok = nullptr, *out = nullptr;
     int* pos = nullptr;
+    DecodeMega* mega = nullptr;                // decode step of all layers as one cooperative kernel (default when the shape fits)
     bool lean_step = false;                    // decode step on decode_linear_kernel (norm / SwiGLU / residual fused)
     bool fused_head = false;                   // LM head with the greedy choice fused (no logits in HBM)
     unsigned long long* head_best = nullptr;   // packed per-sequence maxima of the fused head (zero between launches)
@@ -134,6 +135,11 @@ int decode_step_body(TbDecoder* g) {
     DeviceCtx* c = g->ctx; cudaStream_t st = g->stream;
     const int S = g->S, D = g->D, H = g->H, hd = g->hd;
     const bool split_rope = getenv("TB_DECODE_SPLIT_ROPE") != nullptr;    // the two-kernel form, for comparison
+    if (g->mega) {
+        // all layers in one cooperative kernel (embedding gather included), then the head as usual
+        TB_TRY(launch_decode_mega(c, g->mega, g->tok, g->pos, g->cos_t, g->sin_t, g->x, g->x2, g->qkv, g->att, g->h, st));
+        return head(g, g->x, S, 1);
+    }
     TB_TRY(launch_embed_fwd(c, P32(g, 0), g->tok, g->x, S, D, st));
     for (int l = 0; l < g->L; ++l) {
         if (g->lean_step) {
@@ -209,6 +215,10 @@ int tb_decoder_create(TbDecoder** out, int V, int D, int H, int L, int F, int ma
     g->lean_step = getenv("TB_DECODE_LEAN") != nullptr && getenv("TB_DECODE_SPLIT_ROPE") == nullptr &&
                    decode_linear_supported((int)S, 3 * D, D, false) && decode_linear_supported((int)S, D, D, false) &&
                    decode_linear_supported((int)S, 2 * F, D, true) && decode_linear_supported((int)S, D, F, false) && D % 4 == 0;
+    // One cooperative kernel for the layers of a decode step (TB_DECODE_NO_MEGA=1: the launch-per-kernel path)
+    if (L > 0 && getenv("TB_DECODE_NO_MEGA") == nullptr && !g->lean_step &&
+        decode_mega_supported(g->ctx, (int)S, D, H, F, max_len))
+        TB_TRY(decode_mega_create(g->ctx, &g->mega, (int)S, D, H, F, L, max_len, eps, g->scale));
     if (g->fused_head) {
         TB_TRY(dalloc(g, &g->head_best, 64)); TB_CUDA(cudaMemset(g->head_best, 0, 64 * sizeof(unsigned long long)));
         TB_TRY(dalloc(g, &g->head_ticket, 1)); TB_CUDA(cudaMemset(g->head_ticket, 0, sizeof(unsigned int)));
@@ -243,6 +253,7 @@ int tb_decoder_destroy(TbDecoder* g) {
     cudaDeviceSynchronize();
     if (g->step_graph) cudaGraphExecDestroy(g->step_graph);
     for (void* p : g->allocs) cudaFree(p);
+    decode_mega_destroy(g->mega);
     cudaFreeHost(g->h_pinned);
     delete g;
     return 0;
@@ -255,6 +266,9 @@ int tb_decoder_upload(TbDecoder* g, const float* h_flat) {
     TB_H2D_SYNC(g->params, h_flat, (size_t)g->total * 4);
     TB_CHECK(g->total < (1LL << 31), "model too large for the single-row pack");
     TB_TRY(launch_pack_bf16(g->ctx, g->params, g->params16, 1, (int)g->total, g->total, g->total, 1, 0, 0, g->stream));
+    if (g->mega)
+        TB_TRY(decode_mega_set_weights(g->ctx, g->mega, g->params, g->params16, g->offsets.data(), g->Kc.data(), g->Vc.data(),
+                                       g->stream));
     TB_CUDA(cudaStreamSynchronize(g->stream));
     return 0;
 }
@@ -316,7 +330,8 @@ int tb_decoder_generate(TbDecoder* g, int n) {
     TB_CUDA(cudaSetDevice(g->device));
     TB_CHECK(g->generated >= 1, "tb_decoder_generate: call tb_decoder_prefill first");
     TB_CHECK(g->prompt_len + g->generated + n <= g->cap + 1, "cache capacity %d exceeded", g->cap);
-    const bool use_graph = getenv("TB_NO_GRAPH") == nullptr && !g->ctx->prof_on;
+    // (with the one-kernel step there are three launches per token: nothing for a graph to save)
+    const bool use_graph = getenv("TB_NO_GRAPH") == nullptr && !g->ctx->prof_on && g->mega == nullptr;
     for (int i = 0; i < n; ++i) {
         if (!use_graph || g->step_state == 0) {
             TB_TRY(decode_step_body(g));
