@@ -37,6 +37,7 @@ struct MegaLayer {
     const float *attn_norm, *bqkv, *bo, *ffn_norm, *bgu, *bdown;
     const bf16 *wqkv, *wo, *wgu, *wdown;          // slab layout
     bf16 *Kc, *Vc;                                  // [S, H, cap, hd]
+    const CUtensorMap *mapK, *mapV;                 // (hd, cap, S*H) views of the caches: 64-row boxes, 128B swizzle
 };
 
 struct MegaParams {
@@ -217,52 +218,67 @@ __device__ __forceinline__ void slab_product(const bf16* Xs, const bf16* Ws, int
 }
 
 // ---- rotary embedding of the new q and k, cache append, attention over the cache ------------------------------
-// The arithmetic of rope_attn_decode_kernel (the launch-per-kernel path), for up to three (sequence, head) pairs at
-// a time: a CTA has ~2.6 pairs per layer, and one pair alone is a chain of four dependent memory round trips (new
-// row, keys, values, result) that 256 threads cannot hide.  Every stage runs for all pairs before the next begins.
-// When the cache rows of the pairs fit into shared memory (3 * cap * head_dim bf16), they come in by bulk copies:
-// the keys of the first three pairs are requested before the grid barrier in front of this phase (rows written by
-// earlier steps do not depend on this one), the values while the softmax runs; rows read by the threads themselves
-// with 16-byte loads arrived at 16 bytes per clock and SM.  head_dim <= 64.
+// The function of rope_attn_decode_kernel (the launch-per-kernel path) for up to three (sequence, head) pairs of a
+// CTA at a time.  The cache rows of the pairs are brought into shared memory by TMA (64-row boxes, 128B swizzle):
+// the keys of the first pairs are requested before the grid barrier in front of this phase (rows written by earlier
+// steps do not depend on this one), the values while the softmax runs.  Scores and the weighted sum of the values are
+// warp-level mma.sync products over those tiles -- as SIMT loops they took ~5,000 cycles each for 3 x 256 keys.
+// The float32 operand of each product (q, then the exponentials) enters as a bf16 pair hi + lo in two columns / rows
+// of the fragment, so the products keep float32 accuracy on that side (the cache rows are bf16 anyway).
 constexpr int ATT_ITEMS = 3;
-constexpr int ATT_VG = 32;                 // key groups of the value pass (256 threads / 8 column groups of 8)
+constexpr int KV_BOX_ROWS = 64;
+constexpr int KV_BOX_BYTES = KV_BOX_ROWS * 128;
 
 struct AttSmem {
-    float* scratch;        // per pair: q [hd] | pr [cap] | red [32] | part [32][hd] | vnew [hd]
-    bf16* kv;              // [ATT_ITEMS][cap][hd] staged cache rows, or nullptr (rows read from global memory)
+    float* scratch;        // per pair: q [hd] | pr [cap rounded up to 16] | red [32] | vnew [hd] | e_hi, e_lo [cap16 bf16 each]
+    uint8_t* tiles;        // [items][blocks][64 rows x 128 B] staged cache rows, 1024-byte aligned
     uint64_t* bar;         // staged rows have landed
+    int items;             // pairs per round (1 .. ATT_ITEMS): what fits
+    int blocks;            // boxes per pair: ceil(cap / 64)
 };
-__host__ __device__ inline int att_per_floats(int hd, int cap) { return hd + cap + 32 + ATT_VG * hd + hd; }
+__host__ __device__ inline int att_cap16(int cap) { return (cap + 15) & ~15; }
+__host__ __device__ inline int att_per_floats(int hd, int cap) { return hd + att_cap16(cap) + 32 + hd + att_cap16(cap); }
 
-// requests rows [0, t) of the keys (or values) of the pairs
-__device__ __forceinline__ void begin_cache_rows(const AttSmem& a, bf16* const* src, int n, int t, int cap, int hd) {
-    if (t <= 0) return;
-    if (threadIdx.x == 0) mbar_expect_tx(a.bar, (uint32_t)(n * t * hd * 2));
-    if ((int)threadIdx.x < n) bulk_load(a.kv + (size_t)threadIdx.x * cap * hd, src[threadIdx.x], (uint32_t)(t * hd * 2), a.bar);
+// byte address of (row r, 16-byte piece j) of a pair's tile
+__device__ __forceinline__ const uint8_t* tile_piece(const uint8_t* tile, int r, int j) {
+    return tile + (r >> 6) * KV_BOX_BYTES + (r & 63) * 128 + ((j ^ (r & 7)) << 4);
+}
+
+// requests the boxes that hold rows [0, rows) of the keys (or values) of the pairs.  rows = position + 1 rounded up to
+// 16: the products read whole 16-row tiles, so the rows behind the newest one must hold finite numbers (the cache
+// is zero-filled at creation and only ever holds finite values; rows past its end are zero-filled by the copy)
+__device__ __forceinline__ void begin_cache_tiles(const AttSmem& a, const CUtensorMap* map, const int* items, int n, int rows) {
+    const int nblk = (rows + KV_BOX_ROWS - 1) / KV_BOX_ROWS;
+    if (threadIdx.x == 0) mbar_expect_tx(a.bar, (uint32_t)(n * nblk * KV_BOX_BYTES));
+    if ((int)threadIdx.x < n * nblk) {
+        const int i = threadIdx.x / nblk, blk = threadIdx.x % nblk;
+        tma_load_3d(a.tiles + ((size_t)i * a.blocks + blk) * KV_BOX_BYTES, map, a.bar, 0, blk * KV_BOX_ROWS, items[i]);
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float x, float y) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// x = hi + lo with hi = bf16(x), lo = bf16(x - hi)
+__device__ __forceinline__ void split_bf16(float x, float& hi, float& lo) {
+    hi = __bfloat162float(__float2bfloat16_rn(x));
+    lo = x - hi;
 }
 
 // returns false when a bounded wait gave up
 __device__ bool attend_items(const MegaParams& p, const MegaLayer& ly, const int* items, int n, int t, const AttSmem& a,
                              bool keys_requested, uint32_t& parity, volatile int* abort_sh) {
-    const int hd = p.hd, H = p.H, cap = p.cap, D = H * hd, half = hd >> 1, hd8 = hd >> 3;
-    const int L = t + 1;
+    const int hd = p.hd, H = p.H, D = H * hd, half = hd >> 1;
+    const int L = t + 1, L16 = (L + 15) & ~15;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int per = att_per_floats(hd, cap);
+    const int per = att_per_floats(hd, p.cap), cap16 = att_cap16(p.cap);
     float* sh = a.scratch;
-    const bool staged = a.kv != nullptr;
-    bf16* Kb[ATT_ITEMS]; bf16* Vb[ATT_ITEMS];
-    const bf16* Ks[ATT_ITEMS]; const bf16* Vs[ATT_ITEMS];          // where the stages read the rows from
-#pragma unroll
-    for (int i = 0; i < ATT_ITEMS; ++i) {
-        const int it = i < n ? items[i] : items[0];
-        Kb[i] = ly.Kc + (long long)it * cap * hd;            // it = sq * H + h
-        Vb[i] = ly.Vc + (long long)it * cap * hd;
-        Ks[i] = staged ? a.kv + (size_t)i * cap * hd : Kb[i];
-        Vs[i] = staged ? a.kv + (size_t)i * cap * hd : Vb[i];
-    }
-    __syncthreads();                                         // the scratch of the previous pairs is no longer read
-    if (staged && !keys_requested) begin_cache_rows(a, Kb, n, t, cap, hd);
+    fence_proxy_async();                                     // (row t of the previous pairs' tiles was an ordinary store)
+    __syncthreads();                                         // the scratch and tiles of the previous pairs are no longer read
+    if (!keys_requested) begin_cache_tiles(a, ly.mapK, items, n, L16);
     // rotary embedding of the new q and k, new cache row: pair i on threads [i * half, (i + 1) * half)
+    __nv_bfloat162 kn = __floats2bfloat162_rn(0.f, 0.f);
     {
         const int i = tid / half, k = tid % half;
         if (i < n) {
@@ -275,68 +291,83 @@ __device__ bool attend_items(const MegaParams& p, const MegaLayer& ly, const int
             float* q = sh + i * per;
             q[2 * k] = qq.x * c - qq.y * sn;
             q[2 * k + 1] = qq.x * sn + qq.y * c;
-            const long long o = (long long)t * hd + 2 * k;
-            const __nv_bfloat162 kn = __floats2bfloat162_rn(kk.x * c - kk.y * sn, kk.x * sn + kk.y * c);
+            const long long o = (long long)items[i] * p.cap * hd + (long long)t * hd + 2 * k;
+            kn = __floats2bfloat162_rn(kk.x * c - kk.y * sn, kk.x * sn + kk.y * c);
             const __nv_bfloat162 vn = __floats2bfloat162_rn(v.x, v.y);
-            *reinterpret_cast<__nv_bfloat162*>(Kb[i] + o) = kn;
-            *reinterpret_cast<__nv_bfloat162*>(Vb[i] + o) = vn;
-            if (staged) {                                    // row t of the staged copies: the keys now, the values later
-                *reinterpret_cast<__nv_bfloat162*>(a.kv + (size_t)i * cap * hd + o) = kn;
-                *reinterpret_cast<__nv_bfloat162*>(sh + i * per + per - hd + k) = vn;      // vnew, as bf16 pairs
+            *reinterpret_cast<__nv_bfloat162*>(ly.Kc + o) = kn;
+            *reinterpret_cast<__nv_bfloat162*>(ly.Vc + o) = vn;
+            *reinterpret_cast<__nv_bfloat162*>(sh + i * per + hd + cap16 + 32 + k) = vn;      // vnew, as bf16 pairs
+        }
+        // the weights behind the last key take part in the value product: zero
+        for (int j = tid; j < n * 16; j += MEGA_THREADS) {
+            const int ii = j >> 4, l = L16 - 16 + (j & 15);
+            bf16* ehi = reinterpret_cast<bf16*>(sh + ii * per + hd + cap16 + 32 + hd);
+            if (l >= L) { ehi[l] = __float2bfloat16_rn(0.0f); ehi[cap16 + l] = __float2bfloat16_rn(0.0f); }
+        }
+    }
+    if (!mbar_wait(a.bar, parity, abort_sh)) return false;
+    parity ^= 1u;
+    // row t of the key tiles is this step's: written after the copy (whose box may cover it with the old contents)
+    {
+        const int i = tid / half, k = tid % half;
+        if (i < n)
+            *reinterpret_cast<__nv_bfloat162*>(const_cast<uint8_t*>(tile_piece(a.tiles + (size_t)i * a.blocks * KV_BOX_BYTES, t, k >> 2)) + (k & 3) * 4) = kn;
+    }
+    __syncthreads();
+    // scores: s[l] = scale * <q, K[l]>, one mma tile = 16 keys; columns 0 | 1 of the B fragment hold q_hi | q_lo
+    // (built once per pair: lanes 0-3 hold column 0, lanes 4-7 column 1, the other columns are zero)
+    const int mtiles = L16 >> 4;
+    uint32_t bq[ATT_ITEMS][4][2];
+    {
+        // every lane computes (without branches, so that the twelve short chains overlap); lanes 8-31 keep zeros
+        const int k0 = (lane & 3) * 2;
+#pragma unroll
+        for (int i = 0; i < ATT_ITEMS; ++i) {
+            const float* q = sh + (i < n ? i : 0) * per;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const int kk = ks < (hd >> 4) ? ks * 16 + k0 : k0;
+                float h0, l0, h1, l1, h8, l8, h9, l9;
+                split_bf16(q[kk], h0, l0); split_bf16(q[kk + 1], h1, l1);
+                split_bf16(q[kk + 8], h8, l8); split_bf16(q[kk + 9], h9, l9);
+                const uint32_t hi0 = pack_bf16(h0, h1), lo0 = pack_bf16(l0, l1);
+                const uint32_t hi8 = pack_bf16(h8, h9), lo8 = pack_bf16(l8, l9);
+                bq[i][ks][0] = lane < 4 ? hi0 : lane < 8 ? lo0 : 0u;
+                bq[i][ks][1] = lane < 4 ? hi8 : lane < 8 ? lo8 : 0u;
             }
         }
     }
-    __syncthreads();                                         // the new rows are visible to the whole block
-    if (staged && t > 0) {
-        if (!mbar_wait(a.bar, parity, abort_sh)) return false;
-        parity ^= 1u;
-    }
-    // scores: thread = key.  Staged rows are read with the 16-byte pieces rotated by the row number, so that the eight
-    // threads of a quarter warp touch different banks (rows are 64 or 128 bytes apart)
-    const int rot_shift = hd8 == 8 ? 0 : 1;                  // rows per 128 bytes: 1 (head_dim 64) or 2 (32)
-    const bool rotate = staged && (hd8 == 8 || hd8 == 4);
     float mx[ATT_ITEMS];
 #pragma unroll
     for (int i = 0; i < ATT_ITEMS; ++i) mx[i] = -3.0e38f;
-    for (int l0 = 0; l0 < L; l0 += MEGA_THREADS) {
-        const int l = l0 + tid;
-        const int rot = rotate ? (l >> rot_shift) : 0;
-        uint4 kv[ATT_ITEMS][8];
+    // the pairs of a key tile are worked on together: their products are independent chains
+    for (int mt = warp; mt < mtiles; mt += MEGA_THREADS / 32) {
+        float acc[ATT_ITEMS][4];
 #pragma unroll
-        for (int i = 0; i < ATT_ITEMS; ++i)
+        for (int i = 0; i < ATT_ITEMS; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
+        const int r = mt * 16 + (lane & 15);
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                if (i < n && l < L && c < hd8) {
-                    const int cc = rotate ? ((c + rot) & (hd8 - 1)) : c;
-                    kv[i][c] = *reinterpret_cast<const uint4*>(Ks[i] + (long long)l * hd + cc * 8);
-                }
+        for (int ks = 0; ks < 4; ++ks) {
+            if (ks < (hd >> 4)) {
 #pragma unroll
-        for (int i = 0; i < ATT_ITEMS; ++i) {
-            if (i < n && l < L) {
-                const float* q = sh + i * per;
-                float part[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    part[c] = 0.0f;
-                    if (c < hd8) {
-                        const int cc = rotate ? ((c + rot) & (hd8 - 1)) : c;
-                        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv[i][c]);
-                        float s8 = 0.0f;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 f = __bfloat1622float2(k2[e]);
-                            s8 += q[cc * 8 + 2 * e] * f.x;
-                            s8 += q[cc * 8 + 2 * e + 1] * f.y;
-                        }
-                        part[c] = s8;
+                for (int i = 0; i < ATT_ITEMS; ++i) {
+                    if (i < n) {
+                        uint32_t af[4];
+                        ldmatrix_x4(af, tile_piece(a.tiles + (size_t)i * a.blocks * KV_BOX_BYTES, r, ks * 2 + (lane >> 4)));
+                        mma_bf16(acc[i], af, bq[i][ks]);
                     }
                 }
-                float s = 0.0f;
+            }
+        }
+        if ((lane & 3) == 0) {
+            const int r0 = mt * 16 + (lane >> 2), r1 = r0 + 8;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) s += part[c];
-                s *= p.scale;
-                sh[i * per + hd + l] = s;
-                mx[i] = fmaxf(mx[i], s);
+            for (int i = 0; i < ATT_ITEMS; ++i) {
+                if (i < n) {
+                    const float s0 = (acc[i][0] + acc[i][1]) * p.scale, s1 = (acc[i][2] + acc[i][3]) * p.scale;
+                    if (r0 < L) { sh[i * per + hd + r0] = s0; mx[i] = fmaxf(mx[i], s0); }
+                    if (r1 < L) { sh[i * per + hd + r1] = s1; mx[i] = fmaxf(mx[i], s1); }
+                }
             }
         }
     }
@@ -345,21 +376,16 @@ __device__ bool attend_items(const MegaParams& p, const MegaLayer& ly, const int
     for (int i = 0; i < ATT_ITEMS; ++i) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], o));
-        if (lane == 0) sh[i * per + hd + cap + warp] = mx[i];
+        if (lane == 0) sh[i * per + hd + cap16 + warp] = mx[i];
     }
-    __syncthreads();                                         // every key row has been read
-    if (staged) {
-        // the values take the place of the keys: rows [0, t) by bulk copy while the softmax runs, row t from vnew
-        begin_cache_rows(a, Vb, n, t, cap, hd);
-        const int i = tid / half, k = tid % half;
-        if (i < n)
-            *reinterpret_cast<__nv_bfloat162*>(a.kv + (size_t)i * cap * hd + (long long)t * hd + 2 * k) =
-                *reinterpret_cast<const __nv_bfloat162*>(sh + i * per + per - hd + k);
-    }
+    fence_proxy_async();
+    __syncthreads();                                         // every key tile has been read
+    // the values take the place of the keys while the softmax runs
+    begin_cache_tiles(a, ly.mapV, items, n, L16);
     float sum[ATT_ITEMS];
 #pragma unroll
     for (int i = 0; i < ATT_ITEMS; ++i) {
-        const float* red = sh + i * per + hd + cap;
+        const float* red = sh + i * per + hd + cap16;
         float m = red[0];
         for (int w = 1; w < MEGA_THREADS / 32; ++w) m = fmaxf(m, red[w]);
         mx[i] = m;
@@ -369,74 +395,91 @@ __device__ bool attend_items(const MegaParams& p, const MegaLayer& ly, const int
 #pragma unroll
         for (int i = 0; i < ATT_ITEMS; ++i) {
             if (i < n) {
-                float* pr = sh + i * per + hd;
-                const float e = expf(pr[l] - mx[i]);
-                pr[l] = e;
+                const float e = expf(sh[i * per + hd + l] - mx[i]);
                 sum[i] += e;
+                float eh, el;
+                split_bf16(e, eh, el);
+                bf16* ehi = reinterpret_cast<bf16*>(sh + i * per + hd + cap16 + 32 + hd);
+                ehi[l] = __float2bfloat16_rn(eh);
+                ehi[cap16 + l] = __float2bfloat16_rn(el);
             }
         }
     }
 #pragma unroll
     for (int i = 0; i < ATT_ITEMS; ++i) {
         sum[i] = warp_sum_f(sum[i]);
-        if (lane == 0) sh[i * per + hd + cap + 16 + warp] = sum[i];
+        if (lane == 0) sh[i * per + hd + cap16 + 16 + warp] = sum[i];
+    }
+    if (!mbar_wait(a.bar, parity, abort_sh)) return false;
+    parity ^= 1u;
+    {
+        const int i = tid / half, k = tid % half;
+        if (i < n)
+            *reinterpret_cast<__nv_bfloat162*>(const_cast<uint8_t*>(tile_piece(a.tiles + (size_t)i * a.blocks * KV_BOX_BYTES, t, k >> 2)) + (k & 3) * 4) =
+                *reinterpret_cast<const __nv_bfloat162*>(sh + i * per + hd + cap16 + 32 + k);
     }
     __syncthreads();
-    if (staged && t > 0) {
-        if (!mbar_wait(a.bar, parity, abort_sh)) return false;
-        parity ^= 1u;
-    }
-    // values: thread = (key group g of 32, eight head-dim columns c8)
+    // out[d] = sum_l e[l] V[l][d] / sum_l e[l] as out^T = V^T e: the A fragment (16 head-dim columns x 16 keys) comes
+    // transposed out of the row-major value tile, columns 0 | 1 of the B fragment hold e_hi | e_lo.  (With e as the A
+    // operand only 2 of its 16 rows would be used and twice as many mma were needed; an mma.sync costs a warp ~100
+    // cycles here.)  The warps split the keys; their partial sums are added in warp order.
+    const int dtiles = hd >> 4;
     {
-        const int g = tid / hd8, c8 = (tid % hd8) * 8;
-        const int G = MEGA_THREADS / hd8 < ATT_VG ? MEGA_THREADS / hd8 : ATT_VG;       // 32 at head_dim 64
-        float acc[ATT_ITEMS][8];
+        float acc[ATT_ITEMS][4][4];
 #pragma unroll
         for (int i = 0; i < ATT_ITEMS; ++i)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[i][e] = 0.0f;
-        for (int l0 = g; l0 < L; l0 += 4 * G) {
-            uint4 vv[ATT_ITEMS][4];
+            for (int m = 0; m < 4; ++m) { acc[i][m][0] = acc[i][m][1] = acc[i][m][2] = acc[i][m][3] = 0.0f; }
+        for (int kt = warp; kt < mtiles; kt += MEGA_THREADS / 32) {
+            const int k0 = kt * 16 + (lane & 3) * 2;
+            const int key = kt * 16 + ((lane >> 4) << 3) + (lane & 7);
 #pragma unroll
-            for (int i = 0; i < ATT_ITEMS; ++i)
+            for (int i = 0; i < ATT_ITEMS; ++i) {
+                if (i < n) {
+                    const uint8_t* tile = a.tiles + (size_t)i * a.blocks * KV_BOX_BYTES;
+                    const bf16* ew = reinterpret_cast<const bf16*>(sh + i * per + hd + cap16 + 32 + hd) + (lane >= 4 ? cap16 : 0);
+                    uint32_t be[2] = {0u, 0u};
+                    if (lane < 8) {
+                        be[0] = *reinterpret_cast<const uint32_t*>(ew + k0);
+                        be[1] = *reinterpret_cast<const uint32_t*>(ew + k0 + 8);
+                    }
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (i < n && g < G && l0 + u * G < L) vv[i][u] = *reinterpret_cast<const uint4*>(Vs[i] + (long long)(l0 + u * G) * hd + c8);
-#pragma unroll
-            for (int i = 0; i < ATT_ITEMS; ++i)
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (i < n && g < G && l0 + u * G < L) {
-                        const float w = sh[i * per + hd + l0 + u * G];
-                        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vv[i][u]);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 f = __bfloat1622float2(v2[e]);
-                            acc[i][2 * e] += w * f.x;
-                            acc[i][2 * e + 1] += w * f.y;
+                    for (int m = 0; m < 4; ++m) {
+                        if (m < dtiles) {
+                            uint32_t av[4];
+                            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(av[0]), "=r"(av[1]), "=r"(av[2]), "=r"(av[3])
+                                         : "r"(smem_u32(tile_piece(tile, key, m * 2 + ((lane >> 3) & 1)))));
+                            mma_bf16(acc[i][m], av, be);
                         }
                     }
-        }
-#pragma unroll
-        for (int i = 0; i < ATT_ITEMS; ++i)
-            if (i < n && g < G) {
-                float* dst = sh + i * per + hd + cap + 32 + g * hd + c8;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) dst[e] = acc[i][e];
+                }
             }
+        }
+        // partial sums of this warp
+        float* part = sh + ATT_ITEMS * per;                   // [8 warps][ATT_ITEMS][hd], behind the pairs' scratch
+        if ((lane & 3) == 0) {
+#pragma unroll
+            for (int i = 0; i < ATT_ITEMS; ++i)
+#pragma unroll
+                for (int m = 0; m < 4; ++m)
+                    if (i < n && m < dtiles) {
+                        float* dst = part + (warp * ATT_ITEMS + i) * hd + m * 16 + (lane >> 2);
+                        dst[0] = acc[i][m][0] + acc[i][m][1];
+                        dst[8] = acc[i][m][2] + acc[i][m][3];
+                    }
+        }
     }
     __syncthreads();
-    // result: pair i, column d on thread i * hd + d; partial sums added in key-group order
     {
         const int i = tid / hd, d = tid % hd;
         if (i < n) {
-            const float* red = sh + i * per + hd + cap + 16;
+            const float* red = sh + i * per + hd + cap16 + 16;
             float tot = red[0];
             for (int w = 1; w < MEGA_THREADS / 32; ++w) tot += red[w];
-            const float* part = sh + i * per + hd + cap + 32;
-            const int G = MEGA_THREADS / hd8 < ATT_VG ? MEGA_THREADS / hd8 : ATT_VG;
-            float o = part[d];
-            for (int k = 1; k < G; ++k) o += part[k * hd + d];
+            const float* part = sh + ATT_ITEMS * per;
+            float o = part[i * hd + d];
+            for (int w = 1; w < MEGA_THREADS / 32; ++w) o += part[(w * ATT_ITEMS + i) * hd + d];
             const int sq = items[i] / H, h = items[i] % H;
             p.att[(long long)sq * (D + 8) + h * hd + d] = __float2bfloat16_rn(o / tot);
         }
@@ -453,17 +496,26 @@ __host__ __device__ inline size_t mega_fixed_bytes(int D, int F) {
     return (size_t)16 * (kmax + 8) * 2 + 2 * MEGA_ROWS * 16 * 4 + 48;       // Ws | Cs | flag, three mbarriers
 }
 __host__ __device__ inline size_t att_scratch_bytes(int hd, int cap) {
-    return ((size_t)ATT_ITEMS * att_per_floats(hd, cap) * 4 + 15) & ~(size_t)15;
+    return ((size_t)ATT_ITEMS * att_per_floats(hd, cap) + (size_t)(MEGA_THREADS / 32) * ATT_ITEMS * hd) * 4;    // + value partials
 }
-// the cache rows of three pairs are staged in shared memory when everything stays within 225 KB
-__host__ __device__ inline bool mega_kv_staged(int D, int F, int hd, int cap) {
-    return mega_fixed_bytes(D, F) + att_scratch_bytes(hd, cap) + (size_t)ATT_ITEMS * cap * hd * 2 <= 225 * 1024;
-}
-__host__ __device__ inline size_t mega_x_region_bytes(int D, int F, int hd, int cap) {
+__host__ __device__ inline int att_blocks(int cap) { return (att_cap16(cap) + KV_BOX_ROWS - 1) / KV_BOX_ROWS; }
+__host__ __device__ inline size_t mega_gemm_region_bytes(int D, int F) {
     const size_t tile_f = (size_t)MEGA_ROWS * (F + 8) * 2;
     const size_t norm = (size_t)MEGA_ROWS * (D + 8) * 2 + (size_t)MEGA_ROWS * D * 4;
-    const size_t att = att_scratch_bytes(hd, cap) + (mega_kv_staged(D, F, hd, cap) ? (size_t)ATT_ITEMS * cap * hd * 2 : 0);
-    size_t m = tile_f > norm ? tile_f : norm;
+    return tile_f > norm ? tile_f : norm;
+}
+// (sequence, head) pairs whose cache tiles fit beside the scratch (0: none -- the kernel is not used).  The tiles
+// start on a 1024-byte boundary, so a kilobyte of slack is counted.
+__host__ __device__ inline int mega_att_items(int D, int F, int hd, int cap) {
+    const size_t budget = 225 * 1024 - mega_fixed_bytes(D, F);
+    const size_t need0 = att_scratch_bytes(hd, cap) + 1024;
+    if (need0 >= budget) return 0;
+    const size_t n = (budget - need0) / ((size_t)att_blocks(cap) * KV_BOX_BYTES);
+    return n > ATT_ITEMS ? ATT_ITEMS : (int)n;
+}
+__host__ __device__ inline size_t mega_x_region_bytes(int D, int F, int hd, int cap) {
+    const size_t att = att_scratch_bytes(hd, cap) + 1024 + (size_t)mega_att_items(D, F, hd, cap) * att_blocks(cap) * KV_BOX_BYTES;
+    const size_t m = mega_gemm_region_bytes(D, F);
     return m > att ? m : att;
 }
 __host__ __device__ inline size_t mega_smem_bytes(int D, int F, int hd, int cap) {
@@ -485,8 +537,13 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
     float* stage = reinterpret_cast<float*>(Xs + MEGA_ROWS * KD);                  // float32 rows of the RMSNorm phases
     AttSmem att;                                                                   // the attention phase reuses the X region
     att.scratch = reinterpret_cast<float*>(Xs);
-    att.kv = mega_kv_staged(D, F, p.hd, p.cap) ? reinterpret_cast<bf16*>(reinterpret_cast<uint8_t*>(Xs) + att_scratch_bytes(p.hd, p.cap)) : nullptr;
+    {
+        const uint32_t after = smem_u32(Xs) + (uint32_t)att_scratch_bytes(p.hd, p.cap);
+        att.tiles = reinterpret_cast<uint8_t*>(Xs) + att_scratch_bytes(p.hd, p.cap) + ((1024u - (after & 1023u)) & 1023u);
+    }
     att.bar = bar_x + 2;
+    att.items = mega_att_items(D, F, p.hd, p.cap);
+    att.blocks = att_blocks(p.cap);
     volatile int* abort_sh = sh_flag + 1;
     const int tid = threadIdx.x;
     const int cta = blockIdx.x, ncta = gridDim.x;
@@ -529,32 +586,29 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
             __syncthreads();
         }
         if (cta < slabs_o) begin_w_slab(Ws, KD, ly.wo + (long long)cta * 8 * KD, 8, bar_w);       // for the phase after next
-        // the keys of this CTA's first (sequence, head) pairs: their rows of earlier steps can come in during the barrier
+        // the keys of this CTA's first (sequence, head) pairs: rows of earlier steps can come in during the barrier
         int items0[ATT_ITEMS];
         int n0 = 0;
 #pragma unroll
         for (int i = 0; i < ATT_ITEMS; ++i) {
             items0[i] = cta + i * ncta;
-            if (items0[i] < S * p.H) n0 = i + 1;
+            if (i < att.items && items0[i] < S * p.H) n0 = i + 1;
         }
-        if (att.kv != nullptr && n0 > 0) {
+        if (n0 > 0) {
             fence_proxy_async();                      // this phase's ordinary stores into the region come first
             __syncthreads();
-            bf16* src[ATT_ITEMS];
-#pragma unroll
-            for (int i = 0; i < ATT_ITEMS; ++i) src[i] = ly.Kc + (long long)(i < n0 ? items0[i] : items0[0]) * p.cap * p.hd;
-            begin_cache_rows(att, src, n0, t, p.cap, p.hd);
+            begin_cache_tiles(att, ly.mapK, items0, n0, (t + 16) & ~15);
         }
         if (!grid_barrier(p, nbar++, sh_flag)) return;
         // ------------------------------------------------------------- rotary + cache append + attention
         // (the out-projection weights requested above land in Ws, which this phase leaves alone)
-        for (int first = cta; first < S * p.H; first += ATT_ITEMS * ncta) {
+        for (int first = cta; first < S * p.H; first += att.items * ncta) {
             int items[ATT_ITEMS];
             int n = 0;
 #pragma unroll
             for (int i = 0; i < ATT_ITEMS; ++i) {
                 items[i] = first + i * ncta;
-                if (items[i] < S * p.H) n = i + 1;
+                if (i < att.items && items[i] < S * p.H) n = i + 1;
             }
             if (!attend_items(p, ly, items, n, t, att, first == cta, pk, abort_sh)) { atomicCAS(p.err, 0, 43); *abort_sh = 1; return; }
         }
@@ -656,6 +710,7 @@ struct DecodeMega {
     MegaLayer* d_layers = nullptr;
     bf16* wt = nullptr;
     bf16 *att = nullptr, *h = nullptr;         // [64][D + 8], [64][F + 8]
+    CUtensorMap* d_maps = nullptr;             // [L][2]: K and V cache views
     unsigned int* barrier = nullptr;
     size_t smem = 0;
     int grid = 0, nv = 0;
@@ -664,8 +719,9 @@ struct DecodeMega {
 bool decode_mega_supported(const DeviceCtx* ctx, int S, int D, int H, int F, int cap) {
     const int hd = H > 0 ? D / H : 0;
     if (S < 1 || S > MEGA_ROWS || D % 128 != 0 || D > 1024 || F % 32 != 0 || F > 1024) return false;
-    if (hd < 8 || hd > 64 || hd % 8 != 0 || cap > 8192) return false;
-    if (MEGA_THREADS / (hd / 2) < ATT_ITEMS || MEGA_THREADS / hd < ATT_ITEMS) return false;     // thread ranges of the pairs
+    if (hd < 16 || hd > 64 || hd % 16 != 0) return false;                       // k-steps of 16 head-dim columns
+    if (MEGA_THREADS / hd < ATT_ITEMS) return false;                            // thread ranges of the pairs
+    if (mega_att_items(D, F, hd, cap) < 1 || ATT_ITEMS * att_blocks(cap) > MEGA_THREADS) return false;
     return mega_smem_bytes(D, F, hd, cap) <= 225 * 1024 && ctx->sm_count >= 8;
 }
 
@@ -685,6 +741,7 @@ int decode_mega_create(DeviceCtx* ctx, DecodeMega** out, int S, int D, int H, in
     TB_CUDA(cudaMalloc(&m->wt, decode_mega_weight_scalars(D, F, L > 0 ? L : 1) * sizeof(bf16)));
     TB_CUDA(cudaMalloc(&m->barrier, 256));
     TB_CUDA(cudaMemset(m->barrier, 0, 256));
+    TB_CUDA(cudaMalloc(&m->d_maps, sizeof(CUtensorMap) * 2 * (size_t)(L > 0 ? L : 1)));
     TB_CUDA(cudaMalloc(&m->att, (size_t)MEGA_ROWS * (D + 8) * sizeof(bf16)));
     TB_CUDA(cudaMemset(m->att, 0, (size_t)MEGA_ROWS * (D + 8) * sizeof(bf16)));
     TB_CUDA(cudaMalloc(&m->h, (size_t)MEGA_ROWS * (F + 8) * sizeof(bf16)));
@@ -697,7 +754,7 @@ int decode_mega_create(DeviceCtx* ctx, DecodeMega** out, int S, int D, int H, in
 
 void decode_mega_destroy(DecodeMega* m) {
     if (!m) return;
-    cudaFree(m->d_layers); cudaFree(m->wt); cudaFree(m->barrier); cudaFree(m->att); cudaFree(m->h);
+    cudaFree(m->d_layers); cudaFree(m->wt); cudaFree(m->barrier); cudaFree(m->att); cudaFree(m->h); cudaFree(m->d_maps);
     delete m;
 }
 
@@ -706,6 +763,7 @@ int decode_mega_set_weights(DeviceCtx* ctx, DecodeMega* m, const float* params, 
                             bf16* const* Kc, bf16* const* Vc, cudaStream_t st) {
     const int D = m->p.D, F = m->p.F, L = m->p.L;
     std::vector<MegaLayer> hl((size_t)(L > 0 ? L : 1));
+    std::vector<CUtensorMap> hmaps(2 * (size_t)(L > 0 ? L : 1));
     bf16* w = m->wt;
     for (int l = 0; l < L; ++l) {
         const long long* o = offsets + 1 + 10LL * l;
@@ -713,6 +771,9 @@ int decode_mega_set_weights(DeviceCtx* ctx, DecodeMega* m, const float* params, 
         y.attn_norm = params + o[0]; y.bqkv = params + o[2]; y.bo = params + o[4]; y.ffn_norm = params + o[5];
         y.bgu = params + o[7]; y.bdown = params + o[9];
         y.Kc = Kc[l]; y.Vc = Vc[l];
+        TB_TRY(make_operand_map(&hmaps[2 * l], Kc[l], m->p.hd, m->p.cap, m->p.hd, m->p.S * m->p.H, (long long)m->p.cap * m->p.hd, KV_BOX_ROWS));
+        TB_TRY(make_operand_map(&hmaps[2 * l + 1], Vc[l], m->p.hd, m->p.cap, m->p.hd, m->p.S * m->p.H, (long long)m->p.cap * m->p.hd, KV_BOX_ROWS));
+        y.mapK = m->d_maps + 2 * l; y.mapV = m->d_maps + 2 * l + 1;
         auto relayout = [&](const bf16* src, int K, int N, int pair_off, const bf16** dst) -> int {
             const long long total = (long long)(K + 8) * N;
             int blocks = (int)((total + 255) / 256);
@@ -728,6 +789,7 @@ int decode_mega_set_weights(DeviceCtx* ctx, DecodeMega* m, const float* params, 
         TB_TRY(relayout(params16 + o[6], D, 2 * F, F, &y.wgu));
         TB_TRY(relayout(params16 + o[8], F, D, 0, &y.wdown));
     }
+    TB_CUDA(cudaMemcpyAsync(m->d_maps, hmaps.data(), sizeof(CUtensorMap) * hmaps.size(), cudaMemcpyHostToDevice, st));
     TB_CUDA(cudaMemcpyAsync(m->d_layers, hl.data(), sizeof(MegaLayer) * hl.size(), cudaMemcpyHostToDevice, st));
     TB_CUDA(cudaStreamSynchronize(st));          // hl goes out of scope
     m->p.embed = params;

@@ -200,7 +200,10 @@ class DataParallel:
         self.g = trainer
         self._lib = lib.load()
         if mode is None:
-            mode = {"sharded": SHARDED, "overlap": OVERLAP}.get(os.environ.get("TB_DP_MODE", "allreduce"), ALLREDUCE)
+            # TB_DP_MODE = allreduce | sharded | overlap.  Unset: the sharded optimiser from four ranks on (measured at 8
+            # GPUs: 5.78 ms per step against 5.86 with the all-reduce; the two are equal at 2 GPUs), else one all-reduce.
+            name = os.environ.get("TB_DP_MODE", "sharded" if world >= 4 else "allreduce")
+            mode = {"sharded": SHARDED, "overlap": OVERLAP}.get(name, ALLREDUCE)
         uid = None
         if world > 1:
             buf = (C.c_ubyte * 128)()
