@@ -687,7 +687,7 @@ def bench_c3():
     return {"workload": "B=16, H=6, T=1024, head dim 64, bf16; q, k, v ~ N(0,1), seed 2",
             "fwd": {"us": round(f_us, 1), "causal_useful_tflops": round(f_tf, 1), "frac_of_burst_bf16_peak": round(f_tf / pk["burst"], 4)},
             "bwd": {"us": round(b_us, 1), "causal_useful_tflops": round(b_tf, 1), "frac_of_burst_bf16_peak": round(b_tf / pk["burst"], 4),
-                    "kernels": "delta + dK/dV + dQ (S is recomputed: 5 triangular products)"},
+                    "kernels": "delta + dK/dV + dQ (dS blocks handed from the dK/dV kernel to the dQ kernel: 5 triangular products)"},
             "algorithmic_mb_fwd": round(4 * B * H * T * hd * 2 / 1e6, 1),
             "timing": "device time per call inside a CUDA graph, 4 operand sets in rotation (252 MB > L2)"}
 
