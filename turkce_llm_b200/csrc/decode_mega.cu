@@ -129,13 +129,13 @@ __device__ __forceinline__ void begin_x_f32(float* stage, const MegaParams& p, c
 }
 
 // RMSNorm of the staged rows -> bf16 Xs.  The summation order is the one of rmsnorm_fwd_vec_kernel: lane owns columns
-// 4 * (lane + 32 k), k ascending, then the butterfly.  A warp works on four rows at a time: one row is a chain of
+// 4 * (lane + 32 k), k ascending, then the butterfly.  A warp works on its eight rows at once: one row is a chain of
 // dependent steps (sum, shuffles, square root, scaling) of ~600 cycles.
 template <int NV>
 __device__ __forceinline__ void norm_staged(bf16* Xs, int KP, const float* stage, const MegaParams& p, const float* w) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int D = p.D;
-    constexpr int WARPS = MEGA_THREADS / 32, RU = 4;
+    constexpr int WARPS = MEGA_THREADS / 32, RU = 8;
     float4 wv[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) wv[k] = __ldg(reinterpret_cast<const float4*>(w + 4 * (lane + 32 * k)));
@@ -570,17 +570,19 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
         // ------------------------------------------------------------- RMSNorm + QKV projection
         if (cta < slabs_qkv) {
             begin_x_f32(stage, p, p.x, l == 0, bar_x);
+            // (what the epilogue of this CTA's first slab adds is requested now: thread = column c of rows r0, r0 + 32)
+            const float pre_b = __ldg(ly.bqkv + cta * 8 + (tid & 7));
             MEGA_WAIT(bar_x, px);
             norm_staged<NV>(Xs, KD, stage, p, ly.attn_norm);
             for (int slab = cta; slab < slabs_qkv; slab += ncta) {
                 if (slab != cta) { __syncthreads(); begin_w_slab(Ws, KD, ly.wqkv + (long long)slab * 8 * KD, 8, bar_w); }
                 MEGA_WAIT(bar_w, pw);
                 __syncthreads();
-                    slab_product<1>(Xs, Ws, KD, D, Cs);
+                slab_product<1>(Xs, Ws, KD, D, Cs);
                 __syncthreads();
-                    for (int i = tid; i < MEGA_ROWS * 8; i += MEGA_THREADS) {
+                for (int i = tid; i < MEGA_ROWS * 8; i += MEGA_THREADS) {
                     const int r = i >> 3, c = i & 7, col = slab * 8 + c;
-                    if (r < S) p.qkv[(long long)r * 3 * D + col] = Cs[r * 16 + c] + Cs[MEGA_ROWS * 16 + r * 16 + c] + __ldg(ly.bqkv + col);
+                    if (r < S) p.qkv[(long long)r * 3 * D + col] = Cs[r * 16 + c] + Cs[MEGA_ROWS * 16 + r * 16 + c] + (slab == cta ? pre_b : __ldg(ly.bqkv + col));
                 }
             }
             __syncthreads();
@@ -616,6 +618,14 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
         // ------------------------------------------------------------- out-projection + residual -> x2
         if (cta < slabs_o) {
             begin_x_bf16(Xs, KD, p.att, bar_x);
+            const int pc = cta * 8 + (tid & 7), pr0 = tid >> 3;
+            const float pre_b = __ldg(ly.bo + pc);
+            float pre_r[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int r = pr0 + 32 * u;
+                pre_r[u] = r < S ? (l == 0 ? __ldg(p.embed + (long long)p.tok[r] * D + pc) : __ldcg(p.x + (long long)r * D + pc)) : 0.0f;
+            }
             MEGA_WAIT(bar_x, px);
             for (int slab = cta; slab < slabs_o; slab += ncta) {
                 if (slab != cta) { __syncthreads(); begin_w_slab(Ws, KD, ly.wo + (long long)slab * 8 * KD, 8, bar_w); }
@@ -626,8 +636,10 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
                 for (int i = tid; i < MEGA_ROWS * 8; i += MEGA_THREADS) {
                     const int r = i >> 3, c = i & 7, col = slab * 8 + c;
                     if (r < S) {
-                        const float res = l == 0 ? __ldg(p.embed + (long long)p.tok[r] * D + col) : __ldcg(p.x + (long long)r * D + col);
-                        p.x2[(long long)r * D + col] = Cs[r * 16 + c] + Cs[MEGA_ROWS * 16 + r * 16 + c] + __ldg(ly.bo + col) + res;
+                        const bool pre = slab == cta;
+                        const float res = pre ? (i >= MEGA_THREADS ? pre_r[1] : pre_r[0])
+                                              : (l == 0 ? __ldg(p.embed + (long long)p.tok[r] * D + col) : __ldcg(p.x + (long long)r * D + col));
+                        p.x2[(long long)r * D + col] = Cs[r * 16 + c] + Cs[MEGA_ROWS * 16 + r * 16 + c] + (pre ? pre_b : __ldg(ly.bo + col)) + res;
                     }
                 }
             }
@@ -638,6 +650,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
         // ------------------------------------------------------------- RMSNorm + gate|up projection + SwiGLU -> h
         if (cta < slabs_gu) {
             begin_x_f32(stage, p, p.x2, false, bar_x);
+            const float pre_bg = __ldg(ly.bgu + cta * 8 + (tid & 7)), pre_bu = __ldg(ly.bgu + F + cta * 8 + (tid & 7));
             MEGA_WAIT(bar_x, px);
             norm_staged<NV>(Xs, KD, stage, p, ly.ffn_norm);
             for (int slab = cta; slab < slabs_gu; slab += ncta) {
@@ -649,8 +662,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
                 for (int i = tid; i < MEGA_ROWS * 8; i += MEGA_THREADS) {
                     const int r = i >> 3, c = i & 7, col = slab * 8 + c;
                     if (r < S) {
-                        const float gv = Cs[r * 16 + c] + Cs[MEGA_ROWS * 16 + r * 16 + c] + __ldg(ly.bgu + col);
-                        const float uv = Cs[r * 16 + 8 + c] + Cs[MEGA_ROWS * 16 + r * 16 + 8 + c] + __ldg(ly.bgu + F + col);
+                        const float gv = Cs[r * 16 + c] + Cs[MEGA_ROWS * 16 + r * 16 + c] + (slab == cta ? pre_bg : __ldg(ly.bgu + col));
+                        const float uv = Cs[r * 16 + 8 + c] + Cs[MEGA_ROWS * 16 + r * 16 + 8 + c] + (slab == cta ? pre_bu : __ldg(ly.bgu + F + col));
                         const float sg = __fdividef(1.0f, 1.0f + ex2_approx(-gv * 1.4426950408889634f));
                         p.h[(long long)r * KF + col] = __float2bfloat16_rn(gv * sg * uv);
                     }
@@ -663,6 +676,11 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
         // ------------------------------------------------------------- down-projection + residual -> x
         if (cta < slabs_down) {
             begin_x_bf16(Xs, KF, p.h, bar_x);
+            const int pc = cta * 8 + (tid & 7), pr0 = tid >> 3;
+            const float pre_b = __ldg(ly.bdown + pc);
+            float pre_r[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) pre_r[u] = pr0 + 32 * u < S ? __ldcg(p.x2 + (long long)(pr0 + 32 * u) * D + pc) : 0.0f;
             MEGA_WAIT(bar_x, px);
             for (int slab = cta; slab < slabs_down; slab += ncta) {
                 if (slab != cta) { __syncthreads(); begin_w_slab(Ws, KF, ly.wdown + (long long)slab * 8 * KF, 8, bar_w); }
@@ -672,9 +690,11 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_layers_kernel(const Me
                 __syncthreads();
                 for (int i = tid; i < MEGA_ROWS * 8; i += MEGA_THREADS) {
                     const int r = i >> 3, c = i & 7, col = slab * 8 + c;
-                    if (r < S)
-                        p.x[(long long)r * D + col] = Cs[r * 16 + c] + Cs[MEGA_ROWS * 16 + r * 16 + c] + __ldg(ly.bdown + col) +
-                                                      __ldcg(p.x2 + (long long)r * D + col);
+                    if (r < S) {
+                        const bool pre = slab == cta;
+                        p.x[(long long)r * D + col] = Cs[r * 16 + c] + Cs[MEGA_ROWS * 16 + r * 16 + c] + (pre ? pre_b : __ldg(ly.bdown + col)) +
+                                                      (pre ? (i >= MEGA_THREADS ? pre_r[1] : pre_r[0]) : __ldcg(p.x2 + (long long)r * D + col));
+                    }
                 }
             }
             __syncthreads();
