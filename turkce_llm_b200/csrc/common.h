@@ -112,6 +112,7 @@ struct GemmArgs {
     CausalMode causal = CAUSAL_NONE;
     int splits = 0;                         // 0 = choose; >1 uses scratch for fixed-order partial sums
     int bn = 0;                             // 0 = choose tile width (64, 128 or 192; 256 = a CTA pair on a 256 x 256 tile)
+    int max_ctas = 0;                       // > 0: at most this many CTAs (two products that share the SMs side by side)
     bool tf32 = false;                      // operands are float32 in memory and enter the tensor cores as tf32
     bool pad_cols_writable = false;         // columns N .. round_up(N, 16 bytes) of each output row are padding
     // Fused SwiGLU epilogue (kind NN, N = 2F with gate columns [0,F) and up columns [F,2F), F % 64 == 0):

@@ -944,7 +944,8 @@ static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
 int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
     if (a.causal != CAUSAL_NONE) return 1;
     const int tile_m = bn == 256 ? 2 * BM : BM;                     // a CTA pair owns 256 rows
-    const int workers = bn == 256 ? ctx->sm_count / 2 : ctx->sm_count;
+    const int sms = (a.max_ctas > 0 && a.max_ctas < ctx->sm_count) ? a.max_ctas : ctx->sm_count;
+    const int workers = bn == 256 ? sms / 2 : sms;
     const long long tiles = (long long)((a.M + tile_m - 1) / tile_m) * ((a.N + bn - 1) / bn) * a.batch;
     const int bke = a.tf32 ? BK_TF32 : BK;
     const int kb_total = (a.K + bke - 1) / bke;
@@ -968,12 +969,13 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
         attr_set[ctx->device & 63] = true;
     }
     const long long total = (long long)p.batch * p.splits * p.mt * p.nt;
+    const int sms = (a.max_ctas > 0 && a.max_ctas < ctx->sm_count) ? a.max_ctas : ctx->sm_count;
     int grid;
     if (PAIR) {
-        const long long pairs = ctx->sm_count / 2;
+        const long long pairs = sms / 2;
         grid = 2 * (int)(total < pairs ? total : pairs);      // one cluster of two CTAs per tile in flight
     } else {
-        grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+        grid = (int)(total < sms ? total : sms);
     }
     if (grid < 1) grid = PAIR ? 2 : 1;
     TB_CUDA(launch_kernel_cluster((gemm_bf16_kernel<BN, TF32, PAIR>), dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES,
@@ -981,7 +983,6 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
-    (void)a;
     return 0;
 }
 
