@@ -192,6 +192,7 @@ int reduce_bucket(TbDp* dp, size_t b) {
 
 // The backward pass of one batch.  reduce: this is the step's last micro-batch and the mode is TB_DP_OVERLAP.
 int backward_all(TbDp* dp, bool reduce = false) {
+    if (!reduce) return trainer_backward_all(dp->g);      // no collective between the layers: one graph
     size_t b = 0;
     TB_TRY(tb_trainer_backward_head(dp->g));
     if (reduce) TB_TRY(reduce_bucket(dp, b++));
@@ -211,6 +212,7 @@ int backward_all(TbDp* dp, bool reduce = false) {
 
 int mean_loss_to_slot(TbDp* dp, int accumulate) {
     const TrainerView& v = dp->v;
+    TB_TRY(trainer_grads_ready(dp->g));        // the slot lies in the gradient buffer, which may still be being cleared
     const int threads = 32 * (v.B < 32 ? v.B : 32);          // one warp per sequence, up to 32 warps
     prof_mark(v.ctx, "loss_mean", 0.0, 0.0, v.stream);
     TB_CUDA(launch_kernel(loss_mean_kernel, dim3(1), dim3(threads), (size_t)v.B * sizeof(float), v.stream, v.loss_rows,

@@ -108,8 +108,9 @@ struct TbTrainer {
     // per pair in a graph, M = 8192: 29.3 -> 23.0, 19.2 -> 14.7, 46.3 -> 42.1, 29.3 -> 23.5 us; without the cap on the
     // CTAs the two persistent kernels only take each other's SMs and nothing is gained.)
     cudaStream_t side = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_done[4] = {nullptr, nullptr, nullptr, nullptr};   // after each of a layer's four dW
     int pair_ctas = 0;             // CTAs per product of such a pair; 0 = one after the other
+    cudaEvent_t ev_zero = nullptr; bool zero_pending = false;     // the gradient buffer is being cleared on `side`
 };
 
 namespace {
@@ -160,9 +161,13 @@ int linear_dx(TbTrainer* g, const void* dY, const void* W, float* dX32, bf16* dX
 }
 
 // dW[K,N] += X[M,K]^T @ dY[M,N] : the reference's gemm1(GEMM_TN, beta=1) (gpu_train.c:417,425,432,461)
-// Issued on the second stream when the pair runs side by side (linear_dx follows on the main stream, then
-// pair_join); the split-K workspace is the weight gradients' alone, no other product of the step splits K.
-int linear_dw(TbTrainer* g, const void* X, const void* dY, float* dW, int M, int N, int K) {
+// Issued on the second stream when the pair runs side by side (linear_dx follows on the main stream); which = 0..3
+// numbers the layer's four weight gradients (down, gate|up, out, qkv).  The main stream does not wait at once: the
+// memory-bound kernels that follow the input-gradient product run beside the tail of the weight-gradient product,
+// and pair_wait(which) stands in front of the first kernel that overwrites an operand of that product.
+// The split-K workspace is the weight gradients' alone (they are in order on their stream); no other product of the
+// step splits K.
+int linear_dw(TbTrainer* g, const void* X, const void* dY, float* dW, int M, int N, int K, int which) {
     GemmArgs a;
     a.kind = GEMM_TN; a.A = X; a.B = dY; a.M = K; a.N = N; a.K = M; a.lda = K; a.ldb = N;
     a.C32 = dW; a.ldc32 = N; a.beta = 1.0f;
@@ -171,13 +176,14 @@ int linear_dw(TbTrainer* g, const void* X, const void* dY, float* dW, int M, int
     a.max_ctas = g->ctx->sm_count - g->pair_ctas;
     TB_CUDA(cudaEventRecord(g->ev_fork, g->stream));
     TB_CUDA(cudaStreamWaitEvent(g->side, g->ev_fork, 0));
-    return launch_gemm_bf16_ws(g->ctx, a, g->splitk_ws, g->splitk_floats, g->side);
+    TB_TRY(launch_gemm_bf16_ws(g->ctx, a, g->splitk_ws, g->splitk_floats, g->side));
+    TB_CUDA(cudaEventRecord(g->ev_done[which], g->side));
+    return 0;
 }
-// everything the main stream launches from here on comes after the weight-gradient product on the second stream
-int pair_join(TbTrainer* g) {
+// everything the main stream launches from here on comes after weight-gradient product `which` of this layer
+int pair_wait(TbTrainer* g, int which) {
     if (!pair_on(g)) return 0;
-    TB_CUDA(cudaEventRecord(g->ev_join, g->side));
-    TB_CUDA(cudaStreamWaitEvent(g->stream, g->ev_join, 0));
+    TB_CUDA(cudaStreamWaitEvent(g->stream, g->ev_done[which], 0));
     return 0;
 }
 
@@ -324,31 +330,29 @@ int backward_layer(TbTrainer* g, int l) {
     // the gradient of the residual stream as a GEMM operand: bf16 copy, or the float32 buffer itself (TF32 mode)
     const void* dres_op = g->tf32 ? (const void*)g->dres : (const void*)g->dres16;
     // ---- FFN: x3 = x2 + (h @ Wd + bd); dres = dx3
-    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.h32 : (const void*)a.h, dres_op, G32(g, pidx(l, PK_WDOWN)), N, D, F));
+    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.h32 : (const void*)a.h, dres_op, G32(g, pidx(l, PK_WDOWN)), N, D, F, 0));
     // (b_down's gradient, the column sum of dres, was produced together with dres)
     TB_TRY(linear_dx(g, dres_op, WOP(g, pidx(l, PK_WDOWN)), g->dh, nullptr, N, D, F));
-    TB_TRY(pair_join(g));
     // (fused path: the gate|up bias gradient, the column sums of dgu, comes out of the same kernel)
     if (g->fused_swiglu)
         TB_TRY(launch_swiglu_bwd_colsum(c, a.gu16, g->dh, g->dgu, G32(g, pidx(l, PK_BGU)), g->swiglu_scratch, N, F, st));
     else TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->tf32 ? nullptr : g->dgu, N, F, st, g->dgu32));
     const void* dgu_op = g->tf32 ? (const void*)g->dgu32 : (const void*)g->dgu;
-    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.n2_32 : (const void*)a.n2, dgu_op, G32(g, pidx(l, PK_WGU)), N, 2 * F, D));
+    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.n2_32 : (const void*)a.n2, dgu_op, G32(g, pidx(l, PK_WGU)), N, 2 * F, D, 1));
     if (!g->fused_swiglu) {
         if (g->tf32) TB_TRY(launch_colsum_f32(c, g->dgu32, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
         else TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
     }
     TB_TRY(linear_dx(g, dgu_op, WOP(g, pidx(l, PK_WGU)), g->dn, nullptr, N, 2 * F, D));
-    TB_TRY(pair_join(g));
+    TB_TRY(pair_wait(g, 0));           // the norm backward overwrites dres16, which the down-projection's dW reads
     TB_TRY(launch_rmsnorm_bwd_dw(c, a.x2, P32(g, pidx(l, PK_FFN_NORM)), a.r2, g->dn, g->dres, g->dres16,
                                  G32(g, pidx(l, PK_FFN_NORM)), G32(g, pidx(l, PK_BO)), g->norm_scratch, N, D, 1, st));
 
     // ---- attention: x2 = x + (att @ Wo + bo); dres = dx2
     if (g->tf32) TB_TRY(launch_widen_bf16(c, a.att, g->att32, (long long)N * D, st));
-    TB_TRY(linear_dw(g, g->tf32 ? (const void*)g->att32 : (const void*)a.att, dres_op, G32(g, pidx(l, PK_WO)), N, D, D));
+    TB_TRY(linear_dw(g, g->tf32 ? (const void*)g->att32 : (const void*)a.att, dres_op, G32(g, pidx(l, PK_WO)), N, D, D, 2));
     // (bo's gradient came with dres as well)
     TB_TRY(linear_dx(g, dres_op, WOP(g, pidx(l, PK_WO)), nullptr, g->datt, N, D, D));
-    TB_TRY(pair_join(g));
     if (g->fused_attention) {
         // dQ, dK, dV leave the kernels rotated back and merged as bf16 dqkv [N, 3D]
         TB_TRY(launch_attention_bwd(c, a.Q, a.K, a.V, a.att, g->datt, a.lse, g->att_delta, nullptr, nullptr, nullptr, B,
@@ -388,13 +392,15 @@ int backward_layer(TbTrainer* g, int l) {
     }
     if (g->tf32) TB_TRY(launch_widen_bf16(c, g->dqkv, g->dqkv32, (long long)N * 3 * D, st));
     const void* dqkv_op = g->tf32 ? (const void*)g->dqkv32 : (const void*)g->dqkv;
-    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.n1_32 : (const void*)a.n1, dqkv_op, G32(g, pidx(l, PK_WQKV)), N, 3 * D, D));
+    TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.n1_32 : (const void*)a.n1, dqkv_op, G32(g, pidx(l, PK_WQKV)), N, 3 * D, D, 3));
     TB_TRY(launch_colsum_bf16(c, g->dqkv, G32(g, pidx(l, PK_BQKV)), g->colsum_partial, N, 3 * D, st));
     TB_TRY(linear_dx(g, dqkv_op, WOP(g, pidx(l, PK_WQKV)), g->dn, nullptr, N, 3 * D, D));
-    TB_TRY(pair_join(g));
+    TB_TRY(pair_wait(g, 2));           // the norm backward overwrites dres16, which the out-projection's dW reads
     TB_TRY(launch_rmsnorm_bwd_dw(c, a.x_in, P32(g, pidx(l, PK_ATTN_NORM)), a.r1, g->dn, g->dres, g->dres16,
                                  G32(g, pidx(l, PK_ATTN_NORM)), l > 0 ? G32(g, pidx(l - 1, PK_BDOWN)) : nullptr,
                                  g->norm_scratch, N, D, 1, st));
+    // the layer below overwrites dgu and dqkv; a graph of this layer alone must end with the second stream joined
+    TB_TRY(pair_wait(g, 3));
     return 0;
 }
 
@@ -404,7 +410,7 @@ int backward_embed(TbTrainer* g) {
                             g->D, g->stream);
 }
 
-enum { SEG_FWD_TRAIN = 0, SEG_FWD_EVAL, SEG_HEAD_BWD, SEG_EMBED_BWD, SEG_ZERO, SEG_STEP, SEG_LAYER0 };
+enum { SEG_FWD_TRAIN = 0, SEG_FWD_EVAL, SEG_HEAD_BWD, SEG_EMBED_BWD, SEG_ZERO, SEG_STEP, SEG_BWD_ALL, SEG_LAYER0 };
 
 // Runs `body` (a fixed sequence of launches on g->stream): eagerly the first time, under stream
 // capture the second time, as a graph launch from then on.
@@ -523,6 +529,14 @@ int adam_launch(TbTrainer* g, uint64_t t, float lr, float b1, float b2, float ep
 }  // namespace
 
 namespace tb {
+int trainer_grads_ready(TbTrainer* g) {
+    if (g->zero_pending) {
+        TB_CUDA(cudaStreamWaitEvent(g->stream, g->ev_zero, 0));
+        g->zero_pending = false;
+    }
+    return 0;
+}
+
 int trainer_view(TbTrainer* g, TrainerView* v) {
     TB_CHECK(g != nullptr && v != nullptr, "trainer_view: null argument");
     v->ctx = g->ctx; v->stream = g->stream; v->device = g->device;
@@ -678,7 +692,8 @@ int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, i
     if (getenv("TB_NO_DW_PAIR") == nullptr) {
         TB_CUDA(cudaStreamCreateWithFlags(&g->side, cudaStreamNonBlocking));
         TB_CUDA(cudaEventCreateWithFlags(&g->ev_fork, cudaEventDisableTiming));
-        TB_CUDA(cudaEventCreateWithFlags(&g->ev_join, cudaEventDisableTiming));
+        for (int i = 0; i < 4; ++i) TB_CUDA(cudaEventCreateWithFlags(&g->ev_done[i], cudaEventDisableTiming));
+        TB_CUDA(cudaEventCreateWithFlags(&g->ev_zero, cudaEventDisableTiming));
         g->pair_ctas = g->ctx->sm_count / 2;
         if (const char* e = getenv("TB_DW_PAIR_CTAS")) {
             const int v = atoi(e);
@@ -716,7 +731,8 @@ int tb_trainer_destroy(TbTrainer* g) {
     cudaFreeHost(g->h_loss_rows); cudaFreeHost(g->h_norm);
     if (g->staged) cudaEventDestroy(g->staged);
     if (g->ev_fork) cudaEventDestroy(g->ev_fork);
-    if (g->ev_join) cudaEventDestroy(g->ev_join);
+    for (int i = 0; i < 4; ++i) if (g->ev_done[i]) cudaEventDestroy(g->ev_done[i]);
+    if (g->ev_zero) cudaEventDestroy(g->ev_zero);
     if (g->side) cudaStreamDestroy(g->side);
     delete g;
     return 0;
@@ -772,10 +788,21 @@ int tb_trainer_download(TbTrainer* g, int which, float* h_flat) {
     return 0;
 }
 
+// The clearing (134 MB, ~25 us) runs on the second stream, beside the forward pass, which does not touch the
+// gradients; trainer_grads_ready stands in front of the first writer.
 int tb_trainer_zero_grads(TbTrainer* g) {
-    TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->padded * 4, g->stream));
+    if (g->side == nullptr || g->ctx->prof_on) {
+        TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->padded * 4, g->stream));
+        return 0;
+    }
+    TB_CUDA(cudaEventRecord(g->ev_fork, g->stream));          // after whatever still reads or writes the buffer
+    TB_CUDA(cudaStreamWaitEvent(g->side, g->ev_fork, 0));
+    TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->padded * 4, g->side));
+    TB_CUDA(cudaEventRecord(g->ev_zero, g->side));
+    g->zero_pending = true;
     return 0;
 }
+
 
 void* tb_trainer_stream(TbTrainer* g) { return g->stream; }
 
@@ -802,8 +829,17 @@ int tb_trainer_step_resident(TbTrainer* g, uint64_t t, float lr, float beta1, fl
     // zeroing, forward and the whole backward are one graph (a single-GPU step has no reason to stop between
     // layers); the optimiser's scalars change every step, so clip + Adam stay ordinary launches
     TB_TRY(run_segment(g, SEG_STEP, [&]() {
-        TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->padded * 4, g->stream));
-        TB_TRY(forward(g, true));
+        if (pair_on(g)) {          // cleared beside the forward pass (inside the same graph)
+            TB_CUDA(cudaEventRecord(g->ev_fork, g->stream));
+            TB_CUDA(cudaStreamWaitEvent(g->side, g->ev_fork, 0));
+            TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->padded * 4, g->side));
+            TB_CUDA(cudaEventRecord(g->ev_done[0], g->side));
+            TB_TRY(forward(g, true));
+            TB_CUDA(cudaStreamWaitEvent(g->stream, g->ev_done[0], 0));
+        } else {
+            TB_CUDA(cudaMemsetAsync(g->grads, 0, (size_t)g->padded * 4, g->stream));
+            TB_TRY(forward(g, true));
+        }
         TB_TRY(backward_head(g));
         for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
         return backward_embed(g);
@@ -824,6 +860,7 @@ int tb_trainer_last_norm(TbTrainer* g, double* norm_out) {
 }
 
 int tb_trainer_backward_head(TbTrainer* g) {
+    TB_TRY(trainer_grads_ready(g));
     return run_segment(g, SEG_HEAD_BWD, [&]() { return backward_head(g); });
 }
 int tb_trainer_backward_layer(TbTrainer* g, int layer) {
@@ -833,15 +870,21 @@ int tb_trainer_backward_layer(TbTrainer* g, int layer) {
 int tb_trainer_backward_embed(TbTrainer* g) {
     return run_segment(g, SEG_EMBED_BWD, [&]() { return backward_embed(g); });
 }
+static int backward_all_segment(TbTrainer* g) {
+    TB_TRY(trainer_grads_ready(g));
+    return run_segment(g, SEG_BWD_ALL, [&]() {
+        TB_TRY(backward_head(g));
+        for (int l = g->L - 1; l >= 0; --l) TB_TRY(backward_layer(g, l));
+        return backward_embed(g);
+    });
+}
 int tb_trainer_read_loss(TbTrainer* g, float* loss_out) { return read_loss(g, loss_out); }
 
 int tb_trainer_forward_backward(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_targets, float* loss_out) {
     TB_CUDA(cudaSetDevice(g->device));
     TB_TRY(tb_trainer_zero_grads(g));
     TB_TRY(tb_trainer_forward(g, h_ids, h_targets, 1));
-    TB_TRY(tb_trainer_backward_head(g));
-    for (int l = g->L - 1; l >= 0; --l) TB_TRY(tb_trainer_backward_layer(g, l));
-    TB_TRY(tb_trainer_backward_embed(g));
+    TB_TRY(backward_all_segment(g));
     return read_loss(g, loss_out);
 }
 
@@ -852,6 +895,7 @@ int tb_trainer_eval_loss(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h_
 }
 
 int tb_trainer_grad_norm(TbTrainer* g, double* norm_out) {
+    TB_TRY(trainer_grads_ready(g));
     TB_TRY(launch_sumsq_partial(g->ctx, g->grads, g->total, g->norm_partial, g->stream));
     TB_TRY(launch_clip_scale(g->ctx, g->norm_partial, 0.0f, 1.0f, g->scalars, g->norm64, g->stream));
     TB_CUDA(cudaMemcpyAsync(g->h_norm, g->norm64, sizeof(double), cudaMemcpyDeviceToHost, g->stream));
@@ -871,6 +915,7 @@ int tb_trainer_adam_step_scaled(TbTrainer* g, uint64_t t, float lr, float beta1,
 int tb_trainer_clip_adam_async(TbTrainer* g, uint64_t t, float lr, float beta1, float beta2, float eps,
                                float max_norm, float grad_scale) {
     TB_CHECK(t >= 1, "Adam step counter starts at 1");
+    TB_TRY(trainer_grads_ready(g));
     TB_TRY(launch_sumsq_partial(g->ctx, g->grads, g->total, g->norm_partial, g->stream));
     TB_TRY(launch_clip_scale(g->ctx, g->norm_partial, max_norm, grad_scale, g->scalars, g->norm64, g->stream));
     TB_CUDA(cudaMemcpyAsync(g->h_norm, g->norm64, sizeof(double), cudaMemcpyDeviceToHost, g->stream));
@@ -882,9 +927,7 @@ int tb_trainer_train_step(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h
     TB_CUDA(cudaSetDevice(g->device));
     TB_TRY(tb_trainer_zero_grads(g));
     TB_TRY(tb_trainer_forward(g, h_ids, h_targets, 1));
-    TB_TRY(tb_trainer_backward_head(g));
-    for (int l = g->L - 1; l >= 0; --l) TB_TRY(tb_trainer_backward_layer(g, l));
-    TB_TRY(tb_trainer_backward_embed(g));
+    TB_TRY(backward_all_segment(g));
     TB_TRY(tb_trainer_clip_adam_async(g, t, lr, beta1, beta2, eps, max_norm, 1.0f));
     TB_TRY(read_loss(g, loss_out));
     if (norm_out) *norm_out = *g->h_norm;
@@ -892,3 +935,7 @@ int tb_trainer_train_step(TbTrainer* g, const uint32_t* h_ids, const uint32_t* h
 }
 
 }  // extern "C"
+
+namespace tb {
+int trainer_backward_all(TbTrainer* g) { return backward_all_segment(g); }
+}  // namespace tb

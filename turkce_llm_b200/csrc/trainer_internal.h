@@ -19,5 +19,11 @@ struct TrainerView {
 };
 
 int trainer_view(TbTrainer* g, TrainerView* out);
+// tb_trainer_zero_grads may clear the gradient buffer on the trainer's second stream while the forward pass runs;
+// whoever writes into the flat gradient buffer (or its loss slot) first calls this before.
+int trainer_grads_ready(TbTrainer* g);
+// head, layers L-1 .. 0 and embedding backward as ONE graph (tb_trainer_backward_head / _layer / _embed are a graph each,
+// for a caller that puts collectives between them)
+int trainer_backward_all(TbTrainer* g);
 
 }  // namespace tb
