@@ -247,6 +247,39 @@ def test_bf16_entry_tiles_splits_outputs(tb, oracle, kind):
         results.append(got)
 
 
+@pytest.mark.parametrize("kind", ["NN", "TN"])
+@pytest.mark.parametrize("shape", [(777, 384, 2112), (512, 300, 4160), (1024, 384, 4096), (130, 264, 200)])
+def test_bf16_entry_384_column_pair_tiles(tb, oracle, kind, shape):
+    """256 x 384 tiles on a CTA pair (three 128-column tensor-core instructions per K step, one accumulator): the form
+    the LM-head gradients take (N = d_model <= 384, K = vocabulary or tokens).  B must be stored [K, N]."""
+    k = KINDS[kind]
+    M, N, K = shape
+    rng = np.random.default_rng(40 + k + M)
+    (ar, ac), (br, bc) = stored_shapes(k, M, N, K)
+    lda, ldb = (ac + 7) // 8 * 8, (bc + 7) // 8 * 8
+    A = np.zeros((ar, lda), np.float32)
+    B = np.zeros((br, ldb), np.float32)
+    A[:, :ac] = oracle.round(rng.standard_normal((ar, ac)).astype(np.float32), BF16)
+    B[:, :bc] = oracle.round(rng.standard_normal((br, bc)).astype(np.float32), BF16)
+    A16, B16 = dev(A).to(torch.bfloat16), dev(B).to(torch.bfloat16)
+    bias = rng.standard_normal(N).astype(np.float32)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    want = oracle.gemm(k // 2, k % 2, A, B, M, N, K, lda, ldb, N, beta=1.0, C_in=C0).reshape(M, N) + bias
+    for tile_n, splits in ((384, 1), (384, 2), (384, 3), (0, 0)):
+        C = dev(C0.copy())
+        tb.gemm_bf16(k, A16, B16, M, N, K, lda, ldb, C32=C, ldc32=N, bias=dev(bias), beta=1.0, splits=splits, tile_n=tile_n)
+        tb.sync_check()
+        assert rel_to_maxabs(C.cpu().numpy(), want) <= TOL_SAME_OPERANDS, (tile_n, splits)
+        C2 = dev(C0.copy())
+        tb.gemm_bf16(k, A16, B16, M, N, K, lda, ldb, C32=C2, ldc32=N, bias=dev(bias), beta=1.0, splits=splits, tile_n=tile_n)
+        assert torch.equal(C, C2), "same launch twice must be bitwise identical"
+    if kind == "NN":        # the same product with B stored [N, K] cannot take this tile
+        Bt = dev(np.ascontiguousarray(np.zeros((N, (K + 7) // 8 * 8), np.float32))).to(torch.bfloat16)
+        with pytest.raises(Exception):
+            tb.gemm_bf16(KINDS["NT"], A16, Bt, M, N, K, lda, Bt.shape[1], C32=dev(C0.copy()), ldc32=N, tile_n=384)
+            tb.sync_check()
+
+
 def test_causal_modes(tb, oracle):
     """Batched square attention products restricted to the lower triangle."""
     rng = np.random.default_rng(20)

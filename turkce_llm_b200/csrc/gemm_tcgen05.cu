@@ -39,12 +39,16 @@ constexpr int STAGE_LD = 36;        // floats per staging row (32 + 4 pad: confl
 
 // PAIR: two CTAs of a cluster share a 256 x BN tile (cta_group::2): each loads its own 128 rows of A and
 // BN/2 columns of B, so a CTA's shared-memory traffic per output element drops by BN/(128 + BN/2)/(BN/(128+BN)).
+// BN = 384 (PAIR, B stored [K, N]): for products with N <= 384 and a long K (the LM-head gradients): one tile spans
+// the whole N, 40 KB per K slice feed 768 tensor-core cycles (53 B/clk against 64 for 256 x 256 with half of the
+// second tile empty).  The tensor core takes N <= 256, so a K step is three instructions of 128 columns; each CTA
+// loads the 64-column boxes at n0 + 128 j + 64 rank, which keeps accumulator column = output column.  One accumulator.
 template <int BN, bool PAIR = false> struct GemmCfg {
     static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN;   // columns of B this CTA loads
     static constexpr int A_BYTES = BM * ROW_BYTES;      // one K slice: 128-byte rows for either operand type
     static constexpr int B_BYTES = BN_LOCAL * ROW_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = PAIR ? 4 : (BN == 192) ? 3 : (BN == 128) ? 4 : 5;
+    static constexpr int STAGES = (PAIR && BN == 384) ? 3 : PAIR ? 4 : (BN == 192) ? 3 : (BN == 128) ? 4 : 5;
     // per epilogue warp: 2 output buffers + 1 residual buffer of 32 rows x 128 B (TMA path);
     // the generic path uses the front of the same region (32 x 36 floats per warp)
     static constexpr int EPI_WARP_BYTES = 3 * 4096;
@@ -52,6 +56,8 @@ template <int BN, bool PAIR = false> struct GemmCfg {
     static constexpr int BAR_BYTES = 512;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
     static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;   // power of two
+    // accumulators in TMEM: two (the epilogue of tile i overlaps the main loop of tile i+1) unless one fills it
+    static constexpr int NBUF = (2 * BN <= 512) ? 2 : 1;
 };
 
 struct GemmParams {
@@ -119,7 +125,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     static_assert(!(PAIR && TF32), "CTA pairs are built for bf16 operands only");
     using Cfg = GemmCfg<BN, PAIR>;
     constexpr int STAGES = Cfg::STAGES;
+    constexpr int NBUF = Cfg::NBUF;
     constexpr int BNL = Cfg::BN_LOCAL;
+    static_assert(BN != 384 || PAIR, "384-column tiles are built for CTA pairs");
     constexpr int TILE_M = PAIR ? 2 * BM : BM;
     // PAIR: rank in the CTA pair; rank 0 issues the UMMAs and owns the barriers the loads are counted on
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
@@ -204,7 +212,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     } else {
 #pragma unroll
                         for (int j = 0; j < BNL / MNW; ++j) {
-                            int n = nb0 + j * MNW;
+                            int n = BN == 384 ? c.n0 + 128 * j + 64 * (int)rank : nb0 + j * MNW;
                             if (p.tma_mode == 3) {     // paired tile: first half gate columns, second half their up columns
                                 const int jj = (int)rank * (BNL / MNW) + j;      // box index inside the whole tile
                                 n = (c.n0 >> 1) + (jj < BN / MNW / 2 ? jj * MNW : p.pair_off + (jj - BN / MNW / 2) * MNW);
@@ -228,7 +236,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer (PAIR: rank 0 for both CTAs)
         if (lane == 0 && rank == 0) {
-            const uint32_t idesc = umma_idesc(TF32 ? 2u : 1u, (uint32_t)p.a_mn, (uint32_t)p.b_mn, TILE_M, BN);
+            constexpr int UMMA_N = BN == 384 ? 128 : BN;       // columns per tensor-core instruction
+            constexpr int NSUB = BN / UMMA_N;
+            const uint32_t idesc = umma_idesc(TF32 ? 2u : 1u, (uint32_t)p.a_mn, (uint32_t)p.b_mn, TILE_M, UMMA_N);
+            // (BN = 384: instruction j takes the j-th 64-column box of B in either CTA and accumulator columns 128 j ..)
+            constexpr uint64_t B_SUB_STEP = (uint64_t)(MN_BOX_BYTES >> 4);
             // Shared-memory descriptors are built once: the descriptor of stage 0, the step between stages
             // and the step between the four UMMAs of a K slice are all that changes (the start address sits
             // in the low 14 bits, in 16-byte units, and never carries out of them below 256 KB).  One thread
@@ -251,8 +263,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int t = worker; t < total_tiles && ok; t += nworkers) {
                 const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
                 if (c.skip) continue;
-                const int buf = it & 1;
-                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                const int buf = it % NBUF;
+                const uint32_t acc_phase = (uint32_t)(it / NBUF) & 1u;
                 if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
@@ -262,7 +274,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {          // 4 UMMAs of 32 bytes of K per 128-byte slice
                         if (TF32)      umma_tf32(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
-                        else if (PAIR) umma_bf16_pair(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                        else if (PAIR) {
+#pragma unroll
+                            for (int j = 0; j < NSUB; ++j)
+                                umma_bf16_pair(d_tmem + (uint32_t)(j * UMMA_N), a_desc + k * a_kstep, b_desc + k * b_kstep + j * B_SUB_STEP,
+                                               idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
+                        }
                         else           umma_bf16(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, (kb > c.kb0 || k > 0) ? 1u : 0u);
                     }
                     if (PAIR) umma_commit_pair(&empty_bar[stage]);   // stage reusable (in both CTAs) once these MMAs have read it
@@ -297,8 +314,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int t = worker; t < total_tiles && ok; t += nworkers) {
             const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
             if (c.skip) continue;
-            const int buf = it & 1;
-            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const int buf = it % NBUF;
+            const uint32_t acc_phase = (uint32_t)(it / NBUF) & 1u;
             const bool have_acc = c.kb1 > c.kb0;
             const int zc = c.z * p.splits + c.s;
             const int zo = zc / p.c_inner, zi = zc % p.c_inner;
@@ -576,8 +593,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int t = worker; t < total_tiles && ok; t += nworkers) {
             const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
             if (c.skip) continue;
-            const int buf = it & 1;
-            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const int buf = it % NBUF;
+            const uint32_t acc_phase = (uint32_t)(it / NBUF) & 1u;
             const bool have_acc = c.kb1 > c.kb0;
             if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -920,7 +937,11 @@ static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
     if (a.swiglu_h)      // paired gate/up tile: 128 wide, or 256 wide on a CTA pair
         return ((a.bn == 256 || (a.bn == 0 && pair_ok && cost_of(256) < cost_of(128))) && a.N % 256 == 0) ? 256 : 128;
     if (a.ce_mode != 0) return a.bn == 256 ? 256 : 192;     // the statistics are laid out per tile of this width
-    if (a.bn == 64 || a.bn == 128 || a.bn == 192 || a.bn == 256) return a.bn;
+    if (a.bn == 64 || a.bn == 128 || a.bn == 192 || a.bn == 256 || a.bn == 384) return a.bn;
+    // one 256 x 384 pair tile over the whole N where K is long (the LM-head gradients: dE 225 -> ~125 us)
+    if (pair_ok && a.kind != GEMM_NT && a.N > 256 && a.N <= 384 && a.K >= 4096 && !a.swiglu_h && !a.rope_qkv &&
+        getenv("TB_GEMM_NO_384") == nullptr)
+        return 384;
     if (a.N <= 64) return 64;
     const long long t128 = mt * ((a.N + 127) / 128) * a.batch;
     if (t128 * 2 <= ctx->sm_count && a.K >= 16 * (a.tf32 ? BK_TF32 : BK)) {
@@ -943,9 +964,9 @@ static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
 
 int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
     if (a.causal != CAUSAL_NONE) return 1;
-    const int tile_m = bn == 256 ? 2 * BM : BM;                     // a CTA pair owns 256 rows
+    const int tile_m = bn >= 256 ? 2 * BM : BM;                     // a CTA pair owns 256 rows
     const int sms = (a.max_ctas > 0 && a.max_ctas < ctx->sm_count) ? a.max_ctas : ctx->sm_count;
-    const int workers = bn == 256 ? sms / 2 : sms;
+    const int workers = bn >= 256 ? sms / 2 : sms;
     const long long tiles = (long long)((a.M + tile_m - 1) / tile_m) * ((a.N + bn - 1) / bn) * a.batch;
     const int bke = a.tf32 ? BK_TF32 : BK;
     const int kb_total = (a.K + bke - 1) / bke;
@@ -1020,10 +1041,13 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     const int bke = a.tf32 ? BK_TF32 : BK;
     if (!a_mn) TB_TRY(make_operand_map_es(&tmA, a.A, es, a.K, a.M, a.lda, a.batch, a.strideA, BM));
     else       TB_TRY(make_operand_map_es(&tmA, a.A, es, a.M, a.K, a.lda, a.batch, a.strideA, bke, true));
-    const bool pair = bn == 256;
+    const bool pair = bn == 256 || bn == 384;
     if (pair)
         TB_CHECK(!a.tf32 && a.batch == 1 && a.causal == CAUSAL_NONE && a.c_inner <= 1,
                  "256-wide CTA-pair tiles take one plain bf16 product (no batch, no causal mode)");
+    if (bn == 384)
+        TB_CHECK(b_mn && !a.swiglu_h && a.ce_mode == 0 && !a.rope_qkv,
+                 "384-wide CTA-pair tiles take B stored [K, N] (kinds NN and TN) and a plain epilogue");
     if (!b_mn) TB_TRY(make_operand_map_es(&tmB, a.B, es, a.K, a.N, a.ldb, a.batch, a.strideB, pair ? bn / 2 : bn));
     else       TB_TRY(make_operand_map_es(&tmB, a.B, es, a.N, a.K, a.ldb, a.batch, a.strideB, bke, true));
 
@@ -1135,7 +1159,9 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
             prof_mark(ctx, prof_intern(tag), a.ce_mode == 2 ? 0.0 : 2.0 * macs, in_bytes + out_bytes, stream);
         }
     }
-    if (pair) {
+    if (pair && bn == 384) {
+        TB_TRY((launch_impl<384, false, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+    } else if (pair) {
         TB_TRY((launch_impl<256, false, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
     } else if (a.tf32) {
         if (bn == 64)       TB_TRY((launch_impl<64, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));

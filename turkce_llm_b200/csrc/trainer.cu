@@ -310,7 +310,7 @@ int backward_head(TbTrainer* g) {
         GemmArgs a;
         a.kind = GEMM_NN; a.A = g->tf32 ? (const void*)g->dlogits32 : (const void*)g->dlogits; a.B = WOP(g, 0);
         a.tf32 = g->tf32; a.M = N; a.N = D; a.K = V; a.lda = g->Vp; a.ldb = D;
-        a.C32 = g->dn; a.ldc32 = D; a.splits = 1;
+        a.C32 = g->dn; a.ldc32 = D; a.splits = 0;         // (two splits on 256 x 384 pair tiles when D <= 384, else one)
         TB_TRY(gemm(g, a));
     }
     // dres (the gradient of the last layer's output) also yields that layer's b_down gradient
@@ -672,6 +672,9 @@ int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, i
         // tile per SM, plus one unsplit copy of the largest weight matrix for rounding slack
         size_t biggest = std::max({(size_t)D * 2 * F, (size_t)D * 3 * D, (size_t)F * D, (size_t)D * D});
         g->splitk_floats = biggest + 2 * (size_t)g->ctx->sm_count * 128 * 128;
+        // the LM head's input gradient [N, D] may run split along K on 256-row pair tiles: splits <= pairs / tiles, so
+        // splits * N * D stays below one 256-row slab per CTA pair (plus the unsplit size for rounding slack)
+        g->splitk_floats = std::max(g->splitk_floats, ((size_t)g->ctx->sm_count / 2 + 2) * 256 * (size_t)D + 2 * (size_t)N * D);
         TB_TRY(dalloc(g, &g->splitk_ws, g->splitk_floats));
     }
 
