@@ -113,6 +113,12 @@ struct GemmArgs {
     int splits = 0;                         // 0 = choose; >1 uses scratch for fixed-order partial sums
     int bn = 0;                             // 0 = choose tile width (64, 128 or 192; 256 = a CTA pair on a 256 x 256 tile)
     int max_ctas = 0;                       // > 0: at most this many CTAs (two products that share the SMs side by side)
+    // SwiGLU backward in the epilogue (bf16 NT product with N = F, the input gradient of the down-projection): the
+    // product dh [M, F] is not stored; with the saved gate|up projection dsw_gu [M, 2F] (leading dimension ldgu) the
+    // tile leaves as dsw_dgu [M, 2F] (same leading dimension): dg = dh u s (1 + g (1 - s)), du = dh g s, s = sigmoid(g).
+    // F must be a multiple of 64.
+    const bf16* dsw_gu = nullptr;
+    bf16* dsw_dgu = nullptr;
     bool tf32 = false;                      // operands are float32 in memory and enter the tensor cores as tf32
     bool pad_cols_writable = false;         // columns N .. round_up(N, 16 bytes) of each output row are padding
     // Fused SwiGLU epilogue (kind NN, N = 2F with gate columns [0,F) and up columns [F,2F), F % 64 == 0):

@@ -82,6 +82,9 @@ struct GemmParams {
     const uint32_t* ce_targets; float* ce_stats; float* ce_ztarget; const float* ce_lse; float ce_scale;
     int pair_off;               // mode 3: F; tile columns [0,BN/2) are gate columns n0/2.., [BN/2,BN) up columns F + n0/2..
     int keep_gu;
+    int wide16;                 // bf16 tiles leave two 32-column chunks at a time: 32 rows x 128 bytes per store through the
+                                // 64-column map (tmR; with dsw: tmC), a last odd chunk through the 32-column map tmC
+    int dsw;                    // SwiGLU backward: the product is dh; tmR = saved gate|up [M,2F] bf16, tmC = dgu [M,2F] bf16
     int tma_res;                // TMA path: add res_scale * (tile of tmR) -- the residual, or the old C for beta
     float res_scale;
     int bias_vec;               // bias pointer is 16-byte aligned
@@ -150,7 +153,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint64_t* empty_bar = bars + STAGES;          // [STAGES]
     uint64_t* acc_full = bars + 2 * STAGES;       // [2]
     uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
-    uint64_t* res_bar = bars + 2 * STAGES + 4;    // [EPI_WARPS]
+    uint64_t* res_bar = bars + 2 * STAGES + 4;    // [2][EPI_WARPS] (the second set: SwiGLU backward's other g / u buffer)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + EPI_WARPS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -166,7 +169,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.tma_mode != 0 && p.tma_mode != 4) tma_prefetch_desc(&tmC);
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], PAIR ? 2 * EPI_WARPS : EPI_WARPS); }
-        for (int i = 0; i < EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
+        for (int i = 0; i < 2 * EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -454,15 +457,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 mbar_expect_tx(rbar, 4096);
                 tma_load_4d(rbuf, &tmR, rbar, col0, gm0, 0, c.z);
             }
+            // SwiGLU backward: g and u of chunk ch + 1 are fetched while chunk ch is computed
+            auto dsw_fetch = [&](int ch) {
+                mbar_expect_tx(rbar, 4096);
+                tma_load_4d(rbuf, &tmR, rbar, col0 + ch * 32, gm0, 0, 0);
+                tma_load_4d(rbuf + 2048, &tmR, rbar, p.pair_off + col0 + ch * 32, gm0, 0, 0);
+            };
+            if (p.dsw && lane == 0 && rows_in && col0 < p.N) dsw_fetch(0);
             if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
 #pragma unroll 1
             for (int ch = 0; ch < NCH; ++ch) {
-                const uint32_t b = cnt & 1u;
+                // a store unit is one chunk, or in wide16 mode a pair of chunks (an odd last chunk stays alone);
+                // with dsw a unit fills both output buffers (dg | du), else the units alternate between them
+                const bool paired = p.wide16 && ((ch & 1) || ch + 1 < NCH);
+                const bool second = paired && (ch & 1);
+                const uint32_t b = p.dsw ? 0u : (cnt & 1u);
                 const int gn0 = col0 + ch * 32;
                 const bool active = rows_in && gn0 < p.N;
-                if (lane == 0) tma_store_wait_read<1>();      // output buffer b (chunk cnt-2) has been read out
+                if (lane == 0 && !second) {                   // the unit's output buffer has been read out
+                    if (p.dsw) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
+                }
                 __syncwarp();
                 uint32_t v[32];
                 if (have_acc) {
@@ -539,14 +555,57 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         o[j] = pr * p.ce_scale;
                     }
                 }
-                if (p.tma_mode == 1) {
+                if (p.dsw) {
+                    // SwiGLU backward (the reference's k_swiglu_bwd on the product's tile, cuda/train_kernels.cu:709-721):
+                    // o = dh (zero in rows past M, whose operand rows the tile loads fill with zeros); with the saved
+                    // g, u of the same rows and hidden units, a = g s, s = sigmoid(g):
+                    //   dg = dh u (s + a - a s),  du = dh a
+                    // leave as bf16 boxes of dgu at columns gn0 and F + gn0
+                    if (active) {
+                        if (!mbar_wait(rbar, rphase, abort_flag)) { ok = false; break; }
+                        rphase ^= 1u;
+                        constexpr float NLOG2E = -1.4426950408889634f;
+                        const uint8_t* grow = rbuf + lane * 64;
+                        // paired: dg rows of 128 bytes in obuf, du rows in obuf + 4096; alone: 64-byte rows, du at + 2048
+                        uint8_t* orow = obuf + lane * (paired ? 128 : 64);
+                        const int uoff = paired ? 4096 : 2048;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int sw = (j ^ ((lane >> 1) & 3)) << 4;
+                            const int so = paired ? (((second ? 4 : 0) + j) ^ (lane & 7)) << 4 : sw;
+                            const uint4 g4 = *reinterpret_cast<const uint4*>(grow + sw);
+                            const uint4 u4 = *reinterpret_cast<const uint4*>(grow + 2048 + sw);
+                            const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+                            uint32_t pg[4], pu[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[e]));
+                                const float2 uu = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[e]));
+                                const float d0 = o[8 * j + 2 * e], d1 = o[8 * j + 2 * e + 1];
+                                const float s0 = __fdividef(1.0f, 1.0f + ex2_approx(gg.x * NLOG2E));
+                                const float s1 = __fdividef(1.0f, 1.0f + ex2_approx(gg.y * NLOG2E));
+                                const float a0 = gg.x * s0, a1 = gg.y * s1;
+                                const float q0 = fmaf(-a0, s0, a0) + s0, q1 = fmaf(-a1, s1, a1) + s1;
+                                __nv_bfloat162 hg = __floats2bfloat162_rn(d0 * uu.x * q0, d1 * uu.y * q1);
+                                __nv_bfloat162 hu = __floats2bfloat162_rn(d0 * a0, d1 * a1);
+                                pg[e] = *reinterpret_cast<uint32_t*>(&hg); pu[e] = *reinterpret_cast<uint32_t*>(&hu);
+                            }
+                            *reinterpret_cast<uint4*>(orow + so) = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                            *reinterpret_cast<uint4*>(orow + uoff + so) = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+                        }
+                        // the g / u buffer is free again: fetch the next chunk's boxes into it
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0 && ch + 1 < NCH && gn0 + 32 < p.N) dsw_fetch(ch + 1);
+                    }
+                } else if (p.tma_mode == 1) {
                     uint8_t* orow = obuf + b * 4096 + lane * 128;
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         *reinterpret_cast<float4*>(orow + ((j ^ (lane & 7)) << 4)) =
                             make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
                 } else {
-                    uint8_t* orow = obuf + b * 4096 + lane * 64;
+                    uint8_t* orow = obuf + b * 4096 + lane * (paired ? 128 : 64);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint4 pk;
@@ -556,16 +615,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * j + 6], o[8 * j + 7]);
                         pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
                         pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                        *reinterpret_cast<uint4*>(orow + ((j ^ ((lane >> 1) & 3)) << 4)) = pk;
+                        const int so = paired ? (((second ? 4 : 0) + j) ^ (lane & 7)) << 4 : (j ^ ((lane >> 1) & 3)) << 4;
+                        *reinterpret_cast<uint4*>(orow + so) = pk;
                     }
                 }
+                if (paired && !second) continue;              // the unit leaves after its second chunk
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) {
+                if (lane == 0 && paired) {
+                    // rows of 128 bytes: columns gn0 - 32 .. gn0 + 31 (what lies past N is clipped by the hardware)
+                    if (rows_in && gn0 - 32 < p.N) {
+                        if (p.dsw) {
+                            tma_store_4d(&tmC, obuf, gn0 - 32, gm0, 0, 0);
+                            tma_store_4d(&tmC, obuf + 4096, p.pair_off + gn0 - 32, gm0, 0, 0);
+                        } else {
+                            tma_store_4d(&tmR, obuf + b * 4096, gn0 - 32, gm0, zi, zo);
+                        }
+                    }
+                    tma_store_commit();
+                } else if (lane == 0) {
                     if (active && p.tma_mode == 5) {
                         const int which = gn0 >= 2 * rope_D ? 2 : (gn0 >= rope_D ? 1 : 0);
                         const int cin = gn0 - which * rope_D;
                         tma_store_5d(&tmC, obuf + b * 4096, cin & (p.rope_hd - 1), rope_t0, cin >> rope_shift, rope_b, which);
+                    } else if (active && p.dsw) {
+                        tma_store_4d(&tmC, obuf + b * 4096, gn0, gm0, 0, 0);
+                        tma_store_4d(&tmC, obuf + b * 4096 + 2048, p.pair_off + gn0, gm0, 0, 0);
                     } else if (active) {
                         tma_store_4d(&tmC, obuf + b * 4096, gn0, gm0, zi, zo);
                     }
@@ -890,8 +965,10 @@ int make_operand_map4(CUtensorMap* map, const bf16* ptr, long long inner, long l
 
 // 4-D view (columns, rows, inner batch, outer batch) of an output or residual matrix with a
 // 32 x 32 element box: 128-byte rows for float32 (128B swizzle), 64-byte rows for bf16 (64B swizzle).
+// wide (bf16 only): a 64 x 32 element box, 128-byte rows with the 128B swizzle.
 static int make_map_out(CUtensorMap* map, const void* ptr, int elem_bytes, long long cols, long long rows,
-                        long long ld, long long inner, long long stride_in, long long outer, long long stride_out) {
+                        long long ld, long long inner, long long stride_in, long long outer, long long stride_out,
+                        bool wide = false) {
     EncodeTiledFn enc = get_encode_fn();
     TB_CHECK(enc != nullptr, "cuTensorMapEncodeTiled entry point not available");
     const cuuint64_t row_bytes = (cuuint64_t)ld * elem_bytes;
@@ -901,11 +978,11 @@ static int make_map_out(CUtensorMap* map, const void* ptr, int elem_bytes, long 
     if (s_out == 0) s_out = 16;
     cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)inner, (cuuint64_t)outer};
     cuuint64_t strides[3] = {row_bytes, s_in, s_out};
-    cuuint32_t box[4] = {32u, 32u, 1u, 1u};
+    cuuint32_t box[4] = {wide ? 64u : 32u, 32u, 1u, 1u};
     cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     CUresult r = enc(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
                      const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     elem_bytes == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     (elem_bytes == 4 || wide) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (output) failed with code %d (cols=%lld rows=%lld ld=%lld)",
              (int)r, cols, rows, ld);
@@ -936,6 +1013,7 @@ static int pick_bn(const DeviceCtx* ctx, const GemmArgs& a) {
     };
     if (a.swiglu_h)      // paired gate/up tile: 128 wide, or 256 wide on a CTA pair
         return ((a.bn == 256 || (a.bn == 0 && pair_ok && cost_of(256) < cost_of(128))) && a.N % 256 == 0) ? 256 : 128;
+    if (a.dsw_dgu) return (a.bn == 256 || (a.bn == 0 && pair_ok)) ? 256 : 128;      // its chunks leave in pairs
     if (a.ce_mode != 0) return a.bn == 256 ? 256 : 192;     // the statistics are laid out per tile of this width
     if (a.bn == 64 || a.bn == 128 || a.bn == 192 || a.bn == 256 || a.bn == 384) return a.bn;
     // one 256 x 384 pair tile over the whole N where K is long (the LM-head gradients: dE 225 -> ~125 us)
@@ -1010,7 +1088,7 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
 static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, float* ws, cudaStream_t stream) {
     TB_CHECK(a.M > 0 && a.N > 0 && a.K > 0 && a.batch > 0, "GEMM dims must be positive (M=%d N=%d K=%d batch=%d)",
              a.M, a.N, a.K, a.batch);
-    TB_CHECK(a.A && a.B && (a.C32 || a.C16 || a.swiglu_h || a.ce_mode == 1 || a.rope_qkv),
+    TB_CHECK(a.A && a.B && (a.C32 || a.C16 || a.swiglu_h || a.ce_mode == 1 || a.rope_qkv || a.dsw_dgu),
              "GEMM needs A, B and at least one output");
     if (a.rope_qkv) {
         TB_CHECK(a.kind == GEMM_NN && !a.tf32 && a.batch == 1 && splits == 1 && a.alpha == 1.0f && a.beta == 0.0f &&
@@ -1025,6 +1103,14 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
                  "fused cross-entropy GEMM: needs a plain NT bf16 product with 192-column tiles and the targets");
         if (a.ce_mode == 1) TB_CHECK(a.ce_stats && a.ce_ztarget && !a.C16, "cross-entropy pass 1 writes statistics only");
         else TB_CHECK(a.ce_mode == 2 && a.ce_lse && a.C16, "cross-entropy pass 2 needs the row log-sum-exp and a bf16 output");
+    }
+    if (a.dsw_dgu) {
+        TB_CHECK(!a.tf32 && a.batch == 1 && splits == 1 && a.alpha == 1.0f && a.beta == 0.0f && !a.bias && !a.residual &&
+                     !a.C32 && !a.C16 && !a.swiglu_h && a.ce_mode == 0 && !a.rope_qkv && a.causal == CAUSAL_NONE &&
+                     a.dsw_gu && a.N % 64 == 0 && a.ldgu % 8 == 0 && a.ldgu >= 2 * a.N &&
+                     aligned16(a.dsw_gu) && aligned16(a.dsw_dgu),
+                 "SwiGLU-backward GEMM: needs a plain bf16 product with N = F (a multiple of 64), the saved gate|up "
+                 "projection and the output, 16-byte aligned with ldgu %% 8 == 0");
     }
     const bool swiglu = a.swiglu_h != nullptr;
     if (swiglu) {
@@ -1056,6 +1142,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     p.mt = pair ? (a.M + 2 * BM - 1) / (2 * BM) : (a.M + BM - 1) / BM;      // a pair owns 256 rows
     p.nt = (a.N + bn - 1) / bn;
     p.a_mn = a_mn; p.b_mn = b_mn; p.causal = (int)a.causal;
+    p.dsw = 0; p.wide16 = 0;
     p.err = ctx->d_err;
     if (splits > 1) {
         // partial tiles, one [M,N] slab per (batch, split); everything else happens in the reduction
@@ -1103,6 +1190,11 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (QKV output) failed with code %d", (int)r);
         p.tma_mode = 5;
+    } else if (a.dsw_dgu) {
+        TB_CHECK(bn == 128 || bn == 256, "SwiGLU-backward GEMM: tiles of 128 or 256 columns (chunks leave in pairs)");
+        TB_TRY(make_map_out(&tmC, a.dsw_dgu, 2, 2 * a.N, a.M, a.ldgu, 1, 0, 1, 0, true));
+        TB_TRY(make_map_out(&tmR, a.dsw_gu, 2, 2 * a.N, a.M, a.ldgu, 1, 0, 1, 0));
+        p.tma_mode = 2; p.dsw = 1; p.wide16 = 1; p.pair_off = a.N;
     } else if (swiglu) {
         const int F = a.N / 2;
         TB_TRY(make_map_out(&tmC, a.swiglu_h, 2, F, a.M, a.ldh, 1, 0, 1, 0));
@@ -1138,6 +1230,11 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
                 p.tma_res = 1; p.res_scale = p.beta;
             }
             p.tma_mode = p.C32 ? 1 : 2;
+            if (!p.C32 && bn >= 128 && getenv("TB_GEMM_NO_WIDE16") == nullptr) {
+                // bf16 tiles leave in rows of 128 bytes (two chunks per store); tmR is free: no residual with a bf16 output
+                TB_TRY(make_map_out(&tmR, cptr, es, p.N, p.M, ld, p.c_inner, si, nz / p.c_inner, so, true));
+                p.wide16 = 1;
+            }
         }
     }
     {
@@ -1145,6 +1242,7 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
         const double macs = (double)a.M * a.N * a.K * a.batch * (a.causal != CAUSAL_NONE ? 0.5 : 1.0);
         const double out_bytes = a.rope_qkv ? 2.0 * a.M * a.N
                                  : a.ce_mode == 1 ? 16.0 * a.M * ((a.N + 191) / 192)
+                                 : a.dsw_dgu   ? 8.0 * a.M * a.N          // g, u read and dg, du written, bf16
                                  : swiglu      ? (double)a.M * a.N * (a.swiglu_gu ? 3.0 : 1.0)
                                         : (double)a.M * a.N * a.batch * ((a.C32 ? 4.0 : 0.0) + (a.C16 ? 2.0 : 0.0)) *
                                               (a.causal == CAUSAL_SKIP_UPPER ? 0.5 : 1.0);

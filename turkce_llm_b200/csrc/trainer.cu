@@ -66,6 +66,7 @@ struct TbTrainer {
     float *dQ = nullptr, *dK = nullptr, *dV = nullptr;
     bf16 *dres16 = nullptr, *dgu = nullptr, *datt = nullptr, *dO = nullptr, *dS = nullptr, *dqkv = nullptr;
     float* colsum_partial = nullptr;
+    float* colsum_partial2 = nullptr;       // for the column sum that runs on the weight gradients' stream
     float* norm_scratch = nullptr;
     float* swiglu_scratch = nullptr;
     float* splitk_ws = nullptr; size_t splitk_floats = 0;
@@ -93,6 +94,7 @@ struct TbTrainer {
     bool fused_attention = true;   // head_dim <= 64: scores stay on chip
     bool fused_rope = true;        // T % 32 == 0, head_dim 32 or 64: rotation and head split in the QKV GEMM epilogue
     bool fused_ce = true;          // cross-entropy inside the LM-head GEMM epilogues: no [N, V] logits
+    bool fused_dswiglu = false;    // SwiGLU backward in the epilogue of the down-projection's input-gradient GEMM
     bool fused_swiglu = true;      // d_ff % 64 == 0: silu(gate) * up formed in the gate|up GEMM's epilogue
     // TF32 mode (TB_PREC_TF32): every linear-layer GEMM (forward, dX, dW, LM head) reads float32 operands as tf32
     // (kind::tf32); weights are the float32 masters, activations and gradients that feed a GEMM are kept in float32.
@@ -110,6 +112,7 @@ struct TbTrainer {
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_done[4] = {nullptr, nullptr, nullptr, nullptr};   // after each of a layer's four dW
     int pair_ctas = 0;             // CTAs per product of such a pair; 0 = one after the other
+    int pair_ctas_down = 0;        // CTAs of the down-projection's input-gradient product when it carries SwiGLU backward
     cudaEvent_t ev_zero = nullptr; bool zero_pending = false;     // the gradient buffer is being cleared on `side`
 };
 
@@ -173,7 +176,7 @@ int linear_dw(TbTrainer* g, const void* X, const void* dY, float* dW, int M, int
     a.C32 = dW; a.ldc32 = N; a.beta = 1.0f;
     a.splits = 0; a.tf32 = g->tf32;
     if (!pair_on(g)) return gemm(g, a);
-    a.max_ctas = g->ctx->sm_count - g->pair_ctas;
+    a.max_ctas = g->ctx->sm_count - ((which == 0 && g->fused_dswiglu) ? g->pair_ctas_down : g->pair_ctas);
     TB_CUDA(cudaEventRecord(g->ev_fork, g->stream));
     TB_CUDA(cudaStreamWaitEvent(g->side, g->ev_fork, 0));
     TB_TRY(launch_gemm_bf16_ws(g->ctx, a, g->splitk_ws, g->splitk_floats, g->side));
@@ -332,13 +335,30 @@ int backward_layer(TbTrainer* g, int l) {
     // ---- FFN: x3 = x2 + (h @ Wd + bd); dres = dx3
     TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.h32 : (const void*)a.h, dres_op, G32(g, pidx(l, PK_WDOWN)), N, D, F, 0));
     // (b_down's gradient, the column sum of dres, was produced together with dres)
+    if (g->fused_dswiglu) {
+        // dh = dres @ Wd^T never reaches HBM: the product's epilogue turns each tile into dgu with the saved gate|up
+        // projection; the gate|up bias gradient (the column sums of dgu) is taken beside the next products
+        GemmArgs x;
+        x.kind = GEMM_NT; x.A = g->dres16; x.B = WOP(g, pidx(l, PK_WDOWN)); x.M = N; x.N = F; x.K = D; x.lda = D; x.ldb = D;
+        x.splits = 1; x.dsw_gu = a.gu16; x.dsw_dgu = g->dgu; x.ldgu = 2 * F;
+        if (pair_on(g)) x.max_ctas = g->pair_ctas_down;
+        TB_TRY(gemm(g, x));
+    } else {
     TB_TRY(linear_dx(g, dres_op, WOP(g, pidx(l, PK_WDOWN)), g->dh, nullptr, N, D, F));
     // (fused path: the gate|up bias gradient, the column sums of dgu, comes out of the same kernel)
     if (g->fused_swiglu)
         TB_TRY(launch_swiglu_bwd_colsum(c, a.gu16, g->dh, g->dgu, G32(g, pidx(l, PK_BGU)), g->swiglu_scratch, N, F, st));
     else TB_TRY(launch_swiglu_bwd(c, a.gu, g->dh, g->tf32 ? nullptr : g->dgu, N, F, st, g->dgu32));
+    }
     const void* dgu_op = g->tf32 ? (const void*)g->dgu32 : (const void*)g->dgu;
     TB_TRY(linear_dw(g, g->tf32 ? (const void*)a.n2_32 : (const void*)a.n2, dgu_op, G32(g, pidx(l, PK_WGU)), N, 2 * F, D, 1));
+    if (g->fused_dswiglu) {
+        // on the weight gradients' stream when the pair runs side by side (in order behind the product above and ahead
+        // of the layer's last weight gradient, whose event the layer's end waits for); with a scratch buffer of its
+        // own, because the main stream's column sum of dqkv may run at the same time
+        cudaStream_t cs = pair_on(g) ? g->side : st;
+        TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial2, N, 2 * F, cs));
+    }
     if (!g->fused_swiglu) {
         if (g->tf32) TB_TRY(launch_colsum_f32(c, g->dgu32, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
         else TB_TRY(launch_colsum_bf16(c, g->dgu, G32(g, pidx(l, PK_BGU)), g->colsum_partial, N, 2 * F, st));
@@ -578,6 +598,7 @@ int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, i
     g->fused_attention = (D / H) <= 64 && getenv("TB_NO_FUSED_ATTENTION") == nullptr;
     TB_CHECK(!g->tf32 || g->fused_attention, "the TF32 mode needs head_dim <= 64 (the attention core is the fused bf16 kernel)");
     g->fused_swiglu = !g->tf32 && F % 64 == 0 && getenv("TB_NO_FUSED_SWIGLU") == nullptr;
+    g->fused_dswiglu = g->fused_swiglu && getenv("TB_NO_FUSED_DSWIGLU") == nullptr;
     g->fused_rope = !g->tf32 && T % 32 == 0 && (D / H == 32 || D / H == 64) && getenv("TB_NO_FUSED_ROPE") == nullptr;
     g->V = V; g->D = D; g->H = H; g->L = L; g->F = F; g->T = T; g->B = B; g->N = B * T; g->hd = D / H;
     g->Vp = round_up(V, 8);
@@ -655,6 +676,8 @@ int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, i
     {
         const size_t nc = colsum_partial_floats(std::max(3 * D, 2 * F)), nn = rmsnorm_bwd_scratch_floats(D);
         TB_TRY(dalloc(g, &g->colsum_partial, nc));
+        TB_TRY(dalloc(g, &g->colsum_partial2, nc));
+        TB_CUDA(cudaMemset(g->colsum_partial2, 0, nc * 4));
         TB_TRY(dalloc(g, &g->norm_scratch, nn));
         TB_TRY(dalloc(g, &g->swiglu_scratch, swiglu_bwd_scratch_floats(F)));
         TB_CUDA(cudaMemset(g->colsum_partial, 0, nc * 4));     // ticket words start at zero
@@ -701,6 +724,14 @@ int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, i
         if (const char* e = getenv("TB_DW_PAIR_CTAS")) {
             const int v = atoi(e);
             if (v >= 8 && v <= g->ctx->sm_count - 8) g->pair_ctas = v;
+        }
+        // the input-gradient product of the down-projection carries SwiGLU backward in its epilogue and takes 5/8 of
+        // the SMs (measured on the benchmark step: 74 CTAs 5.27 ms, 82 5.27, 90 5.18, 98 5.18, 104 5.11 against 5.09 at 90
+        // on another GPU of the pool)
+        g->pair_ctas_down = g->fused_dswiglu ? g->ctx->sm_count * 5 / 8 : g->pair_ctas;
+        if (const char* e = getenv("TB_DSW_PAIR_CTAS")) {
+            const int v = atoi(e);
+            if (v >= 8 && v <= g->ctx->sm_count - 8) g->pair_ctas_down = v;
         }
     }
 
