@@ -414,10 +414,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         const float sg = __fdividef(1.0f, 1.0f + ex2_approx(-gv[j] * 1.4426950408889634f));
                         hv[j] = gv[j] * sg * uv[j];
                     }
-                    if (lane == 0) tma_store_wait_read<0>();            // the previous chunk's stores have left the buffers
+                    // wide16 (256-column tiles: two chunks per warp): both chunks fill one set of buffers with rows of
+                    // 128 bytes and leave together through 64-column maps
+                    const bool second = p.wide16 && ch == 1;
+                    if (lane == 0 && !second) tma_store_wait_read<0>(); // the previous stores have left the buffers
                     __syncwarp();
                     auto stage_bf16 = [&](uint8_t* base, const float (&o)[32]) {
-                        uint8_t* orow = base + lane * 64;               // 32 x 64 B, 64B swizzle
+                        uint8_t* orow = base + lane * (p.wide16 ? 128 : 64);     // 32 x 64 B, 64B swizzle (wide: 128 B, 128B)
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             uint4 pk;
@@ -427,19 +430,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * j + 6], o[8 * j + 7]);
                             pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
                             pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(orow + ((j ^ ((lane >> 1) & 3)) << 4)) = pk;
+                            const int so = p.wide16 ? (((second ? 4 : 0) + j) ^ (lane & 7)) << 4 : (j ^ ((lane >> 1) & 3)) << 4;
+                            *reinterpret_cast<uint4*>(orow + so) = pk;
                         }
                     };
                     stage_bf16(obuf, hv);
                     if (p.keep_gu) { stage_bf16(obuf + 4096, gv); stage_bf16(rbuf, uv); }
+                    if (p.wide16 && !second) continue;
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
                         if (rows_in) {
-                            tma_store_4d(&tmC, obuf, hj0, gm0, 0, 0);
+                            const int hs = p.wide16 ? hj0 - 32 : hj0;
+                            tma_store_4d(&tmC, obuf, hs, gm0, 0, 0);
                             if (p.keep_gu) {
-                                tma_store_4d(&tmR, obuf + 4096, hj0, gm0, 0, 0);
-                                tma_store_4d(&tmR, rbuf, p.pair_off + hj0, gm0, 0, 0);
+                                tma_store_4d(&tmR, obuf + 4096, hs, gm0, 0, 0);
+                                tma_store_4d(&tmR, rbuf, p.pair_off + hs, gm0, 0, 0);
                             }
                         }
                         tma_store_commit();
@@ -1197,9 +1203,12 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
         p.tma_mode = 2; p.dsw = 1; p.wide16 = 1; p.pair_off = a.N;
     } else if (swiglu) {
         const int F = a.N / 2;
-        TB_TRY(make_map_out(&tmC, a.swiglu_h, 2, F, a.M, a.ldh, 1, 0, 1, 0));
-        if (a.swiglu_gu) TB_TRY(make_map_out(&tmR, a.swiglu_gu, 2, a.N, a.M, a.ldgu, 1, 0, 1, 0));
+        // 256-column tiles: a warp's two chunks are 64 adjacent hidden units and leave in rows of 128 bytes
+        const bool wide = bn == 256 && F % 64 == 0 && getenv("TB_GEMM_NO_WIDE16") == nullptr;
+        TB_TRY(make_map_out(&tmC, a.swiglu_h, 2, F, a.M, a.ldh, 1, 0, 1, 0, wide));
+        if (a.swiglu_gu) TB_TRY(make_map_out(&tmR, a.swiglu_gu, 2, a.N, a.M, a.ldgu, 1, 0, 1, 0, wide));
         else tmR = tmC;
+        p.wide16 = wide ? 1 : 0;
         p.tma_mode = 3; p.pair_off = F; p.keep_gu = a.swiglu_gu ? 1 : 0;
     } else {
         const bool one_out = (p.C32 != nullptr) != (p.C16 != nullptr);
