@@ -631,7 +631,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (lane == 0 && paired) {
                     // rows of 128 bytes: columns gn0 - 32 .. gn0 + 31 (what lies past N is clipped by the hardware)
                     if (rows_in && gn0 - 32 < p.N) {
-                        if (p.dsw) {
+                        if (p.tma_mode == 5) {                // the pair is one head's 64 values of 32 positions
+                            const int g0 = gn0 - 32;
+                            const int which = g0 >= 2 * rope_D ? 2 : (g0 >= rope_D ? 1 : 0);
+                            tma_store_5d(&tmC, obuf + b * 4096, 0, rope_t0, (g0 - which * rope_D) >> 6, rope_b, which);
+                        } else if (p.dsw) {
                             tma_store_4d(&tmC, obuf, gn0 - 32, gm0, 0, 0);
                             tma_store_4d(&tmC, obuf + 4096, p.pair_off + gn0 - 32, gm0, 0, 0);
                         } else {
@@ -1189,11 +1193,14 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
         const cuuint64_t hd = (cuuint64_t)a.rope_hd, T = (cuuint64_t)a.rope_T, H = (cuuint64_t)a.rope_H, Bn = (cuuint64_t)(a.M / a.rope_T);
         cuuint64_t dims[5] = {hd, T, H, Bn, 3};
         cuuint64_t strides[4] = {hd * 2, T * hd * 2, H * T * hd * 2, Bn * H * T * hd * 2};
-        cuuint32_t box[5] = {32u, 32u, 1u, 1u, 1u};
+        // head dim 64 on 128- or 256-column tiles: a warp's chunk pairs are whole heads and leave in rows of 128 bytes
+        const bool wide = a.rope_hd == 64 && (bn == 128 || bn == 256) && getenv("TB_GEMM_NO_WIDE16") == nullptr;
+        cuuint32_t box[5] = {wide ? 64u : 32u, 32u, 1u, 1u, 1u};
         cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
         CUresult r = enc(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, a.rope_qkv, dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        p.wide16 = wide ? 1 : 0;
         TB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (QKV output) failed with code %d", (int)r);
         p.tma_mode = 5;
     } else if (a.dsw_dgu) {
