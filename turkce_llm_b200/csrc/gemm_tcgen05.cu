@@ -64,6 +64,7 @@ struct GemmParams {
     int M, N, K;
     int batch, splits;
     int mt, nt;                 // tiles along M, N
+    int kb_total, kb_per;       // K slices in all, and per split
     int a_mn, b_mn;             // 1 = operand tile is MN-major (stored transposed)
     int causal;
     float* C32; long long ldc32, strideC32, strideC32_in;
@@ -96,14 +97,20 @@ struct TileCoord { int z, s, m0, n0, kb0, kb1; bool skip; };
 template <int BN, int BKE, int TILE_M = BM>
 __device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t, int row_off = 0) {
     TileCoord c;
+    // (integer divisions by run-time values cost ~100 cycles each on the path to a tile's first load: the K-slice
+    // counts come from the host, and the common single-split, single-batch launch skips two more)
     const int n_idx = t % p.nt; t /= p.nt;
-    const int m_idx = t % p.mt; t /= p.mt;
-    c.s = t % p.splits;
-    c.z = t / p.splits;
+    int m_idx = t;
+    c.s = 0; c.z = 0;
+    if (p.batch * p.splits != 1) {
+        m_idx = t % p.mt; t /= p.mt;
+        c.s = t % p.splits;
+        c.z = t / p.splits;
+    }
     c.m0 = m_idx * TILE_M + row_off;
     c.n0 = n_idx * BN;
-    const int kb_total = (p.K + BKE - 1) / BKE;
-    const int kb_per = (kb_total + p.splits - 1) / p.splits;
+    const int kb_total = p.kb_total;
+    const int kb_per = p.kb_per;
     c.kb0 = c.s * kb_per;
     c.kb1 = min(kb_total, c.kb0 + kb_per);
     c.skip = false;
@@ -177,6 +184,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (PAIR) { tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish_pair(); }
         else      { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
     }
+    // every role's first tile, worked out while the barriers and the tensor memory are being set up
+    const TileCoord c_first = tile_of<BN, BKE, TILE_M>(p, worker < total_tiles ? worker : 0, row_off);
     tc_fence_before();
     __syncthreads();
     if (PAIR) cluster_sync();          // both CTAs' barriers exist before either signals the other's
@@ -190,7 +199,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int t = worker; t < total_tiles && ok; t += nworkers) {
-                const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
+                const TileCoord c = t == worker ? c_first : tile_of<BN, BKE, TILE_M>(p, t, row_off);
                 if (c.skip) continue;
                 for (int kb = c.kb0; kb < c.kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -264,7 +273,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int it = 0;
             bool ok = true;
             for (int t = worker; t < total_tiles && ok; t += nworkers) {
-                const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
+                const TileCoord c = t == worker ? c_first : tile_of<BN, BKE, TILE_M>(p, t, row_off);
                 if (c.skip) continue;
                 const int buf = it % NBUF;
                 const uint32_t acc_phase = (uint32_t)(it / NBUF) & 1u;
@@ -315,7 +324,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int it = 0;
         bool ok = true;
         for (int t = worker; t < total_tiles && ok; t += nworkers) {
-            const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
+            const TileCoord c = t == worker ? c_first : tile_of<BN, BKE, TILE_M>(p, t, row_off);
             if (c.skip) continue;
             const int buf = it % NBUF;
             const uint32_t acc_phase = (uint32_t)(it / NBUF) & 1u;
@@ -676,7 +685,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int it = 0;
         bool ok = true;
         for (int t = worker; t < total_tiles && ok; t += nworkers) {
-            const TileCoord c = tile_of<BN, BKE, TILE_M>(p, t, row_off);
+            const TileCoord c = t == worker ? c_first : tile_of<BN, BKE, TILE_M>(p, t, row_off);
             if (c.skip) continue;
             const int buf = it % NBUF;
             const uint32_t acc_phase = (uint32_t)(it / NBUF) & 1u;
@@ -1151,6 +1160,8 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch; p.splits = splits;
     p.mt = pair ? (a.M + 2 * BM - 1) / (2 * BM) : (a.M + BM - 1) / BM;      // a pair owns 256 rows
     p.nt = (a.N + bn - 1) / bn;
+    p.kb_total = (a.K + bke - 1) / bke;
+    p.kb_per = (p.kb_total + splits - 1) / splits;
     p.a_mn = a_mn; p.b_mn = b_mn; p.causal = (int)a.causal;
     p.dsw = 0; p.wide16 = 0;
     p.err = ctx->d_err;
