@@ -2,7 +2,7 @@
 """Benchmark of the matmul hot path: training tokens/s of the 33.49M-parameter decoder.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
-    python bench.py --only gemm|attention|decode|lmhead ...      (single-kernel programs, see --help)
+    python bench.py --only gemm|timeline|attention|decode|lmhead ...      (single-kernel programs, see --help)
 
 Workload (N=1): one full training step -- forward, backward, gradient-norm clip, Adam -- of the
 12-layer d_model-384 decoder at batch 8 x context 1024 with N(0, 0.02) weights and Zipf(1.1) token
@@ -966,6 +966,7 @@ def run_reference(args):
 def run_only(args):
     """Small single-kernel programs (also the commands of the ncu captures): python bench.py --only <what> <numbers>
          gemm M N K kind [iters] [out=f32|bf16] [tile_n] [splits]      kind: 0 = NN, 1 = NT, 2 = TN
+         timeline M N K kind [out=f32|bf16] [tile_n]     (a library built with TB_NVCC_FLAGS=-DTB_GEMM_STAMPS)
          attention B H T hd [iters]
          decode S prompt_len new_tokens
          lmhead S [V] [K] [iters] [copies]"""
@@ -995,6 +996,46 @@ def run_only(args):
         us = graph_time_us(run, iters)
         print("gemm kind=%d %dx%dx%d out=%s tile_n=%d splits=%d: %.2f us per call in a CUDA graph = %.1f TFLOP/s"
               % (kind, M, N, K, out, tile_n, splits, us, 2.0 * M * N * K / us / 1e6), flush=True)
+    elif args.only == "timeline":
+        # where one GEMM launch spends its time: needs a library built with TB_NVCC_FLAGS=-DTB_GEMM_STAMPS
+        import ctypes as C
+        L = lib.load()
+        if not hasattr(L, "tb_debug_gemm_stamps"):
+            print("timeline: the library was built without -DTB_GEMM_STAMPS", flush=True)
+            return 1
+        M, N, K, kind = (int(x) for x in a[:4])
+        out = a[4] if len(a) > 4 else "f32"
+        tile_n = int(a[5]) if len(a) > 5 else 0
+        a_shape = (K, M) if kind == 2 else (M, K)
+        b_shape = (N, K) if kind == 1 else (K, N)
+        sets = []
+        for _ in range(4):          # 4 operand sets in turn: the last launch does not find its operands in L2 by luck
+            A = torch.randn(a_shape, device="cuda").to(torch.bfloat16)
+            B = (torch.randn(b_shape, device="cuda") * 0.02).to(torch.bfloat16)
+            C32 = torch.empty(M, N, device="cuda") if out == "f32" else None
+            C16 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16) if out == "bf16" else None
+            sets.append((A, B, C32, C16))
+        buf = np.zeros((160, 16), dtype=np.uint64)
+        for i in range(6):
+            A, B, C32, C16 = sets[i % 4]
+            if i == 5:
+                lib.sync_check()
+                L.tb_debug_gemm_stamps(buf.ctypes.data_as(C.c_void_p))        # clears what the earlier launches left
+            lib.gemm_bf16(kind, A, B, M, N, K, a_shape[1], b_shape[1], C32=C32, ldc32=N, C16=C16, ldc16=N, splits=1,
+                          tile_n=tile_n)
+        lib.sync_check()
+        L.tb_debug_gemm_stamps(buf.ctypes.data_as(C.c_void_p))
+        ts = buf.astype(np.int64)
+        t0 = ts[:, 0][ts[:, 0] > 0].min()
+        names = ["entry", "set-up done", "first loads issued", "all loads issued", "first operands arrived",
+                 "first tile's products done", "last tile's products done", "epilogue: first accumulator seen",
+                 "epilogue: first tile stored", "epilogue: last tile stored", "stores have left shared memory"]
+        print("gemm kind=%d %dx%dx%d out=%s tile_n=%d: %d CTAs; us after the first CTA's entry (min / median / max over CTAs)"
+              % (kind, M, N, K, out, tile_n, int((ts[:, 0] > 0).sum())), flush=True)
+        for i, n in enumerate(names):
+            col = (ts[:, i][ts[:, i] > 0] - t0) / 1e3
+            if len(col):
+                print("  %-34s %6.2f %6.2f %6.2f" % (n, col.min(), float(np.median(col)), col.max()), flush=True)
     elif args.only == "attention":
         B, H, T, hd = (int(x) for x in a[:4])
         iters = int(a[4]) if len(a) > 4 else 10
@@ -1040,7 +1081,7 @@ def main():
     ap.add_argument("--global-batch", type=int, default=0,
                     help="fixed global batch in sequences (strong scaling, e.g. 128); default: 8 sequences per GPU")
     ap.add_argument("--no-extras", action="store_true", help="headline record only (no c1/c3/c4/c5 sub-records)")
-    ap.add_argument("--only", choices=["gemm", "attention", "decode", "lmhead"], default=None, help=run_only.__doc__)
+    ap.add_argument("--only", choices=["gemm", "timeline", "attention", "decode", "lmhead"], default=None, help=run_only.__doc__)
     ap.add_argument("numbers", nargs="*")
     args = ap.parse_args()
     if args.only:

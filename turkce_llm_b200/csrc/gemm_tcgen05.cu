@@ -92,6 +92,20 @@ struct GemmParams {
     int* err;
 };
 
+// Built with -DTB_GEMM_STAMPS (TB_NVCC_FLAGS of the build script), every CTA records %globaltimer at the points of its
+// life named in tb_debug_gemm_stamps' header comment; `python bench.py --only timeline ...` prints them.  Off by default.
+#ifdef TB_GEMM_STAMPS
+__device__ unsigned long long g_gemm_stamps[160][16];
+__device__ __forceinline__ void gemm_stamp(int slot) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    if (blockIdx.x < 160) g_gemm_stamps[blockIdx.x][slot] = t;
+}
+#define TS(slot) gemm_stamp(slot)
+#else
+#define TS(slot) do { } while (0)
+#endif
+
 struct TileCoord { int z, s, m0, n0, kb0, kb1; bool skip; };
 
 template <int BN, int BKE, int TILE_M = BM>
@@ -160,13 +174,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint64_t* empty_bar = bars + STAGES;          // [STAGES]
     uint64_t* acc_full = bars + 2 * STAGES;       // [2]
     uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
-    uint64_t* res_bar = bars + 2 * STAGES + 4;    // [2][EPI_WARPS] (the second set: SwiGLU backward's other g / u buffer)
+    uint64_t* res_bar = bars + 2 * STAGES + 4;    // [EPI_WARPS]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + EPI_WARPS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_tiles = p.batch * p.splits * p.mt * p.nt;
+    if (threadIdx.x == 0) TS(0);
 
     // Prologue: nothing here reads or writes memory an earlier kernel of the stream produces, so it
     // may overlap that kernel's tail (programmatic dependent launch); pdl_wait() below is the fence.
@@ -176,7 +191,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.tma_mode != 0 && p.tma_mode != 4) tma_prefetch_desc(&tmC);
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], PAIR ? 2 * EPI_WARPS : EPI_WARPS); }
-        for (int i = 0; i < 2 * EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
+        for (int i = 0; i < EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -191,6 +206,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (PAIR) cluster_sync();          // both CTAs' barriers exist before either signals the other's
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) TS(1);
     pdl_wait();
 
     if (warp == 0) {
@@ -233,8 +249,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if (t == worker && kb == c.kb0) TS(2);
                 }
             }
+            TS(3);
             if (PAIR && ok) {
                 // every release of a stage must have arrived (from rank 0's commits) before this CTA may exit
                 for (int i = 0; i < STAGES && ok; ++i) {
@@ -282,6 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                 for (int kb = c.kb0; kb < c.kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    if (it == 0 && kb == c.kb0) TS(4);
                     tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {          // 4 UMMAs of 32 bytes of K per 128-byte slice
@@ -302,8 +321,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (!ok) break;
                 if (PAIR) umma_commit_pair(&acc_full[buf]);      // accumulator complete (each CTA reads its own 128 rows)
                 else      umma_commit(&acc_full[buf]);
+                if (it == 0) TS(5);
                 ++it;
             }
+            TS(6);
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 2); }
         }
     } else if (p.tma_mode != 0) {
@@ -480,6 +501,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             };
             if (p.dsw && lane == 0 && rows_in && col0 < p.N) dsw_fetch(0);
             if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
+            if (warp == 2 && lane == 0 && it == 0) TS(7);
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
 #pragma unroll 1
@@ -671,9 +693,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) { if (PAIR) mbar_arrive_leader(&acc_empty[buf]); else mbar_arrive(&acc_empty[buf]); }
+            if (warp == 2 && lane == 0) { if (it == 0) TS(8); TS(9); }
             ++it;
         }
         if (lane == 0) tma_store_wait_read<0>();
+        if (warp == 2 && lane == 0) TS(10);
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 3); }
     } else {
         // ------------------------------------------- epilogue, generic (any alignment)
@@ -1406,6 +1430,19 @@ int static_setup(int dev, StaticSetup** out) {
 }  // namespace
 
 }  // namespace tb
+
+#ifdef TB_GEMM_STAMPS
+// host[160][16] <- the stamps of the last launch (ns of %globaltimer; 0 = not reached), then cleared.  Slots per CTA:
+// 0 entry, 1 barriers and tensor memory set up, 2 first tile's first loads issued, 3 all loads issued, 4 first operands
+// arrived, 5 first tile's products committed, 6 last tile's products committed, 7 epilogue sees the first accumulator,
+// 8 first tile stored, 9 last tile stored, 10 the stores have left shared memory.  (TMA-store epilogue, warp 2.)
+extern "C" int tb_debug_gemm_stamps(unsigned long long* host) {
+    int rc = (int)cudaMemcpyFromSymbol(host, tb::g_gemm_stamps, sizeof(tb::g_gemm_stamps));
+    static unsigned long long zero[160][16];
+    rc |= (int)cudaMemcpyToSymbol(tb::g_gemm_stamps, zero, sizeof(zero));
+    return rc;
+}
+#endif
 
 extern "C" int tb_gemm_bf16_splitk_static(int kind, const void* d_A, const void* d_B, int M, int N, int K,
                                           int64_t lda, int64_t ldb, float* d_C32, int64_t ldc32,
