@@ -727,7 +727,7 @@ int tb_trainer_create_prec(TbTrainer** out, int V, int D, int H, int L, int F, i
         }
         // the input-gradient product of the down-projection carries SwiGLU backward in its epilogue and takes 5/8 of
         // the SMs (measured on the benchmark step: 74 CTAs 5.27 ms, 82 5.27, 90 5.18, 98 5.18, 104 5.11 against 5.09 at 90
-        // on another GPU of the pool)
+        // on a second GPU)
         g->pair_ctas_down = g->fused_dswiglu ? g->ctx->sm_count * 5 / 8 : g->pair_ctas;
         if (const char* e = getenv("TB_DSW_PAIR_CTAS")) {
             const int v = atoi(e);
