@@ -141,7 +141,14 @@ __device__ __forceinline__ TileCoord tile_of(const GemmParams& p, int t, int row
 
 // TF32 = true: float32 operands in shared memory, kind::tf32 (the tensor core reads the top 19 bits),
 // K slices of 32 elements; everything else is shared with the bf16 path.
-template <int BN, bool TF32, bool PAIR = false>
+// EPI: the epilogue the instantiation is compiled for.  EPI_ANY keeps every mode behind run-time checks (one kernel
+// for all of them: its epilogue loop then steps over the code of the modes it does not run, ~40 KB of instructions, and
+// a 32-column chunk costs ~0.15 us more in instruction fetches); the other values fix the mode at compile time and
+// drop the rest -- measured on an [8192 x 384 x 1152] launch: last tile's epilogue 2.42 -> 1.89 us (float32 out),
+// 2.02 -> 1.54 us (bf16 out).
+enum { EPI_ANY = 0, EPI_F32, EPI_BF16, EPI_SWIGLU, EPI_CE1, EPI_ROPE, EPI_CE2, EPI_DSW };
+
+template <int BN, bool TF32, bool PAIR = false, int EPI = EPI_ANY>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
@@ -181,6 +188,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_tiles = p.batch * p.splits * p.mt * p.nt;
+    // the epilogue mode: constants in a specialised instantiation, the launch's parameters in the general one
+    constexpr bool ANY = EPI == EPI_ANY;
+    const bool m_generic = ANY && p.tma_mode == 0;                       // predicated stores, any alignment
+    const bool m_f32 = ANY ? p.tma_mode == 1 : EPI == EPI_F32;           // float32 tiles by TMA
+    const bool m_swiglu = ANY ? p.tma_mode == 3 : EPI == EPI_SWIGLU;
+    const bool m_ce1 = ANY ? p.tma_mode == 4 : EPI == EPI_CE1;
+    const bool m_rope = ANY ? p.tma_mode == 5 : EPI == EPI_ROPE;
+    const bool m_ce2 = ANY ? p.ce_mode == 2 : EPI == EPI_CE2;
+    const bool m_dsw = ANY ? p.dsw != 0 : EPI == EPI_DSW;
+    const bool m_res = (ANY || EPI == EPI_F32) && p.tma_res != 0;        // a residual / previous-C tile only with float32 tiles
+    const bool m_bias = (ANY || EPI == EPI_F32 || EPI == EPI_BF16 || EPI == EPI_ROPE) && p.bias != nullptr;
+    const bool m_wide = (ANY || EPI == EPI_BF16 || EPI == EPI_ROPE || EPI == EPI_CE2) ? p.wide16 != 0 : EPI == EPI_DSW;
     if (threadIdx.x == 0) TS(0);
 
     // Prologue: nothing here reads or writes memory an earlier kernel of the stream produces, so it
@@ -188,7 +207,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
-        if (p.tma_mode != 0 && p.tma_mode != 4) tma_prefetch_desc(&tmC);
+        if (!m_generic && !m_ce1) tma_prefetch_desc(&tmC);
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], PAIR ? 2 * EPI_WARPS : EPI_WARPS); }
         for (int i = 0; i < EPI_WARPS; ++i) mbar_init(&res_bar[i], 1);
@@ -241,7 +260,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < BNL / MNW; ++j) {
                             int n = BN == 384 ? c.n0 + 128 * j + 64 * (int)rank : nb0 + j * MNW;
-                            if (p.tma_mode == 3) {     // paired tile: first half gate columns, second half their up columns
+                            if (m_swiglu) {            // paired tile: first half gate columns, second half their up columns
                                 const int jj = (int)rank * (BNL / MNW) + j;      // box index inside the whole tile
                                 n = (c.n0 >> 1) + (jj < BN / MNW / 2 ? jj * MNW : p.pair_off + (jj - BN / MNW / 2) * MNW);
                             }
@@ -327,7 +346,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             TS(6);
             if (!ok) { *abort_flag = 1; atomicExch(p.err, 2); }
         }
-    } else if (p.tma_mode != 0) {
+    } else if (!m_generic) {
         // ------------------------------------------------ epilogue, tile stores by TMA
         // Per 32-column chunk: tcgen05.ld -> registers (+bias, +scaled residual tile) -> this warp's
         // 32 x 128 B staging buffer in the 128B-swizzle pattern -> one TMA store (clipped at the
@@ -354,7 +373,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int zo = zc / p.c_inner, zi = zc % p.c_inner;
             const int gm0 = c.m0 + q * 32;
             const bool rows_in = gm0 < p.M;
-            if (p.tma_mode == 4) {
+            if (m_ce1) {
                 // Cross-entropy pass 1: running max and sum of exponentials of this warp's 32 rows over its
                 // half of the tile's columns (online update per 32-column chunk); nothing leaves but the pair
                 if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
@@ -409,7 +428,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 ++it;
                 continue;
             }
-            if (p.tma_mode == 3) {
+            if (m_swiglu) {
                 // SwiGLU: this warp owns 32 rows x BN/4 hidden units: gate in accumulator columns half*BN/4..,
                 // up in columns BN/2 + half*BN/4..; h = silu(g) * u leaves as bf16, g and u (bf16) on request
                 if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
@@ -488,8 +507,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // mode 5: position of this thread's row, and of the 32-row chunk, inside its sequence (once per tile)
             const int rope_D = p.rope_H * p.rope_hd, rope_shift = p.rope_hd == 64 ? 6 : 5;
             int rope_b = 0, rope_t0 = 0, rope_t = 0;
-            if (p.tma_mode == 5) { rope_b = gm0 / p.rope_T; rope_t0 = gm0 - rope_b * p.rope_T; rope_t = rope_t0 + lane; }
-            if (p.tma_res && lane == 0 && rows_in && col0 < p.N) {
+            if (m_rope) { rope_b = gm0 / p.rope_T; rope_t0 = gm0 - rope_b * p.rope_T; rope_t = rope_t0 + lane; }
+            if (m_res && lane == 0 && rows_in && col0 < p.N) {
                 mbar_expect_tx(rbar, 4096);
                 tma_load_4d(rbuf, &tmR, rbar, col0, gm0, 0, c.z);
             }
@@ -499,7 +518,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 tma_load_4d(rbuf, &tmR, rbar, col0 + ch * 32, gm0, 0, 0);
                 tma_load_4d(rbuf + 2048, &tmR, rbar, p.pair_off + col0 + ch * 32, gm0, 0, 0);
             };
-            if (p.dsw && lane == 0 && rows_in && col0 < p.N) dsw_fetch(0);
+            if (m_dsw && lane == 0 && rows_in && col0 < p.N) dsw_fetch(0);
             if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag)) { ok = false; break; }
             if (warp == 2 && lane == 0 && it == 0) TS(7);
             tc_fence_after();
@@ -508,13 +527,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int ch = 0; ch < NCH; ++ch) {
                 // a store unit is one chunk, or in wide16 mode a pair of chunks (an odd last chunk stays alone);
                 // with dsw a unit fills both output buffers (dg | du), else the units alternate between them
-                const bool paired = p.wide16 && ((ch & 1) || ch + 1 < NCH);
+                const bool paired = m_wide && ((ch & 1) || ch + 1 < NCH);
                 const bool second = paired && (ch & 1);
-                const uint32_t b = p.dsw ? 0u : (cnt & 1u);
+                const uint32_t b = m_dsw ? 0u : (cnt & 1u);
                 const int gn0 = col0 + ch * 32;
                 const bool active = rows_in && gn0 < p.N;
                 if (lane == 0 && !second) {                   // the unit's output buffer has been read out
-                    if (p.dsw) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
+                    if (m_dsw) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
                 }
                 __syncwarp();
                 uint32_t v[32];
@@ -528,7 +547,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 float o[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(v[j]) * p.alpha;
-                if (p.bias) {
+                if (m_bias) {
                     if (p.bias_vec && gn0 + 32 <= p.N) {
                         const float4* b4 = reinterpret_cast<const float4*>(p.bias + gn0);
 #pragma unroll
@@ -541,7 +560,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         for (int j = 0; j < 32; ++j) if (gn0 + j < p.N) o[j] += __ldg(p.bias + gn0 + j);
                     }
                 }
-                if (p.tma_res && active) {
+                if (m_res && active) {
                     if (!mbar_wait(rbar, rphase, abort_flag)) { ok = false; break; }
                     rphase ^= 1u;
                     const uint8_t* rrow = rbuf + lane * 128;
@@ -559,7 +578,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         tma_load_4d(rbuf, &tmR, rbar, gn0 + 32, gm0, 0, c.z);
                     }
                 }
-                if (p.tma_mode == 5) {
+                if (m_rope) {
                     // position embedding on the q and k columns: pairs (2k, 2k+1) of a head rotate by the
                     // angle of (position, k); this chunk is 32 consecutive head-dim values of one head
                     if (gn0 < 2 * rope_D) {
@@ -579,7 +598,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         }
                     }
                 }
-                if (p.ce_mode == 2) {
+                if (m_ce2) {
                     // cross-entropy pass 2: the logits turn into their gradient before they are stored
                     constexpr float LOG2E = 1.4426950408889634f;
                     const int row = gm0 + lane;
@@ -592,7 +611,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         o[j] = pr * p.ce_scale;
                     }
                 }
-                if (p.dsw) {
+                if (m_dsw) {
                     // SwiGLU backward (the reference's k_swiglu_bwd on the product's tile, cuda/train_kernels.cu:709-721):
                     // o = dh (zero in rows past M, whose operand rows the tile loads fill with zeros); with the saved
                     // g, u of the same rows and hidden units, a = g s, s = sigmoid(g):
@@ -635,7 +654,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         __syncwarp();
                         if (lane == 0 && ch + 1 < NCH && gn0 + 32 < p.N) dsw_fetch(ch + 1);
                     }
-                } else if (p.tma_mode == 1) {
+                } else if (m_f32) {
                     uint8_t* orow = obuf + b * 4096 + lane * 128;
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
@@ -662,11 +681,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (lane == 0 && paired) {
                     // rows of 128 bytes: columns gn0 - 32 .. gn0 + 31 (what lies past N is clipped by the hardware)
                     if (rows_in && gn0 - 32 < p.N) {
-                        if (p.tma_mode == 5) {                // the pair is one head's 64 values of 32 positions
+                        if (m_rope) {                         // the pair is one head's 64 values of 32 positions
                             const int g0 = gn0 - 32;
                             const int which = g0 >= 2 * rope_D ? 2 : (g0 >= rope_D ? 1 : 0);
                             tma_store_5d(&tmC, obuf + b * 4096, 0, rope_t0, (g0 - which * rope_D) >> 6, rope_b, which);
-                        } else if (p.dsw) {
+                        } else if (m_dsw) {
                             tma_store_4d(&tmC, obuf, gn0 - 32, gm0, 0, 0);
                             tma_store_4d(&tmC, obuf + 4096, p.pair_off + gn0 - 32, gm0, 0, 0);
                         } else {
@@ -675,11 +694,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                     tma_store_commit();
                 } else if (lane == 0) {
-                    if (active && p.tma_mode == 5) {
+                    if (active && m_rope) {
                         const int which = gn0 >= 2 * rope_D ? 2 : (gn0 >= rope_D ? 1 : 0);
                         const int cin = gn0 - which * rope_D;
                         tma_store_5d(&tmC, obuf + b * 4096, cin & (p.rope_hd - 1), rope_t0, cin >> rope_shift, rope_b, which);
-                    } else if (active && p.dsw) {
+                    } else if (active && m_dsw) {
                         tma_store_4d(&tmC, obuf + b * 4096, gn0, gm0, 0, 0);
                         tma_store_4d(&tmC, obuf + b * 4096 + 2048, p.pair_off + gn0, gm0, 0, 0);
                     } else if (active) {
@@ -1099,14 +1118,14 @@ int choose_splits(const DeviceCtx* ctx, const GemmArgs& a, int bn) {
     return (kb_total + kb_per - 1) / kb_per;     // no empty split
 }
 
-template <int BN, bool TF32, bool PAIR = false>
+template <int BN, bool TF32, bool PAIR = false, int EPI = EPI_ANY>
 static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, const CUtensorMap& tmA,
                        const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmR,
                        cudaStream_t stream) {
     using Cfg = GemmCfg<BN, PAIR>;
     static bool attr_set[64] = {false};
     if (!attr_set[ctx->device & 63]) {
-        TB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, TF32, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, TF32, PAIR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
         attr_set[ctx->device & 63] = true;
     }
@@ -1120,12 +1139,45 @@ static int launch_impl(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, c
         grid = (int)(total < sms ? total : sms);
     }
     if (grid < 1) grid = PAIR ? 2 : 1;
-    TB_CUDA(launch_kernel_cluster((gemm_bf16_kernel<BN, TF32, PAIR>), dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES,
+    TB_CUDA(launch_kernel_cluster((gemm_bf16_kernel<BN, TF32, PAIR, EPI>), dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES,
                                   stream, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, p));
     TB_CUDA(cudaGetLastError());
     ctx->launches++;
     prof_close(ctx, stream);
     return 0;
+}
+
+// The instantiation compiled for the launch's epilogue where one exists (bf16 operands; the fused epilogues on the tile
+// widths the trainer uses them with), else the general kernel.
+template <int BN, bool PAIR>
+static int launch_bf16(DeviceCtx* ctx, const GemmArgs& a, const GemmParams& p, const CUtensorMap& tmA,
+                       const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmR, cudaStream_t stream) {
+    static const bool general_only = getenv("TB_GEMM_GENERAL_KERNEL") != nullptr;
+    int epi = EPI_ANY;
+    if (!general_only) {
+        switch (p.tma_mode) {
+            case 1: epi = EPI_F32; break;
+            case 2: epi = p.ce_mode == 2 ? EPI_CE2 : p.dsw ? EPI_DSW : EPI_BF16; break;
+            case 3: epi = EPI_SWIGLU; break;
+            case 4: epi = EPI_CE1; break;
+            case 5: epi = EPI_ROPE; break;
+            default: break;
+        }
+    }
+    if (epi == EPI_F32) return launch_impl<BN, false, PAIR, EPI_F32>(ctx, a, p, tmA, tmB, tmC, tmR, stream);
+    if (epi == EPI_BF16) return launch_impl<BN, false, PAIR, EPI_BF16>(ctx, a, p, tmA, tmB, tmC, tmR, stream);
+    if constexpr (BN == 128 || BN == 256) {
+        if (epi == EPI_SWIGLU) return launch_impl<BN, false, PAIR, EPI_SWIGLU>(ctx, a, p, tmA, tmB, tmC, tmR, stream);
+        if (epi == EPI_DSW) return launch_impl<BN, false, PAIR, EPI_DSW>(ctx, a, p, tmA, tmB, tmC, tmR, stream);
+    }
+    if constexpr (BN == 192 || BN == 256) {
+        if (epi == EPI_CE1) return launch_impl<BN, false, PAIR, EPI_CE1>(ctx, a, p, tmA, tmB, tmC, tmR, stream);
+        if (epi == EPI_CE2) return launch_impl<BN, false, PAIR, EPI_CE2>(ctx, a, p, tmA, tmB, tmC, tmR, stream);
+    }
+    if constexpr (BN == 128) {
+        if (epi == EPI_ROPE) return launch_impl<BN, false, PAIR, EPI_ROPE>(ctx, a, p, tmA, tmB, tmC, tmR, stream);
+    }
+    return launch_impl<BN, false, PAIR, EPI_ANY>(ctx, a, p, tmA, tmB, tmC, tmR, stream);
 }
 
 static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, float* ws, cudaStream_t stream) {
@@ -1309,17 +1361,17 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
         }
     }
     if (pair && bn == 384) {
-        TB_TRY((launch_impl<384, false, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        TB_TRY((launch_bf16<384, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
     } else if (pair) {
-        TB_TRY((launch_impl<256, false, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        TB_TRY((launch_bf16<256, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
     } else if (a.tf32) {
         if (bn == 64)       TB_TRY((launch_impl<64, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
         else if (bn == 192) TB_TRY((launch_impl<192, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
         else                TB_TRY((launch_impl<128, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
     } else {
-        if (bn == 64)       TB_TRY((launch_impl<64, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
-        else if (bn == 192) TB_TRY((launch_impl<192, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
-        else                TB_TRY((launch_impl<128, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        if (bn == 64)       TB_TRY((launch_bf16<64, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        else if (bn == 192) TB_TRY((launch_bf16<192, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        else                TB_TRY((launch_bf16<128, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
     }
 
     if (splits > 1) {
