@@ -392,9 +392,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     tmem_ld32(t_row + (uint32_t)(ch * 32), v);
                     tmem_ld_wait();
                     float cm = -INFINITY;
-                    if (gn0 + 32 <= p.N) {
+                    const bool full = gn0 + 32 <= p.N;
+                    if (full) {
+                        // four independent chains instead of one of 32 dependent maxima
+                        float c0 = __uint_as_float(v[0]), c1 = __uint_as_float(v[1]), c2 = __uint_as_float(v[2]), c3 = __uint_as_float(v[3]);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) cm = fmaxf(cm, __uint_as_float(v[j]));
+                        for (int j = 4; j < 32; j += 4) {
+                            c0 = fmaxf(c0, __uint_as_float(v[j]));     c1 = fmaxf(c1, __uint_as_float(v[j + 1]));
+                            c2 = fmaxf(c2, __uint_as_float(v[j + 2])); c3 = fmaxf(c3, __uint_as_float(v[j + 3]));
+                        }
+                        cm = fmaxf(fmaxf(c0, c1), fmaxf(c2, c3));
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) cm = fmaxf(cm, gn0 + j < p.N ? __uint_as_float(v[j]) : -INFINITY);
@@ -407,6 +414,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const float m_new = fmaxf(m_run, cm);
                     const float mb = m_new * LOG2E;
                     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+                    if (full) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            s0 += ex2_approx(__uint_as_float(v[j])     * LOG2E - mb);
+                            s1 += ex2_approx(__uint_as_float(v[j + 1]) * LOG2E - mb);
+                            s2 += ex2_approx(__uint_as_float(v[j + 2]) * LOG2E - mb);
+                            s3 += ex2_approx(__uint_as_float(v[j + 3]) * LOG2E - mb);
+                        }
+                    } else
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         s0 += gn0 + j     < p.N ? ex2_approx(__uint_as_float(v[j])     * LOG2E - mb) : 0.0f;
@@ -604,11 +620,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const int row = gm0 + lane;
                     const float lb = row < p.M ? __ldg(p.ce_lse + row) * LOG2E : 0.0f;
                     const int tgt = row < p.M ? (int)__ldg(p.ce_targets + row) : -1;
+                    if (gn0 + 32 <= p.N && (tgt < gn0 || tgt >= gn0 + 32)) {
+                        // a whole chunk without the row's target column (all but one chunk of a row, and the ragged last)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float pr = gn0 + j < p.N ? ex2_approx(o[j] * LOG2E - lb) : 0.0f;
-                        if (gn0 + j == tgt) pr -= 1.0f;
-                        o[j] = pr * p.ce_scale;
+                        for (int j = 0; j < 32; ++j) o[j] = ex2_approx(o[j] * LOG2E - lb) * p.ce_scale;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float pr = gn0 + j < p.N ? ex2_approx(o[j] * LOG2E - lb) : 0.0f;
+                            if (gn0 + j == tgt) pr -= 1.0f;
+                            o[j] = pr * p.ce_scale;
+                        }
                     }
                 }
                 if (m_dsw) {
