@@ -1387,9 +1387,17 @@ static int launch_core(DeviceCtx* ctx, const GemmArgs& a, int bn, int splits, fl
     } else if (pair) {
         TB_TRY((launch_bf16<256, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
     } else if (a.tf32) {
-        if (bn == 64)       TB_TRY((launch_impl<64, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
-        else if (bn == 192) TB_TRY((launch_impl<192, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
-        else                TB_TRY((launch_impl<128, true>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
+        // (float32 operands read as tf32: plain float32 / bf16 tiles have instantiations of their own, the rest is general)
+        static const bool general_only = getenv("TB_GEMM_GENERAL_KERNEL") != nullptr;
+        const int epi = general_only ? EPI_ANY : p.tma_mode == 1 ? EPI_F32 : (p.tma_mode == 2 && p.ce_mode == 0 && !p.dsw) ? EPI_BF16 : EPI_ANY;
+#define TB_TF32_LAUNCH(W)                                                                                              \
+        (epi == EPI_F32    ? launch_impl<W, true, false, EPI_F32>(ctx, a, p, tmA, tmB, tmC, tmR, stream)                 \
+         : epi == EPI_BF16 ? launch_impl<W, true, false, EPI_BF16>(ctx, a, p, tmA, tmB, tmC, tmR, stream)                \
+                           : launch_impl<W, true, false, EPI_ANY>(ctx, a, p, tmA, tmB, tmC, tmR, stream))
+        if (bn == 64)       TB_TRY(TB_TF32_LAUNCH(64));
+        else if (bn == 192) TB_TRY(TB_TF32_LAUNCH(192));
+        else                TB_TRY(TB_TF32_LAUNCH(128));
+#undef TB_TF32_LAUNCH
     } else {
         if (bn == 64)       TB_TRY((launch_bf16<64, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
         else if (bn == 192) TB_TRY((launch_bf16<192, false>(ctx, a, p, tmA, tmB, tmC, tmR, stream)));
