@@ -251,8 +251,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     mx = fmaxf(mx, e + 32 <= lim ? __uint_as_float(vb[e]) : -INFINITY);
                 }
             } else {
+                // four chains instead of one of 32 dependent maxima
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(va[e]), __uint_as_float(vb[e])));
+                for (int e = 0; e < 32; e += 4) {
+                    m0 = fmaxf(m0, fmaxf(__uint_as_float(va[e]), __uint_as_float(vb[e])));
+                    m1 = fmaxf(m1, fmaxf(__uint_as_float(va[e + 1]), __uint_as_float(vb[e + 1])));
+                    m2 = fmaxf(m2, fmaxf(__uint_as_float(va[e + 2]), __uint_as_float(vb[e + 2])));
+                    m3 = fmaxf(m3, fmaxf(__uint_as_float(va[e + 3]), __uint_as_float(vb[e + 3])));
+                }
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             }
             const float m_new = fmaxf(m, mx * p.scale_log2);
             const float alpha = fast_exp2(m - m_new);        // 0 on the first block (m = -inf)
