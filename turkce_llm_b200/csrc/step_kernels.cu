@@ -425,7 +425,14 @@ int launch_rmsnorm_bwd_dw(DeviceCtx* ctx, const float* x, const float* w, const 
         attr_set[ctx->device & 63] = true;
     }
     int blocks = (rows + warps - 1) / warps;
+    // Three quarters of the SMs, a warp walking several rows: in the training step this kernel runs beside a
+    // weight-gradient GEMM on the second stream, and a grid that fills every SM (one row per warp, 512 blocks) only
+    // takes that GEMM's SMs.  Measured on the benchmark step (148 SMs): 512 blocks 4.69 ms, 296 4.65, 148 4.62, 111 4.58,
+    // 74 4.63 -- although alone the kernel is fastest at 148 (16.6 us with its events against 18.1 at 111, 19.4 at 512).
+    static const int cap_env = getenv("TB_NORM_BLOCKS") ? atoi(getenv("TB_NORM_BLOCKS")) : 0;
+    const int cap = cap_env >= 16 ? cap_env : ctx->sm_count * 3 / 4;
     if (blocks > kNormBwdBlocks) blocks = kNormBwdBlocks;
+    if (blocks > cap) blocks = cap;
     float* partial = scratch + 64;
     const int pc = 2 * cols;
     prof_mark(ctx, "rmsnorm_bwd", 0.0, 0.0, st);
